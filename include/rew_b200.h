@@ -1,0 +1,188 @@
+/* rew_b200 — C ABI of the B200 (sm_100a) backend for Rechenwerk's (bitstormFA/rew)
+ * transformer-decoder inference path.
+ *
+ * Conventions
+ *   - Every function returns an int status: REWB200_OK (0) or REWB200_ERR.  After
+ *     an error rewb200_last_error() returns a thread-local message.  Nothing
+ *     throws or aborts across this boundary, and no call blocks without bound
+ *     (device-side waits are bounded and report through the status).
+ *   - Plain pointers and sizes only.  Host pointers are ordinary host memory
+ *     unless a parameter says "device".
+ *   - dtype codes are the ordinals of rew's DType enum (src/rew/dtype.nim:10-32).
+ *   - Tensors are dense row-major; weights of a Linear are [in, out] as in
+ *     src/rew/nn/linear.nim:21-25.
+ *   - A rew Nim binding stores a rewb200_buffer* in BufferHandle.raw
+ *     (src/rew/buffer.nim:42-65) and calls rewb200_buffer_release from the
+ *     BufferReleaser (src/rew/buffer.nim:33).
+ */
+#ifndef REW_B200_H
+#define REW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define REWB200_OK 0
+#define REWB200_ERR 1
+
+/* DType ordinals, src/rew/dtype.nim:10-32. */
+enum {
+  REWB200_BOOL = 0,
+  REWB200_I8 = 1,
+  REWB200_I16 = 2,
+  REWB200_I32 = 3,
+  REWB200_I64 = 4,
+  REWB200_U8 = 5,
+  REWB200_F16 = 9,
+  REWB200_BF16 = 10,
+  REWB200_F32 = 11,
+  REWB200_F64 = 12
+};
+
+typedef struct rewb200_buffer rewb200_buffer;
+typedef struct rewb200_model rewb200_model;
+typedef struct rewb200_session rewb200_session;
+
+/* ---- runtime ------------------------------------------------------------
+ * Replaces client creation in installEagerBackend (src/rew/eager.nim:1769-1772)
+ * and the PJRT client cache (src/rew/eager.nim:78-140).  `device_ordinals`
+ * lists the CUDA devices this process drives (slot i <-> ordinal i). */
+int rewb200_init(const int* device_ordinals, int n);
+int rewb200_shutdown(void);
+const char* rewb200_last_error(void);
+/* Waits for all queued work of a slot; fails after timeout_ms or when a kernel
+ * recorded a device-side status (bounded wait expired, bad index). */
+int rewb200_sync(int slot, int timeout_ms);
+/* Number of kernels this library has launched on the slot since init. */
+int64_t rewb200_launch_count(int slot);
+
+/* ---- device buffers -------------------------------------------------------
+ * transferToDevice / transferToHost (src/rew/eager.nim:229-247), fromHost /
+ * toHost (src/rew/eager.nim:360-377,558-595), BufferReleaser
+ * (src/rew/buffer.nim:33,69-82: nil-safe, idempotent per handle). */
+int rewb200_buffer_from_host(int slot, const void* src, int dtype, const int64_t* dims, int ndims,
+                             rewb200_buffer** out);
+int rewb200_buffer_alloc(int slot, int dtype, const int64_t* dims, int ndims, rewb200_buffer** out);
+int rewb200_buffer_to_host(const rewb200_buffer* buf, void* dst, size_t nbytes);
+int rewb200_buffer_info(const rewb200_buffer* buf, int* dtype, int64_t* dims, int* ndims);
+void* rewb200_buffer_device_ptr(const rewb200_buffer* buf);
+void rewb200_buffer_release(rewb200_buffer* buf);
+
+/* ---- Tier A: per-op eager dispatch ---------------------------------------
+ * The EagerBackend proc slot (src/rew/dispatch.nim:47-49,65-85) as a C call:
+ * op name, operand buffers, stringly-typed attributes in the wire format of
+ * src/rew/eager.nim:934-948 ("[1,2]" and "@[1, 2]" both accepted), one result.
+ * Ops: add sub mul divide neg exp sqrt rsqrt logistic maximum reshape transpose
+ * broadcastTo dotGeneral reduceSum reduceMax slice concat iota compare select
+ * astype topK. */
+int rewb200_dispatch(const char* op, rewb200_buffer* const* operands, int n_operands,
+                     const char* const* attr_keys, const char* const* attr_vals, int n_attrs,
+                     rewb200_buffer** out, int* n_out);
+
+/* ---- Tier B: fused layer entry points --------------------------------------
+ * Same argument meaning as the rew.nn forwards they stand behind. */
+
+/* Linear.forward, src/rew/nn/linear.nim:43-49.  x [N,in], w [in,out], b [out]
+ * (f32 when w is f32; f32 bias with bf16 x/w). y has x's dtype. */
+int rewb200_linear(const rewb200_buffer* x, const rewb200_buffer* w, const rewb200_buffer* b,
+                   rewb200_buffer** y);
+/* rmsNorm, src/rew/nn/norm.nim:204-224. */
+int rewb200_rmsnorm(const rewb200_buffer* x, const rewb200_buffer* gamma, float eps, rewb200_buffer** y);
+/* LayerNorm.forward, src/rew/nn/norm.nim:41-84 (last axis). */
+int rewb200_layernorm(const rewb200_buffer* x, const rewb200_buffer* gamma, const rewb200_buffer* beta,
+                      float eps, rewb200_buffer** y);
+/* initRotaryPositionEncoding tables, src/rew/nn/rope.nim:112-145: two f32
+ * buffers [max_seq, head_dim], computed on the host exactly as the reference. */
+int rewb200_rope_tables(int slot, int head_dim, int max_seq, double theta, rewb200_buffer** cos_out,
+                        rewb200_buffer** sin_out);
+/* RotaryPositionEncoding.forward, src/rew/nn/rope.nim:153-179.  x [...,S,hd]. */
+int rewb200_rope(const rewb200_buffer* x, const rewb200_buffer* cos_t, const rewb200_buffer* sin_t,
+                 int64_t offset, rewb200_buffer** y);
+/* scaledDotProductAttention with the GQA head expansion folded in
+ * (src/rew/nn/attention.nim:36-81, src/rew/nn/groupedqueryattention.nim:126-133).
+ * q [B,nh,S,hd], k,v [B,kvh,L,hd] -> [B,nh,S,hd].  mask_kind 0 = makeCausalMask
+ * as written (attention.nim:18-34), 1 = conventional causal. */
+int rewb200_gqa_attention(const rewb200_buffer* q, const rewb200_buffer* k, const rewb200_buffer* v,
+                          int causal, int mask_kind, rewb200_buffer** out);
+/* GatedFeedForward.forward, src/rew/nn/gated_ffn.nim:46-67.  x [N,d]. */
+int rewb200_swiglu_ffn(const rewb200_buffer* x, const rewb200_buffer* gate_w, const rewb200_buffer* gate_b,
+                       const rewb200_buffer* up_w, const rewb200_buffer* up_b, const rewb200_buffer* down_w,
+                       const rewb200_buffer* down_b, rewb200_buffer** y);
+/* Embedding.forward on token ids instead of one-hot rows
+ * (src/rew/nn/embedding.nim:39-62).  ids int32 [N] -> [N,d]. */
+int rewb200_embed_gather(const rewb200_buffer* ids, const rewb200_buffer* table, rewb200_buffer** y);
+/* Router of DeepSeekMoE.forward, src/rew/models/deepseek.nim:132-138:
+ * softmax over experts, top-k, renormalise.  x [N,d] f32/bf16, router_w [d,E],
+ * router_b [E] -> weights f32 [N,k], indices int32 [N,k]. */
+int rewb200_moe_route(const rewb200_buffer* x, const rewb200_buffer* router_w, const rewb200_buffer* router_b,
+                      int top_k, rewb200_buffer** weights, rewb200_buffer** indices);
+
+/* ---- model + generate ------------------------------------------------------
+ * LlamaForCausalLM / DeepSeekForCausalLM (src/rew/models/llama.nim:13-44,
+ * src/rew/models/deepseek.nim:20-63) as one object with fused device layouts. */
+typedef struct rewb200_config {
+  int32_t vocab, d_model, n_layers, n_heads, n_kv_heads, head_dim, ffn, max_seq;
+  double theta;
+  float eps;
+  int32_t norm_kind;    /* 0 rmsNorm math, 1 LayerNorm (what LlamaDecoderLayer calls) */
+  int32_t mask_kind;    /* 0 makeCausalMask as written, 1 conventional causal */
+  int32_t n_routed, n_shared, top_k, moe_ffn, first_dense; /* n_routed == 0: dense Llama block */
+  int32_t dtype;        /* REWB200_F32 or REWB200_BF16: weight/activation storage */
+  int32_t tp_rank, tp_size; /* tensor parallel shard of heads / FFN columns */
+  int32_t ep_rank, ep_size; /* expert parallel shard of routed experts */
+} rewb200_config;
+
+int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** out);
+void rewb200_model_free(rewb200_model* m);
+/* Number and canonical order of the logical tensors (see rew_b200/weights.py):
+ * embed; per layer ln1.gamma ln1.beta q.w q.b k.w k.b v.w v.b o.w o.b ln2.gamma
+ * ln2.beta then gate.w gate.b up.w up.b down.w down.b (dense) or router.w
+ * router.b + 6 per expert (shared first); norm.gamma norm.beta lm_head.w lm_head.b. */
+int64_t rewb200_model_tensor_count(const rewb200_model* m);
+/* Uploads logical tensor `index` from host f32 data of the FULL (unsharded)
+ * shape; the library slices for tp/ep rank, converts and fuses. */
+int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host, int64_t numel);
+/* Device-side N(0,std) weights, zero biases, unit gammas (synthetic benchmarks). */
+int rewb200_model_init_random(rewb200_model* m, uint64_t seed, float std);
+int rewb200_model_finalize(rewb200_model* m);
+int64_t rewb200_model_weight_bytes(const rewb200_model* m);
+
+/* A batch of sequences with a paged KV cache (KvCache, src/rew/nn/kv_cache.nim:13-77;
+ * PagedKvCache, src/rew/infer/generate.nim:63-88). */
+int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_session** out);
+void rewb200_session_free(rewb200_session* s);
+int rewb200_session_reset(rewb200_session* s);
+/* Feeds `S` new tokens per sequence (host int32 [batch,S]) at the current
+ * offset, appends K/V, returns greedy next ids (host int32 [batch]) and, when
+ * logits_out != NULL, the last-position logits (host f32 [batch,vocab]). */
+int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32_t* next_ids, float* logits_out);
+/* `n_steps` greedy decode steps entirely on the device starting from the ids
+ * the last forward produced; host out_ids [batch,n_steps]. */
+int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, float* last_logits);
+/* generate (src/rew/infer/generate.nim:231-265), greedy, batched: prompt host
+ * int32 [batch,S]; out_ids host int32 [batch,n_new]; stops early when eos >= 0
+ * and every sequence has produced it. last_logits optional [batch,vocab]. */
+int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
+                     float* last_logits);
+/* Device-time of the last forward / decode call in milliseconds (CUDA events). */
+int rewb200_session_last_ms(const rewb200_session* s, float* prefill_ms, float* decode_ms);
+/* Full no-cache forward, logits for every position, as LlamaForCausalLM.forward
+ * (src/rew/models/llama.nim:131-140): ids host [batch,S] -> logits host [batch,S,vocab]. */
+int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int64_t offset, int causal,
+                              float* logits_out);
+
+/* ---- tensor / expert parallel communication -------------------------------
+ * allReduce / allToAll (src/rew/ops/distributed.nim:62-83,106-128) executed
+ * with NCCL over NVLink; one process per GPU. */
+int rewb200_comm_unique_id(void* id128);                  /* 128 bytes, created on rank 0 */
+int rewb200_comm_init(int slot, const void* id128, int rank, int world);
+int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n);
+int rewb200_comm_destroy(int slot);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,284 @@
+"""Host-side mirror of the rew interfaces this backend stands behind.
+
+Names and argument meaning follow rew (Nim): Tensor/fromHost/toHost
+(src/rew/eager.nim:360-377,558-595), Linear (src/rew/nn/linear.nim), rmsNorm and
+LayerNorm (src/rew/nn/norm.nim), RotaryPositionEncoding (src/rew/nn/rope.nim),
+scaledDotProductAttention (src/rew/nn/attention.nim), GatedFeedForward
+(src/rew/nn/gated_ffn.nim), Embedding (src/rew/nn/embedding.nim), the causal-LM
+models (src/rew/models/llama.nim, deepseek.nim) and generate
+(src/rew/infer/generate.nim).  Everything here is a thin ctypes call into
+librew_b200.so; there is no Python or CPU implementation of any op.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import BF16, F32, I32, RewB200Error, check, lib
+from .weights import ModelConfig, from_bf16_bits, tensor_specs, to_bf16_bits
+
+_NP = {F32: np.float32, I32: np.int32, _lib.I64: np.int64, _lib.F64: np.float64, _lib.U8: np.uint8,
+       _lib.BOOL: np.bool_, _lib.I8: np.int8, _lib.I16: np.int16}
+
+
+class Tensor:
+    """Owning handle of one device buffer (rew's BufferHandle + Tensor metadata)."""
+
+    def __init__(self, handle):
+        self._h = C.c_void_p(handle) if not isinstance(handle, C.c_void_p) else handle
+        dt = C.c_int32()
+        nd = C.c_int32()
+        dims = (C.c_int64 * 8)()
+        check(lib().rewb200_buffer_info(self._h, C.byref(dt), dims, C.byref(nd)))
+        self.dtype = dt.value
+        self.shape = tuple(dims[i] for i in range(nd.value))
+
+    @staticmethod
+    def from_host(array, dtype=None, slot=0):
+        """fromHost: uploads a numpy array.  dtype=BF16 rounds f32 data to bf16 (RNE)."""
+        _lib.init()
+        a = np.ascontiguousarray(array)
+        if dtype is None:
+            dtype = {np.dtype(np.float32): F32, np.dtype(np.int32): I32, np.dtype(np.int64): _lib.I64,
+                     np.dtype(np.float64): _lib.F64}[a.dtype]
+        if dtype == BF16:
+            payload = to_bf16_bits(a.astype(np.float32))
+        else:
+            payload = np.ascontiguousarray(a.astype(_NP[dtype]))
+        dims = (C.c_int64 * max(1, a.ndim))(*a.shape)
+        out = C.c_void_p()
+        check(lib().rewb200_buffer_from_host(slot, payload.ctypes.data_as(C.c_void_p), dtype, dims, a.ndim, C.byref(out)))
+        return Tensor(out)
+
+    def to_host(self):
+        """toHost: bf16 buffers come back widened to float32."""
+        n = int(np.prod(self.shape)) if self.shape else 1
+        if self.dtype == BF16:
+            raw = np.empty(n, np.uint16)
+            check(lib().rewb200_buffer_to_host(self._h, raw.ctypes.data_as(C.c_void_p), raw.nbytes))
+            return from_bf16_bits(raw).reshape(self.shape)
+        raw = np.empty(n, _NP[self.dtype])
+        check(lib().rewb200_buffer_to_host(self._h, raw.ctypes.data_as(C.c_void_p), raw.nbytes))
+        return raw.reshape(self.shape)
+
+    def release(self):
+        if self._h is not None and self._h.value:
+            lib().rewb200_buffer_release(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+def _out():
+    return C.c_void_p()
+
+
+def _h(t):
+    return t._h if t is not None else None
+
+
+class Linear:
+    """y = x @ weight + bias, weight [in,out] (src/rew/nn/linear.nim:21-49)."""
+
+    def __init__(self, weight, bias):
+        self.weight, self.bias = weight, bias
+
+    def forward(self, x):
+        o = _out()
+        check(lib().rewb200_linear(_h(x), _h(self.weight), _h(self.bias), C.byref(o)))
+        return Tensor(o)
+
+
+def rmsNorm(x, gamma, eps=1e-5):
+    o = _out()
+    check(lib().rewb200_rmsnorm(_h(x), _h(gamma), eps, C.byref(o)))
+    return Tensor(o)
+
+
+class LayerNorm:
+    def __init__(self, gamma, beta, eps=1e-5):
+        self.gamma, self.beta, self.eps = gamma, beta, eps
+
+    def forward(self, x):
+        o = _out()
+        check(lib().rewb200_layernorm(_h(x), _h(self.gamma), _h(self.beta), self.eps, C.byref(o)))
+        return Tensor(o)
+
+
+class RotaryPositionEncoding:
+    """initRotaryPositionEncoding + forward (src/rew/nn/rope.nim:112-179)."""
+
+    def __init__(self, headDim, maxSeqLen=2048, theta=10000.0, slot=0):
+        _lib.init()
+        c, s = _out(), _out()
+        check(lib().rewb200_rope_tables(slot, headDim, maxSeqLen, float(theta), C.byref(c), C.byref(s)))
+        self.cosCached, self.sinCached = Tensor(c), Tensor(s)
+        self.headDim, self.maxSeqLen, self.theta = headDim, maxSeqLen, theta
+
+    def forward(self, x, offset=0):
+        o = _out()
+        check(lib().rewb200_rope(_h(x), _h(self.cosCached), _h(self.sinCached), offset, C.byref(o)))
+        return Tensor(o)
+
+
+def scaledDotProductAttention(q, k, v, causal=False, mask_kind=0):
+    """q [B,nh,S,hd]; k, v [B,kvh,L,hd] (kv heads are shared by nh/kvh query heads)."""
+    o = _out()
+    check(lib().rewb200_gqa_attention(_h(q), _h(k), _h(v), int(bool(causal)), mask_kind, C.byref(o)))
+    return Tensor(o)
+
+
+class GatedFeedForward:
+    def __init__(self, gateProj, upProj, downProj):
+        self.gateProj, self.upProj, self.downProj = gateProj, upProj, downProj
+
+    def forward(self, x):
+        o = _out()
+        check(lib().rewb200_swiglu_ffn(_h(x), _h(self.gateProj.weight), _h(self.gateProj.bias), _h(self.upProj.weight),
+                                       _h(self.upProj.bias), _h(self.downProj.weight), _h(self.downProj.bias), C.byref(o)))
+        return Tensor(o)
+
+
+class Embedding:
+    def __init__(self, weight):
+        self.weight = weight
+
+    def forward(self, ids):
+        o = _out()
+        check(lib().rewb200_embed_gather(_h(ids), _h(self.weight), C.byref(o)))
+        return Tensor(o)
+
+
+def moeRoute(x, router, top_k):
+    w, i = _out(), _out()
+    check(lib().rewb200_moe_route(_h(x), _h(router.weight), _h(router.bias), top_k, C.byref(w), C.byref(i)))
+    return Tensor(w), Tensor(i)
+
+
+def dispatch(op, operands, attrs=()):
+    """dispatchEager(op, operands, attrs) (src/rew/dispatch.nim:75-85)."""
+    n = len(operands)
+    arr = (C.c_void_p * max(1, n))(*[t._h for t in operands])
+    keys = (C.c_char_p * max(1, len(attrs)))(*[k.encode() for k, _ in attrs])
+    vals = (C.c_char_p * max(1, len(attrs)))(*[v.encode() for _, v in attrs])
+    outs = (C.c_void_p * 4)()
+    n_out = C.c_int32(4)
+    check(lib().rewb200_dispatch(op.encode(), arr, n, keys, vals, len(attrs), outs, C.byref(n_out)))
+    return [Tensor(C.c_void_p(outs[i])) for i in range(n_out.value)]
+
+
+class CausalLM:
+    """LlamaForCausalLM / DeepSeekForCausalLM on the device."""
+
+    def __init__(self, cfg: ModelConfig, slot=0):
+        _lib.init()
+        self.cfg = cfg
+        self._c = cfg.to_c()
+        h = C.c_void_p()
+        check(lib().rewb200_model_create(slot, C.byref(self._c), C.byref(h)))
+        self._h = h
+
+    def load(self, tensors):
+        """tensors: float32 arrays in canonical order (weights.tensor_specs)."""
+        specs = tensor_specs(self.cfg)
+        assert len(tensors) == len(specs) == lib().rewb200_model_tensor_count(self._h)
+        for i, (t, (name, shape)) in enumerate(zip(tensors, specs)):
+            a = np.ascontiguousarray(t, dtype=np.float32)
+            assert a.shape == tuple(shape), (name, a.shape, shape)
+            check(lib().rewb200_model_set_tensor(self._h, i, a.ctypes.data_as(_lib.F32P), a.size))
+        check(lib().rewb200_model_finalize(self._h))
+        return self
+
+    def init_random(self, seed=0, std=0.02):
+        check(lib().rewb200_model_init_random(self._h, seed, std))
+        check(lib().rewb200_model_finalize(self._h))
+        return self
+
+    def weight_bytes(self):
+        return lib().rewb200_model_weight_bytes(self._h)
+
+    def session(self, batch, max_len):
+        return Session(self, batch, max_len)
+
+    def free(self):
+        if self._h is not None:
+            lib().rewb200_model_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Session:
+    """A batch of sequences with its paged KV cache."""
+
+    def __init__(self, model, batch, max_len):
+        self.model, self.batch, self.max_len = model, batch, max_len
+        h = C.c_void_p()
+        check(lib().rewb200_session_create(model._h, batch, max_len, C.byref(h)))
+        self._h = h
+
+    def _ids(self, ids):
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        if a.ndim == 1:
+            a = a.reshape(1, -1)
+        assert a.shape[0] == self.batch, "ids must be [batch, S]"
+        return a
+
+    def forward(self, ids, want_logits=False):
+        a = self._ids(ids)
+        nxt = np.empty(self.batch, np.int32)
+        logits = np.empty((self.batch, self.model.cfg.vocab), np.float32) if want_logits else None
+        check(lib().rewb200_session_forward(self._h, a.ctypes.data_as(_lib.I32P), a.shape[1], nxt.ctypes.data_as(_lib.I32P),
+                                            logits.ctypes.data_as(_lib.F32P) if want_logits else None))
+        return (nxt, logits) if want_logits else nxt
+
+    def decode(self, n_steps, want_logits=False):
+        out = np.empty((self.batch, n_steps), np.int32)
+        logits = np.empty((self.batch, self.model.cfg.vocab), np.float32) if want_logits else None
+        check(lib().rewb200_session_decode(self._h, n_steps, out.ctypes.data_as(_lib.I32P),
+                                           logits.ctypes.data_as(_lib.F32P) if want_logits else None))
+        return (out, logits) if want_logits else out
+
+    def generate(self, prompt, max_new_tokens, eos=-1, want_logits=False):
+        """generate (src/rew/infer/generate.nim:231-265), greedy, batched."""
+        a = self._ids(prompt)
+        out = np.empty((self.batch, max_new_tokens), np.int32)
+        logits = np.empty((self.batch, self.model.cfg.vocab), np.float32) if want_logits else None
+        check(lib().rewb200_generate(self._h, a.ctypes.data_as(_lib.I32P), a.shape[1], max_new_tokens, eos,
+                                     out.ctypes.data_as(_lib.I32P), logits.ctypes.data_as(_lib.F32P) if want_logits else None))
+        return (out, logits) if want_logits else out
+
+    def forward_all(self, ids, offset=0, causal=True):
+        """Model.forward without a cache: logits for every position [batch,S,vocab]."""
+        a = self._ids(ids)
+        logits = np.empty((self.batch, a.shape[1], self.model.cfg.vocab), np.float32)
+        check(lib().rewb200_model_forward_all(self._h, a.ctypes.data_as(_lib.I32P), a.shape[1], offset, int(bool(causal)),
+                                              logits.ctypes.data_as(_lib.F32P)))
+        return logits
+
+    def reset(self):
+        check(lib().rewb200_session_reset(self._h))
+
+    def last_ms(self):
+        p, d = C.c_float(), C.c_float()
+        check(lib().rewb200_session_last_ms(self._h, C.byref(p), C.byref(d)))
+        return p.value, d.value
+
+    def free(self):
+        if self._h is not None:
+            lib().rewb200_session_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

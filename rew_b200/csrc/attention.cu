@@ -1,0 +1,630 @@
+// Grouped-query attention over a (paged or contiguous) KV cache.
+//
+// Restates scaledDotProductAttention (src/rew/nn/attention.nim:36-81) with the
+// GQA head expansion of src/rew/nn/groupedqueryattention.nim:126-133 folded into
+// indexing (query head h reads kv head h / group; nothing is materialised):
+//   scores = q.k ; scores *= 1/sqrt(hd) ; + mask ; softmax(max, exp, sum, div) ; @ v
+// mask_kind 0 is makeCausalMask exactly as written (attention.nim:18-34: key j is
+// visible to query i iff i <= j); mask_kind 1 is the conventional causal mask
+// for a query block that ends at the last key.
+//
+// Three kernels:
+//   attn_f32_kernel      any head_dim, f32, CUDA cores (the f32 parity path)
+//   attn_decode_kernel   bf16, one query token: split-KV flash-decode.  K/V tiles
+//                        of 64 tokens arrive by TMA (128-byte swizzle) in a
+//                        3-stage mbarrier ring; the kv head's query group forms
+//                        the M rows of mma.sync tiles so each K/V byte is read
+//                        once per group; softmax state lives in registers
+//                        (quad shuffles), warps and splits merge by log-sum-exp.
+//   attn_prefill_kernel  bf16, S > 1: flash-attention forward, 64 queries per CTA.
+#include <math.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace rewb {
+
+extern int64_t g_launch_total;
+
+namespace {
+
+constexpr int TILE = 64;  // tokens per K/V tile == tokens per cache page
+
+struct AttnDev {
+  const void* q;
+  int64_t q_sb, q_ss, q_sh;   // element strides of q: batch, position, head
+  void* out;
+  int64_t o_sb, o_ss, o_sh;
+  const void* k;
+  const void* v;
+  const int* pos0;
+  const int* block_table;
+  int max_pages;
+  int kvh, nh, group, S, hd;
+  int64_t kv_len_fixed;
+  int64_t contiguous_len;
+  int causal, mask_kind;
+  float scale;
+  float* part_o;    // [B][nh][nsplit][hd]
+  float* part_ml;   // [B][nh][nsplit][2]
+  int nsplit;
+  int* status;
+};
+
+__device__ __forceinline__ int kv_len_of(const AttnDev& a, int b) {
+  return a.kv_len_fixed >= 0 ? (int)a.kv_len_fixed : a.pos0[b] + a.S;
+}
+__device__ __forceinline__ bool visible(const AttnDev& a, int i, int j, int ctx) {
+  if (!a.causal) return true;
+  return a.mask_kind == 0 ? (i <= j) : (j <= i + ctx);
+}
+// Row index (in units of head_dim elements) of key j of kv head h of sequence b.
+__device__ __forceinline__ int64_t kv_row(const AttnDev& a, int b, int h, int j) {
+  if (a.block_table) {
+    const int page = a.block_table[(int64_t)b * a.max_pages + j / TILE];
+    return ((int64_t)page * a.kvh + h) * TILE + j % TILE;
+  }
+  return ((int64_t)b * a.kvh + h) * a.contiguous_len + j;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ------------------------------------------------------------------ f32
+// One CTA per (query i, head h, sequence b).  Dynamic smem: kv_len scores +
+// 128 floats of reduction space.
+__global__ void __launch_bounds__(128) attn_f32_kernel(AttnDev a) {
+  extern __shared__ float sm[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kv_len = kv_len_of(a, b), ctx = kv_len - a.S;
+  const int hd = a.hd, hk = h / a.group;
+  float* scores = sm;
+  float* red = sm + kv_len;
+  const float* q = reinterpret_cast<const float*>(a.q) + b * a.q_sb + i * a.q_ss + h * a.q_sh;
+  const float* K = reinterpret_cast<const float*>(a.k);
+  const float* V = reinterpret_cast<const float*>(a.v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+
+  for (int j = warp; j < kv_len; j += nw) {
+    const float* kr = K + kv_row(a, b, hk, j) * hd;
+    float d = 0.f;
+    for (int e = lane; e < hd; e += 32) d += q[e] * kr[e];
+    d = warp_sum(d);
+    if (lane == 0) {
+      float s = d * a.scale;
+      if (a.causal) s = s + (visible(a, i, j, ctx) ? 0.0f : -1e9f);
+      scores[j] = s;
+    }
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j < kv_len; j += blockDim.x) mx = fmaxf(mx, scores[j]);
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int w = 1; w < nw; ++w) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < kv_len; j += blockDim.x) {
+    const float e = expf(scores[j] - mx);
+    scores[j] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = 0.f;
+  for (int w = 0; w < nw; ++w) sum += red[w];
+  __syncthreads();
+  for (int j = threadIdx.x; j < kv_len; j += blockDim.x) scores[j] = scores[j] / sum;
+  __syncthreads();
+  // attn @ v: thread (grp, d) sums keys grp, grp+ngroups, ...
+  const int ngroups = max(1, (int)blockDim.x / hd);
+  float* outp = reinterpret_cast<float*>(a.out) + b * a.o_sb + i * a.o_ss + h * a.o_sh;
+  for (int d0 = 0; d0 < hd; d0 += blockDim.x) {
+    const int d = d0 + (threadIdx.x % min(hd, (int)blockDim.x));
+    const int grp = threadIdx.x / min(hd, (int)blockDim.x);
+    float acc = 0.f;
+    if (d < hd && grp < ngroups)
+      for (int j = grp; j < kv_len; j += ngroups) acc += scores[j] * V[kv_row(a, b, hk, j) * hd + d];
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    if (grp == 0 && d < hd) {
+      float t = 0.f;
+      for (int g2 = 0; g2 < ngroups; ++g2) t += red[g2 * min(hd, (int)blockDim.x) + (d - d0)];
+      outp[d] = t;
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------ bf16 shared pieces
+constexpr int ATT_STAGES = 3;
+
+template <int HD>
+struct ATile {
+  static constexpr int BOXES = HD / 64;
+  static constexpr int BOX_BYTES = TILE * 128;
+  static constexpr int KV_BYTES = BOXES * BOX_BYTES;  // one of K or V
+  static constexpr int STAGE_BYTES = 2 * KV_BYTES;
+  static constexpr int SMEM = ATT_STAGES * STAGE_BYTES + 1024 + 128;
+};
+
+// Issues the TMA loads of one 64-token K/V tile.
+template <int HD>
+__device__ __forceinline__ void load_tile(uint8_t* stage, uint64_t* bar, const CUtensorMap* tmK,
+                                          const CUtensorMap* tmV, int64_t row0) {
+  using T = ATile<HD>;
+  mbar_expect_tx(bar, T::STAGE_BYTES);
+#pragma unroll
+  for (int bx = 0; bx < T::BOXES; ++bx) {
+    tma_load_2d(stage + bx * T::BOX_BYTES, tmK, bar, bx * 64, (int)row0);
+    tma_load_2d(stage + T::KV_BYTES + bx * T::BOX_BYTES, tmV, bar, bx * 64, (int)row0);
+  }
+}
+
+__device__ __forceinline__ int64_t tile_row0(const AttnDev& a, int b, int hk, int tile) {
+  if (a.block_table) {
+    const int page = a.block_table[(int64_t)b * a.max_pages + tile];
+    return ((int64_t)page * a.kvh + hk) * TILE;
+  }
+  return ((int64_t)b * a.kvh + hk) * a.contiguous_len + (int64_t)tile * TILE;
+}
+
+template <int HD>
+__device__ __forceinline__ uint32_t kv_addr(uint32_t base, uint32_t row, uint32_t chunk) {
+  return base + (chunk >> 3) * ATile<HD>::BOX_BYTES + swz128(row, chunk & 7);
+}
+
+// ------------------------------------------------------------------ bf16 decode (S == 1)
+// grid (nsplit, kvh, B), 128 threads.  Warp w owns tokens 16w..16w+15 of every tile.
+template <int HD>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                          const __grid_constant__ CUtensorMap tmV, AttnDev a) {
+  using T = ATile<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + ATT_STAGES * T::STAGE_BYTES);
+
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3, l8 = lane & 7, lq = lane >> 3;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ATT_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    pdl_launch_dependents();
+  }
+  __syncthreads();
+  pdl_wait();
+
+  const int kv_len = kv_len_of(a, b);
+  const int ntiles = (kv_len + TILE - 1) / TILE;
+  const int tps = (ntiles + a.nsplit - 1) / a.nsplit;
+  const int t0 = split * tps, t1 = min(ntiles, t0 + tps);
+  const int nt_local = max(0, t1 - t0);
+
+  // Q fragments: rows = heads of this kv head's group (rows >= group are zero).
+  uint32_t qf[HD / 16][4];
+  {
+    const bf16* qb = reinterpret_cast<const bf16*>(a.q) + b * a.q_sb;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int row = g + (r & 1) * 8;
+        const int dim = kk * 16 + (r >> 1) * 8 + 2 * t;
+        uint32_t v = 0;
+        if (row < a.group) v = *reinterpret_cast<const uint32_t*>(qb + (hk * a.group + row) * a.q_sh + dim);
+        qf[kk][r] = v;
+      }
+  }
+
+  if (threadIdx.x == 0)
+    for (int i = 0; i < min(ATT_STAGES - 1, nt_local); ++i)
+      load_tile<HD>(smem + i * T::STAGE_BYTES, &full[i], &tmK, &tmV, tile_row0(a, b, hk, t0 + i));
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
+
+  const uint32_t smem_base = smem_u32(smem);
+  bool ok = true;
+  for (int it = 0; it < nt_local; ++it) {
+    const int s = it % ATT_STAGES;
+    if (threadIdx.x == 0 && it + ATT_STAGES - 1 < nt_local) {
+      const int nx = it + ATT_STAGES - 1;
+      load_tile<HD>(smem + (nx % ATT_STAGES) * T::STAGE_BYTES, &full[nx % ATT_STAGES], &tmK, &tmV,
+                    tile_row0(a, b, hk, t0 + nx));
+    }
+    ok = mbar_wait(&full[s], (it / ATT_STAGES) & 1, a.status);
+    if (!ok) break;
+    const uint32_t kb = smem_base + s * T::STAGE_BYTES;
+    const uint32_t vb = kb + T::KV_BYTES;
+
+    float sc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) sc[i][r] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+      uint32_t k0, k1, k2, k3;
+      ldmatrix_x4(k0, k1, k2, k3, kv_addr<HD>(kb, warp * 16 + (lq >> 1) * 8 + l8, kk * 2 + (lq & 1)));
+      mma_bf16_16816(sc[0], qf[kk], k0, k1);
+      mma_bf16_16816(sc[1], qf[kk], k2, k3);
+    }
+    const int jbase = (t0 + it) * TILE + warp * 16;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int j = jbase + nt * 8 + 2 * t + (r & 1);
+        sc[nt][r] = (j < kv_len) ? sc[nt][r] * a.scale : -INFINITY;
+      }
+    uint32_t pa[4];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      float mx = fmaxf(fmaxf(sc[0][2 * hf], sc[0][2 * hf + 1]), fmaxf(sc[1][2 * hf], sc[1][2 * hf + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[hf], mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = __expf(m_run[hf] - m_use);
+      const float p00 = __expf(sc[0][2 * hf] - m_use), p01 = __expf(sc[0][2 * hf + 1] - m_use);
+      const float p10 = __expf(sc[1][2 * hf] - m_use), p11 = __expf(sc[1][2 * hf + 1] - m_use);
+      l_run[hf] = l_run[hf] * alpha + (p00 + p01 + p10 + p11);
+      m_run[hf] = m_new;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[i][2 * hf] *= alpha;
+        o[i][2 * hf + 1] *= alpha;
+      }
+      pa[hf] = pack_bf16(p00, p01);
+      pa[2 + hf] = pack_bf16(p10, p11);
+    }
+#pragma unroll
+    for (int jp = 0; jp < HD / 16; ++jp) {
+      uint32_t v0, v1, v2, v3;
+      ldmatrix_x4_trans(v0, v1, v2, v3, kv_addr<HD>(vb, warp * 16 + (lq & 1) * 8 + l8, 2 * jp + (lq >> 1)));
+      mma_bf16_16816(o[2 * jp], pa, v0, v1);
+      mma_bf16_16816(o[2 * jp + 1], pa, v2, v3);
+    }
+    __syncthreads();  // everyone is done with stage s before it is refilled
+  }
+  if (!ok) return;
+
+  // ---- merge the four warps (log-sum-exp) through shared memory
+  __syncthreads();
+  float* sO = reinterpret_cast<float*>(smem);             // [4][16][HD]
+  float* sM = sO + 4 * 16 * HD;                           // [4][16]
+  float* sL = sM + 64;                                    // [4][16]
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    float l = l_run[hf];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = g + hf * 8;
+    if (t == 0) {
+      sM[warp * 16 + row] = m_run[hf];
+      sL[warp * 16 + row] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      float* dst = sO + ((warp * 16 + row) * HD) + i * 8 + 2 * t;
+      dst[0] = o[i][2 * hf];
+      dst[1] = o[i][2 * hf + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < a.group * HD; idx += blockDim.x) {
+    const int row = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w * 16 + row]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = __expf(sM[w * 16 + row] - Mu);
+      L += sL[w * 16 + row] * f;
+      acc += sO[(w * 16 + row) * HD + d] * f;
+    }
+    const int head = hk * a.group + row;
+    if (a.nsplit == 1) {
+      bf16* op = reinterpret_cast<bf16*>(a.out) + b * a.o_sb + head * a.o_sh;
+      op[d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const int64_t pi = ((int64_t)b * a.nh + head) * a.nsplit + split;
+      a.part_o[pi * HD + d] = acc;
+      if (d == 0) {
+        a.part_ml[pi * 2] = M;
+        a.part_ml[pi * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// grid (nh, B), HD threads: combine split partials.
+__global__ void attn_merge_kernel(AttnDev a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int64_t base = ((int64_t)b * a.nh + head) * a.nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, a.part_ml[(base + s) * 2]);
+  const float Mu = (M == -INFINITY) ? 0.f : M;
+  float L = 0.f, acc = 0.f;
+  for (int s = 0; s < a.nsplit; ++s) {
+    const float f = __expf(a.part_ml[(base + s) * 2] - Mu);
+    L += a.part_ml[(base + s) * 2 + 1] * f;
+    acc += a.part_o[(base + s) * a.hd + d] * f;
+  }
+  bf16* op = reinterpret_cast<bf16*>(a.out) + b * a.o_sb + head * a.o_sh;
+  op[d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+}
+
+// ------------------------------------------------------------------ bf16 prefill (S > 1)
+// grid (ceil(S/64), nh, B), 128 threads; warp w owns query rows 16w..16w+15 of the block.
+template <int HD>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                           const __grid_constant__ CUtensorMap tmV, AttnDev a) {
+  using T = ATile<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + ATT_STAGES * T::STAGE_BYTES);
+
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / a.group;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3, l8 = lane & 7, lq = lane >> 3;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ATT_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    pdl_launch_dependents();
+  }
+  __syncthreads();
+  pdl_wait();
+
+  const int kv_len = kv_len_of(a, b), ctx = kv_len - a.S;
+  const int ntiles = (kv_len + TILE - 1) / TILE;
+  int t_lo = 0, t_hi = ntiles;
+  if (a.causal) {
+    if (a.mask_kind == 0) t_lo = min(ntiles, (qb * 64) / TILE);
+    else t_hi = min(ntiles, (min(a.S - 1, qb * 64 + 63) + ctx) / TILE + 1);
+  }
+  const int nt_local = max(0, t_hi - t_lo);
+
+  const int i0 = qb * 64 + warp * 16;  // first query row of this warp
+  uint32_t qf[HD / 16][4];
+  {
+    const bf16* qbase = reinterpret_cast<const bf16*>(a.q) + b * a.q_sb + h * a.q_sh;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i = i0 + g + (r & 1) * 8;
+        const int dim = kk * 16 + (r >> 1) * 8 + 2 * t;
+        qf[kk][r] = (i < a.S) ? *reinterpret_cast<const uint32_t*>(qbase + i * a.q_ss + dim) : 0u;
+      }
+  }
+
+  if (threadIdx.x == 0)
+    for (int i = 0; i < min(ATT_STAGES - 1, nt_local); ++i)
+      load_tile<HD>(smem + i * T::STAGE_BYTES, &full[i], &tmK, &tmV, tile_row0(a, b, hk, t_lo + i));
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
+
+  const uint32_t smem_base = smem_u32(smem);
+  bool ok = true;
+  for (int it = 0; it < nt_local; ++it) {
+    const int s = it % ATT_STAGES;
+    if (threadIdx.x == 0 && it + ATT_STAGES - 1 < nt_local) {
+      const int nx = it + ATT_STAGES - 1;
+      load_tile<HD>(smem + (nx % ATT_STAGES) * T::STAGE_BYTES, &full[nx % ATT_STAGES], &tmK, &tmV,
+                    tile_row0(a, b, hk, t_lo + nx));
+    }
+    ok = mbar_wait(&full[s], (it / ATT_STAGES) & 1, a.status);
+    if (!ok) break;
+    const uint32_t kb = smem_base + s * T::STAGE_BYTES;
+    const uint32_t vb = kb + T::KV_BYTES;
+
+    float sc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) sc[i][r] = 0.f;
+#pragma unroll
+    for (int np = 0; np < 4; ++np)
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        uint32_t k0, k1, k2, k3;
+        ldmatrix_x4(k0, k1, k2, k3, kv_addr<HD>(kb, np * 16 + (lq >> 1) * 8 + l8, kk * 2 + (lq & 1)));
+        mma_bf16_16816(sc[2 * np], qf[kk], k0, k1);
+        mma_bf16_16816(sc[2 * np + 1], qf[kk], k2, k3);
+      }
+    const int jbase = (t_lo + it) * TILE;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int j = jbase + nt * 8 + 2 * t + (r & 1);
+        const int i = i0 + g + (r >> 1) * 8;
+        const bool vis = (j < kv_len) && visible(a, i, j, ctx);
+        sc[nt][r] = vis ? sc[nt][r] * a.scale : -INFINITY;
+      }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) mx = fmaxf(mx, fmaxf(sc[nt][2 * hf], sc[nt][2 * hf + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[hf], mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = __expf(m_run[hf] - m_use);
+      float ls = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        sc[nt][2 * hf] = __expf(sc[nt][2 * hf] - m_use);
+        sc[nt][2 * hf + 1] = __expf(sc[nt][2 * hf + 1] - m_use);
+        ls += sc[nt][2 * hf] + sc[nt][2 * hf + 1];
+      }
+      l_run[hf] = l_run[hf] * alpha + ls;
+      m_run[hf] = m_new;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[i][2 * hf] *= alpha;
+        o[i][2 * hf + 1] *= alpha;
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+      pa[1] = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
+      pa[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+      pa[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+      for (int jp = 0; jp < HD / 16; ++jp) {
+        uint32_t v0, v1, v2, v3;
+        ldmatrix_x4_trans(v0, v1, v2, v3, kv_addr<HD>(vb, ks * 16 + (lq & 1) * 8 + l8, 2 * jp + (lq >> 1)));
+        mma_bf16_16816(o[2 * jp], pa, v0, v1);
+        mma_bf16_16816(o[2 * jp + 1], pa, v2, v3);
+      }
+    }
+    __syncthreads();
+  }
+  if (!ok) return;
+
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    float l = l_run[hf];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int i = i0 + g + hf * 8;
+    if (i >= a.S) continue;
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    bf16* op = reinterpret_cast<bf16*>(a.out) + b * a.o_sb + i * a.o_ss + h * a.o_sh;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt)
+      *reinterpret_cast<uint32_t*>(op + nt * 8 + 2 * t) = pack_bf16(o[nt][2 * hf] * inv, o[nt][2 * hf + 1] * inv);
+  }
+}
+
+int decode_splits(Ctx* c, int64_t B, int kvh) {
+  const int64_t base = B * kvh;
+  if (base >= c->sm_count) return 1;
+  int64_t s = (2 * c->sm_count + base - 1) / base;
+  return (int)std::min<int64_t>(s, 16);
+}
+
+}  // namespace
+
+size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits) {
+  return (size_t)B * nh * max_splits * (hd + 2) * sizeof(float);
+}
+
+int attn_launch(Ctx* c, const AttnArgs& h) {
+  if (h.B == 0 || h.S == 0) return REWB200_OK;
+  AttnDev a;
+  a.q = h.q; a.q_sb = h.q_sb; a.q_ss = h.q_ss; a.q_sh = h.q_sh;
+  a.out = h.out; a.o_sb = h.o_sb; a.o_ss = h.o_ss; a.o_sh = h.o_sh;
+  a.k = h.kv.k; a.v = h.kv.v;
+  a.pos0 = h.pos0;
+  a.block_table = h.kv.block_table;
+  a.max_pages = h.kv.max_pages;
+  a.kvh = h.kv.kvh; a.nh = h.nh; a.group = h.nh / h.kv.kvh; a.S = h.S; a.hd = h.kv.hd;
+  a.kv_len_fixed = h.kv_len_fixed;
+  a.contiguous_len = h.kv.contiguous_len;
+  a.causal = h.causal; a.mask_kind = h.mask_kind;
+  a.scale = h.scale != 0.f ? h.scale : 1.0f / sqrtf((float)h.kv.hd);
+  a.part_o = nullptr; a.part_ml = nullptr; a.nsplit = 1;
+  a.status = c->d_status;
+  RB_REQUIRE(h.nh % h.kv.kvh == 0, "numHeads must be divisible by numKVHeads");
+  RB_REQUIRE(h.pos0 != nullptr || h.kv_len_fixed >= 0, "attention needs per-sequence positions or a fixed key length");
+  RB_REQUIRE(!h.kv.block_table || h.kv.page == TILE, "paged KV cache must use 64-token pages");
+
+  if (h.dtype == REWB200_F32) {
+    RB_REQUIRE(h.max_kv_len > 0, "f32 attention needs the maximum key length");
+    const size_t smem = ((size_t)h.max_kv_len + 128 + 32) * sizeof(float);
+    RB_REQUIRE(smem <= 200 * 1024, "f32 attention supports at most ~50k keys per sequence");
+    RB_REQUIRE(a.hd <= 128 || a.hd % 128 == 0, "f32 attention: head_dim above 128 must be a multiple of 128");
+    static size_t cur = 48 * 1024;
+    if (smem > cur) {
+      RB_CUDA(cudaFuncSetAttribute(attn_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      cur = smem;
+    }
+    RB_CUDA(launch_k(attn_f32_kernel, dim3((unsigned)h.S, (unsigned)h.nh, (unsigned)h.B), dim3(128), smem, c->stream,
+                     c->use_pdl, a));
+    ++g_launch_total;
+    return REWB200_OK;
+  }
+  RB_REQUIRE(h.dtype == REWB200_BF16, "attention supports f32 and bf16");
+  RB_REQUIRE(a.hd == 128 || a.hd == 64, "bf16 attention supports head_dim 64 and 128, got " + std::to_string(a.hd));
+  RB_REQUIRE(h.q_sh % 2 == 0 && h.q_sb % 2 == 0 && h.q_ss % 2 == 0, "bf16 attention: q strides must be even");
+  RB_REQUIRE(h.tmK != nullptr && h.tmV != nullptr, "bf16 attention needs K/V tensor maps");
+  static bool attrs = false;
+  if (!attrs) {
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATile<128>::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATile<64>::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATile<128>::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATile<64>::SMEM));
+    attrs = true;
+  }
+  if (h.S == 1) {
+    RB_REQUIRE(a.group <= 16, "bf16 decode attention supports query groups of at most 16 heads");
+    int nsplit = decode_splits(c, h.B, a.kvh);
+    if (nsplit > 1) {
+      const size_t need = attn_scratch_bytes(h.B, h.nh, a.hd, nsplit);
+      RB_REQUIRE(h.scratch != nullptr && h.scratch_bytes >= need, "attention scratch too small for split-KV decode");
+      a.part_o = h.scratch;
+      a.part_ml = h.scratch + (size_t)h.B * h.nh * nsplit * a.hd;
+    }
+    a.nsplit = nsplit;
+    dim3 grid((unsigned)nsplit, (unsigned)a.kvh, (unsigned)h.B);
+    if (a.hd == 128)
+      RB_CUDA(launch_k(attn_decode_kernel<128>, grid, dim3(128), (size_t)ATile<128>::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
+    else
+      RB_CUDA(launch_k(attn_decode_kernel<64>, grid, dim3(128), (size_t)ATile<64>::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
+    ++g_launch_total;
+    if (nsplit > 1) {
+      RB_CUDA(launch_k(attn_merge_kernel, dim3((unsigned)h.nh, (unsigned)h.B), dim3((unsigned)a.hd), 0, c->stream, c->use_pdl, a));
+      ++g_launch_total;
+    }
+    return REWB200_OK;
+  }
+  dim3 grid((unsigned)((h.S + 63) / 64), (unsigned)h.nh, (unsigned)h.B);
+  if (a.hd == 128)
+    RB_CUDA(launch_k(attn_prefill_kernel<128>, grid, dim3(128), (size_t)ATile<128>::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
+  else
+    RB_CUDA(launch_k(attn_prefill_kernel<64>, grid, dim3(128), (size_t)ATile<64>::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+}  // namespace rewb

@@ -1,0 +1,219 @@
+// Shared host-side declarations of the rew_b200 CUDA library: runtime context,
+// device buffers, error convention, and the launchers each .cu file exports to
+// the others.  Nothing here is part of the public C ABI (see include/rew_b200.h).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/rew_b200.h"
+
+namespace rewb {
+
+typedef __nv_bfloat16 bf16;
+
+// ---------------------------------------------------------------- errors
+void set_error(const std::string& msg);
+int fail(const std::string& msg);  // records msg, returns REWB200_ERR
+
+#define RB_CUDA(expr)                                                                          \
+  do {                                                                                         \
+    cudaError_t _e = (expr);                                                                   \
+    if (_e != cudaSuccess)                                                                     \
+      return ::rewb::fail(std::string(#expr) + ": " + cudaGetErrorString(_e) + " at " __FILE__ \
+                          ":" + std::to_string(__LINE__));                                     \
+  } while (0)
+#define RB_TRY(expr)            \
+  do {                          \
+    int _s = (expr);            \
+    if (_s != REWB200_OK) return _s; \
+  } while (0)
+#define RB_REQUIRE(cond, msg)                       \
+  do {                                              \
+    if (!(cond)) return ::rewb::fail(msg);          \
+  } while (0)
+
+// ---------------------------------------------------------------- context
+struct Ctx {
+  int device = -1;
+  cudaStream_t stream = nullptr;
+  int* d_status = nullptr;   // kernels record KernelStatus codes here
+  int* h_status = nullptr;   // pinned mirror
+  int sm_count = 0;
+  bool use_pdl = true;
+  void* pinned = nullptr;    // pinned host staging for H2D/D2H of buffers
+  size_t pinned_bytes = 0;
+};
+Ctx* ctx_get(int slot);       // nullptr + error when not initialised
+Ctx* ctx_current();           // slot 0
+int ctx_check_status(Ctx* c); // reads d_status after a sync; non-zero -> error
+
+size_t dtype_size(int dtype);
+
+// Encodes a 2D row-major bf16 tensor map: `inner` contiguous elements per row,
+// `outer` rows, `row_stride_bytes` between rows (multiple of 16), box =
+// box_inner x box_outer elements, 128-byte swizzle (box_inner must be 64).
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+// 3D variant (dim 2 = groups, e.g. experts) with box depth 1.
+int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer, uint64_t groups,
+                      uint64_t row_stride_bytes, uint64_t group_stride_bytes, uint32_t box_inner,
+                      uint32_t box_outer);
+
+// Launch helper that optionally attaches the programmatic-stream-serialization
+// attribute (the kernel then starts early and calls griddepcontrol.wait itself).
+extern int64_t g_launch_total;  // kernels launched by this library since load
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                     Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ---------------------------------------------------------------- buffers
+}  // namespace rewb
+
+// Opaque to C callers.  One contiguous row-major device allocation.
+struct rewb200_buffer {
+  int slot = 0;
+  int dtype = 0;
+  int ndims = 0;
+  int64_t dims[8] = {0};
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  bool owned = true;
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int i = 0; i < ndims; ++i) n *= dims[i];
+    return n;
+  }
+};
+
+namespace rewb {
+
+int buffer_new(Ctx* c, int dtype, const int64_t* dims, int ndims, rewb200_buffer** out);
+
+// ---------------------------------------------------------------- launchers
+enum Epilogue : int {
+  EPI_PARTIAL_F32 = 0,  // out_f32[split][row][col] = acc
+  EPI_BIAS_F32 = 1,     // out_f32[row][col] = acc + bias[col]
+  EPI_BIAS_BF16 = 2,    // out_bf16[row][col] = acc + bias[col]
+  EPI_SWIGLU_BF16 = 3,  // columns interleaved gate/up in groups of 8: out[row][col/2..] = silu(g+bg)*(u+bu)
+};
+
+struct LinearBf16Plan {
+  CUtensorMap tmW;       // W [K rows][N cols] bf16 (reference layout [in,out]); 3D when groups > 1
+  int64_t K = 0, N = 0;
+  int groups = 1;
+};
+// y = x @ W (+bias); x [M,K] bf16 row-major (ldx elements), W as planned.
+// ksplit > 1 requires EPI_PARTIAL_F32 (out holds ksplit slabs of M*N floats).
+// For grouped launches (plan.groups > 1) group g uses rows
+// [row_offsets[g], row_offsets[g+1]) of x/out (device array, groups+1 ints).
+int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi,
+                       int ksplit, void* out, int64_t ldo, const float* bias, const int* row_offsets, int max_rows_per_group);
+int linear_bf16_plan(LinearBf16Plan* plan, const bf16* W, int64_t K, int64_t N, int groups);
+int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N);
+
+// f32 path: C[M,N] = A[M,K] @ B[K,N] (+ bias[N]).
+int gemm_f32_launch(Ctx* c, const float* A, const float* B, const float* bias, float* C, int64_t M, int64_t K,
+                    int64_t N);
+
+struct NormArgs {
+  float* x_res;           // [rows,d] residual stream (in/out)
+  const float* partial;   // [nsplit][rows][d] or nullptr
+  int nsplit;
+  int64_t split_stride;   // elements between partial slabs
+  const float* bias;      // [d] or nullptr (added once)
+  const void* embed;      // embedding table [V,d] (model dtype) or nullptr
+  const int* ids;         // [rows] token ids when embed != nullptr
+  int embed_dtype;
+  const float* gamma;
+  const float* beta;
+  float eps;
+  int norm_kind;          // 0 rms, 1 layernorm, -1 none (only update x_res)
+  int64_t d;
+  void* out;              // normalised output, out_dtype
+  int out_dtype;
+  int vocab;
+  int* status;
+};
+int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows);
+
+struct KvLayout {
+  void* k;                // [n_pages][kvh][page][hd]
+  void* v;
+  const int* block_table; // [B][max_pages] page ids, or nullptr for contiguous [B][kvh][L][hd]
+  int max_pages;
+  int page;               // tokens per page (64)
+  int kvh, hd;
+  int64_t contiguous_len; // L when block_table == nullptr
+  int dtype;
+};
+
+struct QkvPostArgs {
+  const float* partial;   // [nsplit][rows][nq+2nkv] f32 (bias not yet added)
+  int nsplit;
+  int64_t split_stride;
+  const float* bias;      // [nq+2nkv]
+  const float* cosT;      // [max_seq][hd]
+  const float* sinT;
+  const int* pos0;        // [B] position of each sequence's first new token
+  int S;                  // new tokens per sequence (rows = B*S)
+  int rope_shift;         // RoPE table row = cache position + rope_shift (the reference's `offset`)
+  int kv_capacity;        // tokens the cache can hold per sequence
+  int nh, kvh, hd;
+  int max_seq;            // rows of the RoPE tables
+  void* q_out;            // [rows][nh][hd], act dtype
+  int act_dtype;
+  KvLayout kv;
+  int* status;
+};
+int qkv_post_launch(Ctx* c, const QkvPostArgs& a, int64_t B);
+
+struct AttnArgs {
+  const void* q;          // element strides below: batch, position, head (head_dim contiguous)
+  int64_t q_sb, q_ss, q_sh;
+  void* out;
+  int64_t o_sb, o_ss, o_sh;
+  KvLayout kv;
+  const int* pos0;        // [B] device: context length before these S queries, or nullptr
+  int64_t B;
+  int S;
+  int nh;
+  int causal;             // 0: every key visible
+  int mask_kind;          // 0 as written (key j visible to query i iff i <= j), 1 conventional causal
+  int64_t kv_len_fixed;   // >= 0: keys per sequence (used when pos0 == nullptr)
+  int64_t max_kv_len;     // upper bound of keys per sequence (sizes the f32 kernel's shared memory)
+  float scale;            // 0: 1/sqrt(head_dim)
+  int dtype;
+  float* scratch;         // split-KV partials (bf16 decode)
+  size_t scratch_bytes;
+  const CUtensorMap* tmK; // bf16: TMA maps over the K / V rows ([rows][head_dim], box 64x64)
+  const CUtensorMap* tmV;
+};
+int attn_launch(Ctx* c, const AttnArgs& a);
+size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits);
+
+int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out_ids);
+int swiglu_f32_launch(Ctx* c, const float* g, const float* u, float* out, int64_t n);
+int cast_launch(Ctx* c, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n);
+int fill_normal_launch(Ctx* c, void* dst, int dtype, int64_t n, uint64_t seed, float std);
+int fill_const_launch(Ctx* c, void* dst, int dtype, int64_t n, float v);
+int rope_tables_host(int hd, int max_seq, double theta, std::vector<float>* cosT, std::vector<float>* sinT);
+
+}  // namespace rewb

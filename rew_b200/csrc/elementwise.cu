@@ -1,0 +1,388 @@
+// Row-wise kernels between the GEMMs of a decoder block, each replacing a chain
+// of single-op dispatches in the reference:
+//   residual_norm  : split-K / tensor-parallel partial sum + bias + residual add
+//                    + rmsNorm (src/rew/nn/norm.nim:204-224) or LayerNorm
+//                    (src/rew/nn/norm.nim:41-84); or embedding row gather
+//                    (src/rew/nn/embedding.nim:39-62) + norm for the first layer.
+//   qkv_post       : partial sum + bias + interleaved-pair RoPE from the host
+//                    tables (src/rew/nn/rope.nim:56-108,153-179) + KV-cache append
+//                    (src/rew/nn/kv_cache.nim:47-77) written straight into pages.
+//   argmax         : sampleGreedy, first maximum (src/rew/infer/generate.nim:152-159).
+#include <math.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace rewb {
+
+int64_t g_launch_total = 0;
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sum over the block; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = (lane < nw) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_PER_THREAD = 64;  // d <= 16384
+
+template <typename TE, typename TO>
+__global__ void __launch_bounds__(NORM_THREADS) residual_norm_kernel(NormArgs a) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int64_t d = a.d;
+  float vals[NORM_MAX_PER_THREAD];
+  int cnt = 0;
+  float* xr = a.x_res + row * d;
+  const TE* erow = nullptr;
+  if (a.embed) {
+    int64_t id = row;  // without ids the table is read row by row (a plain typed input)
+    if (a.ids) {
+      id = a.ids[row];
+      if (id < 0 || id >= a.vocab) {
+        if (threadIdx.x == 0) atomicExch(a.status, KS_BAD_INDEX);
+        id = 0;
+      }
+    }
+    erow = reinterpret_cast<const TE*>(a.embed) + id * d;
+  }
+  for (int64_t i = threadIdx.x; i < d; i += NORM_THREADS, ++cnt) {
+    float v = erow ? to_f<TE>(erow[i]) : xr[i];  // x_res is required when there is no table
+    if (a.partial) {
+      float p = 0.f;
+      for (int s = 0; s < a.nsplit; ++s) p += a.partial[s * a.split_stride + row * d + i];
+      if (a.bias) p += a.bias[i];
+      v += p;
+    }
+    vals[cnt] = v;
+    if (a.x_res && (erow || a.partial)) xr[i] = v;
+  }
+  if (a.norm_kind < 0) return;
+  TO* orow = reinterpret_cast<TO*>(a.out) + row * d;
+  if (a.norm_kind == 0) {
+    float ss = 0.f;
+    for (int k = 0; k < cnt; ++k) ss += vals[k] * vals[k];
+    ss = block_sum(ss, red);
+    const float rms = sqrtf(ss / (float)d + a.eps);
+    cnt = 0;
+    for (int64_t i = threadIdx.x; i < d; i += NORM_THREADS, ++cnt)
+      orow[i] = from_f<TO>(a.gamma[i] * (vals[cnt] / rms));
+  } else {
+    float s1 = 0.f;
+    for (int k = 0; k < cnt; ++k) s1 += vals[k];
+    const float mean = block_sum(s1, red) / (float)d;
+    float s2 = 0.f;
+    for (int k = 0; k < cnt; ++k) {
+      const float c = vals[k] - mean;
+      s2 += c * c;
+    }
+    const float var = block_sum(s2, red) / (float)d;
+    const float inv = 1.0f / sqrtf(var + a.eps);
+    cnt = 0;
+    for (int64_t i = threadIdx.x; i < d; i += NORM_THREADS, ++cnt)
+      orow[i] = from_f<TO>(a.gamma[i] * ((vals[cnt] - mean) * inv) + a.beta[i]);
+  }
+}
+
+// One CTA per new token row.  Threads walk (head, pair) items of the fused
+// q|k|v row.
+template <typename TA>
+__global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int b = (int)(row / a.S), s = (int)(row % a.S);
+  const int pos = a.pos0[b] + s;
+  const int hd = a.hd, half = hd / 2;
+  const int nq = a.nh * hd, nkv = a.kvh * hd, ntot = nq + 2 * nkv;
+  const int rpos = pos + a.rope_shift;
+  if (pos < 0 || pos >= a.kv_capacity || rpos < 0 || rpos >= a.max_seq) {
+    if (threadIdx.x == 0) atomicExch(a.status, KS_BAD_INDEX);
+    return;
+  }
+  const float* cr = a.cosT + (int64_t)rpos * hd;
+  const float* sr = a.sinT + (int64_t)rpos * hd;
+  // destination rows of this token in the cache
+  int64_t cache_row_base;  // row index for kv head 0; kv head h adds h * stride
+  int64_t head_stride;
+  if (a.kv.block_table) {
+    const int page = a.kv.block_table[(int64_t)b * a.kv.max_pages + pos / a.kv.page];
+    cache_row_base = ((int64_t)page * a.kvh) * a.kv.page + pos % a.kv.page;
+    head_stride = a.kv.page;
+  } else {
+    cache_row_base = ((int64_t)b * a.kvh) * a.kv.contiguous_len + pos;
+    head_stride = a.kv.contiguous_len;
+  }
+  TA* q_out = reinterpret_cast<TA*>(a.q_out) + row * nq;
+  TA* kc = reinterpret_cast<TA*>(a.kv.k);
+  TA* vc = reinterpret_cast<TA*>(a.kv.v);
+  const int npairs = ntot / 2;
+  for (int p = threadIdx.x; p < npairs; p += blockDim.x) {
+    const int col = 2 * p;
+    float v0 = 0.f, v1 = 0.f;
+    for (int sp = 0; sp < a.nsplit; ++sp) {
+      const float2 t = *reinterpret_cast<const float2*>(a.partial + sp * a.split_stride + row * ntot + col);
+      v0 += t.x;
+      v1 += t.y;
+    }
+    if (a.bias) {
+      v0 += a.bias[col];
+      v1 += a.bias[col + 1];
+    }
+    if (col < nq + nkv) {
+      const int i = (col % hd) / 2;
+      const float c0 = cr[2 * i], s0 = sr[2 * i];
+      const float r0 = c0 * v0 - s0 * v1;
+      const float r1 = s0 * v0 + c0 * v1;
+      if (col < nq) {
+        q_out[col] = from_f<TA>(r0);
+        q_out[col + 1] = from_f<TA>(r1);
+      } else {
+        const int h = (col - nq) / hd, e = (col - nq) % hd;
+        TA* dst = kc + (cache_row_base + h * head_stride) * hd + e;
+        dst[0] = from_f<TA>(r0);
+        dst[1] = from_f<TA>(r1);
+      }
+    } else {
+      const int h = (col - nq - nkv) / hd, e = (col - nq - nkv) % hd;
+      TA* dst = vc + (cache_row_base + h * head_stride) * hd + e;
+      dst[0] = from_f<TA>(v0);
+      dst[1] = from_f<TA>(v1);
+    }
+  }
+  (void)half;
+}
+
+// First maximum of each row.  One CTA per row.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t V, int* out) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* r = logits + (int64_t)blockIdx.x * V;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = r[i];
+    if (v > best || (v == best && (int)i < bi)) {
+      best = v;
+      bi = (int)i;
+    }
+  }
+  // NaN-free inputs assumed, as in the reference's host loop (a NaN never wins a '>' test).
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+  }
+}
+
+__global__ void swiglu_f32_kernel(const float* g, const float* u, float* out, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  // src/rew/nn/activation.nim:28-38: x * (1 / (1 + exp(-x)))
+  const float x = g[i];
+  const float sig = 1.0f / (1.0f + expf(-x));
+  out[i] = (x * sig) * u[i];
+}
+
+template <typename TS, typename TD>
+__global__ void cast_kernel(const TS* src, TD* dst, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = from_f<TD>(to_f<TS>(src[i]));
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+// Counter-based N(0,std): Box-Muller on two hashed uniforms per element pair.
+template <typename T>
+__global__ void fill_normal_kernel(T* dst, int64_t n, uint64_t seed, float std) {
+  const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t i = 2 * p;
+  if (i >= n) return;
+  const uint64_t h = splitmix64(seed ^ splitmix64((uint64_t)p));
+  const float u1 = ((uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777217.0f);
+  const float u2 = (uint32_t)((h >> 8) & 0xFFFFFF) * (1.0f / 16777216.0f);
+  const float r = sqrtf(-2.0f * logf(u1)) * std;
+  float s, c;
+  sincospif(2.0f * u2, &s, &c);
+  dst[i] = from_f<T>(r * c);
+  if (i + 1 < n) dst[i + 1] = from_f<T>(r * s);
+}
+
+template <typename T>
+__global__ void fill_const_kernel(T* dst, int64_t n, float v) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = from_f<T>(v);
+}
+
+}  // namespace
+
+int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows) {
+  if (rows == 0) return REWB200_OK;
+  RB_REQUIRE(a.d <= (int64_t)NORM_THREADS * NORM_MAX_PER_THREAD, "norm width above 16384 is not supported");
+  const bool e16 = a.embed_dtype == REWB200_BF16, o16 = a.out_dtype == REWB200_BF16;
+  cudaError_t e;
+  dim3 grid((unsigned)rows), block(NORM_THREADS);
+  if (e16 && o16) e = launch_k(residual_norm_kernel<bf16, bf16>, grid, block, 0, c->stream, c->use_pdl, a);
+  else if (e16) e = launch_k(residual_norm_kernel<bf16, float>, grid, block, 0, c->stream, c->use_pdl, a);
+  else if (o16) e = launch_k(residual_norm_kernel<float, bf16>, grid, block, 0, c->stream, c->use_pdl, a);
+  else e = launch_k(residual_norm_kernel<float, float>, grid, block, 0, c->stream, c->use_pdl, a);
+  RB_CUDA(e);
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int qkv_post_launch(Ctx* c, const QkvPostArgs& a, int64_t B) {
+  const int64_t rows = B * a.S;
+  if (rows == 0) return REWB200_OK;
+  RB_REQUIRE(a.hd % 2 == 0, "head_dim must be even for RoPE");
+  cudaError_t e;
+  if (a.act_dtype == REWB200_BF16)
+    e = launch_k(qkv_post_kernel<bf16>, dim3((unsigned)rows), dim3(256), 0, c->stream, c->use_pdl, a);
+  else
+    e = launch_k(qkv_post_kernel<float>, dim3((unsigned)rows), dim3(256), 0, c->stream, c->use_pdl, a);
+  RB_CUDA(e);
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out_ids) {
+  if (rows == 0) return REWB200_OK;
+  RB_CUDA(launch_k(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, c->stream, c->use_pdl, logits, V, out_ids));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int swiglu_f32_launch(Ctx* c, const float* g, const float* u, float* out, int64_t n) {
+  if (n == 0) return REWB200_OK;
+  swiglu_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(g, u, out, n);
+  RB_CUDA(cudaGetLastError());
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int cast_launch(Ctx* c, const void* src, int sd, void* dst, int dd, int64_t n) {
+  if (n == 0) return REWB200_OK;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (sd == REWB200_F32 && dd == REWB200_BF16)
+    cast_kernel<float, bf16><<<blocks, 256, 0, c->stream>>>((const float*)src, (bf16*)dst, n);
+  else if (sd == REWB200_BF16 && dd == REWB200_F32)
+    cast_kernel<bf16, float><<<blocks, 256, 0, c->stream>>>((const bf16*)src, (float*)dst, n);
+  else if (sd == REWB200_F32 && dd == REWB200_F32)
+    cast_kernel<float, float><<<blocks, 256, 0, c->stream>>>((const float*)src, (float*)dst, n);
+  else if (sd == REWB200_BF16 && dd == REWB200_BF16)
+    cast_kernel<bf16, bf16><<<blocks, 256, 0, c->stream>>>((const bf16*)src, (bf16*)dst, n);
+  else
+    return fail("cast: only f32 and bf16 are supported");
+  RB_CUDA(cudaGetLastError());
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int fill_normal_launch(Ctx* c, void* dst, int dtype, int64_t n, uint64_t seed, float std) {
+  if (n == 0) return REWB200_OK;
+  const int64_t pairs = (n + 1) / 2;
+  const unsigned blocks = (unsigned)((pairs + 255) / 256);
+  if (dtype == REWB200_BF16) fill_normal_kernel<bf16><<<blocks, 256, 0, c->stream>>>((bf16*)dst, n, seed, std);
+  else if (dtype == REWB200_F32) fill_normal_kernel<float><<<blocks, 256, 0, c->stream>>>((float*)dst, n, seed, std);
+  else return fail("fill_normal: only f32 and bf16 are supported");
+  RB_CUDA(cudaGetLastError());
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int fill_const_launch(Ctx* c, void* dst, int dtype, int64_t n, float v) {
+  if (n == 0) return REWB200_OK;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == REWB200_BF16) fill_const_kernel<bf16><<<blocks, 256, 0, c->stream>>>((bf16*)dst, n, v);
+  else if (dtype == REWB200_F32) fill_const_kernel<float><<<blocks, 256, 0, c->stream>>>((float*)dst, n, v);
+  else return fail("fill_const: only f32 and bf16 are supported");
+  RB_CUDA(cudaGetLastError());
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+// src/rew/nn/rope.nim:123-138, computed on the host as the reference does
+// (double pow, float angle, float cos/sin, each value stored twice).
+int rope_tables_host(int hd, int max_seq, double theta, std::vector<float>* cosT, std::vector<float>* sinT) {
+  RB_REQUIRE(hd > 0 && hd % 2 == 0, "initRotaryPositionEncoding: headDim must be positive and even, got " + std::to_string(hd));
+  RB_REQUIRE(max_seq > 0, "initRotaryPositionEncoding: maxSeqLen must be positive");
+  const int half = hd / 2;
+  std::vector<float> inv(half);
+  for (int i = 0; i < half; ++i) inv[i] = 1.0f / (float)pow(theta, (double)(2 * i) / (double)hd);
+  cosT->resize((size_t)max_seq * hd);
+  sinT->resize((size_t)max_seq * hd);
+  for (int p = 0; p < max_seq; ++p) {
+    const float fp = (float)p;
+    for (int i = 0; i < half; ++i) {
+      const float angle = fp * inv[i];
+      const float cv = cosf(angle), sv = sinf(angle);
+      const size_t base = (size_t)p * hd + 2 * i;
+      (*cosT)[base] = cv;
+      (*cosT)[base + 1] = cv;
+      (*sinT)[base] = sv;
+      (*sinT)[base + 1] = sv;
+    }
+  }
+  return REWB200_OK;
+}
+
+}  // namespace rewb

@@ -1,0 +1,880 @@
+// Model + session engine: LlamaForCausalLM / DeepSeekForCausalLM
+// (src/rew/models/llama.nim:106-140, src/rew/models/deepseek.nim:198-231) with a
+// paged KV cache (src/rew/nn/kv_cache.nim, src/rew/infer/generate.nim:63-88) and
+// the generate loop (src/rew/infer/generate.nim:231-265) driven on the device.
+//
+// Device layouts (chosen for B200, not the reference's per-tensor buffers):
+//   - q|k|v projection weights concatenated along `out` into one [d, nq+2nkv]
+//     matrix so one GEMM streams them; gate|up concatenated the same way, with
+//     the bf16 variant interleaving gate/up columns in groups of 8 so the GEMM
+//     epilogue can apply SiLU(gate)*up in registers.
+//   - The residual stream stays f32; GEMM inputs are the model dtype.
+//   - Row-parallel outputs (o-proj, down-proj) are written as f32 split-K
+//     partials and summed by the residual+norm kernel, which is also where a
+//     tensor-parallel all-reduce result lands.
+//   - KV cache pages of 64 tokens: [page][kv_head][64][head_dim].
+//   - One decode step (batch fixed, positions read from device memory) is
+//     captured once into a CUDA graph and replayed; token ids, positions and
+//     the step counter live on the device, so a run of n steps needs no host
+//     round trip until the ids are copied back.
+#include <algorithm>
+#include <cstring>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+using namespace rewb;
+
+namespace rewb {
+
+namespace {
+
+constexpr int PAGE = 64;
+
+struct LinW {
+  void* w = nullptr;   // [K,N] model dtype
+  float* b = nullptr;  // [N]
+  int64_t K = 0, N = 0;
+  LinearBf16Plan plan;
+};
+
+struct LayerDev {
+  float *ln1g = nullptr, *ln1b = nullptr, *ln2g = nullptr, *ln2b = nullptr;
+  LinW qkv, o, gu, down;
+  int64_t ffn_local = 0;
+  bool moe = false;
+};
+
+__global__ void scatter_cols_f32_kernel(const float* src, int64_t src_ld, int64_t row0, int64_t col0, int64_t rows,
+                                        int64_t cols, void* dst, int dst_bf16, int64_t ldd, int64_t gran,
+                                        int64_t gstride, int64_t off) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * cols) return;
+  const int64_t r = i / cols, c = i % cols;
+  const float v = src[(row0 + r) * src_ld + col0 + c];
+  const int64_t dc = (c / gran) * gstride + (c % gran) + off;
+  if (dst_bf16) reinterpret_cast<bf16*>(dst)[r * ldd + dc] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(dst)[r * ldd + dc] = v;
+}
+
+// f32 path: out[r][c] = silu(gu[r][c]) * gu[r][f + c]   (src/rew/nn/gated_ffn.nim:55-59)
+__global__ void swiglu_rows_f32_kernel(const float* gu, float* out, int64_t rows, int64_t f) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * f) return;
+  const int64_t r = i / f, c = i % f;
+  const float x = gu[r * 2 * f + c];
+  const float sig = 1.0f / (1.0f + expf(-x));
+  out[i] = (x * sig) * gu[r * 2 * f + f + c];
+}
+
+// End of a step: publish the sampled ids, make them the next step's input,
+// advance positions and the step counter.
+__global__ void advance_kernel(const int* next, int* ids, int* pos, int* out_ids, int* step, int B, int S,
+                               int max_steps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int st = *step;
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    ids[b] = next[b];
+    pos[b] += S;
+    if (out_ids && st < max_steps) out_ids[(int64_t)st * B + b] = next[b];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *step = st + 1;
+}
+
+}  // namespace
+}  // namespace rewb
+
+struct rewb200_model {
+  Ctx* c = nullptr;
+  rewb200_config cfg;
+  int nh_l = 0, kvh_l = 0;      // local heads under tensor parallelism
+  int64_t nq = 0, nkv = 0, nqkv = 0;
+  void* embed = nullptr;
+  std::vector<LayerDev> layers;
+  float *ng = nullptr, *nb = nullptr;
+  LinW lm;
+  float *cosT = nullptr, *sinT = nullptr;
+  float* stage = nullptr;       // f32 upload staging
+  size_t stage_bytes = 0;
+  bool finalized = false;
+  int64_t weight_bytes = 0;
+  std::vector<void*> allocs;
+};
+
+struct rewb200_session {
+  rewb200_model* m = nullptr;
+  int B = 0, max_len = 0, max_pages = 0;
+  std::vector<void*> kc, vc;           // per layer
+  std::vector<CUtensorMap> tmK, tmV;   // per layer (bf16)
+  int* block_table = nullptr;
+  int *d_pos = nullptr, *d_ids = nullptr, *d_next = nullptr, *d_out = nullptr, *d_step = nullptr;
+  int out_capacity = 0;
+  int32_t* h_ids = nullptr;            // pinned
+  // activations, sized for `rows_cap` rows
+  int64_t rows_cap = 0;
+  float* x_res = nullptr;
+  void* xn = nullptr;
+  void* q = nullptr;
+  void* attn = nullptr;
+  void* h = nullptr;
+  float* part = nullptr;               // split-K partials (largest user)
+  size_t part_bytes = 0;
+  float* gu32 = nullptr;               // f32 path: gate|up GEMM output
+  float* logits = nullptr;             // [B or rows][V]
+  int64_t logits_rows = 0;
+  float* attn_scratch = nullptr;
+  size_t attn_scratch_bytes = 0;
+  cudaGraphExec_t graph = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float prefill_ms = 0.f, decode_ms = 0.f;
+  int host_pos = 0;                    // tokens so far (all sequences advance together)
+};
+
+namespace rewb {
+namespace {
+
+int dev_alloc(rewb200_model* m, void** p, size_t bytes) {
+  RB_CUDA(cudaMalloc(p, std::max<size_t>(bytes, 256)));
+  m->allocs.push_back(*p);
+  m->weight_bytes += (int64_t)bytes;
+  return REWB200_OK;
+}
+
+bool layer_is_moe(const rewb200_config& c, int l) { return c.n_routed > 0 && !(c.first_dense > 0 && l == 0); }
+
+int alloc_lin(rewb200_model* m, LinW* w, int64_t K, int64_t N) {
+  w->K = K;
+  w->N = N;
+  RB_TRY(dev_alloc(m, &w->w, (size_t)K * N * dtype_size(m->cfg.dtype)));
+  RB_TRY(dev_alloc(m, (void**)&w->b, (size_t)N * sizeof(float)));
+  RB_CUDA(cudaMemsetAsync(w->b, 0, (size_t)N * sizeof(float), m->c->stream));
+  return REWB200_OK;
+}
+
+// Tensor index -> (layer, slot).  Slots follow the canonical order in the header.
+struct TensorRef {
+  int layer;  // -1: embed, -2: final
+  int slot;
+};
+int locate(const rewb200_model* m, int64_t index, TensorRef* out) {
+  const rewb200_config& c = m->cfg;
+  if (index == 0) {
+    *out = {-1, 0};
+    return REWB200_OK;
+  }
+  int64_t i = 1;
+  for (int l = 0; l < c.n_layers; ++l) {
+    const int64_t n = 12 + (layer_is_moe(c, l) ? 2 + 6 * (int64_t)(c.n_shared + c.n_routed) : 6);
+    if (index < i + n) {
+      *out = {l, (int)(index - i)};
+      return REWB200_OK;
+    }
+    i += n;
+  }
+  if (index < i + 4) {
+    *out = {-2, (int)(index - i)};
+    return REWB200_OK;
+  }
+  return fail("tensor index " + std::to_string(index) + " out of range");
+}
+
+int upload_stage(rewb200_model* m, const float* host, int64_t numel) {
+  Ctx* c = m->c;
+  const size_t bytes = (size_t)numel * sizeof(float);
+  if (bytes > m->stage_bytes) {
+    if (m->stage) RB_CUDA(cudaFree(m->stage));
+    RB_CUDA(cudaMalloc((void**)&m->stage, bytes));
+    m->stage_bytes = bytes;
+  }
+  size_t off = 0;
+  while (off < bytes) {
+    const size_t n = std::min(c->pinned_bytes, bytes - off);
+    memcpy(c->pinned, (const char*)host + off, n);
+    RB_CUDA(cudaMemcpyAsync((char*)m->stage + off, c->pinned, n, cudaMemcpyHostToDevice, c->stream));
+    RB_CUDA(cudaStreamSynchronize(c->stream));
+    off += n;
+  }
+  return REWB200_OK;
+}
+
+// Copies a [rows, cols] window of the staged f32 tensor into a device matrix
+// with column mapping dst_col = (c / gran) * gstride + c % gran + off.
+int scatter(rewb200_model* m, int64_t src_ld, int64_t row0, int64_t col0, int64_t rows, int64_t cols, void* dst,
+            bool dst_model_dtype, int64_t ldd, int64_t gran, int64_t gstride, int64_t off) {
+  const int64_t n = rows * cols;
+  if (n == 0) return REWB200_OK;
+  const int bf = (dst_model_dtype && m->cfg.dtype == REWB200_BF16) ? 1 : 0;
+  scatter_cols_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, m->c->stream>>>(m->stage, src_ld, row0, col0, rows, cols,
+                                                                                dst, bf, ldd, gran, gstride, off);
+  RB_CUDA(cudaGetLastError());
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
+  rewb200_model* m = s->m;
+  const rewb200_config& c = m->cfg;
+  const size_t es = dtype_size(c.dtype);
+  if (rows > s->rows_cap) {
+    RB_CUDA(cudaStreamSynchronize(m->c->stream));
+    void** ptrs[] = {(void**)&s->x_res, &s->xn, &s->q, &s->attn, &s->h, (void**)&s->part, (void**)&s->gu32};
+    for (void** p : ptrs)
+      if (*p) {
+        RB_CUDA(cudaFree(*p));
+        *p = nullptr;
+      }
+    int64_t fmax = 0;
+    for (const LayerDev& L : m->layers) fmax = std::max(fmax, L.ffn_local);
+    RB_CUDA(cudaMalloc((void**)&s->x_res, (size_t)rows * c.d_model * sizeof(float)));
+    RB_CUDA(cudaMalloc(&s->xn, (size_t)rows * c.d_model * es));
+    RB_CUDA(cudaMalloc(&s->q, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
+    RB_CUDA(cudaMalloc(&s->attn, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
+    RB_CUDA(cudaMalloc(&s->h, (size_t)rows * std::max<int64_t>(fmax, 1) * es));
+    const int64_t widest = std::max<int64_t>(m->nqkv, c.d_model);
+    s->part_bytes = (size_t)rows * widest * sizeof(float) * 16;  // up to 16 split-K slabs at decode sizes
+    if (rows > 32) s->part_bytes = (size_t)rows * widest * sizeof(float);
+    RB_CUDA(cudaMalloc((void**)&s->part, s->part_bytes));
+    if (c.dtype == REWB200_F32) RB_CUDA(cudaMalloc((void**)&s->gu32, (size_t)rows * 2 * std::max<int64_t>(fmax, 1) * sizeof(float)));
+    s->rows_cap = rows;
+    if (s->graph) {
+      cudaGraphExecDestroy(s->graph);
+      s->graph = nullptr;
+    }
+  }
+  if (logits_rows > s->logits_rows) {
+    RB_CUDA(cudaStreamSynchronize(m->c->stream));
+    if (s->logits) RB_CUDA(cudaFree(s->logits));
+    RB_CUDA(cudaMalloc((void**)&s->logits, (size_t)logits_rows * c.vocab * sizeof(float)));
+    s->logits_rows = logits_rows;
+    if (s->graph) {
+      cudaGraphExecDestroy(s->graph);
+      s->graph = nullptr;
+    }
+  }
+  return REWB200_OK;
+}
+
+// y = x @ W for the model dtype.  `partial` selects the f32 split-K slab
+// output (bias deferred to the consumer) over a finished output with bias.
+int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, int64_t rows, bool partial, int epi,
+               void* out, int64_t ldo, int* ksplit_out) {
+  Ctx* c = s->m->c;
+  if (s->m->cfg.dtype == REWB200_BF16) {
+    int ks = 1;
+    if (partial) {
+      ks = linear_bf16_pick_ksplit(c, rows, w.K, w.N);
+      while (ks > 1 && (size_t)ks * rows * ldo * sizeof(float) > s->part_bytes) ks /= 2;
+    }
+    if (ksplit_out) *ksplit_out = ks;
+    return linear_bf16_launch(c, w.plan, (const bf16*)x, ldx, rows, partial ? EPI_PARTIAL_F32 : epi, ks, out, ldo,
+                              partial ? nullptr : w.b, nullptr, 0);
+  }
+  if (ksplit_out) *ksplit_out = 1;
+  RB_REQUIRE(ldx == w.K && ldo == w.N, "f32 Linear expects dense rows");
+  return gemm_f32_launch(c, (const float*)x, (const float*)w.w, partial ? nullptr : w.b, (float*)out, rows, w.K, w.N);
+}
+
+struct FwdOpts {
+  int S = 1;
+  int rope_shift = 0;
+  int causal = 1;
+  bool all_logits = false;  // lm_head on every row instead of the last position
+  bool from_device_ids = false;
+};
+
+// Enqueues one forward over rows = B*S tokens whose ids are in s->d_ids.
+int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  const rewb200_config& cf = m->cfg;
+  const int64_t rows = (int64_t)s->B * o.S;
+  const int64_t d = cf.d_model;
+  const int dt = cf.dtype;
+
+  NormArgs na;
+  memset(&na, 0, sizeof(na));
+  na.x_res = s->x_res;
+  na.d = d;
+  na.eps = cf.eps;
+  na.norm_kind = cf.norm_kind;
+  na.out = s->xn;
+  na.out_dtype = dt;
+  na.vocab = cf.vocab;
+  na.status = c->d_status;
+  na.embed_dtype = dt;
+
+  // embedding gather + first norm
+  {
+    NormArgs a = na;
+    a.embed = m->embed;
+    a.ids = s->d_ids;
+    a.gamma = m->layers[0].ln1g;
+    a.beta = m->layers[0].ln1b;
+    RB_TRY(residual_norm_launch(c, a, rows));
+  }
+  for (int l = 0; l < cf.n_layers; ++l) {
+    LayerDev& L = m->layers[l];
+    int ks = 1;
+    RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks));
+    QkvPostArgs qa;
+    memset(&qa, 0, sizeof(qa));
+    qa.partial = s->part;
+    qa.nsplit = ks;
+    qa.split_stride = rows * m->nqkv;
+    qa.bias = L.qkv.b;
+    qa.cosT = m->cosT;
+    qa.sinT = m->sinT;
+    qa.pos0 = s->d_pos;
+    qa.S = o.S;
+    qa.rope_shift = o.rope_shift;
+    qa.nh = m->nh_l;
+    qa.kvh = m->kvh_l;
+    qa.hd = cf.head_dim;
+    qa.max_seq = cf.max_seq;
+    qa.q_out = s->q;
+    qa.act_dtype = dt;
+    qa.kv.k = s->kc[l];
+    qa.kv.v = s->vc[l];
+    qa.kv.block_table = s->block_table;
+    qa.kv.max_pages = s->max_pages;
+    qa.kv.page = PAGE;
+    qa.kv.kvh = m->kvh_l;
+    qa.kv.hd = cf.head_dim;
+    qa.kv.dtype = dt;
+    qa.kv_capacity = s->max_len;
+    qa.status = c->d_status;
+    RB_TRY(qkv_post_launch(c, qa, s->B));
+
+    AttnArgs aa;
+    memset(&aa, 0, sizeof(aa));
+    aa.q = s->q;
+    aa.q_sb = (int64_t)o.S * m->nq;
+    aa.q_ss = m->nq;
+    aa.q_sh = cf.head_dim;
+    aa.out = s->attn;
+    aa.o_sb = aa.q_sb;
+    aa.o_ss = aa.q_ss;
+    aa.o_sh = aa.q_sh;
+    aa.kv = qa.kv;
+    aa.pos0 = s->d_pos;
+    aa.B = s->B;
+    aa.S = o.S;
+    aa.nh = m->nh_l;
+    aa.causal = o.causal;
+    aa.mask_kind = cf.mask_kind;
+    aa.kv_len_fixed = -1;
+    aa.max_kv_len = s->max_len;
+    aa.scale = 0.f;
+    aa.dtype = dt;
+    aa.scratch = s->attn_scratch;
+    aa.scratch_bytes = s->attn_scratch_bytes;
+    if (dt == REWB200_BF16) {
+      aa.tmK = &s->tmK[l];
+      aa.tmV = &s->tmV[l];
+    }
+    RB_TRY(attn_launch(c, aa));
+
+    RB_TRY(run_linear(s, L.o, s->attn, m->nq, rows, true, 0, s->part, d, &ks));
+    // TODO(tp): all-reduce of the partial slab goes here.
+    {
+      NormArgs a = na;
+      a.partial = s->part;
+      a.nsplit = ks;
+      a.split_stride = rows * d;
+      a.bias = L.o.b;
+      a.gamma = L.ln2g;
+      a.beta = L.ln2b;
+      RB_TRY(residual_norm_launch(c, a, rows));
+    }
+    if (dt == REWB200_BF16) {
+      RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr));
+    } else {
+      RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_BIAS_F32, s->gu32, 2 * L.ffn_local, nullptr));
+      const int64_t n = rows * L.ffn_local;
+      swiglu_rows_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(s->gu32, (float*)s->h, rows, L.ffn_local);
+      RB_CUDA(cudaGetLastError());
+      ++g_launch_total;
+    }
+    RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
+    {
+      NormArgs a = na;
+      a.partial = s->part;
+      a.nsplit = ks;
+      a.split_stride = rows * d;
+      a.bias = L.down.b;
+      const bool last = (l + 1 == cf.n_layers);
+      a.gamma = last ? m->ng : m->layers[l + 1].ln1g;
+      a.beta = last ? m->nb : m->layers[l + 1].ln1b;
+      RB_TRY(residual_norm_launch(c, a, rows));
+    }
+  }
+  // lm_head: last position of every sequence (generate.nim:172-190) or every row.
+  const int64_t lrows = o.all_logits ? rows : s->B;
+  const char* xl = (const char*)s->xn + (o.all_logits ? 0 : (size_t)(o.S - 1) * d * dtype_size(dt));
+  const int64_t ldx = o.all_logits ? d : (int64_t)o.S * d;
+  if (dt == REWB200_BF16) {
+    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)xl, ldx, lrows, EPI_BIAS_F32, 1, s->logits, cf.vocab, m->lm.b,
+                              nullptr, 0));
+  } else {
+    if (o.all_logits || o.S == 1) {
+      RB_TRY(gemm_f32_launch(c, (const float*)xl, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, cf.vocab));
+    } else {
+      // gather the last rows into the head of q (free at this point), then GEMM
+      for (int b = 0; b < s->B; ++b)
+        RB_CUDA(cudaMemcpyAsync((float*)s->q + (size_t)b * d, (const float*)s->xn + ((size_t)b * o.S + o.S - 1) * d,
+                                d * sizeof(float), cudaMemcpyDeviceToDevice, c->stream));
+      RB_TRY(gemm_f32_launch(c, (const float*)s->q, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, cf.vocab));
+    }
+  }
+  if (!o.all_logits) {
+    RB_TRY(argmax_launch(c, s->logits, s->B, cf.vocab, s->d_next));
+    RB_CUDA(launch_k(advance_kernel, dim3(1), dim3(256), 0, c->stream, c->use_pdl,
+                     (const int*)s->d_next, s->d_ids, s->d_pos, s->d_out, s->d_step, s->B, o.S, s->out_capacity));
+    ++g_launch_total;
+  }
+  return REWB200_OK;
+}
+
+}  // namespace
+}  // namespace rewb
+
+extern "C" {
+
+int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** out) {
+  Ctx* c = ctx_get(slot);
+  if (!c) return REWB200_ERR;
+  RB_REQUIRE(cfg && out, "rewb200_model_create: NULL argument");
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_REQUIRE(cfg->dtype == REWB200_F32 || cfg->dtype == REWB200_BF16, "model dtype must be f32 or bf16");
+  RB_REQUIRE(cfg->vocab > 0 && cfg->d_model > 0 && cfg->n_layers > 0 && cfg->head_dim > 0 && cfg->max_seq > 0,
+             "model dimensions must be positive");
+  RB_REQUIRE(cfg->n_kv_heads > 0 && cfg->n_heads % cfg->n_kv_heads == 0,
+             "initGroupedQueryAttention: numHeads " + std::to_string(cfg->n_heads) + " must be divisible by numKVHeads " +
+                 std::to_string(cfg->n_kv_heads));
+  RB_REQUIRE(cfg->head_dim % 2 == 0, "initRotaryPositionEncoding: headDim must be positive and even, got " +
+                                         std::to_string(cfg->head_dim));
+  const int tp = std::max(1, cfg->tp_size);
+  RB_REQUIRE(cfg->tp_rank >= 0 && cfg->tp_rank < tp, "tp_rank out of range");
+  RB_REQUIRE(cfg->n_heads % tp == 0 && cfg->n_kv_heads % tp == 0 && cfg->ffn % tp == 0,
+             "shardLayout: heads, kv heads and FFN width must be divisible by the tensor-parallel size");
+  RB_REQUIRE(cfg->n_routed == 0, "MoE models are created through this entry only after rewb200 MoE support is built in");
+  rewb200_model* m = new rewb200_model();
+  m->c = c;
+  m->cfg = *cfg;
+  m->cfg.tp_size = tp;
+  m->nh_l = cfg->n_heads / tp;
+  m->kvh_l = cfg->n_kv_heads / tp;
+  m->nq = (int64_t)m->nh_l * cfg->head_dim;
+  m->nkv = (int64_t)m->kvh_l * cfg->head_dim;
+  m->nqkv = m->nq + 2 * m->nkv;
+  const int64_t d = cfg->d_model;
+  if (cfg->dtype == REWB200_BF16)
+    RB_REQUIRE(d % 8 == 0 && m->nqkv % 8 == 0 && (cfg->ffn / tp) % 8 == 0 && cfg->vocab % 8 == 0 &&
+                   (cfg->head_dim == 64 || cfg->head_dim == 128),
+               "bf16 models need d_model, ffn/tp, vocab multiples of 8 and head_dim 64 or 128");
+  const size_t es = dtype_size(cfg->dtype);
+  RB_TRY(dev_alloc(m, &m->embed, (size_t)cfg->vocab * d * es));
+  m->layers.resize(cfg->n_layers);
+  auto alloc_vec = [&](float** p, float v) -> int {
+    RB_TRY(dev_alloc(m, (void**)p, d * sizeof(float)));
+    return fill_const_launch(c, *p, REWB200_F32, d, v);
+  };
+  for (int l = 0; l < cfg->n_layers; ++l) {
+    LayerDev& L = m->layers[l];
+    RB_TRY(alloc_vec(&L.ln1g, 1.f));
+    RB_TRY(alloc_vec(&L.ln1b, 0.f));
+    RB_TRY(alloc_vec(&L.ln2g, 1.f));
+    RB_TRY(alloc_vec(&L.ln2b, 0.f));
+    L.ffn_local = cfg->ffn / tp;
+    RB_TRY(alloc_lin(m, &L.qkv, d, m->nqkv));
+    RB_TRY(alloc_lin(m, &L.o, m->nq, d));
+    RB_TRY(alloc_lin(m, &L.gu, d, 2 * L.ffn_local));
+    RB_TRY(alloc_lin(m, &L.down, L.ffn_local, d));
+  }
+  RB_TRY(alloc_vec(&m->ng, 1.f));
+  RB_TRY(alloc_vec(&m->nb, 0.f));
+  RB_TRY(alloc_lin(m, &m->lm, d, cfg->vocab));
+  std::vector<float> ct, st;
+  RB_TRY(rope_tables_host(cfg->head_dim, cfg->max_seq, cfg->theta, &ct, &st));
+  RB_TRY(dev_alloc(m, (void**)&m->cosT, ct.size() * sizeof(float)));
+  RB_TRY(dev_alloc(m, (void**)&m->sinT, st.size() * sizeof(float)));
+  RB_CUDA(cudaMemcpyAsync(m->cosT, ct.data(), ct.size() * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  RB_CUDA(cudaMemcpyAsync(m->sinT, st.data(), st.size() * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  *out = m;
+  return REWB200_OK;
+}
+
+void rewb200_model_free(rewb200_model* m) {
+  if (!m) return;
+  cudaSetDevice(m->c->device);
+  cudaStreamSynchronize(m->c->stream);
+  for (void* p : m->allocs) cudaFree(p);
+  if (m->stage) cudaFree(m->stage);
+  delete m;
+}
+
+int64_t rewb200_model_tensor_count(const rewb200_model* m) {
+  if (!m) return 0;
+  int64_t n = 1;
+  for (int l = 0; l < m->cfg.n_layers; ++l)
+    n += 12 + (layer_is_moe(m->cfg, l) ? 2 + 6 * (int64_t)(m->cfg.n_shared + m->cfg.n_routed) : 6);
+  return n + 4;
+}
+
+int64_t rewb200_model_weight_bytes(const rewb200_model* m) { return m ? m->weight_bytes : 0; }
+
+int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host, int64_t numel) {
+  RB_REQUIRE(m && host, "rewb200_model_set_tensor: NULL argument");
+  RB_REQUIRE(!m->finalized, "model already finalized");
+  RB_CUDA(cudaSetDevice(m->c->device));
+  const rewb200_config& c = m->cfg;
+  TensorRef r;
+  RB_TRY(locate(m, index, &r));
+  const int64_t d = c.d_model, hd = c.head_dim;
+  const int64_t NQ = (int64_t)c.n_heads * hd, NKV = (int64_t)c.n_kv_heads * hd, F = c.ffn;
+  const int tp = c.tp_size, rk = c.tp_rank;
+  const bool bf = c.dtype == REWB200_BF16;
+  auto expect = [&](int64_t n) -> int {
+    RB_REQUIRE(numel == n, "tensor " + std::to_string(index) + ": expected " + std::to_string(n) + " elements, got " +
+                               std::to_string(numel));
+    return upload_stage(m, host, numel);
+  };
+  auto vec = [&](float* dst, int64_t n_full, int64_t off, int64_t n) -> int {
+    RB_TRY(expect(n_full));
+    return scatter(m, n_full, 0, off, 1, n, dst, false, n, n, n, 0);
+  };
+  if (r.layer == -1) {
+    RB_TRY(expect((int64_t)c.vocab * d));
+    return scatter(m, d, 0, 0, c.vocab, d, m->embed, true, d, d, d, 0);
+  }
+  if (r.layer == -2) {
+    switch (r.slot) {
+      case 0: return vec(m->ng, d, 0, d);
+      case 1: return vec(m->nb, d, 0, d);
+      case 2: RB_TRY(expect(d * c.vocab)); return scatter(m, c.vocab, 0, 0, d, c.vocab, m->lm.w, true, c.vocab, c.vocab, c.vocab, 0);
+      default: return vec(m->lm.b, c.vocab, 0, c.vocab);
+    }
+  }
+  LayerDev& L = m->layers[r.layer];
+  const int64_t nq = m->nq, nkv = m->nkv, nqkv = m->nqkv, fl = L.ffn_local;
+  // gate/up column mapping: bf16 interleaves groups of 8 (gate at +0, up at +8 of each 16); f32 concatenates.
+  const int64_t ggran = bf ? 8 : fl, gstride = bf ? 16 : fl;
+  switch (r.slot) {
+    case 0: return vec(L.ln1g, d, 0, d);
+    case 1: return vec(L.ln1b, d, 0, d);
+    case 2: RB_TRY(expect(d * NQ)); return scatter(m, NQ, 0, rk * nq, d, nq, L.qkv.w, true, nqkv, nq, nq, 0);
+    case 3: RB_TRY(expect(NQ)); return scatter(m, NQ, 0, rk * nq, 1, nq, L.qkv.b, false, nqkv, nq, nq, 0);
+    case 4: RB_TRY(expect(d * NKV)); return scatter(m, NKV, 0, rk * nkv, d, nkv, L.qkv.w, true, nqkv, nkv, nkv, nq);
+    case 5: RB_TRY(expect(NKV)); return scatter(m, NKV, 0, rk * nkv, 1, nkv, L.qkv.b, false, nqkv, nkv, nkv, nq);
+    case 6: RB_TRY(expect(d * NKV)); return scatter(m, NKV, 0, rk * nkv, d, nkv, L.qkv.w, true, nqkv, nkv, nkv, nq + nkv);
+    case 7: RB_TRY(expect(NKV)); return scatter(m, NKV, 0, rk * nkv, 1, nkv, L.qkv.b, false, nqkv, nkv, nkv, nq + nkv);
+    case 8: RB_TRY(expect(NQ * d)); return scatter(m, d, rk * nq, 0, nq, d, L.o.w, true, d, d, d, 0);
+    case 9: return vec(L.o.b, d, 0, d);
+    case 10: return vec(L.ln2g, d, 0, d);
+    case 11: return vec(L.ln2b, d, 0, d);
+    case 12: RB_TRY(expect(d * F)); return scatter(m, F, 0, rk * fl, d, fl, L.gu.w, true, 2 * fl, ggran, gstride, 0);
+    case 13: RB_TRY(expect(F)); return scatter(m, F, 0, rk * fl, 1, fl, L.gu.b, false, 2 * fl, ggran, gstride, 0);
+    case 14: RB_TRY(expect(d * F)); return scatter(m, F, 0, rk * fl, d, fl, L.gu.w, true, 2 * fl, ggran, gstride, bf ? 8 : fl);
+    case 15: RB_TRY(expect(F)); return scatter(m, F, 0, rk * fl, 1, fl, L.gu.b, false, 2 * fl, ggran, gstride, bf ? 8 : fl);
+    case 16: RB_TRY(expect(F * d)); return scatter(m, d, rk * fl, 0, fl, d, L.down.w, true, d, d, d, 0);
+    case 17: return vec(L.down.b, d, 0, d);
+    default: (void)tp; return fail("tensor slot not supported for this layer kind");
+  }
+}
+
+int rewb200_model_init_random(rewb200_model* m, uint64_t seed, float std) {
+  RB_REQUIRE(m, "rewb200_model_init_random: NULL model");
+  RB_REQUIRE(!m->finalized, "model already finalized");
+  RB_CUDA(cudaSetDevice(m->c->device));
+  Ctx* c = m->c;
+  const int dt = m->cfg.dtype;
+  uint64_t k = seed * 1000003ull;
+  RB_TRY(fill_normal_launch(c, m->embed, dt, (int64_t)m->cfg.vocab * m->cfg.d_model, ++k, std));
+  for (LayerDev& L : m->layers) {
+    RB_TRY(fill_normal_launch(c, L.qkv.w, dt, L.qkv.K * L.qkv.N, ++k, std));
+    RB_TRY(fill_normal_launch(c, L.o.w, dt, L.o.K * L.o.N, ++k, std));
+    RB_TRY(fill_normal_launch(c, L.gu.w, dt, L.gu.K * L.gu.N, ++k, std));
+    RB_TRY(fill_normal_launch(c, L.down.w, dt, L.down.K * L.down.N, ++k, std));
+  }
+  RB_TRY(fill_normal_launch(c, m->lm.w, dt, m->lm.K * m->lm.N, ++k, std));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  return REWB200_OK;
+}
+
+int rewb200_model_finalize(rewb200_model* m) {
+  RB_REQUIRE(m, "rewb200_model_finalize: NULL model");
+  if (m->finalized) return REWB200_OK;
+  RB_CUDA(cudaSetDevice(m->c->device));
+  if (m->cfg.dtype == REWB200_BF16) {
+    for (LayerDev& L : m->layers) {
+      RB_TRY(linear_bf16_plan(&L.qkv.plan, (const bf16*)L.qkv.w, L.qkv.K, L.qkv.N, 1));
+      RB_TRY(linear_bf16_plan(&L.o.plan, (const bf16*)L.o.w, L.o.K, L.o.N, 1));
+      RB_TRY(linear_bf16_plan(&L.gu.plan, (const bf16*)L.gu.w, L.gu.K, L.gu.N, 1));
+      RB_TRY(linear_bf16_plan(&L.down.plan, (const bf16*)L.down.w, L.down.K, L.down.N, 1));
+    }
+    RB_TRY(linear_bf16_plan(&m->lm.plan, (const bf16*)m->lm.w, m->lm.K, m->lm.N, 1));
+  }
+  if (m->stage) {
+    RB_CUDA(cudaStreamSynchronize(m->c->stream));
+    RB_CUDA(cudaFree(m->stage));
+    m->stage = nullptr;
+    m->stage_bytes = 0;
+  }
+  RB_CUDA(cudaStreamSynchronize(m->c->stream));
+  m->finalized = true;
+  return REWB200_OK;
+}
+
+int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_session** out) {
+  RB_REQUIRE(m && out, "rewb200_session_create: NULL argument");
+  RB_REQUIRE(m->finalized, "rewb200_session_create: call rewb200_model_finalize first");
+  RB_REQUIRE(batch > 0 && max_len > 0, "initKvCache: batch and maxLen must be positive");
+  RB_REQUIRE(max_len <= m->cfg.max_seq, "KvCache maxLen " + std::to_string(max_len) + " exceeds maxSeqLen " +
+                                            std::to_string(m->cfg.max_seq) + " of the RoPE tables");
+  Ctx* c = m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  rewb200_session* s = new rewb200_session();
+  s->m = m;
+  s->B = batch;
+  s->max_len = max_len;
+  s->max_pages = (max_len + PAGE - 1) / PAGE;
+  const int64_t n_pages = (int64_t)batch * s->max_pages;
+  const size_t es = dtype_size(m->cfg.dtype);
+  const int64_t cache_rows = n_pages * m->kvh_l * PAGE;
+  const size_t cache_bytes = (size_t)cache_rows * m->cfg.head_dim * es;
+  s->kc.resize(m->cfg.n_layers);
+  s->vc.resize(m->cfg.n_layers);
+  s->tmK.resize(m->cfg.n_layers);
+  s->tmV.resize(m->cfg.n_layers);
+  for (int l = 0; l < m->cfg.n_layers; ++l) {
+    RB_CUDA(cudaMalloc(&s->kc[l], cache_bytes));
+    RB_CUDA(cudaMalloc(&s->vc[l], cache_bytes));
+    RB_CUDA(cudaMemsetAsync(s->kc[l], 0, cache_bytes, c->stream));
+    RB_CUDA(cudaMemsetAsync(s->vc[l], 0, cache_bytes, c->stream));
+    if (m->cfg.dtype == REWB200_BF16) {
+      RB_TRY(make_tmap_2d_bf16(&s->tmK[l], s->kc[l], m->cfg.head_dim, cache_rows, (uint64_t)m->cfg.head_dim * 2, 64, 64));
+      RB_TRY(make_tmap_2d_bf16(&s->tmV[l], s->vc[l], m->cfg.head_dim, cache_rows, (uint64_t)m->cfg.head_dim * 2, 64, 64));
+    }
+  }
+  std::vector<int> bt((size_t)n_pages);
+  for (int64_t i = 0; i < n_pages; ++i) bt[i] = (int)i;  // sequence b owns pages [b*max_pages, (b+1)*max_pages)
+  RB_CUDA(cudaMalloc((void**)&s->block_table, n_pages * sizeof(int)));
+  RB_CUDA(cudaMemcpyAsync(s->block_table, bt.data(), n_pages * sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  RB_CUDA(cudaMalloc((void**)&s->d_pos, batch * sizeof(int)));
+  RB_CUDA(cudaMalloc((void**)&s->d_next, batch * sizeof(int)));
+  RB_CUDA(cudaMalloc((void**)&s->d_step, sizeof(int)));
+  RB_CUDA(cudaMalloc((void**)&s->d_ids, (size_t)batch * max_len * sizeof(int)));
+  s->out_capacity = max_len;
+  RB_CUDA(cudaMalloc((void**)&s->d_out, (size_t)batch * s->out_capacity * sizeof(int)));
+  RB_CUDA(cudaMallocHost((void**)&s->h_ids, (size_t)batch * max_len * sizeof(int)));
+  RB_CUDA(cudaMemsetAsync(s->d_pos, 0, batch * sizeof(int), c->stream));
+  RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
+  s->attn_scratch_bytes = attn_scratch_bytes(batch, m->nh_l, m->cfg.head_dim, 16);
+  RB_CUDA(cudaMalloc((void**)&s->attn_scratch, s->attn_scratch_bytes));
+  RB_CUDA(cudaEventCreate(&s->ev0));
+  RB_CUDA(cudaEventCreate(&s->ev1));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  *out = s;
+  return REWB200_OK;
+}
+
+void rewb200_session_free(rewb200_session* s) {
+  if (!s) return;
+  Ctx* c = s->m->c;
+  cudaSetDevice(c->device);
+  cudaStreamSynchronize(c->stream);
+  if (s->graph) cudaGraphExecDestroy(s->graph);
+  for (void* p : s->kc) cudaFree(p);
+  for (void* p : s->vc) cudaFree(p);
+  void* ptrs[] = {s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
+                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch};
+  for (void* p : ptrs)
+    if (p) cudaFree(p);
+  if (s->h_ids) cudaFreeHost(s->h_ids);
+  if (s->ev0) cudaEventDestroy(s->ev0);
+  if (s->ev1) cudaEventDestroy(s->ev1);
+  delete s;
+}
+
+int rewb200_session_reset(rewb200_session* s) {
+  RB_REQUIRE(s, "rewb200_session_reset: NULL session");
+  Ctx* c = s->m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_CUDA(cudaMemsetAsync(s->d_pos, 0, s->B * sizeof(int), c->stream));
+  RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
+  s->host_pos = 0;
+  return REWB200_OK;
+}
+
+int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32_t* next_ids, float* logits_out) {
+  RB_REQUIRE(s && ids, "rewb200_session_forward: NULL argument");
+  RB_REQUIRE(S > 0, "generate: tokenIds must not be empty");
+  RB_REQUIRE(s->host_pos + S <= s->max_len, "KvCache.append: total length " + std::to_string(s->host_pos + S) +
+                                                " exceeds maxLen " + std::to_string(s->max_len));
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  const int64_t rows = (int64_t)s->B * S;
+  for (int64_t i = 0; i < rows; ++i)
+    RB_REQUIRE(ids[i] >= 0 && ids[i] < m->cfg.vocab, "generate: token id out of range at index " + std::to_string(i));
+  RB_TRY(ensure_acts(s, rows, s->B));
+  memcpy(s->h_ids, ids, rows * sizeof(int32_t));
+  RB_CUDA(cudaEventRecord(s->ev0, c->stream));
+  RB_CUDA(cudaMemcpyAsync(s->d_ids, s->h_ids, rows * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
+  RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
+  FwdOpts o;
+  o.S = S;
+  RB_TRY(enqueue_forward(s, o));
+  RB_CUDA(cudaEventRecord(s->ev1, c->stream));
+  if (next_ids)
+    RB_CUDA(cudaMemcpyAsync(next_ids, s->d_next, s->B * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  if (logits_out)
+    RB_CUDA(cudaMemcpyAsync(logits_out, s->logits, (size_t)s->B * m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost,
+                            c->stream));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_CUDA(cudaEventElapsedTime(&s->prefill_ms, s->ev0, s->ev1));
+  s->host_pos += S;
+  return ctx_check_status(c);
+}
+
+int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, float* last_logits) {
+  RB_REQUIRE(s, "rewb200_session_decode: NULL session");
+  RB_REQUIRE(n_steps >= 0, "n_steps must be non-negative");
+  RB_REQUIRE(s->host_pos > 0, "rewb200_session_decode: feed a prompt with rewb200_session_forward first");
+  RB_REQUIRE(s->host_pos + n_steps <= s->max_len, "KvCache.append: total length " +
+                                                      std::to_string(s->host_pos + n_steps) + " exceeds maxLen " +
+                                                      std::to_string(s->max_len));
+  RB_REQUIRE(n_steps <= s->out_capacity, "too many decode steps for the session's id buffer");
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_TRY(ensure_acts(s, std::max<int64_t>(s->B, s->rows_cap), s->B));
+  FwdOpts o;
+  o.S = 1;
+  const char* nograph = getenv("REW_B200_NO_GRAPH");
+  const bool use_graph = !(nograph && nograph[0] == '1');
+  if (use_graph && !s->graph && n_steps > 0) {
+    cudaGraph_t g;
+    RB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    int st = enqueue_forward(s, o);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+    if (st != REWB200_OK) {
+      if (e == cudaSuccess) cudaGraphDestroy(g);
+      return st;
+    }
+    RB_CUDA(e);
+    RB_CUDA(cudaGraphInstantiate(&s->graph, g, 0));
+    RB_CUDA(cudaGraphDestroy(g));
+  }
+  RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
+  RB_CUDA(cudaEventRecord(s->ev0, c->stream));
+  for (int i = 0; i < n_steps; ++i) {
+    if (use_graph) RB_CUDA(cudaGraphLaunch(s->graph, c->stream));
+    else RB_TRY(enqueue_forward(s, o));
+  }
+  RB_CUDA(cudaEventRecord(s->ev1, c->stream));
+  if (out_ids && n_steps > 0) {
+    // device layout [step][B] -> host [B][n_steps]
+    std::vector<int32_t> tmp((size_t)n_steps * s->B);
+    RB_CUDA(cudaMemcpyAsync(tmp.data(), s->d_out, tmp.size() * sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
+    RB_CUDA(cudaStreamSynchronize(c->stream));
+    for (int st = 0; st < n_steps; ++st)
+      for (int b = 0; b < s->B; ++b) out_ids[(size_t)b * n_steps + st] = tmp[(size_t)st * s->B + b];
+  }
+  if (last_logits)
+    RB_CUDA(cudaMemcpyAsync(last_logits, s->logits, (size_t)s->B * m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost,
+                            c->stream));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_CUDA(cudaEventElapsedTime(&s->decode_ms, s->ev0, s->ev1));
+  s->host_pos += n_steps;
+  return ctx_check_status(c);
+}
+
+int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
+                     float* last_logits) {
+  RB_REQUIRE(s && prompt && out_ids, "rewb200_generate: NULL argument");
+  RB_REQUIRE(n_new >= 1, "generate: maxNewTokens must be positive");
+  RB_TRY(rewb200_session_reset(s));
+  std::vector<int32_t> first(s->B);
+  RB_TRY(rewb200_session_forward(s, prompt, S, first.data(), n_new == 1 ? last_logits : nullptr));
+  for (int b = 0; b < s->B; ++b) out_ids[(size_t)b * n_new] = first[b];
+  if (n_new == 1) return REWB200_OK;
+  auto all_done = [&](int upto) {
+    if (eos < 0) return false;
+    for (int b = 0; b < s->B; ++b) {
+      bool hit = false;
+      for (int t = 0; t < upto; ++t) hit |= (out_ids[(size_t)b * n_new + t] == eos);
+      if (!hit) return false;
+    }
+    return true;
+  };
+  if (eos < 0) {
+    std::vector<int32_t> rest((size_t)s->B * (n_new - 1));
+    RB_TRY(rewb200_session_decode(s, n_new - 1, rest.data(), last_logits));
+    for (int b = 0; b < s->B; ++b)
+      for (int t = 1; t < n_new; ++t) out_ids[(size_t)b * n_new + t] = rest[(size_t)b * (n_new - 1) + t - 1];
+    return REWB200_OK;
+  }
+  // With a stop token the host looks at the ids every 8 steps.
+  int done = 1;
+  for (int b = 0; b < s->B; ++b)
+    for (int t = 1; t < n_new; ++t) out_ids[(size_t)b * n_new + t] = -1;
+  while (done < n_new && !all_done(done)) {
+    const int chunk = std::min(8, n_new - done);
+    std::vector<int32_t> rest((size_t)s->B * chunk);
+    RB_TRY(rewb200_session_decode(s, chunk, rest.data(), last_logits));
+    for (int b = 0; b < s->B; ++b)
+      for (int t = 0; t < chunk; ++t) out_ids[(size_t)b * n_new + done + t] = rest[(size_t)b * chunk + t];
+    done += chunk;
+  }
+  // ids after a sequence's first eos are not part of its output (generate.nim:263-264)
+  for (int b = 0; b < s->B; ++b) {
+    bool hit = false;
+    for (int t = 0; t < n_new; ++t) {
+      if (hit) out_ids[(size_t)b * n_new + t] = -1;
+      else if (out_ids[(size_t)b * n_new + t] == eos) hit = true;
+    }
+  }
+  return REWB200_OK;
+}
+
+int rewb200_session_last_ms(const rewb200_session* s, float* prefill_ms, float* decode_ms) {
+  RB_REQUIRE(s, "rewb200_session_last_ms: NULL session");
+  if (prefill_ms) *prefill_ms = s->prefill_ms;
+  if (decode_ms) *decode_ms = s->decode_ms;
+  return REWB200_OK;
+}
+
+int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int64_t offset, int causal,
+                              float* logits_out) {
+  RB_REQUIRE(s && ids && logits_out, "rewb200_model_forward_all: NULL argument");
+  RB_REQUIRE(S > 0 && S <= s->max_len, "sequence length out of range for this session");
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  RB_REQUIRE(offset >= 0 && offset + S <= m->cfg.max_seq, "RotaryPositionEncoding.forward: position " +
+                                                             std::to_string(offset + S) + " exceeds maxSeqLen " +
+                                                             std::to_string(m->cfg.max_seq));
+  RB_CUDA(cudaSetDevice(c->device));
+  const int64_t rows = (int64_t)s->B * S;
+  for (int64_t i = 0; i < rows; ++i)
+    RB_REQUIRE(ids[i] >= 0 && ids[i] < m->cfg.vocab, "token id out of range at index " + std::to_string(i));
+  RB_TRY(rewb200_session_reset(s));
+  RB_TRY(ensure_acts(s, rows, rows));
+  memcpy(s->h_ids, ids, rows * sizeof(int32_t));
+  RB_CUDA(cudaMemcpyAsync(s->d_ids, s->h_ids, rows * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
+  FwdOpts o;
+  o.S = S;
+  o.rope_shift = (int)offset;
+  o.causal = causal;
+  o.all_logits = true;
+  RB_TRY(enqueue_forward(s, o));
+  RB_CUDA(cudaMemcpyAsync(logits_out, s->logits, (size_t)rows * m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost,
+                          c->stream));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  return ctx_check_status(c);
+}
+
+}  // extern "C"
