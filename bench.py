@@ -1,0 +1,316 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the rew_b200 backend (one JSON line on stdout).
+
+    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
+
+A "step" is one greedy decode step of the whole batch (one token per sequence)
+with a KV cache, after a prefill of the prompt.  Workloads (synthetic weights
+N(0, 0.02) generated on the device, uniform random prompt ids):
+
+    l8_b32   Llama-3-8B-shaped, bf16, batch 32, prompt 512   (default)
+    l8_b1    same model, batch 1
+    tiny     the tiny fp32 Llama of the parity tests
+
+`value` is decode tokens/s of the whole job with ids, weights and cache resident
+in HBM (CUDA events around K graph replays); `e2e` is tokens/s of one generate()
+call through the C ABI from host prompt ids to host output ids (prefill, K decode
+steps, host<->device copies inside the timed region).  With --impl reference the
+reference's CPU path is timed instead: the CPU restatement in oracle/ (the
+reference's Nim + XLA-plugin build cannot run here), all host threads.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tokens/s"
+
+WORKLOADS = {
+    "l8_b32": dict(model="llama3_8b", batch=32, prompt=512),
+    "l8_b1": dict(model="llama3_8b", batch=1, prompt=512),
+    "tiny": dict(model="tiny_llama", batch=1, prompt=32),
+}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            j = json.load(f)
+        return float(j["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(mx))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def make_cfg(name):
+    from rew_b200 import weights as W
+    return getattr(W, name)()
+
+
+def run_reference(args, wl, rank):
+    """CPU arm: the oracle port, timed on the host cores.  Bounded sample: ONE decoder layer plus the
+    lm_head of the same shapes at the workload's mean context, extrapolated to all layers."""
+    if rank != 0:
+        return
+    from oracle import orc
+    from rew_b200 import _lib, weights as W
+    cfg = make_cfg(wl["model"])
+    full_layers = cfg.n_layers
+    cfg.n_layers = 1 if cfg.n_layers > 2 else cfg.n_layers
+    cfg.dtype = _lib.F32
+    B = wl["batch"]
+    ctx = wl["prompt"] + args.warmup + args.steps // 2
+    cfg.max_seq = max(cfg.max_seq, ctx + args.steps + args.warmup + 8)
+    rng = np.random.default_rng(0)
+    tensors = []
+    for name, shape in W.tensor_specs(cfg):
+        if len(shape) == 2:
+            t = rng.standard_normal(size=shape, dtype=np.float32)
+            t *= 0.02
+        else:
+            t = np.ones(shape, np.float32) if name.endswith("gamma") else np.zeros(shape, np.float32)
+        tensors.append(t)
+    orc.set_accum64(0)  # f32 accumulation, the fastest setting of the port
+    steps = max(1, min(args.steps, 3))
+    warm = max(1, min(args.warmup, 1))
+    # lm_head-only time: a model with zero layers is not expressible, so time the 1-layer model and
+    # a second call with a doubled step count to separate nothing; instead scale analytically below.
+    orc.decode_bench(cfg, tensors, B, ctx, warm)
+    t = orc.decode_bench(cfg, tensors, B, ctx, steps) / steps
+    # per-step time = layers * t_layer + t_head; split t by parameter count (both are weight-streaming GEMMs)
+    specs = W.tensor_specs(cfg)
+    p_layer = sum(int(np.prod(s)) for n, s in specs if ".layers.0." in n and len(s) == 2)
+    p_head = cfg.d_model * cfg.vocab
+    t_layer = t * p_layer / (p_layer + p_head)
+    t_head = t * p_head / (p_layer + p_head)
+    t_full = full_layers * t_layer + t_head
+    value = B / t_full
+    sample = ("%d timed decode steps of 1 of %d layers + lm_head, batch %d, context %d, f32, extrapolated by layer count"
+              % (steps, full_layers, B, ctx))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t_full * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "batch": B, "prompt": wl["prompt"], "decode_steps": args.steps},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "rew's own CPU path (Nim + XLA PJRT plugin) cannot be built or run here; this is the C++ restatement in oracle/",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_leg(args, wl):
+    """Bounded CPU sample for the GPU arm's line (rank 0, N=1 only)."""
+    try:
+        from oracle import orc
+        from rew_b200 import _lib, weights as W
+        cfg = make_cfg(wl["model"])
+        full_layers = cfg.n_layers
+        if cfg.n_layers > 2:
+            cfg.n_layers = 1
+        cfg.dtype = _lib.F32
+        B = wl["batch"]
+        ctx = wl["prompt"] + args.steps // 2
+        cfg.max_seq = max(cfg.max_seq, ctx + 16)
+        rng = np.random.default_rng(0)
+        tensors = []
+        for name, shape in W.tensor_specs(cfg):
+            if len(shape) == 2:
+                t = rng.standard_normal(size=shape, dtype=np.float32)
+                t *= 0.02
+            else:
+                t = np.ones(shape, np.float32) if name.endswith("gamma") else np.zeros(shape, np.float32)
+            tensors.append(t)
+        orc.set_accum64(0)
+        orc.decode_bench(cfg, tensors, B, ctx, 1)
+        n = 2
+        t = orc.decode_bench(cfg, tensors, B, ctx, n) / n
+        specs = W.tensor_specs(cfg)
+        p_layer = sum(int(np.prod(s)) for nm, s in specs if ".layers.0." in nm and len(s) == 2)
+        p_head = cfg.d_model * cfg.vocab
+        t_full = full_layers * t * p_layer / (p_layer + p_head) + t * p_head / (p_layer + p_head)
+        return {"value": B / t_full, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
+                "sample": "%d decode steps of 1 of %d layers + lm_head, batch %d, context %d, f32, extrapolated by layer count"
+                          % (n, full_layers, B, ctx)}
+    except Exception as e:  # the baseline must never take the GPU number down with it
+        return {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %r" % (e,)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="l8_b32", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="rew_b200", choices=["rew_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank, local_rank, world = dist_env()
+
+    if args.impl == "reference":
+        run_reference(args, wl, rank)
+        return
+
+    import ctypes as C
+    from rew_b200 import _lib, api
+    _lib.init(local_rank)
+    L = _lib.lib()
+
+    pg = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo")  # host-side rendezvous only: barrier and max over ranks
+        pg = dist
+
+    cfg = make_cfg(wl["model"])
+    B, S, K, Wm = wl["batch"], wl["prompt"], args.steps, args.warmup
+    max_len = S + Wm + K + 8
+    cfg.max_seq = max(cfg.max_seq, max_len)
+    model = api.CausalLM(cfg).init_random(seed=1234 + rank, std=0.02)
+    sess = model.session(B, max_len)
+    prompt = np.random.default_rng(1 + rank).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+
+    # ---- device-resident decode: prefill, W warm-up steps, K timed steps
+    sess.forward(prompt)
+    prefill_ms, _ = sess.last_ms()
+    if Wm > 0:
+        sess.decode(Wm)
+    if pg:
+        pg.barrier()
+    L.rewb200_sync(0, 0)
+    launches0 = L.rewb200_launch_count(0)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    sess.decode(K)
+    _, decode_ms = sess.last_ms()
+    L.rewb200_sync(0, 0)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = L.rewb200_launch_count(0) - launches0
+    if pg:
+        import torch
+        t = torch.tensor([decode_ms], dtype=torch.float64)
+        pg.all_reduce(t, op=pg.ReduceOp.MAX)
+        decode_ms = float(t[0])
+        pg.barrier()
+    tokens = B * K * world
+    value = tokens / (decode_ms * 1e-3)
+
+    # ---- end to end through the C ABI: host prompt ids -> host output ids
+    t0 = time.perf_counter()
+    out = sess.generate(prompt, K)
+    e2e_s = time.perf_counter() - t0
+    if pg:
+        import torch
+        t = torch.tensor([e2e_s], dtype=torch.float64)
+        pg.all_reduce(t, op=pg.ReduceOp.MAX)
+        e2e_s = float(t[0])
+    e2e = {"value": tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": prompt.nbytes / K,
+           "d2h_bytes_per_step": out.nbytes / K,
+           "what": "one generate() call: prefill of the prompt + %d decode steps, ids host->device->host" % K}
+
+    # ---- roofline of the dominant kernel (the bf16 weight-streaming Linear)
+    roofline = None
+    if cfg.dtype == _lib.BF16:
+        ms = C.c_float()
+        nbytes = C.c_int64()
+        nl = C.c_int32()
+        _lib.check(L.rewb200_session_profile_linears(sess._h, 20, C.byref(ms), C.byref(nbytes), C.byref(nl)))
+        peak, which = measured_peaks()
+        ach = nbytes.value / (ms.value * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                    "kernel": "linear_bf16_kernel", "launches_per_step": nl.value, "ms_per_step": ms.value,
+                    "bytes_per_step": nbytes.value, "peak_source": which}
+        # whole decode step against the same roof: weights + KV read once per step
+        kv_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
+        step_bytes = model.weight_bytes() - cfg.vocab * cfg.d_model * 2 + kv_bytes
+        roofline["step_frac"] = step_bytes / (decode_ms / K * 1e-3) / 1e9 / peak
+
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
+        "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if cfg.dtype == _lib.BF16 else "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": B, "prompt": S, "decode_steps": K,
+                   "parallelism": "replicas" if world > 1 else "single",
+                   "l2": "weights per step (%.1f GB) exceed the 126 MB L2" % (model.weight_bytes() / 1e9)},
+        "prefill": {"tokens_per_s": B * S * world / (prefill_ms * 1e-3), "ms": prefill_ms},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_leg(args, wl)
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

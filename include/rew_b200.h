@@ -24,6 +24,9 @@
 #ifdef __cplusplus
 extern "C" {
 #endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library itself is built with hidden visibility */
+#endif
 
 #define REWB200_OK 0
 #define REWB200_ERR 1
@@ -169,6 +172,13 @@ int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new
                      float* last_logits);
 /* Device-time of the last forward / decode call in milliseconds (CUDA events). */
 int rewb200_session_last_ms(const rewb200_session* s, float* prefill_ms, float* decode_ms);
+/* Kernels in one captured decode step (0 before the first decode). */
+int rewb200_session_graph_kernels(const rewb200_session* s);
+/* Measurement aid: runs only the Linear launches of one decode step (same
+ * buffers, tiles and split-K as the real step) `iters` times between CUDA
+ * events; reports milliseconds, algorithmic bytes and launches per step. */
+int rewb200_session_profile_linears(rewb200_session* s, int iters, float* ms_per_step, int64_t* bytes_per_step,
+                                    int* launches_per_step);
 /* Full no-cache forward, logits for every position, as LlamaForCausalLM.forward
  * (src/rew/models/llama.nim:131-140): ids host [batch,S] -> logits host [batch,S,vocab]. */
 int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int64_t offset, int causal,
@@ -182,6 +192,9 @@ int rewb200_comm_init(int slot, const void* id128, int rank, int world);
 int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n);
 int rewb200_comm_destroy(int slot);
 
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 #ifdef __cplusplus
 }
 #endif

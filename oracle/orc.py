@@ -43,6 +43,7 @@ def lib():
         _lib.orc_reduce_sum.restype = C.c_float
         _lib.orc_log_prob_of.restype = C.c_float
         _lib.orc_tensor_count.restype = C.c_int64
+        _lib.orc_decode_bench.restype = C.c_double
     return _lib
 
 
@@ -282,3 +283,11 @@ def generate_loop(forward, prompt, vocab, max_new, eos):
     n = lib().orc_generate_loop(cb, None, _ip(prompt), C.c_int64(prompt.size), C.c_int64(vocab), max_new, eos, _ip(toks),
                                 _p(lps))
     return toks[:n].tolist(), lps[:n].tolist()
+
+
+def decode_bench(mc, tensors, batch, ctx, n_steps):
+    """Seconds for n_steps cached decode steps of `batch` sequences at context `ctx`."""
+    cfg = cfg_of(mc)
+    keep, arr = _tensor_array(tensors)
+    last = np.empty(batch, np.int32)
+    return float(lib().orc_decode_bench(C.byref(cfg), arr, C.c_int64(batch), C.c_int64(ctx), n_steps, _ip(last)))

@@ -17,6 +17,7 @@
 // (default) and in float, left to right, otherwise.
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
@@ -38,24 +39,42 @@ int g_accum64 = 1;
 
 // src/rew/ops/linalg.nim:239-252 (matmul = dotGeneral contracting a.1 with b.0)
 void matmul(const float* a, const float* b, float* out, int64_t M, int64_t K, int64_t N) {
-#pragma omp parallel for schedule(static)
-  for (int64_t m = 0; m < M; ++m) {
-    if (g_accum64) {
-      std::vector<double> acc(N, 0.0);
-      for (int64_t k = 0; k < K; ++k) {
-        const double av = a[m * K + k];
-        const float* br = b + k * N;
-        for (int64_t n = 0; n < N; ++n) acc[n] += av * (double)br[n];
+  // Threads split the output columns, row blocks of 32 keep the accumulators in
+  // cache; every (m, n) still sums over k in ascending order.
+  constexpr int64_t NB = 128, MB = 32;
+  const int64_t nblocks = (N + NB - 1) / NB;
+#pragma omp parallel for schedule(dynamic)
+  for (int64_t nb = 0; nb < nblocks; ++nb) {
+    const int64_t n0 = nb * NB, nw = std::min(NB, N - n0);
+    for (int64_t m0 = 0; m0 < M; m0 += MB) {
+      const int64_t mw = std::min(MB, M - m0);
+      if (g_accum64) {
+        double acc[MB][NB];
+        for (int64_t i = 0; i < mw; ++i)
+          for (int64_t n = 0; n < nw; ++n) acc[i][n] = 0.0;
+        for (int64_t k = 0; k < K; ++k) {
+          const float* br = b + k * N + n0;
+          for (int64_t i = 0; i < mw; ++i) {
+            const double av = a[(m0 + i) * K + k];
+            for (int64_t n = 0; n < nw; ++n) acc[i][n] += av * (double)br[n];
+          }
+        }
+        for (int64_t i = 0; i < mw; ++i)
+          for (int64_t n = 0; n < nw; ++n) out[(m0 + i) * N + n0 + n] = (float)acc[i][n];
+      } else {
+        float acc[MB][NB];
+        for (int64_t i = 0; i < mw; ++i)
+          for (int64_t n = 0; n < nw; ++n) acc[i][n] = 0.f;
+        for (int64_t k = 0; k < K; ++k) {
+          const float* br = b + k * N + n0;
+          for (int64_t i = 0; i < mw; ++i) {
+            const float av = a[(m0 + i) * K + k];
+            for (int64_t n = 0; n < nw; ++n) acc[i][n] += av * br[n];
+          }
+        }
+        for (int64_t i = 0; i < mw; ++i)
+          for (int64_t n = 0; n < nw; ++n) out[(m0 + i) * N + n0 + n] = acc[i][n];
       }
-      for (int64_t n = 0; n < N; ++n) out[m * N + n] = (float)acc[n];
-    } else {
-      std::vector<float> acc(N, 0.f);
-      for (int64_t k = 0; k < K; ++k) {
-        const float av = a[m * K + k];
-        const float* br = b + k * N;
-        for (int64_t n = 0; n < N; ++n) acc[n] += av * br[n];
-      }
-      for (int64_t n = 0; n < N; ++n) out[m * N + n] = acc[n];
     }
   }
 }
@@ -735,4 +754,41 @@ ORC_API int orc_generate_loop(orc_forward_fn fn, void* user, const int32_t* prom
     if (next == eos) break;
   }
   return (int)gen.size();
+}
+
+// Timed CPU baseline for the decode metric: fabricates a KV cache of `ctx`
+// random entries per layer, then runs `n_steps` single-token steps
+// (backbone with S = 1, lm_head on the last position, greedy argmax) for B
+// sequences and returns the wall-clock seconds of those steps alone.
+ORC_API double orc_decode_bench(const Cfg* c, const float* const* tensors, int64_t B, int64_t ctx, int n_steps,
+                                int32_t* last_ids) {
+  Model m = build(*c, tensors);
+  const int64_t d = c->d_model, V = c->vocab;
+  std::vector<KV> kvs(c->n_layers);
+  uint64_t st = 0x243F6A8885A308D3ull;
+  auto rnd = [&]() {
+    st = st * 6364136223846793005ull + 1442695040888963407ull;
+    return ((float)((st >> 40) & 0xFFFF) / 65536.0f - 0.5f) * 0.2f;
+  };
+  for (auto& kv : kvs) {
+    kv.k.resize((size_t)B * c->n_kv_heads * ctx * c->head_dim);
+    kv.v.resize(kv.k.size());
+    for (auto& x : kv.k) x = rnd();
+    for (auto& x : kv.v) x = rnd();
+    kv.len = ctx;
+  }
+  std::vector<int32_t> cur(B);
+  for (int64_t b = 0; b < B; ++b) cur[b] = (int32_t)((b * 7919) % V);
+  std::vector<float> logits(B * V), h(B * d);
+  const auto t0 = std::chrono::steady_clock::now();
+  int64_t offset = ctx;
+  for (int step = 0; step < n_steps; ++step) {
+    backbone(m, cur.data(), h.data(), B, 1, offset, 1, &kvs);
+    linear(h.data(), m.lw, m.lb, logits.data(), B, d, V);
+    for (int64_t b = 0; b < B; ++b) cur[b] = sample_greedy(&logits[b * V], V);
+    offset += 1;
+  }
+  const auto t1 = std::chrono::steady_clock::now();
+  if (last_ids) std::memcpy(last_ids, cur.data(), sizeof(int32_t) * B);
+  return std::chrono::duration<double>(t1 - t0).count();
 }

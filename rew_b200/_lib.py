@@ -75,6 +75,8 @@ SIGNATURES = {
     "rewb200_session_decode": (C.c_int, [P, C.c_int, I32P, F32P]),
     "rewb200_generate": (C.c_int, [P, I32P, C.c_int, C.c_int, C.c_int, I32P, F32P]),
     "rewb200_session_last_ms": (C.c_int, [P, F32P, F32P]),
+    "rewb200_session_graph_kernels": (C.c_int, [P]),
+    "rewb200_session_profile_linears": (C.c_int, [P, C.c_int, F32P, I64P, I32P]),
     "rewb200_model_forward_all": (C.c_int, [P, I32P, C.c_int, C.c_int64, C.c_int, F32P]),
     "rewb200_comm_unique_id": (C.c_int, [P]),
     "rewb200_comm_init": (C.c_int, [C.c_int, P, C.c_int, C.c_int]),

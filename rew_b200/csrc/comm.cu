@@ -1,0 +1,161 @@
+// Tensor/expert-parallel communication: allReduce / allToAll of
+// src/rew/ops/distributed.nim:62-83,106-128 executed with NCCL over NVLink, one
+// process per GPU.  NCCL is resolved at run time (dlopen) so the library loads
+// on hosts without it and shares the copy a host process may already have
+// loaded.  Collectives run on the slot's stream, so they can be captured into
+// the decode graph.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+namespace rewb {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+};
+static NcclApi g_nccl;
+
+struct Comm {
+  ncclComm_t comm = nullptr;
+  int rank = 0, world = 1;
+};
+static Comm g_comm[16];
+
+static int nccl_load() {
+  if (g_nccl.handle) return REWB200_OK;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  void* h = nullptr;
+  for (const char* n : names) {
+    h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (h) break;
+  }
+  RB_REQUIRE(h != nullptr, std::string("NCCL library not found (dlopen libnccl.so.2): ") + dlerror());
+#define RB_SYM(field, name)                                                     \
+  *(void**)(&g_nccl.field) = dlsym(h, name);                                    \
+  RB_REQUIRE(g_nccl.field != nullptr, std::string("NCCL symbol missing: ") + name)
+  RB_SYM(GetUniqueId, "ncclGetUniqueId");
+  RB_SYM(CommInitRank, "ncclCommInitRank");
+  RB_SYM(CommDestroy, "ncclCommDestroy");
+  RB_SYM(CommAbort, "ncclCommAbort");
+  RB_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
+  RB_SYM(GetErrorString, "ncclGetErrorString");
+  RB_SYM(AllReduce, "ncclAllReduce");
+  RB_SYM(AllGather, "ncclAllGather");
+  RB_SYM(Send, "ncclSend");
+  RB_SYM(Recv, "ncclRecv");
+  RB_SYM(GroupStart, "ncclGroupStart");
+  RB_SYM(GroupEnd, "ncclGroupEnd");
+#undef RB_SYM
+  g_nccl.handle = h;
+  return REWB200_OK;
+}
+
+#define RB_NCCL(expr)                                                                                   \
+  do {                                                                                                  \
+    ncclResult_t _r = (expr);                                                                           \
+    if (_r != ncclSuccess) return fail(std::string(#expr) + ": " + g_nccl.GetErrorString(_r));          \
+  } while (0)
+
+int comm_world(int slot) { return (slot >= 0 && slot < 16 && g_comm[slot].comm) ? g_comm[slot].world : 1; }
+int comm_rank(int slot) { return (slot >= 0 && slot < 16 && g_comm[slot].comm) ? g_comm[slot].rank : 0; }
+
+int comm_allreduce_sum_f32(Ctx* c, int slot, float* ptr, int64_t n) {
+  RB_REQUIRE(slot >= 0 && slot < 16 && g_comm[slot].comm, "rewb200_comm_init has not been called for this slot");
+  RB_NCCL(g_nccl.AllReduce(ptr, ptr, (size_t)n, ncclFloat, ncclSum, g_comm[slot].comm, c->stream));
+  return REWB200_OK;
+}
+
+int comm_allgather_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_rank) {
+  RB_REQUIRE(slot >= 0 && slot < 16 && g_comm[slot].comm, "rewb200_comm_init has not been called for this slot");
+  RB_NCCL(g_nccl.AllGather(send, recv, bytes_per_rank, ncclChar, g_comm[slot].comm, c->stream));
+  return REWB200_OK;
+}
+
+// Equal-count all-to-all: rank r sends bytes [p*bytes, (p+1)*bytes) of `send` to peer p.
+int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_peer) {
+  RB_REQUIRE(slot >= 0 && slot < 16 && g_comm[slot].comm, "rewb200_comm_init has not been called for this slot");
+  Comm& cm = g_comm[slot];
+  RB_NCCL(g_nccl.GroupStart());
+  for (int p = 0; p < cm.world; ++p) {
+    RB_NCCL(g_nccl.Send((const char*)send + (size_t)p * bytes_per_peer, bytes_per_peer, ncclChar, p, cm.comm, c->stream));
+    RB_NCCL(g_nccl.Recv((char*)recv + (size_t)p * bytes_per_peer, bytes_per_peer, ncclChar, p, cm.comm, c->stream));
+  }
+  RB_NCCL(g_nccl.GroupEnd());
+  return REWB200_OK;
+}
+
+}  // namespace rewb
+
+using namespace rewb;
+
+extern "C" {
+
+int rewb200_comm_unique_id(void* id128) {
+  RB_REQUIRE(id128 != nullptr, "rewb200_comm_unique_id: NULL buffer");
+  RB_TRY(nccl_load());
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+  ncclUniqueId id;
+  RB_NCCL(g_nccl.GetUniqueId(&id));
+  memcpy(id128, &id, 128);
+  return REWB200_OK;
+}
+
+int rewb200_comm_init(int slot, const void* id128, int rank, int world) {
+  Ctx* c = ctx_get(slot);
+  if (!c) return REWB200_ERR;
+  RB_REQUIRE(id128 != nullptr && world >= 1 && rank >= 0 && rank < world, "rewb200_comm_init: bad rank/world");
+  RB_REQUIRE(slot < 16 && !g_comm[slot].comm, "rewb200_comm_init: communicator already exists for this slot");
+  RB_TRY(nccl_load());
+  RB_CUDA(cudaSetDevice(c->device));
+  ncclUniqueId id;
+  memcpy(&id, id128, 128);
+  RB_NCCL(g_nccl.CommInitRank(&g_comm[slot].comm, world, id, rank));
+  g_comm[slot].rank = rank;
+  g_comm[slot].world = world;
+  return REWB200_OK;
+}
+
+int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n) {
+  Ctx* c = ctx_get(slot);
+  if (!c) return REWB200_ERR;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_TRY(comm_allreduce_sum_f32(c, slot, (float*)device_ptr, n));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  ncclResult_t async = ncclSuccess;
+  RB_NCCL(g_nccl.CommGetAsyncError(g_comm[slot].comm, &async));
+  if (async != ncclSuccess) {
+    g_nccl.CommAbort(g_comm[slot].comm);
+    g_comm[slot].comm = nullptr;
+    return fail(std::string("NCCL asynchronous error: ") + g_nccl.GetErrorString(async));
+  }
+  return REWB200_OK;
+}
+
+int rewb200_comm_destroy(int slot) {
+  if (slot < 0 || slot >= 16 || !g_comm[slot].comm) return REWB200_OK;
+  Ctx* c = ctx_get(slot);
+  if (c) {
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+  }
+  g_nccl.CommDestroy(g_comm[slot].comm);
+  g_comm[slot].comm = nullptr;
+  return REWB200_OK;
+}
+
+}  // extern "C"

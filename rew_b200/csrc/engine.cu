@@ -130,6 +130,7 @@ struct rewb200_session {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float prefill_ms = 0.f, decode_ms = 0.f;
   int host_pos = 0;                    // tokens so far (all sequences advance together)
+  int graph_kernels = 0;               // kernels in one captured decode step
 };
 
 namespace rewb {
@@ -758,8 +759,10 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
   const bool use_graph = !(nograph && nograph[0] == '1');
   if (use_graph && !s->graph && n_steps > 0) {
     cudaGraph_t g;
+    const int64_t before = g_launch_total;
     RB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     int st = enqueue_forward(s, o);
+    s->graph_kernels = (int)(g_launch_total - before);
     cudaError_t e = cudaStreamEndCapture(c->stream, &g);
     if (st != REWB200_OK) {
       if (e == cudaSuccess) cudaGraphDestroy(g);
@@ -772,8 +775,12 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
   RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
   RB_CUDA(cudaEventRecord(s->ev0, c->stream));
   for (int i = 0; i < n_steps; ++i) {
-    if (use_graph) RB_CUDA(cudaGraphLaunch(s->graph, c->stream));
-    else RB_TRY(enqueue_forward(s, o));
+    if (use_graph) {
+      RB_CUDA(cudaGraphLaunch(s->graph, c->stream));
+      g_launch_total += s->graph_kernels;
+    } else {
+      RB_TRY(enqueue_forward(s, o));
+    }
   }
   RB_CUDA(cudaEventRecord(s->ev1, c->stream));
   if (out_ids && n_steps > 0) {
@@ -847,6 +854,56 @@ int rewb200_session_last_ms(const rewb200_session* s, float* prefill_ms, float* 
   if (decode_ms) *decode_ms = s->decode_ms;
   return REWB200_OK;
 }
+
+// Times only the Linear launches of one decode step (q|k|v, o, gate|up, down of
+// every layer and lm_head, same buffers and split-K choices as the real step),
+// `iters` times back to back, with CUDA events on the launching stream.
+int rewb200_session_profile_linears(rewb200_session* s, int iters, float* ms_per_step, int64_t* bytes_per_step,
+                                    int* launches_per_step) {
+  RB_REQUIRE(s && ms_per_step && iters > 0, "rewb200_session_profile_linears: bad argument");
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  RB_REQUIRE(m->cfg.dtype == REWB200_BF16, "linear profiling is for bf16 models");
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_TRY(ensure_acts(s, std::max<int64_t>(s->B, s->rows_cap), s->B));
+  const int64_t rows = s->B, d = m->cfg.d_model;
+  int64_t bytes = 0;
+  int launches = 0;
+  auto one_step = [&](bool count) -> int {
+    for (LayerDev& L : m->layers) {
+      int ks = 1;
+      RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks));
+      if (count) bytes += (L.qkv.K * L.qkv.N + rows * L.qkv.K) * 2 + (int64_t)ks * rows * L.qkv.N * 4;
+      RB_TRY(run_linear(s, L.o, s->attn, m->nq, rows, true, 0, s->part, d, &ks));
+      if (count) bytes += (L.o.K * L.o.N + rows * L.o.K) * 2 + (int64_t)ks * rows * L.o.N * 4;
+      RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr));
+      if (count) bytes += (L.gu.K * L.gu.N + rows * L.gu.K) * 2 + rows * L.ffn_local * 2;
+      RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
+      if (count) bytes += (L.down.K * L.down.N + rows * L.down.K) * 2 + (int64_t)ks * rows * L.down.N * 4;
+      if (count) launches += 4;
+    }
+    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->logits, m->cfg.vocab, m->lm.b,
+                              nullptr, 0));
+    if (count) {
+      bytes += (m->lm.K * m->lm.N + rows * m->lm.K) * 2 + rows * m->lm.N * 4;
+      launches += 1;
+    }
+    return REWB200_OK;
+  };
+  RB_TRY(one_step(true));  // warm-up, also counts bytes
+  RB_CUDA(cudaEventRecord(s->ev0, c->stream));
+  for (int i = 0; i < iters; ++i) RB_TRY(one_step(false));
+  RB_CUDA(cudaEventRecord(s->ev1, c->stream));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  float ms = 0.f;
+  RB_CUDA(cudaEventElapsedTime(&ms, s->ev0, s->ev1));
+  *ms_per_step = ms / iters;
+  if (bytes_per_step) *bytes_per_step = bytes;
+  if (launches_per_step) *launches_per_step = launches;
+  return ctx_check_status(c);
+}
+
+int rewb200_session_graph_kernels(const rewb200_session* s) { return s ? s->graph_kernels : 0; }
 
 int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int64_t offset, int causal,
                               float* logits_out) {

@@ -51,9 +51,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Returns false (and records KS_MBAR_TIMEOUT) if the phase never completed.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// The bound is both an iteration count and ~2 s of wall time (try_wait may
+// itself block for an implementation-defined slice).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
+  uint64_t t0 = 0;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 127u) == 127u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 2000000000ull) break;
+    }
+  }
   if (status) atomicExch(status, KS_MBAR_TIMEOUT);
   return false;
 }
