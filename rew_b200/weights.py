@@ -1,7 +1,6 @@
 """Model configurations and the canonical order of a model's logical tensors.
 
-The order is the one rewb200_model_set_tensor indexes by and the one the
-oracle's tensor array uses.  Names follow rew's pytree fields
+The order is the one rewb200_model_set_tensor indexes by.  Names follow rew's pytree fields
 (src/rew/models/llama.nim:27-44, src/rew/models/deepseek.nim:36-63).
 """
 from dataclasses import dataclass, asdict
