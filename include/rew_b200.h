@@ -123,6 +123,21 @@ int rewb200_embed_gather(const rewb200_buffer* ids, const rewb200_buffer* table,
 int rewb200_moe_route(const rewb200_buffer* x, const rewb200_buffer* router_w, const rewb200_buffer* router_b,
                       int top_k, rewb200_buffer** weights, rewb200_buffer** indices);
 
+/* Linear for callers that cannot allocate device memory (no counterpart in the
+ * reference, which always allocates through its PJRT client).  Same math as
+ * rewb200_linear for bf16 with M <= 32: y[M,N] = x[M,K] @ w[K,N] + bias, but on
+ * raw device pointers the caller owns and with the split-K partial sums kept in
+ * a fixed 8 MiB array inside the library image instead of pool memory, so the
+ * call performs no cudaMalloc / cudaFree / pool allocation.  Meant for hosts
+ * whose own allocator holds the whole device heap, and for sections where the
+ * device-wide synchronisation of cudaMalloc is not acceptable.  Sizes with
+ * M*N*4 bytes above 8 MiB are rejected.  Every call shares the one array:
+ * calls that overlap on the GPU race; calls on one slot are stream-ordered.
+ * The first call on a device resolves the array's address; make it outside
+ * any stream capture.  bias may be NULL. */
+int rewb200_linear_noalloc(int slot, const void* x_bf16, const void* w_bf16, const float* bias, void* y_bf16,
+                           int64_t M, int64_t K, int64_t N);
+
 /* ---- model + generate ------------------------------------------------------
  * LlamaForCausalLM / DeepSeekForCausalLM (src/rew/models/llama.nim:13-44,
  * src/rew/models/deepseek.nim:20-63) as one object with fused device layouts. */

@@ -61,6 +61,7 @@ SIGNATURES = {
     "rewb200_swiglu_ffn": (C.c_int, [P, P, P, P, P, P, P, PP]),
     "rewb200_embed_gather": (C.c_int, [P, P, PP]),
     "rewb200_moe_route": (C.c_int, [P, P, P, C.c_int, PP, PP]),
+    "rewb200_linear_noalloc": (C.c_int, [C.c_int, P, P, P, P, C.c_int64, C.c_int64, C.c_int64]),
     "rewb200_model_create": (C.c_int, [C.c_int, C.POINTER(Config), PP]),
     "rewb200_model_free": (None, [P]),
     "rewb200_model_tensor_count": (C.c_int64, [P]),
