@@ -212,6 +212,7 @@ def main():
     ap.add_argument("--workload", default="l8_b32", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="rew_b200", choices=["rew_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     rank, local_rank, world = dist_env()
@@ -232,6 +233,8 @@ def main():
         pg = dist
 
     cfg = make_cfg(wl["model"])
+    if args.layers > 0:
+        cfg.n_layers = args.layers
     B, S, K, Wm = wl["batch"], wl["prompt"], args.steps, args.warmup
     max_len = S + Wm + K + 8
     cfg.max_seq = max(cfg.max_seq, max_len)
@@ -288,7 +291,7 @@ def main():
         peak, which = measured_peaks()
         ach = nbytes.value / (ms.value * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                    "kernel": "linear_bf16_kernel", "launches_per_step": nl.value, "ms_per_step": ms.value,
+                    "kernel": "linear_tc_kernel<32>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>", "launches_per_step": nl.value, "ms_per_step": ms.value,
                     "bytes_per_step": nbytes.value, "peak_source": which}
         # whole decode step against the same roof: weights + KV read once per step
         kv_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
@@ -301,7 +304,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
         "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if cfg.dtype == _lib.BF16 else "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": B, "prompt": S, "decode_steps": K,
+        "config": {"workload": args.workload + ("" if args.layers <= 0 else "_%dlayers" % args.layers), "batch_per_gpu": B, "prompt": S, "decode_steps": K,
                    "parallelism": "replicas" if world > 1 else "single",
                    "l2": "weights per step (%.1f GB) exceed the 126 MB L2" % (model.weight_bytes() / 1e9)},
         "prefill": {"tokens_per_s": B * S * world / (prefill_ms * 1e-3), "ms": prefill_ms},

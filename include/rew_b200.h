@@ -59,6 +59,12 @@ const char* rewb200_last_error(void);
 /* Waits for all queued work of a slot; fails after timeout_ms or when a kernel
  * recorded a device-side status (bounded wait expired, bad index). */
 int rewb200_sync(int slot, int timeout_ms);
+/* Run-time switches (also read from the environment at init):
+ *   "linear" = "mma" | "tc_prefill" | "tc"   bf16 Linear on mma.sync, on tcgen05 for more than 32
+ *                                            rows, or on tcgen05 always   (REW_B200_LINEAR)
+ *   "pdl"    = "0" | "1"                     programmatic dependent launch (REW_B200_PDL)
+ * Takes effect for later launches; sessions re-capture their decode graph on the next decode. */
+int rewb200_set_option(int slot, const char* key, const char* value);
 /* Number of kernels this library has launched on the slot since init. */
 int64_t rewb200_launch_count(int slot);
 

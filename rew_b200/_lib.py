@@ -44,6 +44,7 @@ SIGNATURES = {
     "rewb200_shutdown": (C.c_int, []),
     "rewb200_last_error": (C.c_char_p, []),
     "rewb200_sync": (C.c_int, [C.c_int, C.c_int]),
+    "rewb200_set_option": (C.c_int, [C.c_int, C.c_char_p, C.c_char_p]),
     "rewb200_launch_count": (C.c_int64, [C.c_int]),
     "rewb200_buffer_from_host": (C.c_int, [C.c_int, P, C.c_int, I64P, C.c_int, PP]),
     "rewb200_buffer_alloc": (C.c_int, [C.c_int, C.c_int, I64P, C.c_int, PP]),

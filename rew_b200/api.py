@@ -282,3 +282,9 @@ class Session:
             self.free()
         except Exception:
             pass
+
+
+def set_option(key, value, slot=0):
+    """rewb200_set_option: run-time switches such as ("linear", "tc")."""
+    _lib.init()
+    check(lib().rewb200_set_option(slot, key.encode(), value.encode()))

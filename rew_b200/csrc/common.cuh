@@ -45,6 +45,8 @@ struct Ctx {
   int* h_status = nullptr;   // pinned mirror
   int sm_count = 0;
   bool use_pdl = true;
+  int linear_impl = 2;       // bf16 Linear: 0 mma.sync, 1 tcgen05 when rows > 32, 2 tcgen05 always (default)
+  int option_epoch = 0;      // bumped by rewb200_set_option; captured graphs from older epochs are rebuilt
   void* pinned = nullptr;    // pinned host staging for H2D/D2H of buffers
   size_t pinned_bytes = 0;
 };
@@ -126,6 +128,8 @@ struct LinearBf16Plan {
 // [row_offsets[g], row_offsets[g+1]) of x/out (device array, groups+1 ints).
 int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi,
                        int ksplit, void* out, int64_t ldo, const float* bias, const int* row_offsets, int max_rows_per_group);
+int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, int ksplit,
+                     void* out, int64_t ldo, const float* bias);
 int linear_bf16_plan(LinearBf16Plan* plan, const bf16* W, int64_t K, int64_t N, int groups);
 int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N);
 
@@ -209,7 +213,8 @@ struct AttnArgs {
 int attn_launch(Ctx* c, const AttnArgs& a);
 size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits);
 
-int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out_ids);
+// scratch (optional): rows*64*8 bytes lets wide rows be scanned by several CTAs each
+int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out_ids, void* scratch, size_t scratch_bytes);
 int swiglu_f32_launch(Ctx* c, const float* g, const float* u, float* out, int64_t n);
 int cast_launch(Ctx* c, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n);
 int fill_normal_launch(Ctx* c, void* dst, int dtype, int64_t n, uint64_t seed, float std);

@@ -10,6 +10,8 @@
 //   argmax         : sampleGreedy, first maximum (src/rew/infer/generate.nim:152-159).
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -111,8 +113,132 @@ __global__ void __launch_bounds__(NORM_THREADS) residual_norm_kernel(NormArgs a)
   }
 }
 
-// One CTA per new token row.  Threads walk (head, pair) items of the fused
-// q|k|v row.
+// Vectorised variant for d % 4 == 0: 512 threads, each owning NCH float4 chunks
+// held in registers; the split-K slab loads of a chunk are independent and
+// issued together, so the kernel is bound by L2 bandwidth, not by a chain of
+// dependent loads.
+constexpr int NORMV_THREADS = 512;
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ float4 load(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  static __device__ __forceinline__ void store(bf16* p, float4 v) {
+    uint2 u;
+    u.x = pack_bf16(v.x, v.y);
+    u.y = pack_bf16(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+template <typename TE, typename TO, int NCH>
+__global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormArgs a) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int64_t d = a.d;
+  float* xr = a.x_res + row * d;
+  const TE* erow = nullptr;
+  if (a.embed) {
+    int64_t id = row;
+    if (a.ids) {
+      id = a.ids[row];
+      if (id < 0 || id >= a.vocab) {
+        if (threadIdx.x == 0) atomicExch(a.status, KS_BAD_INDEX);
+        id = 0;
+      }
+    }
+    erow = reinterpret_cast<const TE*>(a.embed) + id * d;
+  }
+  float4 vals[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int64_t i = ((int64_t)c * NORMV_THREADS + threadIdx.x) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < d) {
+      v = erow ? Vec4<TE>::load(erow + i) : *reinterpret_cast<const float4*>(xr + i);
+      if (a.partial) {
+        const float* pp = a.partial + row * d + i;
+        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+        int s = 0;
+        for (; s + 4 <= a.nsplit; s += 4) {
+          const float4 p0 = *reinterpret_cast<const float4*>(pp + (s + 0) * a.split_stride);
+          const float4 p1 = *reinterpret_cast<const float4*>(pp + (s + 1) * a.split_stride);
+          const float4 p2 = *reinterpret_cast<const float4*>(pp + (s + 2) * a.split_stride);
+          const float4 p3 = *reinterpret_cast<const float4*>(pp + (s + 3) * a.split_stride);
+          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
+          p.x += p1.x; p.y += p1.y; p.z += p1.z; p.w += p1.w;
+          p.x += p2.x; p.y += p2.y; p.z += p2.z; p.w += p2.w;
+          p.x += p3.x; p.y += p3.y; p.z += p3.z; p.w += p3.w;
+        }
+        for (; s < a.nsplit; ++s) {
+          const float4 p0 = *reinterpret_cast<const float4*>(pp + s * a.split_stride);
+          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
+        }
+        if (a.bias) {
+          const float4 b = *reinterpret_cast<const float4*>(a.bias + i);
+          p.x += b.x; p.y += b.y; p.z += b.z; p.w += b.w;
+        }
+        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+      }
+      if (a.x_res && (erow || a.partial)) *reinterpret_cast<float4*>(xr + i) = v;
+    }
+    vals[c] = v;
+  }
+  if (a.norm_kind < 0) return;
+  TO* orow = reinterpret_cast<TO*>(a.out) + row * d;
+  float mean = 0.f, scale;
+  if (a.norm_kind == 0) {
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) ss += vals[c].x * vals[c].x + vals[c].y * vals[c].y + vals[c].z * vals[c].z + vals[c].w * vals[c].w;
+    ss = block_sum(ss, red);
+    scale = sqrtf(ss / (float)d + a.eps);  // rmsNorm divides by this
+  } else {
+    float s1 = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) s1 += vals[c].x + vals[c].y + vals[c].z + vals[c].w;
+    mean = block_sum(s1, red) / (float)d;
+    float s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int64_t i = ((int64_t)c * NORMV_THREADS + threadIdx.x) * 4;
+      if (i < d) {
+        const float cx = vals[c].x - mean, cy = vals[c].y - mean, cz = vals[c].z - mean, cw = vals[c].w - mean;
+        s2 += cx * cx + cy * cy + cz * cz + cw * cw;
+      }
+    }
+    const float var = block_sum(s2, red) / (float)d;
+    scale = 1.0f / sqrtf(var + a.eps);    // LayerNorm multiplies by this
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int64_t i = ((int64_t)c * NORMV_THREADS + threadIdx.x) * 4;
+    if (i >= d) continue;
+    const float4 g = *reinterpret_cast<const float4*>(a.gamma + i);
+    float4 o;
+    if (a.norm_kind == 0) {
+      o.x = g.x * (vals[c].x / scale); o.y = g.y * (vals[c].y / scale);
+      o.z = g.z * (vals[c].z / scale); o.w = g.w * (vals[c].w / scale);
+    } else {
+      const float4 b = *reinterpret_cast<const float4*>(a.beta + i);
+      o.x = g.x * ((vals[c].x - mean) * scale) + b.x; o.y = g.y * ((vals[c].y - mean) * scale) + b.y;
+      o.z = g.z * ((vals[c].z - mean) * scale) + b.z; o.w = g.w * ((vals[c].w - mean) * scale) + b.w;
+    }
+    Vec4<TO>::store(orow + i, o);
+  }
+}
+
+// One CTA per (token row, chunk of 256 column pairs) of the fused q|k|v row.
 template <typename TA>
 __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
   pdl_launch_dependents();
@@ -144,11 +270,25 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
   TA* kc = reinterpret_cast<TA*>(a.kv.k);
   TA* vc = reinterpret_cast<TA*>(a.kv.v);
   const int npairs = ntot / 2;
-  for (int p = threadIdx.x; p < npairs; p += blockDim.x) {
+  {
+    const int p = blockIdx.y * blockDim.x + threadIdx.x;
+    if (p >= npairs) return;
     const int col = 2 * p;
     float v0 = 0.f, v1 = 0.f;
-    for (int sp = 0; sp < a.nsplit; ++sp) {
-      const float2 t = *reinterpret_cast<const float2*>(a.partial + sp * a.split_stride + row * ntot + col);
+    const float* pp = a.partial + row * ntot + col;
+    int sp = 0;
+    for (; sp + 4 <= a.nsplit; sp += 4) {
+      const float2 t0 = *reinterpret_cast<const float2*>(pp + (sp + 0) * a.split_stride);
+      const float2 t1 = *reinterpret_cast<const float2*>(pp + (sp + 1) * a.split_stride);
+      const float2 t2 = *reinterpret_cast<const float2*>(pp + (sp + 2) * a.split_stride);
+      const float2 t3 = *reinterpret_cast<const float2*>(pp + (sp + 3) * a.split_stride);
+      v0 += t0.x; v1 += t0.y;
+      v0 += t1.x; v1 += t1.y;
+      v0 += t2.x; v1 += t2.y;
+      v0 += t3.x; v1 += t3.y;
+    }
+    for (; sp < a.nsplit; ++sp) {
+      const float2 t = *reinterpret_cast<const float2*>(pp + sp * a.split_stride);
       v0 += t.x;
       v1 += t.y;
     }
@@ -180,16 +320,20 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
   (void)half;
 }
 
-// First maximum of each row.  One CTA per row.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t V, int* out) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
+// First maximum of each row (sampleGreedy).  grid (rows, chunks): each CTA scans
+// one column chunk; with more than one chunk the (value, index) partials are
+// merged by argmax_final_kernel.
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int64_t V, int64_t chunk_w,
+                                                      int* out, float* part_v, int* part_i) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
   pdl_launch_dependents();
   pdl_wait();
   const float* r = logits + (int64_t)blockIdx.x * V;
+  const int64_t c0 = (int64_t)blockIdx.y * chunk_w, c1 = min(V, c0 + chunk_w);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
+  for (int64_t i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
     const float v = r[i];
     if (v > best || (v == best && (int)i < bi)) {
       best = v;
@@ -212,21 +356,44 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     si[warp] = bi;
   }
   __syncthreads();
-  if (warp == 0) {
-    const int nw = blockDim.x >> 5;
-    best = lane < nw ? sv[lane] : -INFINITY;
-    bi = lane < nw ? si[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        best = sv[w];
+        bi = si[w];
       }
+    if (gridDim.y == 1) {
+      out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    } else {
+      part_v[blockIdx.x * gridDim.y + blockIdx.y] = best;
+      part_i[blockIdx.x * gridDim.y + blockIdx.y] = bi;
     }
-    if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
   }
+}
+
+__global__ void __launch_bounds__(32) argmax_final_kernel(const float* part_v, const int* part_i, int nchunks, int* out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < nchunks; i += 32) {
+    const float v = part_v[blockIdx.x * nchunks + i];
+    const int ix = part_i[blockIdx.x * nchunks + i];
+    if (v > best || (v == best && ix < bi)) {
+      best = v;
+      bi = ix;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
 __global__ void swiglu_f32_kernel(const float* g, const float* u, float* out, int64_t n) {
@@ -280,6 +447,23 @@ int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows) {
   RB_REQUIRE(a.d <= (int64_t)NORM_THREADS * NORM_MAX_PER_THREAD, "norm width above 16384 is not supported");
   const bool e16 = a.embed_dtype == REWB200_BF16, o16 = a.out_dtype == REWB200_BF16;
   cudaError_t e;
+  if (a.d % 4 == 0) {
+    const int nch = (int)((a.d / 4 + NORMV_THREADS - 1) / NORMV_THREADS);
+    dim3 g((unsigned)rows), b(NORMV_THREADS);
+#define RB_NORMV(TE, TO)                                                                                   \
+  (nch <= 1   ? launch_k(residual_norm_vec_kernel<TE, TO, 1>, g, b, 0, c->stream, c->use_pdl, a)             \
+   : nch <= 2 ? launch_k(residual_norm_vec_kernel<TE, TO, 2>, g, b, 0, c->stream, c->use_pdl, a)             \
+   : nch <= 4 ? launch_k(residual_norm_vec_kernel<TE, TO, 4>, g, b, 0, c->stream, c->use_pdl, a)             \
+              : launch_k(residual_norm_vec_kernel<TE, TO, 8>, g, b, 0, c->stream, c->use_pdl, a))
+    if (e16 && o16) e = RB_NORMV(bf16, bf16);
+    else if (e16) e = RB_NORMV(bf16, float);
+    else if (o16) e = RB_NORMV(float, bf16);
+    else e = RB_NORMV(float, float);
+#undef RB_NORMV
+    RB_CUDA(e);
+    ++g_launch_total;
+    return REWB200_OK;
+  }
   dim3 grid((unsigned)rows), block(NORM_THREADS);
   if (e16 && o16) e = launch_k(residual_norm_kernel<bf16, bf16>, grid, block, 0, c->stream, c->use_pdl, a);
   else if (e16) e = launch_k(residual_norm_kernel<bf16, float>, grid, block, 0, c->stream, c->use_pdl, a);
@@ -295,19 +479,35 @@ int qkv_post_launch(Ctx* c, const QkvPostArgs& a, int64_t B) {
   if (rows == 0) return REWB200_OK;
   RB_REQUIRE(a.hd % 2 == 0, "head_dim must be even for RoPE");
   cudaError_t e;
+  const int npairs = (a.nh + 2 * a.kvh) * a.hd / 2;
+  dim3 grid((unsigned)rows, (unsigned)((npairs + 255) / 256));
   if (a.act_dtype == REWB200_BF16)
-    e = launch_k(qkv_post_kernel<bf16>, dim3((unsigned)rows), dim3(256), 0, c->stream, c->use_pdl, a);
+    e = launch_k(qkv_post_kernel<bf16>, grid, dim3(256), 0, c->stream, c->use_pdl, a);
   else
-    e = launch_k(qkv_post_kernel<float>, dim3((unsigned)rows), dim3(256), 0, c->stream, c->use_pdl, a);
+    e = launch_k(qkv_post_kernel<float>, grid, dim3(256), 0, c->stream, c->use_pdl, a);
   RB_CUDA(e);
   ++g_launch_total;
   return REWB200_OK;
 }
 
-int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out_ids) {
+int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out_ids, void* scratch, size_t scratch_bytes) {
   if (rows == 0) return REWB200_OK;
-  RB_CUDA(launch_k(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, c->stream, c->use_pdl, logits, V, out_ids));
+  int nchunks = 1;
+  if (scratch && V >= 8192) {
+    nchunks = (int)std::min<int64_t>(64, (V + 4095) / 4096);
+    while (nchunks > 1 && (size_t)rows * nchunks * 8 > scratch_bytes) nchunks /= 2;
+  }
+  const int64_t chunk_w = (V + nchunks - 1) / nchunks;
+  float* pv = (float*)scratch;
+  int* pi = (int*)((char*)scratch + (size_t)rows * nchunks * 4);
+  RB_CUDA(launch_k(argmax_kernel, dim3((unsigned)rows, (unsigned)nchunks), dim3(256), 0, c->stream, c->use_pdl, logits, V,
+                   chunk_w, out_ids, pv, pi));
   ++g_launch_total;
+  if (nchunks > 1) {
+    RB_CUDA(launch_k(argmax_final_kernel, dim3((unsigned)rows), dim3(32), 0, c->stream, c->use_pdl, (const float*)pv,
+                     (const int*)pi, nchunks, out_ids));
+    ++g_launch_total;
+  }
   return REWB200_OK;
 }
 

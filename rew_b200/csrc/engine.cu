@@ -126,11 +126,13 @@ struct rewb200_session {
   int64_t logits_rows = 0;
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
+  void* argmax_scratch = nullptr;      // [B][64] (value, index) partials
   cudaGraphExec_t graph = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float prefill_ms = 0.f, decode_ms = 0.f;
   int host_pos = 0;                    // tokens so far (all sequences advance together)
   int graph_kernels = 0;               // kernels in one captured decode step
+  int graph_epoch = -1;                // option epoch the graph was captured under
 };
 
 namespace rewb {
@@ -430,7 +432,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     }
   }
   if (!o.all_logits) {
-    RB_TRY(argmax_launch(c, s->logits, s->B, cf.vocab, s->d_next));
+    RB_TRY(argmax_launch(c, s->logits, s->B, cf.vocab, s->d_next, s->argmax_scratch, (size_t)s->B * 64 * 8));
     RB_CUDA(launch_k(advance_kernel, dim3(1), dim3(256), 0, c->stream, c->use_pdl,
                      (const int*)s->d_next, s->d_ids, s->d_pos, s->d_out, s->d_step, s->B, o.S, s->out_capacity));
     ++g_launch_total;
@@ -675,6 +677,7 @@ int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_ses
   RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
   s->attn_scratch_bytes = attn_scratch_bytes(batch, m->nh_l, m->cfg.head_dim, 16);
   RB_CUDA(cudaMalloc((void**)&s->attn_scratch, s->attn_scratch_bytes));
+  RB_CUDA(cudaMalloc(&s->argmax_scratch, (size_t)batch * 64 * 8));
   RB_CUDA(cudaEventCreate(&s->ev0));
   RB_CUDA(cudaEventCreate(&s->ev1));
   RB_CUDA(cudaStreamSynchronize(c->stream));
@@ -691,7 +694,7 @@ void rewb200_session_free(rewb200_session* s) {
   for (void* p : s->kc) cudaFree(p);
   for (void* p : s->vc) cudaFree(p);
   void* ptrs[] = {s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
-                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch};
+                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   if (s->h_ids) cudaFreeHost(s->h_ids);
@@ -757,7 +760,12 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
   o.S = 1;
   const char* nograph = getenv("REW_B200_NO_GRAPH");
   const bool use_graph = !(nograph && nograph[0] == '1');
+  if (s->graph && s->graph_epoch != c->option_epoch) {
+    cudaGraphExecDestroy(s->graph);
+    s->graph = nullptr;
+  }
   if (use_graph && !s->graph && n_steps > 0) {
+    s->graph_epoch = c->option_epoch;
     cudaGraph_t g;
     const int64_t before = g_launch_total;
     RB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));

@@ -271,7 +271,9 @@ int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N) {
   const int nkb = (int)((K + BK - 1) / BK);
   const int target = 2 * c->sm_count;
   int split = 1;
-  while (tiles * split < target && nkb / (split * 2) >= 8 && split < 16) split *= 2;
+  // stop doubling once the CTA count would overshoot the resident slots by more than a quarter:
+  // every extra split is another f32 slab the consumer kernel has to read back
+  while (tiles * split * 2 <= target + target / 4 && nkb / (split * 2) >= 8 && split < 16) split *= 2;
   return split;
 }
 
@@ -284,6 +286,8 @@ int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_
   RB_REQUIRE(epi != EPI_SWIGLU_BF16 || plan.N % 16 == 0, "SwiGLU epilogue needs interleaved width % 16 == 0");
   if (M == 0) return REWB200_OK;
   const bool grouped = plan.groups > 1;
+  if (!grouped && (c->linear_impl == 2 || (c->linear_impl == 1 && M > 32)))
+    return linear_tc_launch(c, plan, x, ldx, M, epi, ksplit, out, ldo, bias);
   RB_REQUIRE(!grouped || (row_offsets != nullptr && ksplit == 1), "grouped Linear needs row offsets and no split-K");
   const int64_t rows_for_tile = grouped ? max_rows_per_group : M;
   const bool small = rows_for_tile <= 32;

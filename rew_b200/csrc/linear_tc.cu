@@ -1,0 +1,286 @@
+// bf16 Linear on the 5th-generation tensor cores (tcgen05.mma, accumulator in
+// tensor memory): y[M,N] = x[M,K] @ W[K,N] (+ b), src/rew/nn/linear.nim:43-49.
+//
+// Operand roles follow the reference's weight layout.  W is [in,out] row-major,
+// i.e. `out` is contiguous, which is an MN-major UMMA operand: W is the A
+// operand (UMMA M = 128 output features per CTA), the activations x[token][k]
+// (k contiguous, K-major) are the B operand (UMMA N = TN tokens).  The f32
+// accumulator D[feature][token] lives in TMEM: lane = output feature, column =
+// token.
+//
+// Roles inside the CTA (192 threads):
+//   warp 0   TMA producer: cp.async.bulk.tensor boxes of W (64 k x 64 features,
+//            two per stage) and x (64 k x TN tokens), 128-byte swizzle, into a
+//            multi-stage mbarrier ring; W loads are issued before
+//            griddepcontrol.wait so the ramp overlaps the previous kernel.
+//   warp 1   allocates TMEM, then one elected thread issues four
+//            tcgen05.mma.kind::f16 (K = 16 each) per stage from shared-memory
+//            descriptors and releases the stage with tcgen05.commit.
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp owns 32 lanes),
+//            apply bias / SwiGLU, store.
+// All waits are bounded; on a timeout the roles fall through to the common
+// exit, where TMEM is released.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace rewb {
+namespace {
+
+constexpr int BM = 128;  // output features per CTA
+constexpr int BK = 64;
+constexpr int A_BYTES = 2 * BK * 64 * 2;  // two 64x64 boxes
+
+template <int TN>
+struct TcCfg {
+  static constexpr int STAGES = (TN <= 64) ? 5 : (TN <= 128 ? 5 : 4);
+  static constexpr int B_BYTES = TN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
+};
+
+struct TcArgs {
+  int64_t M, N, K;
+  int kb_per_split;
+  int epi;
+  void* out;
+  int64_t ldo;
+  int64_t split_stride;
+  const float* bias;
+  int* status;
+};
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  // start address, leading / stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x * (1.0f / (1.0f + __expf(-x))); }
+
+template <int TN>
+__global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                         const __grid_constant__ CUtensorMap tmX, TcArgs a) {
+  using C = TcCfg<TN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tmem_full = empty + C::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col0 = blockIdx.x * BM;          // first output feature of the tile
+  const int row0 = blockIdx.y * TN;          // first token of the tile
+  const int split = blockIdx.z;
+  const int rows_valid = (int)min((int64_t)TN, a.M - row0);
+  const int nkb_total = (int)((a.K + BK - 1) / BK);
+  const int kb0 = split * a.kb_per_split;
+  const int nkb = max(0, min(a.kb_per_split, nkb_total - kb0));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    fence_barrier_init();
+    pdl_launch_dependents();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      tma_prefetch_desc(&tmX);
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      const int pre = min(C::STAGES, nkb);
+      for (int kb = 0; kb < pre; ++kb) {
+        uint8_t* st = smem + kb * C::STAGE_BYTES;
+        mbar_expect_tx(&full[kb], C::STAGE_BYTES);
+        const int k = (kb0 + kb) * BK;
+        tma_load_2d_hint(st, &tmW, &full[kb], col0, k, pol_w);
+        tma_load_2d_hint(st + A_BYTES / 2, &tmW, &full[kb], col0 + 64, k, pol_w);
+      }
+      pdl_wait();
+      for (int kb = 0; kb < pre; ++kb)
+        tma_load_2d_hint(smem + kb * C::STAGE_BYTES + A_BYTES, &tmX, &full[kb], (kb0 + kb) * BK, row0, pol_x);
+      for (int kb = pre; kb < nkb; ++kb) {
+        const int s = kb % C::STAGES;
+        if (!mbar_wait(&empty[s], ((kb / C::STAGES) - 1) & 1, a.status)) break;
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        mbar_expect_tx(&full[s], C::STAGE_BYTES);
+        const int k = (kb0 + kb) * BK;
+        tma_load_2d_hint(st, &tmW, &full[s], col0, k, pol_w);
+        tma_load_2d_hint(st + A_BYTES / 2, &tmW, &full[s], col0 + 64, k, pol_w);
+        tma_load_2d_hint(st + A_BYTES, &tmX, &full[s], k, row0, pol_x);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nkb > 0) {
+      // instruction descriptor: D f32, A/B bf16, A MN-major, B K-major, N = TN, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(TN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      const uint32_t smem_base = smem_u32(smem);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % C::STAGES;
+        ok = mbar_wait(&full[s], (kb / C::STAGES) & 1, a.status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sa = smem_base + s * C::STAGE_BYTES;
+        const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk) {
+          // A: 16 k-rows of 128 bytes = two 8-row swizzle atoms 1024 B apart (SBO); the second
+          //    64-feature box is 8192 B further (LBO).  B: rows of 128 B, 8-row atoms 1024 B apart.
+          const uint64_t da = smem_desc(sa + kk * 2048, A_BYTES / 2, 1024);
+          const uint64_t db = smem_desc(sb + kk * 32, 16, 1024);
+          umma_bf16(tmem_base, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);  // stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(tmem_full);
+    }
+  } else {
+    // ---------------- epilogue warps 2..5; TMEM lanes 32*(warp%4) .. +31
+    const int q = warp & 3;
+    bool ok = true;
+    if (nkb > 0) {
+      ok = mbar_wait(tmem_full, 0, a.status);
+      tc_fence_after();
+    }
+    pdl_wait();
+    if (ok) {
+      const int64_t feat = (int64_t)col0 + q * 32 + lane;
+      const bool feat_ok = feat < a.N;
+      const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        uint32_t r[32];
+        if (nkb > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (c0 >= rows_valid) break;
+        if (a.epi == EPI_SWIGLU_BF16) {
+          // gate features sit in lanes with (lane % 16) < 8, their up partners 8 lanes higher
+          const bool is_gate = (lane & 15) < 8;
+          const int64_t oc = ((int64_t)col0 + q * 32) / 2 + (lane >> 4) * 8 + (lane & 7);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = __uint_as_float(r[j]) + bias_v;
+            const float up = __shfl_down_sync(0xffffffffu, v, 8);
+            if (is_gate && feat_ok && c0 + j < rows_valid)
+              reinterpret_cast<bf16*>(a.out)[(int64_t)(row0 + c0 + j) * a.ldo + oc] = __float2bfloat16_rn(silu_f(v) * up);
+          }
+        } else if (feat_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (c0 + j >= rows_valid) break;
+            const float v = __uint_as_float(r[j]) + bias_v;
+            const int64_t grow = row0 + c0 + j;
+            if (a.epi == EPI_PARTIAL_F32)
+              reinterpret_cast<float*>(a.out)[split * a.split_stride + grow * a.ldo + feat] = v;
+            else if (a.epi == EPI_BIAS_F32)
+              reinterpret_cast<float*>(a.out)[grow * a.ldo + feat] = v;
+            else
+              reinterpret_cast<bf16*>(a.out)[grow * a.ldo + feat] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+  }
+}
+
+template <int TN>
+int launch_tn(Ctx* c, const LinearBf16Plan& plan, const CUtensorMap& tmX, const TcArgs& a, dim3 grid) {
+  using C = TcCfg<TN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    RB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    attr_set = true;
+  }
+  RB_CUDA(launch_k(linear_tc_kernel<TN>, grid, dim3(192), (size_t)C::SMEM, c->stream, c->use_pdl, plan.tmW, tmX, a));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+}  // namespace
+
+// Same contract as linear_bf16_launch (ungrouped).
+int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, int ksplit,
+                     void* out, int64_t ldo, const float* bias) {
+  RB_REQUIRE(plan.groups == 1, "the tcgen05 Linear does not take grouped weights");
+  RB_REQUIRE(ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0, "bf16 Linear: activations must be 16-byte aligned rows");
+  RB_REQUIRE(ksplit >= 1 && (ksplit == 1 || epi == EPI_PARTIAL_F32), "split-K needs the partial epilogue");
+  RB_REQUIRE(epi != EPI_SWIGLU_BF16 || plan.N % 16 == 0, "SwiGLU epilogue needs interleaved width % 16 == 0");
+  if (M == 0) return REWB200_OK;
+  const int TN = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+  CUtensorMap tmX;
+  RB_TRY(make_tmap_2d_bf16(&tmX, x, (uint64_t)plan.K, (uint64_t)M, (uint64_t)ldx * 2, 64, TN));
+  TcArgs a;
+  a.M = M;
+  a.N = plan.N;
+  a.K = plan.K;
+  const int nkb = (int)((plan.K + BK - 1) / BK);
+  a.kb_per_split = (nkb + ksplit - 1) / ksplit;
+  a.epi = epi;
+  a.out = out;
+  a.ldo = ldo;
+  a.split_stride = M * ldo;
+  a.bias = bias;
+  a.status = c->d_status;
+  dim3 grid((unsigned)((plan.N + BM - 1) / BM), (unsigned)((M + TN - 1) / TN), (unsigned)ksplit);
+  switch (TN) {
+    case 32: return launch_tn<32>(c, plan, tmX, a, grid);
+    case 64: return launch_tn<64>(c, plan, tmX, a, grid);
+    case 128: return launch_tn<128>(c, plan, tmX, a, grid);
+    default: return launch_tn<256>(c, plan, tmX, a, grid);
+  }
+}
+
+}  // namespace rewb

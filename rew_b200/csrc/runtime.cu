@@ -184,6 +184,8 @@ int rewb200_init(const int* device_ordinals, int n) {
     RB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh));
     const char* pdl = getenv("REW_B200_PDL");
     c->use_pdl = !(pdl && pdl[0] == '0');
+    const char* li = getenv("REW_B200_LINEAR");
+    if (li) c->linear_impl = !strcmp(li, "mma") ? 0 : (!strcmp(li, "tc_prefill") ? 1 : 2);
     g_ctx.push_back(c);
   }
   RB_CUDA(cudaSetDevice(g_ctx[0]->device));
@@ -229,6 +231,24 @@ int rewb200_sync(int slot, int timeout_ms) {
   }
   cudaEventDestroy(ev);
   return ctx_check_status(c);
+}
+
+int rewb200_set_option(int slot, const char* key, const char* value) {
+  Ctx* c = ctx_get(slot);
+  if (!c) return REWB200_ERR;
+  RB_REQUIRE(key && value, "rewb200_set_option: NULL argument");
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  const std::string k(key), v(value);
+  if (k == "linear") {
+    RB_REQUIRE(v == "mma" || v == "tc_prefill" || v == "tc", "option linear: expected mma, tc_prefill or tc");
+    c->linear_impl = v == "tc" ? 2 : (v == "tc_prefill" ? 1 : 0);
+  } else if (k == "pdl") {
+    c->use_pdl = v != "0";
+  } else {
+    return fail("rewb200_set_option: unknown option '" + k + "'");
+  }
+  ++c->option_epoch;
+  return REWB200_OK;
 }
 
 int64_t rewb200_launch_count(int slot) {

@@ -1,0 +1,57 @@
+"""The tcgen05 / tensor-memory Linear against the oracle and against the mma.sync Linear,
+through the C ABI (option "linear" = "tc")."""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from rew_b200 import weights as W
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def rb_tc():
+    from rew_b200 import _lib, api
+    _lib.init()
+    api.set_option("linear", "tc")
+    yield api
+    api.set_option("linear", "tc")  # the default
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 64, 8), (32, 64, 128), (32, 4096, 1024), (7, 688, 256), (32, 256, 1376),
+                                   (33, 128, 136), (64, 512, 256), (100, 320, 264), (128, 1024, 384),
+                                   (200, 320, 264), (256, 2048, 512), (300, 576, 640)])
+def test_tc_linear_shapes(rb_tc, orc, M, K, N):
+    from rew_b200 import _lib
+    rng = np.random.default_rng(M * 1000 + N)
+    x = orc.bf16_round(rng.normal(size=(M, K)))
+    w = orc.bf16_round(rng.normal(0, 0.05, size=(K, N)))
+    b = rng.normal(0, 0.1, size=(N,)).astype(np.float32)
+    want = orc.linear(x, w, b)
+    T = rb_tc.Tensor.from_host
+    got = rb_tc.Linear(T(w, _lib.BF16), T(b)).forward(T(x, _lib.BF16)).to_host()
+    assert got.shape == (M, N)
+    assert rel_l2(got, want) < 5e-3
+
+
+def test_tc_model_matches_oracle_and_mma_path(rb_tc, orc):
+    """Whole bf16 model on the tcgen05 Linear: split-K partial, SwiGLU and f32-logit epilogues."""
+    from rew_b200 import _lib
+    cfg = W.ModelConfig(vocab=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=64, ffn=688, max_seq=256,
+                        theta=500000.0, dtype=_lib.BF16, mask_kind=1)
+    t = [orc.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(cfg, seed=4, std=0.05, trivial_affine=False)]
+    for B, S in ((3, 70), (32, 16), (2, 150)):
+        prompt = np.random.default_rng(B).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+        sess = rb_tc.CausalLM(cfg).load(t).session(B, S + 8)
+        nxt, logits = sess.forward(prompt, want_logits=True)
+        want = orc.model_forward(cfg, t, prompt, 0, True)[:, -1]
+        assert rel_l2(logits, want) <= 2e-2
+        ids, last = sess.decode(3, want_logits=True)
+        seq = np.concatenate([prompt, nxt[:, None], ids[:, :2]], 1)
+        want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
+        assert rel_l2(last, want) <= 2e-2
+        rb_tc.set_option("linear", "mma")
+        sess2 = rb_tc.CausalLM(cfg).load(t).session(B, S + 8)
+        _, logits_mma = sess2.forward(prompt, want_logits=True)
+        rb_tc.set_option("linear", "tc")
+        assert rel_l2(logits, logits_mma) <= 1e-2
