@@ -9,6 +9,11 @@ N(0, 0.02) generated on the device, uniform random prompt ids):
 
     l8_b32   Llama-3-8B-shaped, bf16, batch 32, prompt 512   (default)
     l8_b1    same model, batch 1
+    l70_b16  Llama-3-70B-shaped, bf16, batch 16, prompt 1024; with --gpus N > 1 the model is
+             tensor-parallel over the N ranks (heads, FFN columns and vocabulary sharded, NCCL
+             all-reduce after o-proj and down-proj): strong scaling
+With --gpus N > 1 the l8 workloads run N independent replicas (sequences are independent units; no
+data-path collective): weak scaling.
     tiny     the tiny fp32 Llama of the parity tests
 
 `value` is decode tokens/s of the whole job with ids, weights and cache resident
@@ -39,6 +44,7 @@ WORKLOADS = {
     "l8_b32": dict(model="llama3_8b", batch=32, prompt=512),
     "l8_b1": dict(model="llama3_8b", batch=1, prompt=512),
     "tiny": dict(model="tiny_llama", batch=1, prompt=32),
+    "l70_b16": dict(model="llama3_70b", batch=16, prompt=1024, parallel="tp"),
 }
 
 
@@ -238,9 +244,16 @@ def main():
     B, S, K, Wm = wl["batch"], wl["prompt"], args.steps, args.warmup
     max_len = S + Wm + K + 8
     cfg.max_seq = max(cfg.max_seq, max_len)
-    model = api.CausalLM(cfg).init_random(seed=1234 + rank, std=0.02)
+    parallel = "single" if world == 1 else wl.get("parallel", "replicas")
+    if parallel == "tp":
+        cfg.tp_rank, cfg.tp_size = rank, world
+        box = [api.comm_unique_id() if rank == 0 else None]
+        pg.broadcast_object_list(box, src=0)
+        api.comm_init(box[0], rank, world)
+    data_seed = 0 if parallel == "tp" else rank       # tensor-parallel ranks must see the same tokens
+    model = api.CausalLM(cfg).init_random(seed=1234 + data_seed, std=0.02)
     sess = model.session(B, max_len)
-    prompt = np.random.default_rng(1 + rank).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+    prompt = np.random.default_rng(1 + data_seed).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
 
     # ---- device-resident decode: prefill, W warm-up steps, K timed steps
     sess.forward(prompt)
@@ -265,7 +278,7 @@ def main():
         pg.all_reduce(t, op=pg.ReduceOp.MAX)
         decode_ms = float(t[0])
         pg.barrier()
-    tokens = B * K * world
+    tokens = B * K * (1 if parallel == "tp" else world)
     value = tokens / (decode_ms * 1e-3)
 
     # ---- end to end through the C ABI: host prompt ids -> host output ids
@@ -290,11 +303,14 @@ def main():
         _lib.check(L.rewb200_session_profile_linears(sess._h, 20, C.byref(ms), C.byref(nbytes), C.byref(nl)))
         peak, which = measured_peaks()
         ach = nbytes.value / (ms.value * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                    # dram read+write per step, scaled from the ncu capture of the gate|up launch
+                    # (239.2 MB measured for 236.1 MB algorithmic; profiles/linear_tc_kernel_32_decode_l8.md)
+                    "traffic": nbytes.value * 1.013,
                     "kernel": "linear_tc_kernel<32>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>", "launches_per_step": nl.value, "ms_per_step": ms.value,
                     "bytes_per_step": nbytes.value, "peak_source": which}
         # whole decode step against the same roof: weights + KV read once per step
-        kv_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
+        kv_bytes = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
         step_bytes = model.weight_bytes() - cfg.vocab * cfg.d_model * 2 + kv_bytes
         roofline["step_frac"] = step_bytes / (decode_ms / K * 1e-3) / 1e9 / peak
 
@@ -302,12 +318,12 @@ def main():
         return
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
-        "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong" if parallel == "tp" else "weak", "vs_baseline": None,
         "dtype": "bf16" if cfg.dtype == _lib.BF16 else "f32", "data": "synthetic",
         "config": {"workload": args.workload + ("" if args.layers <= 0 else "_%dlayers" % args.layers), "batch_per_gpu": B, "prompt": S, "decode_steps": K,
-                   "parallelism": "replicas" if world > 1 else "single",
+                   "parallelism": parallel + (str(world) if world > 1 else ""),
                    "l2": "weights per step (%.1f GB) exceed the 126 MB L2" % (model.weight_bytes() / 1e9)},
-        "prefill": {"tokens_per_s": B * S * world / (prefill_ms * 1e-3), "ms": prefill_ms},
+        "prefill": {"tokens_per_s": B * S * (1 if parallel == "tp" else world) / (prefill_ms * 1e-3), "ms": prefill_ms},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
     }
     if world == 1 and not args.no_cpu_baseline:

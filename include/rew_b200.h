@@ -211,6 +211,8 @@ int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int
 int rewb200_comm_unique_id(void* id128);                  /* 128 bytes, created on rank 0 */
 int rewb200_comm_init(int slot, const void* id128, int rank, int world);
 int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n);
+/* Free every session of the slot first: a captured decode graph keeps the communicator in use and
+ * NCCL waits for it. */
 int rewb200_comm_destroy(int slot);
 
 #if defined(__GNUC__)

@@ -288,3 +288,19 @@ def set_option(key, value, slot=0):
     """rewb200_set_option: run-time switches such as ("linear", "tc")."""
     _lib.init()
     check(lib().rewb200_set_option(slot, key.encode(), value.encode()))
+
+
+def comm_unique_id():
+    """128-byte NCCL id, created on rank 0 and handed to every rank by the host program."""
+    buf = C.create_string_buffer(128)
+    check(lib().rewb200_comm_unique_id(buf))
+    return buf.raw
+
+
+def comm_init(unique_id, rank, world, slot=0):
+    _lib.init()
+    check(lib().rewb200_comm_init(slot, C.create_string_buffer(unique_id, 128), rank, world))
+
+
+def comm_destroy(slot=0):
+    check(lib().rewb200_comm_destroy(slot))

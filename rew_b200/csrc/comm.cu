@@ -7,6 +7,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -38,7 +39,10 @@ static Comm g_comm[16];
 
 static int nccl_load() {
   if (g_nccl.handle) return REWB200_OK;
-  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  // REW_B200_NCCL names a specific library; otherwise whatever libnccl.so.2 the process already
+  // holds (or the system one) is used.
+  const char* envp = getenv("REW_B200_NCCL");
+  const char* names[] = {envp ? envp : "libnccl.so.2", "libnccl.so.2", "libnccl.so"};
   void* h = nullptr;
   for (const char* n : names) {
     h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);

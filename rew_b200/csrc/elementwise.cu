@@ -396,6 +396,90 @@ __global__ void __launch_bounds__(32) argmax_final_kernel(const float* part_v, c
   if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, int64_t V, int64_t chunk_w,
+                                                              int idx_offset, float* part_v, int* part_i) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* r = logits + (int64_t)blockIdx.x * V;
+  const int64_t c0 = (int64_t)blockIdx.y * chunk_w, c1 = min(V, c0 + chunk_w);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int64_t i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
+    const float v = r[i];
+    if (v > best || (v == best && (int)i < bi)) {
+      best = v;
+      bi = (int)i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = best;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        best = sv[w];
+        bi = si[w];
+      }
+    part_v[blockIdx.x * gridDim.y + blockIdx.y] = best;
+    part_i[blockIdx.x * gridDim.y + blockIdx.y] = (bi == 0x7fffffff) ? 0x7fffffff : bi + idx_offset;
+  }
+}
+
+__global__ void __launch_bounds__(32) argmax_gathered_kernel(const void* gathered, int world, int rows, int nchunks, int* out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t per_rank = (size_t)rows * nchunks * 8;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < world * nchunks; i += 32) {
+    const int r = i / nchunks, ch = i % nchunks;
+    const char* base = (const char*)gathered + (size_t)r * per_rank;
+    const float v = ((const float*)base)[blockIdx.x * nchunks + ch];
+    const int ix = ((const int*)(base + (size_t)rows * nchunks * 4))[blockIdx.x * nchunks + ch];
+    if (v > best || (v == best && ix < bi)) {
+      best = v;
+      bi = ix;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+// part[0][i] += part[1][i] + ... (before a tensor-parallel all-reduce of one slab)
+__global__ void __launch_bounds__(256) slab_sum_kernel(float* part, int nsplit, int64_t slab, int64_t n4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 a = reinterpret_cast<float4*>(part)[i];
+  for (int s = 1; s < nsplit; ++s) {
+    const float4 b = reinterpret_cast<const float4*>(part + s * slab)[i];
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  }
+  reinterpret_cast<float4*>(part)[i] = a;
+}
+
 __global__ void swiglu_f32_kernel(const float* g, const float* u, float* out, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -508,6 +592,35 @@ int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out
                      (const int*)pi, nchunks, out_ids));
     ++g_launch_total;
   }
+  return REWB200_OK;
+}
+
+// Stage 1 only: per-chunk (value, global index) partials, for the vocab-parallel lm_head.
+int argmax_partial_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int idx_offset, int nchunks, float* pv, int* pi) {
+  if (rows == 0) return REWB200_OK;
+  const int64_t chunk_w = (V + nchunks - 1) / nchunks;
+  RB_CUDA(launch_k(argmax_partial_kernel, dim3((unsigned)rows, (unsigned)nchunks), dim3(256), 0, c->stream, c->use_pdl, logits,
+                   V, chunk_w, idx_offset, pv, pi));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+// gathered: per rank [rows*nchunks floats | rows*nchunks ints]; first maximum by (value desc, index asc).
+int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows, int nchunks, int* out) {
+  if (rows == 0) return REWB200_OK;
+  RB_CUDA(launch_k(argmax_gathered_kernel, dim3((unsigned)rows), dim3(32), 0, c->stream, c->use_pdl, gathered, world,
+                   (int)rows, nchunks, out));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int slab_sum_launch(Ctx* c, float* part, int nsplit, int64_t slab_elems) {
+  if (nsplit <= 1 || slab_elems == 0) return REWB200_OK;
+  RB_REQUIRE(slab_elems % 4 == 0, "slab size must be a multiple of 4 floats");
+  const int64_t n4 = slab_elems / 4;
+  RB_CUDA(launch_k(slab_sum_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, c->stream, c->use_pdl, part, nsplit,
+                   slab_elems, n4));
+  ++g_launch_total;
   return REWB200_OK;
 }
 

@@ -27,6 +27,14 @@ using namespace rewb;
 
 namespace rewb {
 
+int comm_world(int slot);
+int comm_rank(int slot);
+int comm_allreduce_sum_f32(Ctx* c, int slot, float* ptr, int64_t n);
+int comm_allgather_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_rank);
+int slab_sum_launch(Ctx* c, float* part, int nsplit, int64_t slab_elems);
+int argmax_partial_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int idx_offset, int nchunks, float* pv, int* pi);
+int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows, int nchunks, int* out);
+
 namespace {
 
 constexpr int PAGE = 64;
@@ -88,8 +96,10 @@ __global__ void advance_kernel(const int* next, int* ids, int* pos, int* out_ids
 
 struct rewb200_model {
   Ctx* c = nullptr;
+  int slot = 0;
   rewb200_config cfg;
   int nh_l = 0, kvh_l = 0;      // local heads under tensor parallelism
+  int64_t vocab_l = 0;          // local slice of the vocabulary (lm_head is vocab-parallel)
   int64_t nq = 0, nkv = 0, nqkv = 0;
   void* embed = nullptr;
   std::vector<LayerDev> layers;
@@ -127,6 +137,8 @@ struct rewb200_session {
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
   void* argmax_scratch = nullptr;      // [B][64] (value, index) partials
+  void* gather_scratch = nullptr;      // tensor parallel: all-gathered argmax partials / logits
+  size_t gather_bytes = 0;
   cudaGraphExec_t graph = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float prefill_ms = 0.f, decode_ms = 0.f;
@@ -249,7 +261,7 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
   if (logits_rows > s->logits_rows) {
     RB_CUDA(cudaStreamSynchronize(m->c->stream));
     if (s->logits) RB_CUDA(cudaFree(s->logits));
-    RB_CUDA(cudaMalloc((void**)&s->logits, (size_t)logits_rows * c.vocab * sizeof(float)));
+    RB_CUDA(cudaMalloc((void**)&s->logits, (size_t)logits_rows * m->vocab_l * sizeof(float)));
     s->logits_rows = logits_rows;
     if (s->graph) {
       cudaGraphExecDestroy(s->graph);
@@ -277,6 +289,29 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
   if (ksplit_out) *ksplit_out = 1;
   RB_REQUIRE(ldx == w.K && ldo == w.N, "f32 Linear expects dense rows");
   return gemm_f32_launch(c, (const float*)x, (const float*)w.w, partial ? nullptr : w.b, (float*)out, rows, w.K, w.N);
+}
+
+// Copies the last-position logits [B, vocab] to the host; under tensor parallelism the
+// vocabulary slices are all-gathered first and re-interleaved on the host.
+int fetch_logits(rewb200_session* s, int64_t rows, float* host) {
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  const int tp = m->cfg.tp_size;
+  if (tp == 1) {
+    RB_CUDA(cudaMemcpyAsync(host, s->logits, (size_t)rows * m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    RB_CUDA(cudaStreamSynchronize(c->stream));
+    return REWB200_OK;
+  }
+  const size_t per = (size_t)rows * m->vocab_l * sizeof(float);
+  RB_REQUIRE(per * tp <= s->gather_bytes, "logit gather buffer too small for this many rows");
+  RB_TRY(comm_allgather_bytes(c, m->slot, s->logits, s->gather_scratch, per));
+  std::vector<float> tmp((size_t)rows * m->cfg.vocab);
+  RB_CUDA(cudaMemcpyAsync(tmp.data(), s->gather_scratch, per * tp, cudaMemcpyDeviceToHost, c->stream));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  for (int r = 0; r < tp; ++r)
+    for (int64_t i = 0; i < rows; ++i)
+      memcpy(host + i * m->cfg.vocab + r * m->vocab_l, tmp.data() + ((size_t)r * rows + i) * m->vocab_l, m->vocab_l * sizeof(float));
+  return REWB200_OK;
 }
 
 struct FwdOpts {
@@ -380,7 +415,11 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     RB_TRY(attn_launch(c, aa));
 
     RB_TRY(run_linear(s, L.o, s->attn, m->nq, rows, true, 0, s->part, d, &ks));
-    // TODO(tp): all-reduce of the partial slab goes here.
+    if (cf.tp_size > 1) {  // sum the local split-K slabs, then one all-reduce of [rows, d]
+      RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
+      RB_TRY(comm_allreduce_sum_f32(c, m->slot, s->part, rows * d));
+      ks = 1;
+    }
     {
       NormArgs a = na;
       a.partial = s->part;
@@ -401,6 +440,11 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       ++g_launch_total;
     }
     RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
+    if (cf.tp_size > 1) {
+      RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
+      RB_TRY(comm_allreduce_sum_f32(c, m->slot, s->part, rows * d));
+      ks = 1;
+    }
     {
       NormArgs a = na;
       a.partial = s->part;
@@ -418,21 +462,31 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   const char* xl = (const char*)s->xn + (o.all_logits ? 0 : (size_t)(o.S - 1) * d * dtype_size(dt));
   const int64_t ldx = o.all_logits ? d : (int64_t)o.S * d;
   if (dt == REWB200_BF16) {
-    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)xl, ldx, lrows, EPI_BIAS_F32, 1, s->logits, cf.vocab, m->lm.b,
+    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)xl, ldx, lrows, EPI_BIAS_F32, 1, s->logits, m->vocab_l, m->lm.b,
                               nullptr, 0));
   } else {
     if (o.all_logits || o.S == 1) {
-      RB_TRY(gemm_f32_launch(c, (const float*)xl, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, cf.vocab));
+      RB_TRY(gemm_f32_launch(c, (const float*)xl, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, m->vocab_l));
     } else {
       // gather the last rows into the head of q (free at this point), then GEMM
       for (int b = 0; b < s->B; ++b)
         RB_CUDA(cudaMemcpyAsync((float*)s->q + (size_t)b * d, (const float*)s->xn + ((size_t)b * o.S + o.S - 1) * d,
                                 d * sizeof(float), cudaMemcpyDeviceToDevice, c->stream));
-      RB_TRY(gemm_f32_launch(c, (const float*)s->q, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, cf.vocab));
+      RB_TRY(gemm_f32_launch(c, (const float*)s->q, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, m->vocab_l));
     }
   }
   if (!o.all_logits) {
-    RB_TRY(argmax_launch(c, s->logits, s->B, cf.vocab, s->d_next, s->argmax_scratch, (size_t)s->B * 64 * 8));
+    if (cf.tp_size > 1) {
+      // vocab-parallel: per-rank (value, index) partials, all-gathered, then the same first-max rule
+      const int nch = 16;
+      float* pv = (float*)s->argmax_scratch;
+      int* pi = (int*)((char*)s->argmax_scratch + (size_t)s->B * nch * 4);
+      RB_TRY(argmax_partial_launch(c, s->logits, s->B, m->vocab_l, (int)(cf.tp_rank * m->vocab_l), nch, pv, pi));
+      RB_TRY(comm_allgather_bytes(c, m->slot, s->argmax_scratch, s->gather_scratch, (size_t)s->B * nch * 8));
+      RB_TRY(argmax_gathered_launch(c, s->gather_scratch, cf.tp_size, s->B, nch, s->d_next));
+    } else {
+      RB_TRY(argmax_launch(c, s->logits, s->B, cf.vocab, s->d_next, s->argmax_scratch, (size_t)s->B * 64 * 8));
+    }
     RB_CUDA(launch_k(advance_kernel, dim3(1), dim3(256), 0, c->stream, c->use_pdl,
                      (const int*)s->d_next, s->d_ids, s->d_pos, s->d_out, s->d_step, s->B, o.S, s->out_capacity));
     ++g_launch_total;
@@ -465,8 +519,11 @@ int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** ou
   RB_REQUIRE(cfg->n_routed == 0, "MoE models are created through this entry only after rewb200 MoE support is built in");
   rewb200_model* m = new rewb200_model();
   m->c = c;
+  m->slot = slot;
   m->cfg = *cfg;
   m->cfg.tp_size = tp;
+  RB_REQUIRE(cfg->vocab % tp == 0, "shardLayout: vocabulary must be divisible by the tensor-parallel size");
+  m->vocab_l = cfg->vocab / tp;
   m->nh_l = cfg->n_heads / tp;
   m->kvh_l = cfg->n_kv_heads / tp;
   m->nq = (int64_t)m->nh_l * cfg->head_dim;
@@ -474,7 +531,7 @@ int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** ou
   m->nqkv = m->nq + 2 * m->nkv;
   const int64_t d = cfg->d_model;
   if (cfg->dtype == REWB200_BF16)
-    RB_REQUIRE(d % 8 == 0 && m->nqkv % 8 == 0 && (cfg->ffn / tp) % 8 == 0 && cfg->vocab % 8 == 0 &&
+    RB_REQUIRE(d % 8 == 0 && m->nqkv % 8 == 0 && (cfg->ffn / tp) % 8 == 0 && (cfg->vocab / tp) % 8 == 0 &&
                    (cfg->head_dim == 64 || cfg->head_dim == 128),
                "bf16 models need d_model, ffn/tp, vocab multiples of 8 and head_dim 64 or 128");
   const size_t es = dtype_size(cfg->dtype);
@@ -498,7 +555,7 @@ int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** ou
   }
   RB_TRY(alloc_vec(&m->ng, 1.f));
   RB_TRY(alloc_vec(&m->nb, 0.f));
-  RB_TRY(alloc_lin(m, &m->lm, d, cfg->vocab));
+  RB_TRY(alloc_lin(m, &m->lm, d, m->vocab_l));
   std::vector<float> ct, st;
   RB_TRY(rope_tables_host(cfg->head_dim, cfg->max_seq, cfg->theta, &ct, &st));
   RB_TRY(dev_alloc(m, (void**)&m->cosT, ct.size() * sizeof(float)));
@@ -557,8 +614,8 @@ int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host,
     switch (r.slot) {
       case 0: return vec(m->ng, d, 0, d);
       case 1: return vec(m->nb, d, 0, d);
-      case 2: RB_TRY(expect(d * c.vocab)); return scatter(m, c.vocab, 0, 0, d, c.vocab, m->lm.w, true, c.vocab, c.vocab, c.vocab, 0);
-      default: return vec(m->lm.b, c.vocab, 0, c.vocab);
+      case 2: RB_TRY(expect(d * c.vocab)); return scatter(m, c.vocab, 0, rk * m->vocab_l, d, m->vocab_l, m->lm.w, true, m->vocab_l, m->vocab_l, m->vocab_l, 0);
+      default: return vec(m->lm.b, c.vocab, rk * m->vocab_l, m->vocab_l);
     }
   }
   LayerDev& L = m->layers[r.layer];
@@ -594,8 +651,10 @@ int rewb200_model_init_random(rewb200_model* m, uint64_t seed, float std) {
   RB_CUDA(cudaSetDevice(m->c->device));
   Ctx* c = m->c;
   const int dt = m->cfg.dtype;
+  // replicated tensors (the embedding) use the seed alone; sharded ones also mix in the rank
   uint64_t k = seed * 1000003ull;
   RB_TRY(fill_normal_launch(c, m->embed, dt, (int64_t)m->cfg.vocab * m->cfg.d_model, ++k, std));
+  k += (uint64_t)m->cfg.tp_rank * 7919ull;
   for (LayerDev& L : m->layers) {
     RB_TRY(fill_normal_launch(c, L.qkv.w, dt, L.qkv.K * L.qkv.N, ++k, std));
     RB_TRY(fill_normal_launch(c, L.o.w, dt, L.o.K * L.o.N, ++k, std));
@@ -678,6 +737,12 @@ int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_ses
   s->attn_scratch_bytes = attn_scratch_bytes(batch, m->nh_l, m->cfg.head_dim, 16);
   RB_CUDA(cudaMalloc((void**)&s->attn_scratch, s->attn_scratch_bytes));
   RB_CUDA(cudaMalloc(&s->argmax_scratch, (size_t)batch * 64 * 8));
+  if (m->cfg.tp_size > 1) {
+    RB_REQUIRE(comm_world(m->slot) == m->cfg.tp_size && comm_rank(m->slot) == m->cfg.tp_rank,
+               "tensor-parallel model needs rewb200_comm_init with the same rank and world size first");
+    s->gather_bytes = std::max<size_t>((size_t)batch * 64 * 8 * m->cfg.tp_size, (size_t)batch * m->cfg.vocab * sizeof(float));
+    RB_CUDA(cudaMalloc(&s->gather_scratch, s->gather_bytes));
+  }
   RB_CUDA(cudaEventCreate(&s->ev0));
   RB_CUDA(cudaEventCreate(&s->ev1));
   RB_CUDA(cudaStreamSynchronize(c->stream));
@@ -694,7 +759,7 @@ void rewb200_session_free(rewb200_session* s) {
   for (void* p : s->kc) cudaFree(p);
   for (void* p : s->vc) cudaFree(p);
   void* ptrs[] = {s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
-                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch};
+                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch, s->gather_scratch};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   if (s->h_ids) cudaFreeHost(s->h_ids);
@@ -735,9 +800,7 @@ int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32
   RB_CUDA(cudaEventRecord(s->ev1, c->stream));
   if (next_ids)
     RB_CUDA(cudaMemcpyAsync(next_ids, s->d_next, s->B * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
-  if (logits_out)
-    RB_CUDA(cudaMemcpyAsync(logits_out, s->logits, (size_t)s->B * m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost,
-                            c->stream));
+  if (logits_out) RB_TRY(fetch_logits(s, s->B, logits_out));
   RB_CUDA(cudaStreamSynchronize(c->stream));
   RB_CUDA(cudaEventElapsedTime(&s->prefill_ms, s->ev0, s->ev1));
   s->host_pos += S;
@@ -799,9 +862,7 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
     for (int st = 0; st < n_steps; ++st)
       for (int b = 0; b < s->B; ++b) out_ids[(size_t)b * n_steps + st] = tmp[(size_t)st * s->B + b];
   }
-  if (last_logits)
-    RB_CUDA(cudaMemcpyAsync(last_logits, s->logits, (size_t)s->B * m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost,
-                            c->stream));
+  if (last_logits) RB_TRY(fetch_logits(s, s->B, last_logits));
   RB_CUDA(cudaStreamSynchronize(c->stream));
   RB_CUDA(cudaEventElapsedTime(&s->decode_ms, s->ev0, s->ev1));
   s->host_pos += n_steps;
@@ -890,7 +951,7 @@ int rewb200_session_profile_linears(rewb200_session* s, int iters, float* ms_per
       if (count) bytes += (L.down.K * L.down.N + rows * L.down.K) * 2 + (int64_t)ks * rows * L.down.N * 4;
       if (count) launches += 4;
     }
-    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->logits, m->cfg.vocab, m->lm.b,
+    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->logits, m->vocab_l, m->lm.b,
                               nullptr, 0));
     if (count) {
       bytes += (m->lm.K * m->lm.N + rows * m->lm.K) * 2 + rows * m->lm.N * 4;
@@ -936,9 +997,7 @@ int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int
   o.causal = causal;
   o.all_logits = true;
   RB_TRY(enqueue_forward(s, o));
-  RB_CUDA(cudaMemcpyAsync(logits_out, s->logits, (size_t)rows * m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost,
-                          c->stream));
-  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_TRY(fetch_logits(s, rows, logits_out));
   return ctx_check_status(c);
 }
 

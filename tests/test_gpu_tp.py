@@ -1,0 +1,82 @@
+"""Tensor parallelism over 2 GPUs (heads / FFN columns / vocabulary sharded, NCCL all-reduce after
+o-proj and down-proj) against the single-device oracle.  Needs two GPUs; skipped otherwise."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from rew_b200 import weights as W
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _gpu_count():
+    try:
+        out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
+        return sum(1 for l in out.splitlines() if l.startswith("GPU "))
+    except Exception:
+        return 0
+
+
+def _bundled_nccl():
+    import importlib.util
+    spec = importlib.util.find_spec("nvidia.nccl")
+    if spec and spec.submodule_search_locations:
+        p = os.path.join(list(spec.submodule_search_locations)[0], "lib", "libnccl.so.2")
+        return p if os.path.exists(p) else None
+    return None
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_tp2_generate_matches_oracle(orc):
+    from rew_b200 import _lib
+    with tempfile.TemporaryDirectory() as d:
+        idfile = os.path.join(d, "nccl_id")
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", NCCL_DEBUG="WARN")
+        nccl = _bundled_nccl()
+        if nccl and "REW_B200_NCCL" not in env:
+            env["REW_B200_NCCL"] = nccl  # the newest NCCL on the machine, without importing its owner
+        logs = [open(os.path.join(d, "rank%d.log" % r), "w+") for r in range(2)]
+        procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", idfile,
+                                   os.path.join(d, "out%d.npz" % r)], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
+                 for r in range(2)]
+        codes = []
+        for p in procs:
+            try:
+                codes.append(p.wait(timeout=120))
+            except subprocess.TimeoutExpired:
+                codes.append("timeout")
+        for p in procs:
+            if p.poll() is None:
+                p.kill()  # exactly the children started above
+        tails = []
+        for f in logs:
+            f.seek(0)
+            tails.append(f.read()[-3000:])
+            f.close()
+        assert codes == [0, 0], "rank exit codes %r\n--- rank 0 ---\n%s\n--- rank 1 ---\n%s" % (codes, tails[0], tails[1])
+        outs = [np.load(os.path.join(d, "out%d.npz" % r)) for r in range(2)]
+    prompt = np.random.default_rng(3).integers(0, 512, size=(3, 20)).astype(np.int32)
+    for name, dtype, hd, nh, kvh in (("f32", _lib.F32, 32, 8, 2), ("bf16", _lib.BF16, 64, 4, 2)):
+        cfg = W.ModelConfig(vocab=512, d_model=256, n_layers=2, n_heads=nh, n_kv_heads=kvh, head_dim=hd, ffn=688, max_seq=128,
+                            theta=500000.0, dtype=dtype, mask_kind=1, norm_kind=0)
+        t = W.init_weights(cfg, seed=9, std=0.05, trivial_affine=False)
+        if dtype == _lib.BF16:
+            t = [W.bf16_round(a) if a.ndim == 2 else a for a in t]
+        # both ranks agree bit for bit
+        assert np.array_equal(outs[0][name + "_ids"], outs[1][name + "_ids"])
+        assert np.array_equal(outs[0][name + "_logits"], outs[1][name + "_logits"])
+        if name == "f32":
+            want_ids, want_logits = orc.generate_greedy(cfg, t, prompt, 6)
+            assert np.array_equal(outs[0]["f32_ids"], want_ids)
+            assert rel_l2(outs[0]["f32_logits"], want_logits) <= 1e-5
+        else:
+            ids = outs[0]["bf16_ids"]
+            seq = np.concatenate([prompt, ids[:, :5]], 1)
+            want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
+            assert rel_l2(outs[0]["bf16_logits"], want) <= 2e-2

@@ -1,0 +1,51 @@
+"""One tensor-parallel rank of tests/test_gpu_tp.py (run as a child process, one per GPU)."""
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world, idfile, outfile = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+    from rew_b200 import _lib, api, weights as W
+    print("rank", rank, "starting", flush=True)
+    _lib.init(rank)
+    if rank == 0:
+        uid = api.comm_unique_id()
+        with open(idfile + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(idfile + ".tmp", idfile)
+    else:
+        t0 = time.time()
+        while not os.path.exists(idfile):
+            if time.time() - t0 > 60:
+                raise RuntimeError("rank 0 never published the communicator id")
+            time.sleep(0.05)
+        uid = open(idfile, "rb").read()
+    api.comm_init(uid, rank, world)
+    print("rank", rank, "communicator ready", flush=True)
+    results = {}
+    for name, dtype, hd, nh, kvh in (("f32", _lib.F32, 32, 8, 2), ("bf16", _lib.BF16, 64, 4, 2)):
+        cfg = W.ModelConfig(vocab=512, d_model=256, n_layers=2, n_heads=nh, n_kv_heads=kvh, head_dim=hd, ffn=688, max_seq=128,
+                            theta=500000.0, dtype=dtype, mask_kind=1, norm_kind=0, tp_rank=rank, tp_size=world)
+        full = W.ModelConfig(**{**cfg.__dict__, "tp_rank": 0, "tp_size": 1})
+        t = W.init_weights(full, seed=9, std=0.05, trivial_affine=False)
+        if dtype == _lib.BF16:
+            t = [W.bf16_round(a) if a.ndim == 2 else a for a in t]
+        prompt = np.random.default_rng(3).integers(0, cfg.vocab, size=(3, 20)).astype(np.int32)
+        sess = api.CausalLM(cfg).load(t).session(3, 64)
+        ids, logits = sess.generate(prompt, 6, want_logits=True)
+        print("rank", rank, name, "done", flush=True)
+        results[name + "_ids"] = ids
+        results[name + "_logits"] = logits
+        sess.free()  # the captured decode graph holds the communicator; release it before comm_destroy
+    np.savez(outfile, **results)
+    api.comm_destroy()
+
+
+if __name__ == "__main__":
+    main()
