@@ -10,6 +10,7 @@ models (src/rew/models/llama.nim, deepseek.nim) and generate
 librew_b200.so; there is no Python or CPU implementation of any op.
 """
 import ctypes as C
+import weakref
 
 import numpy as np
 
@@ -181,6 +182,7 @@ class CausalLM:
         h = C.c_void_p()
         check(lib().rewb200_model_create(slot, C.byref(self._c), C.byref(h)))
         self._h = h
+        self._sessions = weakref.WeakSet()  # sessions point into the model: they are freed first
 
     def load(self, tensors):
         """tensors: float32 arrays in canonical order (weights.tensor_specs)."""
@@ -202,10 +204,14 @@ class CausalLM:
         return lib().rewb200_model_weight_bytes(self._h)
 
     def session(self, batch, max_len):
-        return Session(self, batch, max_len)
+        s = Session(self, batch, max_len)
+        self._sessions.add(s)
+        return s
 
     def free(self):
         if self._h is not None:
+            for s in list(self._sessions):
+                s.free()
             lib().rewb200_model_free(self._h)
             self._h = None
 
@@ -274,7 +280,8 @@ class Session:
 
     def free(self):
         if self._h is not None:
-            lib().rewb200_session_free(self._h)
+            if self.model._h is not None:  # a freed model has already released its sessions
+                lib().rewb200_session_free(self._h)
             self._h = None
 
     def __del__(self):

@@ -120,11 +120,11 @@ enum Epilogue : int {
 struct LinearBf16Plan {
   CUtensorMap tmW;       // W [K rows][N cols] bf16 (reference layout [in,out]); 3D when groups > 1
   int64_t K = 0, N = 0;
-  int groups = 1;
+  int groups = 0;        // 0: one matrix; >= 1: that many stacked matrices (experts), 3-D tensor map
 };
 // y = x @ W (+bias); x [M,K] bf16 row-major (ldx elements), W as planned.
 // ksplit > 1 requires EPI_PARTIAL_F32 (out holds ksplit slabs of M*N floats).
-// For grouped launches (plan.groups > 1) group g uses rows
+// For grouped launches (plan.groups >= 1) group g uses rows
 // [row_offsets[g], row_offsets[g+1]) of x/out (device array, groups+1 ints).
 int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi,
                        int ksplit, void* out, int64_t ldo, const float* bias, const int* row_offsets, int max_rows_per_group);

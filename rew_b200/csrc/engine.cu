@@ -32,6 +32,16 @@ int comm_rank(int slot);
 int comm_allreduce_sum_f32(Ctx* c, int slot, float* ptr, int64_t n);
 int comm_allgather_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_rank);
 int slab_sum_launch(Ctx* c, float* part, int nsplit, int64_t slab_elems);
+int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_peer);
+int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi);
+int moe_reset_launch(Ctx* c, int* cursor, int n_cursor, int* count, int n_count, int* meta, int n_meta);
+int moe_dispatch_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d,
+                        int experts_per_rank, int capacity, int* cursor, void* send_x, int* send_meta, int* pair_slot);
+int moe_group_launch(Ctx* c, const void* recv_x, int dtype, const int* recv_meta, int n_slots, int64_t d, int n_experts,
+                     int* count, int* offsets, int* cursor2, void* xs, int* slot_pos);
+int moe_return_launch(Ctx* c, const float* ys, const int* slot_pos, int n_slots, int64_t d, float* ret);
+int moe_combine_launch(Ctx* c, const float* back, const int* pair_slot, const float* topw, int64_t tokens, int k, int64_t d,
+                       float* out, int accumulate);
 int argmax_partial_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int idx_offset, int nchunks, float* pv, int* pi);
 int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows, int nchunks, int* out);
 
@@ -46,12 +56,39 @@ struct LinW {
   LinearBf16Plan plan;
 };
 
+// Routed experts of one DeepSeekMoE layer held by this rank (src/rew/models/deepseek.nim:36-52).
+struct MoeDev {
+  LinW router;                 // gate: [d, n_routed]
+  void* gu = nullptr;          // [E_l][d][2f]  gate|up per expert (bf16: interleaved in groups of 8)
+  float* gu_b = nullptr;       // [E_l][2f]
+  void* down = nullptr;        // [E_l][f][d]
+  float* down_b = nullptr;     // [E_l][d]
+  LinearBf16Plan plan_gu, plan_down;
+  int E_l = 0;
+  int64_t f = 0;
+  std::vector<float> shared_down_bias;  // sum of the shared experts' down biases (uploaded at finalize)
+};
+
 struct LayerDev {
   float *ln1g = nullptr, *ln1b = nullptr, *ln2g = nullptr, *ln2b = nullptr;
-  LinW qkv, o, gu, down;
+  LinW qkv, o, gu, down;       // for a MoE layer gu/down are the fused SHARED experts (width n_shared * moe_ffn)
   int64_t ffn_local = 0;
   bool moe = false;
+  MoeDev x;
 };
+
+// f32 path: out[t] (+)= w_e(t) * y[t], w_e(t) = sum_j topw[t][j] * (topi[t][j] == e)
+// (routedWeightForExpert, src/rew/models/deepseek.nim:114-120,140-144)
+__global__ void moe_dense_acc_kernel(const float* y, const float* topw, const int* topi, int k, int e, int64_t rows,
+                                     int64_t d, float* out, int accumulate) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * d) return;
+  const int64_t t = i / d;
+  float w = 0.f;
+  for (int j = 0; j < k; ++j) w += topw[t * k + j] * (topi[t * k + j] == e ? 1.f : 0.f);
+  const float v = y[i] * w;
+  out[i] = accumulate ? out[i] + v : v;
+}
 
 __global__ void scatter_cols_f32_kernel(const float* src, int64_t src_ld, int64_t row0, int64_t col0, int64_t rows,
                                         int64_t cols, void* dst, int dst_bf16, int64_t ldd, int64_t gran,
@@ -139,6 +176,13 @@ struct rewb200_session {
   void* argmax_scratch = nullptr;      // [B][64] (value, index) partials
   void* gather_scratch = nullptr;      // tensor parallel: all-gathered argmax partials / logits
   size_t gather_bytes = 0;
+  // MoE scratch, sized for rows_cap tokens (capacity = tokens * top_k slots per peer)
+  float* moe_logits = nullptr;
+  float* moe_topw = nullptr;
+  int* moe_topi = nullptr;
+  int* moe_ints = nullptr;             // cursor | count | offsets | cursor2 | send_meta | recv_meta | pair_slot | slot_pos
+  void *moe_send = nullptr, *moe_recv = nullptr, *moe_xs = nullptr, *moe_hs = nullptr;
+  float *moe_ys = nullptr, *moe_ret = nullptr, *moe_back = nullptr, *moe_tmp = nullptr;
   cudaGraphExec_t graph = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float prefill_ms = 0.f, decode_ms = 0.f;
@@ -234,7 +278,10 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
   const size_t es = dtype_size(c.dtype);
   if (rows > s->rows_cap) {
     RB_CUDA(cudaStreamSynchronize(m->c->stream));
-    void** ptrs[] = {(void**)&s->x_res, &s->xn, &s->q, &s->attn, &s->h, (void**)&s->part, (void**)&s->gu32};
+    void** ptrs[] = {(void**)&s->x_res, &s->xn, &s->q, &s->attn, &s->h, (void**)&s->part, (void**)&s->gu32,
+                     (void**)&s->moe_logits, (void**)&s->moe_topw, (void**)&s->moe_topi, (void**)&s->moe_ints, &s->moe_send,
+                     &s->moe_recv, &s->moe_xs, &s->moe_hs, (void**)&s->moe_ys, (void**)&s->moe_ret, (void**)&s->moe_back,
+                     (void**)&s->moe_tmp};
     for (void** p : ptrs)
       if (*p) {
         RB_CUDA(cudaFree(*p));
@@ -242,6 +289,7 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
       }
     int64_t fmax = 0;
     for (const LayerDev& L : m->layers) fmax = std::max(fmax, L.ffn_local);
+    if (c.n_routed > 0) fmax = std::max<int64_t>(fmax, c.moe_ffn);
     RB_CUDA(cudaMalloc((void**)&s->x_res, (size_t)rows * c.d_model * sizeof(float)));
     RB_CUDA(cudaMalloc(&s->xn, (size_t)rows * c.d_model * es));
     RB_CUDA(cudaMalloc(&s->q, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
@@ -252,6 +300,26 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
     if (rows > 32) s->part_bytes = (size_t)rows * widest * sizeof(float);
     RB_CUDA(cudaMalloc((void**)&s->part, s->part_bytes));
     if (c.dtype == REWB200_F32) RB_CUDA(cudaMalloc((void**)&s->gu32, (size_t)rows * 2 * std::max<int64_t>(fmax, 1) * sizeof(float)));
+    if (c.n_routed > 0) {
+      const int ep = c.ep_size, k = c.top_k, E_l = c.n_routed / ep;
+      const int64_t cap = rows * k, slots = cap * ep;
+      RB_CUDA(cudaMalloc((void**)&s->moe_logits, (size_t)rows * c.n_routed * sizeof(float)));
+      RB_CUDA(cudaMalloc((void**)&s->moe_topw, (size_t)rows * k * sizeof(float)));
+      RB_CUDA(cudaMalloc((void**)&s->moe_topi, (size_t)rows * k * sizeof(int)));
+      RB_CUDA(cudaMalloc((void**)&s->moe_ints, (size_t)(ep + 3 * (E_l + 1) + 3 * slots + rows * k) * sizeof(int)));
+      RB_CUDA(cudaMalloc((void**)&s->moe_tmp, (size_t)rows * c.d_model * sizeof(float)));
+      if (c.dtype == REWB200_BF16) {
+        RB_CUDA(cudaMalloc(&s->moe_send, (size_t)slots * c.d_model * es));
+        if (ep > 1) RB_CUDA(cudaMalloc(&s->moe_recv, (size_t)slots * c.d_model * es));
+        RB_CUDA(cudaMalloc(&s->moe_xs, (size_t)(slots + 128) * c.d_model * es));
+        RB_CUDA(cudaMalloc(&s->moe_hs, (size_t)(slots + 128) * c.moe_ffn * es));
+        RB_CUDA(cudaMemset(s->moe_xs, 0, (size_t)(slots + 128) * c.d_model * es));
+        RB_CUDA(cudaMemset(s->moe_hs, 0, (size_t)(slots + 128) * c.moe_ffn * es));
+        RB_CUDA(cudaMalloc((void**)&s->moe_ys, (size_t)slots * c.d_model * sizeof(float)));
+        RB_CUDA(cudaMalloc((void**)&s->moe_ret, (size_t)slots * c.d_model * sizeof(float)));
+        if (ep > 1) RB_CUDA(cudaMalloc((void**)&s->moe_back, (size_t)slots * c.d_model * sizeof(float)));
+      }
+    }
     s->rows_cap = rows;
     if (s->graph) {
       cudaGraphExecDestroy(s->graph);
@@ -289,6 +357,76 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
   if (ksplit_out) *ksplit_out = 1;
   RB_REQUIRE(ldx == w.K && ldo == w.N, "f32 Linear expects dense rows");
   return gemm_f32_launch(c, (const float*)x, (const float*)w.w, partial ? nullptr : w.b, (float*)out, rows, w.K, w.N);
+}
+
+// Routed experts of one MoE layer for the normalised rows in s->xn: router, top-k, dispatch to the
+// owning ranks, grouped expert GEMMs, return, weighted combine into slab 0 of s->part
+// (DeepSeekMoE.forward, src/rew/models/deepseek.nim:132-144).
+int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate) {
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  const rewb200_config& cf = m->cfg;
+  MoeDev& X = L.x;
+  const int64_t d = cf.d_model, f = X.f;
+  const int k = cf.top_k, ep = cf.ep_size, E_l = X.E_l;
+  const int dt = cf.dtype;
+  if (dt == REWB200_BF16)
+    RB_TRY(linear_bf16_launch(c, X.router.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->moe_logits, cf.n_routed,
+                              X.router.b, nullptr, 0));
+  else
+    RB_TRY(gemm_f32_launch(c, (const float*)s->xn, (const float*)X.router.w, X.router.b, s->moe_logits, rows, d, cf.n_routed));
+  RB_TRY(moe_route_launch(c, s->moe_logits, rows, cf.n_routed, k, s->moe_topw, s->moe_topi));
+  if (dt == REWB200_F32) {
+    // parity path: every local expert on every token, masked by its routing weight, as the reference does
+    for (int e = 0; e < E_l; ++e) {
+      const float* gw = (const float*)X.gu + (size_t)e * d * 2 * f;
+      const float* dw = (const float*)X.down + (size_t)e * f * d;
+      RB_TRY(gemm_f32_launch(c, (const float*)s->xn, gw, X.gu_b + (size_t)e * 2 * f, s->gu32, rows, d, 2 * f));
+      const int64_t n = rows * f;
+      swiglu_rows_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(s->gu32, (float*)s->h, rows, f);
+      RB_CUDA(cudaGetLastError());
+      RB_TRY(gemm_f32_launch(c, (const float*)s->h, dw, X.down_b + (size_t)e * d, s->moe_tmp, rows, f, d));
+      const int64_t nd = rows * d;
+      moe_dense_acc_kernel<<<(unsigned)((nd + 255) / 256), 256, 0, c->stream>>>(s->moe_tmp, s->moe_topw, s->moe_topi, k, e, rows,
+                                                                                d, s->part, (accumulate || e > 0) ? 1 : 0);
+      RB_CUDA(cudaGetLastError());
+      g_launch_total += 2;
+    }
+    return REWB200_OK;
+  }
+  const int64_t cap = rows * k, slots = cap * ep;
+  int* cursor = s->moe_ints;
+  int* count = cursor + ep;
+  int* offsets = count + (E_l + 1);
+  int* cursor2 = offsets + (E_l + 1);
+  int* send_meta = cursor2 + (E_l + 1);
+  int* recv_meta = send_meta + slots;
+  int* slot_pos = recv_meta + slots;
+  int* pair_slot = slot_pos + slots;
+  RB_TRY(moe_reset_launch(c, cursor, ep, count, E_l + 1, send_meta, (int)slots));
+  RB_TRY(moe_dispatch_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, (int)cap, cursor, s->moe_send, send_meta, pair_slot));
+  const void* rx = s->moe_send;
+  const int* rmeta = send_meta;
+  if (ep > 1) {
+    RB_TRY(comm_alltoall_bytes(c, m->slot, s->moe_send, s->moe_recv, (size_t)cap * d * dtype_size(dt)));
+    RB_TRY(comm_alltoall_bytes(c, m->slot, send_meta, recv_meta, (size_t)cap * sizeof(int)));
+    rx = s->moe_recv;
+    rmeta = recv_meta;
+  }
+  RB_TRY(moe_group_launch(c, rx, dt, rmeta, (int)slots, d, E_l, count, offsets, cursor2, s->moe_xs, slot_pos));
+  // an expert receives each token at most once: at most rows * ep rows per group
+  const int max_rows = (int)std::min<int64_t>(rows * ep, slots);
+  RB_TRY(linear_bf16_launch(c, X.plan_gu, (const bf16*)s->moe_xs, d, slots, EPI_SWIGLU_BF16, 1, s->moe_hs, f, X.gu_b, offsets,
+                            max_rows));
+  RB_TRY(linear_bf16_launch(c, X.plan_down, (const bf16*)s->moe_hs, f, slots, EPI_BIAS_F32, 1, s->moe_ys, d, X.down_b, offsets,
+                            max_rows));
+  RB_TRY(moe_return_launch(c, s->moe_ys, slot_pos, (int)slots, d, s->moe_ret));
+  const float* back = s->moe_ret;
+  if (ep > 1) {
+    RB_TRY(comm_alltoall_bytes(c, m->slot, s->moe_ret, s->moe_back, (size_t)cap * d * sizeof(float)));
+    back = s->moe_back;
+  }
+  return moe_combine_launch(c, back, pair_slot, s->moe_topw, rows, k, d, s->part, accumulate ? 1 : 0);
 }
 
 // Copies the last-position logits [B, vocab] to the host; under tensor parallelism the
@@ -430,16 +568,23 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       a.beta = L.ln2b;
       RB_TRY(residual_norm_launch(c, a, rows));
     }
-    if (dt == REWB200_BF16) {
-      RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr));
-    } else {
-      RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_BIAS_F32, s->gu32, 2 * L.ffn_local, nullptr));
-      const int64_t n = rows * L.ffn_local;
-      swiglu_rows_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(s->gu32, (float*)s->h, rows, L.ffn_local);
-      RB_CUDA(cudaGetLastError());
-      ++g_launch_total;
+    ks = 0;  // slabs of s->part that hold FFN output so far
+    if (L.ffn_local > 0) {  // dense FFN, or the fused shared experts of a MoE layer
+      if (dt == REWB200_BF16) {
+        RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr));
+      } else {
+        RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_BIAS_F32, s->gu32, 2 * L.ffn_local, nullptr));
+        const int64_t n = rows * L.ffn_local;
+        swiglu_rows_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(s->gu32, (float*)s->h, rows, L.ffn_local);
+        RB_CUDA(cudaGetLastError());
+        ++g_launch_total;
+      }
+      RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
     }
-    RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
+    if (L.moe) {
+      RB_TRY(moe_routed(s, L, rows, ks > 0));
+      if (ks == 0) ks = 1;
+    }
     if (cf.tp_size > 1) {
       RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
       RB_TRY(comm_allreduce_sum_f32(c, m->slot, s->part, rows * d));
@@ -450,7 +595,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       a.partial = s->part;
       a.nsplit = ks;
       a.split_stride = rows * d;
-      a.bias = L.down.b;
+      a.bias = L.ffn_local > 0 ? L.down.b : nullptr;
       const bool last = (l + 1 == cf.n_layers);
       a.gamma = last ? m->ng : m->layers[l + 1].ln1g;
       a.beta = last ? m->nb : m->layers[l + 1].ln1b;
@@ -516,12 +661,25 @@ int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** ou
   RB_REQUIRE(cfg->tp_rank >= 0 && cfg->tp_rank < tp, "tp_rank out of range");
   RB_REQUIRE(cfg->n_heads % tp == 0 && cfg->n_kv_heads % tp == 0 && cfg->ffn % tp == 0,
              "shardLayout: heads, kv heads and FFN width must be divisible by the tensor-parallel size");
-  RB_REQUIRE(cfg->n_routed == 0, "MoE models are created through this entry only after rewb200 MoE support is built in");
+  const int ep = std::max(1, cfg->ep_size);
+  if (cfg->n_routed > 0) {
+    RB_REQUIRE(tp == 1, "MoE models shard by experts (ep_size), not by tensor parallelism");
+    RB_REQUIRE(cfg->ep_rank >= 0 && cfg->ep_rank < ep && cfg->n_routed % ep == 0, "initDeepSeekMoE: numRouted must divide by ep_size");
+    RB_REQUIRE(cfg->n_shared >= 0, "initDeepSeekMoE: numShared must be non-negative");
+    RB_REQUIRE(cfg->top_k >= 1 && cfg->top_k <= cfg->n_routed, "initDeepSeekMoE: numExpertsPerTok must be in 1..numRouted");
+    RB_REQUIRE(cfg->moe_ffn > 0 && cfg->n_routed <= 256, "initDeepSeekMoE: hiddenSize and intermediateSize must be positive");
+    RB_REQUIRE(cfg->dtype == REWB200_BF16 || ep == 1, "expert parallelism is built for bf16 models");
+    if (cfg->dtype == REWB200_BF16)
+      RB_REQUIRE(cfg->moe_ffn % 8 == 0 && cfg->n_routed % 8 == 0, "bf16 MoE needs moe_ffn and numRouted multiples of 8");
+  } else {
+    RB_REQUIRE(ep == 1, "ep_size > 1 needs a MoE model");
+  }
   rewb200_model* m = new rewb200_model();
   m->c = c;
   m->slot = slot;
   m->cfg = *cfg;
   m->cfg.tp_size = tp;
+  m->cfg.ep_size = std::max(1, cfg->ep_size);
   RB_REQUIRE(cfg->vocab % tp == 0, "shardLayout: vocabulary must be divisible by the tensor-parallel size");
   m->vocab_l = cfg->vocab / tp;
   m->nh_l = cfg->n_heads / tp;
@@ -547,11 +705,29 @@ int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** ou
     RB_TRY(alloc_vec(&L.ln1b, 0.f));
     RB_TRY(alloc_vec(&L.ln2g, 1.f));
     RB_TRY(alloc_vec(&L.ln2b, 0.f));
-    L.ffn_local = cfg->ffn / tp;
+    L.moe = layer_is_moe(*cfg, l);
+    if (L.moe) L.ffn_local = (int64_t)cfg->n_shared * cfg->moe_ffn;
+    else if (cfg->n_routed > 0 && cfg->first_dense > 0) L.ffn_local = cfg->first_dense;
+    else L.ffn_local = cfg->ffn / tp;
     RB_TRY(alloc_lin(m, &L.qkv, d, m->nqkv));
     RB_TRY(alloc_lin(m, &L.o, m->nq, d));
-    RB_TRY(alloc_lin(m, &L.gu, d, 2 * L.ffn_local));
-    RB_TRY(alloc_lin(m, &L.down, L.ffn_local, d));
+    if (L.ffn_local > 0) {
+      RB_TRY(alloc_lin(m, &L.gu, d, 2 * L.ffn_local));
+      RB_TRY(alloc_lin(m, &L.down, L.ffn_local, d));
+    }
+    if (L.moe) {
+      MoeDev& X = L.x;
+      X.E_l = cfg->n_routed / m->cfg.ep_size;
+      X.f = cfg->moe_ffn;
+      X.shared_down_bias.assign(d, 0.f);
+      RB_TRY(alloc_lin(m, &X.router, d, cfg->n_routed));
+      RB_TRY(dev_alloc(m, &X.gu, (size_t)X.E_l * d * 2 * X.f * es));
+      RB_TRY(dev_alloc(m, &X.down, (size_t)X.E_l * X.f * d * es));
+      RB_TRY(dev_alloc(m, (void**)&X.gu_b, (size_t)X.E_l * 2 * X.f * sizeof(float)));
+      RB_TRY(dev_alloc(m, (void**)&X.down_b, (size_t)X.E_l * d * sizeof(float)));
+      RB_CUDA(cudaMemsetAsync(X.gu_b, 0, (size_t)X.E_l * 2 * X.f * sizeof(float), c->stream));
+      RB_CUDA(cudaMemsetAsync(X.down_b, 0, (size_t)X.E_l * d * sizeof(float), c->stream));
+    }
   }
   RB_TRY(alloc_vec(&m->ng, 1.f));
   RB_TRY(alloc_vec(&m->nb, 0.f));
@@ -594,7 +770,7 @@ int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host,
   TensorRef r;
   RB_TRY(locate(m, index, &r));
   const int64_t d = c.d_model, hd = c.head_dim;
-  const int64_t NQ = (int64_t)c.n_heads * hd, NKV = (int64_t)c.n_kv_heads * hd, F = c.ffn;
+  const int64_t NQ = (int64_t)c.n_heads * hd, NKV = (int64_t)c.n_kv_heads * hd;
   const int tp = c.tp_size, rk = c.tp_rank;
   const bool bf = c.dtype == REWB200_BF16;
   auto expect = [&](int64_t n) -> int {
@@ -622,7 +798,8 @@ int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host,
   const int64_t nq = m->nq, nkv = m->nkv, nqkv = m->nqkv, fl = L.ffn_local;
   // gate/up column mapping: bf16 interleaves groups of 8 (gate at +0, up at +8 of each 16); f32 concatenates.
   const int64_t ggran = bf ? 8 : fl, gstride = bf ? 16 : fl;
-  switch (r.slot) {
+  const int64_t F = (c.n_routed > 0 && c.first_dense > 0) ? c.first_dense : c.ffn;  // dense block width
+  if (!(L.moe && r.slot >= 12)) switch (r.slot) {
     case 0: return vec(L.ln1g, d, 0, d);
     case 1: return vec(L.ln1b, d, 0, d);
     case 2: RB_TRY(expect(d * NQ)); return scatter(m, NQ, 0, rk * nq, d, nq, L.qkv.w, true, nqkv, nq, nq, 0);
@@ -641,7 +818,53 @@ int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host,
     case 15: RB_TRY(expect(F)); return scatter(m, F, 0, rk * fl, 1, fl, L.gu.b, false, 2 * fl, ggran, gstride, bf ? 8 : fl);
     case 16: RB_TRY(expect(F * d)); return scatter(m, d, rk * fl, 0, fl, d, L.down.w, true, d, d, d, 0);
     case 17: return vec(L.down.b, d, 0, d);
-    default: (void)tp; return fail("tensor slot not supported for this layer kind");
+    default: break;
+  }
+  (void)tp;
+  RB_REQUIRE(L.moe, "tensor slot not supported for this layer kind");
+  {
+    MoeDev& X = L.x;
+    const int64_t f = X.f, E = c.n_routed;
+    if (r.slot == 12) {
+      RB_TRY(expect(d * E));
+      return scatter(m, E, 0, 0, d, E, X.router.w, true, E, E, E, 0);
+    }
+    if (r.slot == 13) return vec(X.router.b, E, 0, E);
+    const int idx = r.slot - 14, ei = idx / 6, which = idx % 6;
+    RB_REQUIRE(ei < c.n_shared + c.n_routed, "expert index out of range");
+    // column mapping of gate / up inside a fused [.., 2*width] block
+    const int64_t gran = bf ? 8 : f, gstr = bf ? 16 : f;
+    if (ei < c.n_shared) {
+      const int64_t ns = c.n_shared, W2 = 2 * ns * f;
+      const int64_t g_off = bf ? ei * 2 * f : ei * f, u_off = bf ? ei * 2 * f + 8 : ns * f + ei * f;
+      switch (which) {
+        case 0: RB_TRY(expect(d * f)); return scatter(m, f, 0, 0, d, f, L.gu.w, true, W2, gran, gstr, g_off);
+        case 1: RB_TRY(expect(f)); return scatter(m, f, 0, 0, 1, f, L.gu.b, false, W2, gran, gstr, g_off);
+        case 2: RB_TRY(expect(d * f)); return scatter(m, f, 0, 0, d, f, L.gu.w, true, W2, gran, gstr, u_off);
+        case 3: RB_TRY(expect(f)); return scatter(m, f, 0, 0, 1, f, L.gu.b, false, W2, gran, gstr, u_off);
+        case 4: RB_TRY(expect(f * d));
+          return scatter(m, d, 0, 0, f, d, (char*)L.down.w + (size_t)ei * f * d * dtype_size(c.dtype), true, d, d, d, 0);
+        default:
+          RB_REQUIRE(numel == d, "expert down bias must have d_model elements");
+          for (int64_t i = 0; i < d; ++i) X.shared_down_bias[i] += host[i];
+          return REWB200_OK;
+      }
+    }
+    const int e = ei - c.n_shared;
+    if (e / X.E_l != c.ep_rank) return REWB200_OK;  // another rank's expert
+    const int64_t le = e % X.E_l;
+    const size_t es2 = dtype_size(c.dtype);
+    char* gw = (char*)X.gu + (size_t)le * d * 2 * f * es2;
+    float* gb = X.gu_b + le * 2 * f;
+    const int64_t u_off = bf ? 8 : f;
+    switch (which) {
+      case 0: RB_TRY(expect(d * f)); return scatter(m, f, 0, 0, d, f, gw, true, 2 * f, gran, gstr, 0);
+      case 1: RB_TRY(expect(f)); return scatter(m, f, 0, 0, 1, f, gb, false, 2 * f, gran, gstr, 0);
+      case 2: RB_TRY(expect(d * f)); return scatter(m, f, 0, 0, d, f, gw, true, 2 * f, gran, gstr, u_off);
+      case 3: RB_TRY(expect(f)); return scatter(m, f, 0, 0, 1, f, gb, false, 2 * f, gran, gstr, u_off);
+      case 4: RB_TRY(expect(f * d)); return scatter(m, d, 0, 0, f, d, (char*)X.down + (size_t)le * f * d * es2, true, d, d, d, 0);
+      default: RB_TRY(expect(d)); return scatter(m, d, 0, 0, 1, d, X.down_b + le * d, false, d, d, d, 0);
+    }
   }
 }
 
@@ -658,8 +881,17 @@ int rewb200_model_init_random(rewb200_model* m, uint64_t seed, float std) {
   for (LayerDev& L : m->layers) {
     RB_TRY(fill_normal_launch(c, L.qkv.w, dt, L.qkv.K * L.qkv.N, ++k, std));
     RB_TRY(fill_normal_launch(c, L.o.w, dt, L.o.K * L.o.N, ++k, std));
-    RB_TRY(fill_normal_launch(c, L.gu.w, dt, L.gu.K * L.gu.N, ++k, std));
-    RB_TRY(fill_normal_launch(c, L.down.w, dt, L.down.K * L.down.N, ++k, std));
+    if (L.ffn_local > 0) {
+      RB_TRY(fill_normal_launch(c, L.gu.w, dt, L.gu.K * L.gu.N, ++k, std));
+      RB_TRY(fill_normal_launch(c, L.down.w, dt, L.down.K * L.down.N, ++k, std));
+    }
+    if (L.moe) {
+      const uint64_t router_seed = seed * 1000003ull + 500000ull + (uint64_t)(&L - &m->layers[0]);  // same on every rank
+      RB_TRY(fill_normal_launch(c, L.x.router.w, dt, L.x.router.K * L.x.router.N, router_seed, std));
+      k += (uint64_t)m->cfg.ep_rank * 104729ull;
+      RB_TRY(fill_normal_launch(c, L.x.gu, dt, (int64_t)L.x.E_l * m->cfg.d_model * 2 * L.x.f, ++k, std));
+      RB_TRY(fill_normal_launch(c, L.x.down, dt, (int64_t)L.x.E_l * L.x.f * m->cfg.d_model, ++k, std));
+    }
   }
   RB_TRY(fill_normal_launch(c, m->lm.w, dt, m->lm.K * m->lm.N, ++k, std));
   RB_CUDA(cudaStreamSynchronize(c->stream));
@@ -672,13 +904,24 @@ int rewb200_model_finalize(rewb200_model* m) {
   RB_CUDA(cudaSetDevice(m->c->device));
   if (m->cfg.dtype == REWB200_BF16) {
     for (LayerDev& L : m->layers) {
-      RB_TRY(linear_bf16_plan(&L.qkv.plan, (const bf16*)L.qkv.w, L.qkv.K, L.qkv.N, 1));
-      RB_TRY(linear_bf16_plan(&L.o.plan, (const bf16*)L.o.w, L.o.K, L.o.N, 1));
-      RB_TRY(linear_bf16_plan(&L.gu.plan, (const bf16*)L.gu.w, L.gu.K, L.gu.N, 1));
-      RB_TRY(linear_bf16_plan(&L.down.plan, (const bf16*)L.down.w, L.down.K, L.down.N, 1));
+      RB_TRY(linear_bf16_plan(&L.qkv.plan, (const bf16*)L.qkv.w, L.qkv.K, L.qkv.N, 0));
+      RB_TRY(linear_bf16_plan(&L.o.plan, (const bf16*)L.o.w, L.o.K, L.o.N, 0));
+      if (L.ffn_local > 0) {
+        RB_TRY(linear_bf16_plan(&L.gu.plan, (const bf16*)L.gu.w, L.gu.K, L.gu.N, 0));
+        RB_TRY(linear_bf16_plan(&L.down.plan, (const bf16*)L.down.w, L.down.K, L.down.N, 0));
+      }
+      if (L.moe) {
+        RB_TRY(linear_bf16_plan(&L.x.router.plan, (const bf16*)L.x.router.w, L.x.router.K, L.x.router.N, 0));
+        RB_TRY(linear_bf16_plan(&L.x.plan_gu, (const bf16*)L.x.gu, m->cfg.d_model, 2 * L.x.f, L.x.E_l));
+        RB_TRY(linear_bf16_plan(&L.x.plan_down, (const bf16*)L.x.down, L.x.f, m->cfg.d_model, L.x.E_l));
+      }
     }
-    RB_TRY(linear_bf16_plan(&m->lm.plan, (const bf16*)m->lm.w, m->lm.K, m->lm.N, 1));
+    RB_TRY(linear_bf16_plan(&m->lm.plan, (const bf16*)m->lm.w, m->lm.K, m->lm.N, 0));
   }
+  for (LayerDev& L : m->layers)  // shared experts' down biases were summed on the host
+    if (L.moe && L.ffn_local > 0)
+      RB_CUDA(cudaMemcpyAsync(L.down.b, L.x.shared_down_bias.data(), m->cfg.d_model * sizeof(float), cudaMemcpyHostToDevice,
+                              m->c->stream));
   if (m->stage) {
     RB_CUDA(cudaStreamSynchronize(m->c->stream));
     RB_CUDA(cudaFree(m->stage));
@@ -759,7 +1002,8 @@ void rewb200_session_free(rewb200_session* s) {
   for (void* p : s->kc) cudaFree(p);
   for (void* p : s->vc) cudaFree(p);
   void* ptrs[] = {s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
-                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch, s->gather_scratch};
+                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch, s->gather_scratch, s->moe_logits, s->moe_topw, s->moe_topi, s->moe_ints,
+                  s->moe_send, s->moe_recv, s->moe_xs, s->moe_hs, s->moe_ys, s->moe_ret, s->moe_back, s->moe_tmp};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   if (s->h_ids) cudaFreeHost(s->h_ids);
@@ -940,6 +1184,7 @@ int rewb200_session_profile_linears(rewb200_session* s, int iters, float* ms_per
   int launches = 0;
   auto one_step = [&](bool count) -> int {
     for (LayerDev& L : m->layers) {
+      if (L.moe || L.ffn_local == 0) return fail("linear profiling covers dense decoder blocks only");
       int ks = 1;
       RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks));
       if (count) bytes += (L.qkv.K * L.qkv.N + rows * L.qkv.K) * 2 + (int64_t)ks * rows * L.qkv.N * 4;

@@ -67,6 +67,9 @@ __global__ void __launch_bounds__(160) linear_bf16_kernel(const __grid_constant_
   const int col0 = blockIdx.x * BN;
   int row0, rows_valid, group = 0;
   if (a.grouped) {
+    // the row offsets are produced by earlier kernels of the same step: under programmatic
+    // dependent launch they may only be read after griddepcontrol.wait
+    pdl_wait();
     group = blockIdx.z;
     const int r_begin = a.row_offsets[group], r_end = a.row_offsets[group + 1];
     row0 = r_begin + blockIdx.y * ROWS;
@@ -187,6 +190,8 @@ __global__ void __launch_bounds__(160) linear_bf16_kernel(const __grid_constant_
   // ---------------- epilogue (writes wait for the previous kernel's readers)
   pdl_wait();
   if (!ok) return;
+  // grouped launches keep one bias row per group: [groups][N]
+  const float* bias = a.bias ? a.bias + (a.grouped ? (int64_t)group * a.N : 0) : nullptr;
   const int g = lane >> 2, t = lane & 3;
   const int wcol0 = col0 + warp * 32;
 #pragma unroll
@@ -201,10 +206,10 @@ __global__ void __launch_bounds__(160) linear_bf16_kernel(const __grid_constant_
         for (int nt = 0; nt < 4; nt += 2) {
           const int64_t cg = wcol0 + nt * 8 + 2 * t;  // gate column in the interleaved matrix
           if (cg >= a.N) continue;
-          const float g0 = acc[mt][nt][half * 2 + 0] + (a.bias ? a.bias[cg] : 0.f);
-          const float g1 = acc[mt][nt][half * 2 + 1] + (a.bias ? a.bias[cg + 1] : 0.f);
-          const float u0 = acc[mt][nt + 1][half * 2 + 0] + (a.bias ? a.bias[cg + 8] : 0.f);
-          const float u1 = acc[mt][nt + 1][half * 2 + 1] + (a.bias ? a.bias[cg + 9] : 0.f);
+          const float g0 = acc[mt][nt][half * 2 + 0] + (bias ? bias[cg] : 0.f);
+          const float g1 = acc[mt][nt][half * 2 + 1] + (bias ? bias[cg + 1] : 0.f);
+          const float u0 = acc[mt][nt + 1][half * 2 + 0] + (bias ? bias[cg + 8] : 0.f);
+          const float u1 = acc[mt][nt + 1][half * 2 + 1] + (bias ? bias[cg + 9] : 0.f);
           const int64_t oc = (wcol0 + nt * 8) / 2 + 2 * t;
           uint32_t v = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
           *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(a.out) + grow * a.ldo + oc) = v;
@@ -219,9 +224,9 @@ __global__ void __launch_bounds__(160) linear_bf16_kernel(const __grid_constant_
             float* o = reinterpret_cast<float*>(a.out) + split * a.split_stride + grow * a.ldo + c;
             *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
           } else {
-            if (a.bias) {
-              v0 += a.bias[c];
-              v1 += a.bias[c + 1];
+            if (bias) {
+              v0 += bias[c];
+              v1 += bias[c + 1];
             }
             if (a.epi == EPI_BIAS_F32) {
               float* o = reinterpret_cast<float*>(a.out) + grow * a.ldo + c;
@@ -257,7 +262,7 @@ int linear_bf16_plan(LinearBf16Plan* plan, const bf16* W, int64_t K, int64_t N, 
   plan->K = K;
   plan->N = N;
   plan->groups = groups;
-  if (groups > 1)
+  if (groups >= 1)  // grouped (one weight matrix per expert); 0 = a single matrix
     return make_tmap_3d_bf16(&plan->tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)groups, (uint64_t)N * 2,
                              (uint64_t)K * N * 2, 64, BK);
   return make_tmap_2d_bf16(&plan->tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, BK);
@@ -285,12 +290,12 @@ int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_
   RB_REQUIRE(ksplit >= 1 && (ksplit == 1 || epi == EPI_PARTIAL_F32), "split-K needs the partial epilogue");
   RB_REQUIRE(epi != EPI_SWIGLU_BF16 || plan.N % 16 == 0, "SwiGLU epilogue needs interleaved width % 16 == 0");
   if (M == 0) return REWB200_OK;
-  const bool grouped = plan.groups > 1;
+  const bool grouped = plan.groups >= 1;
   if (!grouped && (c->linear_impl == 2 || (c->linear_impl == 1 && M > 32)))
     return linear_tc_launch(c, plan, x, ldx, M, epi, ksplit, out, ldo, bias);
   RB_REQUIRE(!grouped || (row_offsets != nullptr && ksplit == 1), "grouped Linear needs row offsets and no split-K");
   const int64_t rows_for_tile = grouped ? max_rows_per_group : M;
-  const bool small = rows_for_tile <= 32;
+  const bool small = rows_for_tile <= 64;  // 33..64 rows: two 32-row tiles keep two CTAs per SM
   const int ROWS = small ? 32 : 128;
   CUtensorMap tmX;
   RB_TRY(make_tmap_2d_bf16(&tmX, x, (uint64_t)plan.K, (uint64_t)M, (uint64_t)ldx * 2, 64, ROWS));

@@ -95,8 +95,23 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col0 = blockIdx.x * BM;          // first output feature of the tile
-  const int row0 = blockIdx.y * TN;          // first token of the tile
+  // Tile order: with several token tiles the CTAs walk groups of 8 token tiles per feature tile,
+  // so a wave touches ~8 x-tiles and ~18 W-tiles instead of one x-tile and every W-tile; without
+  // this a weight matrix larger than L2 is re-streamed from HBM once per token tile.
+  int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  if (gridDim.y > 1) {
+    constexpr int GROUP_M = 8;
+    const int lin = blockIdx.x + gridDim.x * blockIdx.y;
+    const int per_group = GROUP_M * gridDim.x;
+    const int group = lin / per_group;
+    const int first_m = group * GROUP_M;
+    const int group_rows = min(GROUP_M, (int)gridDim.y - first_m);
+    const int in_group = lin - group * per_group;
+    tile_m = first_m + in_group % group_rows;
+    tile_n = in_group / group_rows;
+  }
+  const int col0 = tile_n * BM;              // first output feature of the tile
+  const int row0 = tile_m * TN;              // first token of the tile
   const int split = blockIdx.z;
   const int rows_valid = (int)min((int64_t)TN, a.M - row0);
   const int nkb_total = (int)((a.K + BK - 1) / BK);
@@ -179,44 +194,46 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
     }
   } else {
     // ---------------- epilogue warps 2..5; TMEM lanes 32*(warp%4) .. +31
+    // The accumulator is D[feature][token]; the output is [token][feature].  Each thread owns one
+    // feature, so the tile is transposed through shared memory (the pipeline stages are free once
+    // tmem_full fires) and then written with 16-byte, fully coalesced stores.
     const int q = warp & 3;
+    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
     bool ok = true;
     if (nkb > 0) {
       ok = mbar_wait(tmem_full, 0, a.status);
       tc_fence_after();
     }
     pdl_wait();
-    if (ok) {
-      const int64_t feat = (int64_t)col0 + q * 32 + lane;
-      const bool feat_ok = feat < a.N;
-      const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 32) {
+    if constexpr (TN == 32) {
+      // decode-size tile: the output is a few KB, direct stores (32 lanes = 32 consecutive features)
+      if (ok) {
+        const int64_t feat = (int64_t)col0 + q * 32 + lane;
+        const bool feat_ok = feat < a.N;
+        const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
         uint32_t r[32];
         if (nkb > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16), r);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (c0 >= rows_valid) break;
         if (a.epi == EPI_SWIGLU_BF16) {
-          // gate features sit in lanes with (lane % 16) < 8, their up partners 8 lanes higher
           const bool is_gate = (lane & 15) < 8;
           const int64_t oc = ((int64_t)col0 + q * 32) / 2 + (lane >> 4) * 8 + (lane & 7);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float v = __uint_as_float(r[j]) + bias_v;
             const float up = __shfl_down_sync(0xffffffffu, v, 8);
-            if (is_gate && feat_ok && c0 + j < rows_valid)
-              reinterpret_cast<bf16*>(a.out)[(int64_t)(row0 + c0 + j) * a.ldo + oc] = __float2bfloat16_rn(silu_f(v) * up);
+            if (is_gate && feat_ok && j < rows_valid)
+              reinterpret_cast<bf16*>(a.out)[(int64_t)(row0 + j) * a.ldo + oc] = __float2bfloat16_rn(silu_f(v) * up);
           }
         } else if (feat_ok) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            if (c0 + j >= rows_valid) break;
+            if (j >= rows_valid) break;
             const float v = __uint_as_float(r[j]) + bias_v;
-            const int64_t grow = row0 + c0 + j;
+            const int64_t grow = row0 + j;
             if (a.epi == EPI_PARTIAL_F32)
               reinterpret_cast<float*>(a.out)[split * a.split_stride + grow * a.ldo + feat] = v;
             else if (a.epi == EPI_BIAS_F32)
@@ -226,6 +243,65 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
           }
         }
       }
+    } else {
+      const bool swiglu = a.epi == EPI_SWIGLU_BF16;
+      const bool out_f32 = a.epi == EPI_PARTIAL_F32 || a.epi == EPI_BIAS_F32;
+      const int tile_cols = swiglu ? 64 : 128;
+      const int row_bytes = tile_cols * (out_f32 ? 4 : 2);
+      uint8_t* stg = smem;
+      if (ok) {
+        const int64_t feat = (int64_t)col0 + q * 32 + lane;
+        const bool feat_ok = feat < a.N;
+        const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
+        // gate features sit in lanes with (lane % 16) < 8, their up partners 8 lanes higher
+        const bool is_gate = (lane & 15) < 8;
+        const int hcol = q * 16 + (lane >> 4) * 8 + (lane & 7);
+  #pragma unroll 1
+        for (int c0 = 0; c0 < TN; c0 += 32) {
+          if (c0 >= rows_valid) break;
+          uint32_t r[32];
+          if (nkb > 0) {
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+          } else {
+  #pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          if (swiglu) {
+  #pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float v = __uint_as_float(r[j]) + bias_v;
+              const float up = __shfl_down_sync(0xffffffffu, v, 8);
+              if (is_gate) reinterpret_cast<bf16*>(stg + (c0 + j) * row_bytes)[hcol] = __float2bfloat16_rn(silu_f(v) * up);
+            }
+          } else if (out_f32) {
+  #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              reinterpret_cast<float*>(stg + (c0 + j) * row_bytes)[q * 32 + lane] = __uint_as_float(r[j]) + bias_v;
+          } else {
+  #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              reinterpret_cast<bf16*>(stg + (c0 + j) * row_bytes)[q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[j]) + bias_v);
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+      if (ok) {
+        const int chunks_per_row = row_bytes / 16;           // 32 (f32), 16 (bf16), 8 (SwiGLU)
+        const int elems_per_chunk = out_f32 ? 4 : 8;
+        const int64_t out_col0 = swiglu ? col0 / 2 : col0;
+        const int64_t out_cols = swiglu ? a.N / 2 : a.N;
+        const size_t esz = out_f32 ? 4 : 2;
+        uint8_t* obase = reinterpret_cast<uint8_t*>(a.out) + (a.epi == EPI_PARTIAL_F32 ? (size_t)split * a.split_stride * 4 : 0);
+        const int total = rows_valid * chunks_per_row;
+        for (int i = et; i < total; i += 128) {
+          const int row = i / chunks_per_row, ch = i % chunks_per_row;
+          const int64_t col = out_col0 + (int64_t)ch * elems_per_chunk;
+          if (col >= out_cols) continue;
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + row * row_bytes + ch * 16);
+          *reinterpret_cast<uint4*>(obase + ((size_t)(row0 + row) * a.ldo + col) * esz) = v;
+        }
+      }
+
     }
   }
   tc_fence_before();
@@ -254,7 +330,7 @@ int launch_tn(Ctx* c, const LinearBf16Plan& plan, const CUtensorMap& tmX, const 
 // Same contract as linear_bf16_launch (ungrouped).
 int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, int ksplit,
                      void* out, int64_t ldo, const float* bias) {
-  RB_REQUIRE(plan.groups == 1, "the tcgen05 Linear does not take grouped weights");
+  RB_REQUIRE(plan.groups == 0, "the tcgen05 Linear does not take grouped weights");
   RB_REQUIRE(ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0, "bf16 Linear: activations must be 16-byte aligned rows");
   RB_REQUIRE(ksplit >= 1 && (ksplit == 1 || epi == EPI_PARTIAL_F32), "split-K needs the partial epilogue");
   RB_REQUIRE(epi != EPI_SWIGLU_BF16 || plan.N % 16 == 0, "SwiGLU epilogue needs interleaved width % 16 == 0");

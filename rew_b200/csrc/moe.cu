@@ -8,6 +8,8 @@
 // expert index), renormalised by their sum.
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -90,7 +92,181 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   for (int j = lane; j < k; j += 32) topw[tok * k + j] = topw[tok * k + j] / denom;
 }
 
+
+// ---- dispatch / gather / combine around the grouped expert GEMMs -------------
+// Pairs (token, j) are sent to the rank that owns expert topi[token][j] into
+// fixed-capacity per-peer slot arrays (capacity = tokens * k, the worst case), so
+// an expert-parallel all-to-all needs no count exchange.  Slot order inside a
+// peer comes from an atomic counter and may vary between runs; results do not
+// depend on it because every pair is computed independently and each token sums
+// its k results in the fixed order j = 0..k-1.
+
+__global__ void moe_reset_kernel(int* cursor, int n_cursor, int* count, int n_count, int* meta, int n_meta) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_cursor) cursor[i] = 0;
+  if (i < n_count) count[i] = 0;
+  if (i < n_meta) meta[i] = -1;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_dispatch_kernel(const T* __restrict__ x, const int* __restrict__ topi, int k,
+                                                           int64_t d, int experts_per_rank, int capacity, int* cursor,
+                                                           T* send_x, int* send_meta, int* pair_slot) {
+  __shared__ int s_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int e = topi[pair];
+    const int p = e / experts_per_rank;
+    const int slot = p * capacity + atomicAdd(&cursor[p], 1);
+    send_meta[slot] = e % experts_per_rank;
+    pair_slot[pair] = slot;
+    s_slot = slot;
+  }
+  __syncthreads();
+  const int tok = pair / k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)tok * d);
+  uint4* dst = reinterpret_cast<uint4*>(send_x + (int64_t)s_slot * d);
+  const int n16 = (int)(d * sizeof(T) / 16);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void moe_count_kernel(const int* __restrict__ meta, int n_slots, int* count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_slots && meta[i] >= 0) atomicAdd(&count[meta[i]], 1);
+}
+
+__global__ void moe_scan_kernel(const int* count, int n_experts, int* offsets, int* cursor2) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      offsets[e] = acc;
+      cursor2[e] = acc;
+      acc += count[e];
+    }
+    offsets[n_experts] = acc;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ recv_x, const int* __restrict__ recv_meta,
+                                                         int64_t d, int* cursor2, T* xs, int* slot_pos) {
+  __shared__ int s_pos;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x;
+  const int e = recv_meta[slot];
+  if (e < 0) {
+    if (threadIdx.x == 0) slot_pos[slot] = -1;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    s_pos = atomicAdd(&cursor2[e], 1);
+    slot_pos[slot] = s_pos;
+  }
+  __syncthreads();
+  const uint4* src = reinterpret_cast<const uint4*>(recv_x + (int64_t)slot * d);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (int64_t)s_pos * d);
+  const int n16 = (int)(d * sizeof(T) / 16);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+}
+
+// ret[slot] = ys[slot_pos[slot]] (zeros for empty slots): results back in the sender's slot order.
+__global__ void __launch_bounds__(128) moe_return_kernel(const float* __restrict__ ys, const int* __restrict__ slot_pos,
+                                                         int64_t d, float* ret) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x;
+  const int pos = slot_pos[slot];
+  float4* dst = reinterpret_cast<float4*>(ret + (int64_t)slot * d);
+  const int n4 = (int)(d / 4);
+  if (pos < 0) {
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
+  const float4* src = reinterpret_cast<const float4*>(ys + (int64_t)pos * d);
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = src[i];
+}
+
+// out[token] (+)= sum_j topw[token][j] * back[pair_slot[token][j]]   (deepseek.nim:140-144 for the
+// experts a token actually selected; the others have weight 0 in the reference).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ back, const int* __restrict__ pair_slot,
+                                                          const float* __restrict__ topw, int k, int64_t d, float* out,
+                                                          int accumulate) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x;
+  const int n4 = (int)(d / 4);
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+      const float w = topw[tok * k + j];
+      const float4 v = reinterpret_cast<const float4*>(back + (int64_t)pair_slot[tok * k + j] * d)[i];
+      acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    }
+    float4* o = reinterpret_cast<float4*>(out + (int64_t)tok * d) + i;
+    if (accumulate) {
+      const float4 p = *o;
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    *o = acc;
+  }
+}
+
 }  // namespace
+
+#define RB_LAUNCH(kernel, grid, block, ...)                                                   \
+  do {                                                                                        \
+    RB_CUDA(launch_k(kernel, dim3((unsigned)(grid)), dim3(block), 0, c->stream, c->use_pdl, __VA_ARGS__)); \
+    ++g_launch_total;                                                                         \
+  } while (0)
+
+int moe_reset_launch(Ctx* c, int* cursor, int n_cursor, int* count, int n_count, int* meta, int n_meta) {
+  const int n = std::max(n_cursor, std::max(n_count, n_meta));
+  RB_LAUNCH(moe_reset_kernel, (n + 255) / 256, 256, cursor, n_cursor, count, n_count, meta, n_meta);
+  return REWB200_OK;
+}
+int moe_dispatch_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d,
+                        int experts_per_rank, int capacity, int* cursor, void* send_x, int* send_meta, int* pair_slot) {
+  if (tokens == 0) return REWB200_OK;
+  RB_REQUIRE((d * dtype_size(dtype)) % 16 == 0, "MoE dispatch needs rows that are multiples of 16 bytes");
+  if (dtype == REWB200_BF16)
+    RB_LAUNCH(moe_dispatch_kernel<bf16>, tokens * k, 128, (const bf16*)x, topi, k, d, experts_per_rank, capacity, cursor,
+              (bf16*)send_x, send_meta, pair_slot);
+  else
+    RB_LAUNCH(moe_dispatch_kernel<float>, tokens * k, 128, (const float*)x, topi, k, d, experts_per_rank, capacity, cursor,
+              (float*)send_x, send_meta, pair_slot);
+  return REWB200_OK;
+}
+int moe_group_launch(Ctx* c, const void* recv_x, int dtype, const int* recv_meta, int n_slots, int64_t d, int n_experts,
+                     int* count, int* offsets, int* cursor2, void* xs, int* slot_pos) {
+  if (n_slots == 0) return REWB200_OK;
+  RB_LAUNCH(moe_count_kernel, (n_slots + 255) / 256, 256, recv_meta, n_slots, count);
+  RB_LAUNCH(moe_scan_kernel, 1, 32, (const int*)count, n_experts, offsets, cursor2);
+  if (dtype == REWB200_BF16)
+    RB_LAUNCH(moe_gather_kernel<bf16>, n_slots, 128, (const bf16*)recv_x, recv_meta, d, cursor2, (bf16*)xs, slot_pos);
+  else
+    RB_LAUNCH(moe_gather_kernel<float>, n_slots, 128, (const float*)recv_x, recv_meta, d, cursor2, (float*)xs, slot_pos);
+  return REWB200_OK;
+}
+int moe_return_launch(Ctx* c, const float* ys, const int* slot_pos, int n_slots, int64_t d, float* ret) {
+  if (n_slots == 0) return REWB200_OK;
+  RB_LAUNCH(moe_return_kernel, n_slots, 128, ys, slot_pos, d, ret);
+  return REWB200_OK;
+}
+int moe_combine_launch(Ctx* c, const float* back, const int* pair_slot, const float* topw, int64_t tokens, int k, int64_t d,
+                       float* out, int accumulate) {
+  if (tokens == 0) return REWB200_OK;
+  RB_LAUNCH(moe_combine_kernel, tokens, 256, back, pair_slot, topw, k, d, out, accumulate);
+  return REWB200_OK;
+}
 
 int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi) {
   RB_REQUIRE(E >= 1 && E <= 32 * MAX_E_PER_LANE, "MoE routing supports up to 256 experts");

@@ -81,7 +81,7 @@ extern "C" int rewb200_linear_noalloc(int slot, const void* x, const void* w, co
   int ks = linear_bf16_pick_ksplit(c, M, K, N);
   while (ks > 1 && (size_t)ks * slab_bytes > kNoAllocScratchBytes) ks /= 2;
   LinearBf16Plan plan;
-  RB_TRY(linear_bf16_plan(&plan, (const bf16*)w, K, N, 1));
+  RB_TRY(linear_bf16_plan(&plan, (const bf16*)w, K, N, 0));
   RB_TRY(linear_bf16_launch(c, plan, (const bf16*)x, K, M, EPI_PARTIAL_F32, ks, scratch, N, nullptr, nullptr, 0));
   const int64_t n = M * N;
   sum_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(scratch, ks, M * N, bias, (bf16*)y, M, N);

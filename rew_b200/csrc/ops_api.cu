@@ -107,7 +107,7 @@ int rewb200_linear(const rewb200_buffer* x, const rewb200_buffer* w, const rewb2
     return gemm_f32_launch(c, (const float*)x->ptr, (const float*)w->ptr, bias, (float*)(*y)->ptr, M, K, N);
   RB_REQUIRE(x->dtype == REWB200_BF16, "Linear.forward: dtype must be f32 or bf16");
   LinearBf16Plan plan;
-  RB_TRY(linear_bf16_plan(&plan, (const bf16*)w->ptr, K, N, 1));
+  RB_TRY(linear_bf16_plan(&plan, (const bf16*)w->ptr, K, N, 0));
   return linear_bf16_launch(c, plan, (const bf16*)x->ptr, K, M, EPI_BIAS_BF16, 1, (*y)->ptr, N, bias, nullptr, 0);
 }
 
