@@ -12,6 +12,9 @@ N(0, 0.02) generated on the device, uniform random prompt ids):
     l70_b16  Llama-3-70B-shaped, bf16, batch 16, prompt 1024; with --gpus N > 1 the model is
              tensor-parallel over the N ranks (heads, FFN columns and vocabulary sharded, NCCL
              all-reduce after o-proj and down-proj): strong scaling
+    moe_b64  DeepSeek-V2-Lite-shaped MoE, bf16, global batch 64, prompt 256; with --gpus N > 1 the
+             routed experts are sharded over the ranks (expert parallel), every rank owns 64/N
+             sequences and each MoE layer does an all-to-all dispatch and combine
 With --gpus N > 1 the l8 workloads run N independent replicas (sequences are independent units; no
 data-path collective): weak scaling.
     tiny     the tiny fp32 Llama of the parity tests
@@ -45,6 +48,7 @@ WORKLOADS = {
     "l8_b1": dict(model="llama3_8b", batch=1, prompt=512),
     "tiny": dict(model="tiny_llama", batch=1, prompt=32),
     "l70_b16": dict(model="llama3_70b", batch=16, prompt=1024, parallel="tp"),
+    "moe_b64": dict(model="deepseek_v2_lite", batch=64, prompt=256, parallel="ep"),
 }
 
 
@@ -245,13 +249,17 @@ def main():
     max_len = S + Wm + K + 8
     cfg.max_seq = max(cfg.max_seq, max_len)
     parallel = "single" if world == 1 else wl.get("parallel", "replicas")
-    if parallel == "tp":
-        cfg.tp_rank, cfg.tp_size = rank, world
+    if parallel == "ep":
+        cfg.ep_rank, cfg.ep_size = rank, world
+        B = B // world
+    if parallel in ("tp", "ep"):
+        if parallel == "tp":
+            cfg.tp_rank, cfg.tp_size = rank, world
         box = [api.comm_unique_id() if rank == 0 else None]
         pg.broadcast_object_list(box, src=0)
         api.comm_init(box[0], rank, world)
     data_seed = 0 if parallel == "tp" else rank       # tensor-parallel ranks must see the same tokens
-    model = api.CausalLM(cfg).init_random(seed=1234 + data_seed, std=0.02)
+    model = api.CausalLM(cfg).init_random(seed=1234 if parallel == "ep" else 1234 + data_seed, std=0.02)
     sess = model.session(B, max_len)
     prompt = np.random.default_rng(1 + data_seed).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
 
@@ -278,7 +286,7 @@ def main():
         pg.all_reduce(t, op=pg.ReduceOp.MAX)
         decode_ms = float(t[0])
         pg.barrier()
-    tokens = B * K * (1 if parallel == "tp" else world)
+    tokens = B * K * (1 if parallel == "tp" else world)   # B is per rank for replicas and ep
     value = tokens / (decode_ms * 1e-3)
 
     # ---- end to end through the C ABI: host prompt ids -> host output ids
@@ -296,7 +304,15 @@ def main():
 
     # ---- roofline of the dominant kernel (the bf16 weight-streaming Linear)
     roofline = None
-    if cfg.dtype == _lib.BF16:
+    peak, which = measured_peaks()
+    kv_b = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
+    if cfg.n_routed > 0:
+        # MoE: whole-step figure only (weights of every local expert + KV, read once per step)
+        step_bytes = model.weight_bytes() - cfg.vocab * cfg.d_model * 2 + kv_b
+        ach = step_bytes / (decode_ms / K * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                    "kernel": "whole decode step", "bytes_per_step": step_bytes, "peak_source": which}
+    elif cfg.dtype == _lib.BF16:
         ms = C.c_float()
         nbytes = C.c_int64()
         nl = C.c_int32()

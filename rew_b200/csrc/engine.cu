@@ -888,9 +888,10 @@ int rewb200_model_init_random(rewb200_model* m, uint64_t seed, float std) {
     if (L.moe) {
       const uint64_t router_seed = seed * 1000003ull + 500000ull + (uint64_t)(&L - &m->layers[0]);  // same on every rank
       RB_TRY(fill_normal_launch(c, L.x.router.w, dt, L.x.router.K * L.x.router.N, router_seed, std));
-      k += (uint64_t)m->cfg.ep_rank * 104729ull;
-      RB_TRY(fill_normal_launch(c, L.x.gu, dt, (int64_t)L.x.E_l * m->cfg.d_model * 2 * L.x.f, ++k, std));
-      RB_TRY(fill_normal_launch(c, L.x.down, dt, (int64_t)L.x.E_l * L.x.f * m->cfg.d_model, ++k, std));
+      // experts differ per rank; everything else above must be identical on every rank
+      const uint64_t ke = (router_seed * 31ull + 7ull) ^ ((uint64_t)(m->cfg.ep_rank + 1) << 40);
+      RB_TRY(fill_normal_launch(c, L.x.gu, dt, (int64_t)L.x.E_l * m->cfg.d_model * 2 * L.x.f, ke + 1, std));
+      RB_TRY(fill_normal_launch(c, L.x.down, dt, (int64_t)L.x.E_l * L.x.f * m->cfg.d_model, ke + 2, std));
     }
   }
   RB_TRY(fill_normal_launch(c, m->lm.w, dt, m->lm.K * m->lm.N, ++k, std));

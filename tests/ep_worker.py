@@ -1,0 +1,66 @@
+"""One expert-parallel rank of tests/test_gpu_ep.py (child process, one per GPU): its own sequences,
+its own slice of the routed experts, all-to-all dispatch / combine with the other rank."""
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def config(rank, world):
+    from rew_b200 import _lib, weights as W
+    return W.ModelConfig(vocab=256, d_model=128, n_layers=3, n_heads=2, n_kv_heads=2, head_dim=64, ffn=192, max_seq=128,
+                         theta=10000.0, eps=1e-6, n_routed=8, n_shared=2, top_k=3, moe_ffn=64, first_dense=192,
+                         dtype=_lib.BF16, mask_kind=1, ep_rank=rank, ep_size=world)
+
+
+def weights(cfg):
+    from rew_b200 import weights as W
+    t = W.init_weights(cfg, seed=31, std=0.08, trivial_affine=False)
+    names = [n for n, _ in W.tensor_specs(cfg)]
+    for l in (1, 2):  # a router bias that fixes the chosen experts, spread over both ranks' slices
+        b = np.zeros(8, np.float32)
+        b[[1, 4, 6]] = 50.0
+        t[names.index("model.layers.%d.moe.gate.bias" % l)] = b
+    return [W.bf16_round(a) if a.ndim == 2 else a for a in t]
+
+
+def prompt_of(rank):
+    return np.random.default_rng(40 + rank).integers(0, 256, size=(2, 19)).astype(np.int32)
+
+
+def main():
+    rank, world, idfile, outfile = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+    from rew_b200 import _lib, api
+    print("rank", rank, "starting", flush=True)
+    _lib.init(rank)
+    if rank == 0:
+        uid = api.comm_unique_id()
+        with open(idfile + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(idfile + ".tmp", idfile)
+    else:
+        t0 = time.time()
+        while not os.path.exists(idfile):
+            if time.time() - t0 > 60:
+                raise RuntimeError("rank 0 never published the communicator id")
+            time.sleep(0.05)
+        uid = open(idfile, "rb").read()
+    api.comm_init(uid, rank, world)
+    cfg = config(rank, world)
+    prompt = prompt_of(rank)
+    # every rank feeds the same number of tokens per step: the all-to-all slot arrays have one fixed capacity
+    sess = api.CausalLM(cfg).load(weights(cfg)).session(prompt.shape[0], 64)
+    nxt, logits = sess.forward(prompt, want_logits=True)
+    ids, last = sess.decode(4, want_logits=True)
+    print("rank", rank, "done", flush=True)
+    np.savez(outfile, nxt=nxt, logits=logits, ids=ids, last=last)
+    sess.free()
+    api.comm_destroy()
+
+
+if __name__ == "__main__":
+    main()
