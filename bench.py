@@ -258,6 +258,12 @@ def main():
         box = [api.comm_unique_id() if rank == 0 else None]
         pg.broadcast_object_list(box, src=0)
         api.comm_init(box[0], rank, world)
+        if parallel == "tp" and os.environ.get("REW_B200_TP_ALLREDUCE", "fused") == "fused":
+            # decode-size all-reduces run fused into the residual+norm kernel over peer memory
+            mine = api.comm_peer_alloc(64 * cfg.d_model * 4)
+            handles = [None] * world
+            pg.all_gather_object(handles, mine)
+            api.comm_peer_attach(handles)
     data_seed = 0 if parallel == "tp" else rank       # tensor-parallel ranks must see the same tokens
     model = api.CausalLM(cfg).init_random(seed=1234 if parallel == "ep" else 1234 + data_seed, std=0.02)
     sess = model.session(B, max_len)

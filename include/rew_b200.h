@@ -211,6 +211,13 @@ int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int
 int rewb200_comm_unique_id(void* id128);                  /* 128 bytes, created on rank 0 */
 int rewb200_comm_init(int slot, const void* id128, int rank, int world);
 int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n);
+/* Fused one-shot all-reduce for decode-size tensor-parallel steps: each rank allocates an exchange heap
+ * (two buffers of buf_bytes) and exports a 64-byte CUDA IPC handle; after the host has gathered every
+ * rank's handle (rank order, world*64 bytes), attach maps the peers.  Sessions created afterwards sum the
+ * row-parallel partials by reading all ranks' buffers inside the residual+norm kernel (plain peer loads
+ * over NVLink behind a bounded flag barrier) whenever rows*d_model*4 <= buf_bytes; larger steps use NCCL. */
+int rewb200_comm_peer_alloc(int slot, int64_t buf_bytes, void* handle64);
+int rewb200_comm_peer_attach(int slot, const void* handles_all);
 /* Free every session of the slot first: a captured decode graph keeps the communicator in use and
  * NCCL waits for it. */
 int rewb200_comm_destroy(int slot);

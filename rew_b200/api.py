@@ -311,3 +311,16 @@ def comm_init(unique_id, rank, world, slot=0):
 
 def comm_destroy(slot=0):
     check(lib().rewb200_comm_destroy(slot))
+
+
+def comm_peer_alloc(buf_bytes, slot=0):
+    """Allocates this rank's exchange heap for the fused all-reduce; returns its 64-byte IPC handle."""
+    buf = C.create_string_buffer(64)
+    check(lib().rewb200_comm_peer_alloc(slot, buf_bytes, buf))
+    return buf.raw
+
+
+def comm_peer_attach(handles, slot=0):
+    """handles: the 64-byte handles of all ranks, in rank order."""
+    blob = b"".join(handles)
+    check(lib().rewb200_comm_peer_attach(slot, C.create_string_buffer(blob, len(blob))))

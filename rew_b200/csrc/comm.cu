@@ -103,11 +103,79 @@ int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t b
   return REWB200_OK;
 }
 
+// ---- peer heap for the fused one-shot all-reduce ------------------------------
+// One cudaMalloc per rank: [16 flag ints | pad][epoch int | pad][buffer A][buffer B], exported with
+// CUDA IPC and mapped by every other rank of the node.  Peers are only ever read with plain loads.
+struct PeerHeap {
+  void* local = nullptr;
+  void* mapped[8] = {};
+  PeerInfo info;
+  bool attached = false;
+};
+static PeerHeap g_heap[16];
+
+static void heap_layout(void* base, size_t buf_bytes, int** flags, int** epoch, float** a, float** b) {
+  char* p = (char*)base;
+  *flags = (int*)p;
+  *epoch = (int*)(p + 256);
+  *a = (float*)(p + 512);
+  *b = (float*)(p + 512 + buf_bytes);
+}
+
+const PeerInfo* comm_peer_info(int slot) {
+  return (slot >= 0 && slot < 16 && g_heap[slot].attached) ? &g_heap[slot].info : nullptr;
+}
+
 }  // namespace rewb
 
 using namespace rewb;
 
 extern "C" {
+
+int rewb200_comm_peer_alloc(int slot, int64_t buf_bytes, void* handle64) {
+  Ctx* c = ctx_get(slot);
+  if (!c) return REWB200_ERR;
+  RB_REQUIRE(handle64 != nullptr && buf_bytes > 0 && buf_bytes % 256 == 0, "rewb200_comm_peer_alloc: buffer size must be a positive multiple of 256");
+  RB_REQUIRE(slot < 16 && g_comm[slot].comm, "rewb200_comm_peer_alloc: call rewb200_comm_init first");
+  RB_REQUIRE(g_comm[slot].world <= 8, "the fused all-reduce supports up to 8 ranks");
+  RB_REQUIRE(!g_heap[slot].local, "rewb200_comm_peer_alloc: already allocated for this slot");
+  RB_CUDA(cudaSetDevice(c->device));
+  PeerHeap& h = g_heap[slot];
+  const size_t total = 512 + 2 * (size_t)buf_bytes;
+  RB_CUDA(cudaMalloc(&h.local, total));
+  RB_CUDA(cudaMemset(h.local, 0, total));
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
+  cudaIpcMemHandle_t ih;
+  RB_CUDA(cudaIpcGetMemHandle(&ih, h.local));
+  memcpy(handle64, &ih, 64);
+  h.info.world = g_comm[slot].world;
+  h.info.rank = g_comm[slot].rank;
+  h.info.buf_bytes = (size_t)buf_bytes;
+  return REWB200_OK;
+}
+
+int rewb200_comm_peer_attach(int slot, const void* handles_all) {
+  Ctx* c = ctx_get(slot);
+  if (!c) return REWB200_ERR;
+  RB_REQUIRE(slot < 16 && g_heap[slot].local && handles_all, "rewb200_comm_peer_attach: call rewb200_comm_peer_alloc first");
+  RB_CUDA(cudaSetDevice(c->device));
+  PeerHeap& h = g_heap[slot];
+  for (int r = 0; r < h.info.world; ++r) {
+    void* base = h.local;
+    if (r != h.info.rank) {
+      cudaIpcMemHandle_t ih;
+      memcpy(&ih, (const char*)handles_all + (size_t)r * 64, 64);
+      RB_CUDA(cudaIpcOpenMemHandle(&h.mapped[r], ih, cudaIpcMemLazyEnablePeerAccess));
+      base = h.mapped[r];
+    }
+    int* ep = nullptr;
+    heap_layout(base, h.info.buf_bytes, &h.info.flags[r], &ep, &h.info.bufs[0][r], &h.info.bufs[1][r]);
+    if (r == h.info.rank) h.info.epoch = ep;
+  }
+  RB_CUDA(cudaDeviceSynchronize());
+  h.attached = true;
+  return REWB200_OK;
+}
 
 int rewb200_comm_unique_id(void* id128) {
   RB_REQUIRE(id128 != nullptr, "rewb200_comm_unique_id: NULL buffer");
@@ -156,6 +224,13 @@ int rewb200_comm_destroy(int slot) {
   if (c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
+  }
+  PeerHeap& h = g_heap[slot];
+  if (h.local) {
+    for (int r = 0; r < 8; ++r)
+      if (h.mapped[r]) cudaIpcCloseMemHandle(h.mapped[r]);
+    cudaFree(h.local);
+    h = PeerHeap();
   }
   g_nccl.CommDestroy(g_comm[slot].comm);
   g_comm[slot].comm = nullptr;

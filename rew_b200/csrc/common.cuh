@@ -155,6 +155,16 @@ struct NormArgs {
   int out_dtype;
   int vocab;
   int* status;
+  // One-shot tensor-parallel all-reduce fused into this kernel (n_peers > 0): slab r of the sum is
+  // read from rank r's memory (peer_part[r], plain peer loads over NVLink; own rank included) after a
+  // flag barrier: this rank stores `*epoch + barrier_offset` into its cell of every rank's flag array
+  // and waits (bounded) until every cell of its own flag array has reached that value.
+  int n_peers;
+  int my_rank;
+  const float* peer_part[8];
+  int* peer_flags[8];     // flag arrays of all ranks (index by rank), 16 ints each
+  const int* epoch;       // device counter, advanced once per forward on every rank alike
+  int barrier_offset;
 };
 int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows);
 
@@ -214,6 +224,16 @@ int attn_launch(Ctx* c, const AttnArgs& a);
 size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits);
 
 // scratch (optional): rows*64*8 bytes lets wide rows be scanned by several CTAs each
+struct PeerInfo {
+  int world = 0, rank = 0;
+  size_t buf_bytes = 0;        // capacity of each of the two exchange buffers
+  float* bufs[2][8] = {};      // [which][rank] (own rank: the local allocation)
+  int* flags[8] = {};          // [rank]
+  int* epoch = nullptr;        // local device counter
+};
+// nullptr when no peer heap has been attached for the slot
+const PeerInfo* comm_peer_info(int slot);
+
 int argmax_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int* out_ids, void* scratch, size_t scratch_bytes);
 int swiglu_f32_launch(Ctx* c, const float* g, const float* u, float* out, int64_t n);
 int cast_launch(Ctx* c, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n);

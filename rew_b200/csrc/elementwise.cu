@@ -159,6 +159,28 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
     }
     erow = reinterpret_cast<const TE*>(a.embed) + id * d;
   }
+  if (a.n_peers > 0) {
+    // flag barrier across the tensor-parallel ranks (bounded wait; a timeout is reported, never a hang)
+    const int target = *a.epoch + a.barrier_offset;
+    if (blockIdx.x == 0 && threadIdx.x < a.n_peers) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flags[threadIdx.x] + a.my_rank), "r"(target) : "memory");
+    }
+    if (threadIdx.x < a.n_peers) {
+      const int* cell = a.peer_flags[a.my_rank] + threadIdx.x;
+      const uint64_t t0 = global_timer_ns();
+      for (uint32_t it = 0;; ++it) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(cell) : "memory");
+        if (v - target >= 0) break;
+        if ((it & 63u) == 63u && global_timer_ns() - t0 > 2000000000ull) {
+          atomicExch(a.status, KS_PEER_TIMEOUT);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
   float4 vals[NCH];
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
@@ -166,7 +188,18 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < d) {
       v = erow ? Vec4<TE>::load(erow + i) : *reinterpret_cast<const float4*>(xr + i);
-      if (a.partial) {
+      if (a.n_peers > 0) {
+        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < a.n_peers; ++r) {  // fixed rank order: every rank computes the same sum
+          const float4 q = __ldcv(reinterpret_cast<const float4*>(a.peer_part[r] + row * d + i));
+          p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
+        }
+        if (a.bias) {
+          const float4 b = *reinterpret_cast<const float4*>(a.bias + i);
+          p.x += b.x; p.y += b.y; p.z += b.z; p.w += b.w;
+        }
+        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+      } else if (a.partial) {
         const float* pp = a.partial + row * d + i;
         float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
         int s = 0;
@@ -190,7 +223,7 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
         }
         v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
       }
-      if (a.x_res && (erow || a.partial)) *reinterpret_cast<float4*>(xr + i) = v;
+      if (a.x_res && (erow || a.partial || a.n_peers > 0)) *reinterpret_cast<float4*>(xr + i) = v;
     }
     vals[c] = v;
   }
@@ -466,6 +499,26 @@ __global__ void __launch_bounds__(32) argmax_gathered_kernel(const void* gathere
   if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
+// dst[i] = part[0][i] + part[1][i] + ...  (dst: this rank's exchange buffer for the fused all-reduce)
+__global__ void __launch_bounds__(256) slab_sum_to_kernel(const float* part, int nsplit, int64_t slab, int64_t n4, float* dst) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 a = reinterpret_cast<const float4*>(part)[i];
+  for (int s = 1; s < nsplit; ++s) {
+    const float4 b = reinterpret_cast<const float4*>(part + s * slab)[i];
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  }
+  reinterpret_cast<float4*>(dst)[i] = a;
+}
+
+__global__ void epoch_bump_kernel(int* epoch, int by) {
+  pdl_launch_dependents();
+  pdl_wait();
+  *epoch += by;
+}
+
 // part[0][i] += part[1][i] + ... (before a tensor-parallel all-reduce of one slab)
 __global__ void __launch_bounds__(256) slab_sum_kernel(float* part, int nsplit, int64_t slab, int64_t n4) {
   pdl_launch_dependents();
@@ -531,6 +584,7 @@ int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows) {
   RB_REQUIRE(a.d <= (int64_t)NORM_THREADS * NORM_MAX_PER_THREAD, "norm width above 16384 is not supported");
   const bool e16 = a.embed_dtype == REWB200_BF16, o16 = a.out_dtype == REWB200_BF16;
   cudaError_t e;
+  RB_REQUIRE(a.n_peers == 0 || a.d % 4 == 0, "the fused all-reduce needs d_model % 4 == 0");
   if (a.d % 4 == 0) {
     const int nch = (int)((a.d / 4 + NORMV_THREADS - 1) / NORMV_THREADS);
     dim3 g((unsigned)rows), b(NORMV_THREADS);
@@ -610,6 +664,22 @@ int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows
   if (rows == 0) return REWB200_OK;
   RB_CUDA(launch_k(argmax_gathered_kernel, dim3((unsigned)rows), dim3(32), 0, c->stream, c->use_pdl, gathered, world,
                    (int)rows, nchunks, out));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int slab_sum_to_launch(Ctx* c, const float* part, int nsplit, int64_t slab_elems, float* dst) {
+  if (slab_elems == 0) return REWB200_OK;
+  RB_REQUIRE(slab_elems % 4 == 0, "slab size must be a multiple of 4 floats");
+  const int64_t n4 = slab_elems / 4;
+  RB_CUDA(launch_k(slab_sum_to_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, c->stream, c->use_pdl, part, nsplit,
+                   slab_elems, n4, dst));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
+int epoch_bump_launch(Ctx* c, int* epoch, int by) {
+  RB_CUDA(launch_k(epoch_bump_kernel, dim3(1), dim3(1), 0, c->stream, c->use_pdl, epoch, by));
   ++g_launch_total;
   return REWB200_OK;
 }

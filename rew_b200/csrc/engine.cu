@@ -32,6 +32,8 @@ int comm_rank(int slot);
 int comm_allreduce_sum_f32(Ctx* c, int slot, float* ptr, int64_t n);
 int comm_allgather_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_rank);
 int slab_sum_launch(Ctx* c, float* part, int nsplit, int64_t slab_elems);
+int slab_sum_to_launch(Ctx* c, const float* part, int nsplit, int64_t slab_elems, float* dst);
+int epoch_bump_launch(Ctx* c, int* epoch, int by);
 int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_peer);
 int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi);
 int moe_reset_launch(Ctx* c, int* cursor, int n_cursor, int* count, int n_count, int* meta, int n_meta);
@@ -490,6 +492,32 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     a.beta = m->layers[0].ln1b;
     RB_TRY(residual_norm_launch(c, a, rows));
   }
+  // Tensor parallel: decode-size steps sum the row-parallel partials with the fused one-shot
+  // all-reduce (peer loads inside residual_norm); larger ones go through NCCL.
+  const PeerInfo* pi = cf.tp_size > 1 ? comm_peer_info(m->slot) : nullptr;
+  const bool oneshot = pi != nullptr && d % 4 == 0 && (size_t)rows * d * sizeof(float) <= pi->buf_bytes &&
+                       pi->world == cf.tp_size;
+  auto tp_reduce = [&](int l, int which, int& ks, NormArgs& a) -> int {
+    if (cf.tp_size <= 1) return REWB200_OK;
+    if (oneshot) {
+      RB_TRY(slab_sum_to_launch(c, s->part, ks, rows * d, pi->bufs[which][pi->rank]));
+      a.n_peers = pi->world;
+      a.my_rank = pi->rank;
+      for (int r = 0; r < pi->world; ++r) {
+        a.peer_part[r] = pi->bufs[which][r];
+        a.peer_flags[r] = pi->flags[r];
+      }
+      a.epoch = pi->epoch;
+      a.barrier_offset = 2 * l + which + 1;
+      a.partial = nullptr;
+      return REWB200_OK;
+    }
+    RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
+    RB_TRY(comm_allreduce_sum_f32(c, m->slot, s->part, rows * d));
+    ks = 1;
+    a.nsplit = 1;
+    return REWB200_OK;
+  };
   for (int l = 0; l < cf.n_layers; ++l) {
     LayerDev& L = m->layers[l];
     int ks = 1;
@@ -553,11 +581,6 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     RB_TRY(attn_launch(c, aa));
 
     RB_TRY(run_linear(s, L.o, s->attn, m->nq, rows, true, 0, s->part, d, &ks));
-    if (cf.tp_size > 1) {  // sum the local split-K slabs, then one all-reduce of [rows, d]
-      RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
-      RB_TRY(comm_allreduce_sum_f32(c, m->slot, s->part, rows * d));
-      ks = 1;
-    }
     {
       NormArgs a = na;
       a.partial = s->part;
@@ -566,6 +589,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       a.bias = L.o.b;
       a.gamma = L.ln2g;
       a.beta = L.ln2b;
+      RB_TRY(tp_reduce(l, 0, ks, a));
       RB_TRY(residual_norm_launch(c, a, rows));
     }
     ks = 0;  // slabs of s->part that hold FFN output so far
@@ -585,11 +609,6 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       RB_TRY(moe_routed(s, L, rows, ks > 0));
       if (ks == 0) ks = 1;
     }
-    if (cf.tp_size > 1) {
-      RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
-      RB_TRY(comm_allreduce_sum_f32(c, m->slot, s->part, rows * d));
-      ks = 1;
-    }
     {
       NormArgs a = na;
       a.partial = s->part;
@@ -599,9 +618,11 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       const bool last = (l + 1 == cf.n_layers);
       a.gamma = last ? m->ng : m->layers[l + 1].ln1g;
       a.beta = last ? m->nb : m->layers[l + 1].ln1b;
+      RB_TRY(tp_reduce(l, 1, ks, a));
       RB_TRY(residual_norm_launch(c, a, rows));
     }
   }
+  if (oneshot) RB_TRY(epoch_bump_launch(c, pi->epoch, 2 * cf.n_layers));  // same on every rank
   // lm_head: last position of every sequence (generate.nim:172-190) or every row.
   const int64_t lrows = o.all_logits ? rows : s->B;
   const char* xl = (const char*)s->xn + (o.all_logits ? 0 : (size_t)(o.S - 1) * d * dtype_size(dt));

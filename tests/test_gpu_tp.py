@@ -33,7 +33,10 @@ def _bundled_nccl():
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_tp2_generate_matches_oracle(orc):
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
+def test_tp2_generate_matches_oracle(orc, mode):
+    """mode nccl: every all-reduce through NCCL; fused: decode-size steps use the one-shot all-reduce
+    over peer memory inside the residual+norm kernel (prefill rows here are small enough to use it too)."""
     from rew_b200 import _lib
     with tempfile.TemporaryDirectory() as d:
         idfile = os.path.join(d, "nccl_id")
@@ -43,7 +46,7 @@ def test_tp2_generate_matches_oracle(orc):
             env["REW_B200_NCCL"] = nccl  # the newest NCCL on the machine, without importing its owner
         logs = [open(os.path.join(d, "rank%d.log" % r), "w+") for r in range(2)]
         procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "tp_worker.py"), str(r), "2", idfile,
-                                   os.path.join(d, "out%d.npz" % r)], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
+                                   os.path.join(d, "out%d.npz" % r), mode], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
                  for r in range(2)]
         codes = []
         for p in procs:

@@ -28,6 +28,22 @@ def main():
         uid = open(idfile, "rb").read()
     api.comm_init(uid, rank, world)
     print("rank", rank, "communicator ready", flush=True)
+    fused = len(sys.argv) > 5 and sys.argv[5] == "fused"
+    if fused:  # exchange the IPC handles of the all-reduce heaps through files
+        mine = api.comm_peer_alloc(1 << 20)
+        with open("%s.h%d.tmp" % (idfile, rank), "wb") as f:
+            f.write(mine)
+        os.replace("%s.h%d.tmp" % (idfile, rank), "%s.h%d" % (idfile, rank))
+        handles = []
+        for r in range(world):
+            t0 = time.time()
+            while not os.path.exists("%s.h%d" % (idfile, r)):
+                if time.time() - t0 > 60:
+                    raise RuntimeError("rank %d never published its heap handle" % r)
+                time.sleep(0.05)
+            handles.append(open("%s.h%d" % (idfile, r), "rb").read())
+        api.comm_peer_attach(handles)
+        print("rank", rank, "peer heap attached", flush=True)
     results = {}
     for name, dtype, hd, nh, kvh in (("f32", _lib.F32, 32, 8, 2), ("bf16", _lib.BF16, 64, 4, 2)):
         cfg = W.ModelConfig(vocab=512, d_model=256, n_layers=2, n_heads=nh, n_kv_heads=kvh, head_dim=hd, ffn=688, max_seq=128,
