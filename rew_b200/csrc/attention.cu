@@ -18,6 +18,7 @@
 //                        (quad shuffles), warps and splits merge by log-sum-exp.
 //   attn_prefill_kernel  bf16, S > 1: flash-attention forward, 64 queries per CTA.
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -537,6 +538,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
 }
 
 int decode_splits(Ctx* c, int64_t B, int kvh) {
+  if (const char* e = getenv("REW_B200_ATTN_SPLITS")) {  // tuning override
+    const int v = atoi(e);
+    if (v >= 1 && v <= 16) return v;
+  }
   const int64_t base = B * kvh;
   if (base >= c->sm_count) return 1;
   int64_t s = (2 * c->sm_count + base - 1) / base;

@@ -14,8 +14,10 @@
 //   - Split-K partials (f32) go to scratch and are summed by the consumer
 //     kernel (residual+norm or QKV post-processing), never by atomics, so
 //     results are deterministic.
-// The same kernel with 128-row tiles serves prefill until the tcgen05 path takes
-// it over; grouped launches (blockIdx.z = expert) serve the MoE experts.
+// The default bf16 Linear is the tcgen05 kernel of linear_tc.cu; this mma.sync
+// kernel serves the grouped launches of the MoE experts (blockIdx.z = expert,
+// 3-D tensor map, device-side row offsets) and stays selectable for everything
+// else with the option linear = "mma" (128-row tiles for more than 64 rows).
 #include "common.cuh"
 #include "ptx.cuh"
 

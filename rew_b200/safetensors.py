@@ -1,0 +1,134 @@
+"""safetensors files and the Hugging Face Llama naming → this backend's canonical tensors.
+
+File format as rew reads it (src/rew/safetensors.nim:1-80): 8-byte little-endian header length, a JSON
+header {name: {"dtype", "shape", "data_offsets": [start, end]}, "__metadata__": {...}}, then the raw
+tensor bytes.  rew's own loadLlamaWeights (src/rew/hf/hub.nim:395-430) walks the Hugging Face names but
+discards every tensor; this module does the mapping that stub leaves out:
+
+  * HF Linear weights are [out, in]; rew's are [in, out] (src/rew/nn/linear.nim:21-25): transpose.
+  * HF Llama applies RoPE to the pairs (i, i + head_dim/2) ("rotate half"); rew rotates the interleaved
+    pairs (2i, 2i+1) (src/rew/nn/rope.nim:56-108).  Permuting the output features of q_proj and k_proj
+    inside every head (rew feature 2i <- HF i, 2i+1 <- HF i + head_dim/2) makes the two equivalent:
+    scores are dot products over the head dimension, so a common permutation of q and k cancels.
+  * RMSNorm weights become gamma with beta = 0 (use norm_kind = 0); missing biases are zero; a missing
+    lm_head.weight is tied to the embedding.
+"""
+import json
+import struct
+
+import numpy as np
+
+from .weights import from_bf16_bits, tensor_specs, to_bf16_bits
+
+_DTYPES = {"F32": np.float32, "F16": np.float16, "F64": np.float64, "I32": np.int32, "I64": np.int64, "U8": np.uint8,
+           "I8": np.int8, "I16": np.int16, "BOOL": np.bool_}
+
+
+def read_safetensors(path):
+    """{name: float32/int numpy array}; BF16 and F16 are widened to float32."""
+    with open(path, "rb") as f:
+        raw = f.read()
+    if len(raw) < 8:
+        raise ValueError("safetensors: file too short")
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    if 8 + hlen > len(raw):
+        raise ValueError("safetensors: header length exceeds the file")
+    header = json.loads(raw[8:8 + hlen].decode("utf-8"))
+    data = memoryview(raw)[8 + hlen:]
+    out = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        start, end = info["data_offsets"]
+        shape = tuple(info["shape"])
+        buf = data[start:end]
+        dt = info["dtype"]
+        if dt == "BF16":
+            arr = from_bf16_bits(np.frombuffer(buf, dtype=np.uint16)).reshape(shape)
+        elif dt in _DTYPES:
+            arr = np.frombuffer(buf, dtype=_DTYPES[dt]).reshape(shape)
+            if dt in ("F16", "F64"):
+                arr = arr.astype(np.float32)
+        else:
+            raise ValueError("unsupported safetensors dtype: " + dt)
+        if arr.size * arr.itemsize != (end - start) and dt != "BF16" and dt not in ("F16", "F64"):
+            raise ValueError("safetensors: tensor %s has inconsistent offsets" % name)
+        out[name] = arr
+    return out
+
+
+def write_safetensors(path, tensors, dtype="F32"):
+    """Writes {name: array}; dtype F32 or BF16 for floating tensors."""
+    header, blobs, off = {}, [], 0
+    for name, a in tensors.items():
+        a = np.ascontiguousarray(a)
+        if a.dtype == np.float32 and dtype == "BF16":
+            blob, dt = to_bf16_bits(a).tobytes(), "BF16"
+        else:
+            blob = a.tobytes()
+            dt = {np.dtype(np.float32): "F32", np.dtype(np.int32): "I32", np.dtype(np.int64): "I64"}[a.dtype]
+        header[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + len(blob)]}
+        blobs.append(blob)
+        off += len(blob)
+    hj = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+def _interleave_heads(w_out_in, n_heads, head_dim):
+    """Reorders output features (axis 0 of an HF [out, in] weight, or a bias) inside each head from the
+    rotate-half layout to rew's interleaved layout."""
+    half = head_dim // 2
+    perm = np.empty(head_dim, np.int64)
+    perm[0::2] = np.arange(half)
+    perm[1::2] = np.arange(half) + half
+    idx = (np.arange(n_heads)[:, None] * head_dim + perm[None, :]).ravel()
+    return w_out_in[idx]
+
+
+def llama_from_hf(cfg, hf):
+    """Canonical tensor list (rew_b200.weights.tensor_specs order) from Hugging Face Llama tensors."""
+    d, hd = cfg.d_model, cfg.head_dim
+
+    def get(name, default=None):
+        if name in hf:
+            return np.asarray(hf[name], np.float32)
+        if default is None:
+            raise KeyError("safetensors: missing tensor " + name)
+        return default
+
+    out = {}
+    embed = get("model.embed_tokens.weight")
+    out["model.embedTokens.weight"] = embed
+    for l in range(cfg.n_layers):
+        hp, p = "model.layers.%d." % l, "model.layers.%d." % l
+        for hf_name, name, heads in (("q_proj", "qProj", cfg.n_heads), ("k_proj", "kProj", cfg.n_kv_heads),
+                                     ("v_proj", "vProj", 0), ("o_proj", "outProj", 0)):
+            w = get(hp + "self_attn.%s.weight" % hf_name)                       # [out, in]
+            b = get(hp + "self_attn.%s.bias" % hf_name, np.zeros(w.shape[0], np.float32))
+            if heads:
+                w, b = _interleave_heads(w, heads, hd), _interleave_heads(b, heads, hd)
+            out[p + "selfAttn.%s.weight" % name] = np.ascontiguousarray(w.T)      # [in, out]
+            out[p + "selfAttn.%s.bias" % name] = b
+        for hf_name, name in (("gate_proj", "gateProj"), ("up_proj", "upProj"), ("down_proj", "downProj")):
+            w = get(hp + "mlp.%s.weight" % hf_name)
+            out[p + "mlp.%s.weight" % name] = np.ascontiguousarray(w.T)
+            out[p + "mlp.%s.bias" % name] = get(hp + "mlp.%s.bias" % hf_name, np.zeros(w.shape[0], np.float32))
+        out[p + "inputLayernorm.gamma"] = get(hp + "input_layernorm.weight")
+        out[p + "inputLayernorm.beta"] = np.zeros(d, np.float32)
+        out[p + "postAttentionLayernorm.gamma"] = get(hp + "post_attention_layernorm.weight")
+        out[p + "postAttentionLayernorm.beta"] = np.zeros(d, np.float32)
+    out["model.norm.gamma"] = get("model.norm.weight")
+    out["model.norm.beta"] = np.zeros(d, np.float32)
+    lm = get("lm_head.weight", embed)                                            # tied when absent
+    out["lmHead.weight"] = np.ascontiguousarray(lm.T)
+    out["lmHead.bias"] = np.zeros(cfg.vocab, np.float32)
+    specs = tensor_specs(cfg)
+    for name, shape in specs:
+        if tuple(out[name].shape) != tuple(shape):
+            raise ValueError("safetensors: %s has shape %r, expected %r" % (name, out[name].shape, shape))
+    return [out[name] for name, _ in specs]

@@ -1,0 +1,87 @@
+"""safetensors reading and the Hugging Face Llama -> rew layout mapping (transpose, rotate-half ->
+interleaved RoPE permutation), checked on CPU against a Hugging-Face-convention forward in PyTorch."""
+import numpy as np
+import torch
+
+from conftest import rel_l2
+from rew_b200 import safetensors as ST
+from rew_b200 import weights as W
+
+
+def _hf_weights(cfg, seed):
+    rng = np.random.default_rng(seed)
+    d, hd = cfg.d_model, cfg.head_dim
+    t = {"model.embed_tokens.weight": rng.normal(0, 0.05, (cfg.vocab, d)), "model.norm.weight": 1 + 0.1 * rng.normal(size=d),
+         "lm_head.weight": rng.normal(0, 0.05, (cfg.vocab, d))}
+    for l in range(cfg.n_layers):
+        p = "model.layers.%d." % l
+        t[p + "self_attn.q_proj.weight"] = rng.normal(0, 0.05, (cfg.n_heads * hd, d))
+        t[p + "self_attn.k_proj.weight"] = rng.normal(0, 0.05, (cfg.n_kv_heads * hd, d))
+        t[p + "self_attn.v_proj.weight"] = rng.normal(0, 0.05, (cfg.n_kv_heads * hd, d))
+        t[p + "self_attn.o_proj.weight"] = rng.normal(0, 0.05, (d, cfg.n_heads * hd))
+        t[p + "mlp.gate_proj.weight"] = rng.normal(0, 0.05, (cfg.ffn, d))
+        t[p + "mlp.up_proj.weight"] = rng.normal(0, 0.05, (cfg.ffn, d))
+        t[p + "mlp.down_proj.weight"] = rng.normal(0, 0.05, (d, cfg.ffn))
+        t[p + "input_layernorm.weight"] = 1 + 0.1 * rng.normal(size=d)
+        t[p + "post_attention_layernorm.weight"] = 1 + 0.1 * rng.normal(size=d)
+    return {k: v.astype(np.float32) for k, v in t.items()}
+
+
+def _hf_forward(cfg, t, ids):
+    """Llama as Hugging Face computes it: x @ W.T, RMSNorm, rotate-half RoPE, causal attention."""
+    P = {k: torch.from_numpy(v.astype(np.float64)) for k, v in t.items()}
+    B, S = ids.shape
+    hd, nh, kvh = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+    inv = 1.0 / (cfg.theta ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    ang = torch.arange(S, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+
+    def rot(x):
+        x1, x2 = x[..., :hd // 2], x[..., hd // 2:]
+        return x * cos + torch.cat([-x2, x1], -1) * sin
+
+    def rms(x, g):
+        return g * (x / torch.sqrt((x * x).mean(-1, keepdim=True) + cfg.eps))
+
+    h = P["model.embed_tokens.weight"][torch.from_numpy(ids).long()]
+    mask = torch.triu(torch.full((S, S), float("-inf"), dtype=torch.float64), 1)
+    for l in range(cfg.n_layers):
+        p = "model.layers.%d." % l
+        x = rms(h, P[p + "input_layernorm.weight"])
+        q = (x @ P[p + "self_attn.q_proj.weight"].T).view(B, S, nh, hd).transpose(1, 2)
+        k = (x @ P[p + "self_attn.k_proj.weight"].T).view(B, S, kvh, hd).transpose(1, 2)
+        v = (x @ P[p + "self_attn.v_proj.weight"].T).view(B, S, kvh, hd).transpose(1, 2)
+        q, k = rot(q), rot(k)
+        k, v = k.repeat_interleave(nh // kvh, 1), v.repeat_interleave(nh // kvh, 1)
+        a = torch.softmax(q @ k.transpose(-1, -2) / np.sqrt(hd) + mask, -1) @ v
+        h = h + a.transpose(1, 2).reshape(B, S, nh * hd) @ P[p + "self_attn.o_proj.weight"].T
+        x = rms(h, P[p + "post_attention_layernorm.weight"])
+        g, u = x @ P[p + "mlp.gate_proj.weight"].T, x @ P[p + "mlp.up_proj.weight"].T
+        h = h + (torch.nn.functional.silu(g) * u) @ P[p + "mlp.down_proj.weight"].T
+    return (rms(h, P["model.norm.weight"]) @ P["lm_head.weight"].T).numpy()
+
+
+def test_safetensors_round_trip(tmp_path):
+    cfg = W.tiny_llama(mask_kind=1)
+    t = _hf_weights(cfg, 0)
+    ST.write_safetensors(str(tmp_path / "m.safetensors"), t)
+    back = ST.read_safetensors(str(tmp_path / "m.safetensors"))
+    assert set(back) == set(t) and all(np.array_equal(back[k], t[k]) for k in t)
+    ST.write_safetensors(str(tmp_path / "b.safetensors"), t, dtype="BF16")
+    back = ST.read_safetensors(str(tmp_path / "b.safetensors"))
+    assert all(np.array_equal(back[k], W.bf16_round(t[k])) for k in t)
+
+
+def test_hf_llama_mapping_reproduces_hf_semantics(tmp_path, orc):
+    cfg = W.tiny_llama(mask_kind=1, norm_kind=0)
+    t = _hf_weights(cfg, 1)
+    ST.write_safetensors(str(tmp_path / "m.safetensors"), t)
+    canon = ST.llama_from_hf(cfg, ST.read_safetensors(str(tmp_path / "m.safetensors")))
+    ids = np.random.default_rng(2).integers(0, cfg.vocab, size=(2, 12)).astype(np.int32)
+    got = orc.model_forward(cfg, canon, ids, 0, True)     # rew semantics on the converted weights
+    want = _hf_forward(cfg, t, ids)                       # Hugging Face semantics on the original ones
+    assert rel_l2(got, want) < 5e-6
+    # tied head when lm_head.weight is absent
+    t2 = {k: v for k, v in t.items() if k != "lm_head.weight"}
+    canon2 = ST.llama_from_hf(cfg, t2)
+    assert np.array_equal(canon2[-2], t["model.embed_tokens.weight"].T)
