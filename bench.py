@@ -223,6 +223,8 @@ def main():
     ap.add_argument("--impl", default="rew_b200", choices=["rew_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
+    ap.add_argument("--sampling", default="greedy", choices=["greedy", "top_k", "top_p"],
+                    help="next-token rule of the decode step; greedy is the metric's configuration")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     rank, local_rank, world = dist_env()
@@ -267,6 +269,10 @@ def main():
     data_seed = 0 if parallel == "tp" else rank       # tensor-parallel ranks must see the same tokens
     model = api.CausalLM(cfg).init_random(seed=1234 if parallel == "ep" else 1234 + data_seed, std=0.02)
     sess = model.session(B, max_len)
+    if args.sampling == "top_k":
+        sess.set_sampling(temperature=0.8, top_k=50, repetition_penalty=1.1, seeds=np.arange(B, dtype=np.uint64))
+    elif args.sampling == "top_p":
+        sess.set_sampling(temperature=0.8, top_k=0, top_p=0.9, repetition_penalty=1.1, seeds=np.arange(B, dtype=np.uint64))
     prompt = np.random.default_rng(1 + data_seed).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
 
     # ---- device-resident decode: prefill, W warm-up steps, K timed steps
@@ -343,7 +349,7 @@ def main():
         "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong" if parallel == "tp" else "weak", "vs_baseline": None,
         "dtype": "bf16" if cfg.dtype == _lib.BF16 else "f32", "data": "synthetic",
         "config": {"workload": args.workload + ("" if args.layers <= 0 else "_%dlayers" % args.layers), "batch_per_gpu": B, "prompt": S, "decode_steps": K,
-                   "parallelism": parallel + (str(world) if world > 1 else ""),
+                   "parallelism": parallel + (str(world) if world > 1 else ""), "sampling": args.sampling,
                    "l2": "weights per step (%.1f GB) exceed the 126 MB L2" % (model.weight_bytes() / 1e9)},
         "prefill": {"tokens_per_s": B * S * (1 if parallel == "tp" else world) / (prefill_ms * 1e-3), "ms": prefill_ms},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,

@@ -63,6 +63,9 @@ int rewb200_sync(int slot, int timeout_ms);
  *   "linear" = "mma" | "tc_prefill" | "tc"   bf16 Linear on mma.sync, on tcgen05 for more than 32
  *                                            rows, or on tcgen05 always   (REW_B200_LINEAR)
  *   "pdl"    = "0" | "1"                     programmatic dependent launch (REW_B200_PDL)
+ *   "sampling" = "bucket" | "radix"          top-k / top-p selection: bucket histograms with the
+ *                                            radix select as the exact fallback (default), or
+ *                                            the radix select always
  * Takes effect for later launches; sessions re-capture their decode graph on the next decode. */
 int rewb200_set_option(int slot, const char* key, const char* value);
 /* Number of kernels this library has launched on the slot since init. */
@@ -191,6 +194,24 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
  * and every sequence has produced it. last_logits optional [batch,vocab]. */
 int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
                      float* last_logits);
+/* GenerationConfig sampling on the device (src/rew/infer/generate.nim:12-58 for
+ * the fields and their checks, :92-159 sampleTopK / sampleTopP / sampleGreedy,
+ * :192-218 applySamplingConfig, :231-265 the loop).  After this call forward,
+ * decode and rewb200_generate pick each next token as generate() does:
+ * repetition penalty over prompt + generated tokens, temperature, min-p, then
+ * greedy (do_sample == 0 or temperature <= 0.01), top-k (top_k > 0, at most
+ * 1024) or top-p.  Sequence b draws from Key = initKey(seeds[b]) (seeds NULL:
+ * all 0, the reference's default key) and folds the step number in after every
+ * token (src/rew/rng.nim:33-80).  Keys and step counters restart at
+ * rewb200_session_reset, hence at every rewb200_generate.  Not available on a
+ * tensor-parallel model. */
+int rewb200_session_set_sampling(rewb200_session* s, float temperature, int top_k, float top_p, float min_p,
+                                 float repetition_penalty, int do_sample, const uint64_t* seeds);
+/* Back to plain greedy argmax. */
+int rewb200_session_clear_sampling(rewb200_session* s);
+/* logProbOf (generate.nim:220-227) of the first n tokens sampled since the last
+ * reset, host f32 [batch,n]. */
+int rewb200_session_logprobs(rewb200_session* s, int n, float* out);
 /* Device-time of the last forward / decode call in milliseconds (CUDA events). */
 int rewb200_session_last_ms(const rewb200_session* s, float* prefill_ms, float* decode_ms);
 /* Kernels in one captured decode step (0 before the first decode). */

@@ -291,3 +291,45 @@ def decode_bench(mc, tensors, batch, ctx, n_steps):
     keep, arr = _tensor_array(tensors)
     last = np.empty(batch, np.int32)
     return float(lib().orc_decode_bench(C.byref(cfg), arr, C.c_int64(batch), C.c_int64(ctx), n_steps, _ip(last)))
+
+
+# ---- random keys and sampling (src/rew/rng.nim, src/rew/infer/generate.nim:92-150) ----
+def threefry(ka, kb, ca, cb):
+    out = (C.c_uint32 * 2)()
+    lib().orc_threefry(C.c_uint32(ka), C.c_uint32(kb), C.c_uint32(ca), C.c_uint32(cb), out)
+    return int(out[0]), int(out[1])
+
+
+def uniform01(seed, folds=()):
+    """uniformF32(key, 1, 0, 1)[0] for key = initKey(seed) folded with each value of `folds` in turn."""
+    lib().orc_uniform01.restype = C.c_float
+    f = (C.c_uint64 * max(1, len(folds)))(*folds)
+    return float(lib().orc_uniform01(C.c_uint64(seed), len(folds), f))
+
+
+def sample_top_k(logits, top_k, seed):
+    lg = _f(logits)
+    return int(lib().orc_sample_top_k(_p(lg), C.c_int64(lg.size), int(top_k), C.c_uint64(seed)))
+
+
+def sample_top_p(logits, top_p, seed):
+    lg = _f(logits)
+    return int(lib().orc_sample_top_p(_p(lg), C.c_int64(lg.size), C.c_float(top_p), C.c_uint64(seed)))
+
+
+def generate_sampled(mc, tensors, prompt, n_new, temperature=1.0, top_k=50, top_p=1.0, min_p=0.0,
+                     repetition_penalty=1.0, do_sample=True, seeds=None):
+    """generate() with a GenerationConfig per sequence of `prompt` [B,S]; returns (ids [B,n_new], logprobs [B,n_new])."""
+    cfg = cfg_of(mc)
+    keep, arr = _tensor_array(tensors)
+    pr = np.ascontiguousarray(prompt, dtype=np.int32)
+    if pr.ndim == 1:
+        pr = pr.reshape(1, -1)
+    B, S = pr.shape
+    sd = np.zeros(B, np.uint64) if seeds is None else np.ascontiguousarray(seeds, dtype=np.uint64)
+    ids = np.empty((B, n_new), np.int32)
+    lps = np.empty((B, n_new), np.float32)
+    lib().orc_generate_sampled(C.byref(cfg), arr, _ip(pr), C.c_int64(B), C.c_int64(S), int(n_new), C.c_float(temperature),
+                               int(top_k), C.c_float(top_p), C.c_float(min_p), C.c_float(repetition_penalty),
+                               int(bool(do_sample)), sd.ctypes.data_as(C.POINTER(C.c_uint64)), _ip(ids), _p(lps))
+    return ids, lps

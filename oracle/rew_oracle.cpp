@@ -792,3 +792,149 @@ ORC_API double orc_decode_bench(const Cfg* c, const float* const* tensors, int64
   if (last_ids) std::memcpy(last_ids, cur.data(), sizeof(int32_t) * B);
   return std::chrono::duration<double>(t1 - t0).count();
 }
+
+// ---------------------------------------------------------------- sampling
+// Threefry-2x32, four rounds, src/rew/rng.nim:33-56; foldIn :75-80; the unit
+// float of src/rew/nn/init.nim:14-17; uniformF32(key, 1, 0, 1)[0] :19-27.
+namespace {
+struct Key { uint32_t a, b; };
+inline uint32_t rotl32(uint32_t x, uint32_t r) { return (x << r) | (x >> (32u - r)); }
+Key threefry2x32(Key key, Key ctr) {
+  static const uint32_t rot[4] = {13u, 15u, 26u, 6u};
+  const uint32_t k0 = key.a, k1 = key.b, k2 = k0 ^ k1 ^ 0x1BD11BDAu;
+  uint32_t x0 = ctr.a + k0, x1 = ctr.b + k1;
+  for (int r = 0; r < 4; ++r) {
+    x0 = x0 + x1;
+    x1 = rotl32(x1, rot[r]);
+    x1 = x1 ^ x0;
+  }
+  x0 = x0 + k1;
+  x1 = x1 + k2 + 1u;
+  return Key{x0, x1};
+}
+Key init_key(uint64_t seed) { return Key{(uint32_t)(seed & 0xFFFFFFFFull), (uint32_t)(seed >> 32)}; }
+Key fold_in(Key k, uint64_t data) { return threefry2x32(k, Key{(uint32_t)(data & 0xFFFFFFFFull), (uint32_t)(data >> 32)}); }
+float unit_float(uint32_t x) { return (float)(x >> 8) * (1.0f / 16777216.0f); }
+float uniform01(Key key) { return 0.0f + (1.0f - 0.0f) * unit_float(fold_in(key, 0).a); }
+
+// (value, index) sorted by value descending; equal values keep ascending index (Nim's sort is stable).
+std::vector<std::pair<float, int>> sorted_desc(const float* logits, int64_t V) {
+  std::vector<std::pair<float, int>> s(V);
+  for (int64_t i = 0; i < V; ++i) s[i] = {logits[i], (int)i};
+  std::stable_sort(s.begin(), s.end(), [](const std::pair<float, int>& x, const std::pair<float, int>& y) { return x.first > y.first; });
+  return s;
+}
+
+// src/rew/infer/generate.nim:92-116
+int sample_top_k(const float* logits, int64_t V, int topK, Key key) {
+  auto s = sorted_desc(logits, V);
+  const int k = (int)std::min<int64_t>(topK, V);
+  std::vector<float> probs(k);
+  float sumExp = 0.f;
+  for (int i = 0; i < k; ++i) {
+    probs[i] = std::exp(s[i].first);
+    sumExp += probs[i];
+  }
+  for (int i = 0; i < k; ++i) probs[i] /= sumExp;
+  const float u = uniform01(key);
+  float cum = 0.f;
+  for (int i = 0; i < k; ++i) {
+    cum += probs[i];
+    if (u <= cum) return s[i].second;
+  }
+  return s[k - 1].second;
+}
+
+// src/rew/infer/generate.nim:118-150
+int sample_top_p(const float* logits, int64_t V, float topP, Key key) {
+  auto s = sorted_desc(logits, V);
+  const float maxLogit = s[0].first;
+  std::vector<float> probs(V);
+  float sumExp = 0.f;
+  for (int64_t i = 0; i < V; ++i) {
+    probs[i] = std::exp(s[i].first - maxLogit);
+    sumExp += probs[i];
+  }
+  for (int64_t i = 0; i < V; ++i) probs[i] /= sumExp;
+  float cum = 0.f;
+  int64_t cutoff = V;
+  for (int64_t i = 0; i < V; ++i) {
+    cum += probs[i];
+    if (cum >= topP) {
+      cutoff = i + 1;
+      break;
+    }
+  }
+  float renorm = 0.f;
+  for (int64_t i = 0; i < cutoff; ++i) renorm += probs[i];
+  for (int64_t i = 0; i < cutoff; ++i) probs[i] /= renorm;
+  const float u = uniform01(key);
+  cum = 0.f;
+  for (int64_t i = 0; i < cutoff; ++i) {
+    cum += probs[i];
+    if (u <= cum) return s[i].second;
+  }
+  return s[cutoff - 1].second;
+}
+}  // namespace
+
+ORC_API void orc_threefry(uint32_t ka, uint32_t kb, uint32_t ca, uint32_t cb, uint32_t* out2) {
+  const Key r = threefry2x32(Key{ka, kb}, Key{ca, cb});
+  out2[0] = r.a;
+  out2[1] = r.b;
+}
+ORC_API float orc_uniform01(uint64_t seed, int n_folds, const uint64_t* folds) {
+  Key k = init_key(seed);
+  for (int i = 0; i < n_folds; ++i) k = fold_in(k, folds[i]);
+  return uniform01(k);
+}
+ORC_API int32_t orc_sample_top_k(const float* logits, int64_t V, int topK, uint64_t seed) {
+  return sample_top_k(logits, V, topK, init_key(seed));
+}
+ORC_API int32_t orc_sample_top_p(const float* logits, int64_t V, float topP, uint64_t seed) {
+  return sample_top_p(logits, V, topP, init_key(seed));
+}
+
+// generate() with a GenerationConfig (src/rew/infer/generate.nim:231-265), one key per sequence
+// (the reference loop is batch-1; sequence b starts from initKey(seeds[b])).  Cached forward as in
+// orc_generate_greedy.  out_ids [B,n_new], out_logprobs [B,n_new].
+ORC_API void orc_generate_sampled(const Cfg* c, const float* const* tensors, const int32_t* prompt, int64_t B, int64_t S,
+                                  int n_new, float temperature, int top_k, float top_p, float min_p,
+                                  float repetition_penalty, int do_sample, const uint64_t* seeds, int32_t* out_ids,
+                                  float* out_logprobs) {
+  Model m = build(*c, tensors);
+  const int64_t d = c->d_model, V = c->vocab;
+  std::vector<KV> kvs(c->n_layers);
+  std::vector<int32_t> cur(prompt, prompt + B * S);
+  std::vector<std::vector<int32_t>> seen(B);
+  std::vector<Key> keys(B);
+  for (int64_t b = 0; b < B; ++b) {
+    seen[b].assign(prompt + b * S, prompt + (b + 1) * S);
+    keys[b] = init_key(seeds[b]);
+  }
+  int64_t curS = S, offset = 0;
+  std::vector<float> logits(B * V);
+  for (int step = 0; step < n_new; ++step) {
+    std::vector<float> h(B * curS * d), last(B * d);
+    backbone(m, cur.data(), h.data(), B, curS, offset, 1, &kvs);
+    for (int64_t b = 0; b < B; ++b) std::memcpy(&last[b * d], &h[(b * curS + curS - 1) * d], sizeof(float) * d);
+    linear(last.data(), m.lw, m.lb, logits.data(), B, d, V);
+    std::vector<int32_t> next(B);
+    for (int64_t b = 0; b < B; ++b) {
+      float* lg = &logits[b * V];
+      orc_apply_sampling_config(lg, V, seen[b].data(), (int64_t)seen[b].size(), temperature, min_p, repetition_penalty);
+      int32_t tok;
+      if (!do_sample || temperature <= 0.01f) tok = sample_greedy(lg, V);
+      else if (top_k > 0) tok = sample_top_k(lg, V, top_k, keys[b]);
+      else tok = sample_top_p(lg, V, top_p, keys[b]);
+      next[b] = tok;
+      out_ids[b * n_new + step] = tok;
+      if (out_logprobs) out_logprobs[b * n_new + step] = orc_log_prob_of(lg, V, tok);
+      seen[b].push_back(tok);
+      keys[b] = fold_in(keys[b], (uint64_t)step);
+    }
+    offset += curS;
+    cur = next;
+    curS = 1;
+  }
+}

@@ -76,6 +76,10 @@ SIGNATURES = {
     "rewb200_session_forward": (C.c_int, [P, I32P, C.c_int, I32P, F32P]),
     "rewb200_session_decode": (C.c_int, [P, C.c_int, I32P, F32P]),
     "rewb200_generate": (C.c_int, [P, I32P, C.c_int, C.c_int, C.c_int, I32P, F32P]),
+    "rewb200_session_set_sampling": (C.c_int, [P, C.c_float, C.c_int, C.c_float, C.c_float, C.c_float, C.c_int,
+                                               C.POINTER(C.c_uint64)]),
+    "rewb200_session_clear_sampling": (C.c_int, [P]),
+    "rewb200_session_logprobs": (C.c_int, [P, C.c_int, F32P]),
     "rewb200_session_last_ms": (C.c_int, [P, F32P, F32P]),
     "rewb200_session_graph_kernels": (C.c_int, [P]),
     "rewb200_session_profile_linears": (C.c_int, [P, C.c_int, F32P, I64P, I32P]),

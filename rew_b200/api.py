@@ -262,6 +262,27 @@ class Session:
                                      out.ctypes.data_as(_lib.I32P), logits.ctypes.data_as(_lib.F32P) if want_logits else None))
         return (out, logits) if want_logits else out
 
+    def set_sampling(self, temperature=1.0, top_k=50, top_p=1.0, min_p=0.0, repetition_penalty=1.0, do_sample=True,
+                     seeds=None):
+        """initGenerationConfig (src/rew/infer/generate.nim:30-58) for this session; the defaults are the
+        reference's.  seeds: one uint64 per sequence (initKey); None = 0, the reference's default key."""
+        sp = None
+        if seeds is not None:
+            sd = np.ascontiguousarray(seeds, dtype=np.uint64)
+            assert sd.shape == (self.batch,), "seeds must hold one value per sequence"
+            sp = sd.ctypes.data_as(C.POINTER(C.c_uint64))
+        check(lib().rewb200_session_set_sampling(self._h, float(temperature), int(top_k), float(top_p), float(min_p),
+                                                 float(repetition_penalty), int(bool(do_sample)), sp))
+
+    def clear_sampling(self):
+        check(lib().rewb200_session_clear_sampling(self._h))
+
+    def logprobs(self, n):
+        """GenerationResult.logProbs of the first n tokens sampled since the last reset, [batch, n]."""
+        out = np.empty((self.batch, n), np.float32)
+        check(lib().rewb200_session_logprobs(self._h, n, out.ctypes.data_as(_lib.F32P)))
+        return out
+
     def forward_all(self, ids, offset=0, causal=True):
         """Model.forward without a cache: logits for every position [batch,S,vocab]."""
         a = self._ids(ids)

@@ -44,6 +44,9 @@ int moe_group_launch(Ctx* c, const void* recv_x, int dtype, const int* recv_meta
 int moe_return_launch(Ctx* c, const float* ys, const int* slot_pos, int n_slots, int64_t d, float* ret);
 int moe_combine_launch(Ctx* c, const float* back, const int* pair_slot, const float* topw, int64_t tokens, int k, int64_t d,
                        float* out, int accumulate);
+int sample_launch(Ctx* c, const float* logits, float* work, int64_t B, int64_t V, int* hist, int* hist_len, int hist_cap,
+                  uint32_t* keys, int* steps, int* next, float* logprob, int logprob_cap, float temperature, int top_k,
+                  float top_p, float min_p, float rep_penalty, int do_sample);
 int argmax_partial_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int idx_offset, int nchunks, float* pv, int* pi);
 int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows, int nchunks, int* out);
 
@@ -191,10 +194,33 @@ struct rewb200_session {
   int host_pos = 0;                    // tokens so far (all sequences advance together)
   int graph_kernels = 0;               // kernels in one captured decode step
   int graph_epoch = -1;                // option epoch the graph was captured under
+  // GenerationConfig sampling (generate.nim:12-58); off = greedy argmax
+  bool samp_on = false;
+  float samp_temperature = 1.f, samp_top_p = 1.f, samp_min_p = 0.f, samp_rep = 1.f;
+  int samp_top_k = 0, samp_do_sample = 0;
+  std::vector<uint64_t> samp_seeds;    // one per sequence; keys restart from these on reset
+  int *samp_hist = nullptr, *samp_hist_len = nullptr, *samp_steps = nullptr;  // [B][max_len], [B], [B]
+  uint32_t* samp_keys = nullptr;       // [B][2]
+  float *samp_work = nullptr, *samp_logprob = nullptr;  // [B][V], [B][max_len]
 };
 
 namespace rewb {
 namespace {
+
+// Sampling restarts with every generate call: keys back to initKey(seed), step counters to zero.
+int samp_restart(rewb200_session* s) {
+  Ctx* c = s->m->c;
+  std::vector<uint32_t> k((size_t)s->B * 2);
+  for (int b = 0; b < s->B; ++b) {  // initKey (src/rew/rng.nim:60-64)
+    k[2 * b] = (uint32_t)(s->samp_seeds[b] & 0xFFFFFFFFull);
+    k[2 * b + 1] = (uint32_t)(s->samp_seeds[b] >> 32);
+  }
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_CUDA(cudaMemcpy(s->samp_keys, k.data(), k.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+  RB_CUDA(cudaMemset(s->samp_steps, 0, s->B * sizeof(int)));
+  RB_CUDA(cudaMemset(s->samp_hist_len, 0, s->B * sizeof(int)));
+  return REWB200_OK;
+}
 
 int dev_alloc(rewb200_model* m, void** p, size_t bytes) {
   RB_CUDA(cudaMalloc(p, std::max<size_t>(bytes, 256)));
@@ -650,6 +676,10 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       RB_TRY(argmax_partial_launch(c, s->logits, s->B, m->vocab_l, (int)(cf.tp_rank * m->vocab_l), nch, pv, pi));
       RB_TRY(comm_allgather_bytes(c, m->slot, s->argmax_scratch, s->gather_scratch, (size_t)s->B * nch * 8));
       RB_TRY(argmax_gathered_launch(c, s->gather_scratch, cf.tp_size, s->B, nch, s->d_next));
+    } else if (s->samp_on) {
+      RB_TRY(sample_launch(c, s->logits, s->samp_work, s->B, cf.vocab, s->samp_hist, s->samp_hist_len, s->max_len,
+                           s->samp_keys, s->samp_steps, s->d_next, s->samp_logprob, s->max_len, s->samp_temperature,
+                           s->samp_top_k, s->samp_top_p, s->samp_min_p, s->samp_rep, s->samp_do_sample));
     } else {
       RB_TRY(argmax_launch(c, s->logits, s->B, cf.vocab, s->d_next, s->argmax_scratch, (size_t)s->B * 64 * 8));
     }
@@ -1024,7 +1054,8 @@ void rewb200_session_free(rewb200_session* s) {
   for (void* p : s->kc) cudaFree(p);
   for (void* p : s->vc) cudaFree(p);
   void* ptrs[] = {s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
-                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch, s->gather_scratch, s->moe_logits, s->moe_topw, s->moe_topi, s->moe_ints,
+                  s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch, s->gather_scratch,
+                  s->samp_hist, s->samp_hist_len, s->samp_steps, s->samp_keys, s->samp_work, s->samp_logprob, s->moe_logits, s->moe_topw, s->moe_topi, s->moe_ints,
                   s->moe_send, s->moe_recv, s->moe_xs, s->moe_hs, s->moe_ys, s->moe_ret, s->moe_back, s->moe_tmp};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -1041,6 +1072,7 @@ int rewb200_session_reset(rewb200_session* s) {
   RB_CUDA(cudaMemsetAsync(s->d_pos, 0, s->B * sizeof(int), c->stream));
   RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
   s->host_pos = 0;
+  if (s->samp_on) RB_TRY(samp_restart(s));
   return REWB200_OK;
 }
 
@@ -1060,6 +1092,13 @@ int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32
   RB_CUDA(cudaEventRecord(s->ev0, c->stream));
   RB_CUDA(cudaMemcpyAsync(s->d_ids, s->h_ids, rows * sizeof(int32_t), cudaMemcpyHostToDevice, c->stream));
   RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
+  if (s->samp_on) {
+    // tokens seen so far = everything fed to the model (generate.nim:248 `tokenIds & generated`)
+    RB_CUDA(cudaMemcpy2DAsync(s->samp_hist + s->host_pos, (size_t)s->max_len * sizeof(int), s->d_ids, (size_t)S * sizeof(int),
+                              (size_t)S * sizeof(int), s->B, cudaMemcpyDeviceToDevice, c->stream));
+    std::vector<int> len((size_t)s->B, s->host_pos + S);
+    RB_CUDA(cudaMemcpy(s->samp_hist_len, len.data(), len.size() * sizeof(int), cudaMemcpyHostToDevice));
+  }
   FwdOpts o;
   o.S = S;
   RB_TRY(enqueue_forward(s, o));
@@ -1180,6 +1219,72 @@ int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new
       else if (out_ids[(size_t)b * n_new + t] == eos) hit = true;
     }
   }
+  return REWB200_OK;
+}
+
+int rewb200_session_set_sampling(rewb200_session* s, float temperature, int top_k, float top_p, float min_p,
+                                 float repetition_penalty, int do_sample, const uint64_t* seeds) {
+  RB_REQUIRE(s, "rewb200_session_set_sampling: NULL session");
+  // initGenerationConfig's checks (generate.nim:30-49)
+  RB_REQUIRE(temperature >= 0.f, "initGenerationConfig: temperature must be non-negative");
+  RB_REQUIRE(top_k >= 0, "initGenerationConfig: topK must be non-negative");
+  RB_REQUIRE(top_p > 0.f && top_p <= 1.f, "initGenerationConfig: topP must be in (0, 1]");
+  RB_REQUIRE(min_p >= 0.f && min_p <= 1.f, "initGenerationConfig: minP must be in [0, 1]");
+  RB_REQUIRE(repetition_penalty > 0.f, "initGenerationConfig: repetitionPenalty must be positive");
+  RB_REQUIRE(top_k <= 1024, "device sampling keeps at most 1024 top-k candidates");
+  rewb200_model* m = s->m;
+  RB_REQUIRE(m->cfg.tp_size <= 1, "device sampling is not available on a vocabulary-sharded (tensor-parallel) model");
+  Ctx* c = m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  if (!s->samp_hist) {
+    RB_CUDA(cudaMalloc((void**)&s->samp_hist, (size_t)s->B * s->max_len * sizeof(int)));
+    RB_CUDA(cudaMalloc((void**)&s->samp_hist_len, s->B * sizeof(int)));
+    RB_CUDA(cudaMalloc((void**)&s->samp_steps, s->B * sizeof(int)));
+    RB_CUDA(cudaMalloc((void**)&s->samp_keys, (size_t)s->B * 2 * sizeof(uint32_t)));
+    RB_CUDA(cudaMalloc((void**)&s->samp_work, (size_t)s->B * m->cfg.vocab * sizeof(float)));
+    RB_CUDA(cudaMalloc((void**)&s->samp_logprob, (size_t)s->B * s->max_len * sizeof(float)));
+  }
+  s->samp_seeds.assign((size_t)s->B, 0);
+  if (seeds)
+    for (int b = 0; b < s->B; ++b) s->samp_seeds[b] = seeds[b];
+  s->samp_temperature = temperature;
+  s->samp_top_k = top_k;
+  s->samp_top_p = top_p;
+  s->samp_min_p = min_p;
+  s->samp_rep = repetition_penalty;
+  s->samp_do_sample = do_sample ? 1 : 0;
+  s->samp_on = true;
+  if (s->graph) {  // the captured decode step carries the old sampling arguments
+    cudaGraphExecDestroy(s->graph);
+    s->graph = nullptr;
+  }
+  return samp_restart(s);
+}
+
+int rewb200_session_clear_sampling(rewb200_session* s) {
+  RB_REQUIRE(s, "rewb200_session_clear_sampling: NULL session");
+  Ctx* c = s->m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  s->samp_on = false;
+  if (s->graph) {
+    cudaGraphExecDestroy(s->graph);
+    s->graph = nullptr;
+  }
+  return REWB200_OK;
+}
+
+int rewb200_session_logprobs(rewb200_session* s, int n, float* out) {
+  RB_REQUIRE(s && out, "rewb200_session_logprobs: NULL argument");
+  RB_REQUIRE(s->samp_on, "rewb200_session_logprobs: call rewb200_session_set_sampling first");
+  RB_REQUIRE(n >= 0 && n <= s->max_len, "rewb200_session_logprobs: n out of range");
+  if (n == 0) return REWB200_OK;
+  Ctx* c = s->m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_CUDA(cudaMemcpy2D(out, (size_t)n * sizeof(float), s->samp_logprob, (size_t)s->max_len * sizeof(float),
+                       (size_t)n * sizeof(float), s->B, cudaMemcpyDeviceToHost));
   return REWB200_OK;
 }
 
