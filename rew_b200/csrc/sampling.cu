@@ -1,9 +1,9 @@
 // Token sampling on the device for generate (src/rew/infer/generate.nim:92-159,192-265).
 // The reference copies every step's logits to the host, sorts the whole vocabulary there and
-// samples in Nim loops; here one CTA per sequence does it next to the lm_head output:
+// samples in Nim loops; here a cluster of four CTAs per sequence does it next to the lm_head output:
 //   applySamplingConfig  repetition penalty once per occurrence among the tokens seen so far (a bitmap in
-//                        shared memory finds the seen ids, a rescan of the history counts them),
-//                        temperature, min-p                                   (generate.nim:192-218)
+//                        shared memory finds the seen ids, the thread holding a token's first occurrence
+//                        counts the others), temperature, min-p               (generate.nim:192-218)
 //   greedy               first maximum                                        (:152-159)
 //   sampleTopK           the k largest, sorted (value descending, index ascending = Nim's stable sort),
 //                        exp WITHOUT max subtraction, sequential cumulative sum, u <= cum   (:92-116)
@@ -14,23 +14,31 @@
 // No full sort: both selections first narrow the vocabulary with histograms over a monotone 24-bit
 // code of (max - value) (three 8-bit levels, quarter-logit buckets at the top level, per-warp private
 // histograms so that shared-memory atomics do not pile up on one address), gather the at most 4096
-// survivors and sort only those.  Inputs that the buckets cannot separate (thousands of equal values,
-// more than k tokens at -inf) take the exact path: a radix select over the order-preserving bits of the
-// float itself with ties resolved by index.  Probability-mass histograms add floats with atomics, so a
-// draw within rounding of the boundary between two tokens may resolve either way; the rest is
-// deterministic.
+// survivors into the first CTA's shared memory and sort only those.  Each CTA of the cluster walks a
+// quarter of the vocabulary row; partial histograms and candidates travel through distributed shared
+// memory, and the first CTA takes every decision so that the four can never disagree on how many
+// cluster barriers follow.  Inputs that the buckets cannot separate (thousands of equal values, more
+// than k tokens at -inf) take the exact path in the first CTA: a radix select over the
+// order-preserving bits of the float itself with ties resolved by index.  Probability-mass histograms
+// add floats with atomics and the cumulative sums run as parallel scans, so a draw within rounding of
+// the boundary between two tokens may resolve either way; the rest is deterministic.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace rewb {
 namespace {
 
 constexpr int ST = 1024;       // threads per CTA
 constexpr int NW = ST / 32;    // warps
+constexpr int CS = 4;          // CTAs per sequence (one cluster)
 constexpr int MAX_TOPK = 1024;
 constexpr int CAP = 4096;      // candidates gathered and sorted in shared memory
+constexpr unsigned FULL = 0xffffffffu;
 
 struct SampleArgs {
   const float* logits;   // [B][V]
@@ -86,24 +94,24 @@ __device__ __forceinline__ uint32_t bcode(float v, float M) {
   return ((uint32_t)l1 << 16) | ((uint32_t)l2 << 8) | (uint32_t)l3;
 }
 
-// Visits every (index, value) of p[0..V) once, block-strided.  One CTA walks a whole vocabulary row out
-// of L2, so the loads must overlap: 16-byte loads, four of them in flight per thread.
+// Visits every (index, value) of p[lo..hi) once, block-strided.  One CTA walks its part of a
+// vocabulary row out of L2, so the loads must overlap: 16-byte loads, four in flight per thread.
 template <typename F>
-__device__ __forceinline__ void for_each_value(const float* p, int64_t V, F f) {
-  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
-    const int64_t n4 = V >> 2;
+__device__ __forceinline__ void for_each_value(const float* p, int64_t lo, int64_t hi, F f) {
+  if (((lo | hi) & 3) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    const int64_t j_lo = lo >> 2, j_hi = hi >> 2;
     const float4* p4 = reinterpret_cast<const float4*>(p);
-    for (int64_t j0 = threadIdx.x; j0 < n4; j0 += (int64_t)ST * 4) {
+    for (int64_t j0 = j_lo + threadIdx.x; j0 < j_hi; j0 += (int64_t)ST * 4) {
       float4 r[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int64_t j = j0 + (int64_t)u * ST;
-        if (j < n4) r[u] = p4[j];
+        if (j < j_hi) r[u] = p4[j];
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int64_t j = j0 + (int64_t)u * ST;
-        if (j < n4) {
+        if (j < j_hi) {
           f(4 * j, r[u].x);
           f(4 * j + 1, r[u].y);
           f(4 * j + 2, r[u].z);
@@ -112,20 +120,20 @@ __device__ __forceinline__ void for_each_value(const float* p, int64_t V, F f) {
       }
     }
   } else {
-    for (int64_t i = threadIdx.x; i < V; i += ST) f(i, p[i]);
+    for (int64_t i = lo + threadIdx.x; i < hi; i += ST) f(i, p[i]);
   }
 }
 
 __device__ float block_reduce_sum(float v, float* red) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
   __syncthreads();
   if (threadIdx.x < 32) {
     float t = red[threadIdx.x];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(FULL, t, o);
     if (threadIdx.x == 0) red[32] = t;
   }
   __syncthreads();
@@ -147,25 +155,40 @@ __device__ int block_exclusive_scan(int v, int* scan, int* total) {
   return scan[threadIdx.x] - v;
 }
 
+struct Decision {        // taken by the first CTA, copied by the others
+  uint32_t prefix;       // digits of the code picked so far
+  int level;
+  int above_cnt;         // elements / mass in buckets before the picked one
+  float above_mass;
+  int ok;                // the picked bucket fits CAP
+  float target;          // mass still to cover inside the picked bucket
+  int need;              // elements still to take inside the picked bucket
+};
+
 struct Shared {
   float red[33];
   int hist_i[256];       // exact path: counts per digit
   int scan[ST];
-  int cnt1[256];         // level-0 bucket totals, kept for the second selection
+  int part_cnt[256];     // this CTA's share of a histogram level
+  float part_mass[256];
+  int cnt1[256];         // first CTA: level-0 totals, kept for the second selection
   float mass1[256];
-  int cntw[256];         // totals of the level being refined
+  int cntw[256];         // first CTA: totals of the level being refined
   float massw[256];
-  uint32_t sel_prefix;
+  float part_f[2];       // scalars exchanged across the cluster
+  int part_i[2];
+  int wsum_c[32];
+  float wsum_m[32];
+  Decision dec;
+  uint32_t sel_prefix;   // exact path
   int sel_need;
   float sel_target;
   float sel_above;
   int slot;
   int result;
-  uint32_t bk_prefix;    // bucket selection: digits picked so far
-  int bk_level;
-  int bk_above_cnt;
-  float bk_above_mass;
-  int bk_ok;
+  int pick;
+  int last_nonempty;
+  int first;
   float nucleus;
 };
 
@@ -177,24 +200,10 @@ struct Dyn {             // carved out of dynamic shared memory
   int* cidx;             // [CAP]
 };
 
-// Per-warp private histograms of one level of the code, reduced into cnt_out / mass_out.
-__device__ void bucket_hist(const float* w, int64_t V, float M, int level, uint32_t prefix, const Dyn& dy, int* cnt_out,
-                            float* mass_out) {
-  for (int i = threadIdx.x; i < NW * 256; i += ST) {
-    dy.hc[i] = 0;
-    dy.hm[i] = 0.f;
-  }
-  __syncthreads();
-  const int wp = threadIdx.x >> 5;
-  const int sh_hi = 24 - 8 * level, sh_d = 16 - 8 * level;
-  for_each_value(w, V, [&](int64_t, float v) {
-    const uint32_t c = bcode(v, M);
-    if ((c >> sh_hi) == prefix) {
-      const int bin = (int)((c >> sh_d) & 255u);
-      atomicAdd(&dy.hc[wp * 256 + bin], 1);
-      atomicAdd(&dy.hm[wp * 256 + bin], expf(v - M));
-    }
-  });
+// ---- bucket path ---------------------------------------------------------------------------------
+
+// Folds the per-warp private histograms into this CTA's share (sh.part_cnt / sh.part_mass).
+__device__ void fold_private_hists(const Dyn& dy, Shared& sh) {
   __syncthreads();
   if (threadIdx.x < 256) {
     int c = 0;
@@ -203,78 +212,134 @@ __device__ void bucket_hist(const float* w, int64_t V, float M, int level, uint3
       c += dy.hc[x * 256 + threadIdx.x];
       m += dy.hm[x * 256 + threadIdx.x];
     }
+    sh.part_cnt[threadIdx.x] = c;
+    sh.part_mass[threadIdx.x] = m;
+  }
+  __syncthreads();
+}
+
+// This CTA's share of one level of the code histogram.
+__device__ void bucket_hist_partial(const float* w, int64_t lo, int64_t hi, float M, int level, uint32_t prefix,
+                                    const Dyn& dy, Shared& sh) {
+  for (int i = threadIdx.x; i < NW * 256; i += ST) {
+    dy.hc[i] = 0;
+    dy.hm[i] = 0.f;
+  }
+  __syncthreads();
+  const int wp = threadIdx.x >> 5;
+  const int sh_hi = 24 - 8 * level, sh_d = 16 - 8 * level;
+  for_each_value(w, lo, hi, [&](int64_t, float v) {
+    const uint32_t c = bcode(v, M);
+    if ((c >> sh_hi) == prefix) {
+      const int bin = (int)((c >> sh_d) & 255u);
+      atomicAdd(&dy.hc[wp * 256 + bin], 1);
+      atomicAdd(&dy.hm[wp * 256 + bin], expf(v - M));
+    }
+  });
+  fold_private_hists(dy, sh);
+}
+
+// First CTA: adds the four shares of a level (call between two cluster barriers).
+__device__ void total_hists(cg::cluster_group& cl, Shared& sh, int* cnt_out, float* mass_out) {
+  if (threadIdx.x < 256) {
+    int c = 0;
+    float m = 0.f;
+    for (unsigned r = 0; r < CS; ++r) {
+      const Shared* rs = cl.map_shared_rank(&sh, r);
+      c += rs->part_cnt[threadIdx.x];
+      m += rs->part_mass[threadIdx.x];
+    }
     cnt_out[threadIdx.x] = c;
     mass_out[threadIdx.x] = m;
   }
   __syncthreads();
 }
 
-// Narrows the vocabulary to one bucket of the code.  MASS: the bucket in which the cumulative mass
-// (largest values first) reaches target_mass; otherwise the bucket holding the target_cnt-th largest
-// value.  Succeeds when that bucket (plus everything above it when include_above) fits CAP.
-// Needs sh.cnt1 / sh.mass1 (level 0).  Results in sh.bk_*.
+// First CTA: picks the bucket of one level.  MASS: the first bucket (largest values first) in which the
+// running mass reaches dec.target; otherwise the bucket that holds the dec.need-th largest element.
 template <bool MASS>
-__device__ bool bucket_select(const float* w, int64_t V, float M, float target_mass, int target_cnt, bool include_above,
-                              const Dyn& dy, Shared& sh) {
+__device__ void pick_bucket(const int* cnt, const float* mass, int level, bool include_above, Shared& sh) {
+  const int t = threadIdx.x, lane = t & 31, wp = t >> 5;
+  int c = 0;
+  float m = 0.f;
+  if (t < 256) {
+    c = cnt[t];
+    m = mass[t];
+  }
+  int ic = c;
+  float im = m;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int oc = __shfl_up_sync(FULL, ic, o);
+    const float om = __shfl_up_sync(FULL, im, o);
+    if (lane >= o) {
+      ic += oc;
+      im += om;
+    }
+  }
+  if (t < 256 && lane == 31) {
+    sh.wsum_c[wp] = ic;
+    sh.wsum_m[wp] = im;
+  }
+  if (t == 0) {
+    sh.pick = 256;
+    sh.last_nonempty = -1;
+  }
+  __syncthreads();
+  if (t < 256) {
+    for (int x = 0; x < wp; ++x) {
+      ic += sh.wsum_c[x];
+      im += sh.wsum_m[x];
+    }
+    const bool hit = MASS ? (m > 0.f && im >= sh.dec.target) : (ic >= sh.dec.need);
+    if (hit) atomicMin(&sh.pick, t);
+    if (MASS && m > 0.f) atomicMax(&sh.last_nonempty, t);
+  }
+  __syncthreads();
+  int pick = sh.pick;
+  // MASS: rounding can leave the target just above the total; take the last bucket with any mass
+  if (pick == 256) pick = MASS ? max(sh.last_nonempty, 0) : 255;
+  if (t == pick) {
+    const int accc = ic - c;
+    const float accm = im - m;
+    if (MASS) sh.dec.target -= accm;
+    else sh.dec.need -= accc;
+    sh.dec.above_cnt += accc;
+    sh.dec.above_mass += accm;
+    sh.dec.prefix = (sh.dec.prefix << 8) | (uint32_t)pick;
+    sh.dec.level = level;
+    sh.dec.ok = (c + (include_above ? sh.dec.above_cnt : 0)) <= CAP;
+  }
+  __syncthreads();
+}
+
+// Narrows the vocabulary to one bucket of the code; true when that bucket (plus everything above it
+// when include_above) fits CAP.  The first CTA needs sh.cnt1 / sh.mass1 (level 0).  Result in sh.dec of
+// every CTA.  Every CTA of the cluster must call it with the same arguments.
+template <bool MASS>
+__device__ bool bucket_select(cg::cluster_group& cl, unsigned rank, const float* w, int64_t lo, int64_t hi, float M,
+                              float target_mass, int target_cnt, bool include_above, const Dyn& dy, Shared& sh) {
   if (threadIdx.x == 0) {
-    sh.bk_prefix = 0;
-    sh.bk_above_cnt = 0;
-    sh.bk_above_mass = 0.f;
-    sh.sel_target = target_mass;
-    sh.sel_need = target_cnt;
-    sh.bk_ok = 0;
+    Decision d;
+    d.prefix = 0; d.level = 0; d.above_cnt = 0; d.above_mass = 0.f; d.ok = 0; d.target = target_mass; d.need = target_cnt;
+    sh.dec = d;
   }
   __syncthreads();
   for (int level = 0; level < 3; ++level) {
-    if (level > 0) bucket_hist(w, V, M, level, sh.bk_prefix, dy, sh.cntw, sh.massw);
-    if (threadIdx.x == 0) {
-      const int* cnt = level == 0 ? sh.cnt1 : sh.cntw;
-      const float* mass = level == 0 ? sh.mass1 : sh.massw;
-      int pick = -1, accc = 0;
-      float accm = 0.f;
-      if (MASS) {
-        int last = -1;
-        for (int b = 0; b < 256; ++b) {
-          const float m = mass[b];
-          if (m > 0.f) {
-            last = b;
-            if (accm + m >= sh.sel_target) {
-              pick = b;
-              break;
-            }
-          }
-          accm += m;
-          accc += cnt[b];
-        }
-        if (pick < 0) {  // rounding left the target just above the total: the last bucket with any mass
-          pick = max(last, 0);
-          accm = 0.f;
-          accc = 0;
-          for (int b = 0; b < pick; ++b) {
-            accm += mass[b];
-            accc += cnt[b];
-          }
-        }
-        sh.sel_target -= accm;
-      } else {
-        for (int b = 0; b < 256; ++b) {
-          if (accc + cnt[b] >= sh.sel_need) {
-            pick = b;
-            break;
-          }
-          accc += cnt[b];
-        }
-        if (pick < 0) pick = 255;
-        sh.sel_need -= accc;
-      }
-      sh.bk_above_cnt += accc;
-      sh.bk_above_mass += accm;
-      sh.bk_prefix = (sh.bk_prefix << 8) | (uint32_t)pick;
-      sh.bk_level = level;
-      sh.bk_ok = (cnt[pick] + (include_above ? sh.bk_above_cnt : 0)) <= CAP;
+    if (level > 0) {
+      bucket_hist_partial(w, lo, hi, M, level, sh.dec.prefix, dy, sh);
+      cl.sync();  // every share is complete
     }
-    __syncthreads();
-    if (sh.bk_ok) return true;
+    if (rank == 0) {
+      if (level > 0) total_hists(cl, sh, sh.cntw, sh.massw);
+      pick_bucket<MASS>(level == 0 ? sh.cnt1 : sh.cntw, level == 0 ? sh.mass1 : sh.massw, level, include_above, sh);
+    }
+    cl.sync();  // the decision is published; shares may be overwritten
+    if (rank != 0) {
+      if (threadIdx.x == 0) sh.dec = *cl.map_shared_rank(&sh.dec, 0);
+      __syncthreads();
+    }
+    if (sh.dec.ok) return true;
   }
   return false;
 }
@@ -300,23 +365,29 @@ __device__ void sort_candidates(const Dyn& dy, int n2) {
     }
 }
 
-// Gathers the selected bucket (and everything above it when include_above) and sorts it.
-__device__ int bucket_gather(const float* w, int64_t V, float M, bool include_above, const Dyn& dy, Shared& sh) {
-  const uint32_t prefix = sh.bk_prefix;
-  const int shift = 16 - 8 * sh.bk_level;
-  if (threadIdx.x == 0) sh.slot = 0;
-  __syncthreads();
-  for_each_value(w, V, [&](int64_t i, float v) {
+// Every CTA sends its elements of the selected bucket (and of everything above it when include_above)
+// to the first CTA, which sorts them.  Returns the number gathered (meaningful in the first CTA).
+__device__ int bucket_gather(cg::cluster_group& cl, unsigned rank, const float* w, int64_t lo, int64_t hi, float M,
+                             bool include_above, const Dyn& dy, Shared& sh) {
+  const uint32_t prefix = sh.dec.prefix;
+  const int shift = 16 - 8 * sh.dec.level;
+  if (rank == 0 && threadIdx.x == 0) sh.slot = 0;
+  cl.sync();
+  int* slot0 = cl.map_shared_rank(&sh.slot, 0);
+  float* cval0 = cl.map_shared_rank(dy.cval, 0);
+  int* cidx0 = cl.map_shared_rank(dy.cidx, 0);
+  for_each_value(w, lo, hi, [&](int64_t i, float v) {
     const uint32_t c = bcode(v, M) >> shift;
     if (include_above ? c <= prefix : c == prefix) {
-      const int s = atomicAdd(&sh.slot, 1);
+      const int s = atomicAdd(slot0, 1);
       if (s < CAP) {
-        dy.cval[s] = v;
-        dy.cidx[s] = (int)i;
+        cval0[s] = v;
+        cidx0[s] = (int)i;
       }
     }
   });
-  __syncthreads();
+  cl.sync();
+  if (rank != 0) return 0;
   const int n = min(sh.slot, CAP);
   int n2 = 1;
   while (n2 < n) n2 <<= 1;
@@ -327,6 +398,49 @@ __device__ int bucket_gather(const float* w, int64_t V, float M, bool include_ab
   __syncthreads();
   sort_candidates(dy, n2);
   return n;
+}
+
+// First CTA: first position of the sorted candidates at which base + running mass reaches target
+// (the last position when it never does); *cum_at = base + mass through that position.
+__device__ int cum_find(const Dyn& dy, int n, float M, float base, float target, float* cum_at, Shared& sh) {
+  const int t = threadIdx.x, lane = t & 31, wp = t >> 5;
+  float e[CAP / ST];
+  float run = 0.f;
+#pragma unroll
+  for (int u = 0; u < CAP / ST; ++u) {
+    const int i = t * (CAP / ST) + u;
+    run += (i < n) ? expf(dy.cval[i] - M) : 0.f;
+    e[u] = run;  // inclusive within the thread
+  }
+  float inc = run;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float other = __shfl_up_sync(FULL, inc, o);
+    if (lane >= o) inc += other;
+  }
+  if (lane == 31) sh.wsum_m[wp] = inc;
+  if (t == 0) sh.first = 0x7fffffff;
+  __syncthreads();
+  float off = base + (inc - run);
+  for (int x = 0; x < wp; ++x) off += sh.wsum_m[x];
+#pragma unroll
+  for (int u = 0; u < CAP / ST; ++u) {
+    const int i = t * (CAP / ST) + u;
+    if (i < n && off + e[u] >= target) {
+      atomicMin(&sh.first, i);
+      break;
+    }
+  }
+  __syncthreads();
+  int first = sh.first;
+  if (first == 0x7fffffff) first = n - 1;
+  if (first < 0 && t == 0) sh.nucleus = base;
+#pragma unroll
+  for (int u = 0; u < CAP / ST; ++u)
+    if (first == t * (CAP / ST) + u) sh.nucleus = off + e[u];
+  __syncthreads();
+  *cum_at = sh.nucleus;
+  return first;
 }
 
 // ---- exact path: radix select over the bits of the float itself --------------------------------
@@ -370,7 +484,7 @@ __device__ int mass_select(const float* w, int64_t V, float M, float target, flo
     const uint32_t pmask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
     for (int i = threadIdx.x; i < NW * 256; i += ST) dy.hm[i] = 0.f;
     __syncthreads();
-    for_each_value(w, V, [&](int64_t, float v) {
+    for_each_value(w, 0, V, [&](int64_t, float v) {
       const uint32_t k = fkey(v);
       if ((k & pmask) == prefix) atomicAdd(&dy.hm[wp * 256 + ((k >> shift) & 255u)], expf(v - M));
     });
@@ -429,7 +543,7 @@ __device__ void exact_top_k(const float* w, int64_t V, int k, const Dyn& dy, Sha
     const uint32_t pmask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
     if (threadIdx.x < 256) sh.hist_i[threadIdx.x] = 0;
     __syncthreads();
-    for_each_value(w, V, [&](int64_t, float v) {
+    for_each_value(w, 0, V, [&](int64_t, float v) {
       const uint32_t kk = fkey(v);
       if ((kk & pmask) == prefix) {
         // one atomic per distinct digit in the warp: equal values would otherwise serialise
@@ -462,7 +576,7 @@ __device__ void exact_top_k(const float* w, int64_t V, int k, const Dyn& dy, Sha
     dy.cidx[i] = 0x7fffffff;
   }
   __syncthreads();
-  for_each_value(w, V, [&](int64_t i, float v) {
+  for_each_value(w, 0, V, [&](int64_t i, float v) {
     if (fkey(v) > T) {
       const int s = atomicAdd(&sh.slot, 1);
       if (s < MAX_TOPK) {
@@ -495,14 +609,17 @@ __device__ void exact_top_k(const float* w, int64_t V, int k, const Dyn& dy, Sha
   sort_candidates(dy, n2);
 }
 
+
 // ---- the kernel --------------------------------------------------------------------------------
 
-__global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
+__global__ void __cluster_dims__(CS, 1, 1) __launch_bounds__(ST) sample_kernel(SampleArgs a) {
   extern __shared__ __align__(16) unsigned char dyn_raw[];
   __shared__ Shared sh;
+  cg::cluster_group cl = cg::this_cluster();
+  const unsigned rank = cl.block_rank();
   pdl_launch_dependents();
   pdl_wait();
-  const int b = blockIdx.x;
+  const int b = blockIdx.x / CS;
   const int64_t V = a.V;
   const int nwords = (int)((V + 31) / 32);
   Dyn dy;
@@ -517,6 +634,9 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
   const int nseen = a.hist_len[b];
   const bool greedy = !a.do_sample || a.temperature <= 0.01f;
   const int wp = threadIdx.x >> 5;
+  // this CTA's quarter of the row (whole float4s when the row allows 16-byte loads)
+  const int64_t q = (V & 3) == 0 ? ((V / 4 + CS - 1) / CS) * 4 : (V + CS - 1) / CS;
+  const int64_t lo = min(V, (int64_t)rank * q), hi = min(V, lo + q);
 
   const bool use_pen = a.rep_penalty != 1.0f;
   if (use_pen) {
@@ -532,7 +652,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
   // applySamplingConfig: penalty, temperature; then the maximum for min-p / softmax
   const float temp = fmaxf(a.temperature, 1e-6f);
   float mx = -INFINITY;
-  for_each_value(lg, V, [&](int64_t i, float x) {
+  for_each_value(lg, lo, hi, [&](int64_t i, float x) {
     if (use_pen && (dy.bitmap[i >> 5] >> (i & 31)) & 1u) return;  // seen tokens: below
     x = x / temp;
     w[i] = x;
@@ -543,12 +663,12 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
     // holds a token's first occurrence counts the others and writes that token's value.
     for (int j = threadIdx.x; j < nseen; j += ST) {
       const int t = hrow[j];
-      if (t < 0 || t >= V) continue;
+      if (t < lo || t >= hi) continue;  // another CTA's quarter (or out of range)
       bool first = true;
-      for (int q = 0; q < j; ++q) first &= (hrow[q] != t);
+      for (int p = 0; p < j; ++p) first &= (hrow[p] != t);
       if (!first) continue;
       int cnt = 1;
-      for (int q = j + 1; q < nseen; ++q) cnt += (hrow[q] == t);
+      for (int p = j + 1; p < nseen; ++p) cnt += (hrow[p] == t);
       float x = lg[t];
       for (int r = 0; r < cnt; ++r) x = (x < 0.f) ? x * a.rep_penalty : x / a.rep_penalty;
       x = x / temp;
@@ -557,12 +677,17 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
     }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
   if ((threadIdx.x & 31) == 0) sh.red[wp] = mx;
   __syncthreads();
-  mx = sh.red[0];
-  for (int i = 1; i < 32; ++i) mx = fmaxf(mx, sh.red[i]);
-  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = sh.red[0];
+    for (int i = 1; i < 32; ++i) m = fmaxf(m, sh.red[i]);
+    sh.part_f[0] = m;
+  }
+  cl.sync();
+  mx = cl.map_shared_rank(&sh, 0)->part_f[0];
+  for (unsigned r = 1; r < CS; ++r) mx = fmaxf(mx, cl.map_shared_rank(&sh, r)->part_f[0]);
 
   // min-p, the softmax denominator and (when sampling) the level-0 bucket histograms in one pass
   if (!greedy)
@@ -573,7 +698,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
   __syncthreads();
   float sum = 0.f;
   const float thresh = a.min_p > 0.f ? mx + logf(a.min_p) : -INFINITY;
-  for_each_value(w, V, [&](int64_t i, float x) {
+  for_each_value(w, lo, hi, [&](int64_t i, float x) {
     if (a.min_p > 0.f && x < thresh) {
       x = -INFINITY;
       w[i] = x;
@@ -586,27 +711,21 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
       atomicAdd(&dy.hm[wp * 256 + bin], e);
     }
   });
-  const float sumExp = block_reduce_sum(sum, sh.red);
-  if (!greedy) {
-    if (threadIdx.x < 256) {
-      int c = 0;
-      float m = 0.f;
-      for (int x = 0; x < NW; ++x) {
-        c += dy.hc[x * 256 + threadIdx.x];
-        m += dy.hm[x * 256 + threadIdx.x];
-      }
-      sh.cnt1[threadIdx.x] = c;
-      sh.mass1[threadIdx.x] = m;
-    }
-    __syncthreads();
-  }
+  const float part_sum = block_reduce_sum(sum, sh.red);
+  if (!greedy) fold_private_hists(dy, sh);
+  if (threadIdx.x == 0) sh.part_f[1] = part_sum;
+  cl.sync();  // (the maxima in part_f[0] have been read by everyone before this barrier)
+  float sumExp = 0.f;
+  for (unsigned r = 0; r < CS; ++r) sumExp += cl.map_shared_rank(&sh, r)->part_f[1];
+  if (!greedy && rank == 0) total_hists(cl, sh, sh.cnt1, sh.mass1);
+  cl.sync();  // shares may be overwritten from here on
 
-  int tok = -1;
+  int tok = -1;  // meaningful in the first CTA
   if (greedy) {
     // sampleGreedy: first maximum
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for_each_value(w, V, [&](int64_t i, float v) {
+    for_each_value(w, lo, hi, [&](int64_t i, float v) {
       if (v > bv || (v == bv && (int)i < bi)) {
         bv = v;
         bi = (int)i;
@@ -614,8 +733,8 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
     });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      const float ov = __shfl_xor_sync(FULL, bv, o);
+      const int oi = __shfl_xor_sync(FULL, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) {
         bv = ov;
         bi = oi;
@@ -633,10 +752,28 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
           bv = sh.red[i];
           bi = sh.scan[i];
         }
-      sh.result = (bi == 0x7fffffff) ? 0 : bi;
+      sh.part_f[0] = bv;
+      sh.part_i[0] = bi;
     }
-    __syncthreads();
-    tok = sh.result;
+    cl.sync();
+    if (rank == 0) {
+      if (threadIdx.x == 0) {
+        float bv0 = -INFINITY;
+        int bi0 = 0x7fffffff;
+        for (unsigned r = 0; r < CS; ++r) {
+          const Shared* rs = cl.map_shared_rank(&sh, r);
+          const float v = rs->part_f[0];
+          const int i = rs->part_i[0];
+          if (v > bv0 || (v == bv0 && i < bi0)) {
+            bv0 = v;
+            bi0 = i;
+          }
+        }
+        sh.result = (bi0 == 0x7fffffff) ? 0 : bi0;
+      }
+      __syncthreads();
+      tok = sh.result;
+    }
   } else {
     // u = uniformF32(key, 1, 0, 1)[0] = unit float of foldIn(key, 0).a
     uint32_t ua, ub;
@@ -644,63 +781,54 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
     const float u = (float)(ua >> 8) * (1.0f / 16777216.0f);
     if (a.top_k > 0) {
       const int k = (int)min((int64_t)min(a.top_k, MAX_TOPK), V);
-      if (!a.exact_only && bucket_select<false>(w, V, mx, 0.f, k, true, dy, sh))
-        bucket_gather(w, V, mx, true, dy, sh);  // everything down to the bucket of the k-th value, sorted
-      else
+      if (!a.exact_only && bucket_select<false>(cl, rank, w, lo, hi, mx, 0.f, k, true, dy, sh)) {
+        // everything down to the bucket of the k-th value, sorted in the first CTA
+        bucket_gather(cl, rank, w, lo, hi, mx, true, dy, sh);
+      } else if (rank == 0) {
         exact_top_k(w, V, k, dy, sh);
-      if (threadIdx.x == 0) {
-        // sampleTopK: exp without max subtraction, sequential sums, u <= cum
-        float sumE = 0.f;
-        for (int i = 0; i < k; ++i) sumE += expf(dy.cval[i]);
-        float cum = 0.f;
-        int pick = dy.cidx[k - 1];
-        for (int i = 0; i < k; ++i) {
-          cum += expf(dy.cval[i]) / sumE;
-          if (u <= cum) {
-            pick = dy.cidx[i];
-            break;
-          }
-        }
-        sh.result = pick;
       }
-      __syncthreads();
-      tok = sh.result;
+      if (rank == 0) {
+        if (threadIdx.x == 0) {
+          // sampleTopK: exp without max subtraction, sequential sums, u <= cum
+          float sumE = 0.f;
+          for (int i = 0; i < k; ++i) sumE += expf(dy.cval[i]);
+          float cum = 0.f;
+          int pick = dy.cidx[k - 1];
+          for (int i = 0; i < k; ++i) {
+            cum += expf(dy.cval[i]) / sumE;
+            if (u <= cum) {
+              pick = dy.cidx[i];
+              break;
+            }
+          }
+          sh.result = pick;
+        }
+        __syncthreads();
+        tok = sh.result;
+      }
     } else {
       // sampleTopP: nucleus cutoff, then the draw inside the nucleus
       bool done = false;
       const float t1 = a.top_p * sumExp;
-      if (!a.exact_only && bucket_select<true>(w, V, mx, t1, 0, false, dy, sh)) {
-        int n = bucket_gather(w, V, mx, false, dy, sh);
-        if (threadIdx.x == 0) {
-          float cum = sh.bk_above_mass;
-          for (int i = 0; i < n; ++i) {
-            cum += expf(dy.cval[i] - mx);
-            if (cum >= t1) break;
-          }
-          sh.nucleus = cum;
+      if (!a.exact_only && bucket_select<true>(cl, rank, w, lo, hi, mx, t1, 0, false, dy, sh)) {
+        int n = bucket_gather(cl, rank, w, lo, hi, mx, false, dy, sh);
+        if (rank == 0) {
+          float cum;
+          cum_find(dy, n, mx, sh.dec.above_mass, t1, &cum, sh);  // leaves the nucleus mass in sh.nucleus
         }
-        __syncthreads();
-        const float t2 = u * sh.nucleus;
-        if (bucket_select<true>(w, V, mx, t2, 0, false, dy, sh)) {
-          n = bucket_gather(w, V, mx, false, dy, sh);
-          if (threadIdx.x == 0) {
-            float cum = sh.bk_above_mass;
-            int pick = n > 0 ? dy.cidx[n - 1] : -1;
-            for (int i = 0; i < n; ++i) {
-              cum += expf(dy.cval[i] - mx);
-              if (cum >= t2) {
-                pick = dy.cidx[i];
-                break;
-              }
-            }
-            sh.result = pick;
+        cl.sync();
+        const float t2 = u * cl.map_shared_rank(&sh, 0)->nucleus;
+        if (bucket_select<true>(cl, rank, w, lo, hi, mx, t2, 0, false, dy, sh)) {
+          n = bucket_gather(cl, rank, w, lo, hi, mx, false, dy, sh);
+          if (rank == 0) {
+            float cum;
+            const int at = cum_find(dy, n, mx, sh.dec.above_mass, t2, &cum, sh);
+            tok = at >= 0 ? dy.cidx[at] : -1;
           }
-          __syncthreads();
-          tok = sh.result;
           done = true;
         }
       }
-      if (!done) {
+      if (!done && rank == 0) {
         float nucleus = 0.f;
         mass_select(w, V, mx, t1, &nucleus, dy, sh);
         __syncthreads();
@@ -709,25 +837,29 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
       }
     }
   }
-  __syncthreads();
-  if (tok < 0 || tok >= V) {
-    if (threadIdx.x == 0) atomicExch(a.status, KS_BAD_INDEX);
-    tok = 0;
-  }
-  if (threadIdx.x == 0) {
-    a.next[b] = tok;
-    const int st = a.steps[b];
-    a.steps[b] = st + 1;
-    if (a.logprob && st < a.logprob_cap) a.logprob[(int64_t)b * a.logprob_cap + st] = w[tok] - mx - logf(sumExp);
-    if (nseen < a.hist_cap) {
-      a.hist[(int64_t)b * a.hist_cap + nseen] = tok;
-      a.hist_len[b] = nseen + 1;
+  if (rank == 0) {
+    __syncthreads();
+    if (tok < 0 || tok >= V) {
+      if (threadIdx.x == 0) atomicExch(a.status, KS_BAD_INDEX);
+      tok = 0;
     }
-    uint32_t na, nb;  // key = foldIn(key, step)
-    threefry2x32(a.keys[2 * b], a.keys[2 * b + 1], (uint32_t)st, 0u, &na, &nb);
-    a.keys[2 * b] = na;
-    a.keys[2 * b + 1] = nb;
+    if (threadIdx.x == 0) {
+      a.next[b] = tok;
+      const int st = a.steps[b];
+      a.steps[b] = st + 1;
+      // w[tok] may have been written by another CTA of the cluster: read it from L2
+      if (a.logprob && st < a.logprob_cap) a.logprob[(int64_t)b * a.logprob_cap + st] = __ldcg(&w[tok]) - mx - logf(sumExp);
+      if (nseen < a.hist_cap) {
+        a.hist[(int64_t)b * a.hist_cap + nseen] = tok;
+        a.hist_len[b] = nseen + 1;
+      }
+      uint32_t na, nb;  // key = foldIn(key, step)
+      threefry2x32(a.keys[2 * b], a.keys[2 * b + 1], (uint32_t)st, 0u, &na, &nb);
+      a.keys[2 * b] = na;
+      a.keys[2 * b + 1] = nb;
+    }
   }
+  cl.sync();  // no CTA leaves while another may still read its shared memory
 }
 
 }  // namespace
@@ -749,7 +881,7 @@ int sample_launch(Ctx* c, const float* logits, float* work, int64_t B, int64_t V
     RB_CUDA(cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cur = smem;
   }
-  RB_CUDA(launch_k(sample_kernel, dim3((unsigned)B), dim3(ST), smem, c->stream, c->use_pdl, a));
+  RB_CUDA(launch_k(sample_kernel, dim3((unsigned)(B * CS)), dim3(ST), smem, c->stream, c->use_pdl, a));
   ++g_launch_total;
   return REWB200_OK;
 }
