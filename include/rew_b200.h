@@ -194,6 +194,31 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
  * and every sequence has produced it. last_logits optional [batch,vocab]. */
 int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
                      float* last_logits);
+/* ---- paged lanes: continuous batching --------------------------------------
+ * PagedKvCache (src/rew/infer/generate.nim:63-88: blockSize, numBlocks,
+ * freeBlocks) made operational.  The session owns `num_blocks` KV blocks of 64
+ * tokens shared by `lanes` sequences; block 0 is the scratch block idle lanes
+ * write to, the others are handed out on demand as a lane's sequence grows and
+ * return to the free list when the lane is released.  Sequences join and leave
+ * between decode steps, each with its own length; the decode step is the same
+ * captured CUDA graph over all lanes (idle lanes report -1).  Not available on
+ * tensor- or expert-parallel models. */
+int rewb200_session_create_paged(rewb200_model* m, int lanes, int max_len, int num_blocks, rewb200_session** out);
+/* Free blocks left in the pool (-1 when the session is not paged). */
+int rewb200_session_free_blocks(const rewb200_session* s);
+/* Tokens in the cache of an active lane (-1: idle lane or bad argument). */
+int rewb200_lane_length(const rewb200_session* s, int lane);
+/* Starts a sequence in an idle lane: reserves blocks for the S prompt tokens
+ * (host int32 [S]), prefills that lane alone and returns its first new token.
+ * With sampling set, the lane's key restarts from initKey(seed). */
+int rewb200_lane_admit(rewb200_session* s, int lane, const int32_t* ids, int S, uint64_t seed, int32_t* next_id);
+/* n_steps decode steps for every active lane; out_ids host int32
+ * [lanes,n_steps], -1 for idle lanes.  Fails without side effects when the pool
+ * cannot cover the growth of every active lane ("out of free blocks"). */
+int rewb200_lanes_step(rewb200_session* s, int n_steps, int32_t* out_ids);
+/* Ends a lane's sequence and returns its blocks to the pool (idempotent). */
+int rewb200_lane_release(rewb200_session* s, int lane);
+
 /* GenerationConfig sampling on the device (src/rew/infer/generate.nim:12-58 for
  * the fields and their checks, :92-159 sampleTopK / sampleTopP / sampleGreedy,
  * :192-218 applySamplingConfig, :231-265 the loop).  After this call forward,
@@ -203,8 +228,9 @@ int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new
  * 1024) or top-p.  Sequence b draws from Key = initKey(seeds[b]) (seeds NULL:
  * all 0, the reference's default key) and folds the step number in after every
  * token (src/rew/rng.nim:33-80).  Keys and step counters restart at
- * rewb200_session_reset, hence at every rewb200_generate.  Not available on a
- * tensor-parallel model. */
+ * rewb200_session_reset, hence at every rewb200_generate.  On a paged session
+ * call it before admitting lanes (each rewb200_lane_admit restarts its lane
+ * from its own seed).  Not available on a tensor-parallel model. */
 int rewb200_session_set_sampling(rewb200_session* s, float temperature, int top_k, float top_p, float min_p,
                                  float repetition_penalty, int do_sample, const uint64_t* seeds);
 /* Back to plain greedy argmax. */

@@ -76,6 +76,12 @@ SIGNATURES = {
     "rewb200_session_forward": (C.c_int, [P, I32P, C.c_int, I32P, F32P]),
     "rewb200_session_decode": (C.c_int, [P, C.c_int, I32P, F32P]),
     "rewb200_generate": (C.c_int, [P, I32P, C.c_int, C.c_int, C.c_int, I32P, F32P]),
+    "rewb200_session_create_paged": (C.c_int, [P, C.c_int, C.c_int, C.c_int, PP]),
+    "rewb200_session_free_blocks": (C.c_int, [P]),
+    "rewb200_lane_length": (C.c_int, [P, C.c_int]),
+    "rewb200_lane_admit": (C.c_int, [P, C.c_int, I32P, C.c_int, C.c_uint64, I32P]),
+    "rewb200_lanes_step": (C.c_int, [P, C.c_int, I32P]),
+    "rewb200_lane_release": (C.c_int, [P, C.c_int]),
     "rewb200_session_set_sampling": (C.c_int, [P, C.c_float, C.c_int, C.c_float, C.c_float, C.c_float, C.c_int,
                                                C.POINTER(C.c_uint64)]),
     "rewb200_session_clear_sampling": (C.c_int, [P]),

@@ -208,6 +208,11 @@ class CausalLM:
         self._sessions.add(s)
         return s
 
+    def paged_session(self, lanes, max_len, num_blocks):
+        s = PagedSession(self, lanes, max_len, num_blocks)
+        self._sessions.add(s)
+        return s
+
     def free(self):
         if self._h is not None:
             for s in list(self._sessions):
@@ -310,6 +315,39 @@ class Session:
             self.free()
         except Exception:
             pass
+
+
+class PagedSession(Session):
+    """Continuous batching: `lanes` sequences of independent length over a shared pool of KV blocks
+    (PagedKvCache, src/rew/infer/generate.nim:63-88).  set_sampling / logprobs / free as Session."""
+
+    def __init__(self, model, lanes, max_len, num_blocks):
+        self.model, self.batch, self.max_len, self.num_blocks = model, lanes, max_len, num_blocks
+        h = C.c_void_p()
+        check(lib().rewb200_session_create_paged(model._h, lanes, max_len, num_blocks, C.byref(h)))
+        self._h = h
+
+    def free_blocks(self):
+        return int(lib().rewb200_session_free_blocks(self._h))
+
+    def lane_length(self, lane):
+        return int(lib().rewb200_lane_length(self._h, lane))
+
+    def admit(self, lane, ids, seed=0):
+        """Prefills one idle lane with the prompt `ids`; returns its first new token."""
+        a = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
+        nxt = C.c_int32(-1)
+        check(lib().rewb200_lane_admit(self._h, lane, a.ctypes.data_as(_lib.I32P), a.size, C.c_uint64(seed), C.byref(nxt)))
+        return int(nxt.value)
+
+    def step(self, n_steps=1):
+        """n decode steps for every active lane: ids [lanes, n_steps], -1 for idle lanes."""
+        out = np.empty((self.batch, n_steps), np.int32)
+        check(lib().rewb200_lanes_step(self._h, n_steps, out.ctypes.data_as(_lib.I32P)))
+        return out
+
+    def release(self, lane):
+        check(lib().rewb200_lane_release(self._h, lane))
 
 
 def set_option(key, value, slot=0):

@@ -46,7 +46,7 @@ int moe_combine_launch(Ctx* c, const float* back, const int* pair_slot, const fl
                        float* out, int accumulate);
 int sample_launch(Ctx* c, const float* logits, float* work, int64_t B, int64_t V, int* hist, int* hist_len, int hist_cap,
                   uint32_t* keys, int* steps, int* next, float* logprob, int logprob_cap, float temperature, int top_k,
-                  float top_p, float min_p, float rep_penalty, int do_sample);
+                  float top_p, float min_p, float rep_penalty, int do_sample, const int* active);
 int argmax_partial_launch(Ctx* c, const float* logits, int64_t rows, int64_t V, int idx_offset, int nchunks, float* pv, int* pi);
 int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows, int nchunks, int* out);
 
@@ -119,15 +119,19 @@ __global__ void swiglu_rows_f32_kernel(const float* gu, float* out, int64_t rows
 
 // End of a step: publish the sampled ids, make them the next step's input,
 // advance positions and the step counter.
-__global__ void advance_kernel(const int* next, int* ids, int* pos, int* out_ids, int* step, int B, int S,
-                               int max_steps) {
+// `active` (optional): lanes with 0 keep their token and position and report -1.
+__global__ void advance_kernel(const int* next, int* ids, int* pos, int* out_ids, int* step, const int* active, int B,
+                               int S, int max_steps) {
   pdl_launch_dependents();
   pdl_wait();
   const int st = *step;
   for (int b = threadIdx.x; b < B; b += blockDim.x) {
-    ids[b] = next[b];
-    pos[b] += S;
-    if (out_ids && st < max_steps) out_ids[(int64_t)st * B + b] = next[b];
+    const bool on = active == nullptr || active[b] != 0;
+    if (on) {
+      ids[b] = next[b];
+      pos[b] += S;
+    }
+    if (out_ids && st < max_steps) out_ids[(int64_t)st * B + b] = on ? next[b] : -1;
   }
   __syncthreads();
   if (threadIdx.x == 0) *step = st + 1;
@@ -202,6 +206,15 @@ struct rewb200_session {
   int *samp_hist = nullptr, *samp_hist_len = nullptr, *samp_steps = nullptr;  // [B][max_len], [B], [B]
   uint32_t* samp_keys = nullptr;       // [B][2]
   float *samp_work = nullptr, *samp_logprob = nullptr;  // [B][V], [B][max_len]
+  // Paged lanes (continuous batching): a shared pool of KV pages handed out on demand
+  bool paged = false;
+  int num_blocks = 0;                  // pages in the pool; page 0 is the scratch page of idle lanes
+  std::vector<int> free_blocks;        // as PagedKvCache.freeBlocks (generate.nim:75,86-88)
+  std::vector<int> lane_len;           // tokens in the cache per lane
+  std::vector<char> lane_active;
+  std::vector<std::vector<int>> lane_pages;
+  int* d_active = nullptr;             // [B] or nullptr (every lane active)
+  int* d_ids_prefill = nullptr;        // ids of a single-lane prefill
 };
 
 namespace rewb {
@@ -486,6 +499,12 @@ struct FwdOpts {
   int causal = 1;
   bool all_logits = false;  // lm_head on every row instead of the last position
   bool from_device_ids = false;
+  // Lanes [b0, b0 + nb) of the session only (nb < 0: all).  The per-lane arrays (positions, block table,
+  // next ids, logits rows, sampling state) are indexed from b0; ids_src overrides where the nb*S input
+  // ids are read, so that a single-lane prefill does not disturb the other lanes' pending tokens.
+  int b0 = 0, nb = -1;
+  const int* ids_src = nullptr;
+  bool record_out = true;    // append the new ids to the session's [step][B] output buffer
 };
 
 // Enqueues one forward over rows = B*S tokens whose ids are in s->d_ids.
@@ -493,8 +512,13 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   rewb200_model* m = s->m;
   Ctx* c = m->c;
   const rewb200_config& cf = m->cfg;
-  const int64_t rows = (int64_t)s->B * o.S;
+  const int b0 = o.b0, nb = o.nb < 0 ? s->B : o.nb;
+  const int64_t rows = (int64_t)nb * o.S;
   const int64_t d = cf.d_model;
+  int* const pos = s->d_pos + b0;
+  const int* const block_table = s->block_table + (size_t)b0 * s->max_pages;
+  float* const logits = o.all_logits ? s->logits : s->logits + (size_t)b0 * m->vocab_l;
+  int* const next = s->d_next + b0;
   const int dt = cf.dtype;
 
   NormArgs na;
@@ -513,7 +537,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   {
     NormArgs a = na;
     a.embed = m->embed;
-    a.ids = s->d_ids;
+    a.ids = o.ids_src ? o.ids_src : s->d_ids;
     a.gamma = m->layers[0].ln1g;
     a.beta = m->layers[0].ln1b;
     RB_TRY(residual_norm_launch(c, a, rows));
@@ -556,7 +580,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     qa.bias = L.qkv.b;
     qa.cosT = m->cosT;
     qa.sinT = m->sinT;
-    qa.pos0 = s->d_pos;
+    qa.pos0 = pos;
     qa.S = o.S;
     qa.rope_shift = o.rope_shift;
     qa.nh = m->nh_l;
@@ -567,7 +591,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     qa.act_dtype = dt;
     qa.kv.k = s->kc[l];
     qa.kv.v = s->vc[l];
-    qa.kv.block_table = s->block_table;
+    qa.kv.block_table = block_table;
     qa.kv.max_pages = s->max_pages;
     qa.kv.page = PAGE;
     qa.kv.kvh = m->kvh_l;
@@ -575,7 +599,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     qa.kv.dtype = dt;
     qa.kv_capacity = s->max_len;
     qa.status = c->d_status;
-    RB_TRY(qkv_post_launch(c, qa, s->B));
+    RB_TRY(qkv_post_launch(c, qa, nb));
 
     AttnArgs aa;
     memset(&aa, 0, sizeof(aa));
@@ -588,8 +612,8 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     aa.o_ss = aa.q_ss;
     aa.o_sh = aa.q_sh;
     aa.kv = qa.kv;
-    aa.pos0 = s->d_pos;
-    aa.B = s->B;
+    aa.pos0 = pos;
+    aa.B = nb;
     aa.S = o.S;
     aa.nh = m->nh_l;
     aa.causal = o.causal;
@@ -650,25 +674,26 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   }
   if (oneshot) RB_TRY(epoch_bump_launch(c, pi->epoch, 2 * cf.n_layers));  // same on every rank
   // lm_head: last position of every sequence (generate.nim:172-190) or every row.
-  const int64_t lrows = o.all_logits ? rows : s->B;
+  const int64_t lrows = o.all_logits ? rows : nb;
   const char* xl = (const char*)s->xn + (o.all_logits ? 0 : (size_t)(o.S - 1) * d * dtype_size(dt));
   const int64_t ldx = o.all_logits ? d : (int64_t)o.S * d;
   if (dt == REWB200_BF16) {
-    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)xl, ldx, lrows, EPI_BIAS_F32, 1, s->logits, m->vocab_l, m->lm.b,
+    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)xl, ldx, lrows, EPI_BIAS_F32, 1, logits, m->vocab_l, m->lm.b,
                               nullptr, 0));
   } else {
     if (o.all_logits || o.S == 1) {
-      RB_TRY(gemm_f32_launch(c, (const float*)xl, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, m->vocab_l));
+      RB_TRY(gemm_f32_launch(c, (const float*)xl, (const float*)m->lm.w, m->lm.b, logits, lrows, d, m->vocab_l));
     } else {
       // gather the last rows into the head of q (free at this point), then GEMM
-      for (int b = 0; b < s->B; ++b)
+      for (int b = 0; b < nb; ++b)
         RB_CUDA(cudaMemcpyAsync((float*)s->q + (size_t)b * d, (const float*)s->xn + ((size_t)b * o.S + o.S - 1) * d,
                                 d * sizeof(float), cudaMemcpyDeviceToDevice, c->stream));
-      RB_TRY(gemm_f32_launch(c, (const float*)s->q, (const float*)m->lm.w, m->lm.b, s->logits, lrows, d, m->vocab_l));
+      RB_TRY(gemm_f32_launch(c, (const float*)s->q, (const float*)m->lm.w, m->lm.b, logits, lrows, d, m->vocab_l));
     }
   }
   if (!o.all_logits) {
     if (cf.tp_size > 1) {
+      RB_REQUIRE(b0 == 0 && nb == s->B, "lane ranges are not available on a tensor-parallel model");
       // vocab-parallel: per-rank (value, index) partials, all-gathered, then the same first-max rule
       const int nch = 16;
       float* pv = (float*)s->argmax_scratch;
@@ -677,14 +702,17 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       RB_TRY(comm_allgather_bytes(c, m->slot, s->argmax_scratch, s->gather_scratch, (size_t)s->B * nch * 8));
       RB_TRY(argmax_gathered_launch(c, s->gather_scratch, cf.tp_size, s->B, nch, s->d_next));
     } else if (s->samp_on) {
-      RB_TRY(sample_launch(c, s->logits, s->samp_work, s->B, cf.vocab, s->samp_hist, s->samp_hist_len, s->max_len,
-                           s->samp_keys, s->samp_steps, s->d_next, s->samp_logprob, s->max_len, s->samp_temperature,
-                           s->samp_top_k, s->samp_top_p, s->samp_min_p, s->samp_rep, s->samp_do_sample));
+      const int* act = s->d_active ? s->d_active + b0 : nullptr;
+      RB_TRY(sample_launch(c, logits, s->samp_work + (size_t)b0 * cf.vocab, nb, cf.vocab, s->samp_hist + (size_t)b0 * s->max_len,
+                           s->samp_hist_len + b0, s->max_len, s->samp_keys + 2 * b0, s->samp_steps + b0, next,
+                           s->samp_logprob + (size_t)b0 * s->max_len, s->max_len, s->samp_temperature, s->samp_top_k,
+                           s->samp_top_p, s->samp_min_p, s->samp_rep, s->samp_do_sample, act));
     } else {
-      RB_TRY(argmax_launch(c, s->logits, s->B, cf.vocab, s->d_next, s->argmax_scratch, (size_t)s->B * 64 * 8));
+      RB_TRY(argmax_launch(c, logits, nb, cf.vocab, next, s->argmax_scratch, (size_t)s->B * 64 * 8));
     }
-    RB_CUDA(launch_k(advance_kernel, dim3(1), dim3(256), 0, c->stream, c->use_pdl,
-                     (const int*)s->d_next, s->d_ids, s->d_pos, s->d_out, s->d_step, s->B, o.S, s->out_capacity));
+    RB_CUDA(launch_k(advance_kernel, dim3(1), dim3(256), 0, c->stream, c->use_pdl, (const int*)next, s->d_ids + b0, pos,
+                     o.record_out ? s->d_out : (int*)nullptr, s->d_step, (const int*)(s->d_active ? s->d_active + b0 : nullptr),
+                     nb, o.S, s->out_capacity));
     ++g_launch_total;
   }
   return REWB200_OK;
@@ -985,7 +1013,7 @@ int rewb200_model_finalize(rewb200_model* m) {
   return REWB200_OK;
 }
 
-int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_session** out) {
+static int session_create_impl(rewb200_model* m, int batch, int max_len, int num_blocks, rewb200_session** out) {
   RB_REQUIRE(m && out, "rewb200_session_create: NULL argument");
   RB_REQUIRE(m->finalized, "rewb200_session_create: call rewb200_model_finalize first");
   RB_REQUIRE(batch > 0 && max_len > 0, "initKvCache: batch and maxLen must be positive");
@@ -998,7 +1026,9 @@ int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_ses
   s->B = batch;
   s->max_len = max_len;
   s->max_pages = (max_len + PAGE - 1) / PAGE;
-  const int64_t n_pages = (int64_t)batch * s->max_pages;
+  s->paged = num_blocks > 0;
+  s->num_blocks = num_blocks;
+  const int64_t n_pages = s->paged ? (int64_t)num_blocks : (int64_t)batch * s->max_pages;
   const size_t es = dtype_size(m->cfg.dtype);
   const int64_t cache_rows = n_pages * m->kvh_l * PAGE;
   const size_t cache_bytes = (size_t)cache_rows * m->cfg.head_dim * es;
@@ -1016,14 +1046,27 @@ int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_ses
       RB_TRY(make_tmap_2d_bf16(&s->tmV[l], s->vc[l], m->cfg.head_dim, cache_rows, (uint64_t)m->cfg.head_dim * 2, 64, 64));
     }
   }
-  std::vector<int> bt((size_t)n_pages);
-  for (int64_t i = 0; i < n_pages; ++i) bt[i] = (int)i;  // sequence b owns pages [b*max_pages, (b+1)*max_pages)
-  RB_CUDA(cudaMalloc((void**)&s->block_table, n_pages * sizeof(int)));
-  RB_CUDA(cudaMemcpyAsync(s->block_table, bt.data(), n_pages * sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  const int64_t n_bt = (int64_t)batch * s->max_pages;
+  std::vector<int> bt((size_t)n_bt, 0);
+  if (!s->paged)
+    for (int64_t i = 0; i < n_bt; ++i) bt[i] = (int)i;  // sequence b owns pages [b*max_pages, (b+1)*max_pages)
+  RB_CUDA(cudaMalloc((void**)&s->block_table, n_bt * sizeof(int)));
+  RB_CUDA(cudaMemcpyAsync(s->block_table, bt.data(), n_bt * sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  if (s->paged) {
+    // every lane idle on the scratch page 0; blocks 1.. are free (PagedKvCache.freeBlocks, generate.nim:86-88)
+    for (int i = num_blocks - 1; i >= 1; --i) s->free_blocks.push_back(i);
+    s->lane_len.assign(batch, 0);
+    s->lane_active.assign(batch, 0);
+    s->lane_pages.assign(batch, {});
+    RB_CUDA(cudaMalloc((void**)&s->d_active, batch * sizeof(int)));
+    RB_CUDA(cudaMemsetAsync(s->d_active, 0, batch * sizeof(int), c->stream));
+    RB_CUDA(cudaMalloc((void**)&s->d_ids_prefill, (size_t)max_len * sizeof(int)));
+  }
   RB_CUDA(cudaMalloc((void**)&s->d_pos, batch * sizeof(int)));
   RB_CUDA(cudaMalloc((void**)&s->d_next, batch * sizeof(int)));
   RB_CUDA(cudaMalloc((void**)&s->d_step, sizeof(int)));
   RB_CUDA(cudaMalloc((void**)&s->d_ids, (size_t)batch * max_len * sizeof(int)));
+  RB_CUDA(cudaMemsetAsync(s->d_ids, 0, (size_t)batch * max_len * sizeof(int), c->stream));  // idle lanes decode token 0
   s->out_capacity = max_len;
   RB_CUDA(cudaMalloc((void**)&s->d_out, (size_t)batch * s->out_capacity * sizeof(int)));
   RB_CUDA(cudaMallocHost((void**)&s->h_ids, (size_t)batch * max_len * sizeof(int)));
@@ -1045,6 +1088,17 @@ int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_ses
   return REWB200_OK;
 }
 
+int rewb200_session_create(rewb200_model* m, int batch, int max_len, rewb200_session** out) {
+  return session_create_impl(m, batch, max_len, 0, out);
+}
+
+int rewb200_session_create_paged(rewb200_model* m, int lanes, int max_len, int num_blocks, rewb200_session** out) {
+  RB_REQUIRE(m && out, "rewb200_session_create_paged: NULL argument");
+  RB_REQUIRE(num_blocks >= 2, "initPagedKvCache: numBlocks must be at least 2 (block 0 is the idle lanes' scratch block)");
+  RB_REQUIRE(m->cfg.tp_size <= 1 && m->cfg.ep_size <= 1, "paged lanes are not available on a sharded model");
+  return session_create_impl(m, lanes, max_len, num_blocks, out);
+}
+
 void rewb200_session_free(rewb200_session* s) {
   if (!s) return;
   Ctx* c = s->m->c;
@@ -1053,7 +1107,7 @@ void rewb200_session_free(rewb200_session* s) {
   if (s->graph) cudaGraphExecDestroy(s->graph);
   for (void* p : s->kc) cudaFree(p);
   for (void* p : s->vc) cudaFree(p);
-  void* ptrs[] = {s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
+  void* ptrs[] = {s->d_active, s->d_ids_prefill, s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
                   s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch, s->gather_scratch,
                   s->samp_hist, s->samp_hist_len, s->samp_steps, s->samp_keys, s->samp_work, s->samp_logprob, s->moe_logits, s->moe_topw, s->moe_topi, s->moe_ints,
                   s->moe_send, s->moe_recv, s->moe_xs, s->moe_hs, s->moe_ys, s->moe_ret, s->moe_back, s->moe_tmp};
@@ -1069,6 +1123,8 @@ int rewb200_session_reset(rewb200_session* s) {
   RB_REQUIRE(s, "rewb200_session_reset: NULL session");
   Ctx* c = s->m->c;
   RB_CUDA(cudaSetDevice(c->device));
+  if (s->paged)
+    for (int b = 0; b < s->B; ++b) RB_TRY(rewb200_lane_release(s, b));
   RB_CUDA(cudaMemsetAsync(s->d_pos, 0, s->B * sizeof(int), c->stream));
   RB_CUDA(cudaMemsetAsync(s->d_step, 0, sizeof(int), c->stream));
   s->host_pos = 0;
@@ -1078,6 +1134,7 @@ int rewb200_session_reset(rewb200_session* s) {
 
 int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32_t* next_ids, float* logits_out) {
   RB_REQUIRE(s && ids, "rewb200_session_forward: NULL argument");
+  RB_REQUIRE(!s->paged, "rewb200_session_forward: a paged session is driven by rewb200_lane_admit / rewb200_lanes_step");
   RB_REQUIRE(S > 0, "generate: tokenIds must not be empty");
   RB_REQUIRE(s->host_pos + S <= s->max_len, "KvCache.append: total length " + std::to_string(s->host_pos + S) +
                                                 " exceeds maxLen " + std::to_string(s->max_len));
@@ -1112,13 +1169,8 @@ int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32
   return ctx_check_status(c);
 }
 
-int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, float* last_logits) {
-  RB_REQUIRE(s, "rewb200_session_decode: NULL session");
-  RB_REQUIRE(n_steps >= 0, "n_steps must be non-negative");
-  RB_REQUIRE(s->host_pos > 0, "rewb200_session_decode: feed a prompt with rewb200_session_forward first");
-  RB_REQUIRE(s->host_pos + n_steps <= s->max_len, "KvCache.append: total length " +
-                                                      std::to_string(s->host_pos + n_steps) + " exceeds maxLen " +
-                                                      std::to_string(s->max_len));
+// n_steps decode steps for every lane of the session (captured once into a CUDA graph, then replayed).
+static int decode_core(rewb200_session* s, int n_steps, int32_t* out_ids, float* last_logits) {
   RB_REQUIRE(n_steps <= s->out_capacity, "too many decode steps for the session's id buffer");
   rewb200_model* m = s->m;
   Ctx* c = m->c;
@@ -1170,13 +1222,26 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
   if (last_logits) RB_TRY(fetch_logits(s, s->B, last_logits));
   RB_CUDA(cudaStreamSynchronize(c->stream));
   RB_CUDA(cudaEventElapsedTime(&s->decode_ms, s->ev0, s->ev1));
-  s->host_pos += n_steps;
   return ctx_check_status(c);
+}
+
+int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, float* last_logits) {
+  RB_REQUIRE(s, "rewb200_session_decode: NULL session");
+  RB_REQUIRE(!s->paged, "rewb200_session_decode: a paged session is driven by rewb200_lane_admit / rewb200_lanes_step");
+  RB_REQUIRE(n_steps >= 0, "n_steps must be non-negative");
+  RB_REQUIRE(s->host_pos > 0, "rewb200_session_decode: feed a prompt with rewb200_session_forward first");
+  RB_REQUIRE(s->host_pos + n_steps <= s->max_len, "KvCache.append: total length " +
+                                                      std::to_string(s->host_pos + n_steps) + " exceeds maxLen " +
+                                                      std::to_string(s->max_len));
+  RB_TRY(decode_core(s, n_steps, out_ids, last_logits));
+  s->host_pos += n_steps;
+  return REWB200_OK;
 }
 
 int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
                      float* last_logits) {
   RB_REQUIRE(s && prompt && out_ids, "rewb200_generate: NULL argument");
+  RB_REQUIRE(!s->paged, "rewb200_generate: a paged session is driven by rewb200_lane_admit / rewb200_lanes_step");
   RB_REQUIRE(n_new >= 1, "generate: maxNewTokens must be positive");
   RB_TRY(rewb200_session_reset(s));
   std::vector<int32_t> first(s->B);
@@ -1219,6 +1284,134 @@ int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new
       else if (out_ids[(size_t)b * n_new + t] == eos) hit = true;
     }
   }
+  return REWB200_OK;
+}
+
+
+// ---- paged lanes: continuous batching over a shared pool of KV blocks -----------------------------
+
+namespace {
+
+// Makes sure `lane` owns blocks for `new_len` tokens and uploads its block-table row when it grew.
+int lane_reserve(rewb200_session* s, int lane, int new_len) {
+  Ctx* c = s->m->c;
+  const int need = (new_len + PAGE - 1) / PAGE;
+  std::vector<int>& pages = s->lane_pages[lane];
+  if ((int)pages.size() >= need) return REWB200_OK;
+  RB_REQUIRE((int)s->free_blocks.size() >= need - (int)pages.size(),
+             "PagedKvCache: out of free blocks (lane " + std::to_string(lane) + " needs " +
+                 std::to_string(need - (int)pages.size()) + ", " + std::to_string(s->free_blocks.size()) + " free)");
+  while ((int)pages.size() < need) {
+    pages.push_back(s->free_blocks.back());
+    s->free_blocks.pop_back();
+  }
+  std::vector<int> row((size_t)s->max_pages, 0);
+  for (size_t i = 0; i < pages.size(); ++i) row[i] = pages[i];
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_CUDA(cudaMemcpy(s->block_table + (size_t)lane * s->max_pages, row.data(), row.size() * sizeof(int), cudaMemcpyHostToDevice));
+  return REWB200_OK;
+}
+
+int lane_check(const rewb200_session* s, int lane, const char* who) {
+  RB_REQUIRE(s, std::string(who) + ": NULL session");
+  RB_REQUIRE(s->paged, std::string(who) + ": the session was not created with rewb200_session_create_paged");
+  RB_REQUIRE(lane >= 0 && lane < s->B, std::string(who) + ": lane " + std::to_string(lane) + " out of range");
+  return REWB200_OK;
+}
+
+}  // namespace
+
+int rewb200_session_free_blocks(const rewb200_session* s) { return (s && s->paged) ? (int)s->free_blocks.size() : -1; }
+
+int rewb200_lane_length(const rewb200_session* s, int lane) {
+  if (!s || !s->paged || lane < 0 || lane >= s->B || !s->lane_active[lane]) return -1;
+  return s->lane_len[lane];
+}
+
+int rewb200_lane_admit(rewb200_session* s, int lane, const int32_t* ids, int S, uint64_t seed, int32_t* next_id) {
+  RB_TRY(lane_check(s, lane, "rewb200_lane_admit"));
+  RB_REQUIRE(ids, "rewb200_lane_admit: NULL ids");
+  RB_REQUIRE(!s->lane_active[lane], "rewb200_lane_admit: lane " + std::to_string(lane) + " is busy; release it first");
+  RB_REQUIRE(S > 0, "generate: tokenIds must not be empty");
+  RB_REQUIRE(S < s->max_len, "KvCache.append: total length " + std::to_string(S + 1) + " exceeds maxLen " + std::to_string(s->max_len));
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  for (int i = 0; i < S; ++i)
+    RB_REQUIRE(ids[i] >= 0 && ids[i] < m->cfg.vocab, "generate: token id out of range at index " + std::to_string(i));
+  RB_TRY(lane_reserve(s, lane, S));
+  RB_TRY(ensure_acts(s, std::max<int64_t>(std::max<int64_t>(S, s->B), s->rows_cap), s->B));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  const int one = 1, zero = 0;
+  RB_CUDA(cudaMemcpy(s->d_ids_prefill, ids, (size_t)S * sizeof(int), cudaMemcpyHostToDevice));
+  RB_CUDA(cudaMemcpy(s->d_pos + lane, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  RB_CUDA(cudaMemcpy(s->d_active + lane, &one, sizeof(int), cudaMemcpyHostToDevice));
+  if (s->samp_on) {
+    // this lane's generate() starts over: Key = initKey(seed), step 0, seen = the prompt
+    s->samp_seeds[lane] = seed;
+    const uint32_t k[2] = {(uint32_t)(seed & 0xFFFFFFFFull), (uint32_t)(seed >> 32)};
+    RB_CUDA(cudaMemcpy(s->samp_keys + 2 * lane, k, sizeof(k), cudaMemcpyHostToDevice));
+    RB_CUDA(cudaMemcpy(s->samp_steps + lane, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    RB_CUDA(cudaMemcpy(s->samp_hist + (size_t)lane * s->max_len, ids, (size_t)S * sizeof(int), cudaMemcpyHostToDevice));
+    RB_CUDA(cudaMemcpy(s->samp_hist_len + lane, &S, sizeof(int), cudaMemcpyHostToDevice));
+  }
+  RB_CUDA(cudaEventRecord(s->ev0, c->stream));
+  FwdOpts o;
+  o.S = S;
+  o.b0 = lane;
+  o.nb = 1;
+  o.ids_src = s->d_ids_prefill;
+  o.record_out = false;
+  RB_TRY(enqueue_forward(s, o));
+  RB_CUDA(cudaEventRecord(s->ev1, c->stream));
+  int32_t first = -1;
+  RB_CUDA(cudaMemcpyAsync(&first, s->d_next + lane, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_CUDA(cudaEventElapsedTime(&s->prefill_ms, s->ev0, s->ev1));
+  s->lane_active[lane] = 1;
+  s->lane_len[lane] = S;
+  if (next_id) *next_id = first;
+  return ctx_check_status(c);
+}
+
+int rewb200_lanes_step(rewb200_session* s, int n_steps, int32_t* out_ids) {
+  RB_TRY(lane_check(s, 0, "rewb200_lanes_step"));
+  RB_REQUIRE(n_steps >= 0, "n_steps must be non-negative");
+  int need_blocks = 0;
+  for (int b = 0; b < s->B; ++b) {
+    if (!s->lane_active[b]) continue;
+    RB_REQUIRE(s->lane_len[b] + n_steps <= s->max_len, "KvCache.append: total length " +
+                                                           std::to_string(s->lane_len[b] + n_steps) + " of lane " +
+                                                           std::to_string(b) + " exceeds maxLen " + std::to_string(s->max_len));
+    need_blocks += std::max(0, (s->lane_len[b] + n_steps + PAGE - 1) / PAGE - (int)s->lane_pages[b].size());
+  }
+  // all or nothing: no lane grows unless every lane can
+  RB_REQUIRE(need_blocks <= (int)s->free_blocks.size(), "PagedKvCache: out of free blocks (" + std::to_string(need_blocks) +
+                                                            " needed for " + std::to_string(n_steps) + " steps, " +
+                                                            std::to_string(s->free_blocks.size()) + " free)");
+  for (int b = 0; b < s->B; ++b)
+    if (s->lane_active[b]) RB_TRY(lane_reserve(s, b, s->lane_len[b] + n_steps));
+  RB_TRY(decode_core(s, n_steps, out_ids, nullptr));
+  for (int b = 0; b < s->B; ++b)
+    if (s->lane_active[b]) s->lane_len[b] += n_steps;
+  return REWB200_OK;
+}
+
+int rewb200_lane_release(rewb200_session* s, int lane) {
+  RB_TRY(lane_check(s, lane, "rewb200_lane_release"));
+  if (!s->lane_active[lane] && s->lane_pages[lane].empty()) return REWB200_OK;  // idempotent
+  Ctx* c = s->m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  const int zero = 0;
+  RB_CUDA(cudaMemcpy(s->d_active + lane, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  RB_CUDA(cudaMemcpy(s->d_pos + lane, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  std::vector<int> row((size_t)s->max_pages, 0);  // back on the scratch block
+  RB_CUDA(cudaMemcpy(s->block_table + (size_t)lane * s->max_pages, row.data(), row.size() * sizeof(int), cudaMemcpyHostToDevice));
+  for (int pg : s->lane_pages[lane]) s->free_blocks.push_back(pg);
+  s->lane_pages[lane].clear();
+  s->lane_active[lane] = 0;
+  s->lane_len[lane] = 0;
   return REWB200_OK;
 }
 

@@ -55,6 +55,7 @@ struct SampleArgs {
   float temperature, top_p, min_p, rep_penalty;
   int top_k, do_sample;
   int exact_only;        // skip the bucket path (testing aid)
+  const int* active;     // [B] or nullptr: sequences with 0 are skipped
   int* status;
 };
 
@@ -620,6 +621,7 @@ __global__ void __cluster_dims__(CS, 1, 1) __launch_bounds__(ST) sample_kernel(S
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x / CS;
+  if (a.active && a.active[b] == 0) return;  // an idle lane: the whole cluster leaves together
   const int64_t V = a.V;
   const int nwords = (int)((V + 31) / 32);
   Dyn dy;
@@ -866,13 +868,13 @@ __global__ void __cluster_dims__(CS, 1, 1) __launch_bounds__(ST) sample_kernel(S
 
 int sample_launch(Ctx* c, const float* logits, float* work, int64_t B, int64_t V, int* hist, int* hist_len, int hist_cap,
                   uint32_t* keys, int* steps, int* next, float* logprob, int logprob_cap, float temperature, int top_k,
-                  float top_p, float min_p, float rep_penalty, int do_sample) {
+                  float top_p, float min_p, float rep_penalty, int do_sample, const int* active) {
   if (B == 0) return REWB200_OK;
   SampleArgs a;
   a.logits = logits; a.work = work; a.V = V; a.hist = hist; a.hist_len = hist_len; a.hist_cap = hist_cap; a.keys = keys;
   a.steps = steps; a.next = next; a.logprob = logprob; a.logprob_cap = logprob_cap;
   a.temperature = temperature; a.top_p = top_p; a.min_p = min_p; a.rep_penalty = rep_penalty;
-  a.top_k = top_k; a.do_sample = do_sample; a.exact_only = c->sampling_exact ? 1 : 0; a.status = c->d_status;
+  a.top_k = top_k; a.do_sample = do_sample; a.exact_only = c->sampling_exact ? 1 : 0; a.active = active; a.status = c->d_status;
   const size_t bitmap_bytes = ((size_t)((V + 31) / 32) * 4 + 15) & ~(size_t)15;
   const size_t smem = bitmap_bytes + (size_t)NW * 256 * 8 + (size_t)CAP * 8;
   RB_REQUIRE(smem <= 200 * 1024, "sampling supports vocabularies up to about 800 000 tokens");
