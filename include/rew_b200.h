@@ -48,6 +48,7 @@ enum {
 typedef struct rewb200_buffer rewb200_buffer;
 typedef struct rewb200_model rewb200_model;
 typedef struct rewb200_session rewb200_session;
+typedef struct rewb200_nf4 rewb200_nf4;
 
 /* ---- runtime ------------------------------------------------------------
  * Replaces client creation in installEagerBackend (src/rew/eager.nim:1769-1772)
@@ -132,6 +133,28 @@ int rewb200_embed_gather(const rewb200_buffer* ids, const rewb200_buffer* table,
 int rewb200_moe_route(const rewb200_buffer* x, const rewb200_buffer* router_w, const rewb200_buffer* router_b,
                       int top_k, rewb200_buffer** weights, rewb200_buffer** indices);
 
+/* ---- NF4 weight-only Linear (QLoRA base projection) -------------------------
+ * nf4Quantize / nf4Dequantize (src/rew/quantize/codecs.nim:13-70) and
+ * QloraLinear (src/rew/nn/lora.nim:173-191,331-431).  The reference dequantises
+ * the frozen weight once on the host and multiplies in fp32; here the 4-bit
+ * codes stay in device memory (0.5625 bytes per weight with the scales) and are
+ * dequantised inside the matrix-vector kernel. */
+/* initQloraLinearFromF32's quantisation step: w [in,out] f32 or bf16 on the
+ * device, blocks of 64 along the flat index; in and out must be multiples of 64. */
+int rewb200_nf4_pack(const rewb200_buffer* w, rewb200_nf4** out);
+void rewb200_nf4_free(rewb200_nf4* h);
+int rewb200_nf4_info(const rewb200_nf4* h, int64_t* in_features, int64_t* out_features);
+/* The reference's representation of the same weight: packed [in*out/2] bytes
+ * (even flat index in the low nibble) and scales [in*out/64], both on the host. */
+int rewb200_nf4_unpack(const rewb200_nf4* h, uint8_t* packed, float* scales);
+/* nf4Dequantize into a new bf16 [in,out] device buffer. */
+int rewb200_nf4_dequantize(const rewb200_nf4* h, rewb200_buffer** w_out);
+/* QloraLinear.forward (lora.nim:410-431): x [...,in] bf16 -> [...,out] bf16 =
+ * x @ dequant(w) + bias + scaling * (x @ A^T) @ B^T.  bias f32 [out] or NULL;
+ * A f32 [rank,in] and B f32 [out,rank], or both NULL for the base projection. */
+int rewb200_qlora_linear(const rewb200_buffer* x, const rewb200_nf4* h, const rewb200_buffer* bias,
+                         const rewb200_buffer* A, const rewb200_buffer* B, float scaling, rewb200_buffer** y);
+
 /* Linear for callers that cannot allocate device memory (no counterpart in the
  * reference, which always allocates through its PJRT client).  Same math as
  * rewb200_linear for bf16 with M <= 32: y[M,N] = x[M,K] @ w[K,N] + bias, but on
@@ -160,6 +183,9 @@ typedef struct rewb200_config {
   int32_t dtype;        /* REWB200_F32 or REWB200_BF16: weight/activation storage */
   int32_t tp_rank, tp_size; /* tensor parallel shard of heads / FFN columns */
   int32_t ep_rank, ep_size; /* expert parallel shard of routed experts */
+  int32_t weight_quant; /* 0: weights in `dtype`; 1: the decoder blocks' Linear weights as NF4 codes in
+                         * blocks of 64 (nf4Quantize, src/rew/quantize/codecs.nim:31-57), quantised at
+                         * rewb200_model_finalize; needs dtype bf16 and a dense (non-MoE) model */
 } rewb200_config;
 
 int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** out);

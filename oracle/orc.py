@@ -333,3 +333,47 @@ def generate_sampled(mc, tensors, prompt, n_new, temperature=1.0, top_k=50, top_
                                int(top_k), C.c_float(top_p), C.c_float(min_p), C.c_float(repetition_penalty),
                                int(bool(do_sample)), sd.ctypes.data_as(C.POINTER(C.c_uint64)), _ip(ids), _p(lps))
     return ids, lps
+
+
+# ---- NF4 codec and QLoRA Linear (src/rew/quantize/codecs.nim:13-74, src/rew/nn/lora.nim:331-431) ----
+U8P = C.POINTER(C.c_uint8)
+
+
+def nf4_quantize(weights, block_size=64):
+    """Flat float32 weights -> (packed uint8 [(n+1)//2], scales float32 [ceil(n/block)])."""
+    w = _f(weights).reshape(-1)
+    n = w.size
+    packed = np.zeros((n + 1) // 2, np.uint8)
+    scales = np.zeros((n + block_size - 1) // block_size, np.float32)
+    lib().orc_nf4_quantize(_p(w), C.c_int64(n), int(block_size), packed.ctypes.data_as(U8P), _p(scales))
+    return packed, scales
+
+
+def nf4_dequantize(packed, scales, n, block_size=64):
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = _f(scales)
+    out = np.empty(n, np.float32)
+    lib().orc_nf4_dequantize(packed.ctypes.data_as(U8P), _p(scales), C.c_int64(n), int(block_size), _p(out))
+    return out
+
+
+def nf4_roundtrip(w, block_size=64):
+    """dequantize(quantize(w)) with w's shape: the frozen base weight a QloraLinear multiplies by."""
+    w = _f(w)
+    p, s = nf4_quantize(w, block_size)
+    return nf4_dequantize(p, s, w.size, block_size).reshape(w.shape)
+
+
+def qlora_forward(x, packed, scales, n_in, n_out, group_size=64, bias=None, A=None, B=None, scaling=1.0):
+    x = _f(x).reshape(-1, n_in)
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = _f(scales)
+    rank = 1 if A is None else np.asarray(A).shape[0]
+    A = np.zeros((rank, n_in), np.float32) if A is None else _f(A)
+    B = np.zeros((n_out, rank), np.float32) if B is None else _f(B)
+    b = None if bias is None else _f(bias)
+    y = np.empty((x.shape[0], n_out), np.float32)
+    lib().orc_qlora_forward(_p(x), C.c_int64(x.shape[0]), packed.ctypes.data_as(U8P), _p(scales), C.c_int64(n_in),
+                            C.c_int64(n_out), int(group_size), _p(b) if b is not None else None, _p(A), _p(B), int(rank),
+                            C.c_float(scaling), _p(y))
+    return y

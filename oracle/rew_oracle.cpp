@@ -938,3 +938,79 @@ ORC_API void orc_generate_sampled(const Cfg* c, const float* const* tensors, con
     curS = 1;
   }
 }
+
+// ---------------------------------------------------------------------------------------------
+// NF4 weight codec and the QLoRA Linear (src/rew/quantize/codecs.nim:13-74, src/rew/nn/lora.nim:217-256,
+// 331-431).  Weights are the flat row-major [in, out] array; a block is `blockSize` consecutive flat
+// elements; two codes per byte, the even element in the low nibble.
+namespace {
+const float kNf4Table[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                             -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                             0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                             0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+// codecs.nim:23-29: nearest table entry, the first one on a tie
+int find_nf4_index(float value) {
+  float minDist = 1e10f;
+  int result = 0;
+  for (int i = 0; i < 16; ++i) {
+    const float dist = std::fabs(value - kNf4Table[i]);
+    if (dist < minDist) {
+      minDist = dist;
+      result = i;
+    }
+  }
+  return result;
+}
+}  // namespace
+
+// codecs.nim:31-57.  packed: (n+1)/2 bytes, scales: ceil(n/blockSize) floats.
+ORC_API void orc_nf4_quantize(const float* weights, int64_t n, int blockSize, uint8_t* packed, float* scales) {
+  const int64_t numBlocks = (n + blockSize - 1) / blockSize;
+  std::memset(packed, 0, (size_t)((n + 1) / 2));
+  for (int64_t blk = 0; blk < numBlocks; ++blk) {
+    const int64_t start = blk * blockSize, endPos = std::min<int64_t>(start + blockSize, n);
+    float absMax = 1e-10f;
+    for (int64_t i = start; i < endPos; ++i) absMax = std::max(absMax, std::fabs(weights[i]));
+    scales[blk] = absMax;
+    for (int64_t i = start; i < endPos; ++i) {
+      float normalized = weights[i] / absMax;
+      normalized = std::min(1.0f, std::max(-1.0f, normalized));
+      const int code = find_nf4_index(normalized) & 0x0F;
+      if ((i % 2) == 0) packed[i / 2] = (uint8_t)code;
+      else packed[i / 2] = (uint8_t)(packed[i / 2] | (code << 4));
+    }
+  }
+}
+
+// codecs.nim:59-70 (lora.nim:217-256 computes the same values group by group)
+ORC_API void orc_nf4_dequantize(const uint8_t* packed, const float* scales, int64_t n, int blockSize, float* out) {
+  for (int64_t i = 0; i < n; ++i) {
+    const int code = (i % 2) == 0 ? (packed[i / 2] & 0x0F) : ((packed[i / 2] >> 4) & 0x0F);
+    out[i] = kNf4Table[code] * scales[i / blockSize];
+  }
+}
+
+// QloraLinear.forward (lora.nim:410-431): x [M,in] @ dequantizedWeight [in,out] + bias + scaling * (x @ A^T) @ B^T,
+// A [rank,in], B [out,rank]; bias may be NULL (hasBias = false).
+ORC_API void orc_qlora_forward(const float* x, int64_t M, const uint8_t* packed, const float* scales, int64_t in, int64_t out,
+                               int groupSize, const float* bias, const float* A, const float* B, int rank, float scaling,
+                               float* y) {
+  std::vector<float> W((size_t)in * out);
+  orc_nf4_dequantize(packed, scales, in * out, groupSize, W.data());
+  std::vector<float> base((size_t)M * out);
+  matmul(x, W.data(), base.data(), M, in, out);
+  if (bias)
+    for (int64_t m = 0; m < M; ++m)
+      for (int64_t o = 0; o < out; ++o) base[m * out + o] = base[m * out + o] + bias[o];
+  std::vector<float> aT((size_t)in * rank), bT((size_t)rank * out), xA((size_t)M * rank), delta((size_t)M * out);
+  for (int64_t r = 0; r < rank; ++r)
+    for (int64_t i = 0; i < in; ++i) aT[i * rank + r] = A[r * in + i];
+  for (int64_t o = 0; o < out; ++o)
+    for (int64_t r = 0; r < rank; ++r) bT[r * out + o] = B[o * rank + r];
+  matmul(x, aT.data(), xA.data(), M, in, rank);
+  matmul(xA.data(), bT.data(), delta.data(), M, rank, out);
+  for (int64_t i = 0; i < M * out; ++i) {
+    const float dlt = scaling != 1.0f ? delta[i] * scaling : delta[i];
+    y[i] = base[i] + dlt;
+  }
+}

@@ -26,7 +26,7 @@ class Config(C.Structure):
         ("theta", C.c_double), ("eps", C.c_float), ("norm_kind", C.c_int32), ("mask_kind", C.c_int32),
         ("n_routed", C.c_int32), ("n_shared", C.c_int32), ("top_k", C.c_int32), ("moe_ffn", C.c_int32),
         ("first_dense", C.c_int32), ("dtype", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32),
-        ("ep_rank", C.c_int32), ("ep_size", C.c_int32),
+        ("ep_rank", C.c_int32), ("ep_size", C.c_int32), ("weight_quant", C.c_int32),
     ]
 
 
@@ -76,6 +76,12 @@ SIGNATURES = {
     "rewb200_session_forward": (C.c_int, [P, I32P, C.c_int, I32P, F32P]),
     "rewb200_session_decode": (C.c_int, [P, C.c_int, I32P, F32P]),
     "rewb200_generate": (C.c_int, [P, I32P, C.c_int, C.c_int, C.c_int, I32P, F32P]),
+    "rewb200_nf4_pack": (C.c_int, [P, PP]),
+    "rewb200_nf4_free": (None, [P]),
+    "rewb200_nf4_info": (C.c_int, [P, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "rewb200_nf4_unpack": (C.c_int, [P, C.POINTER(C.c_uint8), F32P]),
+    "rewb200_nf4_dequantize": (C.c_int, [P, PP]),
+    "rewb200_qlora_linear": (C.c_int, [P, P, P, P, P, C.c_float, PP]),
     "rewb200_session_create_paged": (C.c_int, [P, C.c_int, C.c_int, C.c_int, PP]),
     "rewb200_session_free_blocks": (C.c_int, [P]),
     "rewb200_lane_length": (C.c_int, [P, C.c_int]),

@@ -94,6 +94,48 @@ class Linear:
         return Tensor(o)
 
 
+class QloraLinear:
+    """QloraLinear (src/rew/nn/lora.nim:173-191,331-431) with the frozen weight kept as NF4 codes on the
+    device.  weight: Tensor [in,out] f32 or bf16 (quantised here, blocks of 64); bias f32 [out] or None;
+    A f32 [rank,in], B f32 [out,rank] or None; scaling = alpha / rank."""
+
+    def __init__(self, weight, bias=None, A=None, B=None, scaling=1.0):
+        h = C.c_void_p()
+        check(lib().rewb200_nf4_pack(_h(weight), C.byref(h)))
+        self._q, self.bias, self.A, self.B, self.scaling = h, bias, A, B, float(scaling)
+        k, n = C.c_int64(), C.c_int64()
+        check(lib().rewb200_nf4_info(self._q, C.byref(k), C.byref(n)))
+        self.inFeatures, self.outFeatures = k.value, n.value
+
+    def forward(self, x):
+        o = _out()
+        check(lib().rewb200_qlora_linear(_h(x), self._q, _h(self.bias), _h(self.A), _h(self.B), self.scaling, C.byref(o)))
+        return Tensor(o)
+
+    def unpack(self):
+        """(packed uint8 [in*out/2], scales f32 [in*out/64]) in the reference's nf4Quantize format."""
+        n = self.inFeatures * self.outFeatures
+        packed, scales = np.empty(n // 2, np.uint8), np.empty(n // 64, np.float32)
+        check(lib().rewb200_nf4_unpack(self._q, packed.ctypes.data_as(C.POINTER(C.c_uint8)), scales.ctypes.data_as(_lib.F32P)))
+        return packed, scales
+
+    def dequantized_weight(self):
+        o = _out()
+        check(lib().rewb200_nf4_dequantize(self._q, C.byref(o)))
+        return Tensor(o)
+
+    def release(self):
+        if self._q is not None:
+            lib().rewb200_nf4_free(self._q)
+            self._q = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
 def rmsNorm(x, gamma, eps=1e-5):
     o = _out()
     check(lib().rewb200_rmsnorm(_h(x), _h(gamma), eps, C.byref(o)))

@@ -67,6 +67,27 @@ int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint64_t row_stride_bytes, uint64_t group_stride_bytes, uint32_t box_inner,
                       uint32_t box_outer);
 
+// NF4 weight-only Linear (nf4.cu).  Column map: logical column n of the quantised matrix lives at
+// device column (w / gran) * gstride + w % gran + (n / seg_len) * seg_off with w = n % seg_len
+// (identity: seg_len = gran = gstride = N, seg_off = 0; the bf16 engine's gate|up interleave:
+// seg_len = F, gran = 8, gstride = 16, seg_off = 8).
+struct ColMap {
+  int64_t seg_len, gran, gstride, seg_off;
+};
+struct Nf4W {
+  uint4* q = nullptr;   // [N/64][K/64][4][32] packed codes in mma B-fragment order
+  float* sc = nullptr;  // [N/64][K] scales
+  int64_t K = 0, N = 0;
+};
+int nf4_alloc(Ctx* c, int64_t K, int64_t N, Nf4W* w);
+void nf4_free(Nf4W* w);
+int nf4_quantize_launch(Ctx* c, const void* src, int src_dtype, int64_t ld, ColMap cm, const Nf4W& w);
+int nf4_dequant_launch(Ctx* c, const Nf4W& w, bf16* dst, int64_t ld, ColMap cm);
+int nf4_codes_launch(Ctx* c, const Nf4W& w, uint8_t* codes);
+int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N);
+// out: [ksplit][M][N] f32 partial sums of x[M,K] @ W (no bias); 1 <= M <= 32
+int nf4_gemv_launch(Ctx* c, const Nf4W& w, const bf16* x, int64_t ldx, int64_t M, int ksplit, float* out);
+
 // Launch helper that optionally attaches the programmatic-stream-serialization
 // attribute (the kernel then starts early and calls griddepcontrol.wait itself).
 extern int64_t g_launch_total;  // kernels launched by this library since load

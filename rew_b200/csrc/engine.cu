@@ -55,10 +55,13 @@ namespace {
 constexpr int PAGE = 64;
 
 struct LinW {
-  void* w = nullptr;   // [K,N] model dtype
+  void* w = nullptr;   // [K,N] model dtype (for a quantised Linear: the shared dequantisation scratch)
   float* b = nullptr;  // [N]
   int64_t K = 0, N = 0;
   LinearBf16Plan plan;
+  bool quant = false;  // weight held as NF4 codes
+  Nf4W nf4;
+  ColMap cm = {1, 1, 1, 0};  // logical column (the reference's [in,out]) -> device column of `w`
 };
 
 // Routed experts of one DeepSeekMoE layer held by this rank (src/rew/models/deepseek.nim:36-52).
@@ -115,6 +118,28 @@ __global__ void swiglu_rows_f32_kernel(const float* gu, float* out, int64_t rows
   const float x = gu[r * 2 * f + c];
   const float sig = 1.0f / (1.0f + expf(-x));
   out[i] = (x * sig) * gu[r * 2 * f + f + c];
+}
+
+// Quantised gate|up: sums the split-K slabs of the LOGICAL [rows][gate(f) | up(f)] projection, adds the
+// biases (stored in the bf16 engine's interleaved order: groups of 8 gate, 8 up) and applies SwiGLU
+// (src/rew/nn/gated_ffn.nim:55-59).
+__global__ void swiglu_slabs_kernel(const float* part, int ksplit, int64_t rows, int64_t f, const float* bias_il, bf16* out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * f) return;
+  const int64_t r = i / f, c = i % f;
+  float g = 0.f, u = 0.f;
+  for (int s = 0; s < ksplit; ++s) {
+    const float* p = part + ((int64_t)s * rows + r) * 2 * f;
+    g += p[c];
+    u += p[f + c];
+  }
+  const int64_t bi = (c / 8) * 16 + (c % 8);
+  g += bias_il[bi];
+  u += bias_il[bi + 8];
+  const float sig = 1.0f / (1.0f + expf(-g));
+  out[i] = __float2bfloat16_rn((g * sig) * u);
 }
 
 // End of a step: publish the sampled ids, make them the next step's input,
@@ -339,6 +364,8 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
     const int64_t widest = std::max<int64_t>(m->nqkv, c.d_model);
     s->part_bytes = (size_t)rows * widest * sizeof(float) * 16;  // up to 16 split-K slabs at decode sizes
     if (rows > 32) s->part_bytes = (size_t)rows * widest * sizeof(float);
+    if (c.weight_quant)  // the quantised gate|up GEMV leaves up to 4 slabs of [32][2f] here at decode sizes
+      s->part_bytes = std::max(s->part_bytes, (size_t)32 * std::max<size_t>(16 * widest, 4 * 2 * fmax) * sizeof(float));
     RB_CUDA(cudaMalloc((void**)&s->part, s->part_bytes));
     if (c.dtype == REWB200_F32) RB_CUDA(cudaMalloc((void**)&s->gu32, (size_t)rows * 2 * std::max<int64_t>(fmax, 1) * sizeof(float)));
     if (c.n_routed > 0) {
@@ -385,6 +412,25 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
 int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, int64_t rows, bool partial, int epi,
                void* out, int64_t ldo, int* ksplit_out) {
   Ctx* c = s->m->c;
+  if (w.quant && rows <= 32) {
+    // weight-only NF4: codes dequantised inside the GEMV, f32 split-K slabs
+    int ks = nf4_pick_ksplit(c, w.K, w.N);
+    while (ks > 1 && (size_t)ks * rows * w.N * sizeof(float) > s->part_bytes) --ks;
+    RB_REQUIRE((size_t)ks * rows * w.N * sizeof(float) <= s->part_bytes, "split-K scratch too small for the quantised Linear");
+    RB_TRY(nf4_gemv_launch(c, w.nf4, (const bf16*)x, ldx, rows, ks, s->part));
+    if (partial) {
+      if (ksplit_out) *ksplit_out = ks;
+      return REWB200_OK;
+    }
+    RB_REQUIRE(epi == EPI_SWIGLU_BF16, "quantised Linear: only the SwiGLU epilogue is fused");
+    const int64_t n = rows * (w.N / 2);
+    RB_CUDA(launch_k(swiglu_slabs_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, c->stream, c->use_pdl,
+                     (const float*)s->part, ks, rows, w.N / 2, (const float*)w.b, (bf16*)out));
+    ++g_launch_total;
+    return REWB200_OK;
+  }
+  if (w.quant)  // prefill: expand the codes into the shared bf16 scratch (device column order), then the dense Linear
+    RB_TRY(nf4_dequant_launch(c, w.nf4, (bf16*)w.w, w.N, w.cm));
   if (s->m->cfg.dtype == REWB200_BF16) {
     int ks = 1;
     if (partial) {
@@ -729,6 +775,12 @@ int rewb200_model_create(int slot, const rewb200_config* cfg, rewb200_model** ou
   RB_REQUIRE(cfg && out, "rewb200_model_create: NULL argument");
   RB_CUDA(cudaSetDevice(c->device));
   RB_REQUIRE(cfg->dtype == REWB200_F32 || cfg->dtype == REWB200_BF16, "model dtype must be f32 or bf16");
+  RB_REQUIRE(cfg->weight_quant == 0 || cfg->weight_quant == 1, "weight_quant must be 0 or 1 (NF4)");
+  if (cfg->weight_quant == 1) {
+    RB_REQUIRE(cfg->dtype == REWB200_BF16 && cfg->n_routed == 0, "NF4 weights need a dense bf16 model");
+    RB_REQUIRE(cfg->d_model % 64 == 0 && (cfg->ffn / std::max(1, cfg->tp_size)) % 64 == 0 && cfg->head_dim % 64 == 0,
+               "NF4 weights need d_model, head_dim and the local ffn width to be multiples of 64");
+  }
   RB_REQUIRE(cfg->vocab > 0 && cfg->d_model > 0 && cfg->n_layers > 0 && cfg->head_dim > 0 && cfg->max_seq > 0,
              "model dimensions must be positive");
   RB_REQUIRE(cfg->n_kv_heads > 0 && cfg->n_heads % cfg->n_kv_heads == 0,
@@ -982,6 +1034,34 @@ int rewb200_model_finalize(rewb200_model* m) {
   RB_REQUIRE(m, "rewb200_model_finalize: NULL model");
   if (m->finalized) return REWB200_OK;
   RB_CUDA(cudaSetDevice(m->c->device));
+  if (m->cfg.weight_quant == 1) {
+    // nf4Quantize every decoder-block Linear from its bf16 device copy, drop that copy, and let all of
+    // them share one bf16 scratch (the largest matrix) for prefill-size launches.
+    Ctx* c = m->c;
+    size_t scratch = 0;
+    for (LayerDev& L : m->layers)
+      for (LinW* w : {&L.qkv, &L.o, &L.gu, &L.down}) scratch = std::max(scratch, (size_t)w->K * w->N * sizeof(bf16));
+    void* shared = nullptr;
+    RB_CUDA(cudaMalloc(&shared, scratch));
+    m->allocs.push_back(shared);
+    for (LayerDev& L : m->layers) {
+      L.gu.cm = ColMap{L.ffn_local, 8, 16, 8};  // bf16 engine layout: gate/up interleaved in groups of 8
+      for (LinW* w : {&L.qkv, &L.o, &L.down}) w->cm = ColMap{w->N, w->N, w->N, 0};
+      for (LinW* w : {&L.qkv, &L.o, &L.gu, &L.down}) {
+        RB_TRY(nf4_alloc(c, w->K, w->N, &w->nf4));
+        m->allocs.push_back(w->nf4.q);
+        m->allocs.push_back(w->nf4.sc);
+        RB_TRY(nf4_quantize_launch(c, w->w, REWB200_BF16, w->N, w->cm, w->nf4));
+        RB_CUDA(cudaStreamSynchronize(c->stream));
+        auto it = std::find(m->allocs.begin(), m->allocs.end(), w->w);
+        if (it != m->allocs.end()) m->allocs.erase(it);
+        RB_CUDA(cudaFree(w->w));
+        m->weight_bytes += (int64_t)(w->K * w->N / 2 + w->K * (w->N / 64) * 4) - (int64_t)(w->K * w->N * 2);
+        w->w = shared;
+        w->quant = true;
+      }
+    }
+  }
   if (m->cfg.dtype == REWB200_BF16) {
     for (LayerDev& L : m->layers) {
       RB_TRY(linear_bf16_plan(&L.qkv.plan, (const bf16*)L.qkv.w, L.qkv.K, L.qkv.N, 0));

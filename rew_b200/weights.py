@@ -34,6 +34,7 @@ class ModelConfig:
     tp_size: int = 1
     ep_rank: int = 0
     ep_size: int = 1
+    weight_quant: int = 0   # 1: decoder Linear weights as NF4 codes (blocks of 64) on the device
 
     def to_c(self):
         return _lib.Config(**asdict(self))
