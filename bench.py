@@ -49,6 +49,9 @@ WORKLOADS = {
     "tiny": dict(model="tiny_llama", batch=1, prompt=32),
     "l70_b16": dict(model="llama3_70b", batch=16, prompt=1024, parallel="tp"),
     "moe_b64": dict(model="deepseek_v2_lite", batch=64, prompt=256, parallel="ep"),
+    # the l8 decoder with its block Linears held as NF4 codes (weight-only, QLoRA's frozen base weights)
+    "l8_b32_nf4": dict(model="llama3_8b", batch=32, prompt=512, weight_quant=1),
+    "l8_b1_nf4": dict(model="llama3_8b", batch=1, prompt=512, weight_quant=1),
 }
 
 
@@ -245,6 +248,7 @@ def main():
         pg = dist
 
     cfg = make_cfg(wl["model"])
+    cfg.weight_quant = wl.get("weight_quant", 0)
     if args.layers > 0:
         cfg.n_layers = args.layers
     B, S, K, Wm = wl["batch"], wl["prompt"], args.steps, args.warmup
@@ -334,8 +338,8 @@ def main():
         roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                     # dram read+write per step, scaled from the ncu capture of the gate|up launch
                     # (239.2 MB measured for 236.1 MB algorithmic; profiles/linear_tc_kernel_32_decode_l8.md)
-                    "traffic": nbytes.value * 1.013,
-                    "kernel": "linear_tc_kernel<32>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>", "launches_per_step": nl.value, "ms_per_step": ms.value,
+                    "traffic": None if cfg.weight_quant else nbytes.value * 1.013,
+                    "kernel": ("nf4_gemv_kernel" if cfg.weight_quant else "linear_tc_kernel<32>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>"), "launches_per_step": nl.value, "ms_per_step": ms.value,
                     "bytes_per_step": nbytes.value, "peak_source": which}
         # whole decode step against the same roof: weights + KV read once per step
         kv_bytes = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
@@ -347,7 +351,7 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
         "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong" if parallel == "tp" else "weak", "vs_baseline": None,
-        "dtype": "bf16" if cfg.dtype == _lib.BF16 else "f32", "data": "synthetic",
+        "dtype": ("bf16 activations, NF4 block weights" if cfg.weight_quant else "bf16") if cfg.dtype == _lib.BF16 else "f32", "data": "synthetic",
         "config": {"workload": args.workload + ("" if args.layers <= 0 else "_%dlayers" % args.layers), "batch_per_gpu": B, "prompt": S, "decode_steps": K,
                    "parallelism": parallel + (str(world) if world > 1 else ""), "sampling": args.sampling,
                    "l2": "weights per step (%.1f GB) exceed the 126 MB L2" % (model.weight_bytes() / 1e9)},
