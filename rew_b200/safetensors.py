@@ -91,7 +91,9 @@ def _interleave_heads(w_out_in, n_heads, head_dim):
 
 
 def llama_from_hf(cfg, hf):
-    """Canonical tensor list (rew_b200.weights.tensor_specs order) from Hugging Face Llama tensors."""
+    """Canonical tensor list (rew_b200.weights.tensor_specs order) from Hugging Face Llama tensors, or from a
+    DeepSeek-MoE checkpoint with standard attention (q_proj / k_proj / v_proj / o_proj; MoE blocks named
+    mlp.gate, mlp.experts.N, mlp.shared_experts) when cfg.n_routed > 0."""
     d, hd = cfg.d_model, cfg.head_dim
 
     def get(name, default=None):
@@ -114,10 +116,35 @@ def llama_from_hf(cfg, hf):
                 w, b = _interleave_heads(w, heads, hd), _interleave_heads(b, heads, hd)
             out[p + "selfAttn.%s.weight" % name] = np.ascontiguousarray(w.T)      # [in, out]
             out[p + "selfAttn.%s.bias" % name] = b
-        for hf_name, name in (("gate_proj", "gateProj"), ("up_proj", "upProj"), ("down_proj", "downProj")):
-            w = get(hp + "mlp.%s.weight" % hf_name)
-            out[p + "mlp.%s.weight" % name] = np.ascontiguousarray(w.T)
-            out[p + "mlp.%s.bias" % name] = get(hp + "mlp.%s.bias" % hf_name, np.zeros(w.shape[0], np.float32))
+        def ffn(dst, src, rows=None):
+            """One gated FFN: HF [out,in] -> [in,out]; `rows` selects a slice of the hidden width."""
+            for hf_name, name in (("gate_proj", "gateProj"), ("up_proj", "upProj"), ("down_proj", "downProj")):
+                w = get(src + "%s.weight" % hf_name)
+                if rows is not None:
+                    w = w[:, rows] if hf_name == "down_proj" else w[rows]
+                out[dst + "%s.weight" % name] = np.ascontiguousarray(w.T)
+                b = hf.get(src + "%s.bias" % hf_name)
+                if b is not None and rows is not None:
+                    if hf_name != "down_proj":
+                        b = np.asarray(b, np.float32)[rows]
+                    elif rows.start != 0:
+                        b = None                                                 # the fused FFN's output bias counts once
+                out[dst + "%s.bias" % name] = np.zeros(w.shape[0], np.float32) if b is None else np.asarray(b, np.float32)
+
+        if cfg.layer_is_moe(l):
+            # DeepSeekMoE (src/rew/models/deepseek.nim:36-63): router Linear, shared experts, routed experts.
+            # Hugging Face stores the shared experts as ONE FFN of width n_shared * moe_ffn; a sum of FFNs
+            # over disjoint slices of the hidden width is the same function.
+            f = cfg.moe_ffn
+            gw = get(hp + "mlp.gate.weight")                                         # [n_routed, d]
+            out[p + "moe.gate.weight"] = np.ascontiguousarray(gw.T)
+            out[p + "moe.gate.bias"] = np.zeros(cfg.n_routed, np.float32)
+            for e in range(cfg.n_shared):
+                ffn(p + "moe.sharedExperts.%d." % e, hp + "mlp.shared_experts.", slice(e * f, (e + 1) * f))
+            for e in range(cfg.n_routed):
+                ffn(p + "moe.routedExperts.%d." % e, hp + "mlp.experts.%d." % e)
+        else:
+            ffn(p + "mlp.", hp + "mlp.")
         out[p + "inputLayernorm.gamma"] = get(hp + "input_layernorm.weight")
         out[p + "inputLayernorm.beta"] = np.zeros(d, np.float32)
         out[p + "postAttentionLayernorm.gamma"] = get(hp + "post_attention_layernorm.weight")

@@ -19,9 +19,18 @@ def _hf_weights(cfg, seed):
         t[p + "self_attn.k_proj.weight"] = rng.normal(0, 0.05, (cfg.n_kv_heads * hd, d))
         t[p + "self_attn.v_proj.weight"] = rng.normal(0, 0.05, (cfg.n_kv_heads * hd, d))
         t[p + "self_attn.o_proj.weight"] = rng.normal(0, 0.05, (d, cfg.n_heads * hd))
-        t[p + "mlp.gate_proj.weight"] = rng.normal(0, 0.05, (cfg.ffn, d))
-        t[p + "mlp.up_proj.weight"] = rng.normal(0, 0.05, (cfg.ffn, d))
-        t[p + "mlp.down_proj.weight"] = rng.normal(0, 0.05, (d, cfg.ffn))
+        def ffn(prefix, width):
+            t[prefix + "gate_proj.weight"] = rng.normal(0, 0.05, (width, d))
+            t[prefix + "up_proj.weight"] = rng.normal(0, 0.05, (width, d))
+            t[prefix + "down_proj.weight"] = rng.normal(0, 0.05, (d, width))
+
+        if cfg.layer_is_moe(l):     # DeepSeek-MoE naming: router, one fused shared FFN, routed experts
+            t[p + "mlp.gate.weight"] = rng.normal(0, 0.5, (cfg.n_routed, d))
+            ffn(p + "mlp.shared_experts.", cfg.n_shared * cfg.moe_ffn)
+            for e in range(cfg.n_routed):
+                ffn(p + "mlp.experts.%d." % e, cfg.moe_ffn)
+        else:
+            ffn(p + "mlp.", cfg.first_dense if cfg.n_routed > 0 and cfg.first_dense > 0 else cfg.ffn)
         t[p + "input_layernorm.weight"] = 1 + 0.1 * rng.normal(size=d)
         t[p + "post_attention_layernorm.weight"] = 1 + 0.1 * rng.normal(size=d)
     return {k: v.astype(np.float32) for k, v in t.items()}
@@ -56,8 +65,21 @@ def _hf_forward(cfg, t, ids):
         a = torch.softmax(q @ k.transpose(-1, -2) / np.sqrt(hd) + mask, -1) @ v
         h = h + a.transpose(1, 2).reshape(B, S, nh * hd) @ P[p + "self_attn.o_proj.weight"].T
         x = rms(h, P[p + "post_attention_layernorm.weight"])
-        g, u = x @ P[p + "mlp.gate_proj.weight"].T, x @ P[p + "mlp.up_proj.weight"].T
-        h = h + (torch.nn.functional.silu(g) * u) @ P[p + "mlp.down_proj.weight"].T
+        def ffn(prefix, xx):
+            g, u = xx @ P[prefix + "gate_proj.weight"].T, xx @ P[prefix + "up_proj.weight"].T
+            return (torch.nn.functional.silu(g) * u) @ P[prefix + "down_proj.weight"].T
+
+        if cfg.layer_is_moe(l):     # softmax gate, top-k, renormalised weights, plus the shared FFN
+            scores = torch.softmax(x @ P[p + "mlp.gate.weight"].T, -1)
+            topw, topi = scores.topk(cfg.top_k, -1)
+            topw = topw / topw.sum(-1, keepdim=True)
+            y = ffn(p + "mlp.shared_experts.", x)
+            for e in range(cfg.n_routed):
+                we = (topw * (topi == e)).sum(-1, keepdim=True)
+                y = y + we * ffn(p + "mlp.experts.%d." % e, x)
+            h = h + y
+        else:
+            h = h + ffn(p + "mlp.", x)
     return (rms(h, P["model.norm.weight"]) @ P["lm_head.weight"].T).numpy()
 
 
@@ -85,3 +107,18 @@ def test_hf_llama_mapping_reproduces_hf_semantics(tmp_path, orc):
     t2 = {k: v for k, v in t.items() if k != "lm_head.weight"}
     canon2 = ST.llama_from_hf(cfg, t2)
     assert np.array_equal(canon2[-2], t["model.embed_tokens.weight"].T)
+
+
+def test_hf_deepseek_moe_mapping_reproduces_hf_semantics(orc):
+    """DeepSeek-MoE naming (standard attention, mlp.gate / mlp.experts.N / one fused mlp.shared_experts,
+    dense first layer) mapped onto rew's DeepSeekMoE tensors (src/rew/models/deepseek.nim:36-63)."""
+    cfg = W.ModelConfig(vocab=96, d_model=64, n_layers=3, n_heads=4, n_kv_heads=4, head_dim=16, ffn=0, max_seq=64,
+                        theta=10000.0, eps=1e-6, norm_kind=0, mask_kind=1, n_routed=6, n_shared=2, top_k=2, moe_ffn=48,
+                        first_dense=80)
+    t = _hf_weights(cfg, 5)
+    canon = ST.llama_from_hf(cfg, t)
+    assert len(canon) == len(W.tensor_specs(cfg))
+    ids = np.random.default_rng(6).integers(0, cfg.vocab, size=(2, 9)).astype(np.int32)
+    got = orc.model_forward(cfg, canon, ids, 0, True)
+    want = _hf_forward(cfg, t, ids)
+    assert rel_l2(got, want) < 5e-6
