@@ -7,15 +7,19 @@
 // max(1e-10, absmax), code = nearest of the 16 NF4 levels (first one on a tie), value = level * scale.
 //
 // Device layout (this library's own; rewb200_nf4_unpack gives back the reference's bytes):
-//   q  [N/64][K/64][4 warps][32 lanes] uint4   one 16-byte load per lane and 64 input rows: word i is
-//        k16 step i; nibble j*4+r of a word is W[k][n] with k = 16 i + {2t, 2t+1, 2t+8, 2t+9}[r],
-//        n = 64 g + 16 warp + 8 j + lane/4, t = lane % 4 -- exactly the B fragment of mma.m16n8k16
-//   sc [N/64][K] f32                           the scales of one 64-column group, contiguous along k
-// GEMV (rows <= 32): CTA = one 64-column group x a slice of K; the scale depends on (k, group), so it
-// is folded into the ACTIVATIONS of the CTA (x'[m][k] = x[m][k] * sc[g][k], staged in shared memory)
-// and the B operand is the bare NF4 level, looked up with byte permutes: three PRMT per byte plane
-// (levels 0-7, levels 8-15, select by bit 3) for four codes at once.  f32 accumulation, split-K
-// partials [ksplit][M][N] summed by the consumer as for the bf16 Linear.
+//   q  [N/64][K/64][4 k16 steps][32 lanes] uint4   one 16-byte load per lane and k16 step: word w holds
+//        the column tiles j = 2w and 2w+1; nibble (j&1)*4 + r of a word is W[k][n] with
+//        k = 64 kb + 16 i + {2t, 2t+1, 2t+8, 2t+9}[r], n = 64 g + 8 j + lane/4, t = lane % 4 -- byte b of
+//        a word is therefore one B register (two consecutive k) of mma.m16n8k16 for one tile
+//   sc [N/64][K] f32                                the scales of one 64-column group, contiguous along k
+// GEMV (rows <= 32): a warp owns one 64-column group over a slice of K.  A byte (two codes) indexes a
+// shared-memory table of bf16 level PAIRS, replicated once per lane so that lane l only ever touches
+// bank l: one conflict-free LDS yields a whole B register.  (Integer byte-permute lookups were tried
+// first: 11 ALU operations per four weights saturate the half-rate integer pipe at 0.17 of the HBM
+// roofline.)  The register is multiplied by the bf16 pair of its two rows' scales (HMUL2) and fed to the
+// tensor core; activations are staged per warp with cp.async, double-buffered.  The 8 warps of a CTA
+// split the CTA's K range and add their accumulators through shared memory; CTAs of different K ranges
+// leave f32 slabs [ksplit][M][N] that the consumer sums, as for the bf16 Linear.
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -32,19 +36,34 @@ __constant__ float kNf4[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f
                                -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
                                0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
                                0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+// the same levels rounded to bf16 (round to nearest even)
+__constant__ uint16_t kNf4Bf16[16] = {0xBF80, 0xBF32, 0xBF06, 0xBECA, 0xBE92, 0xBE3D, 0xBDBA, 0x0000,
+                                      0x3DA3, 0x3E25, 0x3E7C, 0x3EAD, 0x3EE2, 0x3F10, 0x3F39, 0x3F80};
 
 __device__ __forceinline__ int64_t map_col(const ColMap& cm, int64_t n) {
   const int64_t seg = n / cm.seg_len, within = n % cm.seg_len;
   return (within / cm.gran) * cm.gstride + (within % cm.gran) + seg * cm.seg_off;
 }
 
+// position of W[64 kb + kk][64 g + nn] inside the (g, kb) tile: k16 step, lane, word, nibble
+__device__ __forceinline__ void tile_pos(int kk, int nn, int& i, int& lane, int& word, int& nib) {
+  i = kk >> 4;
+  const int k16 = kk & 15, j = nn >> 3, c = nn & 7;
+  const int t = (k16 & 7) >> 1, r = (k16 & 1) + ((k16 >> 3) << 1);
+  lane = c * 4 + t;
+  word = j >> 1;
+  nib = (j & 1) * 4 + r;
+}
+
 // grid (N/64, K/64), 64 threads: thread r quantises row kb*64 + r of the group, then the tile is packed.
 template <typename T>
 __global__ void __launch_bounds__(64) nf4_quantize_kernel(const T* src, int64_t ld, ColMap cm, uint4* q, float* sc, int64_t K,
                                                           int64_t N) {
-  __shared__ uint8_t codes[64][64 + 4];
+  __shared__ uint32_t tile[4][32][4];  // [k16 step][lane][word]
   const int g = blockIdx.x, kb = blockIdx.y, r = threadIdx.x;
   const int64_t k = (int64_t)kb * 64 + r;
+  for (int i = threadIdx.x; i < 4 * 32 * 4; i += 64) (&tile[0][0][0])[i] = 0u;
+  __syncthreads();
   float v[64];
   float absMax = 1e-10f;
 #pragma unroll 8
@@ -66,181 +85,201 @@ __global__ void __launch_bounds__(64) nf4_quantize_kernel(const T* src, int64_t 
         code = i;
       }
     }
-    codes[r][n] = (uint8_t)code;
+    int i, lane, word, nib;
+    tile_pos(r, n, i, lane, word, nib);
+    atomicOr(&tile[i][lane][word], (uint32_t)code << (4 * nib));
   }
   __syncthreads();
   const int KB = (int)(K / 64);
-  for (int pair = threadIdx.x; pair < 128; pair += 64) {
-    const int warp = pair >> 5, lane = pair & 31, t = lane & 3, c = lane >> 2;
-    uint32_t words[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t u = 0;
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int rr = 0; rr < 4; ++rr) {
-          const int kk = 16 * i + 2 * t + (rr & 1) + ((rr >> 1) ? 8 : 0);
-          const int nn = 16 * warp + 8 * j + c;
-          u |= (uint32_t)codes[kk][nn] << (4 * (j * 4 + rr));
-        }
-      words[i] = u;
-    }
-    q[(((int64_t)g * KB + kb) * 4 + warp) * 32 + lane] = make_uint4(words[0], words[1], words[2], words[3]);
+  uint4* dst = q + ((int64_t)g * KB + kb) * 128;
+  for (int e = threadIdx.x; e < 128; e += 64) {
+    const uint32_t* w = &tile[e >> 5][e & 31][0];
+    dst[e] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
-// mode 0: dst (bf16, column-mapped) = level * scale; mode 1: dst (uint8 [K][N]) = code
+// dst (bf16, column-mapped) = level * scale, or codes_out (uint8 [K][N]) = code
 __global__ void __launch_bounds__(128) nf4_expand_kernel(const uint4* q, const float* sc, int64_t K, int64_t N, bf16* dst,
                                                          int64_t ld, ColMap cm, uint8_t* codes_out) {
   const int g = blockIdx.x, kb = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3, c = lane >> 2;
   const int KB = (int)(K / 64);
-  const uint4 qv = q[(((int64_t)g * KB + kb) * 4 + warp) * 32 + lane];
-  const uint32_t words[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int rr = 0; rr < 4; ++rr) {
-        const int code = (words[i] >> (4 * (j * 4 + rr))) & 15;
-        const int64_t k = (int64_t)kb * 64 + 16 * i + 2 * t + (rr & 1) + ((rr >> 1) ? 8 : 0);
-        const int64_t n = (int64_t)g * 64 + 16 * warp + 8 * j + c;
-        if (codes_out) codes_out[k * N + n] = (uint8_t)code;
-        else dst[k * ld + map_col(cm, n)] = __float2bfloat16_rn(kNf4[code] * sc[(int64_t)g * K + k]);
-      }
+  const uint32_t* tile = reinterpret_cast<const uint32_t*>(q + ((int64_t)g * KB + kb) * 128);
+  for (int e = threadIdx.x; e < 64 * 64; e += 128) {
+    const int kk = e >> 6, nn = e & 63;
+    int i, lane, word, nib;
+    tile_pos(kk, nn, i, lane, word, nib);
+    const int code = (tile[(i * 32 + lane) * 4 + word] >> (4 * nib)) & 15;
+    const int64_t k = (int64_t)kb * 64 + kk, n = (int64_t)g * 64 + nn;
+    if (codes_out) codes_out[k * N + n] = (uint8_t)code;
+    else dst[k * ld + map_col(cm, n)] = __float2bfloat16_rn(kNf4[code] * sc[(int64_t)g * K + k]);
+  }
 }
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+constexpr int GW = 8;      // warps per CTA
+constexpr int XS_LD = 72;  // bf16 elements per staged row: 144 bytes keeps ldmatrix free of bank conflicts
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
   uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
 
-// bf16 bit patterns of the 16 levels, split into a low-byte and a high-byte plane of four words each
-// (levels 0-3, 4-7, 8-11, 12-15): bf16(-1) = 0xBF80, bf16(-0.6962) = 0xBF32, ...
-struct Nf4Planes {
-  uint32_t lo[4], hi[4];
-};
-__host__ __device__ constexpr uint16_t nf4_bf16_bits(int i) {
-  // round-to-nearest-even bf16 of the table, written out so that host and device agree
-  constexpr uint16_t bits[16] = {0xBF80, 0xBF32, 0xBF06, 0xBECA, 0xBE92, 0xBE3D, 0xBDBA, 0x0000,
-                                 0x3DA3, 0x3E25, 0x3E7C, 0x3EAD, 0x3EE2, 0x3F10, 0x3F39, 0x3F80};
-  return bits[i];
-}
-__device__ __forceinline__ Nf4Planes nf4_planes() {
-  Nf4Planes p;
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      lo |= (uint32_t)(nf4_bf16_bits(4 * w + b) & 0xFF) << (8 * b);
-      hi |= (uint32_t)(nf4_bf16_bits(4 * w + b) >> 8) << (8 * b);
-    }
-    p.lo[w] = lo;
-    p.hi[w] = hi;
-  }
-  return p;
-}
-
-// Four codes (the low 16 bits of q16, code r in nibble r) -> two bf16x2 registers
-// (level[r0] | level[r1] << 16, level[r2] | level[r3] << 16).
-__device__ __forceinline__ void nf4_lookup4(uint32_t q16, const Nf4Planes& p, uint32_t& r01, uint32_t& r23) {
-  const uint32_t s7 = q16 & 0x7777u;                        // index within a half of the table
-  const uint32_t pick = ((q16 >> 1) & 0x4444u) | 0x3210u;   // byte i from the low (bit 3 = 0) or the high half
-  const uint32_t lo = prmt(prmt(p.lo[0], p.lo[1], s7), prmt(p.lo[2], p.lo[3], s7), pick);
-  const uint32_t hi = prmt(prmt(p.hi[0], p.hi[1], s7), prmt(p.hi[2], p.hi[3], s7), pick);
-  r01 = prmt(lo, hi, 0x5140u);
-  r23 = prmt(lo, hi, 0x7362u);
-}
-
-constexpr int XS_LD = 72;  // bf16 elements per staged row: 144 bytes keeps ldmatrix free of bank conflicts
-
 template <int MT>
-__global__ void __launch_bounds__(128) nf4_gemv_kernel(const uint4* __restrict__ q, const float* __restrict__ sc,
-                                                       const bf16* __restrict__ x, int64_t ldx, int M, int64_t K, int64_t N,
-                                                       int kb_per_split, float* __restrict__ out) {
-  __shared__ __align__(16) bf16 xs[2][16 * MT][XS_LD];
-  const int g = blockIdx.x, split = blockIdx.y;
+__global__ void __launch_bounds__(GW * 32, 2) nf4_gemv_kernel(const uint4* __restrict__ q, const float* __restrict__ sc,
+                                                              const bf16* __restrict__ x, int64_t ldx, int M, int64_t K,
+                                                              int64_t N, int kb_per_cta, float* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  uint32_t* lut = reinterpret_cast<uint32_t*>(smem);                      // [256 byte values][32 lanes]
+  bf16* xs_all = reinterpret_cast<bf16*>(smem + 256 * 32 * 4);            // [GW][2][16*MT][XS_LD]
+  constexpr int XT = 16 * MT * XS_LD;                                     // elements of one staged tile
+  float* ss_all = reinterpret_cast<float*>(smem + 256 * 32 * 4 + (size_t)GW * 2 * XT * sizeof(bf16));  // [GW][2][64] scales
+  const int split = blockIdx.y, G = (int)(N / 64);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (int)(K / 64);
-  const int kb0 = split * kb_per_split, kb1 = min(KB, kb0 + kb_per_split);
-  const uint4* qp = q + (((int64_t)g * KB) * 4 + warp) * 32 + lane;
-  const Nf4Planes planes = nf4_planes();
-  float acc[MT][2][4];
+  const int kb0 = split * kb_per_cta, kb1 = min(KB, kb0 + kb_per_cta);
+  const int per = (max(kb1 - kb0, 0) + GW - 1) / GW;
+  const int wk0 = min(kb1, kb0 + warp * per), wk1 = min(kb1, wk0 + per);
+
+  // pair table: entry e = (level[e & 15], level[e >> 4]) as bf16x2, one copy per lane (bank = lane)
+  for (int idx = threadIdx.x; idx < 256 * 8; idx += GW * 32) {  // 16 bytes = four lanes' copies per store
+    const int e = idx >> 3;
+    const uint32_t v = (uint32_t)kNf4Bf16[e & 15] | ((uint32_t)kNf4Bf16[e >> 4] << 16);
+    reinterpret_cast<uint4*>(lut)[idx] = make_uint4(v, v, v, v);
+  }
+  bool first = true;
+  // a CTA walks the column groups blockIdx.x, blockIdx.x + gridDim.x, ...: the table is built once
+  for (int g = blockIdx.x; g < G; g += gridDim.x) {
+  const uint4* qp = q + ((int64_t)g * KB) * 128 + lane;
+  uint4 qv[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) qv[i] = make_uint4(0, 0, 0, 0);
+  if (wk0 < wk1) {  // the weights do not depend on the previous kernel: fetch before waiting for it
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qv[i] = qp[(int64_t)wk0 * 128 + i * 32];
+  }
+  if (first) {
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();
+    first = false;
+  }
+
+  float acc[MT][8][4];
 #pragma unroll
   for (int a = 0; a < MT; ++a)
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int j = 0; j < 8; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[a][j][e] = 0.f;
 
-  // the weights do not depend on the previous kernel: start fetching before waiting for it
-  uint4 qv = make_uint4(0, 0, 0, 0);
-  if (kb0 < kb1) qv = qp[(int64_t)kb0 * 128];
-  pdl_launch_dependents();
-  pdl_wait();
-
-  // staging role: 16*MT rows x 64 k, 16 consecutive k per thread
-  const int srow = threadIdx.x >> 2, sseg = (threadIdx.x & 3) * 16;
-  for (int kb = kb0; kb < kb1; ++kb) {
-    const int buf = (kb - kb0) & 1;
-    uint4 qn = make_uint4(0, 0, 0, 0);
-    if (kb + 1 < kb1) qn = qp[(int64_t)(kb + 1) * 128];
-    for (int row = srow; row < 16 * MT; row += 32) {
-      uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
-      const int64_t k0 = (int64_t)kb * 64 + sseg;
-      if (row < M) {
-        const uint4* xp = reinterpret_cast<const uint4*>(x + (int64_t)row * ldx + k0);
-        xa = xp[0];
-        xb = xp[1];
-      }
-      const float4* sp = reinterpret_cast<const float4*>(sc + (int64_t)g * K + k0);
-      const float4 s0 = sp[0], s1 = sp[1], s2 = sp[2], s3 = sp[3];
-      const float sv[16] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w, s3.x, s3.y, s3.z, s3.w};
-      const uint32_t xin[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-      uint32_t xo[8];
+  bf16* xs = xs_all + (size_t)warp * 2 * XT;
+  float* ss = ss_all + (size_t)warp * 2 * 64;
+  // this warp copies its own activation tile (16*MT rows of 128 bytes) and its group's 64 scales
+  auto stage = [&](int kb, int buf) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float lo = __uint_as_float(xin[e] << 16) * sv[2 * e];
-        const float hi = __uint_as_float(xin[e] & 0xFFFF0000u) * sv[2 * e + 1];
-        xo[e] = pack_bf16(lo, hi);
-      }
-      uint4* dp = reinterpret_cast<uint4*>(&xs[buf][row][sseg]);
-      dp[0] = make_uint4(xo[0], xo[1], xo[2], xo[3]);
-      dp[1] = make_uint4(xo[4], xo[5], xo[6], xo[7]);
+    for (int e = lane; e < 16 * MT * 8; e += 32) {
+      const int row = e >> 3, seg = e & 7;
+      const bf16* src = x + (int64_t)min(row, M - 1) * ldx + (int64_t)kb * 64 + seg * 8;
+      cp_async16(smem_u32(xs + (size_t)buf * XT + row * XS_LD + seg * 8), src, row < M ? 16 : 0);  // rows >= M: zeros
     }
-    __syncthreads();
-    const uint32_t words[4] = {qv.x, qv.y, qv.z, qv.w};
+    if (lane < 16) cp_async16(smem_u32(ss + buf * 64 + lane * 4), sc + (int64_t)g * K + (int64_t)kb * 64 + lane * 4, 16);
+  };
+  if (wk0 < wk1) stage(wk0, 0);
+  cp_async_commit();
+  const unsigned char* lut_bytes = reinterpret_cast<const unsigned char*>(lut);
+  const uint32_t lane4 = (uint32_t)lane * 4;
+  const int t = lane & 3;
+  for (int kb = wk0; kb < wk1; ++kb) {
+    const int buf = (kb - wk0) & 1;
+    const bool more = kb + 1 < wk1;
+    if (more) stage(kb + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();  // everything but the tile just requested has landed
+    __syncwarp();
+    const bf16* xt = xs + (size_t)buf * XT;
+    // scales for the four k16 steps: rows 2t, 2t+1 and 2t+8, 2t+9 as bf16 pairs
+    uint32_t spair[4][2];
+    {
+      const float* sp = ss + buf * 64 + 2 * t;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = *reinterpret_cast<const float2*>(sp + 16 * i);
+        const float2 b = *reinterpret_cast<const float2*>(sp + 16 * i + 8);
+        spair[i][0] = pack_bf16(a.x, a.y);
+        spair[i][1] = pack_bf16(b.x, b.y);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      uint32_t b[2][2];
-      nf4_lookup4(words[i], planes, b[0][0], b[0][1]);
-      nf4_lookup4(words[i] >> 16, planes, b[1][0], b[1][1]);
+      uint32_t af[MT][4];
 #pragma unroll
       for (int a = 0; a < MT; ++a) {
-        uint32_t af[4];
         const int arow = a * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, acol = 16 * i + (lane >> 4) * 8;
-        ldmatrix_x4(af[0], af[1], af[2], af[3], smem_u32(&xs[buf][arow][acol]));
-        mma_bf16_16816(acc[a][0], af, b[0][0], b[0][1]);
-        mma_bf16_16816(acc[a][1], af, b[1][0], b[1][1]);
+        ldmatrix_x4(af[a][0], af[a][1], af[a][2], af[a][3], smem_u32(xt + arow * XS_LD + acol));
+      }
+      const uint32_t words[4] = {qv[i].x, qv[i].y, qv[i].z, qv[i].w};
+      // the codes of this step are in `words`: refill the register with the same step of the next block
+      if (more) qv[i] = qp[(int64_t)(kb + 1) * 128 + i * 32];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t u = words[w];
+        // byte b of the word = one B register.  Pair e of this lane's table copy sits at byte offset
+        // e * 128 + lane * 4: a shift, one (x & mask) | lane4, one LDS.
+        const uint32_t o0 = ((u << 7) & 0x7F80u) | lane4, o1 = ((u >> 1) & 0x7F80u) | lane4;
+        const uint32_t o2 = ((u >> 9) & 0x7F80u) | lane4, o3 = ((u >> 17) & 0x7F80u) | lane4;
+        const uint32_t b00 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o0), spair[i][0]);
+        const uint32_t b01 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o1), spair[i][1]);
+        const uint32_t b10 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o2), spair[i][0]);
+        const uint32_t b11 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o3), spair[i][1]);
+#pragma unroll
+        for (int a = 0; a < MT; ++a) {
+          mma_bf16_16816(acc[a][2 * w], af[a], b00, b01);
+          mma_bf16_16816(acc[a][2 * w + 1], af[a], b10, b11);
+        }
       }
     }
-    qv = qn;
+    __syncwarp();  // all lanes are done with this tile before it is overwritten two iterations on
   }
-  const int t = lane & 3, c = lane >> 2;
-  float* op = out + (int64_t)split * M * N;
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its staging area: reuse it for the reduction
+  float* red = reinterpret_cast<float*>(xs_all);  // [GW][16*MT][64]
+  const int c = lane >> 2;
 #pragma unroll
   for (int a = 0; a < MT; ++a)
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int64_t n = (int64_t)g * 64 + 16 * warp + 8 * j + 2 * t;
-      const int m0 = a * 16 + c, m1 = m0 + 8;
-      if (m0 < M) *reinterpret_cast<float2*>(op + (int64_t)m0 * N + n) = make_float2(acc[a][j][0], acc[a][j][1]);
-      if (m1 < M) *reinterpret_cast<float2*>(op + (int64_t)m1 * N + n) = make_float2(acc[a][j][2], acc[a][j][3]);
+    for (int j = 0; j < 8; ++j) {
+      float* rp = red + ((size_t)warp * 16 * MT + a * 16 + c) * 64 + 8 * j + 2 * t;
+      *reinterpret_cast<float2*>(rp) = make_float2(acc[a][j][0], acc[a][j][1]);
+      *reinterpret_cast<float2*>(rp + 8 * 64) = make_float2(acc[a][j][2], acc[a][j][3]);
     }
+  __syncthreads();
+  float* op = out + (int64_t)split * M * N + (int64_t)g * 64;
+  for (int e = threadIdx.x; e < 16 * MT * 16; e += GW * 32) {  // float4 per thread
+    const int m = e >> 4, n4 = (e & 15) * 4;
+    if (m >= M) continue;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < GW; ++w) {
+      const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)w * 16 * MT + m) * 64 + n4);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    *reinterpret_cast<float4*>(op + (int64_t)m * N + n4) = s;
+  }
+  __syncthreads();  // the reduction area is staging area again
+  }  // column groups
+}
+
+template <int MT>
+constexpr size_t gemv_smem() {
+  return 256 * 32 * 4 + (size_t)GW * 2 * 16 * MT * XS_LD * sizeof(bf16) + (size_t)GW * 2 * 64 * sizeof(float);
 }
 
 }  // namespace
@@ -292,11 +331,14 @@ int nf4_codes_launch(Ctx* c, const Nf4W& w, uint8_t* codes) {
   return REWB200_OK;
 }
 
+// CTAs along K: each of a CTA's 8 warps should own about 4 blocks of 64 rows, but the grid should
+// still cover the GPU about twice.  (Fewer, longer-lived CTAs walking several column groups measured
+// slower: the drain and refill of the per-warp pipeline at every group costs more than the table build.)
 int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N) {
   const int groups = (int)(N / 64), KB = (int)(K / 64);
-  int ks = (c->sm_count * 6 + groups - 1) / groups;
-  ks = std::max(1, std::min(ks, std::max(1, KB / 4)));
-  return ks;
+  int ks = std::max(1, KB / (GW * 4));
+  while (ks < KB / GW && groups * ks < 2 * c->sm_count) ++ks;
+  return std::max(1, std::min(ks, KB));
 }
 
 int nf4_gemv_launch(Ctx* c, const Nf4W& w, const bf16* x, int64_t ldx, int64_t M, int ksplit, float* out) {
@@ -305,13 +347,20 @@ int nf4_gemv_launch(Ctx* c, const Nf4W& w, const bf16* x, int64_t ldx, int64_t M
   const int KB = (int)(w.K / 64);
   ksplit = std::max(1, std::min(ksplit, KB));
   const int per = (KB + ksplit - 1) / ksplit;
+  // one CTA per (column group, K slice); the kernel also accepts fewer CTAs than groups
   const dim3 grid((unsigned)(w.N / 64), (unsigned)ksplit);
+  static bool attr_set = false;
+  if (!attr_set) {
+    RB_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemv_smem<1>()));
+    RB_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemv_smem<2>()));
+    attr_set = true;
+  }
   if (M <= 16)
-    RB_CUDA(launch_k(nf4_gemv_kernel<1>, grid, dim3(128), 0, c->stream, c->use_pdl, (const uint4*)w.q, (const float*)w.sc, x, ldx,
-                     (int)M, w.K, w.N, per, out));
+    RB_CUDA(launch_k(nf4_gemv_kernel<1>, grid, dim3(GW * 32), gemv_smem<1>(), c->stream, c->use_pdl, (const uint4*)w.q,
+                     (const float*)w.sc, x, ldx, (int)M, w.K, w.N, per, out));
   else
-    RB_CUDA(launch_k(nf4_gemv_kernel<2>, grid, dim3(128), 0, c->stream, c->use_pdl, (const uint4*)w.q, (const float*)w.sc, x, ldx,
-                     (int)M, w.K, w.N, per, out));
+    RB_CUDA(launch_k(nf4_gemv_kernel<2>, grid, dim3(GW * 32), gemv_smem<2>(), c->stream, c->use_pdl, (const uint4*)w.q,
+                     (const float*)w.sc, x, ldx, (int)M, w.K, w.N, per, out));
   ++g_launch_total;
   return REWB200_OK;
 }
