@@ -64,6 +64,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *   "linear" = "mma" | "tc_prefill" | "tc"   bf16 Linear on mma.sync, on tcgen05 for more than 32
  *                                            rows, or on tcgen05 always   (REW_B200_LINEAR)
  *   "pdl"    = "0" | "1"                     programmatic dependent launch (REW_B200_PDL)
+ *   "prefill" = "persistent" | "tile"        Linear launches of 256-token tiles: one persistent CTA per SM
+ *                                            with the epilogue overlapped (default), or one CTA per tile
  *   "sampling" = "bucket" | "radix"          top-k / top-p selection: bucket histograms with the
  *                                            radix select as the exact fallback (default), or
  *                                            the radix select always

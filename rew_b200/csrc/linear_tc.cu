@@ -312,6 +312,216 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
   }
 }
 
+// ---- persistent variant for prefill-size launches (256-token tiles, no split-K) -------------------
+// One CTA per SM walks its share of the output tiles.  The accumulator is double-buffered in TMEM
+// (2 x 256 columns), so the epilogue warps drain tile j while the MMA warp already accumulates tile
+// j + 1 and the TMA ring keeps running across tile boundaries; the per-tile cost becomes
+// max(main loop, epilogue) instead of their sum.  The epilogue transposes 32 tokens at a time through
+// two small staging buffers, which leaves room for the same four pipeline stages.
+struct PersistCfg {
+  static constexpr int TN = 256;
+  static constexpr int STAGES = 4;
+  static constexpr int B_BYTES = TN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 48 KB
+  static constexpr int STG_BYTES = 32 * 512;              // 32 tokens x 128 features x 4 bytes
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STG_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+};
+
+__global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                                 const __grid_constant__ CUtensorMap tmX, TcArgs a,
+                                                                 int tiles_n, int tiles_m) {
+  using C = PersistCfg;
+  constexpr int TN = C::TN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stg_base = smem + C::STAGES * C::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(stg_base + 2 * C::STG_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tmem_full = empty + C::STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = tiles_n * tiles_m;
+  const int nkb = (int)((a.K + BK - 1) / BK);
+  // same tile order as the one-tile kernel: groups of 8 token tiles per feature tile
+  auto tile_coords = [&](int lin, int& tile_n, int& tile_m) {
+    constexpr int GROUP_M = 8;
+    const int per_group = GROUP_M * tiles_n;
+    const int group = lin / per_group;
+    const int first_m = group * GROUP_M;
+    const int group_rows = min(GROUP_M, tiles_m - first_m);
+    const int in_group = lin - group * per_group;
+    tile_m = first_m + in_group % group_rows;
+    tile_n = in_group / group_rows;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 1);
+    }
+    fence_barrier_init();
+    pdl_launch_dependents();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      tma_prefetch_desc(&tmX);
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      pdl_wait();  // the activations come from the previous kernel
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int tile_n, tile_m;
+        tile_coords(t, tile_n, tile_m);
+        const int col0 = tile_n * BM, row0 = tile_m * TN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) - 1) & 1, a.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + s * C::STAGE_BYTES;
+          mbar_expect_tx(&full[s], C::STAGE_BYTES);
+          const int k = kb * BK;
+          tma_load_2d_hint(st, &tmW, &full[s], col0, k, pol_w);
+          tma_load_2d_hint(st + A_BYTES / 2, &tmW, &full[s], col0 + 64, k, pol_w);
+          tma_load_2d_hint(st + A_BYTES, &tmX, &full[s], k, row0, pol_x);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(TN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      const uint32_t smem_base = smem_u32(smem);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++j) {
+        const int buf = j & 1;
+        if (j >= 2) {  // the epilogue must have drained this accumulator (tile j - 2)
+          ok = mbar_wait(&tmem_empty[buf], ((j >> 1) - 1) & 1, a.status);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * TN);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          ok = mbar_wait(&full[s], (it / C::STAGES) & 1, a.status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * C::STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = smem_desc(sa + kk * 2048, A_BYTES / 2, 1024);
+            const uint64_t db = smem_desc(sb + kk * 32, 16, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 2..5; TMEM lanes 32*(warp%4) .. +31
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    const bool swiglu = a.epi == EPI_SWIGLU_BF16;
+    const bool out_f32 = a.epi == EPI_PARTIAL_F32 || a.epi == EPI_BIAS_F32;
+    const int tile_cols = swiglu ? 64 : 128;
+    const int row_bytes = tile_cols * (out_f32 ? 4 : 2);
+    const int chunks_per_row = row_bytes / 16;
+    const int elems_per_chunk = out_f32 ? 4 : 8;
+    const size_t esz = out_f32 ? 4 : 2;
+    const int64_t out_cols = swiglu ? a.N / 2 : a.N;
+    const bool is_gate = (lane & 15) < 8;
+    const int hcol = q * 16 + (lane >> 4) * 8 + (lane & 7);
+    pdl_wait();  // the output buffer may still be read by the previous kernel
+    int j = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
+      int tile_n, tile_m;
+      tile_coords(t, tile_n, tile_m);
+      const int col0 = tile_n * BM, row0 = tile_m * TN;
+      const int rows_valid = (int)min((int64_t)TN, a.M - row0);
+      const int buf = j & 1;
+      if (ok) ok = mbar_wait(&tmem_full[buf], (j >> 1) & 1, a.status);
+      tc_fence_after();
+      const int64_t feat = (int64_t)col0 + q * 32 + lane;
+      const bool feat_ok = feat < a.N;
+      const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
+      const int64_t out_col0 = swiglu ? col0 / 2 : col0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        if (c0 >= rows_valid) break;  // uniform over the four warps
+        uint8_t* stg = stg_base + ((c0 >> 5) & 1) * C::STG_BYTES;
+        if (ok) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * TN + c0), r);
+          if (swiglu) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+              const float v = __uint_as_float(r[jj]) + bias_v;
+              const float up = __shfl_down_sync(0xffffffffu, v, 8);
+              if (is_gate) reinterpret_cast<bf16*>(stg + jj * row_bytes)[hcol] = __float2bfloat16_rn(silu_f(v) * up);
+            }
+          } else if (out_f32) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              reinterpret_cast<float*>(stg + jj * row_bytes)[q * 32 + lane] = __uint_as_float(r[jj]) + bias_v;
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              reinterpret_cast<bf16*>(stg + jj * row_bytes)[q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[jj]) + bias_v);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+        if (ok) {
+          const int rows_here = min(32, rows_valid - c0);
+          const int total = rows_here * chunks_per_row;
+          uint8_t* obase = reinterpret_cast<uint8_t*>(a.out);
+          for (int i = et; i < total; i += 128) {
+            const int row = i / chunks_per_row, ch = i % chunks_per_row;
+            const int64_t col = out_col0 + (int64_t)ch * elems_per_chunk;
+            if (col >= out_cols) continue;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + row * row_bytes + ch * 16);
+            *reinterpret_cast<uint4*>(obase + ((size_t)(row0 + c0 + row) * a.ldo + col) * esz) = v;
+          }
+        }
+      }
+      // every epilogue warp has read its part of the accumulator: hand the buffer back
+      tc_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+  }
+}
+
 template <int TN>
 int launch_tn(Ctx* c, const LinearBf16Plan& plan, const CUtensorMap& tmX, const TcArgs& a, dim3 grid) {
   using C = TcCfg<TN>;
@@ -351,6 +561,18 @@ int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t 
   a.bias = bias;
   a.status = c->d_status;
   dim3 grid((unsigned)((plan.N + BM - 1) / BM), (unsigned)((M + TN - 1) / TN), (unsigned)ksplit);
+  if (TN == 256 && ksplit == 1 && c->prefill_persistent && (int64_t)grid.x * grid.y >= 2 * (int64_t)c->sm_count) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      RB_CUDA(cudaFuncSetAttribute(linear_tc_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistCfg::SMEM));
+      attr_set = true;
+    }
+    const int ctas = (int)std::min<int64_t>((int64_t)grid.x * grid.y, c->sm_count);
+    RB_CUDA(launch_k(linear_tc_persist_kernel, dim3((unsigned)ctas), dim3(192), (size_t)PersistCfg::SMEM, c->stream, c->use_pdl,
+                     plan.tmW, tmX, a, (int)grid.x, (int)grid.y));
+    ++g_launch_total;
+    return REWB200_OK;
+  }
   switch (TN) {
     case 32: return launch_tn<32>(c, plan, tmX, a, grid);
     case 64: return launch_tn<64>(c, plan, tmX, a, grid);

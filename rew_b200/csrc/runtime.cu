@@ -244,6 +244,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     c->linear_impl = v == "tc" ? 2 : (v == "tc_prefill" ? 1 : 0);
   } else if (k == "pdl") {
     c->use_pdl = v != "0";
+  } else if (k == "prefill") {
+    RB_REQUIRE(v == "persistent" || v == "tile", "option prefill: expected persistent or tile");
+    c->prefill_persistent = v == "persistent";
   } else if (k == "sampling") {
     RB_REQUIRE(v == "bucket" || v == "radix", "option sampling: expected bucket or radix");
     c->sampling_exact = v == "radix";

@@ -55,3 +55,45 @@ def test_tc_model_matches_oracle_and_mma_path(rb_tc, orc):
         _, logits_mma = sess2.forward(prompt, want_logits=True)
         rb_tc.set_option("linear", "tc")
         assert rel_l2(logits, logits_mma) <= 1e-2
+
+
+def test_persistent_prefill_linear_matches_oracle(rb_tc, orc):
+    """Enough 256-token tiles (17 x 20 >= 2 per SM) for the persistent kernel with the double-buffered
+    accumulator; a ragged last token tile and a last feature tile that is only half there."""
+    from rew_b200 import _lib
+    M, K, N = 4100, 320, 2496
+    rng = np.random.default_rng(11)
+    x = orc.bf16_round(rng.normal(size=(M, K)))
+    w = orc.bf16_round(rng.normal(0, 0.05, size=(K, N)))
+    b = rng.normal(0, 0.1, size=(N,)).astype(np.float32)
+    want = orc.linear(x, w, b)
+    T = rb_tc.Tensor.from_host
+    lin = rb_tc.Linear(T(w, _lib.BF16), T(b))
+    got = lin.forward(T(x, _lib.BF16)).to_host()
+    assert rel_l2(got, want) < 5e-3
+    rb_tc.set_option("prefill", "tile")
+    try:
+        again = lin.forward(T(x, _lib.BF16)).to_host()
+    finally:
+        rb_tc.set_option("prefill", "persistent")
+    assert np.array_equal(got, again)   # same MMA order, same rounding: the two kernels agree bit for bit
+
+
+def test_persistent_prefill_model_equals_tile_kernel(rb_tc):
+    """A 20 480-token prefill puts every decoder Linear (f32 partial, SwiGLU and bf16 epilogues) on the
+    persistent kernel; the logits must equal those of the one-tile-per-CTA kernel exactly."""
+    from rew_b200 import _lib
+    cfg = W.ModelConfig(vocab=512, d_model=512, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1408, max_seq=640,
+                        theta=500000.0, dtype=_lib.BF16, mask_kind=1)
+    model = rb_tc.CausalLM(cfg).init_random(seed=3, std=0.05)
+    B, S = 40, 512
+    prompt = np.random.default_rng(1).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+    sess = model.session(B, S + 8)
+    _, a = sess.forward(prompt, want_logits=True)
+    rb_tc.set_option("prefill", "tile")
+    try:
+        sess.reset()
+        _, b = sess.forward(prompt, want_logits=True)
+    finally:
+        rb_tc.set_option("prefill", "persistent")
+    assert np.isfinite(a).all() and np.array_equal(a, b)
