@@ -323,7 +323,8 @@ struct PersistCfg {
   static constexpr int STAGES = 4;
   static constexpr int B_BYTES = TN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 48 KB
-  static constexpr int STG_BYTES = 32 * 512;              // 32 tokens x 128 features x 4 bytes
+  static constexpr int STG_LD = 528;                      // bytes per staged token row (512 + 16: no bank conflicts)
+  static constexpr int STG_BYTES = 32 * STG_LD;           // 32 tokens x 128 features x 4 bytes
   static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STG_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
 };
@@ -453,8 +454,6 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
     const int elems_per_chunk = out_f32 ? 4 : 8;
     const size_t esz = out_f32 ? 4 : 2;
     const int64_t out_cols = swiglu ? a.N / 2 : a.N;
-    const bool is_gate = (lane & 15) < 8;
-    const int hcol = q * 16 + (lane >> 4) * 8 + (lane & 7);
     pdl_wait();  // the output buffer may still be read by the previous kernel
     int j = 0;
     bool ok = true;
@@ -477,21 +476,15 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
         if (ok) {
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * TN + c0), r);
-          if (swiglu) {
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-              const float v = __uint_as_float(r[jj]) + bias_v;
-              const float up = __shfl_down_sync(0xffffffffu, v, 8);
-              if (is_gate) reinterpret_cast<bf16*>(stg + jj * row_bytes)[hcol] = __float2bfloat16_rn(silu_f(v) * up);
-            }
-          } else if (out_f32) {
+          if (swiglu || out_f32) {
+            // f32 [token][feature]; SwiGLU is applied on the way out, by all 128 threads
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj)
-              reinterpret_cast<float*>(stg + jj * row_bytes)[q * 32 + lane] = __uint_as_float(r[jj]) + bias_v;
+              reinterpret_cast<float*>(stg + jj * C::STG_LD)[q * 32 + lane] = __uint_as_float(r[jj]) + bias_v;
           } else {
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj)
-              reinterpret_cast<bf16*>(stg + jj * row_bytes)[q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[jj]) + bias_v);
+              reinterpret_cast<bf16*>(stg + jj * C::STG_LD)[q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[jj]) + bias_v);
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
@@ -503,7 +496,18 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
             const int row = i / chunks_per_row, ch = i % chunks_per_row;
             const int64_t col = out_col0 + (int64_t)ch * elems_per_chunk;
             if (col >= out_cols) continue;
-            const uint4 v = *reinterpret_cast<const uint4*>(stg + row * row_bytes + ch * 16);
+            uint4 v;
+            if (swiglu) {
+              // features ch*16 .. +7 are gates, +8 .. +15 their up partners (the engine's interleave)
+              const float4* gp = reinterpret_cast<const float4*>(stg + row * C::STG_LD + ch * 64);
+              const float4 g0 = gp[0], g1 = gp[1], u0 = gp[2], u1 = gp[3];
+              v.x = pack_bf16(silu_f(g0.x) * u0.x, silu_f(g0.y) * u0.y);
+              v.y = pack_bf16(silu_f(g0.z) * u0.z, silu_f(g0.w) * u0.w);
+              v.z = pack_bf16(silu_f(g1.x) * u1.x, silu_f(g1.y) * u1.y);
+              v.w = pack_bf16(silu_f(g1.z) * u1.z, silu_f(g1.w) * u1.w);
+            } else {
+              v = *reinterpret_cast<const uint4*>(stg + row * C::STG_LD + ch * 16);
+            }
             *reinterpret_cast<uint4*>(obase + ((size_t)(row0 + c0 + row) * a.ldo + col) * esz) = v;
           }
         }
