@@ -271,6 +271,84 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
   }
 }
 
+template <typename TA>
+__device__ __forceinline__ void store8(TA* dst, const float* r);
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float* r) {
+  *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(r[4], r[5], r[6], r[7]);
+}
+template <>
+__device__ __forceinline__ void store8<bf16>(bf16* dst, const float* r) {
+  *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]), pack_bf16(r[4], r[5]), pack_bf16(r[6], r[7]));
+}
+
+// Same work as qkv_post_kernel, eight consecutive columns (four RoPE pairs) per thread with 16-byte
+// accesses; needs head_dim % 8 == 0.  Prefill-size launches are bandwidth-bound on the f32 partials.
+template <typename TA>
+__global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int b = (int)(row / a.S), s = (int)(row % a.S);
+  const int pos = a.pos0[b] + s;
+  const int hd = a.hd;
+  const int nq = a.nh * hd, nkv = a.kvh * hd, ntot = nq + 2 * nkv;
+  const int rpos = pos + a.rope_shift;
+  if (pos < 0 || pos >= a.kv_capacity || rpos < 0 || rpos >= a.max_seq) {
+    if (threadIdx.x == 0) atomicExch(a.status, KS_BAD_INDEX);
+    return;
+  }
+  const int col = 8 * (blockIdx.y * blockDim.x + threadIdx.x);
+  if (col >= ntot) return;
+  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const float* pp = a.partial + row * ntot + col;
+  for (int sp = 0; sp < a.nsplit; ++sp) {
+    const float4 t0 = *reinterpret_cast<const float4*>(pp + sp * a.split_stride);
+    const float4 t1 = *reinterpret_cast<const float4*>(pp + sp * a.split_stride + 4);
+    v[0] += t0.x; v[1] += t0.y; v[2] += t0.z; v[3] += t0.w;
+    v[4] += t1.x; v[5] += t1.y; v[6] += t1.z; v[7] += t1.w;
+  }
+  if (a.bias) {
+    const float4 b0 = *reinterpret_cast<const float4*>(a.bias + col), b1 = *reinterpret_cast<const float4*>(a.bias + col + 4);
+    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+  }
+  int64_t cache_row_base, head_stride;
+  if (a.kv.block_table) {
+    const int page = a.kv.block_table[(int64_t)b * a.kv.max_pages + pos / a.kv.page];
+    cache_row_base = ((int64_t)page * a.kvh) * a.kv.page + pos % a.kv.page;
+    head_stride = a.kv.page;
+  } else {
+    cache_row_base = ((int64_t)b * a.kvh) * a.kv.contiguous_len + pos;
+    head_stride = a.kv.contiguous_len;
+  }
+  if (col < nq + nkv) {
+    // the tables hold each angle's value twice (elements 2i and 2i+1), so element 2j of the chunk is pair j's
+    const int e0 = col % hd;
+    const float* cr = a.cosT + (int64_t)rpos * hd + e0;
+    const float* sr = a.sinT + (int64_t)rpos * hd + e0;
+    const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
+    const float cs[4] = {c0.x, c0.z, c1.x, c1.z}, sn[4] = {s0.x, s0.z, s1.x, s1.z};
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      r[2 * j] = cs[j] * v[2 * j] - sn[j] * v[2 * j + 1];
+      r[2 * j + 1] = sn[j] * v[2 * j] + cs[j] * v[2 * j + 1];
+    }
+    if (col < nq) {
+      store8<TA>(reinterpret_cast<TA*>(a.q_out) + row * nq + col, r);
+    } else {
+      const int h = (col - nq) / hd, e = (col - nq) % hd;
+      store8<TA>(reinterpret_cast<TA*>(a.kv.k) + (cache_row_base + h * head_stride) * hd + e, r);
+    }
+  } else {
+    const int h = (col - nq - nkv) / hd, e = (col - nq - nkv) % hd;
+    store8<TA>(reinterpret_cast<TA*>(a.kv.v) + (cache_row_base + h * head_stride) * hd + e, v);
+  }
+}
+
 // One CTA per (token row, chunk of 256 column pairs) of the fused q|k|v row.
 template <typename TA>
 __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
@@ -618,6 +696,17 @@ int qkv_post_launch(Ctx* c, const QkvPostArgs& a, int64_t B) {
   RB_REQUIRE(a.hd % 2 == 0, "head_dim must be even for RoPE");
   cudaError_t e;
   const int npairs = (a.nh + 2 * a.kvh) * a.hd / 2;
+  if (a.hd % 8 == 0 && rows > 64) {  // prefill sizes: eight columns per thread
+    const int nchunk = (a.nh + 2 * a.kvh) * a.hd / 8;
+    dim3 vgrid((unsigned)rows, (unsigned)((nchunk + 255) / 256));
+    if (a.act_dtype == REWB200_BF16)
+      e = launch_k(qkv_post_vec_kernel<bf16>, vgrid, dim3(256), 0, c->stream, c->use_pdl, a);
+    else
+      e = launch_k(qkv_post_vec_kernel<float>, vgrid, dim3(256), 0, c->stream, c->use_pdl, a);
+    RB_CUDA(e);
+    ++g_launch_total;
+    return REWB200_OK;
+  }
   dim3 grid((unsigned)rows, (unsigned)((npairs + 255) / 256));
   if (a.act_dtype == REWB200_BF16)
     e = launch_k(qkv_post_kernel<bf16>, grid, dim3(256), 0, c->stream, c->use_pdl, a);
