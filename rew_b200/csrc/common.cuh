@@ -76,8 +76,9 @@ struct ColMap {
   int64_t seg_len, gran, gstride, seg_off;
 };
 struct Nf4W {
-  uint4* q = nullptr;   // [N/64][K/64][4][32] packed codes in mma B-fragment order
-  float* sc = nullptr;  // [N/64][K] scales
+  uint8_t* q = nullptr;     // [ceil(N/128)][K/64][128][32] codes: feature-major, two input rows per byte
+  float* sc = nullptr;      // [N/64][K] scales
+  uint32_t* sc2 = nullptr;  // [N/64][K/2] the scales as bf16 pairs of consecutive input rows
   int64_t K = 0, N = 0;
 };
 int nf4_alloc(Ctx* c, int64_t K, int64_t N, Nf4W* w);

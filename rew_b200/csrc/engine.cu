@@ -1051,12 +1051,13 @@ int rewb200_model_finalize(rewb200_model* m) {
         RB_TRY(nf4_alloc(c, w->K, w->N, &w->nf4));
         m->allocs.push_back(w->nf4.q);
         m->allocs.push_back(w->nf4.sc);
+        m->allocs.push_back(w->nf4.sc2);
         RB_TRY(nf4_quantize_launch(c, w->w, REWB200_BF16, w->N, w->cm, w->nf4));
         RB_CUDA(cudaStreamSynchronize(c->stream));
         auto it = std::find(m->allocs.begin(), m->allocs.end(), w->w);
         if (it != m->allocs.end()) m->allocs.erase(it);
         RB_CUDA(cudaFree(w->w));
-        m->weight_bytes += (int64_t)(w->K * w->N / 2 + w->K * (w->N / 64) * 4) - (int64_t)(w->K * w->N * 2);
+        m->weight_bytes += (int64_t)(w->K * w->N / 2 + w->K * (w->N / 64) * 6) - (int64_t)(w->K * w->N * 2);
         w->w = shared;
         w->quant = true;
       }
@@ -1586,7 +1587,7 @@ int rewb200_session_profile_linears(rewb200_session* s, int iters, float* ms_per
     for (LayerDev& L : m->layers) {
       if (L.moe || L.ffn_local == 0) return fail("linear profiling covers dense decoder blocks only");
       // algorithmic bytes of one Linear: weights (bf16, or NF4 codes + scales) + activations in + result out
-      auto wbytes = [&](const LinW& w) { return w.quant ? w.K * w.N / 2 + w.K * (w.N / 64) * 4 : w.K * w.N * 2; };
+      auto wbytes = [&](const LinW& w) { return w.quant ? w.K * w.N / 2 + w.K * (w.N / 64) * 2 : w.K * w.N * 2; };  // codes + bf16 scale pairs
       int ks = 1;
       RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks));
       if (count) bytes += wbytes(L.qkv) + rows * L.qkv.K * 2 + (int64_t)ks * rows * L.qkv.N * 4;

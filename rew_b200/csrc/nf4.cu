@@ -7,19 +7,24 @@
 // max(1e-10, absmax), code = nearest of the 16 NF4 levels (first one on a tie), value = level * scale.
 //
 // Device layout (this library's own; rewb200_nf4_unpack gives back the reference's bytes):
-//   q  [N/64][K/64][4 k16 steps][32 lanes] uint4   one 16-byte load per lane and k16 step: word w holds
-//        the column tiles j = 2w and 2w+1; nibble (j&1)*4 + r of a word is W[k][n] with
-//        k = 64 kb + 16 i + {2t, 2t+1, 2t+8, 2t+9}[r], n = 64 g + 8 j + lane/4, t = lane % 4 -- byte b of
-//        a word is therefore one B register (two consecutive k) of mma.m16n8k16 for one tile
-//   sc [N/64][K] f32                                the scales of one 64-column group, contiguous along k
-// GEMV (rows <= 32): a warp owns one 64-column group over a slice of K.  A byte (two codes) indexes a
-// shared-memory table of bf16 level PAIRS, replicated once per lane so that lane l only ever touches
-// bank l: one conflict-free LDS yields a whole B register.  (Integer byte-permute lookups were tried
-// first: 11 ALU operations per four weights saturate the half-rate integer pipe at 0.17 of the HBM
-// roofline.)  The register is multiplied by the bf16 pair of its two rows' scales (HMUL2) and fed to the
-// tensor core; activations are staged per warp with cp.async, double-buffered.  The 8 warps of a CTA
-// split the CTA's K range and add their accumulators through shared memory; CTAs of different K ranges
-// leave f32 slabs [ksplit][M][N] that the consumer sums, as for the bf16 Linear.
+//   q   [ceil(N/128)][K/64][128 features][32 bytes]  the 64 codes of one feature and one block of 64 input
+//         rows, byte j = (code of row 2j) | (code of row 2j+1) << 4; features past N hold code 7 (= 0.0)
+//   sc  [N/64][K] f32      the scales of one 64-feature group, contiguous along k
+//   sc2 [N/64][K/2] u32    the same scales as bf16 pairs (rows 2j, 2j+1): what the GEMV multiplies by
+// GEMV (rows <= 32) on the 5th-generation tensor core with the WEIGHT operand in tensor memory:
+//   D[128 features][32 tokens] (TMEM, f32) += A[128 features][64 k] (TMEM, bf16) * B[64 k][32 tokens] (smem)
+//   warp 0      TMA producer, 8-stage ring; a stage = the activation tile (32 tokens x 64 k, 128-byte
+//               swizzle) + the tile's 4 KB of codes + the scale pairs of its two groups (bulk copies)
+//   warp 1      one thread issues four tcgen05.mma (K = 16 each) per block of 64 rows, A read from TMEM
+//   warps 2-9   dequantisers: a warp owns the 32 TMEM lanes (features) of its lane quarter and every
+//               other block; a lane reads its feature's 32 code bytes from the stage, turns each byte into a bf16 pair
+//               with ONE conflict-free LDS from a shared-memory pair table (one copy per lane), multiplies
+//               by the scale pair (HMUL2) and stores its 32 columns with one tcgen05.st into one of four
+//               A buffers.  The dequantised weights never touch shared memory.
+//   epilogue    warps 2-5 read D (tcgen05.ld) and store the f32 split-K slab [ksplit][M][N]
+// (Two earlier versions fed mma.sync from registers: byte-permute lookups saturated the half-rate
+// integer pipe at 0.17 of the HBM roofline; the pair table with per-warp cp.async staging reached 0.22.
+// A variant of this kernel with 512 features per CTA, i.e. four times the codes in flight, was slower.)
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -28,6 +33,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tc.cuh"
 
 namespace rewb {
 namespace {
@@ -45,25 +51,19 @@ __device__ __forceinline__ int64_t map_col(const ColMap& cm, int64_t n) {
   return (within / cm.gran) * cm.gstride + (within % cm.gran) + seg * cm.seg_off;
 }
 
-// position of W[64 kb + kk][64 g + nn] inside the (g, kb) tile: k16 step, lane, word, nibble
-__device__ __forceinline__ void tile_pos(int kk, int nn, int& i, int& lane, int& word, int& nib) {
-  i = kk >> 4;
-  const int k16 = kk & 15, j = nn >> 3, c = nn & 7;
-  const int t = (k16 & 7) >> 1, r = (k16 & 1) + ((k16 >> 3) << 1);
-  lane = c * 4 + t;
-  word = j >> 1;
-  nib = (j & 1) * 4 + r;
+// byte offset of the pair byte of W[k][n] inside q
+__device__ __forceinline__ int64_t code_byte(int64_t k, int64_t n, int64_t KB) {
+  return (((n >> 7) * KB + (k >> 6)) * 128 + (n & 127)) * 32 + ((k & 63) >> 1);
 }
 
-// grid (N/64, K/64), 64 threads: thread r quantises row kb*64 + r of the group, then the tile is packed.
+// grid (N/64, K/64), 64 threads: thread r quantises the 64 features of group g for input row kb*64 + r.
 template <typename T>
-__global__ void __launch_bounds__(64) nf4_quantize_kernel(const T* src, int64_t ld, ColMap cm, uint4* q, float* sc, int64_t K,
-                                                          int64_t N) {
-  __shared__ uint32_t tile[4][32][4];  // [k16 step][lane][word]
+__global__ void __launch_bounds__(64) nf4_quantize_kernel(const T* src, int64_t ld, ColMap cm, uint8_t* q, float* sc,
+                                                          uint32_t* sc2, int64_t K, int64_t N) {
+  __shared__ uint8_t codes[64][64 + 4];  // [row][feature]
+  __shared__ float srow[64];
   const int g = blockIdx.x, kb = blockIdx.y, r = threadIdx.x;
   const int64_t k = (int64_t)kb * 64 + r;
-  for (int i = threadIdx.x; i < 4 * 32 * 4; i += 64) (&tile[0][0][0])[i] = 0u;
-  __syncthreads();
   float v[64];
   float absMax = 1e-10f;
 #pragma unroll 8
@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(64) nf4_quantize_kernel(const T* src, int64_t 
     absMax = fmaxf(absMax, fabsf(v[n]));
   }
   sc[(int64_t)g * K + k] = absMax;
+  srow[r] = absMax;
 #pragma unroll 4
   for (int n = 0; n < 64; ++n) {
     const float normalized = fminf(1.0f, fmaxf(-1.0f, v[n] / absMax));
@@ -85,201 +86,221 @@ __global__ void __launch_bounds__(64) nf4_quantize_kernel(const T* src, int64_t 
         code = i;
       }
     }
-    int i, lane, word, nib;
-    tile_pos(r, n, i, lane, word, nib);
-    atomicOr(&tile[i][lane][word], (uint32_t)code << (4 * nib));
+    codes[r][n] = (uint8_t)code;
   }
   __syncthreads();
-  const int KB = (int)(K / 64);
-  uint4* dst = q + ((int64_t)g * KB + kb) * 128;
-  for (int e = threadIdx.x; e < 128; e += 64) {
-    const uint32_t* w = &tile[e >> 5][e & 31][0];
-    dst[e] = make_uint4(w[0], w[1], w[2], w[3]);
+  const int64_t KB = K / 64;
+  // thread r now packs feature r: 32 bytes, two rows per byte
+  const int64_t n = (int64_t)g * 64 + r;
+  uint32_t words[8];
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    uint32_t u = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int j = 4 * w + b;
+      u |= (uint32_t)(codes[2 * j][r] | (codes[2 * j + 1][r] << 4)) << (8 * b);
+    }
+    words[w] = u;
   }
+  uint4* dst = reinterpret_cast<uint4*>(q + code_byte((int64_t)kb * 64, n, KB));
+  dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+  dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+  if (r < 32) sc2[(int64_t)g * (K / 2) + (int64_t)kb * 32 + r] = pack_bf16(srow[2 * r], srow[2 * r + 1]);
 }
 
 // dst (bf16, column-mapped) = level * scale, or codes_out (uint8 [K][N]) = code
-__global__ void __launch_bounds__(128) nf4_expand_kernel(const uint4* q, const float* sc, int64_t K, int64_t N, bf16* dst,
+__global__ void __launch_bounds__(128) nf4_expand_kernel(const uint8_t* q, const float* sc, int64_t K, int64_t N, bf16* dst,
                                                          int64_t ld, ColMap cm, uint8_t* codes_out) {
   const int g = blockIdx.x, kb = blockIdx.y;
-  const int KB = (int)(K / 64);
-  const uint32_t* tile = reinterpret_cast<const uint32_t*>(q + ((int64_t)g * KB + kb) * 128);
+  const int64_t KB = K / 64;
   for (int e = threadIdx.x; e < 64 * 64; e += 128) {
     const int kk = e >> 6, nn = e & 63;
-    int i, lane, word, nib;
-    tile_pos(kk, nn, i, lane, word, nib);
-    const int code = (tile[(i * 32 + lane) * 4 + word] >> (4 * nib)) & 15;
     const int64_t k = (int64_t)kb * 64 + kk, n = (int64_t)g * 64 + nn;
+    const int code = (q[code_byte(k, n, KB)] >> (4 * (kk & 1))) & 15;
     if (codes_out) codes_out[k * N + n] = (uint8_t)code;
     else dst[k * ld + map_col(cm, n)] = __float2bfloat16_rn(kNf4[code] * sc[(int64_t)g * K + k]);
   }
 }
 
-constexpr int GW = 8;      // warps per CTA
-constexpr int XS_LD = 72;  // bf16 elements per staged row: 144 bytes keeps ldmatrix free of bank conflicts
+constexpr int NT_STAGES = 8;
+constexpr int NT_XBYTES = 32 * 128;          // activations of a stage: 32 tokens x 64 k bf16 (128-byte swizzle)
+constexpr int NT_CBYTES = 128 * 32;          // codes of a stage: 128 features x 32 bytes
+constexpr int NT_SBYTES = 2 * 32 * 4;        // scale pairs of a stage: 2 groups x 32 pairs
+constexpr int NT_STAGE = 9 * 1024;           // stage stride (the activation tile must start 1024-byte aligned)
+constexpr int NT_TX = NT_XBYTES + NT_CBYTES + NT_SBYTES;
+constexpr int NT_DEQ = 8;                    // dequantiser warps
+constexpr int NT_THREADS = (2 + NT_DEQ) * 32;
+constexpr int NT_ABUF = 4;                   // weight-operand buffers in tensor memory
+constexpr int NT_TMEM_COLS = 256;            // D: columns 0-31; A buffer b: columns 32 + 32 b .. +31
+constexpr int NT_LUT_BYTES = 256 * 32 * 4;
+constexpr int NT_SMEM = NT_STAGES * NT_STAGE + NT_LUT_BYTES + 256 + 1024;
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 __device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
 
-template <int MT>
-__global__ void __launch_bounds__(GW * 32, 2) nf4_gemv_kernel(const uint4* __restrict__ q, const float* __restrict__ sc,
-                                                              const bf16* __restrict__ x, int64_t ldx, int M, int64_t K,
-                                                              int64_t N, int kb_per_cta, float* __restrict__ out) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  uint32_t* lut = reinterpret_cast<uint32_t*>(smem);                      // [256 byte values][32 lanes]
-  bf16* xs_all = reinterpret_cast<bf16*>(smem + 256 * 32 * 4);            // [GW][2][16*MT][XS_LD]
-  constexpr int XT = 16 * MT * XS_LD;                                     // elements of one staged tile
-  float* ss_all = reinterpret_cast<float*>(smem + 256 * 32 * 4 + (size_t)GW * 2 * XT * sizeof(bf16));  // [GW][2][64] scales
-  const int split = blockIdx.y, G = (int)(N / 64);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KB = (int)(K / 64);
-  const int kb0 = split * kb_per_cta, kb1 = min(KB, kb0 + kb_per_cta);
-  const int per = (max(kb1 - kb0, 0) + GW - 1) / GW;
-  const int wk0 = min(kb1, kb0 + warp * per), wk1 = min(kb1, wk0 + per);
+__global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ q,
+                                                            const uint32_t* __restrict__ sc2, int M, int64_t K, int64_t N,
+                                                            int kb_per_split, float* __restrict__ out, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* xs = smem;                                                    // [NT_STAGES]{activations | codes | scale pairs}
+  uint32_t* lut = reinterpret_cast<uint32_t*>(smem + NT_STAGES * NT_STAGE);   // [256 byte values][32 lanes]
+  uint64_t* x_full = reinterpret_cast<uint64_t*>(lut + 256 * 32);
+  uint64_t* x_empty = x_full + NT_STAGES;
+  uint64_t* a_full = x_empty + NT_STAGES;   // [NT_ABUF]
+  uint64_t* a_empty = a_full + NT_ABUF;     // [NT_ABUF]
+  uint64_t* d_full = a_empty + NT_ABUF;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
 
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int KB = (int)(K / 64);
+  const int kb0 = split * kb_per_split;
+  const int nkb = max(0, min(kb_per_split, KB - kb0));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NT_STAGES; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&x_empty[s], 1);
+    }
+    for (int b = 0; b < NT_ABUF; ++b) {
+      mbar_init(&a_full[b], 4);   // the four lane quarters
+      mbar_init(&a_empty[b], 1);
+    }
+    mbar_init(d_full, 1);
+    fence_barrier_init();
+    pdl_launch_dependents();
+  }
+  if (warp == 1) tc::alloc(tmem_slot, NT_TMEM_COLS);
   // pair table: entry e = (level[e & 15], level[e >> 4]) as bf16x2, one copy per lane (bank = lane)
-  for (int idx = threadIdx.x; idx < 256 * 8; idx += GW * 32) {  // 16 bytes = four lanes' copies per store
+  for (int idx = threadIdx.x; idx < 256 * 8; idx += NT_THREADS) {
     const int e = idx >> 3;
     const uint32_t v = (uint32_t)kNf4Bf16[e & 15] | ((uint32_t)kNf4Bf16[e >> 4] << 16);
     reinterpret_cast<uint4*>(lut)[idx] = make_uint4(v, v, v, v);
   }
-  bool first = true;
-  // a CTA walks the column groups blockIdx.x, blockIdx.x + gridDim.x, ...: the table is built once
-  for (int g = blockIdx.x; g < G; g += gridDim.x) {
-  const uint4* qp = q + ((int64_t)g * KB) * 128 + lane;
-  uint4 qv[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) qv[i] = make_uint4(0, 0, 0, 0);
-  if (wk0 < wk1) {  // the weights do not depend on the previous kernel: fetch before waiting for it
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qv[i] = qp[(int64_t)wk0 * 128 + i * 32];
-  }
-  if (first) {
-    __syncthreads();
-    pdl_launch_dependents();
-    pdl_wait();
-    first = false;
-  }
+  tc::fence_before();
+  __syncthreads();
+  tc::fence_after();
+  const uint32_t tmem_base = *tmem_slot;
 
-  float acc[MT][8][4];
-#pragma unroll
-  for (int a = 0; a < MT; ++a)
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[a][j][e] = 0.f;
-
-  bf16* xs = xs_all + (size_t)warp * 2 * XT;
-  float* ss = ss_all + (size_t)warp * 2 * 64;
-  // this warp copies its own activation tile (16*MT rows of 128 bytes) and its group's 64 scales
-  auto stage = [&](int kb, int buf) {
-#pragma unroll
-    for (int e = lane; e < 16 * MT * 8; e += 32) {
-      const int row = e >> 3, seg = e & 7;
-      const bf16* src = x + (int64_t)min(row, M - 1) * ldx + (int64_t)kb * 64 + seg * 8;
-      cp_async16(smem_u32(xs + (size_t)buf * XT + row * XS_LD + seg * 8), src, row < M ? 16 : 0);  // rows >= M: zeros
-    }
-    if (lane < 16) cp_async16(smem_u32(ss + buf * 64 + lane * 4), sc + (int64_t)g * K + (int64_t)kb * 64 + lane * 4, 16);
-  };
-  if (wk0 < wk1) stage(wk0, 0);
-  cp_async_commit();
-  const unsigned char* lut_bytes = reinterpret_cast<const unsigned char*>(lut);
-  const uint32_t lane4 = (uint32_t)lane * 4;
-  const int t = lane & 3;
-  for (int kb = wk0; kb < wk1; ++kb) {
-    const int buf = (kb - wk0) & 1;
-    const bool more = kb + 1 < wk1;
-    if (more) stage(kb + 1, buf ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();  // everything but the tile just requested has landed
-    __syncwarp();
-    const bf16* xt = xs + (size_t)buf * XT;
-    // scales for the four k16 steps: rows 2t, 2t+1 and 2t+8, 2t+9 as bf16 pairs
-    uint32_t spair[4][2];
-    {
-      const float* sp = ss + buf * 64 + 2 * t;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 a = *reinterpret_cast<const float2*>(sp + 16 * i);
-        const float2 b = *reinterpret_cast<const float2*>(sp + 16 * i + 8);
-        spair[i][0] = pack_bf16(a.x, a.y);
-        spair[i][1] = pack_bf16(b.x, b.y);
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX);
+      const uint64_t pol_x = policy_evict_last();
+      // a stage = the activation tile (tensor copy) + this tile's 4 KB of codes + the scale pairs of
+      // its two 64-feature groups (plain bulk copies); eight stages deep, so up to 32 KB of codes per
+      // CTA are in flight without costing a register.  Codes and scales do not depend on the previous
+      // kernel: the first ring-full is requested before waiting for it.
+      const int64_t g0 = ((int64_t)tile * 128) >> 6, G = N >> 6;
+      auto load_weights = [&](int kb, int s) {
+        uint8_t* st = xs + s * NT_STAGE;
+        mbar_expect_tx(&x_full[s], NT_TX);
+        bulk_load_1d(st + NT_XBYTES, q + ((int64_t)tile * KB + kb0 + kb) * NT_CBYTES, NT_CBYTES, &x_full[s]);
+        for (int h = 0; h < 2; ++h) {
+          const int64_t g = min(g0 + h, G - 1);  // a half tile past N re-reads the last group (its lanes are never stored)
+          bulk_load_1d(st + NT_XBYTES + NT_CBYTES + h * 128, sc2 + g * (K / 2) + (int64_t)(kb0 + kb) * 32, 128, &x_full[s]);
+        }
+      };
+      const int pre = min(NT_STAGES, nkb);
+      for (int kb = 0; kb < pre; ++kb) load_weights(kb, kb);
+      pdl_wait();  // the activations come from the previous kernel
+      for (int kb = 0; kb < pre; ++kb) tma_load_2d_hint(xs + kb * NT_STAGE, &tmX, &x_full[kb], (kb0 + kb) * 64, 0, pol_x);
+      for (int kb = pre; kb < nkb; ++kb) {
+        const int s = kb % NT_STAGES;
+        if (!mbar_wait(&x_empty[s], ((kb / NT_STAGES) - 1) & 1, status)) break;
+        load_weights(kb, s);
+        tma_load_2d_hint(xs + s * NT_STAGE, &tmX, &x_full[s], (kb0 + kb) * 64, 0, pol_x);
       }
     }
+  } else if (warp == 1) {
+    if (lane == 0 && nkb > 0) {
+      // instruction descriptor: D f32, A and B bf16, both K-major (A lives in tensor memory), N = 32, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(32 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t xs_addr = smem_u32(xs);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int p = kb % NT_ABUF, s = kb % NT_STAGES;
+        ok = mbar_wait(&a_full[p], (kb / NT_ABUF) & 1, status) && mbar_wait(&x_full[s], (kb / NT_STAGES) & 1, status);
+        if (!ok) break;
+        tc::fence_after();
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t af[MT][4];
-#pragma unroll
-      for (int a = 0; a < MT; ++a) {
-        const int arow = a * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, acol = 16 * i + (lane >> 4) * 8;
-        ldmatrix_x4(af[a][0], af[a][1], af[a][2], af[a][3], smem_u32(xt + arow * XS_LD + acol));
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t db = tc::smem_desc(xs_addr + s * NT_STAGE + kk * 32, 16, 1024);
+          tc::umma_bf16_ta(tmem_base, tmem_base + 32 + p * 32 + kk * 8, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc::commit(&x_empty[s]);
+        tc::commit(&a_empty[p]);
       }
-      const uint32_t words[4] = {qv[i].x, qv[i].y, qv[i].z, qv[i].w};
-      // the codes of this step are in `words`: refill the register with the same step of the next block
-      if (more) qv[i] = qp[(int64_t)(kb + 1) * 128 + i * 32];
+      if (ok) tc::commit(d_full);
+    }
+  } else {
+    // ---------------- dequantisers: lane quarter = warp % 4 (the TMEM lanes a warp may touch), parity = which blocks
+    const int dw = warp - 2, p = dw >> 2, quarter = warp & 3;
+    const int64_t n_feat = (int64_t)tile * 128 + quarter * 32 + lane;
+    const bool valid = (int64_t)tile * 128 + quarter * 32 < N;  // N % 64 == 0: a quarter is all in or all out
+    const uint8_t* lut_bytes = reinterpret_cast<const uint8_t*>(lut);
+    const uint32_t lane4 = (uint32_t)lane * 4;
+    const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + 32;
+    bool ok = true;
+    for (int kb = p; kb < nkb; kb += 2) {
+      const int s = kb % NT_STAGES, ab = kb % NT_ABUF, use = kb / NT_ABUF;
+      if (ok) ok = mbar_wait(&x_full[s], (kb / NT_STAGES) & 1, status);
+      const uint8_t* st = xs + s * NT_STAGE;
+      const uint4* cp = reinterpret_cast<const uint4*>(st + NT_XBYTES + (quarter * 32 + lane) * 32);
+      const uint4 qa = cp[0], qb = cp[1];
+      const uint4* sp4 = reinterpret_cast<const uint4*>(st + NT_XBYTES + NT_CBYTES + (quarter >> 1) * 128);
+      const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+      uint32_t r[32];
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < 8; ++w) {
+        const uint4 s4 = sp4[w];  // the same address for every lane: a broadcast
         const uint32_t u = words[w];
-        // byte b of the word = one B register.  Pair e of this lane's table copy sits at byte offset
-        // e * 128 + lane * 4: a shift, one (x & mask) | lane4, one LDS.
+        // pair e of this lane's table copy sits at byte offset e * 128 + lane * 4
         const uint32_t o0 = ((u << 7) & 0x7F80u) | lane4, o1 = ((u >> 1) & 0x7F80u) | lane4;
         const uint32_t o2 = ((u >> 9) & 0x7F80u) | lane4, o3 = ((u >> 17) & 0x7F80u) | lane4;
-        const uint32_t b00 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o0), spair[i][0]);
-        const uint32_t b01 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o1), spair[i][1]);
-        const uint32_t b10 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o2), spair[i][0]);
-        const uint32_t b11 = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o3), spair[i][1]);
+        r[4 * w + 0] = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o0), s4.x);
+        r[4 * w + 1] = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o1), s4.y);
+        r[4 * w + 2] = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o2), s4.z);
+        r[4 * w + 3] = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o3), s4.w);
+      }
+      if (use >= 1 && ok) {  // the tensor core must have consumed this buffer's previous contents
+        ok = mbar_wait(&a_empty[ab], (use - 1) & 1, status);
+        tc::fence_after();
+      }
+      if (valid) tc::st32(a_lane + ab * 32, r);
+      tc::fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_full[ab]);
+    }
+    if (p == 0) {
+      // ---------------- epilogue: D[feature = lane][token = column] -> out[split][token][feature]
+      uint32_t r[32];
 #pragma unroll
-        for (int a = 0; a < MT; ++a) {
-          mma_bf16_16816(acc[a][2 * w], af[a], b00, b01);
-          mma_bf16_16816(acc[a][2 * w + 1], af[a], b10, b11);
-        }
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
+      if (nkb > 0) {
+        ok = mbar_wait(d_full, 0, status) && ok;
+        tc::fence_after();
+        if (ok) tc::ld32(tmem_base + ((uint32_t)(quarter * 32) << 16), r);
+      }
+      pdl_wait();  // the slab buffer may still be read by the previous kernel
+      if (valid && ok) {
+        float* op = out + (int64_t)split * M * N + n_feat;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < M) op[(int64_t)j * N] = __uint_as_float(r[j]);
       }
     }
-    __syncwarp();  // all lanes are done with this tile before it is overwritten two iterations on
   }
-  cp_async_wait<0>();
-  __syncthreads();  // every warp is done with its staging area: reuse it for the reduction
-  float* red = reinterpret_cast<float*>(xs_all);  // [GW][16*MT][64]
-  const int c = lane >> 2;
-#pragma unroll
-  for (int a = 0; a < MT; ++a)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float* rp = red + ((size_t)warp * 16 * MT + a * 16 + c) * 64 + 8 * j + 2 * t;
-      *reinterpret_cast<float2*>(rp) = make_float2(acc[a][j][0], acc[a][j][1]);
-      *reinterpret_cast<float2*>(rp + 8 * 64) = make_float2(acc[a][j][2], acc[a][j][3]);
-    }
+  tc::fence_before();
   __syncthreads();
-  float* op = out + (int64_t)split * M * N + (int64_t)g * 64;
-  for (int e = threadIdx.x; e < 16 * MT * 16; e += GW * 32) {  // float4 per thread
-    const int m = e >> 4, n4 = (e & 15) * 4;
-    if (m >= M) continue;
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int w = 0; w < GW; ++w) {
-      const float4 v = *reinterpret_cast<const float4*>(red + ((size_t)w * 16 * MT + m) * 64 + n4);
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-    }
-    *reinterpret_cast<float4*>(op + (int64_t)m * N + n4) = s;
+  if (warp == 1) {
+    tc::fence_after();
+    tc::dealloc(tmem_base, NT_TMEM_COLS);
   }
-  __syncthreads();  // the reduction area is staging area again
-  }  // column groups
-}
-
-template <int MT>
-constexpr size_t gemv_smem() {
-  return 256 * 32 * 4 + (size_t)GW * 2 * 16 * MT * XS_LD * sizeof(bf16) + (size_t)GW * 2 * 64 * sizeof(float);
 }
 
 }  // namespace
@@ -289,24 +310,29 @@ int nf4_alloc(Ctx* c, int64_t K, int64_t N, Nf4W* w) {
   RB_REQUIRE(K > 0 && N > 0 && K % 64 == 0 && N % 64 == 0, "NF4 weights need in and out features that are multiples of 64");
   w->K = K;
   w->N = N;
-  RB_CUDA(cudaMalloc((void**)&w->q, (size_t)K * N / 2));
+  const int64_t tiles = (N + 127) / 128;
+  RB_CUDA(cudaMalloc((void**)&w->q, (size_t)tiles * 128 * K / 2));
+  RB_CUDA(cudaMemset(w->q, 0x77, (size_t)tiles * 128 * K / 2));  // code 7 = 0.0 for the features past N
   RB_CUDA(cudaMalloc((void**)&w->sc, (size_t)K * (N / 64) * sizeof(float)));
+  RB_CUDA(cudaMalloc((void**)&w->sc2, (size_t)(K / 2) * (N / 64) * sizeof(uint32_t)));
   return REWB200_OK;
 }
 
 void nf4_free(Nf4W* w) {
   if (w->q) cudaFree(w->q);
   if (w->sc) cudaFree(w->sc);
+  if (w->sc2) cudaFree(w->sc2);
   w->q = nullptr;
   w->sc = nullptr;
+  w->sc2 = nullptr;
 }
 
 int nf4_quantize_launch(Ctx* c, const void* src, int src_dtype, int64_t ld, ColMap cm, const Nf4W& w) {
   const dim3 grid((unsigned)(w.N / 64), (unsigned)(w.K / 64));
   if (src_dtype == REWB200_BF16)
-    nf4_quantize_kernel<bf16><<<grid, 64, 0, c->stream>>>((const bf16*)src, ld, cm, w.q, w.sc, w.K, w.N);
+    nf4_quantize_kernel<bf16><<<grid, 64, 0, c->stream>>>((const bf16*)src, ld, cm, w.q, w.sc, w.sc2, w.K, w.N);
   else if (src_dtype == REWB200_F32)
-    nf4_quantize_kernel<float><<<grid, 64, 0, c->stream>>>((const float*)src, ld, cm, w.q, w.sc, w.K, w.N);
+    nf4_quantize_kernel<float><<<grid, 64, 0, c->stream>>>((const float*)src, ld, cm, w.q, w.sc, w.sc2, w.K, w.N);
   else
     return fail("nf4 quantise: weights must be f32 or bf16");
   RB_CUDA(cudaGetLastError());
@@ -331,14 +357,13 @@ int nf4_codes_launch(Ctx* c, const Nf4W& w, uint8_t* codes) {
   return REWB200_OK;
 }
 
-// CTAs along K: each of a CTA's 8 warps should own about 4 blocks of 64 rows, but the grid should
-// still cover the GPU about twice.  (Fewer, longer-lived CTAs walking several column groups measured
-// slower: the drain and refill of the per-warp pipeline at every group costs more than the table build.)
+// CTAs along K: two CTAs fit an SM; fill those slots once (a second, partial wave costs a whole CTA
+// lifetime) and keep at least 4 blocks of 64 rows per CTA.
 int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N) {
-  const int groups = (int)(N / 64), KB = (int)(K / 64);
-  int ks = std::max(1, KB / (GW * 4));
-  while (ks < KB / GW && groups * ks < 2 * c->sm_count) ++ks;
-  return std::max(1, std::min(ks, KB));
+  const int tiles = (int)((N + 127) / 128), KB = (int)(K / 64), slots = 2 * c->sm_count;
+  int ks = std::max(1, slots / tiles);
+  ks = std::min(ks, std::max(1, KB / 4));
+  return std::max(1, std::min(ks, 16));
 }
 
 int nf4_gemv_launch(Ctx* c, const Nf4W& w, const bf16* x, int64_t ldx, int64_t M, int ksplit, float* out) {
@@ -347,20 +372,17 @@ int nf4_gemv_launch(Ctx* c, const Nf4W& w, const bf16* x, int64_t ldx, int64_t M
   const int KB = (int)(w.K / 64);
   ksplit = std::max(1, std::min(ksplit, KB));
   const int per = (KB + ksplit - 1) / ksplit;
-  // one CTA per (column group, K slice); the kernel also accepts fewer CTAs than groups
-  const dim3 grid((unsigned)(w.N / 64), (unsigned)ksplit);
+  CUtensorMap tmX;
+  RB_TRY(make_tmap_2d_bf16(&tmX, x, (uint64_t)w.K, (uint64_t)M, (uint64_t)ldx * 2, 64, 32));
+  const dim3 grid((unsigned)((w.N + 127) / 128), (unsigned)ksplit);
   static bool attr_set = false;
   if (!attr_set) {
-    RB_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemv_smem<1>()));
-    RB_CUDA(cudaFuncSetAttribute(nf4_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemv_smem<2>()));
+    RB_CUDA(cudaFuncSetAttribute(nf4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, NT_SMEM));
+    RB_CUDA(cudaFuncSetAttribute(nf4_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     attr_set = true;
   }
-  if (M <= 16)
-    RB_CUDA(launch_k(nf4_gemv_kernel<1>, grid, dim3(GW * 32), gemv_smem<1>(), c->stream, c->use_pdl, (const uint4*)w.q,
-                     (const float*)w.sc, x, ldx, (int)M, w.K, w.N, per, out));
-  else
-    RB_CUDA(launch_k(nf4_gemv_kernel<2>, grid, dim3(GW * 32), gemv_smem<2>(), c->stream, c->use_pdl, (const uint4*)w.q,
-                     (const float*)w.sc, x, ldx, (int)M, w.K, w.N, per, out));
+  RB_CUDA(launch_k(nf4_tc_kernel, grid, dim3(NT_THREADS), (size_t)NT_SMEM, c->stream, c->use_pdl, tmX, (const uint8_t*)w.q,
+                   (const uint32_t*)w.sc2, (int)M, w.K, w.N, per, out, c->d_status));
   ++g_launch_total;
   return REWB200_OK;
 }
