@@ -43,7 +43,7 @@ class ModelConfig:
         return self.n_routed > 0 and not (self.first_dense > 0 and l == 0)
 
 
-# BASELINE configurations (shapes only; weights are synthetic).
+# Benchmark configurations (shapes only; weights are synthetic).
 def tiny_llama(**kw):
     return ModelConfig(vocab=1024, d_model=256, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=32, ffn=688,
                        max_seq=128, theta=10000.0, eps=1e-5, **kw)

@@ -22,7 +22,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def tiny_generate():
-    """BASELINE config 1: tiny Llama, f32, prompt 32 ids (seed 1), 32 greedy tokens."""
+    """The tiny fp32 configuration: tiny Llama, f32, prompt 32 ids (seed 1), 32 greedy tokens."""
     out = {}
     prompt = np.random.default_rng(1).integers(0, 1024, size=(1, 32)).astype(np.int32)
     out["prompt"] = prompt

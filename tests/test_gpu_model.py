@@ -23,7 +23,7 @@ def rb():
 @pytest.mark.parametrize("norm,mask", [("rms", "as_written"), ("rms", "standard"), ("layernorm", "as_written"),
                                        ("layernorm", "standard")])
 def test_tiny_llama_fp32_generate_token_exact(rb, norm, mask):
-    """BASELINE config 1: greedy ids identical, final logits rel-L2 <= 1e-5."""
+    """The tiny fp32 Llama configuration: greedy ids identical, final logits rel-L2 <= 1e-5."""
     z = np.load(os.path.join(GOLD, "tiny_llama_generate.npz"))
     cfg = W.tiny_llama(norm_kind=0 if norm == "rms" else 1, mask_kind=0 if mask == "as_written" else 1)
     model = rb.CausalLM(cfg).load(W.init_weights(cfg, seed=0))

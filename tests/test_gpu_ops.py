@@ -175,7 +175,7 @@ def test_attention_bf16_prefill(rb, orc, B, nh, kvh, S, hd, mode):
 
 
 def test_attention_config2_bf16_decode_shape(rb, orc):
-    """BASELINE config 2, decode: batch 8, 32 q / 8 kv heads, head_dim 128, cache 4096 (checked on 2 sequences)."""
+    """The attention-operator configuration, decode: batch 8, 32 q / 8 kv heads, head_dim 128, cache 4096 (checked on 2 sequences)."""
     from rew_b200 import _lib
     rng = np.random.default_rng(42)
     B, nh, kvh, L, hd = 8, 32, 8, 4096, 128
