@@ -52,6 +52,8 @@ WORKLOADS = {
     # the l8 decoder with its block Linears held as NF4 codes (weight-only, QLoRA's frozen base weights)
     "l8_b32_nf4": dict(model="llama3_8b", batch=32, prompt=512, weight_quant=1),
     "l8_b1_nf4": dict(model="llama3_8b", batch=1, prompt=512, weight_quant=1),
+    # the attention operator alone: batch 8, 32 query / 8 kv heads, head_dim 128, 4096 positions
+    "attn_op": dict(model=None, batch=8, prompt=4096),
 }
 
 
@@ -217,6 +219,51 @@ def cpu_baseline_leg(args, wl):
         return {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %r" % (e,)}
 
 
+def run_attention_op(args, rank, local_rank):
+    """The attention operator of the decoder alone (bf16, grouped-query, conventional causal mask): a 4096-token
+    prefill (tensor roofline) and one decode query over a 4096-entry cache (HBM roofline), device-timed."""
+    if rank != 0:
+        return
+    import ctypes as C
+    from rew_b200 import _lib, api
+    _lib.init(local_rank)
+    L = _lib.lib()
+    B, nh, kvh, hd, S = 8, 32, 8, 128, 4096
+    rng = np.random.default_rng(0)
+    T = api.Tensor.from_host
+    k = T(rng.standard_normal((B, kvh, S, hd)).astype(np.float32), dtype=_lib.BF16)
+    v = T(rng.standard_normal((B, kvh, S, hd)).astype(np.float32), dtype=_lib.BF16)
+    out = {}
+    for name, sq in (("prefill", S), ("decode", 1)):
+        q = T(rng.standard_normal((B, nh, sq, hd)).astype(np.float32), dtype=_lib.BF16)
+        ms, o = C.c_float(), C.c_void_p()
+        _lib.check(L.rewb200_gqa_attention_timed(q._h, k._h, v._h, 1 if sq > 1 else 0, 1, max(3, args.steps // 8), C.byref(ms),
+                                                 C.byref(o)))
+        api.Tensor(o).release()
+        q.release()
+        out[name] = ms.value
+    hbm, which = measured_peaks()
+    tf_peak = 1608.7
+    pj = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pj):
+        with open(pj) as f:
+            tf_peak = float(json.load(f).get("bf16_tflops", tf_peak))
+    flops = 4.0 * B * nh * hd * S * S / 2          # causal: half of 2 GEMMs of 2*S*S*hd per head
+    kv_bytes = 2.0 * B * kvh * S * hd * 2 + 2.0 * B * nh * hd * 2
+    tfs = flops / (out["prefill"] * 1e-3) / 1e12
+    gbs = kv_bytes / (out["decode"] * 1e-3) / 1e9
+    line = {"metric": "attention_op", "value": tfs, "unit": "TFLOP/s (causal prefill)", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": out["prefill"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "attn_op", "batch": B, "q_heads": nh, "kv_heads": kvh, "head_dim": hd, "positions": S,
+                       "l2": "K and V (134 MB) exceed the 126 MB L2"},
+            "prefill": {"ms": out["prefill"], "tflops": tfs, "frac_of_bf16_peak": tfs / tf_peak, "flops": flops},
+            "decode": {"ms": out["decode"], "gbs": gbs, "frac_of_hbm_peak": gbs / hbm, "bytes": kv_bytes},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None,
+                         "kernel": "attn_decode_kernel<128>", "peak_source": which}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -232,6 +279,9 @@ def main():
     wl = WORKLOADS[args.workload]
     rank, local_rank, world = dist_env()
 
+    if args.workload == "attn_op":
+        run_attention_op(args, rank, local_rank)
+        return
     if args.impl == "reference":
         run_reference(args, wl, rank)
         return

@@ -122,6 +122,10 @@ int rewb200_rope(const rewb200_buffer* x, const rewb200_buffer* cos_t, const rew
  * as written (attention.nim:18-34), 1 = conventional causal. */
 int rewb200_gqa_attention(const rewb200_buffer* q, const rewb200_buffer* k, const rewb200_buffer* v,
                           int causal, int mask_kind, rewb200_buffer** out);
+/* Measurement aid: the same call, then the attention launch `iters` more times
+ * between two CUDA events; *ms_per_call = their mean device time. */
+int rewb200_gqa_attention_timed(const rewb200_buffer* q, const rewb200_buffer* k, const rewb200_buffer* v,
+                                int causal, int mask_kind, int iters, float* ms_per_call, rewb200_buffer** out);
 /* GatedFeedForward.forward, src/rew/nn/gated_ffn.nim:46-67.  x [N,d]. */
 int rewb200_swiglu_ffn(const rewb200_buffer* x, const rewb200_buffer* gate_w, const rewb200_buffer* gate_b,
                        const rewb200_buffer* up_w, const rewb200_buffer* up_b, const rewb200_buffer* down_w,

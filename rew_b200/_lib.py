@@ -59,6 +59,7 @@ SIGNATURES = {
     "rewb200_rope_tables": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_double, PP, PP]),
     "rewb200_rope": (C.c_int, [P, P, P, C.c_int64, PP]),
     "rewb200_gqa_attention": (C.c_int, [P, P, P, C.c_int, C.c_int, PP]),
+    "rewb200_gqa_attention_timed": (C.c_int, [P, P, P, C.c_int, C.c_int, C.c_int, F32P, PP]),
     "rewb200_swiglu_ffn": (C.c_int, [P, P, P, P, P, P, P, PP]),
     "rewb200_embed_gather": (C.c_int, [P, P, PP]),
     "rewb200_moe_route": (C.c_int, [P, P, P, C.c_int, PP, PP]),

@@ -544,7 +544,8 @@ int decode_splits(Ctx* c, int64_t B, int kvh) {
   }
   const int64_t base = B * kvh;
   if (base >= c->sm_count) return 1;
-  int64_t s = (2 * c->sm_count + base - 1) / base;
+  // two CTAs fit an SM: fill those slots once (rounding up would leave a short second wave)
+  const int64_t s = std::max<int64_t>(1, 2 * c->sm_count / base);
   return (int)std::min<int64_t>(s, 16);
 }
 

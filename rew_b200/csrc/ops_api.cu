@@ -164,8 +164,8 @@ int rewb200_rope(const rewb200_buffer* x, const rewb200_buffer* cos_t, const rew
   return REWB200_OK;
 }
 
-int rewb200_gqa_attention(const rewb200_buffer* q, const rewb200_buffer* k, const rewb200_buffer* v, int causal,
-                          int mask_kind, rewb200_buffer** out) {
+static int gqa_attention_impl(const rewb200_buffer* q, const rewb200_buffer* k, const rewb200_buffer* v, int causal,
+                              int mask_kind, rewb200_buffer** out, int iters, float* ms_per_call) {
   RB_REQUIRE(q && k && v && out, "scaledDotProductAttention: NULL argument");
   RB_REQUIRE(q->ndims == 4 && k->ndims == 4 && v->ndims == 4,
              "scaledDotProductAttention: operands must be [batch, heads, len, headDim]");
@@ -219,8 +219,34 @@ int rewb200_gqa_attention(const rewb200_buffer* q, const rewb200_buffer* k, cons
     a.scratch = scratch;
   }
   int st = attn_launch(c, a);
+  if (st == REWB200_OK && iters > 0 && ms_per_call) {
+    // measurement aid: the same launch `iters` more times between two CUDA events
+    cudaEvent_t e0, e1;
+    RB_CUDA(cudaEventCreate(&e0));
+    RB_CUDA(cudaEventCreate(&e1));
+    RB_CUDA(cudaEventRecord(e0, c->stream));
+    for (int i = 0; i < iters && st == REWB200_OK; ++i) st = attn_launch(c, a);
+    RB_CUDA(cudaEventRecord(e1, c->stream));
+    RB_CUDA(cudaStreamSynchronize(c->stream));
+    float ms = 0.f;
+    RB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    *ms_per_call = ms / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  }
   if (scratch) cudaFreeAsync(scratch, c->stream);
   return st;
+}
+
+int rewb200_gqa_attention(const rewb200_buffer* q, const rewb200_buffer* k, const rewb200_buffer* v, int causal,
+                          int mask_kind, rewb200_buffer** out) {
+  return gqa_attention_impl(q, k, v, causal, mask_kind, out, 0, nullptr);
+}
+
+int rewb200_gqa_attention_timed(const rewb200_buffer* q, const rewb200_buffer* k, const rewb200_buffer* v, int causal,
+                                int mask_kind, int iters, float* ms_per_call, rewb200_buffer** out) {
+  RB_REQUIRE(iters > 0 && ms_per_call, "rewb200_gqa_attention_timed: iters must be positive and ms_per_call non-NULL");
+  return gqa_attention_impl(q, k, v, causal, mask_kind, out, iters, ms_per_call);
 }
 
 int rewb200_swiglu_ffn(const rewb200_buffer* x, const rewb200_buffer* gate_w, const rewb200_buffer* gate_b,
