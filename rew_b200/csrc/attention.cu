@@ -22,6 +22,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tc.cuh"
 
 namespace rewb {
 
@@ -537,6 +538,242 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill attention on the 5th-generation tensor core (head_dim 128, conventional causal or no mask).
+// CTA = 128 queries of one head; thread i of the four softmax warps owns query row i = TMEM lane i.
+//   warp 0   TMA: K and V tiles of 128 keys (one stage each; four 64x64 boxes, 128-byte swizzle)
+//   warp 1   one thread issues S = Q K^T (8 x tcgen05.mma, both operands K-major in shared memory,
+//            S[128 queries][128 keys] f32 in TMEM) and O += P V (8 x tcgen05.mma, A = P read from
+//            TMEM as bf16, B = V MN-major from shared memory, O[128][128] f32 in TMEM)
+//   warps 2-5 online softmax in the exp2 domain: read S twice (row maximum, then probabilities),
+//            write P over the columns of S already consumed, rescale O only when some row's maximum
+//            moved; at the end normalise O and store bf16 rows
+// 256 TMEM columns and 96 KB of shared memory per CTA: two CTAs per SM, so one CTA's softmax runs
+// under the other's matrix products.  Every wait is bounded.
+namespace fa {
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int TILE_BYTES = BKV * HD * 2;            // 32 KB: [hd half][128 rows][64 elements]
+constexpr int SMEM = 3 * TILE_BYTES + 256 + 1024;   // Q, K, V + barriers + alignment slack
+constexpr int THREADS = 6 * 32;
+}  // namespace fa
+
+__global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                                      const __grid_constant__ CUtensorMap tmV, AttnDev a) {
+  using namespace fa;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sV = smem + 2 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES);
+  uint64_t *k_full = bars, *k_empty = bars + 1, *v_full = bars + 2, *v_empty = bars + 3, *s_full = bars + 4, *p_full = bars + 5,
+           *o_done = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;   // the long (late) query tiles first
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh_idx = head / a.group;
+  const int q0 = qt * BQ;
+  if (threadIdx.x == 0) {
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);   // the four softmax warps
+    mbar_init(o_done, 1);
+    fence_barrier_init();
+    pdl_launch_dependents();
+  }
+  if (warp == 1) tc::alloc(tmem_slot, 256);
+  tc::fence_before();
+  __syncthreads();
+  tc::fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // q, k, v and positions come from the previous kernels
+
+  const int kv_len = kv_len_of(a, b);
+  const int ctx = kv_len - a.S;
+  // keys this query tile can see: all of them, or up to its last query's position
+  const int last_q = min(a.S, q0 + BQ) - 1;
+  const int kv_end = a.causal ? min(kv_len, last_q + ctx + 1) : kv_len;
+  const int ntiles = (kv_end + BKV - 1) / BKV;
+
+  if (warp >= 2) {
+    // stage Q: 128 rows x 256 bytes into [hd half][row][64 elements] with the 128-byte swizzle TMA would apply
+    const int r = threadIdx.x - 64;
+    const int qi = q0 + r;
+    const bf16* qp = reinterpret_cast<const bf16*>(a.q) + (int64_t)b * a.q_sb + (int64_t)min(qi, a.S - 1) * a.q_ss + (int64_t)head * a.q_sh;
+#pragma unroll
+    for (int ch = 0; ch < 16; ++ch) {  // sixteen 16-byte chunks of the row
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (qi < a.S) v = *reinterpret_cast<const uint4*>(qp + ch * 8);
+      *reinterpret_cast<uint4*>(sQ + (ch >> 3) * (TILE_BYTES / 2) + swz128((uint32_t)r, (uint32_t)(ch & 7))) = v;
+    }
+    fence_proxy_async();  // the tensor core reads these bytes through the async proxy
+  }
+  __syncthreads();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      bool ok = true;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        for (int kv = 0; kv < 2 && ok; ++kv) {  // K first, then V
+          uint64_t* full = kv ? v_full : k_full;
+          uint64_t* empty = kv ? v_empty : k_empty;
+          if (j > 0 && !mbar_wait(empty, (j - 1) & 1, a.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* dst = kv ? sV : sK;
+          mbar_expect_tx(full, TILE_BYTES);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int t = min(j * BKV + half * 64, kv_len - 1) & ~63;   // a half tile past the end re-reads a valid page
+            const int row = (int)kv_row(a, b, kvh_idx, t);
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_2d(dst + c * (TILE_BYTES / 2) + half * 8192, kv ? &tmV : &tmK, full, c * 64, row);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // D f32, A/B bf16, M = 128, N = 128; QK^T: both K-major; PV: A from TMEM (K-major), B = V MN-major
+      const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t idesc_pv = idesc_qk | (1u << 16);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool ok = true;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        ok = mbar_wait(k_full, j & 1, a.status);
+        if (!ok) break;
+        tc::fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // head_dim in steps of 16: two 64-element halves of four steps
+          const uint32_t off = (kk >> 2) * (TILE_BYTES / 2) + (kk & 3) * 32;
+          tc::umma_bf16_ss(tmem_base, tc::smem_desc(q_addr + off, 16, 1024), tc::smem_desc(k_addr + off, 16, 1024), idesc_qk,
+                           kk > 0 ? 1u : 0u);
+        }
+        tc::commit(s_full);
+        tc::commit(k_empty);
+        ok = mbar_wait(p_full, j & 1, a.status) && mbar_wait(v_full, j & 1, a.status);
+        if (!ok) break;
+        tc::fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)  // keys in steps of 16 = two 8-row swizzle atoms
+          tc::umma_bf16_ta(tmem_base + 128, tmem_base + kk * 8, tc::smem_desc(v_addr + kk * 2048, TILE_BYTES / 2, 1024), idesc_pv,
+                           (j > 0 || kk > 0) ? 1u : 0u);
+        tc::commit(o_done);
+        tc::commit(v_empty);
+      }
+    }
+  } else {
+    // ---------------- softmax warps: lane quarter = warp % 4, query row = quarter * 32 + lane
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int qi = q0 + row;
+    const int qlim = a.causal ? qi + ctx : 0x7fffffff;   // last visible key
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const float sl2 = a.scale * 1.4426950408889634f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      if (ok) ok = mbar_wait(s_full, j & 1, a.status);
+      __syncwarp();  // the tensor-memory loads below are warp-collective
+      tc::fence_after();
+      const int k0 = j * BKV;
+      const bool edge = (k0 + BKV - 1 > qlim) || (k0 + BKV > kv_len);   // some key of this tile is masked for this row
+      uint32_t r[32];
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tc::ld32(lane_addr + c * 32, r);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int key = k0 + c * 32 + e;
+          const float sv = (edge && (key > qlim || key >= kv_len)) ? -INFINITY : __uint_as_float(r[e]) * sl2;
+          mx = fmaxf(mx, sv);
+        }
+      }
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = exp2f(m - m_use);   // 0 on the first tile (m = -inf)
+      float lsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        tc::ld32(lane_addr + c * 32, r);
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const int key = k0 + c * 32 + e;
+          const float s0 = (edge && (key > qlim || key >= kv_len)) ? -INFINITY : __uint_as_float(r[e]) * sl2;
+          const float s1 = (edge && (key + 1 > qlim || key + 1 >= kv_len)) ? -INFINITY : __uint_as_float(r[e + 1]) * sl2;
+          const float p0 = exp2f(s0 - m_use), p1 = exp2f(s1 - m_use);
+          lsum += p0 + p1;
+          pk[e >> 1] = pack_bf16(p0, p1);
+        }
+        // P (bf16 pairs) goes over the columns of S that have been consumed: chunk c -> columns 16c .. 16c+15
+        tc::st16(lane_addr + c * 16, pk);
+      }
+      l = l * alpha + lsum;
+      m = mx;
+      // O must be rescaled when this row's maximum moved; skip the TMEM round trip when no row of the warp needs it
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          tc::ld32(lane_addr + 128 + c * 32, r);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+          tc::st32(lane_addr + 128 + c * 32, r);
+        }
+      }
+      tc::fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---------------- epilogue: O / l -> bf16 row
+    if (ntiles > 0 && ok) ok = mbar_wait(o_done, (ntiles - 1) & 1, a.status);
+    __syncwarp();
+    tc::fence_after();
+    {
+      // tcgen05.ld is warp-collective: every lane takes part, only the rows that exist are stored
+      const bool store = qi < a.S && ok;
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      bf16* op = reinterpret_cast<bf16*>(a.out) + (int64_t)b * a.o_sb + (int64_t)min(qi, a.S - 1) * a.o_ss + (int64_t)head * a.o_sh;
+      uint32_t r[32];
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        if (ntiles > 0) {
+          tc::ld32(lane_addr + 128 + c * 32, r);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
+        if (store) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(op + c * 32 + e) = v;
+          }
+        }
+      }
+    }
+  }
+  tc::fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after();
+    tc::dealloc(tmem_base, 256);
+  }
+}
+
 int decode_splits(Ctx* c, int64_t B, int kvh) {
   if (const char* e = getenv("REW_B200_ATTN_SPLITS")) {  // tuning override
     const int v = atoi(e);
@@ -622,6 +859,19 @@ int attn_launch(Ctx* c, const AttnArgs& h) {
       RB_CUDA(launch_k(attn_merge_kernel, dim3((unsigned)h.nh, (unsigned)h.B), dim3((unsigned)a.hd), 0, c->stream, c->use_pdl, a));
       ++g_launch_total;
     }
+    return REWB200_OK;
+  }
+  if (c->attn_tc && a.hd == 128 && h.S >= 128 && (!a.causal || a.mask_kind == 1) && h.q_ss % 8 == 0 && h.q_sh % 8 == 0 &&
+      h.q_sb % 8 == 0 && h.o_ss % 8 == 0 && h.o_sh % 8 == 0 && h.o_sb % 8 == 0) {
+    static bool tc_attr = false;
+    if (!tc_attr) {
+      RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM));
+      RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+      tc_attr = true;
+    }
+    dim3 tgrid((unsigned)((h.S + fa::BQ - 1) / fa::BQ), (unsigned)h.nh, (unsigned)h.B);
+    RB_CUDA(launch_k(attn_prefill_tc_kernel, tgrid, dim3(fa::THREADS), (size_t)fa::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
+    ++g_launch_total;
     return REWB200_OK;
   }
   dim3 grid((unsigned)((h.S + 63) / 64), (unsigned)h.nh, (unsigned)h.B);

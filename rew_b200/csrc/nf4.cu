@@ -283,6 +283,7 @@ __global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constan
       for (int j = 0; j < 32; ++j) r[j] = 0u;
       if (nkb > 0) {
         ok = mbar_wait(d_full, 0, status) && ok;
+        ok = __all_sync(0xffffffffu, ok);  // the load below is warp-collective
         tc::fence_after();
         if (ok) tc::ld32(tmem_base + ((uint32_t)(quarter * 32) << 16), r);
       }

@@ -247,6 +247,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "prefill") {
     RB_REQUIRE(v == "persistent" || v == "tile", "option prefill: expected persistent or tile");
     c->prefill_persistent = v == "persistent";
+  } else if (k == "attention") {
+    RB_REQUIRE(v == "tc" || v == "mma", "option attention: expected tc or mma");
+    c->attn_tc = v == "tc";
   } else if (k == "sampling") {
     RB_REQUIRE(v == "bucket" || v == "radix", "option sampling: expected bucket or radix");
     c->sampling_exact = v == "radix";

@@ -209,3 +209,27 @@ def test_swiglu_and_embedding(rb, orc):
     bad = T(rb, np.array([51], np.int32))
     with pytest.raises(RewB200Error, match="out of range"):
         emb.forward(bad).to_host()
+
+
+@pytest.mark.parametrize("B,nh,kvh,S,L", [(2, 8, 2, 512, 512), (1, 4, 4, 300, 300), (1, 8, 1, 130, 400), (3, 4, 2, 128, 128),
+                                          (1, 2, 2, 1000, 1000)])
+@pytest.mark.parametrize("mode", ["plain", "standard"])
+def test_attention_bf16_prefill_tcgen05(rb, orc, B, nh, kvh, S, L, mode):
+    """head_dim 128 and at least 128 queries: the tcgen05 kernel (S and O in tensor memory).  Ragged last
+    tiles, grouped heads, and a context longer than the query block (keys j <= i + L - S visible)."""
+    from rew_b200 import _lib
+    rng = np.random.default_rng(S + L)
+    q = orc.bf16_round(rng.normal(size=(B, nh, S, 128)))
+    k = orc.bf16_round(rng.normal(size=(B, kvh, L, 128)))
+    v = orc.bf16_round(rng.normal(size=(B, kvh, L, 128)))
+    causal, mk = {"plain": (False, 0), "standard": (True, 1)}[mode]
+    args = (T(rb, q, _lib.BF16), T(rb, k, _lib.BF16), T(rb, v, _lib.BF16), causal, mk)
+    got = rb.scaledDotProductAttention(*args).to_host()
+    want = orc.gqa_attention(q, k, v, causal, mk)
+    assert rel_l2(got, want) < BF16_TOL
+    rb.set_option("attention", "mma")
+    try:
+        ref = rb.scaledDotProductAttention(*args).to_host()
+    finally:
+        rb.set_option("attention", "tc")
+    assert rel_l2(got, ref) < 1e-2   # two correct bf16 kernels agree far inside the tolerance
