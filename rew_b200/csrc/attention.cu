@@ -550,6 +550,12 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
 //            moved; at the end normalise O and store bf16 rows
 // 256 TMEM columns and 96 KB of shared memory per CTA: two CTAs per SM, so one CTA's softmax runs
 // under the other's matrix products.  Every wait is bounded.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 namespace fa {
 constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE_BYTES = BKV * HD * 2;            // 32 KB: [hd half][128 rows][64 elements]
@@ -686,34 +692,50 @@ __global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __gr
       __syncwarp();  // the tensor-memory loads below are warp-collective
       tc::fence_after();
       const int k0 = j * BKV;
-      const bool edge = (k0 + BKV - 1 > qlim) || (k0 + BKV > kv_len);   // some key of this tile is masked for this row
+      // only the last tile or two of a query block contain masked keys; the test is the same for every
+      // thread of the CTA, so the common tile runs without a compare per element
+      const bool edge = (a.causal && k0 + BKV - 1 > q0 + ctx) || (k0 + BKV > kv_len);
       uint32_t r[32];
-      float mx = m;
+      float mraw = -INFINITY;   // maximum of the raw scores (the scale is positive)
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         tc::ld32(lane_addr + c * 32, r);
+        if (edge) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int key = k0 + c * 32 + e;
-          const float sv = (edge && (key > qlim || key >= kv_len)) ? -INFINITY : __uint_as_float(r[e]) * sl2;
-          mx = fmaxf(mx, sv);
+          for (int e = 0; e < 32; ++e) {
+            const int key = k0 + c * 32 + e;
+            if (key <= qlim && key < kv_len) mraw = fmaxf(mraw, __uint_as_float(r[e]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mraw = fmaxf(mraw, __uint_as_float(r[e]));
         }
       }
+      const float mx = fmaxf(m, mraw * sl2);
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = exp2f(m - m_use);   // 0 on the first tile (m = -inf)
+      const float alpha = ex2_approx(m - m_use);   // 0 on the first tile (m = -inf)
       float lsum = 0.f;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         tc::ld32(lane_addr + c * 32, r);
         uint32_t pk[16];
+        if (edge) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const int key = k0 + c * 32 + e;
-          const float s0 = (edge && (key > qlim || key >= kv_len)) ? -INFINITY : __uint_as_float(r[e]) * sl2;
-          const float s1 = (edge && (key + 1 > qlim || key + 1 >= kv_len)) ? -INFINITY : __uint_as_float(r[e + 1]) * sl2;
-          const float p0 = exp2f(s0 - m_use), p1 = exp2f(s1 - m_use);
-          lsum += p0 + p1;
-          pk[e >> 1] = pack_bf16(p0, p1);
+          for (int e = 0; e < 32; e += 2) {
+            const int key = k0 + c * 32 + e;
+            const float p0 = (key <= qlim && key < kv_len) ? ex2_approx(fmaf(__uint_as_float(r[e]), sl2, -m_use)) : 0.f;
+            const float p1 = (key + 1 <= qlim && key + 1 < kv_len) ? ex2_approx(fmaf(__uint_as_float(r[e + 1]), sl2, -m_use)) : 0.f;
+            lsum += p0 + p1;
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(r[e]), sl2, -m_use));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(r[e + 1]), sl2, -m_use));
+            lsum += p0 + p1;
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
         }
         // P (bf16 pairs) goes over the columns of S that have been consumed: chunk c -> columns 16c .. 16c+15
         tc::st16(lane_addr + c * 16, pk);
