@@ -127,3 +127,28 @@ def test_launch_counter_moves(rb):
     sess = rb.CausalLM(cfg).load(W.init_weights(cfg, seed=0)).session(1, 16)
     sess.forward(np.array([[1, 2, 3]], np.int32))
     assert _lib.lib().rewb200_launch_count(0) > before
+
+
+def test_bf16_prefill_attention_kernels_agree_and_chunked_prefill(rb):
+    """head_dim 128 and prompts of 128+ tokens put prefill attention on the tcgen05 kernel: its logits match
+    the mma.sync kernel's, and a prompt fed in two chunks (the second attends to a 150-token context through
+    the paged cache) matches the same prompt fed at once."""
+    from rew_b200 import _lib
+    cfg = W.ModelConfig(vocab=1024, d_model=512, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, max_seq=512,
+                        theta=500000.0, dtype=_lib.BF16, mask_kind=1)
+    model = rb.CausalLM(cfg).init_random(seed=2, std=0.04)
+    B, S = 3, 300
+    prompt = np.random.default_rng(0).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+    sess = model.session(B, 320)
+    _, a = sess.forward(prompt, want_logits=True)
+    rb.set_option("attention", "mma")
+    try:
+        sess.reset()
+        _, b = sess.forward(prompt, want_logits=True)
+    finally:
+        rb.set_option("attention", "tc")
+    assert np.isfinite(a).all() and rel_l2(a, b) <= 1e-2
+    sess.reset()
+    sess.forward(prompt[:, :150])
+    _, c = sess.forward(prompt[:, 150:], want_logits=True)
+    assert rel_l2(c, a) <= 1e-2
