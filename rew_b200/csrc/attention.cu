@@ -540,14 +540,16 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
 
 // ---------------------------------------------------------------------------------------------
 // Prefill attention on the 5th-generation tensor core (head_dim 128, conventional causal or no mask).
-// CTA = 128 queries of one head; thread i of the four softmax warps owns query row i = TMEM lane i.
+// CTA = 128 queries of one head; a softmax thread owns half of query row i = TMEM lane i.
 //   warp 0   TMA: K and V tiles of 128 keys (one stage each; four 64x64 boxes, 128-byte swizzle)
 //   warp 1   one thread issues S = Q K^T (8 x tcgen05.mma, both operands K-major in shared memory,
 //            S[128 queries][128 keys] f32 in TMEM) and O += P V (8 x tcgen05.mma, A = P read from
 //            TMEM as bf16, B = V MN-major from shared memory, O[128][128] f32 in TMEM)
-//   warps 2-5 online softmax in the exp2 domain: read S twice (row maximum, then probabilities),
-//            write P over the columns of S already consumed, rescale O only when some row's maximum
-//            moved; at the end normalise O and store bf16 rows
+//   warps 2-9 online softmax in the exp2 domain, two warps per lane quarter, each on 64 of the 128 keys:
+//            read the scores once into registers, exchange the half-row maxima through shared memory,
+//            write P over the columns of S (after a barrier: the other half's warp may still be
+//            reading them), rescale their half of O only when some row's maximum moved; at the end
+//            normalise O and store bf16 rows
 // 256 TMEM columns and 96 KB of shared memory per CTA: two CTAs per SM, so one CTA's softmax runs
 // under the other's matrix products.  Every wait is bounded.
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -559,11 +561,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
 namespace fa {
 constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE_BYTES = BKV * HD * 2;            // 32 KB: [hd half][128 rows][64 elements]
-constexpr int SMEM = 3 * TILE_BYTES + 256 + 1024;   // Q, K, V + barriers + alignment slack
-constexpr int THREADS = 6 * 32;
+constexpr int XCH = 3 * 2 * 128 * 4;                // row maxima (two buffers) and row sums exchanged by the two column halves
+constexpr int SMEM = 3 * TILE_BYTES + XCH + 256 + 1024;   // Q, K, V + exchange + barriers + alignment slack
+constexpr int THREADS = 10 * 32;
 }  // namespace fa
 
-__global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(fa::THREADS, 2) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK,
                                                                       const __grid_constant__ CUtensorMap tmV, AttnDev a) {
   using namespace fa;
   extern __shared__ uint8_t smem_raw[];
@@ -571,7 +574,9 @@ __global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __gr
   uint8_t* sQ = smem;
   uint8_t* sK = smem + TILE_BYTES;
   uint8_t* sV = smem + 2 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES);
+  float* xmax = reinterpret_cast<float*>(smem + 3 * TILE_BYTES);   // [2 buffers][2 halves][128 rows]
+  float* xsum = xmax + 2 * 2 * 128;                                 // [2 halves][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES + XCH);
   uint64_t *k_full = bars, *k_empty = bars + 1, *v_full = bars + 2, *v_empty = bars + 3, *s_full = bars + 4, *p_full = bars + 5,
            *o_done = bars + 6;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
@@ -587,7 +592,7 @@ __global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __gr
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
-    mbar_init(p_full, 4);   // the four softmax warps
+    mbar_init(p_full, 8);   // the eight softmax warps
     mbar_init(o_done, 1);
     fence_barrier_init();
     pdl_launch_dependents();
@@ -607,15 +612,16 @@ __global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __gr
   const int ntiles = (kv_end + BKV - 1) / BKV;
 
   if (warp >= 2) {
-    // stage Q: 128 rows x 256 bytes into [hd half][row][64 elements] with the 128-byte swizzle TMA would apply
-    const int r = threadIdx.x - 64;
+    // stage Q: 128 rows x 256 bytes into [hd half][row][64 elements] with the 128-byte swizzle TMA would apply;
+    // 256 threads, half a row each
+    const int r = (threadIdx.x - 64) & 127, hh = (threadIdx.x - 64) >> 7;
     const int qi = q0 + r;
     const bf16* qp = reinterpret_cast<const bf16*>(a.q) + (int64_t)b * a.q_sb + (int64_t)min(qi, a.S - 1) * a.q_ss + (int64_t)head * a.q_sh;
 #pragma unroll
-    for (int ch = 0; ch < 16; ++ch) {  // sixteen 16-byte chunks of the row
+    for (int c8 = 0; c8 < 8; ++c8) {  // eight 16-byte chunks: one 64-element half of the row
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (qi < a.S) v = *reinterpret_cast<const uint4*>(qp + ch * 8);
-      *reinterpret_cast<uint4*>(sQ + (ch >> 3) * (TILE_BYTES / 2) + swz128((uint32_t)r, (uint32_t)(ch & 7))) = v;
+      if (qi < a.S) v = *reinterpret_cast<const uint4*>(qp + hh * 64 + c8 * 8);
+      *reinterpret_cast<uint4*>(sQ + hh * (TILE_BYTES / 2) + swz128((uint32_t)r, (uint32_t)c8)) = v;
     }
     fence_proxy_async();  // the tensor core reads these bytes through the async proxy
   }
@@ -678,85 +684,91 @@ __global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __gr
       }
     }
   } else {
-    // ---------------- softmax warps: lane quarter = warp % 4, query row = quarter * 32 + lane
-    const int quarter = warp & 3;
+    // ---------------- softmax warps: lane quarter = warp % 4, query row = quarter * 32 + lane, keys 64 half .. +63
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int qi = q0 + row;
     const int qlim = a.causal ? qi + ctx : 0x7fffffff;   // last visible key
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const float sl2 = a.scale * 1.4426950408889634f;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;   // l: this half's share of the row sum (both halves share m)
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
       if (ok) ok = mbar_wait(s_full, j & 1, a.status);
-      __syncwarp();  // the tensor-memory loads below are warp-collective
+      __syncwarp();  // the tensor-memory accesses below are warp-collective
       tc::fence_after();
-      const int k0 = j * BKV;
+      const int k0 = j * BKV + half * 64;
       // only the last tile or two of a query block contain masked keys; the test is the same for every
       // thread of the CTA, so the common tile runs without a compare per element
-      const bool edge = (a.causal && k0 + BKV - 1 > q0 + ctx) || (k0 + BKV > kv_len);
-      uint32_t r[32];
+      const bool edge = (a.causal && j * BKV + BKV - 1 > q0 + ctx) || (j * BKV + BKV > kv_len);
+      uint32_t r0[32], r1[32];
+      tc::ld32(lane_addr + half * 64, r0);
+      tc::ld32(lane_addr + half * 64 + 32, r1);
       float mraw = -INFINITY;   // maximum of the raw scores (the scale is positive)
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tc::ld32(lane_addr + c * 32, r);
-        if (edge) {
+      if (edge) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = k0 + c * 32 + e;
-            if (key <= qlim && key < kv_len) mraw = fmaxf(mraw, __uint_as_float(r[e]));
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mraw = fmaxf(mraw, __uint_as_float(r[e]));
+        for (int e = 0; e < 32; ++e) {
+          if (k0 + e <= qlim && k0 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r0[e]));
+          if (k0 + 32 + e <= qlim && k0 + 32 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r1[e]));
         }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mraw = fmaxf(mraw, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
       }
+      float* xm = xmax + (j & 1) * 256;
+      xm[half * 128 + row] = mraw;
+      // after this barrier every score of the tile is in registers (P may overwrite S) and both half maxima are visible
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mraw = fmaxf(mraw, xm[(half ^ 1) * 128 + row]);
       const float mx = fmaxf(m, mraw * sl2);
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = ex2_approx(m - m_use);   // 0 on the first tile (m = -inf)
       float lsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        tc::ld32(lane_addr + c * 32, r);
-        uint32_t pk[16];
+      uint32_t pk[16];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const uint32_t* rr = cc ? r1 : r0;
         if (edge) {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const int key = k0 + c * 32 + e;
-            const float p0 = (key <= qlim && key < kv_len) ? ex2_approx(fmaf(__uint_as_float(r[e]), sl2, -m_use)) : 0.f;
-            const float p1 = (key + 1 <= qlim && key + 1 < kv_len) ? ex2_approx(fmaf(__uint_as_float(r[e + 1]), sl2, -m_use)) : 0.f;
+            const int key = k0 + cc * 32 + e;
+            const float p0 = (key <= qlim && key < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use)) : 0.f;
+            const float p1 = (key + 1 <= qlim && key + 1 < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use)) : 0.f;
             lsum += p0 + p1;
             pk[e >> 1] = pack_bf16(p0, p1);
           }
         } else {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(r[e]), sl2, -m_use));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(r[e + 1]), sl2, -m_use));
+            const float p0 = ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use));
             lsum += p0 + p1;
             pk[e >> 1] = pack_bf16(p0, p1);
           }
         }
-        // P (bf16 pairs) goes over the columns of S that have been consumed: chunk c -> columns 16c .. 16c+15
-        tc::st16(lane_addr + c * 16, pk);
+        // P (bf16 pairs): keys 64 half + 32 cc .. +31 -> columns 32 half + 16 cc .. +15
+        tc::st16(lane_addr + half * 32 + cc * 16, pk);
       }
       l = l * alpha + lsum;
       m = mx;
       // O must be rescaled when this row's maximum moved; skip the TMEM round trip when no row of the warp needs it
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          tc::ld32(lane_addr + 128 + c * 32, r);
+        for (int c = 0; c < 2; ++c) {
+          tc::ld32(lane_addr + 128 + half * 64 + c * 32, r0);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-          tc::st32(lane_addr + 128 + c * 32, r);
+          for (int e = 0; e < 32; ++e) r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
+          tc::st32(lane_addr + 128 + half * 64 + c * 32, r0);
         }
       }
       tc::fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    // ---------------- epilogue: O / l -> bf16 row
+    // ---------------- epilogue: O / l -> bf16 row (this warp's 64 of the 128 output columns)
+    xsum[half * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += xsum[(half ^ 1) * 128 + row];
     if (ntiles > 0 && ok) ok = mbar_wait(o_done, (ntiles - 1) & 1, a.status);
     __syncwarp();
     tc::fence_after();
@@ -764,12 +776,13 @@ __global__ void __launch_bounds__(fa::THREADS) attn_prefill_tc_kernel(const __gr
       // tcgen05.ld is warp-collective: every lane takes part, only the rows that exist are stored
       const bool store = qi < a.S && ok;
       const float inv = l > 0.f ? 1.0f / l : 0.f;
-      bf16* op = reinterpret_cast<bf16*>(a.out) + (int64_t)b * a.o_sb + (int64_t)min(qi, a.S - 1) * a.o_ss + (int64_t)head * a.o_sh;
+      bf16* op = reinterpret_cast<bf16*>(a.out) + (int64_t)b * a.o_sb + (int64_t)min(qi, a.S - 1) * a.o_ss + (int64_t)head * a.o_sh +
+                 half * 64;
       uint32_t r[32];
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         if (ntiles > 0) {
-          tc::ld32(lane_addr + 128 + c * 32, r);
+          tc::ld32(lane_addr + 128 + half * 64 + c * 32, r);
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) r[e] = 0u;
