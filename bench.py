@@ -272,6 +272,8 @@ def main():
     ap.add_argument("--workload", default="l8_b32", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="rew_b200", choices=["rew_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
+                    help="run-time switch passed to rewb200_set_option, e.g. norm=row (repeatable)")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "top_k", "top_p"],
                     help="next-token rule of the decode step; greedy is the metric's configuration")
@@ -290,6 +292,9 @@ def main():
     from rew_b200 import _lib, api
     _lib.init(local_rank)
     L = _lib.lib()
+    for kv in args.option:
+        k, _, v = kv.partition("=")
+        api.set_option(k, v)
 
     pg = None
     if world > 1:

@@ -66,6 +66,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *   "pdl"    = "0" | "1"                     programmatic dependent launch (REW_B200_PDL)
  *   "prefill" = "persistent" | "tile"        Linear launches of 256-token tiles: one persistent CTA per SM
  *                                            with the epilogue overlapped (default), or one CTA per tile
+ *   "norm" = "cluster" | "row"               decode-size residual+norm: four CTAs per row exchanging the row
+ *                                            statistics through distributed shared memory (default), or one CTA per row
  *   "attention" = "tc" | "mma"               prefill attention with head_dim 128 on tcgen05 (default) or mma.sync
  *   "sampling" = "bucket" | "radix"          top-k / top-p selection: bucket histograms with the
  *                                            radix select as the exact fallback (default), or

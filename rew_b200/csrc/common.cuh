@@ -47,6 +47,7 @@ struct Ctx {
   bool use_pdl = true;
   int linear_impl = 2;       // bf16 Linear: 0 mma.sync, 1 tcgen05 when rows > 32, 2 tcgen05 always (default)
   bool prefill_persistent = true;  // 256-token Linear tiles on the persistent kernel with overlapped epilogue
+  bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
   int option_epoch = 0;      // bumped by rewb200_set_option; captured graphs from older epochs are rebuilt

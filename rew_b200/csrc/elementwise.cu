@@ -12,8 +12,12 @@
 
 #include <algorithm>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "ptx.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace rewb {
 
@@ -269,6 +273,120 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
     }
     Vec4<TO>::store(orow + i, o);
   }
+}
+
+// Decode-size variant: a cluster of four CTAs per row, each on a quarter of the columns; the row
+// statistics meet through distributed shared memory.  With 32 rows the one-CTA-per-row kernel keeps 32
+// SMs busy reading 8 slabs of 16 KB each; this one spreads the same reads over 128 SMs.
+template <typename TE, int NCH>
+__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_cluster_kernel(NormArgs a) {
+  __shared__ float red[33];
+  __shared__ float part[2];
+  cg::cluster_group cl = cg::this_cluster();
+  const unsigned rank = cl.block_rank();
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t row = blockIdx.x >> 2;
+  const int64_t d = a.d, dq = d >> 2, col0 = (int64_t)rank * dq;
+  float* xr = a.x_res + row * d;
+  const TE* erow = nullptr;
+  if (a.embed) {
+    int64_t id = row;
+    if (a.ids) {
+      id = a.ids[row];
+      if (id < 0 || id >= a.vocab) {
+        if (threadIdx.x == 0 && rank == 0) atomicExch(a.status, KS_BAD_INDEX);
+        id = 0;
+      }
+    }
+    erow = reinterpret_cast<const TE*>(a.embed) + id * d;
+  }
+  float4 vals[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int64_t off = ((int64_t)c * 256 + threadIdx.x) * 4;
+    const int64_t i = col0 + off;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (off < dq) {
+      v = erow ? Vec4<TE>::load(erow + i) : *reinterpret_cast<const float4*>(xr + i);
+      if (a.partial) {
+        const float* pp = a.partial + row * d + i;
+        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+        int s = 0;
+        for (; s + 4 <= a.nsplit; s += 4) {
+          const float4 p0 = *reinterpret_cast<const float4*>(pp + (s + 0) * a.split_stride);
+          const float4 p1 = *reinterpret_cast<const float4*>(pp + (s + 1) * a.split_stride);
+          const float4 p2 = *reinterpret_cast<const float4*>(pp + (s + 2) * a.split_stride);
+          const float4 p3 = *reinterpret_cast<const float4*>(pp + (s + 3) * a.split_stride);
+          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
+          p.x += p1.x; p.y += p1.y; p.z += p1.z; p.w += p1.w;
+          p.x += p2.x; p.y += p2.y; p.z += p2.z; p.w += p2.w;
+          p.x += p3.x; p.y += p3.y; p.z += p3.z; p.w += p3.w;
+        }
+        for (; s < a.nsplit; ++s) {
+          const float4 p0 = *reinterpret_cast<const float4*>(pp + s * a.split_stride);
+          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
+        }
+        if (a.bias) {
+          const float4 b = *reinterpret_cast<const float4*>(a.bias + i);
+          p.x += b.x; p.y += b.y; p.z += b.z; p.w += b.w;
+        }
+        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+      }
+      if (a.x_res && (erow || a.partial)) *reinterpret_cast<float4*>(xr + i) = v;
+    }
+    vals[c] = v;
+  }
+  // sum over the row = sum over the four CTAs' block sums, added in rank order by every CTA alike
+  auto row_sum = [&](float local, int slot) -> float {
+    const float bs = block_sum(local, red);
+    if (threadIdx.x == 0) part[slot] = bs;
+    cl.sync();
+    float t = 0.f;
+    for (unsigned r = 0; r < 4; ++r) t += *cl.map_shared_rank(&part[slot], r);
+    return t;
+  };
+  bf16* orow = reinterpret_cast<bf16*>(a.out) + row * d;
+  float mean = 0.f, scale;
+  if (a.norm_kind == 0) {
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) ss += vals[c].x * vals[c].x + vals[c].y * vals[c].y + vals[c].z * vals[c].z + vals[c].w * vals[c].w;
+    scale = sqrtf(row_sum(ss, 0) / (float)d + a.eps);  // rmsNorm divides by this
+  } else {
+    float s1 = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) s1 += vals[c].x + vals[c].y + vals[c].z + vals[c].w;
+    mean = row_sum(s1, 0) / (float)d;
+    float s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int64_t off = ((int64_t)c * 256 + threadIdx.x) * 4;
+      if (off < dq) {
+        const float cx = vals[c].x - mean, cy = vals[c].y - mean, cz = vals[c].z - mean, cw = vals[c].w - mean;
+        s2 += cx * cx + cy * cy + cz * cz + cw * cw;
+      }
+    }
+    scale = 1.0f / sqrtf(row_sum(s2, 1) / (float)d + a.eps);  // LayerNorm multiplies by this
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int64_t off = ((int64_t)c * 256 + threadIdx.x) * 4;
+    if (off >= dq) continue;
+    const int64_t i = col0 + off;
+    const float4 g = *reinterpret_cast<const float4*>(a.gamma + i);
+    float4 o;
+    if (a.norm_kind == 0) {
+      o.x = g.x * (vals[c].x / scale); o.y = g.y * (vals[c].y / scale);
+      o.z = g.z * (vals[c].z / scale); o.w = g.w * (vals[c].w / scale);
+    } else {
+      const float4 b = *reinterpret_cast<const float4*>(a.beta + i);
+      o.x = g.x * ((vals[c].x - mean) * scale) + b.x; o.y = g.y * ((vals[c].y - mean) * scale) + b.y;
+      o.z = g.z * ((vals[c].z - mean) * scale) + b.z; o.w = g.w * ((vals[c].w - mean) * scale) + b.w;
+    }
+    Vec4<bf16>::store(orow + i, o);
+  }
+  cl.sync();  // no CTA leaves while another may still read its block sums
 }
 
 template <typename TA>
@@ -663,6 +781,19 @@ int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows) {
   const bool e16 = a.embed_dtype == REWB200_BF16, o16 = a.out_dtype == REWB200_BF16;
   cudaError_t e;
   RB_REQUIRE(a.n_peers == 0 || a.d % 4 == 0, "the fused all-reduce needs d_model % 4 == 0");
+  if (a.n_peers == 0 && o16 && a.norm_kind >= 0 && rows <= 64 && a.d % 16 == 0 && a.d <= 16384 && c->norm_cluster) {
+    const int nch = (int)((a.d / 16 + 255) / 256);  // float4 per thread over a quarter row
+    dim3 g((unsigned)(rows * 4)), b(256);
+#define RB_NORMC(TE)                                                                                  \
+  (nch <= 1   ? launch_k(residual_norm_cluster_kernel<TE, 1>, g, b, 0, c->stream, c->use_pdl, a)          \
+   : nch <= 2 ? launch_k(residual_norm_cluster_kernel<TE, 2>, g, b, 0, c->stream, c->use_pdl, a)          \
+              : launch_k(residual_norm_cluster_kernel<TE, 4>, g, b, 0, c->stream, c->use_pdl, a))
+    e = e16 ? RB_NORMC(bf16) : RB_NORMC(float);
+#undef RB_NORMC
+    RB_CUDA(e);
+    ++g_launch_total;
+    return REWB200_OK;
+  }
   if (a.d % 4 == 0) {
     const int nch = (int)((a.d / 4 + NORMV_THREADS - 1) / NORMV_THREADS);
     dim3 g((unsigned)rows), b(NORMV_THREADS);

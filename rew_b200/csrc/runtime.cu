@@ -247,6 +247,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "prefill") {
     RB_REQUIRE(v == "persistent" || v == "tile", "option prefill: expected persistent or tile");
     c->prefill_persistent = v == "persistent";
+  } else if (k == "norm") {
+    RB_REQUIRE(v == "cluster" || v == "row", "option norm: expected cluster or row");
+    c->norm_cluster = v == "cluster";
   } else if (k == "attention") {
     RB_REQUIRE(v == "tc" || v == "mma", "option attention: expected tc or mma");
     c->attn_tc = v == "tc";

@@ -152,3 +152,31 @@ def test_bf16_prefill_attention_kernels_agree_and_chunked_prefill(rb):
     sess.forward(prompt[:, :150])
     _, c = sess.forward(prompt[:, 150:], want_logits=True)
     assert rel_l2(c, a) <= 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("norm_kind,d_model", [(0, 512), (1, 512), (0, 2064)])
+def test_bf16_decode_norm_kernels_agree(rb, norm_kind, d_model):
+    """Decode-size residual+norm runs on clusters of four CTAs per row (row statistics exchanged through
+    distributed shared memory); option norm=row keeps one CTA per row.  Both compute the same rmsNorm /
+    LayerNorm of the same f32 residual stream, so the bf16 logits of a prompt plus a few decode steps
+    agree to summation-order rounding."""
+    from rew_b200 import _lib
+    cfg = W.ModelConfig(vocab=512, d_model=d_model, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=64, ffn=768, max_seq=64,
+                        theta=10000.0, dtype=_lib.BF16, norm_kind=norm_kind)
+    model = rb.CausalLM(cfg).init_random(seed=5, std=0.05)
+    B = 5
+    prompt = np.random.default_rng(1).integers(0, cfg.vocab, size=(B, 7)).astype(np.int32)
+    outs = {}
+    for mode in ("cluster", "row"):
+        rb.set_option("norm", mode)
+        try:
+            sess = model.session(B, 32)
+            _, first = sess.forward(prompt, want_logits=True)
+            _, last = sess.decode(6, want_logits=True)
+            outs[mode] = (first, last)
+        finally:
+            rb.set_option("norm", "cluster")
+    a, b = outs["cluster"], outs["row"]
+    assert np.isfinite(a[0]).all() and rel_l2(a[0], b[0]) <= 2e-3
+    assert np.isfinite(a[1]).all() and rel_l2(a[1], b[1]) <= 5e-3
