@@ -66,6 +66,9 @@ int rewb200_sync(int slot, int timeout_ms);
  *   "pdl"    = "0" | "1"                     programmatic dependent launch (REW_B200_PDL)
  *   "prefill" = "persistent" | "tile"        Linear launches of 256-token tiles: one persistent CTA per SM
  *                                            with the epilogue overlapped (default), or one CTA per tile
+ *   "splitk" = "slabs" | "cluster" | "qkv" | "out"   decode-size split-K: f32 slabs summed by the next kernel (default),
+ *                                            or summed inside thread-block clusters through distributed shared memory
+ *                                            (all launches, only q|k|v with its RoPE / cache-write epilogue, or only the others)
  *   "norm" = "cluster" | "row"               decode-size residual+norm: four CTAs per row exchanging the row
  *                                            statistics through distributed shared memory (default), or one CTA per row
  *   "attention" = "tc" | "mma"               prefill attention with head_dim 128 on tcgen05 (default) or mma.sync

@@ -47,6 +47,7 @@ struct Ctx {
   bool use_pdl = true;
   int linear_impl = 2;       // bf16 Linear: 0 mma.sync, 1 tcgen05 when rows > 32, 2 tcgen05 always (default)
   bool prefill_persistent = true;  // 256-token Linear tiles on the persistent kernel with overlapped epilogue
+  int splitk_cluster = 0;     // decode-size split-K summed inside thread-block clusters instead of through f32 slabs: bit 0 the q|k|v launch, bit 1 the others (off: measured slower)
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
@@ -112,6 +113,27 @@ cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Same, with the thread-block cluster shape given at launch.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_k_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                             dim3 cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---------------------------------------------------------------- buffers
 }  // namespace rewb
 
@@ -156,6 +178,14 @@ int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_
                        int ksplit, void* out, int64_t ldo, const float* bias, const int* row_offsets, int max_rows_per_group);
 int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, int ksplit,
                      void* out, int64_t ldo, const float* bias);
+// Decode-size split-K on thread-block clusters (M <= 32, ksplit in {2,4,8}): the CTAs that share a
+// feature tile sum their accumulators through distributed shared memory and leave ONE f32 slab
+// out[M][ldo] (bias still for the consumer), or, with fuse_qkv, finished q / k / v exactly as
+// qkv_post_kernel would have left them (bf16 activations).
+struct QkvPostArgs;
+bool linear_tc_cluster_ok(Ctx* c, const LinearBf16Plan& plan, int64_t M, int ksplit);
+int linear_tc_cluster_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int ksplit,
+                             float* out, int64_t ldo, const QkvPostArgs* fuse_qkv);
 int linear_bf16_plan(LinearBf16Plan* plan, const bf16* W, int64_t K, int64_t N, int groups);
 int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N);
 

@@ -410,8 +410,9 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
 // y = x @ W for the model dtype.  `partial` selects the f32 split-K slab
 // output (bias deferred to the consumer) over a finished output with bias.
 int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, int64_t rows, bool partial, int epi,
-               void* out, int64_t ldo, int* ksplit_out) {
+               void* out, int64_t ldo, int* ksplit_out, const QkvPostArgs* fuse_qkv = nullptr, bool* fused = nullptr) {
   Ctx* c = s->m->c;
+  if (fused) *fused = false;
   if (w.quant && rows <= 32) {
     // weight-only NF4: codes dequantised inside the GEMV, f32 split-K slabs
     int ks = nf4_pick_ksplit(c, w.K, w.N);
@@ -436,6 +437,13 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
     if (partial) {
       ks = linear_bf16_pick_ksplit(c, rows, w.K, w.N);
       while (ks > 1 && (size_t)ks * rows * ldo * sizeof(float) > s->part_bytes) ks /= 2;
+      // decode-size steps: sum the K slices inside thread-block clusters, one slab (or finished q|k|v) comes out
+      const int kc = std::min(ks, 8);
+      if ((c->splitk_cluster & (fuse_qkv ? 1 : 2)) && linear_tc_cluster_ok(c, w.plan, rows, kc)) {
+        if (ksplit_out) *ksplit_out = 1;
+        if (fused) *fused = fuse_qkv != nullptr;
+        return linear_tc_cluster_launch(c, w.plan, (const bf16*)x, ldx, rows, kc, (float*)out, ldo, fuse_qkv);
+      }
     }
     if (ksplit_out) *ksplit_out = ks;
     return linear_bf16_launch(c, w.plan, (const bf16*)x, ldx, rows, partial ? EPI_PARTIAL_F32 : epi, ks, out, ldo,
@@ -617,7 +625,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   for (int l = 0; l < cf.n_layers; ++l) {
     LayerDev& L = m->layers[l];
     int ks = 1;
-    RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks));
+    bool qkv_done = false;
     QkvPostArgs qa;
     memset(&qa, 0, sizeof(qa));
     qa.partial = s->part;
@@ -645,7 +653,11 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     qa.kv.dtype = dt;
     qa.kv_capacity = s->max_len;
     qa.status = c->d_status;
-    RB_TRY(qkv_post_launch(c, qa, nb));
+    RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks, dt == REWB200_BF16 ? &qa : nullptr, &qkv_done));
+    if (!qkv_done) {
+      qa.nsplit = ks;
+      RB_TRY(qkv_post_launch(c, qa, nb));
+    }
 
     AttnArgs aa;
     memset(&aa, 0, sizeof(aa));

@@ -20,6 +20,8 @@
 //            apply bias / SwiGLU, store.
 // All waits are bounded; on a timeout the roles fall through to the common
 // exit, where TMEM is released.
+#include <string.h>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -48,7 +50,30 @@ struct TcArgs {
   int64_t split_stride;
   const float* bias;
   int* status;
+  int fuse_qkv;       // cluster kernel: finish q|k|v in the epilogue (bias, RoPE, cache write) instead of one f32 slab
+  QkvPostArgs qp;     // what qkv_post_kernel would have been given (partial / nsplit unused)
 };
+
+// ---- thread-block cluster pieces of the split-K kernel
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t saddr, uint32_t rank) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(saddr), "r"(rank));
+  return ra;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
+  return v;
+}
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   // start address, leading / stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle
@@ -83,9 +108,118 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
 
 __device__ __forceinline__ float silu_f(float x) { return x * (1.0f / (1.0f + __expf(-x))); }
 
-template <int TN>
+// Second half of the cluster split-K epilogue, run by the four epilogue warps of every CTA after the
+// cluster barrier: this CTA finishes tokens [rank * 32/KS, (rank+1) * 32/KS) of the tile.  All loads of
+// the peers' tiles are issued before the first add, and the sum runs in split order, so the result
+// equals what the slab consumer kernels compute.
+template <int KS>
+__device__ __forceinline__ void cluster_finish(const TcArgs& a, uint8_t* smem, int q, int lane, int col0, int row0,
+                                               bool epi_ok) {
+  constexpr int TPR = 32 / KS;  // tokens this CTA finishes
+  const uint32_t cr = cluster_ctarank();
+  const int64_t feat = (int64_t)col0 + q * 32 + lane;
+  const bool feat_ok = feat < a.N;
+  const int j0 = (int)cr * TPR;
+  const uint32_t soff = smem_u32(smem) + (uint32_t)(j0 * BM + q * 32 + lane) * 4u;
+  float v[TPR];
+  {
+    float t[KS][TPR];
+#pragma unroll
+    for (int rr = 0; rr < KS; ++rr) {
+      const uint32_t ra = dsmem_addr(soff, (uint32_t)rr);
+#pragma unroll
+      for (int jj = 0; jj < TPR; ++jj) t[rr][jj] = ld_dsmem_f32(ra + (uint32_t)jj * (BM * 4u));
+    }
+#pragma unroll
+    for (int jj = 0; jj < TPR; ++jj) {
+      v[jj] = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < KS; ++rr) v[jj] += t[rr][jj];  // split order
+    }
+  }
+  if (!a.fuse_qkv) {
+    if (feat_ok && epi_ok) {
+#pragma unroll
+      for (int jj = 0; jj < TPR; ++jj) {
+        const int64_t grow = (int64_t)row0 + j0 + jj;
+        if (grow < a.M) reinterpret_cast<float*>(a.out)[grow * a.ldo + feat] = v[jj];
+      }
+    }
+    return;
+  }
+  // ---- q|k|v: bias, RoPE on interleaved pairs, q to its buffer, k / v into the cache.
+  // Lane t < TPR looks up token t's position and cache row once; everyone reads them by shuffle.
+  const QkvPostArgs& p = a.qp;
+  const int hd = p.hd, nq = p.nh * hd, nkv = p.kvh * hd;
+  int m_rpos = -1;          // RoPE table row, -1: row outside the launch or a bad index
+  long long m_crb = 0;      // cache row of kv head 0
+  const int64_t head_stride = p.kv.block_table ? p.kv.page : p.kv.contiguous_len;
+  if (lane < TPR) {
+    const int64_t grow = (int64_t)row0 + j0 + lane;
+    if (grow < a.M) {
+      const int b = (int)(grow / p.S), sidx = (int)(grow % p.S);
+      const int pos = p.pos0[b] + sidx, rpos = pos + p.rope_shift;
+      if (pos < 0 || pos >= p.kv_capacity || rpos < 0 || rpos >= p.max_seq) {
+        atomicExch(p.status, KS_BAD_INDEX);
+      } else {
+        m_rpos = rpos;
+        if (p.kv.block_table) {
+          const int page = p.kv.block_table[(int64_t)b * p.kv.max_pages + pos / p.kv.page];
+          m_crb = ((long long)page * p.kvh) * p.kv.page + pos % p.kv.page;
+        } else {
+          m_crb = ((long long)b * p.kvh) * p.kv.contiguous_len + pos;
+        }
+      }
+    }
+  }
+  const int col = (int)feat;
+  const bool rot = col < nq + nkv;
+  const int e = rot ? col % hd : (col - nq - nkv) % hd;
+  const int hkv = col < nq ? 0 : (rot ? (col - nq) / hd : (col - nq - nkv) / hd);
+  const float bias_v = (p.bias && feat_ok) ? p.bias[feat] : 0.f;
+  int rpos[TPR];
+  long long crb[TPR];
+  float cs[TPR], sn[TPR];
+#pragma unroll
+  for (int jj = 0; jj < TPR; ++jj) {
+    rpos[jj] = __shfl_sync(0xffffffffu, m_rpos, jj);
+    crb[jj] = __shfl_sync(0xffffffffu, m_crb, jj);
+  }
+#pragma unroll
+  for (int jj = 0; jj < TPR; ++jj) {
+    cs[jj] = 1.f;
+    sn[jj] = 0.f;
+    if (rot && feat_ok && rpos[jj] >= 0) {
+      cs[jj] = p.cosT[(int64_t)rpos[jj] * hd + e];
+      sn[jj] = p.sinT[(int64_t)rpos[jj] * hd + e];
+    }
+  }
+#pragma unroll
+  for (int jj = 0; jj < TPR; ++jj) {
+    const float x = v[jj] + bias_v;
+    const float pr = __shfl_xor_sync(0xffffffffu, x, 1);  // the other element of the pair
+    if (!feat_ok || !epi_ok || rpos[jj] < 0) continue;
+    const int64_t grow = (int64_t)row0 + j0 + jj;
+    if (rot) {
+      const float r = (e & 1) ? (sn[jj] * pr + cs[jj] * x) : (cs[jj] * x - sn[jj] * pr);
+      if (col < nq)
+        reinterpret_cast<bf16*>(p.q_out)[grow * nq + col] = __float2bfloat16_rn(r);
+      else
+        reinterpret_cast<bf16*>(p.kv.k)[(crb[jj] + hkv * head_stride) * hd + e] = __float2bfloat16_rn(r);
+    } else {
+      reinterpret_cast<bf16*>(p.kv.v)[(crb[jj] + hkv * head_stride) * hd + e] = __float2bfloat16_rn(x);
+    }
+  }
+}
+
+// CL = 1 (decode tile only): the CTAs of one feature tile that split K form a thread-block cluster
+// along z and sum their accumulators through distributed shared memory, each finishing 32 / ksplit
+// of the tile's tokens, so the launch leaves one finished slab (or finished q / k / v) instead of
+// ksplit partial slabs for the next kernel to add up.
+template <int TN, int CL>
 __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ CUtensorMap tmW,
                                                          const __grid_constant__ CUtensorMap tmX, TcArgs a) {
+  static_assert(CL == 0 || TN == 32, "the cluster reduction is written for the decode tile");
   using C = TcCfg<TN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -138,6 +272,7 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  bool epi_ok = true;
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmW);
@@ -205,7 +340,21 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
       tc_fence_after();
     }
     pdl_wait();
-    if constexpr (TN == 32) {
+    if constexpr (CL == 1) {
+      // own partial tile -> shared memory as [token][feature] f32 (the pipeline stages are free by now)
+      uint32_t r[32];
+      ok = __all_sync(0xffffffffu, ok);  // the tensor-memory load below is warp-collective
+      if (ok && nkb > 0) {
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16), r);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+      float* stg = reinterpret_cast<float*>(smem);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) stg[j * BM + q * 32 + lane] = __uint_as_float(r[j]);
+      epi_ok = ok;
+    } else if constexpr (TN == 32) {
       // decode-size tile: the output is a few KB, direct stores (32 lanes = 32 consecutive features)
       if (ok) {
         const int64_t feat = (int64_t)col0 + q * 32 + lane;
@@ -303,6 +452,21 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
       }
 
     }
+  }
+  (void)epi_ok;
+  if constexpr (CL == 1) {
+    (void)rows_valid;
+    __syncwarp();
+    cluster_sync_all();  // every CTA of the cluster has staged its partial tile
+    if (warp >= 2) {
+      const int q = warp & 3;
+      switch (gridDim.z) {
+        case 2: cluster_finish<2>(a, smem, q, lane, col0, row0, epi_ok); break;
+        case 4: cluster_finish<4>(a, smem, q, lane, col0, row0, epi_ok); break;
+        default: cluster_finish<8>(a, smem, q, lane, col0, row0, epi_ok); break;
+      }
+    }
+    cluster_sync_all();  // nobody leaves while a peer may still read its tile
   }
   tc_fence_before();
   __syncthreads();
@@ -531,15 +695,59 @@ int launch_tn(Ctx* c, const LinearBf16Plan& plan, const CUtensorMap& tmX, const 
   using C = TcCfg<TN>;
   static bool attr_set = false;
   if (!attr_set) {
-    RB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<TN, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     attr_set = true;
   }
-  RB_CUDA(launch_k(linear_tc_kernel<TN>, grid, dim3(192), (size_t)C::SMEM, c->stream, c->use_pdl, plan.tmW, tmX, a));
+  RB_CUDA(launch_k(linear_tc_kernel<TN, 0>, grid, dim3(192), (size_t)C::SMEM, c->stream, c->use_pdl, plan.tmW, tmX, a));
   ++g_launch_total;
   return REWB200_OK;
 }
 
 }  // namespace
+
+bool linear_tc_cluster_ok(Ctx* c, const LinearBf16Plan& plan, int64_t M, int ksplit) {
+  return c->splitk_cluster != 0 && c->linear_impl == 2 && plan.groups == 0 && M >= 1 && M <= 32 &&
+         (ksplit == 2 || ksplit == 4 || ksplit == 8);
+}
+
+int linear_tc_cluster_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int ksplit,
+                             float* out, int64_t ldo, const QkvPostArgs* fuse_qkv) {
+  RB_REQUIRE(linear_tc_cluster_ok(c, plan, M, ksplit), "cluster split-K: at most 32 rows and 2, 4 or 8 splits");
+  RB_REQUIRE(ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0, "bf16 Linear: activations must be 16-byte aligned rows");
+  using C = TcCfg<32>;
+  CUtensorMap tmX;
+  RB_TRY(make_tmap_2d_bf16(&tmX, x, (uint64_t)plan.K, (uint64_t)M, (uint64_t)ldx * 2, 64, 32));
+  TcArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = M;
+  a.N = plan.N;
+  a.K = plan.K;
+  const int nkb = (int)((plan.K + BK - 1) / BK);
+  a.kb_per_split = (nkb + ksplit - 1) / ksplit;
+  a.epi = EPI_PARTIAL_F32;
+  a.out = out;
+  a.ldo = ldo;
+  a.split_stride = 0;
+  a.bias = nullptr;
+  a.status = c->d_status;
+  if (fuse_qkv) {
+    RB_REQUIRE(fuse_qkv->act_dtype == REWB200_BF16 && fuse_qkv->hd % 2 == 0 &&
+                   (int64_t)(fuse_qkv->nh + 2 * fuse_qkv->kvh) * fuse_qkv->hd == plan.N,
+               "fused q|k|v epilogue: bf16 activations and a weight of nq + 2 nkv columns");
+    a.fuse_qkv = 1;
+    a.qp = *fuse_qkv;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    RB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<32, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+    attr_set = true;
+  }
+  dim3 grid((unsigned)((plan.N + BM - 1) / BM), 1u, (unsigned)ksplit);
+  RB_CUDA(launch_k_cluster(linear_tc_kernel<32, 1>, grid, dim3(192), (size_t)C::SMEM, c->stream, c->use_pdl,
+                           dim3(1, 1, (unsigned)ksplit), plan.tmW, tmX, a));
+  ++g_launch_total;
+  return REWB200_OK;
+}
 
 // Same contract as linear_bf16_launch (ungrouped).
 int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, int ksplit,
@@ -553,6 +761,7 @@ int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t 
   CUtensorMap tmX;
   RB_TRY(make_tmap_2d_bf16(&tmX, x, (uint64_t)plan.K, (uint64_t)M, (uint64_t)ldx * 2, 64, TN));
   TcArgs a;
+  memset(&a, 0, sizeof(a));
   a.M = M;
   a.N = plan.N;
   a.K = plan.K;

@@ -247,6 +247,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "prefill") {
     RB_REQUIRE(v == "persistent" || v == "tile", "option prefill: expected persistent or tile");
     c->prefill_persistent = v == "persistent";
+  } else if (k == "splitk") {
+    RB_REQUIRE(v == "cluster" || v == "slabs" || v == "qkv" || v == "out", "option splitk: expected cluster, slabs, qkv or out");
+    c->splitk_cluster = v == "cluster" ? 3 : v == "qkv" ? 1 : v == "out" ? 2 : 0;
   } else if (k == "norm") {
     RB_REQUIRE(v == "cluster" || v == "row", "option norm: expected cluster or row");
     c->norm_cluster = v == "cluster";

@@ -180,3 +180,39 @@ def test_bf16_decode_norm_kernels_agree(rb, norm_kind, d_model):
     a, b = outs["cluster"], outs["row"]
     assert np.isfinite(a[0]).all() and rel_l2(a[0], b[0]) <= 2e-3
     assert np.isfinite(a[1]).all() and rel_l2(a[1], b[1]) <= 5e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim,n_heads,n_kv", [(128, 8, 2), (64, 6, 3)])
+def test_bf16_decode_cluster_splitk_matches_slabs_and_oracle(rb, orc, head_dim, n_heads, n_kv):
+    """With option splitk=cluster, steps of at most 32 rows sum their split-K slices inside thread-block
+    clusters and the q|k|v launch finishes bias, RoPE and the cache write in its epilogue; splitk=slabs
+    (the default) leaves f32 slabs for the next kernel.  Same sums in the same order: the logits of a
+    21-row prompt (3 sequences x 7 tokens) and of decode steps agree to bf16 rounding of q/k, and both
+    stay within the bf16 tolerance of the oracle."""
+    from rew_b200 import _lib
+    cfg = W.ModelConfig(vocab=512, d_model=1024, n_layers=2, n_heads=n_heads, n_kv_heads=n_kv, head_dim=head_dim, ffn=2048,
+                        max_seq=128, theta=10000.0, dtype=_lib.BF16, mask_kind=1)
+    t = [orc.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(cfg, seed=9, std=0.03, trivial_affine=False)]
+    B, S = 3, 7
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+    outs = {}
+    for mode in ("cluster", "slabs"):
+        rb.set_option("splitk", mode)
+        try:
+            sess = rb.CausalLM(cfg).load(t).session(B, 64)
+            nxt, first = sess.forward(prompt, want_logits=True)
+            ids, last = sess.decode(4, want_logits=True)
+            outs[mode] = (nxt, first, ids, last)
+        finally:
+            rb.set_option("splitk", "slabs")
+    a, b = outs["cluster"], outs["slabs"]
+    assert np.isfinite(a[1]).all() and np.isfinite(a[3]).all()
+    assert rel_l2(a[1], b[1]) <= 2e-3
+    want = orc.model_forward(cfg, t, prompt, 0, True)[:, -1]
+    assert rel_l2(a[1], want) <= 2e-2
+    if np.array_equal(a[0], b[0]) and np.array_equal(a[2], b[2]):
+        assert rel_l2(a[3], b[3]) <= 5e-3
+    seq = np.concatenate([prompt, a[0][:, None], a[2][:, :3]], 1)
+    want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
+    assert rel_l2(a[3], want) <= 2e-2
