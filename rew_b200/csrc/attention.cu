@@ -50,6 +50,7 @@ struct AttnDev {
   float* part_o;    // [B][nh][nsplit][hd]
   float* part_ml;   // [B][nh][nsplit][2]
   int nsplit;
+  int early_kv;     // see AttnArgs::kv_tail_only
   int* status;
 };
 
@@ -211,13 +212,22 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     pdl_launch_dependents();
   }
   __syncthreads();
-  pdl_wait();
 
+  // Inside the engine's step, sequence lengths and block tables were written at least two kernels back
+  // in the stream (every kernel of the chain waits on its predecessor before it ends), and the kernel
+  // just before this one writes only the newest cache row, which lies in the last tile.  Then (early_kv)
+  // every other K/V tile can be requested before griddepcontrol.wait, while that predecessor still runs.
+  if (!a.early_kv) pdl_wait();
   const int kv_len = kv_len_of(a, b);
   const int ntiles = (kv_len + TILE - 1) / TILE;
   const int tps = (ntiles + a.nsplit - 1) / a.nsplit;
   const int t0 = split * tps, t1 = min(ntiles, t0 + tps);
   const int nt_local = max(0, t1 - t0);
+  int early = 0;
+  if (threadIdx.x == 0 && a.early_kv)
+    for (; early < min(ATT_STAGES - 1, nt_local) && t0 + early < ntiles - 1; ++early)
+      load_tile<HD>(smem + early * T::STAGE_BYTES, &full[early], &tmK, &tmV, tile_row0(a, b, hk, t0 + early));
+  pdl_wait();
 
   // Q fragments: rows = heads of this kv head's group (rows >= group are zero).
   uint32_t qf[HD / 16][4];
@@ -236,7 +246,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   }
 
   if (threadIdx.x == 0)
-    for (int i = 0; i < min(ATT_STAGES - 1, nt_local); ++i)
+    for (int i = early; i < min(ATT_STAGES - 1, nt_local); ++i)
       load_tile<HD>(smem + i * T::STAGE_BYTES, &full[i], &tmK, &tmV, tile_row0(a, b, hk, t0 + i));
 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -842,6 +852,7 @@ int attn_launch(Ctx* c, const AttnArgs& h) {
   a.causal = h.causal; a.mask_kind = h.mask_kind;
   a.scale = h.scale != 0.f ? h.scale : 1.0f / sqrtf((float)h.kv.hd);
   a.part_o = nullptr; a.part_ml = nullptr; a.nsplit = 1;
+  a.early_kv = (h.kv_tail_only && h.S == 1) ? 1 : 0;
   a.status = c->d_status;
   RB_REQUIRE(h.nh % h.kv.kvh == 0, "numHeads must be divisible by numKVHeads");
   RB_REQUIRE(h.pos0 != nullptr || h.kv_len_fixed >= 0, "attention needs per-sequence positions or a fixed key length");

@@ -271,6 +271,9 @@ struct AttnArgs {
   int64_t max_kv_len;     // upper bound of keys per sequence (sizes the f32 kernel's shared memory)
   float scale;            // 0: 1/sqrt(head_dim)
   int dtype;
+  int kv_tail_only;       // decode (S == 1): the kernel launched just before this one wrote nothing of K, V or pos0
+                          // except the newest cache row, so older K/V tiles may be requested before the stream
+                          // dependency resolves.  Leave 0 unless the caller knows its launch order.
   float* scratch;         // split-KV partials (bf16 decode)
   size_t scratch_bytes;
   const CUtensorMap* tmK; // bf16: TMA maps over the K / V rows ([rows][head_dim], box 64x64)

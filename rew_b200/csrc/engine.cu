@@ -680,6 +680,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     aa.max_kv_len = s->max_len;
     aa.scale = 0.f;
     aa.dtype = dt;
+    aa.kv_tail_only = 1;  // q|k|v post-processing, launched just before, appends one row per sequence
     aa.scratch = s->attn_scratch;
     aa.scratch_bytes = s->attn_scratch_bytes;
     if (dt == REWB200_BF16) {
