@@ -1596,27 +1596,41 @@ int rewb200_session_profile_linears(rewb200_session* s, int iters, float* ms_per
   const int64_t rows = s->B, d = m->cfg.d_model;
   int64_t bytes = 0;
   int launches = 0;
+  const int pm = c->profile_mask;  // option profile_linears: which of the launches to time
   auto one_step = [&](bool count) -> int {
     for (LayerDev& L : m->layers) {
       if (L.moe || L.ffn_local == 0) return fail("linear profiling covers dense decoder blocks only");
       // algorithmic bytes of one Linear: weights (bf16, or NF4 codes + scales) + activations in + result out
       auto wbytes = [&](const LinW& w) { return w.quant ? w.K * w.N / 2 + w.K * (w.N / 64) * 2 : w.K * w.N * 2; };  // codes + bf16 scale pairs
       int ks = 1;
-      RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks));
-      if (count) bytes += wbytes(L.qkv) + rows * L.qkv.K * 2 + (int64_t)ks * rows * L.qkv.N * 4;
-      RB_TRY(run_linear(s, L.o, s->attn, m->nq, rows, true, 0, s->part, d, &ks));
-      if (count) bytes += wbytes(L.o) + rows * L.o.K * 2 + (int64_t)ks * rows * L.o.N * 4;
-      RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr));
-      if (count) bytes += wbytes(L.gu) + rows * L.gu.K * 2 + rows * L.ffn_local * 2;
-      RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
-      if (count) bytes += wbytes(L.down) + rows * L.down.K * 2 + (int64_t)ks * rows * L.down.N * 4;
-      if (count) launches += 4;
+      if (pm & 1) {
+        RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks));
+        if (count) bytes += wbytes(L.qkv) + rows * L.qkv.K * 2 + (int64_t)ks * rows * L.qkv.N * 4;
+        if (count) ++launches;
+      }
+      if (pm & 2) {
+        RB_TRY(run_linear(s, L.o, s->attn, m->nq, rows, true, 0, s->part, d, &ks));
+        if (count) bytes += wbytes(L.o) + rows * L.o.K * 2 + (int64_t)ks * rows * L.o.N * 4;
+        if (count) ++launches;
+      }
+      if (pm & 4) {
+        RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr));
+        if (count) bytes += wbytes(L.gu) + rows * L.gu.K * 2 + rows * L.ffn_local * 2;
+        if (count) ++launches;
+      }
+      if (pm & 8) {
+        RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
+        if (count) bytes += wbytes(L.down) + rows * L.down.K * 2 + (int64_t)ks * rows * L.down.N * 4;
+        if (count) ++launches;
+      }
     }
-    RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->logits, m->vocab_l, m->lm.b,
-                              nullptr, 0));
-    if (count) {
-      bytes += (m->lm.K * m->lm.N + rows * m->lm.K) * 2 + rows * m->lm.N * 4;
-      launches += 1;
+    if (pm & 16) {
+      RB_TRY(linear_bf16_launch(c, m->lm.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->logits, m->vocab_l, m->lm.b,
+                                nullptr, 0));
+      if (count) {
+        bytes += (m->lm.K * m->lm.N + rows * m->lm.K) * 2 + rows * m->lm.N * 4;
+        launches += 1;
+      }
     }
     return REWB200_OK;
   };

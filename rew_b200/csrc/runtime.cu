@@ -247,6 +247,10 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "prefill") {
     RB_REQUIRE(v == "persistent" || v == "tile", "option prefill: expected persistent or tile");
     c->prefill_persistent = v == "persistent";
+  } else if (k == "profile_linears") {
+    const int mask = atoi(v.c_str());
+    RB_REQUIRE(mask >= 1 && mask <= 31, "option profile_linears: a bit mask 1..31 (1 q|k|v, 2 o, 4 gate|up, 8 down, 16 lm_head)");
+    c->profile_mask = mask;
   } else if (k == "splitk") {
     RB_REQUIRE(v == "cluster" || v == "slabs" || v == "qkv" || v == "out", "option splitk: expected cluster, slabs, qkv or out");
     c->splitk_cluster = v == "cluster" ? 3 : v == "qkv" ? 1 : v == "out" ? 2 : 0;
