@@ -142,6 +142,39 @@ __global__ void swiglu_slabs_kernel(const float* part, int ksplit, int64_t rows,
   out[i] = __float2bfloat16_rn((g * sig) * u);
 }
 
+// bf16 gate|up launched with split-K: sums the slabs, which hold the engine's interleaved column order
+// (groups of 8 gate columns followed by their 8 up columns), adds the biases and applies SwiGLU.
+// One thread per group of eight outputs.
+__global__ void swiglu_slabs_il_kernel(const float* part, int ksplit, int64_t rows, int64_t f, const float* bias_il, bf16* out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // group index
+  const int64_t gpr = f / 8;
+  if (i >= rows * gpr) return;
+  const int64_t r = i / gpr, gidx = i % gpr;
+  float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < ksplit; ++s) {
+    const float4* p = reinterpret_cast<const float4*>(part + ((int64_t)s * rows + r) * 2 * f + gidx * 16);
+    const float4 a0 = p[0], a1 = p[1], b0 = p[2], b1 = p[3];
+    g[0] += a0.x; g[1] += a0.y; g[2] += a0.z; g[3] += a0.w; g[4] += a1.x; g[5] += a1.y; g[6] += a1.z; g[7] += a1.w;
+    u[0] += b0.x; u[1] += b0.y; u[2] += b0.z; u[3] += b0.w; u[4] += b1.x; u[5] += b1.y; u[6] += b1.z; u[7] += b1.w;
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 8; j += 2) {
+    float v[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float gg = g[j + h] + (bias_il ? bias_il[gidx * 16 + j + h] : 0.f);
+      const float uu = u[j + h] + (bias_il ? bias_il[gidx * 16 + 8 + j + h] : 0.f);
+      v[h] = gg * (1.0f / (1.0f + __expf(-gg))) * uu;
+    }
+    const __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
+    o[j / 2] = *reinterpret_cast<const uint32_t*>(&pk);
+  }
+  *reinterpret_cast<uint4*>(out + r * f + gidx * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // End of a step: publish the sampled ids, make them the next step's input,
 // advance positions and the step counter.
 // `active` (optional): lanes with 0 keep their token and position and report -1.
@@ -362,8 +395,10 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
     RB_CUDA(cudaMalloc(&s->attn, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
     RB_CUDA(cudaMalloc(&s->h, (size_t)rows * std::max<int64_t>(fmax, 1) * es));
     const int64_t widest = std::max<int64_t>(m->nqkv, c.d_model);
-    s->part_bytes = (size_t)rows * widest * sizeof(float) * 16;  // up to 16 split-K slabs at decode sizes
-    if (rows > 32) s->part_bytes = (size_t)rows * widest * sizeof(float);
+    // up to 16 split-K slabs of the widest residual-side Linear, or 4 of gate|up, at steps of at most 64 rows
+    const size_t small_rows = (size_t)std::min<int64_t>(rows, 64);
+    s->part_bytes = small_rows * std::max<size_t>(16 * widest, 4 * 2 * fmax) * sizeof(float);
+    s->part_bytes = std::max(s->part_bytes, (size_t)rows * widest * sizeof(float));
     if (c.weight_quant)  // the quantised gate|up GEMV leaves up to 4 slabs of [32][2f] here at decode sizes
       s->part_bytes = std::max(s->part_bytes, (size_t)32 * std::max<size_t>(16 * widest, 4 * 2 * fmax) * sizeof(float));
     RB_CUDA(cudaMalloc((void**)&s->part, s->part_bytes));
@@ -446,6 +481,20 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
       }
     }
     if (ksplit_out) *ksplit_out = ks;
+    if (!partial && epi == EPI_SWIGLU_BF16 && rows <= 64 && w.N % 16 == 0) {
+      // a gate|up with too few feature tiles to fill the GPU: split K, then sum + SwiGLU in a second small launch
+      int kg = std::min(4, linear_bf16_pick_ksplit(c, rows, w.K, w.N));
+      while (kg > 1 && (size_t)kg * rows * w.N * sizeof(float) > s->part_bytes) kg /= 2;
+      if (kg > 1) {
+        RB_TRY(linear_bf16_launch(c, w.plan, (const bf16*)x, ldx, rows, EPI_PARTIAL_F32, kg, s->part, w.N, nullptr, nullptr, 0));
+        const int64_t n = rows * (w.N / 16);
+        RB_REQUIRE(ldo == w.N / 2, "SwiGLU output rows must be dense");
+        RB_CUDA(launch_k(swiglu_slabs_il_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, c->stream, c->use_pdl,
+                         (const float*)s->part, kg, rows, w.N / 2, (const float*)w.b, (bf16*)out));
+        ++g_launch_total;
+        return REWB200_OK;
+      }
+    }
     return linear_bf16_launch(c, w.plan, (const bf16*)x, ldx, rows, partial ? EPI_PARTIAL_F32 : epi, ks, out, ldo,
                               partial ? nullptr : w.b, nullptr, 0);
   }

@@ -273,7 +273,7 @@ int linear_bf16_plan(LinearBf16Plan* plan, const bf16* W, int64_t K, int64_t N, 
 // Enough CTAs to keep two resident per SM, but never K slices shorter than 8
 // k-blocks (512 rows): shorter slices spend their time filling the pipeline.
 int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N) {
-  if (M > 32) return 1;
+  if (M > 64) return 1;  // one token tile per feature tile up to here: the weights are streamed once either way
   const int tiles = (int)((N + BN - 1) / BN);
   const int nkb = (int)((K + BK - 1) / BK);
   const int target = 2 * c->sm_count;
