@@ -36,6 +36,10 @@ int slab_sum_to_launch(Ctx* c, const float* part, int nsplit, int64_t slab_elems
 int epoch_bump_launch(Ctx* c, int* epoch, int by);
 int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_peer);
 int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi);
+int moe_route_slabs_launch(Ctx* c, const float* logits, int nsplit, int64_t split_stride, const float* bias, int64_t N, int E,
+                           int k, float* topw, int* topi);
+int moe_group_local_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d, int n_experts,
+                           int* offsets, void* xs, int* pair_pos);
 int moe_reset_launch(Ctx* c, int* cursor, int n_cursor, int* count, int n_count, int* meta, int n_meta);
 int moe_dispatch_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d,
                         int experts_per_rank, int capacity, int* cursor, void* send_x, int* send_meta, int* pair_slot);
@@ -406,7 +410,7 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
     if (c.n_routed > 0) {
       const int ep = c.ep_size, k = c.top_k, E_l = c.n_routed / ep;
       const int64_t cap = rows * k, slots = cap * ep;
-      RB_CUDA(cudaMalloc((void**)&s->moe_logits, (size_t)rows * c.n_routed * sizeof(float)));
+      RB_CUDA(cudaMalloc((void**)&s->moe_logits, (size_t)std::max<int64_t>(rows, 8 * std::min<int64_t>(rows, 64)) * c.n_routed * sizeof(float)));  // or 8 split-K slabs of a small step
       RB_CUDA(cudaMalloc((void**)&s->moe_topw, (size_t)rows * k * sizeof(float)));
       RB_CUDA(cudaMalloc((void**)&s->moe_topi, (size_t)rows * k * sizeof(int)));
       RB_CUDA(cudaMalloc((void**)&s->moe_ints, (size_t)(ep + 3 * (E_l + 1) + 3 * slots + rows * k) * sizeof(int)));
@@ -514,12 +518,23 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate) {
   const int64_t d = cf.d_model, f = X.f;
   const int k = cf.top_k, ep = cf.ep_size, E_l = X.E_l;
   const int dt = cf.dtype;
-  if (dt == REWB200_BF16)
-    RB_TRY(linear_bf16_launch(c, X.router.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->moe_logits, cf.n_routed,
-                              X.router.b, nullptr, 0));
-  else
-    RB_TRY(gemm_f32_launch(c, (const float*)s->xn, (const float*)X.router.w, X.router.b, s->moe_logits, rows, d, cf.n_routed));
-  RB_TRY(moe_route_launch(c, s->moe_logits, rows, cf.n_routed, k, s->moe_topw, s->moe_topi));
+  if (dt == REWB200_BF16 && rows <= 64) {
+    // the router has one feature tile: split K over several CTAs, the routing kernel sums the slabs
+    const int nkb = (int)((d + 63) / 64);
+    int ks = 1;
+    while (ks < 8 && nkb / (ks * 2) >= 4) ks *= 2;
+    RB_TRY(linear_bf16_launch(c, X.router.plan, (const bf16*)s->xn, d, rows, EPI_PARTIAL_F32, ks, s->moe_logits, cf.n_routed,
+                              nullptr, nullptr, 0));
+    RB_TRY(moe_route_slabs_launch(c, s->moe_logits, ks, rows * cf.n_routed, X.router.b, rows, cf.n_routed, k, s->moe_topw,
+                                  s->moe_topi));
+  } else {
+    if (dt == REWB200_BF16)
+      RB_TRY(linear_bf16_launch(c, X.router.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->moe_logits, cf.n_routed,
+                                X.router.b, nullptr, 0));
+    else
+      RB_TRY(gemm_f32_launch(c, (const float*)s->xn, (const float*)X.router.w, X.router.b, s->moe_logits, rows, d, cf.n_routed));
+    RB_TRY(moe_route_launch(c, s->moe_logits, rows, cf.n_routed, k, s->moe_topw, s->moe_topi));
+  }
   if (dt == REWB200_F32) {
     // parity path: every local expert on every token, masked by its routing weight, as the reference does
     for (int e = 0; e < E_l; ++e) {
@@ -547,6 +562,17 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate) {
   int* recv_meta = send_meta + slots;
   int* slot_pos = recv_meta + slots;
   int* pair_slot = slot_pos + slots;
+  if (ep == 1 && cap <= 2048) {
+    // every expert is local and the step is small: one kernel sorts the pairs by expert and copies the
+    // rows, the combine reads the expert outputs in place (no slot arrays, no atomics, no return copy)
+    RB_TRY(moe_group_local_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, offsets, s->moe_xs, pair_slot));
+    const int max_rows_l = (int)std::min<int64_t>(rows, cap);
+    RB_TRY(linear_bf16_launch(c, X.plan_gu, (const bf16*)s->moe_xs, d, cap, EPI_SWIGLU_BF16, 1, s->moe_hs, f, X.gu_b, offsets,
+                              max_rows_l));
+    RB_TRY(linear_bf16_launch(c, X.plan_down, (const bf16*)s->moe_hs, f, cap, EPI_BIAS_F32, 1, s->moe_ys, d, X.down_b, offsets,
+                              max_rows_l));
+    return moe_combine_launch(c, s->moe_ys, pair_slot, s->moe_topw, rows, k, d, s->part, accumulate ? 1 : 0);
+  }
   RB_TRY(moe_reset_launch(c, cursor, ep, count, E_l + 1, send_meta, (int)slots));
   RB_TRY(moe_dispatch_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, (int)cap, cursor, s->moe_send, send_meta, pair_slot));
   const void* rx = s->moe_send;

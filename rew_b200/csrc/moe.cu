@@ -18,7 +18,9 @@ namespace {
 
 constexpr int MAX_E_PER_LANE = 8;  // E <= 256
 
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int64_t N, int E, int k,
+// logits: nsplit slabs [N][E] split_stride apart, summed in slab order, plus bias (may be null).
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int nsplit, int64_t split_stride,
+                                                        const float* __restrict__ bias, int64_t N, int E, int k,
                                                         float* __restrict__ topw, int* __restrict__ topi) {
   pdl_launch_dependents();
   pdl_wait();
@@ -31,7 +33,13 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 #pragma unroll
   for (int i = 0; i < MAX_E_PER_LANE; ++i) {
     const int e = lane + 32 * i;
-    p[i] = (e < E) ? lr[e] : -INFINITY;
+    float v = -INFINITY;
+    if (e < E) {
+      v = 0.f;
+      for (int sp = 0; sp < nsplit; ++sp) v += lr[sp * split_stride + e];
+      if (bias) v += bias[e];
+    }
+    p[i] = v;
     mx = fmaxf(mx, p[i]);
   }
 #pragma unroll
@@ -178,6 +186,47 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ r
   for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
 }
 
+template <typename T>
+__global__ void __launch_bounds__(128) moe_group_local_kernel(const T* __restrict__ x, const int* __restrict__ topi, int n_pairs,
+                                                              int k, int64_t d, int n_experts, int* offsets, T* xs,
+                                                              int* pair_pos) {
+  __shared__ int s_red[4];
+  __shared__ int s_hist[32 * MAX_E_PER_LANE + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  const int e = topi[pair];
+  int before = 0;  // pairs of lower experts, and earlier pairs of the same expert
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int ep = topi[p];
+    before += (ep < e || (ep == e && p < pair)) ? 1 : 0;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = before;
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i <= n_experts; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  const int pos = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+  if (threadIdx.x == 0) pair_pos[pair] = pos;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(pair / k) * d);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (int64_t)pos * d);
+  const int n16 = (int)(d * sizeof(T) / 16);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+  if (blockIdx.x == 0) {
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&s_hist[topi[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int i = 0; i < n_experts; ++i) {
+        offsets[i] = acc;
+        acc += s_hist[i];
+      }
+      offsets[n_experts] = acc;
+    }
+  }
+}
+
 // ret[slot] = ys[slot_pos[slot]] (zeros for empty slots): results back in the sender's slot order.
 __global__ void __launch_bounds__(128) moe_return_kernel(const float* __restrict__ ys, const int* __restrict__ slot_pos,
                                                          int64_t d, float* ret) {
@@ -268,13 +317,34 @@ int moe_combine_launch(Ctx* c, const float* back, const int* pair_slot, const fl
   return REWB200_OK;
 }
 
-int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi) {
+int moe_route_slabs_launch(Ctx* c, const float* logits, int nsplit, int64_t split_stride, const float* bias, int64_t N, int E,
+                           int k, float* topw, int* topi) {
   RB_REQUIRE(E >= 1 && E <= 32 * MAX_E_PER_LANE, "MoE routing supports up to 256 experts");
   RB_REQUIRE(k >= 1 && k <= E, "initDeepSeekMoE: numExpertsPerTok must be in 1..numRouted");
   if (N == 0) return REWB200_OK;
-  RB_CUDA(launch_k(moe_route_kernel, dim3((unsigned)((N + 3) / 4)), dim3(128), 0, c->stream, c->use_pdl, logits, N, E, k,
-                   topw, topi));
+  RB_CUDA(launch_k(moe_route_kernel, dim3((unsigned)((N + 3) / 4)), dim3(128), 0, c->stream, c->use_pdl, logits, nsplit,
+                   split_stride, bias, N, E, k, topw, topi));
   ++g_launch_total;
+  return REWB200_OK;
+}
+int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi) {
+  return moe_route_slabs_launch(c, logits, 1, 0, nullptr, N, E, k, topw, topi);
+}
+
+// One rank owning every expert: pos[pair] = row of pair (token, j) in the expert-sorted activation matrix
+// (experts ascending, pairs ascending inside an expert, so the order is the same on every run), the row
+// is copied there, and block 0 writes the experts' row offsets for the grouped GEMMs.
+int moe_group_local_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d, int n_experts,
+                           int* offsets, void* xs, int* pair_pos) {
+  if (tokens == 0) return REWB200_OK;
+  RB_REQUIRE((d * dtype_size(dtype)) % 16 == 0, "MoE dispatch needs rows that are multiples of 16 bytes");
+  RB_REQUIRE(n_experts <= 32 * MAX_E_PER_LANE, "MoE routing supports up to 256 experts");
+  if (dtype == REWB200_BF16)
+    RB_LAUNCH(moe_group_local_kernel<bf16>, tokens * k, 128, (const bf16*)x, topi, (int)(tokens * k), k, d, n_experts, offsets,
+              (bf16*)xs, pair_pos);
+  else
+    RB_LAUNCH(moe_group_local_kernel<float>, tokens * k, 128, (const float*)x, topi, (int)(tokens * k), k, d, n_experts, offsets,
+              (float*)xs, pair_pos);
   return REWB200_OK;
 }
 
