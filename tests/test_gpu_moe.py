@@ -109,3 +109,29 @@ def test_moe_every_token_to_one_expert_is_handled(rb, orc):
     seq = np.concatenate([prompt, nxt[:, None], ids[:, :3]], 1)
     want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
     assert rel_l2(last, want) <= 2e-2
+
+
+def test_moe_local_grouping_matches_slot_path_and_oracle(rb, orc):
+    """On one rank, steps of at most 2048 (token, expert) pairs sort the pairs by expert in one kernel;
+    larger ones go through the per-peer slot arrays that expert parallelism uses.  An 800-token prompt
+    (2400 pairs) fed at once takes the slot path, the same prompt fed in two chunks the sorting kernel:
+    both match the oracle, with routing forced by the gate bias so that no near-tie can flip."""
+    from rew_b200 import _lib
+    cfg = _moe_cfg(_lib.BF16, head_dim=64, n_heads=2, n_kv_heads=2)
+    t = [orc.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(cfg, seed=29, std=0.05)]
+    names = [n for n, _ in W.tensor_specs(cfg)]
+    for l in (1, 2):
+        b = np.zeros(8, np.float32)
+        b[[0, 3, 7]] = 50.0
+        t[names.index("model.layers.%d.moe.gate.bias" % l)] = b
+    B, S = 8, 100
+    prompt = np.random.default_rng(12).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+    want = orc.model_forward(cfg, t, prompt, 0, True)[:, -1]
+    sess = rb.CausalLM(cfg).load(t).session(B, 112)
+    _, whole = sess.forward(prompt, want_logits=True)
+    sess.reset()
+    sess.forward(prompt[:, :50])
+    _, chunked = sess.forward(prompt[:, 50:], want_logits=True)
+    assert rel_l2(whole, want) <= 2e-2
+    assert rel_l2(chunked, want) <= 2e-2
+    assert rel_l2(chunked, whole) <= 1e-2
