@@ -9,6 +9,7 @@ N(0, 0.02) generated on the device, uniform random prompt ids):
 
     l8_b32   Llama-3-8B-shaped, bf16, batch 32, prompt 512   (default)
     l8_b1    same model, batch 1
+    l8_b128  same model, batch 128, prompt 256 (the 128-row decode tile)
     l70_b16  Llama-3-70B-shaped, bf16, batch 16, prompt 1024; with --gpus N > 1 the model is
              tensor-parallel over the N ranks (heads, FFN columns and vocabulary sharded, NCCL
              all-reduce after o-proj and down-proj): strong scaling
@@ -48,6 +49,7 @@ WORKLOADS = {
     "l8_b1": dict(model="llama3_8b", batch=1, prompt=512),
     "tiny": dict(model="tiny_llama", batch=1, prompt=32),
     "l70_b16": dict(model="llama3_70b", batch=16, prompt=1024, parallel="tp"),
+    "l8_b128": dict(model="llama3_8b", batch=128, prompt=256),
     "moe_b64": dict(model="deepseek_v2_lite", batch=64, prompt=256, parallel="ep"),
     # the l8 decoder with its block Linears held as NF4 codes (weight-only, QLoRA's frozen base weights)
     "l8_b32_nf4": dict(model="llama3_8b", batch=32, prompt=512, weight_quant=1),

@@ -47,6 +47,7 @@ struct Ctx {
   bool use_pdl = true;
   int linear_impl = 2;       // bf16 Linear: 0 mma.sync, 1 tcgen05 when rows > 32, 2 tcgen05 always (default)
   bool prefill_persistent = true;  // 256-token Linear tiles on the persistent kernel with overlapped epilogue
+  int splitk_max_rows = 256;  // largest step (rows) whose Linear launches may split K
   int profile_mask = 31;      // rewb200_session_profile_linears: bit 0 q|k|v, 1 o, 2 gate|up, 3 down, 4 lm_head
   int splitk_cluster = 0;     // decode-size split-K summed inside thread-block clusters instead of through f32 slabs: bit 0 the q|k|v launch, bit 1 the others (off: measured slower)
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row

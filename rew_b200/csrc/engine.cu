@@ -402,6 +402,7 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
     // up to 16 split-K slabs of the widest residual-side Linear, or 4 of gate|up, at steps of at most 64 rows
     const size_t small_rows = (size_t)std::min<int64_t>(rows, 64);
     s->part_bytes = small_rows * std::max<size_t>(16 * widest, 4 * 2 * fmax) * sizeof(float);
+    s->part_bytes = std::max(s->part_bytes, (size_t)std::min<int64_t>(rows, 256) * 4 * widest * sizeof(float));  // 4 slabs up to 256 rows
     s->part_bytes = std::max(s->part_bytes, (size_t)rows * widest * sizeof(float));
     if (c.weight_quant)  // the quantised gate|up GEMV leaves up to 4 slabs of [32][2f] here at decode sizes
       s->part_bytes = std::max(s->part_bytes, (size_t)32 * std::max<size_t>(16 * widest, 4 * 2 * fmax) * sizeof(float));
@@ -475,6 +476,7 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
     int ks = 1;
     if (partial) {
       ks = linear_bf16_pick_ksplit(c, rows, w.K, w.N);
+      if (rows > 64 && c->linear_impl != 2) ks = 1;  // split-K above 64 rows is exercised on the tcgen05 Linear only
       while (ks > 1 && (size_t)ks * rows * ldo * sizeof(float) > s->part_bytes) ks /= 2;
       // decode-size steps: sum the K slices inside thread-block clusters, one slab (or finished q|k|v) comes out
       const int kc = std::min(ks, 8);

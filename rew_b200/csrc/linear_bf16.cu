@@ -273,14 +273,15 @@ int linear_bf16_plan(LinearBf16Plan* plan, const bf16* W, int64_t K, int64_t N, 
 // Enough CTAs to keep two resident per SM, but never K slices shorter than 8
 // k-blocks (512 rows): shorter slices spend their time filling the pipeline.
 int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N) {
-  if (M > 64) return 1;  // one token tile per feature tile up to here: the weights are streamed once either way
+  if (M > 256 || M > c->splitk_max_rows) return 1;  // up to here one token tile covers the step: the weights are streamed once either way
   const int tiles = (int)((N + BN - 1) / BN);
   const int nkb = (int)((K + BK - 1) / BK);
   const int target = 2 * c->sm_count;
+  // every split is another f32 slab of M rows that the consumer kernel reads back: fewer of them as the step grows
+  const int cap = M <= 64 ? 16 : (M <= 128 ? 4 : 2);
   int split = 1;
-  // stop doubling once the CTA count would overshoot the resident slots by more than a quarter:
-  // every extra split is another f32 slab the consumer kernel has to read back
-  while (tiles * split * 2 <= target + target / 4 && nkb / (split * 2) >= 8 && split < 16) split *= 2;
+  // stop doubling once the CTA count would overshoot the resident slots by more than a quarter
+  while (tiles * split * 2 <= target + target / 4 && nkb / (split * 2) >= 8 && split < cap) split *= 2;
   return split;
 }
 

@@ -251,6 +251,10 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     const int mask = atoi(v.c_str());
     RB_REQUIRE(mask >= 1 && mask <= 31, "option profile_linears: a bit mask 1..31 (1 q|k|v, 2 o, 4 gate|up, 8 down, 16 lm_head)");
     c->profile_mask = mask;
+  } else if (k == "splitk_rows") {
+    const int r = atoi(v.c_str());
+    RB_REQUIRE(r >= 0 && r <= 256, "option splitk_rows: 0..256");
+    c->splitk_max_rows = r;
   } else if (k == "splitk") {
     RB_REQUIRE(v == "cluster" || v == "slabs" || v == "qkv" || v == "out", "option splitk: expected cluster, slabs, qkv or out");
     c->splitk_cluster = v == "cluster" ? 3 : v == "qkv" ? 1 : v == "out" ? 2 : 0;

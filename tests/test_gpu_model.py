@@ -101,14 +101,15 @@ def test_bf16_model_logits_within_tolerance(rb, orc, B, S):
     assert rel_l2(last, want) <= 2e-2
 
 
-def test_bf16_cached_decode_equals_prefill_recompute(rb):
+@pytest.mark.parametrize("B,S,n", [(4, 100, 9), (48, 40, 3), (100, 24, 3), (200, 12, 3)])
+def test_bf16_cached_decode_equals_prefill_recompute(rb, B, S, n):
     """Size-independent property at a wider config: logits after n cached decode steps equal the
-    logits of one prefill over the same tokens (same kernels' math, different schedule)."""
+    logits of one prefill over the same tokens (same kernels' math, different schedule).  The batch
+    sizes cover the decode tiles of 32, 64, 128 and 256 rows, each with its own split-K depth."""
     from rew_b200 import _lib
     cfg = W.ModelConfig(vocab=2048, d_model=1024, n_layers=3, n_heads=8, n_kv_heads=2, head_dim=128, ffn=2816, max_seq=512,
                         theta=500000.0, dtype=_lib.BF16, mask_kind=1)
     model = rb.CausalLM(cfg).init_random(seed=1, std=0.02)
-    B, S, n = 4, 100, 9
     prompt = np.random.default_rng(0).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
     sess = model.session(B, 256)
     first = sess.forward(prompt)
