@@ -34,7 +34,9 @@ constexpr int A_BYTES = 2 * BK * 64 * 2;  // two 64x64 boxes
 
 template <int TN>
 struct TcCfg {
-  static constexpr int STAGES = (TN <= 64) ? 5 : (TN <= 128 ? 5 : 4);
+  // 32 tokens: 5 x 20 KB, 64: 4 x 24 KB, 128: 3 x 32 KB, so that two CTAs share an SM (these tiles serve steps
+  // with a single token tile, where a launch has only as many CTAs as feature tiles x splits); 256: 4 x 48 KB
+  static constexpr int STAGES = TN <= 32 ? 5 : (TN <= 64 ? 4 : (TN <= 128 ? 3 : 4));
   static constexpr int B_BYTES = TN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
