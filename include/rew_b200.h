@@ -74,6 +74,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            (all launches, only q|k|v with its RoPE / cache-write epilogue, or only the others)
  *   "norm" = "cluster" | "row"               decode-size residual+norm: four CTAs per row exchanging the row
  *                                            statistics through distributed shared memory (default), or one CTA per row
+ *   "attention_merge" = "launch" | "fused"   split-KV decode attention: a second launch combines the splits (default),
+ *                                            or the last CTA of a (sequence, kv head) does
  *   "attention" = "tc" | "mma"               prefill attention with head_dim 128 on tcgen05 (default) or mma.sync
  *   "sampling" = "bucket" | "radix"          top-k / top-p selection: bucket histograms with the
  *                                            radix select as the exact fallback (default), or

@@ -51,6 +51,7 @@ struct AttnDev {
   float* part_ml;   // [B][nh][nsplit][2]
   int nsplit;
   int early_kv;     // see AttnArgs::kv_tail_only
+  int* tickets;     // [B][kvh] zero between launches: the last split of a (sequence, kv head) merges; nullptr: separate merge launch
   int* status;
 };
 
@@ -370,6 +371,38 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
         a.part_ml[pi * 2 + 1] = L;
       }
     }
+  }
+  if (a.nsplit == 1 || a.tickets == nullptr) return;
+  // ---- the CTA that finishes last for this (sequence, kv head) combines the splits: no second launch.
+  // Every CTA publishes its partials, then takes a ticket; the last ticket holder sees all of them.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* tk = a.tickets + (int64_t)b * a.kvh + hk;
+    const int tkt = atomicAdd(tk, 1);
+    s_last = (tkt == a.nsplit - 1) ? 1 : 0;
+    if (s_last) *tk = 0;  // every other split has already taken its ticket: ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < a.group * HD; idx += blockDim.x) {
+    const int row = idx / HD, d = idx % HD;
+    const int head = hk * a.group + row;
+    const int64_t base = ((int64_t)b * a.nh + head) * a.nsplit;
+    // partials come from other SMs: read them from L2
+    float M = -INFINITY;
+    for (int sp = 0; sp < a.nsplit; ++sp) M = fmaxf(M, __ldcg(a.part_ml + (base + sp) * 2));
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, acc = 0.f;
+    for (int sp = 0; sp < a.nsplit; ++sp) {
+      const float f = __expf(__ldcg(a.part_ml + (base + sp) * 2) - Mu);
+      L += __ldcg(a.part_ml + (base + sp) * 2 + 1) * f;
+      acc += __ldcg(a.part_o + (base + sp) * HD + d) * f;
+    }
+    bf16* op = reinterpret_cast<bf16*>(a.out) + b * a.o_sb + head * a.o_sh;
+    op[d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
 }
 
@@ -853,6 +886,7 @@ int attn_launch(Ctx* c, const AttnArgs& h) {
   a.scale = h.scale != 0.f ? h.scale : 1.0f / sqrtf((float)h.kv.hd);
   a.part_o = nullptr; a.part_ml = nullptr; a.nsplit = 1;
   a.early_kv = (h.kv_tail_only && h.S == 1) ? 1 : 0;
+  a.tickets = nullptr;
   a.status = c->d_status;
   RB_REQUIRE(h.nh % h.kv.kvh == 0, "numHeads must be divisible by numKVHeads");
   RB_REQUIRE(h.pos0 != nullptr || h.kv_len_fixed >= 0, "attention needs per-sequence positions or a fixed key length");
@@ -895,13 +929,14 @@ int attn_launch(Ctx* c, const AttnArgs& h) {
       a.part_ml = h.scratch + (size_t)h.B * h.nh * nsplit * a.hd;
     }
     a.nsplit = nsplit;
+    a.tickets = (nsplit > 1 && c->attn_fused_merge && h.B * a.kvh <= Ctx::kTickets) ? c->d_tickets : nullptr;
     dim3 grid((unsigned)nsplit, (unsigned)a.kvh, (unsigned)h.B);
     if (a.hd == 128)
       RB_CUDA(launch_k(attn_decode_kernel<128>, grid, dim3(128), (size_t)ATile<128>::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
     else
       RB_CUDA(launch_k(attn_decode_kernel<64>, grid, dim3(128), (size_t)ATile<64>::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
     ++g_launch_total;
-    if (nsplit > 1) {
+    if (nsplit > 1 && a.tickets == nullptr) {
       RB_CUDA(launch_k(attn_merge_kernel, dim3((unsigned)h.nh, (unsigned)h.B), dim3((unsigned)a.hd), 0, c->stream, c->use_pdl, a));
       ++g_launch_total;
     }

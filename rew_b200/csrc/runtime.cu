@@ -50,6 +50,7 @@ int ctx_check_status(Ctx* c) {
   st = *c->h_status;
   if (st != 0) {
     RB_CUDA(cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream));
+    RB_CUDA(cudaMemsetAsync(c->d_tickets, 0, Ctx::kTickets * sizeof(int), c->stream));  // a kernel that gave up may have left counts behind
     const char* what = st == KS_MBAR_TIMEOUT ? "a bounded mbarrier wait expired"
                        : st == KS_BAD_INDEX  ? "an index was out of range (token id / page / position)"
                        : st == KS_TMEM_TIMEOUT ? "a bounded tensor-memory wait expired"
@@ -175,6 +176,8 @@ int rewb200_init(const int* device_ordinals, int n) {
     RB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     RB_CUDA(cudaMalloc(&c->d_status, 256));
     RB_CUDA(cudaMemset(c->d_status, 0, 256));
+    RB_CUDA(cudaMalloc(&c->d_tickets, Ctx::kTickets * sizeof(int)));
+    RB_CUDA(cudaMemset(c->d_tickets, 0, Ctx::kTickets * sizeof(int)));
     RB_CUDA(cudaMallocHost(&c->h_status, 256));
     c->pinned_bytes = 64u << 20;
     RB_CUDA(cudaMallocHost(&c->pinned, c->pinned_bytes));
@@ -199,6 +202,7 @@ int rewb200_shutdown(void) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     cudaFree(c->d_status);
+    cudaFree(c->d_tickets);
     cudaFreeHost(c->h_status);
     cudaFreeHost(c->pinned);
     cudaStreamDestroy(c->stream);
@@ -251,6 +255,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     const int mask = atoi(v.c_str());
     RB_REQUIRE(mask >= 1 && mask <= 31, "option profile_linears: a bit mask 1..31 (1 q|k|v, 2 o, 4 gate|up, 8 down, 16 lm_head)");
     c->profile_mask = mask;
+  } else if (k == "attention_merge") {
+    RB_REQUIRE(v == "fused" || v == "launch", "option attention_merge: expected fused or launch");
+    c->attn_fused_merge = v == "fused";
   } else if (k == "splitk_rows") {
     const int r = atoi(v.c_str());
     RB_REQUIRE(r >= 0 && r <= 256, "option splitk_rows: 0..256");

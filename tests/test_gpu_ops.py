@@ -161,6 +161,27 @@ def test_attention_bf16_decode(rb, orc, B, nh, kvh, L, hd):
     assert rel_l2(got, orc.gqa_attention(q, k, v, True, 1)) < BF16_TOL
 
 
+def test_attention_bf16_decode_fused_merge_equals_merge_launch(rb, orc):
+    """Split-KV decode: a second launch combines the splits; with option attention_merge=fused the last CTA
+    of a (sequence, kv head) does it inside the kernel.  Same partials, same arithmetic: equal bits.
+    Run twice so that the arrival counters are shown to return to zero."""
+    from rew_b200 import _lib
+    rng = np.random.default_rng(77)
+    B, nh, kvh, L, hd = 3, 8, 2, 1000, 128
+    q = orc.bf16_round(rng.normal(size=(B, nh, 1, hd)))
+    k = orc.bf16_round(rng.normal(size=(B, kvh, L, hd)))
+    v = orc.bf16_round(rng.normal(size=(B, kvh, L, hd)))
+    tq, tk, tv = T(rb, q, _lib.BF16), T(rb, k, _lib.BF16), T(rb, v, _lib.BF16)
+    two = rb.scaledDotProductAttention(tq, tk, tv, True, 1).to_host()
+    rb.set_option("attention_merge", "fused")
+    try:
+        fused = [rb.scaledDotProductAttention(tq, tk, tv, True, 1).to_host() for _ in range(2)]
+    finally:
+        rb.set_option("attention_merge", "launch")
+    assert np.array_equal(fused[0], two) and np.array_equal(fused[1], two)
+    assert rel_l2(two, orc.gqa_attention(q, k, v, True, 1)) < BF16_TOL
+
+
 @pytest.mark.parametrize("B,nh,kvh,S,hd", [(1, 4, 2, 2, 128), (2, 8, 2, 64, 128), (1, 4, 1, 150, 128), (2, 4, 4, 65, 64)])
 @pytest.mark.parametrize("mode", ["plain", "as_written", "standard"])
 def test_attention_bf16_prefill(rb, orc, B, nh, kvh, S, hd, mode):
