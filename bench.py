@@ -396,7 +396,7 @@ def main():
                     # dram read+write per step, scaled from the ncu capture of the gate|up launch
                     # (239.2 MB measured for 236.1 MB algorithmic; profiles/linear_tc_kernel_32_decode_l8.md)
                     "traffic": None if cfg.weight_quant else nbytes.value * 1.013,
-                    "kernel": ("nf4_tc_kernel" if cfg.weight_quant else "linear_tc_kernel<32>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>"), "launches_per_step": nl.value, "ms_per_step": ms.value,
+                    "kernel": ("nf4_tc_kernel" if cfg.weight_quant else "linear_tc_kernel<32, 0>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>"), "launches_per_step": nl.value, "ms_per_step": ms.value,
                     "bytes_per_step": nbytes.value, "peak_source": which}
         # whole decode step against the same roof: weights + KV read once per step
         kv_bytes = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
