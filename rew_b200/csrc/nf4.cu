@@ -13,8 +13,9 @@
 //   sc2 [N/64][K/2] u32    the same scales as bf16 pairs (rows 2j, 2j+1): what the GEMV multiplies by
 // GEMV (rows <= 32) on the 5th-generation tensor core with the WEIGHT operand in tensor memory:
 //   D[128 features][32 tokens] (TMEM, f32) += A[128 features][64 k] (TMEM, bf16) * B[64 k][32 tokens] (smem)
-//   warp 0      TMA producer, 8-stage ring; a stage = the activation tile (32 tokens x 64 k, 128-byte
-//               swizzle) + the tile's 4 KB of codes + the scale pairs of its two groups (bulk copies)
+//   warp 0      TMA producer, two rings: 14 stages of the tile's 4 KB of codes + the scale pairs of its two
+//               groups (bulk copies out of HBM, 56 KB in flight per CTA), 4 stages of the activation tile
+//               (32 tokens x 64 k, 128-byte swizzle, out of L2)
 //   warp 1      one thread issues four tcgen05.mma (K = 16 each) per block of 64 rows, A read from TMEM
 //   warps 2-9   dequantisers: a warp owns the 32 TMEM lanes (features) of its lane quarter and every
 //               other block; a lane reads its feature's 32 code bytes from the stage, turns each byte into a bf16 pair
@@ -123,18 +124,18 @@ __global__ void __launch_bounds__(128) nf4_expand_kernel(const uint8_t* q, const
   }
 }
 
-constexpr int NT_STAGES = 8;
-constexpr int NT_XBYTES = 32 * 128;          // activations of a stage: 32 tokens x 64 k bf16 (128-byte swizzle)
-constexpr int NT_CBYTES = 128 * 32;          // codes of a stage: 128 features x 32 bytes
-constexpr int NT_SBYTES = 2 * 32 * 4;        // scale pairs of a stage: 2 groups x 32 pairs
-constexpr int NT_STAGE = 9 * 1024;           // stage stride (the activation tile must start 1024-byte aligned)
-constexpr int NT_TX = NT_XBYTES + NT_CBYTES + NT_SBYTES;
+constexpr int NT_XST = 4;                    // activation stages: they come out of L2, a short ring is enough
+constexpr int NT_CST = 14;                   // code stages: 56 KB of packed weights in flight per CTA hide the HBM latency
+constexpr int NT_XBYTES = 32 * 128;          // activations of a block: 32 tokens x 64 k bf16 (128-byte swizzle)
+constexpr int NT_CBYTES = 128 * 32;          // codes of a block: 128 features x 32 bytes
+constexpr int NT_SBYTES = 2 * 32 * 4;        // scale pairs of a block: 2 groups x 32 pairs
+constexpr int NT_CSTAGE = NT_CBYTES + NT_SBYTES;   // code stage = codes | scale pairs
 constexpr int NT_DEQ = 8;                    // dequantiser warps
 constexpr int NT_THREADS = (2 + NT_DEQ) * 32;
 constexpr int NT_ABUF = 4;                   // weight-operand buffers in tensor memory
 constexpr int NT_TMEM_COLS = 256;            // D: columns 0-31; A buffer b: columns 32 + 32 b .. +31
 constexpr int NT_LUT_BYTES = 256 * 32 * 4;
-constexpr int NT_SMEM = NT_STAGES * NT_STAGE + NT_LUT_BYTES + 256 + 1024;
+constexpr int NT_SMEM = NT_XST * NT_XBYTES + NT_CST * NT_CSTAGE + NT_LUT_BYTES + 512 + 1024;
 
 __device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
   uint32_t r;
@@ -147,11 +148,14 @@ __global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constan
                                                             int kb_per_split, float* __restrict__ out, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* xs = smem;                                                    // [NT_STAGES]{activations | codes | scale pairs}
-  uint32_t* lut = reinterpret_cast<uint32_t*>(smem + NT_STAGES * NT_STAGE);   // [256 byte values][32 lanes]
+  uint8_t* xs = smem;                                                    // [NT_XST] activation tiles
+  uint8_t* cs = smem + NT_XST * NT_XBYTES;                               // [NT_CST]{codes | scale pairs}
+  uint32_t* lut = reinterpret_cast<uint32_t*>(cs + NT_CST * NT_CSTAGE);  // [256 byte values][32 lanes]
   uint64_t* x_full = reinterpret_cast<uint64_t*>(lut + 256 * 32);
-  uint64_t* x_empty = x_full + NT_STAGES;
-  uint64_t* a_full = x_empty + NT_STAGES;   // [NT_ABUF]
+  uint64_t* x_empty = x_full + NT_XST;
+  uint64_t* c_full = x_empty + NT_XST;      // [NT_CST]
+  uint64_t* c_empty = c_full + NT_CST;      // [NT_CST]
+  uint64_t* a_full = c_empty + NT_CST;      // [NT_ABUF]
   uint64_t* a_empty = a_full + NT_ABUF;     // [NT_ABUF]
   uint64_t* d_full = a_empty + NT_ABUF;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
@@ -163,9 +167,13 @@ __global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constan
   const int nkb = max(0, min(kb_per_split, KB - kb0));
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NT_STAGES; ++s) {
+    for (int s = 0; s < NT_XST; ++s) {
       mbar_init(&x_full[s], 1);
       mbar_init(&x_empty[s], 1);
+    }
+    for (int s = 0; s < NT_CST; ++s) {
+      mbar_init(&c_full[s], 1);
+      mbar_init(&c_empty[s], 4);  // the four lane quarters of the parity that dequantises the block
     }
     for (int b = 0; b < NT_ABUF; ++b) {
       mbar_init(&a_full[b], 4);   // the four lane quarters
@@ -191,29 +199,41 @@ __global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constan
     if (lane == 0) {
       tma_prefetch_desc(&tmX);
       const uint64_t pol_x = policy_evict_last();
-      // a stage = the activation tile (tensor copy) + this tile's 4 KB of codes + the scale pairs of
-      // its two 64-feature groups (plain bulk copies); eight stages deep, so up to 32 KB of codes per
-      // CTA are in flight without costing a register.  Codes and scales do not depend on the previous
+      // Two rings.  Codes (4 KB per block, plain bulk copy) and the scale pairs of the tile's two
+      // 64-feature groups come from HBM: 14 stages, 56 KB in flight per CTA.  The activation tile of a
+      // block (tensor copy) comes out of L2: 4 stages.  Codes and scales do not depend on the previous
       // kernel: the first ring-full is requested before waiting for it.
       const int64_t g0 = ((int64_t)tile * 128) >> 6, G = N >> 6;
-      auto load_weights = [&](int kb, int s) {
-        uint8_t* st = xs + s * NT_STAGE;
-        mbar_expect_tx(&x_full[s], NT_TX);
-        bulk_load_1d(st + NT_XBYTES, q + ((int64_t)tile * KB + kb0 + kb) * NT_CBYTES, NT_CBYTES, &x_full[s]);
+      auto load_codes = [&](int kb) {
+        const int s = kb % NT_CST;
+        uint8_t* st = cs + s * NT_CSTAGE;
+        mbar_expect_tx(&c_full[s], NT_CSTAGE);
+        bulk_load_1d(st, q + ((int64_t)tile * KB + kb0 + kb) * NT_CBYTES, NT_CBYTES, &c_full[s]);
         for (int h = 0; h < 2; ++h) {
           const int64_t g = min(g0 + h, G - 1);  // a half tile past N re-reads the last group (its lanes are never stored)
-          bulk_load_1d(st + NT_XBYTES + NT_CBYTES + h * 128, sc2 + g * (K / 2) + (int64_t)(kb0 + kb) * 32, 128, &x_full[s]);
+          bulk_load_1d(st + NT_CBYTES + h * 128, sc2 + g * (K / 2) + (int64_t)(kb0 + kb) * 32, 128, &c_full[s]);
         }
       };
-      const int pre = min(NT_STAGES, nkb);
-      for (int kb = 0; kb < pre; ++kb) load_weights(kb, kb);
+      auto load_x = [&](int kb) {
+        const int s = kb % NT_XST;
+        mbar_expect_tx(&x_full[s], NT_XBYTES);
+        tma_load_2d_hint(xs + s * NT_XBYTES, &tmX, &x_full[s], (kb0 + kb) * 64, 0, pol_x);
+      };
+      for (int kb = 0; kb < min(NT_CST, nkb); ++kb) load_codes(kb);
       pdl_wait();  // the activations come from the previous kernel
-      for (int kb = 0; kb < pre; ++kb) tma_load_2d_hint(xs + kb * NT_STAGE, &tmX, &x_full[kb], (kb0 + kb) * 64, 0, pol_x);
-      for (int kb = pre; kb < nkb; ++kb) {
-        const int s = kb % NT_STAGES;
-        if (!mbar_wait(&x_empty[s], ((kb / NT_STAGES) - 1) & 1, status)) break;
-        load_weights(kb, s);
-        tma_load_2d_hint(xs + s * NT_STAGE, &tmX, &x_full[s], (kb0 + kb) * 64, 0, pol_x);
+      for (int kb = 0; kb < min(NT_XST, nkb); ++kb) load_x(kb);
+      // block t, once consumed, frees the activation slot of block t + NT_XST and the code slot of t + NT_CST
+      for (int t = 0; t < nkb; ++t) {
+        const int xk = t + NT_XST, ck = t + NT_CST;
+        if (xk >= nkb && ck >= nkb) break;
+        if (xk < nkb) {
+          if (!mbar_wait(&x_empty[xk % NT_XST], ((xk / NT_XST) - 1) & 1, status)) break;
+          load_x(xk);
+        }
+        if (ck < nkb) {
+          if (!mbar_wait(&c_empty[ck % NT_CST], ((ck / NT_CST) - 1) & 1, status)) break;
+          load_codes(ck);
+        }
       }
     }
   } else if (warp == 1) {
@@ -223,13 +243,13 @@ __global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constan
       const uint32_t xs_addr = smem_u32(xs);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int p = kb % NT_ABUF, s = kb % NT_STAGES;
-        ok = mbar_wait(&a_full[p], (kb / NT_ABUF) & 1, status) && mbar_wait(&x_full[s], (kb / NT_STAGES) & 1, status);
+        const int p = kb % NT_ABUF, s = kb % NT_XST;
+        ok = mbar_wait(&a_full[p], (kb / NT_ABUF) & 1, status) && mbar_wait(&x_full[s], (kb / NT_XST) & 1, status);
         if (!ok) break;
         tc::fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t db = tc::smem_desc(xs_addr + s * NT_STAGE + kk * 32, 16, 1024);
+          const uint64_t db = tc::smem_desc(xs_addr + s * NT_XBYTES + kk * 32, 16, 1024);
           tc::umma_bf16_ta(tmem_base, tmem_base + 32 + p * 32 + kk * 8, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
         }
         tc::commit(&x_empty[s]);
@@ -247,12 +267,12 @@ __global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constan
     const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + 32;
     bool ok = true;
     for (int kb = p; kb < nkb; kb += 2) {
-      const int s = kb % NT_STAGES, ab = kb % NT_ABUF, use = kb / NT_ABUF;
-      if (ok) ok = mbar_wait(&x_full[s], (kb / NT_STAGES) & 1, status);
-      const uint8_t* st = xs + s * NT_STAGE;
-      const uint4* cp = reinterpret_cast<const uint4*>(st + NT_XBYTES + (quarter * 32 + lane) * 32);
+      const int s = kb % NT_CST, ab = kb % NT_ABUF, use = kb / NT_ABUF;
+      if (ok) ok = mbar_wait(&c_full[s], (kb / NT_CST) & 1, status);
+      const uint8_t* st = cs + s * NT_CSTAGE;
+      const uint4* cp = reinterpret_cast<const uint4*>(st + (quarter * 32 + lane) * 32);
       const uint4 qa = cp[0], qb = cp[1];
-      const uint4* sp4 = reinterpret_cast<const uint4*>(st + NT_XBYTES + NT_CBYTES + (quarter >> 1) * 128);
+      const uint4* sp4 = reinterpret_cast<const uint4*>(st + NT_CBYTES + (quarter >> 1) * 128);
       const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
       uint32_t r[32];
 #pragma unroll
@@ -267,6 +287,8 @@ __global__ void __launch_bounds__(NT_THREADS) nf4_tc_kernel(const __grid_constan
         r[4 * w + 2] = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o2), s4.z);
         r[4 * w + 3] = hmul2_bf16(*reinterpret_cast<const uint32_t*>(lut_bytes + o3), s4.w);
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c_empty[s]);  // codes and scales are in registers: the stage may be refilled
       if (use >= 1 && ok) {  // the tensor core must have consumed this buffer's previous contents
         ok = mbar_wait(&a_empty[ab], (use - 1) & 1, status);
         tc::fence_after();
