@@ -24,6 +24,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tc.cuh"
 
 namespace rewb {
 namespace {
@@ -75,37 +76,6 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
   return v;
-}
-
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  // start address, leading / stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
-         (1ull << 46) | (2ull << 61);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x * (1.0f / (1.0f + __expf(-x))); }
@@ -264,14 +234,11 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
     pdl_launch_dependents();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)C::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc::alloc(tmem_slot, (uint32_t)C::TMEM_COLS);
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
-  tc_fence_after();
+  tc::fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   bool epi_ok = true;
@@ -314,20 +281,20 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
         const int s = kb % C::STAGES;
         ok = mbar_wait(&full[s], (kb / C::STAGES) & 1, a.status);
         if (!ok) break;
-        tc_fence_after();
+        tc::fence_after();
         const uint32_t sa = smem_base + s * C::STAGE_BYTES;
         const uint32_t sb = sa + A_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BK / 16; ++kk) {
           // A: 16 k-rows of 128 bytes = two 8-row swizzle atoms 1024 B apart (SBO); the second
           //    64-feature box is 8192 B further (LBO).  B: rows of 128 B, 8-row atoms 1024 B apart.
-          const uint64_t da = smem_desc(sa + kk * 2048, A_BYTES / 2, 1024);
-          const uint64_t db = smem_desc(sb + kk * 32, 16, 1024);
-          umma_bf16(tmem_base, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          const uint64_t da = tc::smem_desc(sa + kk * 2048, A_BYTES / 2, 1024);
+          const uint64_t db = tc::smem_desc(sb + kk * 32, 16, 1024);
+          tc::umma_bf16_ss(tmem_base, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&empty[s]);  // stage is free once these MMAs have read it
+        tc::commit(&empty[s]);  // stage is free once these MMAs have read it
       }
-      if (ok) umma_commit(tmem_full);
+      if (ok) tc::commit(tmem_full);
     }
   } else {
     // ---------------- epilogue warps 2..5; TMEM lanes 32*(warp%4) .. +31
@@ -339,7 +306,7 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
     bool ok = true;
     if (nkb > 0) {
       ok = mbar_wait(tmem_full, 0, a.status);
-      tc_fence_after();
+      tc::fence_after();
     }
     pdl_wait();
     if constexpr (CL == 1) {
@@ -347,7 +314,7 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
       uint32_t r[32];
       ok = __all_sync(0xffffffffu, ok);  // the tensor-memory load below is warp-collective
       if (ok && nkb > 0) {
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16), r);
+        tc::ld32(tmem_base + ((uint32_t)(q * 32) << 16), r);
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = 0u;
@@ -364,7 +331,7 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
         const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
         uint32_t r[32];
         if (nkb > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16), r);
+          tc::ld32(tmem_base + ((uint32_t)(q * 32) << 16), r);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
@@ -412,7 +379,7 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
           if (c0 >= rows_valid) break;
           uint32_t r[32];
           if (nkb > 0) {
-            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+            tc::ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
           } else {
   #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0u;
@@ -470,11 +437,11 @@ __global__ void __launch_bounds__(192) linear_tc_kernel(const __grid_constant__ 
     }
     cluster_sync_all();  // nobody leaves while a peer may still read its tile
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
   if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    tc::fence_after();
+    tc::dealloc(tmem_base, (uint32_t)C::TMEM_COLS);
   }
 }
 
@@ -537,14 +504,11 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
     pdl_launch_dependents();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"((uint32_t)C::TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc::alloc(tmem_slot, (uint32_t)C::TMEM_COLS);
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
-  tc_fence_after();
+  tc::fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
@@ -587,25 +551,25 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
         if (j >= 2) {  // the epilogue must have drained this accumulator (tile j - 2)
           ok = mbar_wait(&tmem_empty[buf], ((j >> 1) - 1) & 1, a.status);
           if (!ok) break;
-          tc_fence_after();
+          tc::fence_after();
         }
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * TN);
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % C::STAGES;
           ok = mbar_wait(&full[s], (it / C::STAGES) & 1, a.status);
           if (!ok) break;
-          tc_fence_after();
+          tc::fence_after();
           const uint32_t sa = smem_base + s * C::STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t da = smem_desc(sa + kk * 2048, A_BYTES / 2, 1024);
-            const uint64_t db = smem_desc(sb + kk * 32, 16, 1024);
-            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            const uint64_t da = tc::smem_desc(sa + kk * 2048, A_BYTES / 2, 1024);
+            const uint64_t db = tc::smem_desc(sb + kk * 32, 16, 1024);
+            tc::umma_bf16_ss(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(&empty[s]);
+          tc::commit(&empty[s]);
         }
-        if (ok) umma_commit(&tmem_full[buf]);
+        if (ok) tc::commit(&tmem_full[buf]);
       }
     }
   } else {
@@ -630,7 +594,7 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
       const int rows_valid = (int)min((int64_t)TN, a.M - row0);
       const int buf = j & 1;
       if (ok) ok = mbar_wait(&tmem_full[buf], (j >> 1) & 1, a.status);
-      tc_fence_after();
+      tc::fence_after();
       const int64_t feat = (int64_t)col0 + q * 32 + lane;
       const bool feat_ok = feat < a.N;
       const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
@@ -641,7 +605,7 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
         uint8_t* stg = stg_base + ((c0 >> 5) & 1) * C::STG_BYTES;
         if (ok) {
           uint32_t r[32];
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * TN + c0), r);
+          tc::ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * TN + c0), r);
           if (swiglu || out_f32) {
             // f32 [token][feature]; SwiGLU is applied on the way out, by all 128 threads
 #pragma unroll
@@ -679,16 +643,16 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
         }
       }
       // every epilogue warp has read its part of the accumulator: hand the buffer back
-      tc_fence_before();
+      tc::fence_before();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (et == 0) mbar_arrive(&tmem_empty[buf]);
     }
   }
-  tc_fence_before();
+  tc::fence_before();
   __syncthreads();
   if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    tc::fence_after();
+    tc::dealloc(tmem_base, (uint32_t)C::TMEM_COLS);
   }
 }
 
