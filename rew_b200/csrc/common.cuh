@@ -257,6 +257,8 @@ struct QkvPostArgs {
   int act_dtype;
   KvLayout kv;
   int* status;
+  int early_lookup;       // positions, block tables and RoPE tables predate every kernel that may still be in flight
+                          // (a captured decode step): they may be read before the stream dependency resolves
 };
 int qkv_post_launch(Ctx* c, const QkvPostArgs& a, int64_t B);
 
@@ -276,9 +278,11 @@ struct AttnArgs {
   int64_t max_kv_len;     // upper bound of keys per sequence (sizes the f32 kernel's shared memory)
   float scale;            // 0: 1/sqrt(head_dim)
   int dtype;
-  int kv_tail_only;       // decode (S == 1): the kernel launched just before this one wrote nothing of K, V or pos0
-                          // except the newest cache row, so older K/V tiles may be requested before the stream
-                          // dependency resolves.  Leave 0 unless the caller knows its launch order.
+  int kv_tail_only;       // decode (S == 1): no kernel that may still be in flight writes K, V, pos0 or the block table,
+                          // except for the newest cache row (a captured decode step: everything older predates the
+                          // graph launch), so older K/V tiles may be requested before the stream dependency
+                          // resolves.  A dependent launch starts once its predecessor has STARTED, so distance in
+                          // the stream proves nothing: leave 0 outside a captured step.
   float* scratch;         // split-KV partials (bf16 decode)
   size_t scratch_bytes;
   const CUtensorMap* tmK; // bf16: TMA maps over the K / V rows ([rows][head_dim], box 64x64)

@@ -285,10 +285,11 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
   cg::cluster_group cl = cg::this_cluster();
   const unsigned rank = cl.block_rank();
   pdl_launch_dependents();
-  pdl_wait();
   const int64_t row = blockIdx.x >> 2;
   const int64_t d = a.d, dq = d >> 2, col0 = (int64_t)rank * dq;
   float* xr = a.x_res + row * d;
+  float4 vals[NCH];
+  pdl_wait();
   const TE* erow = nullptr;
   if (a.embed) {
     int64_t id = row;
@@ -301,7 +302,6 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
     }
     erow = reinterpret_cast<const TE*>(a.embed) + id * d;
   }
-  float4 vals[NCH];
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int64_t off = ((int64_t)c * 256 + threadIdx.x) * 4;
@@ -471,7 +471,11 @@ __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
 template <typename TA>
 __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
   pdl_launch_dependents();
-  pdl_wait();
+  // Inside a captured decode step (early_lookup) positions, block tables and RoPE tables were written
+  // before the graph was launched: look them up while the q|k|v Linear drains; only its slabs have to
+  // wait.  Elsewhere a kernel still in flight may be their producer (a dependent launch starts as soon
+  // as its predecessor has STARTED, so "several launches back" proves nothing): wait first.
+  if (!a.early_lookup) pdl_wait();
   const int64_t row = blockIdx.x;
   const int b = (int)(row / a.S), s = (int)(row % a.S);
   const int pos = a.pos0[b] + s;
@@ -503,6 +507,14 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
     const int p = blockIdx.y * blockDim.x + threadIdx.x;
     if (p >= npairs) return;
     const int col = 2 * p;
+    float c0 = 1.f, s0 = 0.f;
+    if (col < nq + nkv) {
+      const int i = (col % hd) / 2;
+      c0 = cr[2 * i];
+      s0 = sr[2 * i];
+    }
+    const float b0 = a.bias ? a.bias[col] : 0.f, b1 = a.bias ? a.bias[col + 1] : 0.f;
+    pdl_wait();
     float v0 = 0.f, v1 = 0.f;
     const float* pp = a.partial + row * ntot + col;
     int sp = 0;
@@ -522,12 +534,10 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
       v1 += t.y;
     }
     if (a.bias) {
-      v0 += a.bias[col];
-      v1 += a.bias[col + 1];
+      v0 += b0;
+      v1 += b1;
     }
     if (col < nq + nkv) {
-      const int i = (col % hd) / 2;
-      const float c0 = cr[2 * i], s0 = sr[2 * i];
       const float r0 = c0 * v0 - s0 * v1;
       const float r1 = s0 * v0 + c0 * v1;
       if (col < nq) {

@@ -652,6 +652,12 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   int* const next = s->d_next + b0;
   const int dt = cf.dtype;
 
+  // A captured decode step is replayed as one graph launch: positions, block tables and all cache rows but
+  // the newest were written before that launch, which is what lets two kernels read them ahead of their
+  // stream dependency.  Plain launches (prefill, REW_B200_NO_GRAPH) chain across calls and get no such promise.
+  cudaStreamCaptureStatus cap_st = cudaStreamCaptureStatusNone;
+  RB_CUDA(cudaStreamIsCapturing(c->stream, &cap_st));
+  const bool in_graph = cap_st == cudaStreamCaptureStatusActive && o.S == 1;
   NormArgs na;
   memset(&na, 0, sizeof(na));
   na.x_res = s->x_res;
@@ -730,6 +736,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     qa.kv.dtype = dt;
     qa.kv_capacity = s->max_len;
     qa.status = c->d_status;
+    qa.early_lookup = in_graph ? 1 : 0;
     RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks, dt == REWB200_BF16 ? &qa : nullptr, &qkv_done));
     if (!qkv_done) {
       qa.nsplit = ks;
@@ -757,7 +764,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     aa.max_kv_len = s->max_len;
     aa.scale = 0.f;
     aa.dtype = dt;
-    aa.kv_tail_only = 1;  // q|k|v post-processing, launched just before, appends one row per sequence
+    aa.kv_tail_only = in_graph ? 1 : 0;  // inside the captured step only the newest cache row is written
     aa.scratch = s->attn_scratch;
     aa.scratch_bytes = s->attn_scratch_bytes;
     if (dt == REWB200_BF16) {
