@@ -41,6 +41,9 @@ int fail(const std::string& msg);  // records msg, returns REWB200_ERR
 struct Ctx {
   int device = -1;
   cudaStream_t stream = nullptr;
+  cudaStream_t side = nullptr;            // second stream for a branch that runs beside the main one (MoE shared experts)
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  bool moe_overlap = true;
   int* d_status = nullptr;   // kernels record KernelStatus codes here
   static constexpr int kTickets = 16384;
   int* d_tickets = nullptr;  // split-KV decode attention: one arrival counter per (sequence, kv head), zero between launches

@@ -512,7 +512,7 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
 // Routed experts of one MoE layer for the normalised rows in s->xn: router, top-k, dispatch to the
 // owning ranks, grouped expert GEMMs, return, weighted combine into slab 0 of s->part
 // (DeepSeekMoE.forward, src/rew/models/deepseek.nim:132-144).
-int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate) {
+int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, float* out = nullptr) {
   rewb200_model* m = s->m;
   Ctx* c = m->c;
   const rewb200_config& cf = m->cfg;
@@ -573,7 +573,7 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate) {
                               max_rows_l));
     RB_TRY(linear_bf16_launch(c, X.plan_down, (const bf16*)s->moe_hs, f, cap, EPI_BIAS_F32, 1, s->moe_ys, d, X.down_b, offsets,
                               max_rows_l));
-    return moe_combine_launch(c, s->moe_ys, pair_slot, s->moe_topw, rows, k, d, s->part, accumulate ? 1 : 0);
+    return moe_combine_launch(c, s->moe_ys, pair_slot, s->moe_topw, rows, k, d, out ? out : s->part, accumulate ? 1 : 0);
   }
   RB_TRY(moe_reset_launch(c, cursor, ep, count, E_l + 1, send_meta, (int)slots));
   RB_TRY(moe_dispatch_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, (int)cap, cursor, s->moe_send, send_meta, pair_slot));
@@ -598,7 +598,7 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate) {
     RB_TRY(comm_alltoall_bytes(c, m->slot, s->moe_ret, s->moe_back, (size_t)cap * d * sizeof(float)));
     back = s->moe_back;
   }
-  return moe_combine_launch(c, back, pair_slot, s->moe_topw, rows, k, d, s->part, accumulate ? 1 : 0);
+  return moe_combine_launch(c, back, pair_slot, s->moe_topw, rows, k, d, out ? out : s->part, accumulate ? 1 : 0);
 }
 
 // Copies the last-position logits [B, vocab] to the host; under tensor parallelism the
@@ -786,6 +786,42 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       RB_TRY(residual_norm_launch(c, a, rows));
     }
     ks = 0;  // slabs of s->part that hold FFN output so far
+    // MoE layer with shared experts on one rank, small step: the shared experts (three short launches)
+    // run on a second stream beside the routed path (router, sort, two HBM-bound grouped GEMMs, combine).
+    // Their slabs sit behind the gate|up scratch, the routed sum in the slab after them.
+    const size_t gu_scratch = (size_t)4 * rows * 2 * L.ffn_local;  // floats the split gate|up may use at the head of s->part
+    const bool fork = L.moe && L.ffn_local > 0 && dt == REWB200_BF16 && cf.ep_size == 1 && cf.tp_size == 1 && rows <= 64 &&
+                      c->moe_overlap && (gu_scratch + (size_t)17 * rows * d) * sizeof(float) <= s->part_bytes;
+    if (fork) {
+      float* base = s->part + gu_scratch;
+      RB_CUDA(cudaEventRecord(c->ev_fork, c->stream));
+      RB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+      cudaStream_t main_stream = c->stream;
+      const bool pdl = c->use_pdl;
+      c->stream = c->side;
+      c->use_pdl = false;  // first launch behind an event wait: a plain dependency
+      int st = run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr);
+      c->use_pdl = pdl;
+      if (st == REWB200_OK) st = run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, base, d, &ks);
+      c->stream = main_stream;
+      RB_TRY(st);
+      RB_CUDA(cudaEventRecord(c->ev_join, c->side));
+      RB_TRY(moe_routed(s, L, rows, false, base + (size_t)ks * rows * d));
+      RB_CUDA(cudaStreamWaitEvent(c->stream, c->ev_join, 0));
+      NormArgs a = na;
+      a.partial = base;
+      a.nsplit = ks + 1;
+      a.split_stride = rows * d;
+      a.bias = L.down.b;
+      const bool last = (l + 1 == cf.n_layers);
+      a.gamma = last ? m->ng : m->layers[l + 1].ln1g;
+      a.beta = last ? m->nb : m->layers[l + 1].ln1b;
+      c->use_pdl = false;  // two predecessors (combine and the shared down projection): a plain dependency
+      st = residual_norm_launch(c, a, rows);
+      c->use_pdl = pdl;
+      RB_TRY(st);
+      continue;
+    }
     if (L.ffn_local > 0) {  // dense FFN, or the fused shared experts of a MoE layer
       if (dt == REWB200_BF16) {
         RB_TRY(run_linear(s, L.gu, s->xn, d, rows, false, EPI_SWIGLU_BF16, s->h, L.ffn_local, nullptr));

@@ -174,6 +174,9 @@ int rewb200_init(const int* device_ordinals, int n) {
     c->device = dev;
     c->sm_count = prop.multiProcessorCount;
     RB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    RB_CUDA(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
+    RB_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+    RB_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
     RB_CUDA(cudaMalloc(&c->d_status, 256));
     RB_CUDA(cudaMemset(c->d_status, 0, 256));
     RB_CUDA(cudaMalloc(&c->d_tickets, Ctx::kTickets * sizeof(int)));
@@ -206,6 +209,9 @@ int rewb200_shutdown(void) {
     cudaFreeHost(c->h_status);
     cudaFreeHost(c->pinned);
     cudaStreamDestroy(c->stream);
+    cudaStreamDestroy(c->side);
+    cudaEventDestroy(c->ev_fork);
+    cudaEventDestroy(c->ev_join);
     delete c;
   }
   g_ctx.clear();
@@ -258,6 +264,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "attention_merge") {
     RB_REQUIRE(v == "fused" || v == "launch", "option attention_merge: expected fused or launch");
     c->attn_fused_merge = v == "fused";
+  } else if (k == "moe_overlap") {
+    RB_REQUIRE(v == "on" || v == "off", "option moe_overlap: expected on or off");
+    c->moe_overlap = v == "on";
   } else if (k == "splitk_rows") {
     const int r = atoi(v.c_str());
     RB_REQUIRE(r >= 0 && r <= 256, "option splitk_rows: 0..256");
