@@ -57,6 +57,49 @@ def read_safetensors(path):
     return out
 
 
+def read_safetensors_dir(snap_dir):
+    """loadSafetensorsWeights (src/rew/hf/hub.nim:386-394): every *.safetensors file of a snapshot directory
+    merged into one {name: array}, which covers single-file and sharded checkpoints alike (the shard index
+    model.safetensors.index.json is not needed: each shard names its own tensors).  Files are visited in
+    sorted order; a tensor named by two shards is an error rather than a silent overwrite."""
+    import glob
+    import os
+    files = sorted(f for f in glob.glob(os.path.join(snap_dir, "*.safetensors")) if not f.endswith(".index.json"))
+    if not files:
+        raise FileNotFoundError("no *.safetensors file in %s" % snap_dir)
+    out = {}
+    for f in files:
+        for name, arr in read_safetensors(f).items():
+            if name in out:
+                raise ValueError("tensor %s appears in more than one shard of %s" % (name, snap_dir))
+            out[name] = arr
+    return out
+
+
+def llama_config_from_hf(path_or_dict, dtype=None, **overrides):
+    """loadHfConfig + toLlamaConfig (src/rew/hf/hub.nim:344-382): a Hugging Face config.json -> ModelConfig, with
+    the reference's defaults for absent keys (vocab 32000, hidden 4096, intermediate 11008, 32 layers, 32 heads,
+    kv heads = heads, 2048 positions, rope_theta 10000, rms_norm_eps 1e-5).  head_dim is hidden / heads as in
+    initLlamaConfig; norm_kind 0 (RMSNorm weights) and the conventional causal mask are what a Hugging Face
+    checkpoint means."""
+    from .weights import ModelConfig
+    node = path_or_dict
+    if not isinstance(node, dict):
+        with open(path_or_dict) as f:
+            node = json.load(f)
+    heads = int(node.get("num_attention_heads", 32))
+    hidden = int(node.get("hidden_size", 4096))
+    kw = dict(vocab=int(node.get("vocab_size", 32000)), d_model=hidden, n_layers=int(node.get("num_hidden_layers", 32)),
+              n_heads=heads, n_kv_heads=int(node.get("num_key_value_heads", heads)), head_dim=hidden // heads,
+              ffn=int(node.get("intermediate_size", 11008)), max_seq=int(node.get("max_position_embeddings", 2048)),
+              theta=float(node.get("rope_theta", 10000.0)), eps=float(node.get("rms_norm_eps", 1e-5)),
+              norm_kind=0, mask_kind=1)
+    if dtype is not None:
+        kw["dtype"] = dtype
+    kw.update(overrides)
+    return ModelConfig(**kw)
+
+
 def write_safetensors(path, tensors, dtype="F32"):
     """Writes {name: array}; dtype F32 or BF16 for floating tensors."""
     header, blobs, off = {}, [], 0

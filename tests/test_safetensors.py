@@ -1,6 +1,7 @@
 """safetensors reading and the Hugging Face Llama -> rew layout mapping (transpose, rotate-half ->
 interleaved RoPE permutation), checked on CPU against a Hugging-Face-convention forward in PyTorch."""
 import numpy as np
+import pytest
 import torch
 
 from conftest import rel_l2
@@ -122,3 +123,46 @@ def test_hf_deepseek_moe_mapping_reproduces_hf_semantics(orc):
     got = orc.model_forward(cfg, canon, ids, 0, True)
     want = _hf_forward(cfg, t, ids)
     assert rel_l2(got, want) < 5e-6
+
+
+def test_sharded_snapshot_directory_and_hf_config(tmp_path, orc):
+    """A checkpoint split over several *.safetensors shards plus its config.json loads to the same canonical
+    tensors as the single file; a tensor present in two shards is refused; absent config keys take the
+    reference's defaults (src/rew/hf/hub.nim:370-382)."""
+    import json
+    cfg = W.tiny_llama(mask_kind=1, norm_kind=0)
+    t = _hf_weights(cfg, 3)
+    names = sorted(t)
+    snap = tmp_path / "snap"
+    snap.mkdir()
+    third = (len(names) + 2) // 3
+    for i in range(3):
+        part = {k: t[k] for k in names[i * third:(i + 1) * third]}
+        ST.write_safetensors(str(snap / ("model-%05d-of-00003.safetensors" % (i + 1))), part, dtype="BF16" if i == 1 else "F32")
+    (snap / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {}}))
+    hf_cfg = {"vocab_size": cfg.vocab, "hidden_size": cfg.d_model, "intermediate_size": cfg.ffn,
+              "num_hidden_layers": cfg.n_layers, "num_attention_heads": cfg.n_heads,
+              "num_key_value_heads": cfg.n_kv_heads, "max_position_embeddings": cfg.max_seq,
+              "rope_theta": cfg.theta, "rms_norm_eps": cfg.eps, "architectures": ["LlamaForCausalLM"]}
+    (snap / "config.json").write_text(json.dumps(hf_cfg))
+    got_cfg = ST.llama_config_from_hf(str(snap / "config.json"))
+    for f in ("vocab", "d_model", "n_layers", "n_heads", "n_kv_heads", "head_dim", "ffn", "max_seq", "theta", "eps"):
+        assert getattr(got_cfg, f) == getattr(cfg, f), f
+    merged = ST.read_safetensors_dir(str(snap))
+    assert set(merged) == set(t)
+    want = {k: (W.bf16_round(t[k]) if k in names[third:2 * third] else t[k]) for k in t}
+    assert all(np.array_equal(merged[k], want[k]) for k in t)
+    canon = ST.llama_from_hf(got_cfg, merged)
+    ref = ST.llama_from_hf(cfg, want)
+    assert all(np.array_equal(a, b) for a, b in zip(canon, ref))
+    # defaults of toLlamaConfig
+    d = ST.llama_config_from_hf({})
+    assert (d.vocab, d.d_model, d.ffn, d.n_layers, d.n_heads, d.n_kv_heads, d.max_seq, d.theta) == \
+           (32000, 4096, 11008, 32, 32, 32, 2048, 10000.0)
+    assert ST.llama_config_from_hf({"num_attention_heads": 8, "hidden_size": 512}).n_kv_heads == 8
+    # the same tensor in two shards is an error
+    ST.write_safetensors(str(snap / "zz-extra.safetensors"), {names[0]: t[names[0]]})
+    with pytest.raises(ValueError, match="more than one shard"):
+        ST.read_safetensors_dir(str(snap))
+    with pytest.raises(FileNotFoundError):
+        ST.read_safetensors_dir(str(tmp_path))
