@@ -237,6 +237,16 @@ class CausalLM:
         check(lib().rewb200_model_finalize(self._h))
         return self
 
+    @classmethod
+    def from_hf_snapshot(cls, snap_dir, dtype=None, slot=0, **config_overrides):
+        """A Hugging Face Llama snapshot directory (config.json + one or more *.safetensors) on the device:
+        hfDownloadModel's layout read the way loadHfConfig / toLlamaConfig / loadSafetensorsWeights do
+        (src/rew/hf/hub.nim:344-394), with the tensor mapping that loadLlamaWeights leaves out."""
+        import os
+        from . import safetensors as st
+        cfg = st.llama_config_from_hf(os.path.join(snap_dir, "config.json"), dtype=dtype, **config_overrides)
+        return cls(cfg, slot).load(st.llama_from_hf(cfg, st.read_safetensors_dir(snap_dir)))
+
     def init_random(self, seed=0, std=0.02):
         check(lib().rewb200_model_init_random(self._h, seed, std))
         check(lib().rewb200_model_finalize(self._h))

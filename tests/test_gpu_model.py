@@ -217,3 +217,42 @@ def test_bf16_decode_cluster_splitk_matches_slabs_and_oracle(rb, orc, head_dim, 
     seq = np.concatenate([prompt, a[0][:, None], a[2][:, :3]], 1)
     want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
     assert rel_l2(a[3], want) <= 2e-2
+
+
+@pytest.mark.gpu
+def test_model_from_hf_snapshot_directory(rb, orc, tmp_path):
+    """config.json + sharded safetensors with Hugging Face names -> model on the device; greedy ids equal the
+    oracle's on the converted weights (fp32, token-exact)."""
+    import json
+    from rew_b200 import safetensors as ST
+    cfg = W.tiny_llama(mask_kind=1, norm_kind=0)
+    rng = np.random.default_rng(3)
+    d, hd = cfg.d_model, cfg.head_dim
+    hf = {"model.embed_tokens.weight": rng.normal(0, 0.05, (cfg.vocab, d)), "model.norm.weight": 1 + 0.1 * rng.normal(size=d),
+          "lm_head.weight": rng.normal(0, 0.05, (cfg.vocab, d))}
+    for l in range(cfg.n_layers):
+        p = "model.layers.%d." % l
+        hf[p + "self_attn.q_proj.weight"] = rng.normal(0, 0.05, (cfg.n_heads * hd, d))
+        hf[p + "self_attn.k_proj.weight"] = rng.normal(0, 0.05, (cfg.n_kv_heads * hd, d))
+        hf[p + "self_attn.v_proj.weight"] = rng.normal(0, 0.05, (cfg.n_kv_heads * hd, d))
+        hf[p + "self_attn.o_proj.weight"] = rng.normal(0, 0.05, (d, cfg.n_heads * hd))
+        hf[p + "mlp.gate_proj.weight"] = rng.normal(0, 0.05, (cfg.ffn, d))
+        hf[p + "mlp.up_proj.weight"] = rng.normal(0, 0.05, (cfg.ffn, d))
+        hf[p + "mlp.down_proj.weight"] = rng.normal(0, 0.05, (d, cfg.ffn))
+        hf[p + "input_layernorm.weight"] = 1 + 0.1 * rng.normal(size=d)
+        hf[p + "post_attention_layernorm.weight"] = 1 + 0.1 * rng.normal(size=d)
+    hf = {k: v.astype(np.float32) for k, v in hf.items()}
+    names = sorted(hf)
+    half = len(names) // 2
+    ST.write_safetensors(str(tmp_path / "model-00001-of-00002.safetensors"), {k: hf[k] for k in names[:half]})
+    ST.write_safetensors(str(tmp_path / "model-00002-of-00002.safetensors"), {k: hf[k] for k in names[half:]})
+    (tmp_path / "config.json").write_text(json.dumps({
+        "vocab_size": cfg.vocab, "hidden_size": cfg.d_model, "intermediate_size": cfg.ffn, "num_hidden_layers": cfg.n_layers,
+        "num_attention_heads": cfg.n_heads, "num_key_value_heads": cfg.n_kv_heads, "max_position_embeddings": cfg.max_seq,
+        "rope_theta": cfg.theta, "rms_norm_eps": cfg.eps}))
+    model = rb.CausalLM.from_hf_snapshot(str(tmp_path))
+    prompt = np.random.default_rng(5).integers(0, cfg.vocab, size=(2, 9)).astype(np.int32)
+    got = model.session(2, 32).generate(prompt, 8)
+    loaded = ST.llama_from_hf(model.cfg, ST.read_safetensors_dir(str(tmp_path)))
+    want, _ = orc.generate_greedy(model.cfg, loaded, prompt, 8)
+    assert np.array_equal(got, want)
