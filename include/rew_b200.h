@@ -68,6 +68,9 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            with the epilogue overlapped (default), or one CTA per tile
  *   "profile_linears" = "1".."31"            which launches rewb200_session_profile_linears times: bit 0 q|k|v, 1 o,
  *                                            2 gate|up, 3 down, 4 lm_head (default 31, all)
+ *   "ep_exchange" = "auto" | "prefix" | "capacity"   expert-parallel steps of 64+ pairs outside a captured graph (prefill):
+ *                                            exchange the pair counts and then only the occupied prefix of every slot array,
+ *                                            or always the worst-case capacity; auto (default) = prefix from 4 ranks on
  *   "moe_overlap" = "on" | "off"             MoE layers on one rank, steps of at most 64 rows: the shared experts run on a
  *                                            second stream beside the routed experts (default on)
  *   "splitk_rows" = "0".."256"               largest step, in rows, whose Linear launches may split K (default 256)

@@ -103,6 +103,26 @@ int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t b
   return REWB200_OK;
 }
 
+// All-to-all of row prefixes: the block for peer p starts at p * peer_stride_bytes in both buffers; this rank
+// sends its first send_rows[p] rows of it and receives recv_rows[p] rows (host arrays; send_rows[p] here equals
+// recv_rows[this rank] on peer p).
+int comm_alltoallv_rows(Ctx* c, int slot, const void* send, void* recv, size_t peer_stride_bytes, size_t row_bytes,
+                        const int* send_rows, const int* recv_rows) {
+  RB_REQUIRE(slot >= 0 && slot < 16 && g_comm[slot].comm, "rewb200_comm_init has not been called for this slot");
+  Comm& cm = g_comm[slot];
+  RB_NCCL(g_nccl.GroupStart());
+  for (int p = 0; p < cm.world; ++p) {
+    if (send_rows[p] > 0)
+      RB_NCCL(g_nccl.Send((const char*)send + (size_t)p * peer_stride_bytes, (size_t)send_rows[p] * row_bytes, ncclChar, p,
+                          cm.comm, c->stream));
+    if (recv_rows[p] > 0)
+      RB_NCCL(g_nccl.Recv((char*)recv + (size_t)p * peer_stride_bytes, (size_t)recv_rows[p] * row_bytes, ncclChar, p, cm.comm,
+                          c->stream));
+  }
+  RB_NCCL(g_nccl.GroupEnd());
+  return REWB200_OK;
+}
+
 // ---- peer heap for the fused one-shot all-reduce ------------------------------
 // One cudaMalloc per rank: [16 flag ints | pad][epoch int | pad][buffer A][buffer B], exported with
 // CUDA IPC and mapped by every other rank of the node.  Peers are only ever read with plain loads.

@@ -44,6 +44,8 @@ struct Ctx {
   cudaStream_t side = nullptr;            // second stream for a branch that runs beside the main one (MoE shared experts)
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool moe_overlap = true;
+  int ep_prefix = 2;          // expert-parallel prefill: 1 exchange pair counts, then only the occupied slot prefixes;
+                              // 0 always the worst-case capacity; 2 prefixes from 4 ranks on (at 2 ranks they measured no gain)
   int* d_status = nullptr;   // kernels record KernelStatus codes here
   static constexpr int kTickets = 16384;
   int* d_tickets = nullptr;  // split-KV decode attention: one arrival counter per (sequence, kv head), zero between launches

@@ -35,6 +35,8 @@ int slab_sum_launch(Ctx* c, float* part, int nsplit, int64_t slab_elems);
 int slab_sum_to_launch(Ctx* c, const float* part, int nsplit, int64_t slab_elems, float* dst);
 int epoch_bump_launch(Ctx* c, int* epoch, int by);
 int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_peer);
+int comm_alltoallv_rows(Ctx* c, int slot, const void* send, void* recv, size_t peer_stride_bytes, size_t row_bytes,
+                        const int* send_rows, const int* recv_rows);
 int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi);
 int moe_route_slabs_launch(Ctx* c, const float* logits, int nsplit, int64_t split_stride, const float* bias, int64_t N, int E,
                            int k, float* topw, int* topi);
@@ -251,7 +253,8 @@ struct rewb200_session {
   float* moe_logits = nullptr;
   float* moe_topw = nullptr;
   int* moe_topi = nullptr;
-  int* moe_ints = nullptr;             // cursor | count | offsets | cursor2 | send_meta | recv_meta | pair_slot | slot_pos
+  int* moe_ints = nullptr;             // cursor | count | offsets | cursor2 | send_meta | recv_meta | pair_slot | slot_pos | recv counts
+  size_t moe_ints_n = 0;
   void *moe_send = nullptr, *moe_recv = nullptr, *moe_xs = nullptr, *moe_hs = nullptr;
   float *moe_ys = nullptr, *moe_ret = nullptr, *moe_back = nullptr, *moe_tmp = nullptr;
   cudaGraphExec_t graph = nullptr;
@@ -414,7 +417,9 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
       RB_CUDA(cudaMalloc((void**)&s->moe_logits, (size_t)std::max<int64_t>(rows, 8 * std::min<int64_t>(rows, 64)) * c.n_routed * sizeof(float)));  // or 8 split-K slabs of a small step
       RB_CUDA(cudaMalloc((void**)&s->moe_topw, (size_t)rows * k * sizeof(float)));
       RB_CUDA(cudaMalloc((void**)&s->moe_topi, (size_t)rows * k * sizeof(int)));
-      RB_CUDA(cudaMalloc((void**)&s->moe_ints, (size_t)(ep + 3 * (E_l + 1) + 3 * slots + rows * k) * sizeof(int)));
+      // the last 16 ints hold the per-peer counts this rank receives (prefix exchange of large steps)
+      s->moe_ints_n = (size_t)(ep + 3 * (E_l + 1) + 3 * slots + rows * k) + 16;
+      RB_CUDA(cudaMalloc((void**)&s->moe_ints, s->moe_ints_n * sizeof(int)));
       RB_CUDA(cudaMalloc((void**)&s->moe_tmp, (size_t)rows * c.d_model * sizeof(float)));
       if (c.dtype == REWB200_BF16) {
         RB_CUDA(cudaMalloc(&s->moe_send, (size_t)slots * c.d_model * es));
@@ -579,7 +584,31 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
   RB_TRY(moe_dispatch_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, (int)cap, cursor, s->moe_send, send_meta, pair_slot));
   const void* rx = s->moe_send;
   const int* rmeta = send_meta;
-  if (ep > 1) {
+  // Large steps outside a captured graph (prefill): exchange the per-peer pair counts first and move only the
+  // occupied prefix of every slot array instead of its worst-case capacity.  Decode steps keep the fixed-size
+  // exchange, which needs no host round trip and can be captured.
+  cudaStreamCaptureStatus cap_st = cudaStreamCaptureStatusNone;
+  RB_CUDA(cudaStreamIsCapturing(c->stream, &cap_st));
+  const bool prefix = ep > 1 && ep <= 16 && (c->ep_prefix == 1 || (c->ep_prefix == 2 && ep >= 4)) &&
+                      cap_st == cudaStreamCaptureStatusNone && cap >= 64;
+  int* h_send_rows = c->h_status + 16;  // pinned: [16 send | 16 recv]
+  int* h_recv_rows = c->h_status + 32;
+  if (prefix) {
+    int* recv_cnt = s->moe_ints + s->moe_ints_n - 16;
+    RB_TRY(comm_alltoall_bytes(c, m->slot, cursor, recv_cnt, sizeof(int)));
+    RB_CUDA(cudaMemcpyAsync(h_send_rows, cursor, ep * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    RB_CUDA(cudaMemcpyAsync(h_recv_rows, recv_cnt, ep * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    RB_CUDA(cudaMemsetAsync(recv_meta, 0xFF, (size_t)slots * sizeof(int), c->stream));  // -1: slots past a prefix stay empty
+    RB_CUDA(cudaStreamSynchronize(c->stream));
+    for (int p = 0; p < ep; ++p)
+      RB_REQUIRE(h_send_rows[p] >= 0 && h_send_rows[p] <= cap && h_recv_rows[p] >= 0 && h_recv_rows[p] <= cap,
+                 "expert-parallel dispatch: pair count out of range");
+    RB_TRY(comm_alltoallv_rows(c, m->slot, s->moe_send, s->moe_recv, (size_t)cap * d * dtype_size(dt), (size_t)d * dtype_size(dt),
+                               h_send_rows, h_recv_rows));
+    RB_TRY(comm_alltoallv_rows(c, m->slot, send_meta, recv_meta, (size_t)cap * sizeof(int), sizeof(int), h_send_rows, h_recv_rows));
+    rx = s->moe_recv;
+    rmeta = recv_meta;
+  } else if (ep > 1) {
     RB_TRY(comm_alltoall_bytes(c, m->slot, s->moe_send, s->moe_recv, (size_t)cap * d * dtype_size(dt)));
     RB_TRY(comm_alltoall_bytes(c, m->slot, send_meta, recv_meta, (size_t)cap * sizeof(int)));
     rx = s->moe_recv;
@@ -594,7 +623,11 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
                             max_rows));
   RB_TRY(moe_return_launch(c, s->moe_ys, slot_pos, (int)slots, d, s->moe_ret));
   const float* back = s->moe_ret;
-  if (ep > 1) {
+  if (prefix) {  // results go back the way the pairs came: what peer p sent here returns to p
+    RB_TRY(comm_alltoallv_rows(c, m->slot, s->moe_ret, s->moe_back, (size_t)cap * d * sizeof(float), (size_t)d * sizeof(float),
+                               h_recv_rows, h_send_rows));
+    back = s->moe_back;
+  } else if (ep > 1) {
     RB_TRY(comm_alltoall_bytes(c, m->slot, s->moe_ret, s->moe_back, (size_t)cap * d * sizeof(float)));
     back = s->moe_back;
   }

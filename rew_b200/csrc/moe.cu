@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(128) moe_group_local_kernel(const T* __restric
   }
 }
 
-// ret[slot] = ys[slot_pos[slot]] (zeros for empty slots): results back in the sender's slot order.
+// ret[slot] = ys[slot_pos[slot]] for occupied slots: results back in the sender's slot order.
 __global__ void __launch_bounds__(128) moe_return_kernel(const float* __restrict__ ys, const int* __restrict__ slot_pos,
                                                          int64_t d, float* ret) {
   pdl_launch_dependents();
@@ -236,10 +236,7 @@ __global__ void __launch_bounds__(128) moe_return_kernel(const float* __restrict
   const int pos = slot_pos[slot];
   float4* dst = reinterpret_cast<float4*>(ret + (int64_t)slot * d);
   const int n4 = (int)(d / 4);
-  if (pos < 0) {
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    return;
-  }
+  if (pos < 0) return;  // empty slot: nobody reads its row (the combine follows pair_slot, which names occupied slots only)
   const float4* src = reinterpret_cast<const float4*>(ys + (int64_t)pos * d);
   for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = src[i];
 }

@@ -264,6 +264,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "attention_merge") {
     RB_REQUIRE(v == "fused" || v == "launch", "option attention_merge: expected fused or launch");
     c->attn_fused_merge = v == "fused";
+  } else if (k == "ep_exchange") {
+    RB_REQUIRE(v == "prefix" || v == "capacity" || v == "auto", "option ep_exchange: expected auto, prefix or capacity");
+    c->ep_prefix = v == "prefix" ? 1 : (v == "capacity" ? 0 : 2);
   } else if (k == "moe_overlap") {
     RB_REQUIRE(v == "on" || v == "off", "option moe_overlap: expected on or off");
     c->moe_overlap = v == "on";

@@ -54,7 +54,14 @@ def main():
     prompt = prompt_of(rank)
     # every rank feeds the same number of tokens per step: the all-to-all slot arrays have one fixed capacity
     sess = api.CausalLM(cfg).load(weights(cfg)).session(prompt.shape[0], 64)
+    # the prompt goes through the count-then-prefix exchange (ranks receive 38 and 76 pairs), the captured decode
+    # steps through the fixed-capacity one; the same prompt again with fixed capacity must give the same logits
+    api.set_option("ep_exchange", "prefix")
     nxt, logits = sess.forward(prompt, want_logits=True)
+    api.set_option("ep_exchange", "capacity")
+    sess.reset()
+    nxt2, logits2 = sess.forward(prompt, want_logits=True)
+    assert np.array_equal(nxt, nxt2) and np.array_equal(logits, logits2), "prefix and capacity exchange disagree"
     ids, last = sess.decode(4, want_logits=True)
     print("rank", rank, "done", flush=True)
     np.savez(outfile, nxt=nxt, logits=logits, ids=ids, last=last)
