@@ -50,7 +50,8 @@ struct Ctx {
   static constexpr int kTickets = 16384;
   int* d_tickets = nullptr;  // split-KV decode attention: one arrival counter per (sequence, kv head), zero between launches
   bool attn_fused_merge = false;  // measured slower than the separate merge launch (3.20 vs 3.06 ms per step at batch 1)
-  int* h_status = nullptr;   // pinned mirror
+  int* h_status = nullptr;   // pinned, 64 ints: [0] mirror of d_status; [16..31] / [32..47] per-peer pair counts sent /
+                             // received by the expert-parallel prefix exchange
   int sm_count = 0;
   bool use_pdl = true;
   int linear_impl = 2;       // bf16 Linear: 0 mma.sync, 1 tcgen05 when rows > 32, 2 tcgen05 always (default)
