@@ -132,20 +132,32 @@ def make_cfg(name):
     return getattr(W, name)()
 
 
-def run_reference(args, wl, rank):
-    """CPU arm: the oracle port, timed on the host cores.  Bounded sample: ONE decoder layer plus the
-    lm_head of the same shapes at the workload's mean context, extrapolated to all layers."""
-    if rank != 0:
-        return
+def product_config(args, wl, world, model_gb=None):
+    """The `config` object of a bench line; both arms print the same one."""
+    parallel = "single" if world == 1 else wl.get("parallel", "replicas")
+    per_gpu = wl["batch"] // world if parallel == "ep" else wl["batch"]
+    cfg = make_cfg(wl["model"])
+    return {"workload": args.workload + ("" if args.layers <= 0 else "_%dlayers" % args.layers), "batch_per_gpu": per_gpu,
+            "prompt": wl["prompt"], "decode_steps": args.steps, "parallelism": parallel + (str(world) if world > 1 else ""),
+            "sampling": args.sampling, "mask": "conventional" if cfg.mask_kind == 1 else "as_written",
+            "norm": "rmsNorm" if cfg.norm_kind == 0 else "LayerNorm",
+            "l2": "weights streamed per step exceed the 126 MB L2"}
+
+
+def oracle_sample(args, wl, steps, warm):
+    """Times the CPU port on a bounded sample: ONE decoder layer plus the lm_head of the workload's shapes at its
+    mean context, every host thread, then extrapolates to all layers by parameter count (both parts are
+    weight-streaming GEMMs).  Returns (tokens/s of the full model, seconds per sample step, description, threads)."""
     from oracle import orc
     from rew_b200 import _lib, weights as W
+    orc.set_num_threads(os.cpu_count() or 1)   # launchers export OMP_NUM_THREADS=1 for every rank
     cfg = make_cfg(wl["model"])
     full_layers = cfg.n_layers
     cfg.n_layers = 1 if cfg.n_layers > 2 else cfg.n_layers
     cfg.dtype = _lib.F32
     B = wl["batch"]
     ctx = wl["prompt"] + args.warmup + args.steps // 2
-    cfg.max_seq = max(cfg.max_seq, ctx + args.steps + args.warmup + 8)
+    cfg.max_seq = max(cfg.max_seq, ctx + steps + warm + 8)
     rng = np.random.default_rng(0)
     tensors = []
     for name, shape in W.tensor_specs(cfg):
@@ -156,28 +168,34 @@ def run_reference(args, wl, rank):
             t = np.ones(shape, np.float32) if name.endswith("gamma") else np.zeros(shape, np.float32)
         tensors.append(t)
     orc.set_accum64(0)  # f32 accumulation, the fastest setting of the port
-    steps = max(1, min(args.steps, 3))
-    warm = max(1, min(args.warmup, 1))
-    # lm_head-only time: a model with zero layers is not expressible, so time the 1-layer model and
-    # a second call with a doubled step count to separate nothing; instead scale analytically below.
-    orc.decode_bench(cfg, tensors, B, ctx, warm)
+    if warm > 0:
+        orc.decode_bench(cfg, tensors, B, ctx, warm)
     t = orc.decode_bench(cfg, tensors, B, ctx, steps) / steps
-    # per-step time = layers * t_layer + t_head; split t by parameter count (both are weight-streaming GEMMs)
     specs = W.tensor_specs(cfg)
-    p_layer = sum(int(np.prod(s)) for n, s in specs if ".layers.0." in n and len(s) == 2)
+    p_layer = sum(int(np.prod(sh)) for n, sh in specs if ".layers.0." in n and len(sh) == 2)
     p_head = cfg.d_model * cfg.vocab
-    t_layer = t * p_layer / (p_layer + p_head)
-    t_head = t * p_head / (p_layer + p_head)
-    t_full = full_layers * t_layer + t_head
-    value = B / t_full
-    sample = ("%d timed decode steps of 1 of %d layers + lm_head, batch %d, context %d, f32, extrapolated by layer count"
-              % (steps, full_layers, B, ctx))
+    layers_run = cfg.n_layers
+    p_run = layers_run * p_layer + p_head
+    t_full = full_layers * (t * p_layer / p_run) + t * p_head / p_run
+    sample = ("%d timed decode steps of %d of %d layers + lm_head, batch %d, context %d, f32, extrapolated by layer count"
+              % (steps, layers_run, full_layers, B, ctx))
+    return B / t_full, t, t_full, sample, orc.num_threads()
+
+
+def run_reference(args, wl, rank, world):
+    """CPU arm: the oracle port on the host cores, rank 0 only.  Every step is the bounded sample of
+    oracle_sample; `ms_per_step` is the time of one sample step, `ms_per_full_step` the extrapolated one."""
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    warm = max(1, min(args.warmup, 2))
+    value, t_sample, t_full, sample, cores = oracle_sample(args, wl, steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": t_full * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "batch": B, "prompt": wl["prompt"], "decode_steps": args.steps},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.num_threads(), "kind": "port", "sample": sample},
+        "warmup": args.warmup, "ms_per_step": t_sample * 1e3, "ms_per_full_step": t_full * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": product_config(args, wl, world),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "rew's own CPU path (Nim + XLA PJRT plugin) cannot be built or run here; this is the C++ restatement in oracle/",
     }
@@ -187,36 +205,8 @@ def run_reference(args, wl, rank):
 def cpu_baseline_leg(args, wl):
     """Bounded CPU sample for the GPU arm's line (rank 0, N=1 only)."""
     try:
-        from oracle import orc
-        from rew_b200 import _lib, weights as W
-        cfg = make_cfg(wl["model"])
-        full_layers = cfg.n_layers
-        if cfg.n_layers > 2:
-            cfg.n_layers = 1
-        cfg.dtype = _lib.F32
-        B = wl["batch"]
-        ctx = wl["prompt"] + args.steps // 2
-        cfg.max_seq = max(cfg.max_seq, ctx + 16)
-        rng = np.random.default_rng(0)
-        tensors = []
-        for name, shape in W.tensor_specs(cfg):
-            if len(shape) == 2:
-                t = rng.standard_normal(size=shape, dtype=np.float32)
-                t *= 0.02
-            else:
-                t = np.ones(shape, np.float32) if name.endswith("gamma") else np.zeros(shape, np.float32)
-            tensors.append(t)
-        orc.set_accum64(0)
-        orc.decode_bench(cfg, tensors, B, ctx, 1)
-        n = 2
-        t = orc.decode_bench(cfg, tensors, B, ctx, n) / n
-        specs = W.tensor_specs(cfg)
-        p_layer = sum(int(np.prod(s)) for nm, s in specs if ".layers.0." in nm and len(s) == 2)
-        p_head = cfg.d_model * cfg.vocab
-        t_full = full_layers * t * p_layer / (p_layer + p_head) + t * p_head / (p_layer + p_head)
-        return {"value": B / t_full, "unit": UNIT, "cores": orc.num_threads(), "kind": "port",
-                "sample": "%d decode steps of 1 of %d layers + lm_head, batch %d, context %d, f32, extrapolated by layer count"
-                          % (n, full_layers, B, ctx)}
+        value, _, _, sample, cores = oracle_sample(args, wl, 2, 1)
+        return {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
     except Exception as e:  # the baseline must never take the GPU number down with it
         return {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %r" % (e,)}
 
@@ -266,67 +256,54 @@ def run_attention_op(args, rank, local_rank):
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="l8_b32", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="rew_b200", choices=["rew_b200", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
-                    help="run-time switch passed to rewb200_set_option, e.g. norm=row (repeatable)")
-    ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
-    ap.add_argument("--sampling", default="greedy", choices=["greedy", "top_k", "top_p"],
-                    help="next-token rule of the decode step; greedy is the metric's configuration")
-    args = ap.parse_args()
-    wl = WORKLOADS[args.workload]
-    rank, local_rank, world = dist_env()
+class Comm:
+    """Communicator and peer heap of a multi-rank run (one per process), shared by the tensor-parallel and
+    expert-parallel measurements."""
 
-    if args.workload == "attn_op":
-        run_attention_op(args, rank, local_rank)
-        return
-    if args.impl == "reference":
-        run_reference(args, wl, rank)
-        return
+    def __init__(self, api, pg, rank, world, allreduce_bytes, alltoall_bytes):
+        self.api, self.rank, self.world = api, rank, world
+        box = [api.comm_unique_id() if rank == 0 else None]
+        pg.broadcast_object_list(box, src=0)
+        api.comm_init(box[0], rank, world)
+        self.fused = os.environ.get("REW_B200_TP_ALLREDUCE", "fused") == "fused"
+        if self.fused:
+            mine = api.comm_peer_alloc(allreduce_bytes, alltoall_bytes)
+            handles = [None] * world
+            pg.all_gather_object(handles, mine)
+            api.comm_peer_attach(handles)
 
+    def close(self):
+        self.api.comm_destroy()
+
+
+def a2a_bytes_for(cfg, tokens_per_rank, world):
+    """Peer-heap bytes the expert-parallel exchange of one step needs (activations, expert ids, f32 results)."""
+    def up(v):
+        return (v + 255) // 256 * 256
+    slots = tokens_per_rank * cfg.top_k * world
+    return up(slots * cfg.d_model * 2) + up(slots * 4) + up(slots * cfg.d_model * 4)
+
+
+def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_profile):
+    """One workload on this process group: prefill, W warm-up steps, K timed decode steps (CUDA events, max over
+    ranks), optionally the end-to-end generate() call and the Linear-launch profile.  Returns a dict."""
     import ctypes as C
     from rew_b200 import _lib, api
-    _lib.init(local_rank)
     L = _lib.lib()
-    for kv in args.option:
-        k, _, v = kv.partition("=")
-        api.set_option(k, v)
-
-    pg = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("gloo")  # host-side rendezvous only: barrier and max over ranks
-        pg = dist
-
+    wl = WORKLOADS[name]
     cfg = make_cfg(wl["model"])
     cfg.weight_quant = wl.get("weight_quant", 0)
     if args.layers > 0:
         cfg.n_layers = args.layers
-    B, S, K, Wm = wl["batch"], wl["prompt"], args.steps, args.warmup
+    B, S = wl["batch"], wl["prompt"]
     max_len = S + Wm + K + 8
     cfg.max_seq = max(cfg.max_seq, max_len)
     parallel = "single" if world == 1 else wl.get("parallel", "replicas")
     if parallel == "ep":
         cfg.ep_rank, cfg.ep_size = rank, world
         B = B // world
-    if parallel in ("tp", "ep"):
-        if parallel == "tp":
-            cfg.tp_rank, cfg.tp_size = rank, world
-        box = [api.comm_unique_id() if rank == 0 else None]
-        pg.broadcast_object_list(box, src=0)
-        api.comm_init(box[0], rank, world)
-        if parallel == "tp" and os.environ.get("REW_B200_TP_ALLREDUCE", "fused") == "fused":
-            # decode-size all-reduces run fused into the residual+norm kernel over peer memory
-            mine = api.comm_peer_alloc(64 * cfg.d_model * 4)
-            handles = [None] * world
-            pg.all_gather_object(handles, mine)
-            api.comm_peer_attach(handles)
+    if parallel == "tp":
+        cfg.tp_rank, cfg.tp_size = rank, world
     data_seed = 0 if parallel == "tp" else rank       # tensor-parallel ranks must see the same tokens
     model = api.CausalLM(cfg).init_random(seed=1234 if parallel == "ep" else 1234 + data_seed, std=0.02)
     sess = model.session(B, max_len)
@@ -353,68 +330,215 @@ def main():
     L.rewb200_sync(0, 0)
     clocks = sampler.stop() if rank == 0 else None
     launches = L.rewb200_launch_count(0) - launches0
-    if pg:
+
+    def max_over_ranks(v):
+        if not pg:
+            return v
         import torch
-        t = torch.tensor([decode_ms], dtype=torch.float64)
+        t = torch.tensor([v], dtype=torch.float64)
         pg.all_reduce(t, op=pg.ReduceOp.MAX)
-        decode_ms = float(t[0])
+        return float(t[0])
+
+    decode_ms = max_over_ranks(decode_ms)
+    prefill_ms = max_over_ranks(prefill_ms)
+    if pg:
         pg.barrier()
-    tokens = B * K * (1 if parallel == "tp" else world)   # B is per rank for replicas and ep
-    value = tokens / (decode_ms * 1e-3)
+    mult = 1 if parallel == "tp" else world            # B is per rank for replicas and ep
+    tokens = B * K * mult
+    out = {"name": name, "parallel": parallel, "batch_per_gpu": B, "prompt": S, "value": tokens / (decode_ms * 1e-3),
+           "ms_per_step": decode_ms / K, "prefill_ms": prefill_ms, "prefill_tokens_per_s": B * S * mult / (prefill_ms * 1e-3),
+           "launches": int(launches), "clocks": clocks, "weight_gb": model.weight_bytes() / 1e9, "cfg": cfg}
 
     # ---- end to end through the C ABI: host prompt ids -> host output ids
-    t0 = time.perf_counter()
-    out = sess.generate(prompt, K)
-    e2e_s = time.perf_counter() - t0
-    if pg:
-        import torch
-        t = torch.tensor([e2e_s], dtype=torch.float64)
-        pg.all_reduce(t, op=pg.ReduceOp.MAX)
-        e2e_s = float(t[0])
-    e2e = {"value": tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": prompt.nbytes / K,
-           "d2h_bytes_per_step": out.nbytes / K,
-           "what": "one generate() call: prefill of the prompt + %d decode steps, ids host->device->host" % K}
+    if with_e2e:
+        t0 = time.perf_counter()
+        ids = sess.generate(prompt, K)
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        out["e2e"] = {"value": tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": prompt.nbytes / K,
+                      "d2h_bytes_per_step": ids.nbytes / K,
+                      "what": "one generate() call: prefill of the prompt + %d decode steps, ids host->device->host" % K}
 
-    # ---- roofline of the dominant kernel (the bf16 weight-streaming Linear)
-    roofline = None
+    # ---- rooflines: whole step (weights + KV read once per step per GPU), and the Linear launches alone
     peak, which = measured_peaks()
-    kv_b = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
-    if cfg.n_routed > 0:
-        # MoE: whole-step figure only (weights of every local expert + KV, read once per step)
-        step_bytes = model.weight_bytes() - cfg.vocab * cfg.d_model * 2 + kv_b
-        ach = step_bytes / (decode_ms / K * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                    "kernel": "whole decode step", "bytes_per_step": step_bytes, "peak_source": which}
-    elif cfg.dtype == _lib.BF16:
-        ms = C.c_float()
-        nbytes = C.c_int64()
-        nl = C.c_int32()
+    kv_bytes = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
+    step_bytes = model.weight_bytes() - cfg.vocab * cfg.d_model * 2 + kv_bytes   # the embedding table is not streamed
+    out["step_bytes_per_gpu"] = step_bytes
+    out["step_frac"] = step_bytes / (decode_ms / K * 1e-3) / 1e9 / peak
+    out["peak"], out["peak_source"] = peak, which
+    if with_profile and cfg.n_routed == 0 and cfg.dtype == _lib.BF16:
+        ms, nbytes, nl = C.c_float(), C.c_int64(), C.c_int32()
         _lib.check(L.rewb200_session_profile_linears(sess._h, 20, C.byref(ms), C.byref(nbytes), C.byref(nl)))
-        peak, which = measured_peaks()
-        ach = nbytes.value / (ms.value * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    # dram read+write per step, scaled from the ncu capture of the gate|up launch
-                    # (239.2 MB measured for 236.1 MB algorithmic; profiles/linear_tc_kernel_32_decode_l8.md)
-                    "traffic": None if cfg.weight_quant else nbytes.value * 1.013,
-                    "kernel": ("nf4_tc_kernel" if cfg.weight_quant else "linear_tc_kernel<32, 0>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>"), "launches_per_step": nl.value, "ms_per_step": ms.value,
-                    "bytes_per_step": nbytes.value, "peak_source": which}
-        # whole decode step against the same roof: weights + KV read once per step
-        kv_bytes = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
-        step_bytes = model.weight_bytes() - cfg.vocab * cfg.d_model * 2 + kv_bytes
-        roofline["step_frac"] = step_bytes / (decode_ms / K * 1e-3) / 1e9 / peak
+        out["linear"] = {"ms_per_step": ms.value, "bytes_per_step": nbytes.value, "launches_per_step": nl.value,
+                         "gbs": nbytes.value / (ms.value * 1e-3) / 1e9}
+    sess.free()
+    model.free()
+    return out
 
+
+def sharded_check(rank, world, pg, kind):
+    """Correctness of the sharded path inside this run: a small bf16 model split over the ranks against the same
+    model unsharded on rank 0 (GPU against GPU; the unsharded path is the one the parity tests hold against the
+    oracle).  Returns {"rel_l2": ..., "ids_equal": ...} on rank 0."""
+    from rew_b200 import _lib, api, weights as W
+    if kind == "tp":
+        base = dict(vocab=1024, d_model=512, n_layers=2, n_heads=8, n_kv_heads=8, head_dim=64, ffn=1024, max_seq=128,
+                    theta=500000.0, dtype=_lib.BF16, mask_kind=1)
+        shard = dict(tp_rank=rank, tp_size=world)
+        prompts = {"fused": np.random.default_rng(5).integers(0, 1024, size=(2, 16)).astype(np.int32),
+                   "nccl_prefill": np.random.default_rng(6).integers(0, 1024, size=(4, 24)).astype(np.int32)}
+    else:
+        base = dict(vocab=512, d_model=256, n_layers=3, n_heads=4, n_kv_heads=4, head_dim=64, ffn=384, max_seq=128,
+                    theta=10000.0, eps=1e-6, n_routed=8, n_shared=2, top_k=3, moe_ffn=128, first_dense=384,
+                    dtype=_lib.BF16, mask_kind=1)
+        shard = dict(ep_rank=rank, ep_size=world)
+        prompts = {"peer": np.random.default_rng(7).integers(0, 512, size=(2, 20)).astype(np.int32)}
+    full = W.ModelConfig(**base)
+    t = [W.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(full, seed=11, std=0.05, trivial_affine=False)]
+    res = {}
+    model = api.CausalLM(W.ModelConfig(**base, **shard)).load(t)
+    got = {}
+    def run(m, pr):
+        sess = m.session(pr.shape[0], 64)
+        nxt, first = sess.forward(pr, want_logits=True)       # prefill: same input on both sides
+        ids, last = sess.decode(4, want_logits=True)           # greedy continuation
+        sess.free()
+        return nxt, first, ids, last
+
+    for tag, pr in prompts.items():
+        got[tag] = run(model, pr)
+    model.free()
+    if pg:
+        pg.barrier()
+    if rank == 0:
+        ref = api.CausalLM(full).load(t)
+
+        def rel(a, b):
+            return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+        for tag, pr in prompts.items():
+            nxt, first, ids, last = run(ref, pr)
+            g_nxt, g_first, g_ids, g_last = got[tag]
+            same = bool(np.array_equal(nxt, g_nxt) and np.array_equal(ids, g_ids))
+            # the last step's logits are comparable only while both greedy paths chose the same tokens
+            res[tag] = {"rel_l2_prefill_logits": rel(g_first, first), "ids_equal": same,
+                        "rel_l2_last_logits": rel(g_last, last) if same else None}
+        ref.free()
+    if pg:
+        pg.barrier()
+    return res
+
+
+def sub_record(r, which_allreduce=None):
+    d = {"workload": r["name"], "parallelism": r["parallel"], "batch_per_gpu": r["batch_per_gpu"], "tokens_per_s": r["value"],
+         "ms_per_step": r["ms_per_step"], "prefill_ms": r["prefill_ms"], "prefill_tokens_per_s": r["prefill_tokens_per_s"],
+         "per_gpu_step_frac": r["step_frac"], "step_bytes_per_gpu": r["step_bytes_per_gpu"], "gpu_launches": r["launches"]}
+    if "linear" in r:
+        d["linear_frac"] = r["linear"]["gbs"] / r["peak"]
+        d["linear_ms_per_step"] = r["linear"]["ms_per_step"]
+    if which_allreduce:
+        d["allreduce"] = which_allreduce
+    return d
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="l8_b32", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="rew_b200", choices=["rew_b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-split", action="store_true",
+                    help="skip the tensor-parallel (l70_b16) and expert-parallel (moe_b64) sub-records of the default workload")
+    ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
+                    help="run-time switch passed to rewb200_set_option, e.g. norm=row (repeatable)")
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
+    ap.add_argument("--sampling", default="greedy", choices=["greedy", "top_k", "top_p"],
+                    help="next-token rule of the decode step; greedy is the metric's configuration")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank, local_rank, world = dist_env()
+
+    if args.workload == "attn_op":
+        run_attention_op(args, rank, local_rank)
+        return
+    if args.impl == "reference":
+        run_reference(args, wl, rank, world)
+        return
+
+    if world > 1 and "NCCL_DEBUG" not in os.environ:
+        # keep NCCL's communicator-init lines ("... rank r nranks n ... Init COMPLETE") in the run's log, off stdout
+        os.environ["NCCL_DEBUG"] = "INFO"
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+
+    from rew_b200 import _lib, api, weights as W
+    _lib.init(local_rank)
+    for kv in args.option:
+        k, _, v = kv.partition("=")
+        api.set_option(k, v)
+
+    pg = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo")  # host-side rendezvous only: barrier, max over ranks, handle exchange
+        pg = dist
+    K, Wm = args.steps, args.warmup
+    split = args.workload == "l8_b32" and not args.no_split and args.layers <= 0
+    parallel = "single" if world == 1 else wl.get("parallel", "replicas")
+    comm = None
+    if world > 1 and (split or parallel in ("tp", "ep")):
+        moe = W.deepseek_v2_lite()
+        need_a2a = a2a_bytes_for(moe, (WORKLOADS["moe_b64"]["batch"] // world) * WORKLOADS["moe_b64"]["prompt"], world)
+        comm = Comm(api, pg, rank, world, 64 * 8192 * 2, need_a2a if (split or parallel == "ep") else 0)
+
+    r = run_model(args, args.workload, rank, local_rank, world, pg, K, Wm, True, True)
+    cfg = r["cfg"]
+    peak, which = r["peak"], r["peak_source"]
+    if cfg.n_routed > 0 or "linear" not in r:
+        ach = r["step_bytes_per_gpu"] / (r["ms_per_step"] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "frac_nominal": ach / 8000.0,
+                    "traffic": None, "kernel": "whole decode step", "bytes_per_step": r["step_bytes_per_gpu"], "peak_source": which}
+    else:
+        lin = r["linear"]
+        kernel = ("nf4_tc_kernel" if cfg.weight_quant else
+                  "linear_tc_kernel<32, 0>" if os.environ.get("REW_B200_LINEAR", "tc") != "mma" else "linear_bf16_kernel<32>")
+        roofline = {"bound": "hbm", "achieved": lin["gbs"], "peak": peak, "unit": "GB/s", "frac": lin["gbs"] / peak,
+                    "frac_nominal": lin["gbs"] / 8000.0,
+                    # not measured in this run: DRAM read+write bytes of one profiler capture of the gate|up launch
+                    # (239.2 MB for 236.1 MB algorithmic), scaled by the bytes of a step
+                    "traffic": None, "traffic_scaled_from_profile": None if cfg.weight_quant else lin["bytes_per_step"] * 1.013,
+                    "kernel": kernel, "launches_per_step": lin["launches_per_step"], "ms_per_step": lin["ms_per_step"],
+                    "bytes_per_step": lin["bytes_per_step"], "peak_source": which,
+                    "step_frac": r["step_frac"], "step_frac_nominal": r["step_frac"] * peak / 8000.0}
+
+    extra = {}
+    if split:
+        ar = ("fused" if comm and comm.fused else "nccl") if world > 1 else None
+        tp = run_model(args, "l70_b16", rank, local_rank, world, pg, K, Wm, False, True)
+        extra["tp"] = sub_record(tp, ar)
+        ep = run_model(args, "moe_b64", rank, local_rank, world, pg, K, Wm, False, False)
+        extra["ep"] = sub_record(ep)
+        if world > 1:
+            extra["ep"]["exchange"] = "peer_heap" if comm.fused else "nccl"
+            extra["tp_check"] = sharded_check(rank, world, pg, "tp")
+            extra["ep_check"] = sharded_check(rank, world, pg, "ep")
+    if comm:
+        comm.close()
+    if pg:
+        pg.barrier()
     if rank != 0:
         return
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
-        "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong" if parallel == "tp" else "weak", "vs_baseline": None,
-        "dtype": ("bf16 activations, NF4 block weights" if cfg.weight_quant else "bf16") if cfg.dtype == _lib.BF16 else "f32", "data": "synthetic",
-        "config": {"workload": args.workload + ("" if args.layers <= 0 else "_%dlayers" % args.layers), "batch_per_gpu": B, "prompt": S, "decode_steps": K,
-                   "parallelism": parallel + (str(world) if world > 1 else ""), "sampling": args.sampling,
-                   "l2": "weights per step (%.1f GB) exceed the 126 MB L2" % (model.weight_bytes() / 1e9)},
-        "prefill": {"tokens_per_s": B * S * (1 if parallel == "tp" else world) / (prefill_ms * 1e-3), "ms": prefill_ms},
-        "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+        "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong" if parallel == "tp" else "weak",
+        "vs_baseline": None,
+        "dtype": ("bf16 activations, NF4 block weights" if cfg.weight_quant else "bf16") if cfg.dtype == _lib.BF16 else "f32",
+        "data": "synthetic", "config": product_config(args, wl, world),
+        "prefill": {"tokens_per_s": r["prefill_tokens_per_s"], "ms": r["prefill_ms"]},
+        "e2e": r["e2e"], "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": roofline,
     }
+    line.update(extra)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_leg(args, wl)
     print(json.dumps(line), flush=True)

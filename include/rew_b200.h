@@ -68,9 +68,12 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            with the epilogue overlapped (default), or one CTA per tile
  *   "profile_linears" = "1".."31"            which launches rewb200_session_profile_linears times: bit 0 q|k|v, 1 o,
  *                                            2 gate|up, 3 down, 4 lm_head (default 31, all)
- *   "ep_exchange" = "auto" | "prefix" | "capacity"   expert-parallel steps of 64+ pairs outside a captured graph (prefill):
- *                                            exchange the pair counts and then only the occupied prefix of every slot array,
- *                                            or always the worst-case capacity; auto (default) = prefix from 4 ranks on
+ *   "ep_exchange" = "auto" | "prefix" | "capacity"   expert-parallel all-to-all: auto (default) = over the peer heap when
+ *                                            one is attached and the step fits (rewb200_comm_peer_alloc), else NCCL as under
+ *                                            "prefix" from 4 ranks on; prefix = NCCL, pair counts first and then only the
+ *                                            occupied prefix of every slot array (steps of 64+ pairs outside a captured
+ *                                            graph); capacity = NCCL, always the worst-case capacity
+ *   "inject_alloc_fail" = "n"                test hook: the n-th activation-buffer allocation from now fails on the host
  *   "moe_overlap" = "on" | "off"             MoE layers on one rank, steps of at most 64 rows: the shared experts run on a
  *                                            second stream beside the routed experts (default on)
  *   "splitk_rows" = "0".."256"               largest step, in rows, whose Linear launches may split K (default 256)
@@ -187,8 +190,10 @@ int rewb200_qlora_linear(const rewb200_buffer* x, const rewb200_nf4* h, const re
  * device-wide synchronisation of cudaMalloc is not acceptable.  Sizes with
  * M*N*4 bytes above 8 MiB are rejected.  Every call shares the one array:
  * calls that overlap on the GPU race; calls on one slot are stream-ordered.
- * The first call on a device resolves the array's address; make it outside
- * any stream capture.  bias may be NULL. */
+ * rewb200_init resolves the array's address on each device it opens and loads
+ * the kernels this call launches (the driver allocates the array when it loads
+ * that code), so the call itself loads nothing.  The GEMM is the one the slot's
+ * "linear" option selects (tcgen05 by default).  bias may be NULL. */
 int rewb200_linear_noalloc(int slot, const void* x_bf16, const void* w_bf16, const float* bias, void* y_bf16,
                            int64_t M, int64_t K, int64_t N);
 
@@ -306,12 +311,22 @@ int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int
 int rewb200_comm_unique_id(void* id128);                  /* 128 bytes, created on rank 0 */
 int rewb200_comm_init(int slot, const void* id128, int rank, int world);
 int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n);
-/* Fused one-shot all-reduce for decode-size tensor-parallel steps: each rank allocates an exchange heap
- * (two buffers of buf_bytes) and exports a 64-byte CUDA IPC handle; after the host has gathered every
- * rank's handle (rank order, world*64 bytes), attach maps the peers.  Sessions created afterwards sum the
- * row-parallel partials by reading all ranks' buffers inside the residual+norm kernel (plain peer loads
- * over NVLink behind a bounded flag barrier) whenever rows*d_model*4 <= buf_bytes; larger steps use NCCL. */
-int rewb200_comm_peer_alloc(int slot, int64_t buf_bytes, void* handle64);
+/* Peer heap: exchange memory that the other ranks of the node write into directly over NVLink (plain peer
+ * stores from inside this library's kernels; nothing is read from a peer and no library kernel is handed a
+ * peer pointer).  Each rank allocates its heap and exports a 64-byte CUDA IPC handle; after the host has
+ * gathered every rank's handle (rank order, world*64 bytes), attach maps the peers.  Sessions created
+ * afterwards use it for
+ *   - the tensor-parallel all-reduce of steps up to 64 rows with rows*d_model*(2 for bf16 models, 4 for
+ *     f32) <= allreduce_bytes: fused into the residual+norm kernel (each CTA pushes its partial to every
+ *     rank, raises a flag, waits with a bound for the peers' flags and sums the partials in rank order;
+ *     src/rew/ops/distributed.nim:62-83).  Larger steps go through NCCL;
+ *   - the expert-parallel all-to-all (src/rew/ops/distributed.nim:106-128) whenever the slot arrays of a
+ *     step (pairs*world rows of d_model activations, their expert ids and the f32 results) fit into
+ *     alltoall_bytes: dispatch and return kernels store the occupied rows straight into the owner's heap
+ *     and hand over the pair counts on the device, so neither a count exchange through the host nor
+ *     padding crosses NVLink.  Larger steps go through NCCL send/recv.
+ * Either size may be 0.  The heap holds 16 KiB + 2*world*allreduce_bytes + alltoall_bytes. */
+int rewb200_comm_peer_alloc(int slot, int64_t allreduce_bytes, int64_t alltoall_bytes, void* handle64);
 int rewb200_comm_peer_attach(int slot, const void* handles_all);
 /* Free every session of the slot first: a captured decode graph keeps the communicator in use and
  * NCCL waits for it. */

@@ -80,6 +80,11 @@ def num_threads():
     return lib().orc_num_threads()
 
 
+def set_num_threads(n):
+    """Thread count of the oracle's OpenMP loops; overrides an inherited OMP_NUM_THREADS."""
+    lib().orc_set_num_threads(int(n))
+
+
 def bf16_round(x):
     x = _f(x)
     out = np.empty_like(x)

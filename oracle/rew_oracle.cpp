@@ -525,6 +525,15 @@ ORC_API int orc_num_threads() {
 #endif
 }
 
+// Worker threads of the OpenMP loops (a launcher may have exported OMP_NUM_THREADS=1 for every rank).
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 // src/rew/ops/literal.nim:112-116: round-to-nearest-even on the bit pattern.
 ORC_API void orc_bf16_round(const float* in, float* out, int64_t n) {
   for (int64_t i = 0; i < n; ++i) {

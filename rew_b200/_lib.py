@@ -100,7 +100,7 @@ SIGNATURES = {
     "rewb200_comm_unique_id": (C.c_int, [P]),
     "rewb200_comm_init": (C.c_int, [C.c_int, P, C.c_int, C.c_int]),
     "rewb200_comm_allreduce_f32": (C.c_int, [C.c_int, P, C.c_int64]),
-    "rewb200_comm_peer_alloc": (C.c_int, [C.c_int, C.c_int64, P]),
+    "rewb200_comm_peer_alloc": (C.c_int, [C.c_int, C.c_int64, C.c_int64, P]),
     "rewb200_comm_peer_attach": (C.c_int, [C.c_int, P]),
     "rewb200_comm_destroy": (C.c_int, [C.c_int]),
 }

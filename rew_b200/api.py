@@ -424,10 +424,11 @@ def comm_destroy(slot=0):
     check(lib().rewb200_comm_destroy(slot))
 
 
-def comm_peer_alloc(buf_bytes, slot=0):
-    """Allocates this rank's exchange heap for the fused all-reduce; returns its 64-byte IPC handle."""
+def comm_peer_alloc(allreduce_bytes, alltoall_bytes=0, slot=0):
+    """Allocates this rank's peer heap (fused all-reduce slots and the expert-parallel all-to-all region);
+    returns its 64-byte IPC handle."""
     buf = C.create_string_buffer(64)
-    check(lib().rewb200_comm_peer_alloc(slot, buf_bytes, buf))
+    check(lib().rewb200_comm_peer_alloc(slot, int(allreduce_bytes), int(alltoall_bytes), buf))
     return buf.raw
 
 

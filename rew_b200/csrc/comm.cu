@@ -78,9 +78,11 @@ static int nccl_load() {
 int comm_world(int slot) { return (slot >= 0 && slot < 16 && g_comm[slot].comm) ? g_comm[slot].world : 1; }
 int comm_rank(int slot) { return (slot >= 0 && slot < 16 && g_comm[slot].comm) ? g_comm[slot].rank : 0; }
 
-int comm_allreduce_sum_f32(Ctx* c, int slot, float* ptr, int64_t n) {
+int comm_allreduce_sum(Ctx* c, int slot, void* ptr, int64_t n, int dtype) {
   RB_REQUIRE(slot >= 0 && slot < 16 && g_comm[slot].comm, "rewb200_comm_init has not been called for this slot");
-  RB_NCCL(g_nccl.AllReduce(ptr, ptr, (size_t)n, ncclFloat, ncclSum, g_comm[slot].comm, c->stream));
+  RB_REQUIRE(dtype == REWB200_F32 || dtype == REWB200_BF16, "all-reduce payload must be f32 or bf16");
+  RB_NCCL(g_nccl.AllReduce(ptr, ptr, (size_t)n, dtype == REWB200_F32 ? ncclFloat : ncclBfloat16, ncclSum, g_comm[slot].comm,
+                           c->stream));
   return REWB200_OK;
 }
 
@@ -123,9 +125,18 @@ int comm_alltoallv_rows(Ctx* c, int slot, const void* send, void* recv, size_t p
   return REWB200_OK;
 }
 
-// ---- peer heap for the fused one-shot all-reduce ------------------------------
-// One cudaMalloc per rank: [16 flag ints | pad][epoch int | pad][buffer A][buffer B], exported with
-// CUDA IPC and mapped by every other rank of the node.  Peers are only ever read with plain loads.
+// ---- peer heap: exchange memory for the fused all-reduce and the expert-parallel all-to-all ----------
+// One cudaMalloc per rank, exported with CUDA IPC and mapped by every other rank of the node:
+//   [0, 16 KiB)   header: epoch counter (int 0), all-to-all epoch (int 1), arrival counters of the all-to-all
+//                 kernels (ints 2, 3); at 256 the all-reduce flags [kPeerChunks][8]; at 256 + 8 KiB the
+//                 all-to-all cells: pair counts [8], dispatch flags [8], return flags [8]
+//   then          two alternating all-reduce exchange buffers of world x buf_bytes each
+//   then          the all-to-all region (a2a_bytes)
+// Peers are written with plain stores and never read; every rank reads only its own memory.
+constexpr size_t kHeapHeader = 16384;
+constexpr size_t kHeapFlagsOff = 256;
+constexpr size_t kHeapA2aCellsOff = 256 + (size_t)kPeerChunks * 8 * sizeof(int);
+
 struct PeerHeap {
   void* local = nullptr;
   void* mapped[8] = {};
@@ -134,12 +145,14 @@ struct PeerHeap {
 };
 static PeerHeap g_heap[16];
 
-static void heap_layout(void* base, size_t buf_bytes, int** flags, int** epoch, float** a, float** b) {
-  char* p = (char*)base;
-  *flags = (int*)p;
-  *epoch = (int*)(p + 256);
-  *a = (float*)(p + 512);
-  *b = (float*)(p + 512 + buf_bytes);
+static void heap_fill(PeerInfo* info, int r, char* base, bool own) {
+  info->flags[r] = (int*)(base + kHeapFlagsOff);
+  const size_t ar = (size_t)info->world * info->buf_bytes;
+  info->bufs[0][r] = base + kHeapHeader;
+  info->bufs[1][r] = base + kHeapHeader + ar;
+  info->a2a_flags[r] = (int*)(base + kHeapA2aCellsOff);
+  info->a2a[r] = info->a2a_bytes ? base + kHeapHeader + 2 * ar : nullptr;
+  if (own) info->epoch = (int*)base;
 }
 
 const PeerInfo* comm_peer_info(int slot) {
@@ -152,25 +165,28 @@ using namespace rewb;
 
 extern "C" {
 
-int rewb200_comm_peer_alloc(int slot, int64_t buf_bytes, void* handle64) {
+int rewb200_comm_peer_alloc(int slot, int64_t allreduce_bytes, int64_t alltoall_bytes, void* handle64) {
   Ctx* c = ctx_get(slot);
   if (!c) return REWB200_ERR;
-  RB_REQUIRE(handle64 != nullptr && buf_bytes > 0 && buf_bytes % 256 == 0, "rewb200_comm_peer_alloc: buffer size must be a positive multiple of 256");
+  RB_REQUIRE(handle64 != nullptr && allreduce_bytes >= 0 && alltoall_bytes >= 0 && allreduce_bytes % 256 == 0 &&
+                 alltoall_bytes % 256 == 0 && allreduce_bytes + alltoall_bytes > 0,
+             "rewb200_comm_peer_alloc: sizes must be non-negative multiples of 256, not both zero");
   RB_REQUIRE(slot < 16 && g_comm[slot].comm, "rewb200_comm_peer_alloc: call rewb200_comm_init first");
-  RB_REQUIRE(g_comm[slot].world <= 8, "the fused all-reduce supports up to 8 ranks");
+  RB_REQUIRE(g_comm[slot].world <= 8, "the peer heap supports up to 8 ranks");
   RB_REQUIRE(!g_heap[slot].local, "rewb200_comm_peer_alloc: already allocated for this slot");
   RB_CUDA(cudaSetDevice(c->device));
   PeerHeap& h = g_heap[slot];
-  const size_t total = 512 + 2 * (size_t)buf_bytes;
+  const size_t total = kHeapHeader + 2 * (size_t)g_comm[slot].world * (size_t)allreduce_bytes + (size_t)alltoall_bytes;
   RB_CUDA(cudaMalloc(&h.local, total));
-  RB_CUDA(cudaMemset(h.local, 0, total));
+  RB_CUDA(cudaMemset(h.local, 0, kHeapHeader));
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
   cudaIpcMemHandle_t ih;
   RB_CUDA(cudaIpcGetMemHandle(&ih, h.local));
   memcpy(handle64, &ih, 64);
   h.info.world = g_comm[slot].world;
   h.info.rank = g_comm[slot].rank;
-  h.info.buf_bytes = (size_t)buf_bytes;
+  h.info.buf_bytes = (size_t)allreduce_bytes;
+  h.info.a2a_bytes = (size_t)alltoall_bytes;
   return REWB200_OK;
 }
 
@@ -178,6 +194,7 @@ int rewb200_comm_peer_attach(int slot, const void* handles_all) {
   Ctx* c = ctx_get(slot);
   if (!c) return REWB200_ERR;
   RB_REQUIRE(slot < 16 && g_heap[slot].local && handles_all, "rewb200_comm_peer_attach: call rewb200_comm_peer_alloc first");
+  RB_REQUIRE(!g_heap[slot].attached, "rewb200_comm_peer_attach: already attached for this slot");
   RB_CUDA(cudaSetDevice(c->device));
   PeerHeap& h = g_heap[slot];
   for (int r = 0; r < h.info.world; ++r) {
@@ -188,9 +205,7 @@ int rewb200_comm_peer_attach(int slot, const void* handles_all) {
       RB_CUDA(cudaIpcOpenMemHandle(&h.mapped[r], ih, cudaIpcMemLazyEnablePeerAccess));
       base = h.mapped[r];
     }
-    int* ep = nullptr;
-    heap_layout(base, h.info.buf_bytes, &h.info.flags[r], &ep, &h.info.bufs[0][r], &h.info.bufs[1][r]);
-    if (r == h.info.rank) h.info.epoch = ep;
+    heap_fill(&h.info, r, (char*)base, r == h.info.rank);
   }
   RB_CUDA(cudaDeviceSynchronize());
   h.attached = true;
@@ -226,7 +241,7 @@ int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n) {
   Ctx* c = ctx_get(slot);
   if (!c) return REWB200_ERR;
   RB_CUDA(cudaSetDevice(c->device));
-  RB_TRY(comm_allreduce_sum_f32(c, slot, (float*)device_ptr, n));
+  RB_TRY(comm_allreduce_sum(c, slot, device_ptr, n, REWB200_F32));
   RB_CUDA(cudaStreamSynchronize(c->stream));
   ncclResult_t async = ncclSuccess;
   RB_NCCL(g_nccl.CommGetAsyncError(g_comm[slot].comm, &async));

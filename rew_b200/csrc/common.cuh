@@ -44,8 +44,9 @@ struct Ctx {
   cudaStream_t side = nullptr;            // second stream for a branch that runs beside the main one (MoE shared experts)
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool moe_overlap = true;
-  int ep_prefix = 2;          // expert-parallel prefill: 1 exchange pair counts, then only the occupied slot prefixes;
-                              // 0 always the worst-case capacity; 2 prefixes from 4 ranks on (at 2 ranks they measured no gain)
+  int ep_prefix = 2;          // expert-parallel exchange: 2 (auto) over the peer heap when one is attached and the step fits,
+                              // else NCCL as under 1 from 4 ranks on; 1 NCCL, pair counts first, then only the occupied slot
+                              // prefixes (outside a captured graph); 0 NCCL, always the worst-case capacity
   int* d_status = nullptr;   // kernels record KernelStatus codes here
   static constexpr int kTickets = 16384;
   int* d_tickets = nullptr;  // split-KV decode attention: one arrival counter per (sequence, kv head), zero between launches
@@ -62,6 +63,7 @@ struct Ctx {
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
+  int inject_alloc_fail = 0;  // test hook: the n-th activation allocation from now fails on the host
   int option_epoch = 0;      // bumped by rewb200_set_option; captured graphs from older epochs are rebuilt
   void* pinned = nullptr;    // pinned host staging for H2D/D2H of buffers
   size_t pinned_bytes = 0;
@@ -222,17 +224,23 @@ struct NormArgs {
   int out_dtype;
   int vocab;
   int* status;
-  // One-shot tensor-parallel all-reduce fused into this kernel (n_peers > 0): slab r of the sum is
-  // read from rank r's memory (peer_part[r], plain peer loads over NVLink; own rank included) after a
-  // flag barrier: this rank stores `*epoch + barrier_offset` into its cell of every rank's flag array
-  // and waits (bounded) until every cell of its own flag array has reached that value.
+  int partial_bf16;       // the partial slabs hold bf16 instead of f32 (a tensor-parallel sum that travelled as bf16)
+  // One-shot tensor-parallel all-reduce fused into this kernel (n_peers > 0), push style: a CTA sums its
+  // columns of the local split-K slabs, stores that partial (payload dtype) into slot `my_rank` of EVERY
+  // peer's exchange buffer with plain peer stores, raises its chunk's flag on every peer (release, system
+  // scope), waits (bounded) until the same chunk's flags of all peers have arrived in its OWN flag array, and
+  // then reads the peers' partials from LOCAL memory and adds them in rank order, so every rank computes
+  // the same bits.  Flag values are `*epoch + barrier_offset`, increasing from one all-reduce to the next.
   int n_peers;
   int my_rank;
-  const float* peer_part[8];
-  int* peer_flags[8];     // flag arrays of all ranks (index by rank), 16 ints each
+  int payload_bf16;       // partials cross NVLink as bf16 (bf16 models) or f32
+  void* peer_buf[8];      // rank r's exchange buffer of this all-reduce: [world][slot_elems] payload elements
+  int* peer_flags[8];     // rank r's flag array: [kPeerChunks][8] ints, cell (chunk, writer rank)
+  int64_t slot_elems;     // payload elements between two writers' slots
   const int* epoch;       // device counter, advanced once per forward on every rank alike
   int barrier_offset;
 };
+constexpr int kPeerChunks = 256;  // CTAs of one fused all-reduce launch (rows * 4 on the cluster kernel)
 int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows);
 
 struct KvLayout {
@@ -300,10 +308,29 @@ size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits);
 // scratch (optional): rows*64*8 bytes lets wide rows be scanned by several CTAs each
 struct PeerInfo {
   int world = 0, rank = 0;
-  size_t buf_bytes = 0;        // capacity of each of the two exchange buffers
-  float* bufs[2][8] = {};      // [which][rank] (own rank: the local allocation)
-  int* flags[8] = {};          // [rank]
+  size_t buf_bytes = 0;        // capacity of ONE writer's slot; an exchange buffer holds `world` of them
+  char* bufs[2][8] = {};       // [which][rank]: the two alternating exchange buffers of every rank (own rank: local)
+  int* flags[8] = {};          // [rank]: flag arrays, kPeerChunks x 8 ints
   int* epoch = nullptr;        // local device counter
+  char* a2a[8] = {};           // [rank]: the expert-parallel all-to-all region of every rank (nullptr without one)
+  size_t a2a_bytes = 0;
+  int* a2a_flags[8] = {};      // [rank]: 4 x 8 ints, cell (phase, writer rank)
+};
+// Expert-parallel all-to-all over the peer heap (src/rew/ops/distributed.nim:106-128): the dispatch kernel
+// stores every (token, expert) pair's row straight into the owning rank's region, the return kernel
+// stores the expert outputs straight into the asking rank's region; pair counts and flags travel the
+// same way, so no count exchange passes through the host and no padding crosses NVLink.
+struct A2aArgs {
+  int world, my_rank;
+  int* cells[8];      // rank r's cells: pair counts [8] | dispatch flags [8] | return flags [8], indexed by writer rank
+  char* region[8];    // rank r's all-to-all region; below, byte offsets inside it (the same on every rank)
+  int64_t off_x;      // recv_x [world][cap][d] activations
+  int64_t off_meta;   // recv_meta [world][cap] local expert ids
+  int64_t off_back;   // back [world][cap][d] f32 expert outputs
+  int* arrive;        // two local arrival counters (dispatch, return), zero between launches
+  const int* epoch;   // local device counter; flag value of this layer = *epoch + offset
+  int offset;
+  int* status;
 };
 // nullptr when no peer heap has been attached for the slot
 const PeerInfo* comm_peer_info(int slot);

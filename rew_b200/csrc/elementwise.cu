@@ -143,6 +143,91 @@ template <> struct Vec4<bf16> {
   }
 };
 
+// Sum of the split-K slabs at element offset `idx` (a multiple of 4), in slab order.
+__device__ __forceinline__ float4 partial_sum4(const NormArgs& a, int64_t idx) {
+  float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (a.partial_bf16) {
+    const bf16* pp = reinterpret_cast<const bf16*>(a.partial) + idx;
+    for (int s = 0; s < a.nsplit; ++s) {
+      const float4 q = Vec4<bf16>::load(pp + s * a.split_stride);
+      p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
+    }
+    return p;
+  }
+  const float* pp = a.partial + idx;
+  int s = 0;
+  for (; s + 4 <= a.nsplit; s += 4) {
+    const float4 p0 = *reinterpret_cast<const float4*>(pp + (s + 0) * a.split_stride);
+    const float4 p1 = *reinterpret_cast<const float4*>(pp + (s + 1) * a.split_stride);
+    const float4 p2 = *reinterpret_cast<const float4*>(pp + (s + 2) * a.split_stride);
+    const float4 p3 = *reinterpret_cast<const float4*>(pp + (s + 3) * a.split_stride);
+    p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
+    p.x += p1.x; p.y += p1.y; p.z += p1.z; p.w += p1.w;
+    p.x += p2.x; p.y += p2.y; p.z += p2.z; p.w += p2.w;
+    p.x += p3.x; p.y += p3.y; p.z += p3.z; p.w += p3.w;
+  }
+  for (; s < a.nsplit; ++s) {
+    const float4 p0 = *reinterpret_cast<const float4*>(pp + s * a.split_stride);
+    p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
+  }
+  return p;
+}
+
+// Tensor-parallel all-reduce of this CTA's columns (see NormArgs): p[c] holds this rank's partial of the
+// float4 at element offset idx[c] (idx[c] < 0: none) and comes back as the sum over all ranks, added in
+// rank order from the values that crossed NVLink, so every rank ends up with the same bits.  `chunk`
+// numbers the CTA; the same CTA of every rank handles the same columns.
+template <int NCH>
+__device__ __forceinline__ void tp_exchange4(const NormArgs& a, float4 (&p)[NCH], const int64_t (&idx)[NCH], int chunk) {
+  const int target = *a.epoch + a.barrier_offset;
+  if (a.payload_bf16) {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (idx[c] < 0) continue;
+      uint2 u;
+      u.x = pack_bf16(p[c].x, p[c].y);
+      u.y = pack_bf16(p[c].z, p[c].w);
+      for (int r = 0; r < a.n_peers; ++r)
+        if (r != a.my_rank)
+          *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.peer_buf[r]) + (int64_t)a.my_rank * a.slot_elems + idx[c]) = u;
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+      p[c] = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));  // what the peers see
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (idx[c] < 0) continue;
+      for (int r = 0; r < a.n_peers; ++r)
+        if (r != a.my_rank)
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.peer_buf[r]) + (int64_t)a.my_rank * a.slot_elems + idx[c]) = p[c];
+    }
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < a.n_peers && (int)threadIdx.x != a.my_rank)
+    peer_flag_release(a.peer_flags[threadIdx.x] + chunk * 8 + a.my_rank, target);
+  peer_flags_wait(a.peer_flags[a.my_rank] + chunk * 8, 1, a.n_peers, a.my_rank, target, a.status);
+  const char* mine = reinterpret_cast<const char*>(a.peer_buf[a.my_rank]);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    if (idx[c] < 0) continue;
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < a.n_peers; ++r) {
+      float4 q = p[c];
+      if (r != a.my_rank) {
+        if (a.payload_bf16) {
+          const uint2 u = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(mine) + (int64_t)r * a.slot_elems + idx[c]));
+          const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+          q = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+        } else {
+          q = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(mine) + (int64_t)r * a.slot_elems + idx[c]));
+        }
+      }
+      t.x += q.x; t.y += q.y; t.z += q.z; t.w += q.w;
+    }
+    p[c] = t;
+  }
+}
+
 template <typename TE, typename TO, int NCH>
 __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormArgs a) {
   __shared__ float red[33];
@@ -163,71 +248,33 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
     }
     erow = reinterpret_cast<const TE*>(a.embed) + id * d;
   }
-  if (a.n_peers > 0) {
-    // flag barrier across the tensor-parallel ranks (bounded wait; a timeout is reported, never a hang)
-    const int target = *a.epoch + a.barrier_offset;
-    if (blockIdx.x == 0 && threadIdx.x < a.n_peers) {
-      __threadfence_system();
-      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(a.peer_flags[threadIdx.x] + a.my_rank), "r"(target) : "memory");
-    }
-    if (threadIdx.x < a.n_peers) {
-      const int* cell = a.peer_flags[a.my_rank] + threadIdx.x;
-      const uint64_t t0 = global_timer_ns();
-      for (uint32_t it = 0;; ++it) {
-        int v;
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(cell) : "memory");
-        if (v - target >= 0) break;
-        if ((it & 63u) == 63u && global_timer_ns() - t0 > 2000000000ull) {
-          atomicExch(a.status, KS_PEER_TIMEOUT);
-          break;
-        }
-      }
-    }
-    __syncthreads();
-  }
   float4 vals[NCH];
+  const bool summed = a.partial != nullptr;
+  if (summed) {
+    int64_t idx[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int64_t i = ((int64_t)c * NORMV_THREADS + threadIdx.x) * 4;
+      idx[c] = i < d ? row * d + i : -1;
+      vals[c] = i < d ? partial_sum4(a, idx[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx, (int)blockIdx.x);
+  }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int64_t i = ((int64_t)c * NORMV_THREADS + threadIdx.x) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < d) {
       v = erow ? Vec4<TE>::load(erow + i) : *reinterpret_cast<const float4*>(xr + i);
-      if (a.n_peers > 0) {
-        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < a.n_peers; ++r) {  // fixed rank order: every rank computes the same sum
-          const float4 q = __ldcv(reinterpret_cast<const float4*>(a.peer_part[r] + row * d + i));
-          p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
-        }
-        if (a.bias) {
-          const float4 b = *reinterpret_cast<const float4*>(a.bias + i);
-          p.x += b.x; p.y += b.y; p.z += b.z; p.w += b.w;
-        }
-        v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
-      } else if (a.partial) {
-        const float* pp = a.partial + row * d + i;
-        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-        int s = 0;
-        for (; s + 4 <= a.nsplit; s += 4) {
-          const float4 p0 = *reinterpret_cast<const float4*>(pp + (s + 0) * a.split_stride);
-          const float4 p1 = *reinterpret_cast<const float4*>(pp + (s + 1) * a.split_stride);
-          const float4 p2 = *reinterpret_cast<const float4*>(pp + (s + 2) * a.split_stride);
-          const float4 p3 = *reinterpret_cast<const float4*>(pp + (s + 3) * a.split_stride);
-          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
-          p.x += p1.x; p.y += p1.y; p.z += p1.z; p.w += p1.w;
-          p.x += p2.x; p.y += p2.y; p.z += p2.z; p.w += p2.w;
-          p.x += p3.x; p.y += p3.y; p.z += p3.z; p.w += p3.w;
-        }
-        for (; s < a.nsplit; ++s) {
-          const float4 p0 = *reinterpret_cast<const float4*>(pp + s * a.split_stride);
-          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
-        }
+      if (summed) {
+        float4 p = vals[c];
         if (a.bias) {
           const float4 b = *reinterpret_cast<const float4*>(a.bias + i);
           p.x += b.x; p.y += b.y; p.z += b.z; p.w += b.w;
         }
         v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
       }
-      if (a.x_res && (erow || a.partial || a.n_peers > 0)) *reinterpret_cast<float4*>(xr + i) = v;
+      if (a.x_res && (erow || summed)) *reinterpret_cast<float4*>(xr + i) = v;
     }
     vals[c] = v;
   }
@@ -302,6 +349,17 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
     }
     erow = reinterpret_cast<const TE*>(a.embed) + id * d;
   }
+  const bool summed = a.partial != nullptr;
+  if (summed) {
+    int64_t idx[NCH];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int64_t off = ((int64_t)c * 256 + threadIdx.x) * 4;
+      idx[c] = off < dq ? row * d + col0 + off : -1;
+      vals[c] = off < dq ? partial_sum4(a, idx[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx, (int)blockIdx.x);
+  }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     const int64_t off = ((int64_t)c * 256 + threadIdx.x) * 4;
@@ -309,31 +367,15 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (off < dq) {
       v = erow ? Vec4<TE>::load(erow + i) : *reinterpret_cast<const float4*>(xr + i);
-      if (a.partial) {
-        const float* pp = a.partial + row * d + i;
-        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-        int s = 0;
-        for (; s + 4 <= a.nsplit; s += 4) {
-          const float4 p0 = *reinterpret_cast<const float4*>(pp + (s + 0) * a.split_stride);
-          const float4 p1 = *reinterpret_cast<const float4*>(pp + (s + 1) * a.split_stride);
-          const float4 p2 = *reinterpret_cast<const float4*>(pp + (s + 2) * a.split_stride);
-          const float4 p3 = *reinterpret_cast<const float4*>(pp + (s + 3) * a.split_stride);
-          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
-          p.x += p1.x; p.y += p1.y; p.z += p1.z; p.w += p1.w;
-          p.x += p2.x; p.y += p2.y; p.z += p2.z; p.w += p2.w;
-          p.x += p3.x; p.y += p3.y; p.z += p3.z; p.w += p3.w;
-        }
-        for (; s < a.nsplit; ++s) {
-          const float4 p0 = *reinterpret_cast<const float4*>(pp + s * a.split_stride);
-          p.x += p0.x; p.y += p0.y; p.z += p0.z; p.w += p0.w;
-        }
+      if (summed) {
+        float4 p = vals[c];
         if (a.bias) {
           const float4 b = *reinterpret_cast<const float4*>(a.bias + i);
           p.x += b.x; p.y += b.y; p.z += b.z; p.w += b.w;
         }
         v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
       }
-      if (a.x_res && (erow || a.partial)) *reinterpret_cast<float4*>(xr + i) = v;
+      if (a.x_res && (erow || summed)) *reinterpret_cast<float4*>(xr + i) = v;
     }
     vals[c] = v;
   }
@@ -705,20 +747,6 @@ __global__ void __launch_bounds__(32) argmax_gathered_kernel(const void* gathere
   if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
-// dst[i] = part[0][i] + part[1][i] + ...  (dst: this rank's exchange buffer for the fused all-reduce)
-__global__ void __launch_bounds__(256) slab_sum_to_kernel(const float* part, int nsplit, int64_t slab, int64_t n4, float* dst) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n4) return;
-  float4 a = reinterpret_cast<const float4*>(part)[i];
-  for (int s = 1; s < nsplit; ++s) {
-    const float4 b = reinterpret_cast<const float4*>(part + s * slab)[i];
-    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-  }
-  reinterpret_cast<float4*>(dst)[i] = a;
-}
-
 __global__ void epoch_bump_kernel(int* epoch, int by) {
   pdl_launch_dependents();
   pdl_wait();
@@ -790,8 +818,10 @@ int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows) {
   RB_REQUIRE(a.d <= (int64_t)NORM_THREADS * NORM_MAX_PER_THREAD, "norm width above 16384 is not supported");
   const bool e16 = a.embed_dtype == REWB200_BF16, o16 = a.out_dtype == REWB200_BF16;
   cudaError_t e;
-  RB_REQUIRE(a.n_peers == 0 || a.d % 4 == 0, "the fused all-reduce needs d_model % 4 == 0");
-  if (a.n_peers == 0 && o16 && a.norm_kind >= 0 && rows <= 64 && a.d % 16 == 0 && a.d <= 16384 && c->norm_cluster) {
+  RB_REQUIRE(a.n_peers == 0 || (a.d % 4 == 0 && a.partial != nullptr && rows * 4 <= kPeerChunks && a.n_peers <= 8),
+             "the fused all-reduce needs d_model % 4 == 0, local partials and at most 64 rows");
+  RB_REQUIRE(!a.partial_bf16 || a.d % 4 == 0, "bf16 partials need d_model % 4 == 0");
+  if (o16 && a.norm_kind >= 0 && rows <= 64 && a.d % 16 == 0 && a.d <= 16384 && c->norm_cluster) {
     const int nch = (int)((a.d / 16 + 255) / 256);  // float4 per thread over a quarter row
     dim3 g((unsigned)(rows * 4)), b(256);
 #define RB_NORMC(TE)                                                                                  \
@@ -894,16 +924,6 @@ int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows
   if (rows == 0) return REWB200_OK;
   RB_CUDA(launch_k(argmax_gathered_kernel, dim3((unsigned)rows), dim3(32), 0, c->stream, c->use_pdl, gathered, world,
                    (int)rows, nchunks, out));
-  ++g_launch_total;
-  return REWB200_OK;
-}
-
-int slab_sum_to_launch(Ctx* c, const float* part, int nsplit, int64_t slab_elems, float* dst) {
-  if (slab_elems == 0) return REWB200_OK;
-  RB_REQUIRE(slab_elems % 4 == 0, "slab size must be a multiple of 4 floats");
-  const int64_t n4 = slab_elems / 4;
-  RB_CUDA(launch_k(slab_sum_to_kernel, dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, c->stream, c->use_pdl, part, nsplit,
-                   slab_elems, n4, dst));
   ++g_launch_total;
   return REWB200_OK;
 }

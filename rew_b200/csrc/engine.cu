@@ -29,10 +29,9 @@ namespace rewb {
 
 int comm_world(int slot);
 int comm_rank(int slot);
-int comm_allreduce_sum_f32(Ctx* c, int slot, float* ptr, int64_t n);
+int comm_allreduce_sum(Ctx* c, int slot, void* ptr, int64_t n, int dtype);
 int comm_allgather_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_rank);
 int slab_sum_launch(Ctx* c, float* part, int nsplit, int64_t slab_elems);
-int slab_sum_to_launch(Ctx* c, const float* part, int nsplit, int64_t slab_elems, float* dst);
 int epoch_bump_launch(Ctx* c, int* epoch, int by);
 int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_peer);
 int comm_alltoallv_rows(Ctx* c, int slot, const void* send, void* recv, size_t peer_stride_bytes, size_t row_bytes,
@@ -50,6 +49,13 @@ int moe_group_launch(Ctx* c, const void* recv_x, int dtype, const int* recv_meta
 int moe_return_launch(Ctx* c, const float* ys, const int* slot_pos, int n_slots, int64_t d, float* ret);
 int moe_combine_launch(Ctx* c, const float* back, const int* pair_slot, const float* topw, int64_t tokens, int k, int64_t d,
                        float* out, int accumulate);
+int moe_dispatch_peer_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d,
+                             int experts_per_rank, int capacity, int* cursor, int* pair_slot, const A2aArgs& a);
+int moe_group_peer_launch(Ctx* c, int dtype, int n_slots, int capacity, int64_t d, int n_experts, int* count, int* offsets,
+                          int* cursor2, void* xs, int* slot_pos, const A2aArgs& a);
+int moe_return_peer_launch(Ctx* c, const float* ys, const int* slot_pos, int n_slots, int capacity, int64_t d, const A2aArgs& a);
+int moe_combine_peer_launch(Ctx* c, const int* pair_slot, const float* topw, int64_t tokens, int k, int64_t d, float* out,
+                            int accumulate, const A2aArgs& a);
 int sample_launch(Ctx* c, const float* logits, float* work, int64_t B, int64_t V, int* hist, int* hist_len, int hist_cap,
                   uint32_t* keys, int* steps, int* next, float* logprob, int logprob_cap, float temperature, int top_k,
                   float top_p, float min_p, float rep_penalty, int do_sample, const int* active);
@@ -378,6 +384,18 @@ int scatter(rewb200_model* m, int64_t src_ld, int64_t row0, int64_t col0, int64_
   return REWB200_OK;
 }
 
+// cudaMalloc of one activation buffer.  The option "inject_alloc_fail" = n makes the n-th call from now
+// fail on the host without touching the device (a test hook for the failed-growth path).
+int acts_alloc(Ctx* c, void** p, size_t bytes) {
+  if (c->inject_alloc_fail > 0 && --c->inject_alloc_fail == 0) return fail("cudaMalloc: out of memory (injected)");
+  RB_CUDA(cudaMalloc(p, bytes));
+  return REWB200_OK;
+}
+template <typename T>
+int acts_alloc(Ctx* c, T** p, size_t bytes) {
+  return acts_alloc(c, (void**)p, bytes);
+}
+
 int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
   rewb200_model* m = s->m;
   const rewb200_config& c = m->cfg;
@@ -388,19 +406,28 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
                      (void**)&s->moe_logits, (void**)&s->moe_topw, (void**)&s->moe_topi, (void**)&s->moe_ints, &s->moe_send,
                      &s->moe_recv, &s->moe_xs, &s->moe_hs, (void**)&s->moe_ys, (void**)&s->moe_ret, (void**)&s->moe_back,
                      (void**)&s->moe_tmp};
+    // From here until every allocation below has succeeded the session holds no activation buffers: a failed
+    // growth must leave it in a state where the next call allocates again instead of launching on NULL.
+    s->rows_cap = 0;
+    s->part_bytes = 0;
+    if (s->graph) {
+      cudaGraphExecDestroy(s->graph);
+      s->graph = nullptr;
+    }
     for (void** p : ptrs)
       if (*p) {
-        RB_CUDA(cudaFree(*p));
+        void* q = *p;
         *p = nullptr;
+        RB_CUDA(cudaFree(q));
       }
     int64_t fmax = 0;
     for (const LayerDev& L : m->layers) fmax = std::max(fmax, L.ffn_local);
     if (c.n_routed > 0) fmax = std::max<int64_t>(fmax, c.moe_ffn);
-    RB_CUDA(cudaMalloc((void**)&s->x_res, (size_t)rows * c.d_model * sizeof(float)));
-    RB_CUDA(cudaMalloc(&s->xn, (size_t)rows * c.d_model * es));
-    RB_CUDA(cudaMalloc(&s->q, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
-    RB_CUDA(cudaMalloc(&s->attn, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
-    RB_CUDA(cudaMalloc(&s->h, (size_t)rows * std::max<int64_t>(fmax, 1) * es));
+    RB_TRY(acts_alloc(m->c, (void**)&s->x_res, (size_t)rows * c.d_model * sizeof(float)));
+    RB_TRY(acts_alloc(m->c, &s->xn, (size_t)rows * c.d_model * es));
+    RB_TRY(acts_alloc(m->c, &s->q, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
+    RB_TRY(acts_alloc(m->c, &s->attn, (size_t)rows * std::max<int64_t>(m->nq, 1) * es));
+    RB_TRY(acts_alloc(m->c, &s->h, (size_t)rows * std::max<int64_t>(fmax, 1) * es));
     const int64_t widest = std::max<int64_t>(m->nqkv, c.d_model);
     // up to 16 split-K slabs of the widest residual-side Linear, or 4 of gate|up, at steps of at most 64 rows
     const size_t small_rows = (size_t)std::min<int64_t>(rows, 64);
@@ -409,45 +436,46 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
     s->part_bytes = std::max(s->part_bytes, (size_t)rows * widest * sizeof(float));
     if (c.weight_quant)  // the quantised gate|up GEMV leaves up to 4 slabs of [32][2f] here at decode sizes
       s->part_bytes = std::max(s->part_bytes, (size_t)32 * std::max<size_t>(16 * widest, 4 * 2 * fmax) * sizeof(float));
-    RB_CUDA(cudaMalloc((void**)&s->part, s->part_bytes));
-    if (c.dtype == REWB200_F32) RB_CUDA(cudaMalloc((void**)&s->gu32, (size_t)rows * 2 * std::max<int64_t>(fmax, 1) * sizeof(float)));
+    RB_TRY(acts_alloc(m->c, (void**)&s->part, s->part_bytes));
+    if (c.dtype == REWB200_F32) RB_TRY(acts_alloc(m->c, (void**)&s->gu32, (size_t)rows * 2 * std::max<int64_t>(fmax, 1) * sizeof(float)));
     if (c.n_routed > 0) {
       const int ep = c.ep_size, k = c.top_k, E_l = c.n_routed / ep;
       const int64_t cap = rows * k, slots = cap * ep;
-      RB_CUDA(cudaMalloc((void**)&s->moe_logits, (size_t)std::max<int64_t>(rows, 8 * std::min<int64_t>(rows, 64)) * c.n_routed * sizeof(float)));  // or 8 split-K slabs of a small step
-      RB_CUDA(cudaMalloc((void**)&s->moe_topw, (size_t)rows * k * sizeof(float)));
-      RB_CUDA(cudaMalloc((void**)&s->moe_topi, (size_t)rows * k * sizeof(int)));
+      RB_TRY(acts_alloc(m->c, (void**)&s->moe_logits, (size_t)std::max<int64_t>(rows, 8 * std::min<int64_t>(rows, 64)) * c.n_routed * sizeof(float)));  // or 8 split-K slabs of a small step
+      RB_TRY(acts_alloc(m->c, (void**)&s->moe_topw, (size_t)rows * k * sizeof(float)));
+      RB_TRY(acts_alloc(m->c, (void**)&s->moe_topi, (size_t)rows * k * sizeof(int)));
       // the last 16 ints hold the per-peer counts this rank receives (prefix exchange of large steps)
       s->moe_ints_n = (size_t)(ep + 3 * (E_l + 1) + 3 * slots + rows * k) + 16;
-      RB_CUDA(cudaMalloc((void**)&s->moe_ints, s->moe_ints_n * sizeof(int)));
-      RB_CUDA(cudaMalloc((void**)&s->moe_tmp, (size_t)rows * c.d_model * sizeof(float)));
+      RB_TRY(acts_alloc(m->c, (void**)&s->moe_ints, s->moe_ints_n * sizeof(int)));
+      RB_TRY(acts_alloc(m->c, (void**)&s->moe_tmp, (size_t)rows * c.d_model * sizeof(float)));
       if (c.dtype == REWB200_BF16) {
-        RB_CUDA(cudaMalloc(&s->moe_send, (size_t)slots * c.d_model * es));
-        if (ep > 1) RB_CUDA(cudaMalloc(&s->moe_recv, (size_t)slots * c.d_model * es));
-        RB_CUDA(cudaMalloc(&s->moe_xs, (size_t)(slots + 128) * c.d_model * es));
-        RB_CUDA(cudaMalloc(&s->moe_hs, (size_t)(slots + 128) * c.moe_ffn * es));
+        RB_TRY(acts_alloc(m->c, &s->moe_send, (size_t)slots * c.d_model * es));
+        if (ep > 1) RB_TRY(acts_alloc(m->c, &s->moe_recv, (size_t)slots * c.d_model * es));
+        RB_TRY(acts_alloc(m->c, &s->moe_xs, (size_t)(slots + 128) * c.d_model * es));
+        RB_TRY(acts_alloc(m->c, &s->moe_hs, (size_t)(slots + 128) * c.moe_ffn * es));
         RB_CUDA(cudaMemset(s->moe_xs, 0, (size_t)(slots + 128) * c.d_model * es));
         RB_CUDA(cudaMemset(s->moe_hs, 0, (size_t)(slots + 128) * c.moe_ffn * es));
-        RB_CUDA(cudaMalloc((void**)&s->moe_ys, (size_t)slots * c.d_model * sizeof(float)));
-        RB_CUDA(cudaMalloc((void**)&s->moe_ret, (size_t)slots * c.d_model * sizeof(float)));
-        if (ep > 1) RB_CUDA(cudaMalloc((void**)&s->moe_back, (size_t)slots * c.d_model * sizeof(float)));
+        RB_TRY(acts_alloc(m->c, (void**)&s->moe_ys, (size_t)slots * c.d_model * sizeof(float)));
+        RB_TRY(acts_alloc(m->c, (void**)&s->moe_ret, (size_t)slots * c.d_model * sizeof(float)));
+        if (ep > 1) RB_TRY(acts_alloc(m->c, (void**)&s->moe_back, (size_t)slots * c.d_model * sizeof(float)));
       }
     }
     s->rows_cap = rows;
-    if (s->graph) {
-      cudaGraphExecDestroy(s->graph);
-      s->graph = nullptr;
-    }
   }
   if (logits_rows > s->logits_rows) {
     RB_CUDA(cudaStreamSynchronize(m->c->stream));
-    if (s->logits) RB_CUDA(cudaFree(s->logits));
-    RB_CUDA(cudaMalloc((void**)&s->logits, (size_t)logits_rows * m->vocab_l * sizeof(float)));
-    s->logits_rows = logits_rows;
+    s->logits_rows = 0;
     if (s->graph) {
       cudaGraphExecDestroy(s->graph);
       s->graph = nullptr;
     }
+    if (s->logits) {
+      float* q = s->logits;
+      s->logits = nullptr;
+      RB_CUDA(cudaFree(q));
+    }
+    RB_TRY(acts_alloc(m->c, (void**)&s->logits, (size_t)logits_rows * m->vocab_l * sizeof(float)));
+    s->logits_rows = logits_rows;
   }
   return REWB200_OK;
 }
@@ -517,7 +545,25 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
 // Routed experts of one MoE layer for the normalised rows in s->xn: router, top-k, dispatch to the
 // owning ranks, grouped expert GEMMs, return, weighted combine into slab 0 of s->part
 // (DeepSeekMoE.forward, src/rew/models/deepseek.nim:132-144).
-int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, float* out = nullptr) {
+// Bytes of the peer heap's all-to-all region a step of `slots` slot rows needs (activations, expert ids, f32 results).
+size_t a2a_need(int64_t slots, int64_t d, size_t es, int64_t* off_meta, int64_t* off_back) {
+  auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+  const size_t x = up((size_t)slots * d * es), meta = up((size_t)slots * sizeof(int));
+  if (off_meta) *off_meta = (int64_t)x;
+  if (off_back) *off_back = (int64_t)(x + meta);
+  return x + meta + up((size_t)slots * d * sizeof(float));
+}
+
+// Whether the expert-parallel exchange of a step of `rows` tokens runs over the peer heap.
+bool ep_uses_peer_heap(const rewb200_model* m, int64_t rows) {
+  const rewb200_config& cf = m->cfg;
+  if (cf.ep_size <= 1 || m->c->ep_prefix == 0 || m->c->ep_prefix == 1) return false;  // options capacity / prefix: NCCL
+  const PeerInfo* pi = comm_peer_info(m->slot);
+  return pi != nullptr && pi->world == cf.ep_size && pi->a2a[pi->rank] != nullptr &&
+         a2a_need(rows * cf.top_k * cf.ep_size, cf.d_model, dtype_size(cf.dtype), nullptr, nullptr) <= pi->a2a_bytes;
+}
+
+int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, float* out = nullptr, int moe_index = 0) {
   rewb200_model* m = s->m;
   Ctx* c = m->c;
   const rewb200_config& cf = m->cfg;
@@ -580,6 +626,33 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
                               max_rows_l));
     return moe_combine_launch(c, s->moe_ys, pair_slot, s->moe_topw, rows, k, d, out ? out : s->part, accumulate ? 1 : 0);
   }
+  if (ep_uses_peer_heap(m, rows)) {
+    const PeerInfo* pi = comm_peer_info(m->slot);
+    A2aArgs a;
+    memset(&a, 0, sizeof(a));
+    a.world = ep;
+    a.my_rank = pi->rank;
+    for (int r = 0; r < ep; ++r) {
+      a.cells[r] = pi->a2a_flags[r];
+      a.region[r] = pi->a2a[r];
+    }
+    a.off_x = 0;
+    a2a_need(slots, d, dtype_size(dt), &a.off_meta, &a.off_back);
+    a.arrive = pi->epoch + 2;
+    a.epoch = pi->epoch + 1;
+    a.offset = moe_index + 1;
+    a.status = c->d_status;
+    RB_TRY(moe_reset_launch(c, cursor, ep, count, E_l + 1, send_meta, 0));
+    RB_TRY(moe_dispatch_peer_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, (int)cap, cursor, pair_slot, a));
+    RB_TRY(moe_group_peer_launch(c, dt, (int)slots, (int)cap, d, E_l, count, offsets, cursor2, s->moe_xs, slot_pos, a));
+    const int max_rows_p = (int)std::min<int64_t>(rows * ep, slots);
+    RB_TRY(linear_bf16_launch(c, X.plan_gu, (const bf16*)s->moe_xs, d, slots, EPI_SWIGLU_BF16, 1, s->moe_hs, f, X.gu_b, offsets,
+                              max_rows_p));
+    RB_TRY(linear_bf16_launch(c, X.plan_down, (const bf16*)s->moe_hs, f, slots, EPI_BIAS_F32, 1, s->moe_ys, d, X.down_b, offsets,
+                              max_rows_p));
+    RB_TRY(moe_return_peer_launch(c, s->moe_ys, slot_pos, (int)slots, (int)cap, d, a));
+    return moe_combine_peer_launch(c, pair_slot, s->moe_topw, rows, k, d, out ? out : s->part, accumulate ? 1 : 0, a);
+  }
   RB_TRY(moe_reset_launch(c, cursor, ep, count, E_l + 1, send_meta, (int)slots));
   RB_TRY(moe_dispatch_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, (int)cap, cursor, s->moe_send, send_meta, pair_slot));
   const void* rx = s->moe_send;
@@ -589,7 +662,7 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
   // exchange, which needs no host round trip and can be captured.
   cudaStreamCaptureStatus cap_st = cudaStreamCaptureStatusNone;
   RB_CUDA(cudaStreamIsCapturing(c->stream, &cap_st));
-  const bool prefix = ep > 1 && ep <= 16 && (c->ep_prefix == 1 || (c->ep_prefix == 2 && ep >= 4)) &&
+  const bool prefix = ep > 1 && ep <= 16 && (c->ep_prefix == 1 || (c->ep_prefix >= 2 && ep >= 4)) &&
                       cap_st == cudaStreamCaptureStatusNone && cap >= 64;
   int* h_send_rows = c->h_status + 16;  // pinned: [16 send | 16 recv]
   int* h_recv_rows = c->h_status + 32;
@@ -712,32 +785,47 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     a.beta = m->layers[0].ln1b;
     RB_TRY(residual_norm_launch(c, a, rows));
   }
-  // Tensor parallel: decode-size steps sum the row-parallel partials with the fused one-shot
-  // all-reduce (peer loads inside residual_norm); larger ones go through NCCL.
+  // Tensor parallel: steps of up to 64 rows sum the row-parallel partials inside residual_norm (each CTA
+  // pushes its columns to every rank's heap and adds the peers' in rank order); larger ones go through
+  // NCCL, bf16 models with a bf16 payload (the o / down projections then write one bf16 slab, no bias).
   const PeerInfo* pi = cf.tp_size > 1 ? comm_peer_info(m->slot) : nullptr;
-  const bool oneshot = pi != nullptr && d % 4 == 0 && (size_t)rows * d * sizeof(float) <= pi->buf_bytes &&
-                       pi->world == cf.tp_size;
+  const bool oneshot = pi != nullptr && pi->buf_bytes > 0 && d % 4 == 0 && rows <= 64 &&
+                       (size_t)rows * d * dtype_size(dt) <= pi->buf_bytes && pi->world == cf.tp_size;
+  const bool tp_bf16_slab = cf.tp_size > 1 && !oneshot && dt == REWB200_BF16 && d % 4 == 0 && rows > 64;  // smaller steps keep split-K slabs
   auto tp_reduce = [&](int l, int which, int& ks, NormArgs& a) -> int {
     if (cf.tp_size <= 1) return REWB200_OK;
     if (oneshot) {
-      RB_TRY(slab_sum_to_launch(c, s->part, ks, rows * d, pi->bufs[which][pi->rank]));
       a.n_peers = pi->world;
       a.my_rank = pi->rank;
+      a.payload_bf16 = dt == REWB200_BF16 ? 1 : 0;
+      a.slot_elems = (int64_t)(pi->buf_bytes / dtype_size(dt));
       for (int r = 0; r < pi->world; ++r) {
-        a.peer_part[r] = pi->bufs[which][r];
+        a.peer_buf[r] = pi->bufs[which][r];
         a.peer_flags[r] = pi->flags[r];
       }
       a.epoch = pi->epoch;
       a.barrier_offset = 2 * l + which + 1;
-      a.partial = nullptr;
       return REWB200_OK;
     }
-    RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
-    RB_TRY(comm_allreduce_sum_f32(c, m->slot, s->part, rows * d));
+    if (tp_bf16_slab) {
+      RB_TRY(comm_allreduce_sum(c, m->slot, s->part, rows * d, REWB200_BF16));
+      a.partial_bf16 = 1;
+    } else {
+      RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
+      RB_TRY(comm_allreduce_sum(c, m->slot, s->part, rows * d, REWB200_F32));
+    }
     ks = 1;
     a.nsplit = 1;
     return REWB200_OK;
   };
+  // o-proj / down-proj: f32 split-K slabs for the consumer kernel, or one bf16 slab ahead of a bf16 NCCL sum
+  auto run_row_parallel = [&](const LinW& w, const void* x, int64_t ldx, int* ks) -> int {
+    if (!tp_bf16_slab || (w.quant && rows <= 32)) return run_linear(s, w, x, ldx, rows, true, 0, s->part, d, ks);
+    *ks = 1;
+    if (w.quant) RB_TRY(nf4_dequant_launch(c, w.nf4, (bf16*)w.w, w.N, w.cm));
+    return linear_bf16_launch(c, w.plan, (const bf16*)x, ldx, rows, EPI_BIAS_BF16, 1, s->part, d, nullptr, nullptr, 0);
+  };
+  int moe_seen = 0;  // MoE layers so far: numbers the flags of the peer-heap all-to-all
   for (int l = 0; l < cf.n_layers; ++l) {
     LayerDev& L = m->layers[l];
     int ks = 1;
@@ -806,7 +894,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     }
     RB_TRY(attn_launch(c, aa));
 
-    RB_TRY(run_linear(s, L.o, s->attn, m->nq, rows, true, 0, s->part, d, &ks));
+    RB_TRY(run_row_parallel(L.o, s->attn, m->nq, &ks));
     {
       NormArgs a = na;
       a.partial = s->part;
@@ -839,7 +927,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       c->stream = main_stream;
       RB_TRY(st);
       RB_CUDA(cudaEventRecord(c->ev_join, c->side));
-      RB_TRY(moe_routed(s, L, rows, false, base + (size_t)ks * rows * d));
+      RB_TRY(moe_routed(s, L, rows, false, base + (size_t)ks * rows * d, moe_seen++));
       RB_CUDA(cudaStreamWaitEvent(c->stream, c->ev_join, 0));
       NormArgs a = na;
       a.partial = base;
@@ -865,10 +953,10 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
         RB_CUDA(cudaGetLastError());
         ++g_launch_total;
       }
-      RB_TRY(run_linear(s, L.down, s->h, L.ffn_local, rows, true, 0, s->part, d, &ks));
+      RB_TRY(run_row_parallel(L.down, s->h, L.ffn_local, &ks));
     }
     if (L.moe) {
-      RB_TRY(moe_routed(s, L, rows, ks > 0));
+      RB_TRY(moe_routed(s, L, rows, ks > 0, nullptr, moe_seen++));
       if (ks == 0) ks = 1;
     }
     {
@@ -885,6 +973,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     }
   }
   if (oneshot) RB_TRY(epoch_bump_launch(c, pi->epoch, 2 * cf.n_layers));  // same on every rank
+  if (moe_seen > 0 && ep_uses_peer_heap(m, rows)) RB_TRY(epoch_bump_launch(c, comm_peer_info(m->slot)->epoch + 1, moe_seen));
   // lm_head: last position of every sequence (generate.nim:172-190) or every row.
   const int64_t lrows = o.all_logits ? rows : nb;
   const char* xl = (const char*)s->xn + (o.all_logits ? 0 : (size_t)(o.S - 1) * d * dtype_size(dt));
@@ -1260,6 +1349,8 @@ int rewb200_model_finalize(rewb200_model* m) {
   return REWB200_OK;
 }
 
+static int session_fill(rewb200_session* s, int batch, int max_len, int num_blocks);
+
 static int session_create_impl(rewb200_model* m, int batch, int max_len, int num_blocks, rewb200_session** out) {
   RB_REQUIRE(m && out, "rewb200_session_create: NULL argument");
   RB_REQUIRE(m->finalized, "rewb200_session_create: call rewb200_model_finalize first");
@@ -1270,6 +1361,21 @@ static int session_create_impl(rewb200_model* m, int batch, int max_len, int num
   RB_CUDA(cudaSetDevice(c->device));
   rewb200_session* s = new rewb200_session();
   s->m = m;
+  const int st = session_fill(s, batch, max_len, num_blocks);
+  if (st != REWB200_OK) {
+    const std::string why = rewb200_last_error();  // freeing must not replace the message of the failure
+    rewb200_session_free(s);
+    set_error(why);
+    return st;
+  }
+  *out = s;
+  return REWB200_OK;
+}
+
+// Allocates everything a new session owns; on an error the caller frees what has been allocated so far.
+static int session_fill(rewb200_session* s, int batch, int max_len, int num_blocks) {
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
   s->B = batch;
   s->max_len = max_len;
   s->max_pages = (max_len + PAGE - 1) / PAGE;
@@ -1331,7 +1437,6 @@ static int session_create_impl(rewb200_model* m, int batch, int max_len, int num
   RB_CUDA(cudaEventCreate(&s->ev0));
   RB_CUDA(cudaEventCreate(&s->ev1));
   RB_CUDA(cudaStreamSynchronize(c->stream));
-  *out = s;
   return REWB200_OK;
 }
 

@@ -272,6 +272,14 @@ int linear_bf16_plan(LinearBf16Plan* plan, const bf16* W, int64_t K, int64_t N, 
 
 // Enough CTAs to keep two resident per SM, but never K slices shorter than 8
 // k-blocks (512 rows): shorter slices spend their time filling the pipeline.
+// As linear_tc_preload, for the mma.sync kernel of steps of up to 32 rows (option linear=mma).
+int linear_bf16_preload() {
+  RB_CUDA(cudaFuncSetAttribute(linear_bf16_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<32>::SMEM));
+  cudaFuncAttributes fa;
+  RB_CUDA(cudaFuncGetAttributes(&fa, linear_bf16_kernel<32>));
+  return REWB200_OK;
+}
+
 int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N) {
   if (M > 256 || M > c->splitk_max_rows) return 1;  // up to here one token tile covers the step: the weights are streamed once either way
   const int tiles = (int)((N + BN - 1) / BN);

@@ -715,6 +715,15 @@ int linear_tc_cluster_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, 
   return REWB200_OK;
 }
 
+// Loads this file's module on the current device and prepares the decode-size kernel (M <= 32), so that a
+// later launch of it neither loads code nor changes function attributes.
+int linear_tc_preload() {
+  RB_CUDA(cudaFuncSetAttribute(linear_tc_kernel<32, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<32>::SMEM));
+  cudaFuncAttributes fa;
+  RB_CUDA(cudaFuncGetAttributes(&fa, linear_tc_kernel<32, 0>));
+  return REWB200_OK;
+}
+
 // Same contract as linear_bf16_launch (ungrouped).
 int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, int ksplit,
                      void* out, int64_t ldo, const float* bias) {

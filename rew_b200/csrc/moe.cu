@@ -266,6 +266,142 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
   }
 }
 
+// ---- the same steps with the all-to-all done by peer stores (A2aArgs) ------------------------------
+// Slot numbering is unchanged: slot = owner_rank * capacity + index on the asking side,
+// source_rank * capacity + index on the owning side.
+
+// Last CTA of a grid to arrive (every CTA calls this once, after its peer stores): returns true in all
+// threads of that CTA.  The fence before the arrival makes the CTA's stores visible system-wide first.
+__device__ __forceinline__ bool a2a_last_cta(int* arrive) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int t = atomicAdd(arrive, 1);
+    s_last = (t == (int)gridDim.x - 1) ? 1 : 0;
+    if (s_last) {
+      __threadfence_system();
+      *arrive = 0;
+    }
+  }
+  __syncthreads();
+  return s_last != 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_dispatch_peer_kernel(const T* __restrict__ x, const int* __restrict__ topi, int k,
+                                                                int64_t d, int experts_per_rank, int capacity, int* cursor,
+                                                                int* pair_slot, A2aArgs a) {
+  __shared__ int s_p, s_idx;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  if (threadIdx.x == 0) {
+    const int e = topi[pair];
+    const int p = e / experts_per_rank;
+    const int idx = atomicAdd(&cursor[p], 1);
+    reinterpret_cast<int*>(a.region[p] + a.off_meta)[(int64_t)a.my_rank * capacity + idx] = e % experts_per_rank;
+    pair_slot[pair] = p * capacity + idx;
+    s_p = p;
+    s_idx = idx;
+  }
+  __syncthreads();
+  const int tok = pair / k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)tok * d);
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.region[s_p] + a.off_x) + ((int64_t)a.my_rank * capacity + s_idx) * d);
+  const int n16 = (int)(d * sizeof(T) / 16);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+  if (a2a_last_cta(a.arrive)) {
+    // every pair of this rank has been stored: hand each owner its pair count, then the flag
+    if ((int)threadIdx.x < a.world) {
+      const int p = threadIdx.x;
+      const int n = atomicAdd(&cursor[p], 0);
+      *reinterpret_cast<volatile int*>(a.cells[p] + a.my_rank) = n;
+      peer_flag_release(a.cells[p] + 8 + a.my_rank, *a.epoch + a.offset);
+    }
+  }
+}
+
+// count[e] = pairs for local expert e among the occupied slots; waits for every rank's dispatch flag first.
+__global__ void __launch_bounds__(256) moe_count_peer_kernel(int n_slots, int capacity, int* count, A2aArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  peer_flags_wait(a.cells[a.my_rank] + 8, 1, a.world, -1, *a.epoch + a.offset, a.status);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_slots) return;
+  const int src = i / capacity, idx = i % capacity;
+  if (idx >= __ldcg(a.cells[a.my_rank] + src)) return;
+  const int e = __ldcg(reinterpret_cast<const int*>(a.region[a.my_rank] + a.off_meta) + i);
+  atomicAdd(&count[e], 1);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gather_peer_kernel(int64_t d, int capacity, int* cursor2, T* xs, int* slot_pos,
+                                                              A2aArgs a) {
+  __shared__ int s_pos;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x;
+  const int src = slot / capacity, idx = slot % capacity;
+  if (idx >= __ldcg(a.cells[a.my_rank] + src)) {
+    if (threadIdx.x == 0) slot_pos[slot] = -1;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    const int e = __ldcg(reinterpret_cast<const int*>(a.region[a.my_rank] + a.off_meta) + slot);
+    s_pos = atomicAdd(&cursor2[e], 1);
+    slot_pos[slot] = s_pos;
+  }
+  __syncthreads();
+  const uint4* src_row = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.region[a.my_rank] + a.off_x) + (int64_t)slot * d);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (int64_t)s_pos * d);
+  const int n16 = (int)(d * sizeof(T) / 16);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src_row + i);
+}
+
+// Expert outputs back to the rank that asked, in its slot order; the last CTA raises the return flags.
+__global__ void __launch_bounds__(128) moe_return_peer_kernel(const float* __restrict__ ys, const int* __restrict__ slot_pos,
+                                                              int64_t d, int capacity, A2aArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int slot = blockIdx.x;
+  const int pos = slot_pos[slot];
+  if (pos >= 0) {
+    const int src = slot / capacity, idx = slot % capacity;
+    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.region[src] + a.off_back) + ((int64_t)a.my_rank * capacity + idx) * d);
+    const float4* from = reinterpret_cast<const float4*>(ys + (int64_t)pos * d);
+    const int n4 = (int)(d / 4);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = from[i];
+  }
+  if (a2a_last_cta(a.arrive + 1)) {
+    if ((int)threadIdx.x < a.world) peer_flag_release(a.cells[threadIdx.x] + 16 + a.my_rank, *a.epoch + a.offset);
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_combine_peer_kernel(const int* __restrict__ pair_slot, const float* __restrict__ topw,
+                                                               int k, int64_t d, float* out, int accumulate, A2aArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  peer_flags_wait(a.cells[a.my_rank] + 16, 1, a.world, -1, *a.epoch + a.offset, a.status);
+  const float* back = reinterpret_cast<const float*>(a.region[a.my_rank] + a.off_back);
+  const int tok = blockIdx.x;
+  const int n4 = (int)(d / 4);
+  for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+      const float w = topw[tok * k + j];
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(back + (int64_t)pair_slot[tok * k + j] * d) + i);
+      acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    }
+    float4* o = reinterpret_cast<float4*>(out + (int64_t)tok * d) + i;
+    if (accumulate) {
+      const float4 p = *o;
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    *o = acc;
+  }
+}
+
 }  // namespace
 
 #define RB_LAUNCH(kernel, grid, block, ...)                                                   \
@@ -311,6 +447,39 @@ int moe_combine_launch(Ctx* c, const float* back, const int* pair_slot, const fl
                        float* out, int accumulate) {
   if (tokens == 0) return REWB200_OK;
   RB_LAUNCH(moe_combine_kernel, tokens, 256, back, pair_slot, topw, k, d, out, accumulate);
+  return REWB200_OK;
+}
+
+// Peer-heap variants (bf16 or f32 activations).  `cursor` (world ints) and `count` (n_experts + 1 ints) must be zero.
+int moe_dispatch_peer_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d,
+                             int experts_per_rank, int capacity, int* cursor, int* pair_slot, const A2aArgs& a) {
+  RB_REQUIRE(tokens > 0, "expert-parallel dispatch needs at least one token on every rank");
+  RB_REQUIRE((d * dtype_size(dtype)) % 16 == 0, "MoE dispatch needs rows that are multiples of 16 bytes");
+  if (dtype == REWB200_BF16)
+    RB_LAUNCH(moe_dispatch_peer_kernel<bf16>, tokens * k, 128, (const bf16*)x, topi, k, d, experts_per_rank, capacity, cursor,
+              pair_slot, a);
+  else
+    RB_LAUNCH(moe_dispatch_peer_kernel<float>, tokens * k, 128, (const float*)x, topi, k, d, experts_per_rank, capacity, cursor,
+              pair_slot, a);
+  return REWB200_OK;
+}
+int moe_group_peer_launch(Ctx* c, int dtype, int n_slots, int capacity, int64_t d, int n_experts, int* count, int* offsets,
+                          int* cursor2, void* xs, int* slot_pos, const A2aArgs& a) {
+  RB_LAUNCH(moe_count_peer_kernel, (n_slots + 255) / 256, 256, n_slots, capacity, count, a);
+  RB_LAUNCH(moe_scan_kernel, 1, 32, (const int*)count, n_experts, offsets, cursor2);
+  if (dtype == REWB200_BF16)
+    RB_LAUNCH(moe_gather_peer_kernel<bf16>, n_slots, 128, d, capacity, cursor2, (bf16*)xs, slot_pos, a);
+  else
+    RB_LAUNCH(moe_gather_peer_kernel<float>, n_slots, 128, d, capacity, cursor2, (float*)xs, slot_pos, a);
+  return REWB200_OK;
+}
+int moe_return_peer_launch(Ctx* c, const float* ys, const int* slot_pos, int n_slots, int capacity, int64_t d, const A2aArgs& a) {
+  RB_LAUNCH(moe_return_peer_kernel, n_slots, 128, ys, slot_pos, d, capacity, a);
+  return REWB200_OK;
+}
+int moe_combine_peer_launch(Ctx* c, const int* pair_slot, const float* topw, int64_t tokens, int k, int64_t d, float* out,
+                            int accumulate, const A2aArgs& a) {
+  RB_LAUNCH(moe_combine_peer_kernel, tokens, 256, pair_slot, topw, k, d, out, accumulate, a);
   return REWB200_OK;
 }
 

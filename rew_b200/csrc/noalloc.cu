@@ -1,5 +1,8 @@
-// rewb200_linear_noalloc: the decode-size bf16 Linear (split-K weight streamer
-// of linear_bf16.cu) for callers that cannot allocate device memory.
+// rewb200_linear_noalloc: the decode-size bf16 Linear for callers that cannot
+// allocate device memory.  The GEMM is the kernel the slot's "linear" option
+// selects for rewb200_linear too: the tcgen05 weight streamer of linear_tc.cu by
+// default, the mma.sync one of linear_bf16.cu under linear=mma; both leave f32
+// split-K slabs that a small kernel here sums.
 //
 // Who that is: a host runtime that has handed the whole device heap to its own
 // allocator (for example a serving process that reserves all free HBM for KV
@@ -26,8 +29,9 @@ namespace {
 constexpr size_t kNoAllocScratchBytes = 8u << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
-// Host-side cache of the array's device address, per device ordinal.  The
-// symbol's name is only a host stand-in; kernels must be given this address.
+// Host-side cache of the array's device address, per device ordinal, filled by
+// noalloc_setup under rewb200_init's lock.  The symbol's name is only a host
+// stand-in; kernels must be given this address.
 float* g_scratch_addr[64] = {nullptr};
 
 __global__ void __launch_bounds__(256) sum_partials_kernel(const float* __restrict__ part, int nsplit, int64_t slab,
@@ -42,28 +46,43 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float* __restri
 }
 
 int scratch_address(Ctx* c, float** out) {
-  RB_REQUIRE(c->device >= 0 && c->device < 64, "device ordinal out of range");
-  if (!g_scratch_addr[c->device]) {
-    void* p = nullptr;
-    RB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
-    RB_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null address for the scratch array");
-    g_scratch_addr[c->device] = (float*)p;
-  }
+  RB_REQUIRE(c->device >= 0 && c->device < 64 && g_scratch_addr[c->device] != nullptr,
+             "rewb200_linear_noalloc: the scratch array was not resolved for this device (rewb200_init does that)");
   *out = g_scratch_addr[c->device];
   return REWB200_OK;
 }
 
 }  // namespace
+
+int linear_tc_preload();
+int linear_bf16_preload();
+
+// Called by rewb200_init for every device it opens, with that device current.  CUDA loads modules
+// lazily: the first cudaGetSymbolAddress of the array and the first launch of a kernel load the module
+// that holds them, and loading the module with the 8 MiB array allocates device memory inside the driver.
+// All of that happens here, so that no call of rewb200_linear_noalloc loads code or reserves memory.
+int noalloc_setup(Ctx* c) {
+  RB_REQUIRE(c->device >= 0 && c->device < 64, "device ordinal out of range");
+  void* p = nullptr;
+  RB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+  RB_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null address for the scratch array");
+  g_scratch_addr[c->device] = (float*)p;
+  cudaFuncAttributes fa;
+  RB_CUDA(cudaFuncGetAttributes(&fa, sum_partials_kernel));
+  RB_TRY(linear_tc_preload());
+  RB_TRY(linear_bf16_preload());
+  return REWB200_OK;
+}
+
 }  // namespace rewb
 
 using namespace rewb;
 
 // y[M,N] (bf16) = x[M,K] (bf16) @ w[K,N] (bf16) + bias[N] (f32, may be NULL).
 // All pointers are device pointers the caller owns; M <= 32.
-// The first call on a device looks up the scratch array's address
-// (cudaGetSymbolAddress, with that device current); make that first call
-// outside any stream capture.  No cudaMalloc, cudaFree, pool or library
-// allocation happens in any call.
+// rewb200_init has resolved the scratch array's address (cudaGetSymbolAddress,
+// with the device current) and loaded the kernels used here, so no call loads a
+// module; no cudaMalloc, cudaFree, pool or library allocation happens in any call.
 extern "C" int rewb200_linear_noalloc(int slot, const void* x, const void* w, const float* bias, void* y, int64_t M,
                                       int64_t K, int64_t N) {
   Ctx* c = ctx_get(slot);

@@ -126,6 +126,41 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// ---- flags between the ranks of a node (peer heap) ------------------------------------------------
+// Writer: every thread of the CTA has issued its stores into the peer's memory; after the CTA barrier
+// the flag store (release, system scope) orders them before the flag.  Reader: polls a cell of its OWN
+// memory with acquire loads.  Flag values only grow; `v - target >= 0` also accepts a later round.
+__device__ __forceinline__ void peer_flag_release(int* cell, int value) {
+  __threadfence_system();
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(cell), "r"(value) : "memory");
+}
+__device__ __forceinline__ int peer_flag_acquire(const int* cell) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(cell) : "memory");
+  return v;
+}
+// Threads 0..n-1 (except `skip`) each wait for one cell; bounded by 2 s, and cut short once any wait on
+// this GPU has already timed out, so a lost peer costs one timeout per step and never a hang.  Ends with a
+// CTA barrier: afterwards every thread may read what the peers stored before raising their flags.
+__device__ __forceinline__ void peer_flags_wait(const int* cells, int stride, int n, int skip, int target, int* status) {
+  if ((int)threadIdx.x < n && (int)threadIdx.x != skip) {
+    const int* cell = cells + (int64_t)threadIdx.x * stride;
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+      if (peer_flag_acquire(cell) - target >= 0) break;
+      if ((it & 63u) == 63u) {
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > 2000000000ull || *reinterpret_cast<volatile int*>(status) == KS_PEER_TIMEOUT) {
+          atomicExch(status, KS_PEER_TIMEOUT);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)

@@ -113,6 +113,8 @@ int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return REWB200_OK;
 }
 
+int noalloc_setup(Ctx* c);  // noalloc.cu
+
 int buffer_new(Ctx* c, int dtype, const int64_t* dims, int ndims, rewb200_buffer** out) {
   RB_REQUIRE(ndims >= 0 && ndims <= 8, "buffer rank must be 0..8");
   const size_t es = dtype_size(dtype);
@@ -192,6 +194,7 @@ int rewb200_init(const int* device_ordinals, int n) {
     c->use_pdl = !(pdl && pdl[0] == '0');
     const char* li = getenv("REW_B200_LINEAR");
     if (li) c->linear_impl = !strcmp(li, "mma") ? 0 : (!strcmp(li, "tc_prefill") ? 1 : 2);
+    RB_TRY(noalloc_setup(c));  // resolves rewb200_linear_noalloc's scratch array and loads its kernels on this device
     g_ctx.push_back(c);
   }
   RB_CUDA(cudaSetDevice(g_ctx[0]->device));
@@ -267,6 +270,10 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "ep_exchange") {
     RB_REQUIRE(v == "prefix" || v == "capacity" || v == "auto", "option ep_exchange: expected auto, prefix or capacity");
     c->ep_prefix = v == "prefix" ? 1 : (v == "capacity" ? 0 : 2);
+  } else if (k == "inject_alloc_fail") {
+    const int n = atoi(v.c_str());
+    RB_REQUIRE(n >= 0, "option inject_alloc_fail: a non-negative count");
+    c->inject_alloc_fail = n;
   } else if (k == "moe_overlap") {
     RB_REQUIRE(v == "on" || v == "off", "option moe_overlap: expected on or off");
     c->moe_overlap = v == "on";

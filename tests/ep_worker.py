@@ -50,19 +50,41 @@ def main():
             time.sleep(0.05)
         uid = open(idfile, "rb").read()
     api.comm_init(uid, rank, world)
+    # peer heap with an all-to-all region: the default exchange (stores into the owner's memory, counts and
+    # flags on the device); handles travel through files like the communicator id
+    mine = api.comm_peer_alloc(0, 4 << 20)
+    with open("%s.h%d.tmp" % (idfile, rank), "wb") as f:
+        f.write(mine)
+    os.replace("%s.h%d.tmp" % (idfile, rank), "%s.h%d" % (idfile, rank))
+    handles = []
+    for r in range(world):
+        t0 = time.time()
+        while not os.path.exists("%s.h%d" % (idfile, r)):
+            if time.time() - t0 > 60:
+                raise RuntimeError("rank %d never published its heap handle" % r)
+            time.sleep(0.05)
+        handles.append(open("%s.h%d" % (idfile, r), "rb").read())
+    api.comm_peer_attach(handles)
     cfg = config(rank, world)
     prompt = prompt_of(rank)
     # every rank feeds the same number of tokens per step: the all-to-all slot arrays have one fixed capacity
     sess = api.CausalLM(cfg).load(weights(cfg)).session(prompt.shape[0], 64)
-    # the prompt goes through the count-then-prefix exchange (ranks receive 38 and 76 pairs), the captured decode
-    # steps through the fixed-capacity one; the same prompt again with fixed capacity must give the same logits
+    # The same prompt through the three exchanges must give the same bits: NCCL count-then-prefix (ranks
+    # receive 38 and 76 pairs), NCCL fixed capacity, and the peer heap (auto, the default); then the captured
+    # decode steps over the peer heap and over NCCL fixed capacity.
     api.set_option("ep_exchange", "prefix")
     nxt, logits = sess.forward(prompt, want_logits=True)
     api.set_option("ep_exchange", "capacity")
     sess.reset()
     nxt2, logits2 = sess.forward(prompt, want_logits=True)
     assert np.array_equal(nxt, nxt2) and np.array_equal(logits, logits2), "prefix and capacity exchange disagree"
+    ids2, last2 = sess.decode(4, want_logits=True)
+    api.set_option("ep_exchange", "auto")
+    sess.reset()
+    nxt3, logits3 = sess.forward(prompt, want_logits=True)
+    assert np.array_equal(nxt, nxt3) and np.array_equal(logits, logits3), "peer-heap and NCCL exchange disagree (prefill)"
     ids, last = sess.decode(4, want_logits=True)
+    assert np.array_equal(ids, ids2) and np.array_equal(last, last2), "peer-heap and NCCL exchange disagree (decode)"
     print("rank", rank, "done", flush=True)
     np.savez(outfile, nxt=nxt, logits=logits, ids=ids, last=last)
     sess.free()

@@ -48,3 +48,13 @@ def test_product_arm_fails_loudly_without_a_gpu():
     r = _run("--workload", "tiny", "--steps", "1", "--warmup", "1", "--no-cpu-baseline")
     assert r.returncode != 0
     assert not [l for l in r.stdout.splitlines() if l.startswith("{")]
+
+
+def test_reference_arm_ignores_an_inherited_single_thread_setting():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 for every rank; the CPU arm sets its own thread count."""
+    r = _run("--impl", "reference", "--workload", "tiny", "--steps", "1", "--warmup", "1", env={"OMP_NUM_THREADS": "1"})
+    assert r.returncode == 0, r.stderr[-2000:]
+    j = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][0])
+    assert j["cpu_baseline"]["cores"] == (os.cpu_count() or 1)
+    # same config keys as the product arm prints for this workload
+    assert set(j["config"]) == {"workload", "batch_per_gpu", "prompt", "decode_steps", "parallelism", "sampling", "mask", "norm", "l2"}

@@ -35,8 +35,9 @@ def _bundled_nccl():
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("mode", ["nccl", "fused"])
 def test_tp2_generate_matches_oracle(orc, mode):
-    """mode nccl: every all-reduce through NCCL; fused: decode-size steps use the one-shot all-reduce
-    over peer memory inside the residual+norm kernel (prefill rows here are small enough to use it too)."""
+    """mode nccl: every all-reduce through NCCL; fused: steps of up to 64 rows use the push all-reduce over
+    the peer heap inside the residual+norm kernel (a 60-row prefill too; a 120-row prefill goes through NCCL,
+    with a bf16 payload on the bf16 model)."""
     from rew_b200 import _lib
     with tempfile.TemporaryDirectory() as d:
         idfile = os.path.join(d, "nccl_id")
@@ -64,22 +65,24 @@ def test_tp2_generate_matches_oracle(orc, mode):
             f.close()
         assert codes == [0, 0], "rank exit codes %r\n--- rank 0 ---\n%s\n--- rank 1 ---\n%s" % (codes, tails[0], tails[1])
         outs = [np.load(os.path.join(d, "out%d.npz" % r)) for r in range(2)]
-    prompt = np.random.default_rng(3).integers(0, 512, size=(3, 20)).astype(np.int32)
     for name, dtype, hd, nh, kvh in (("f32", _lib.F32, 32, 8, 2), ("bf16", _lib.BF16, 64, 4, 2)):
         cfg = W.ModelConfig(vocab=512, d_model=256, n_layers=2, n_heads=nh, n_kv_heads=kvh, head_dim=hd, ffn=688, max_seq=128,
                             theta=500000.0, dtype=dtype, mask_kind=1, norm_kind=0)
         t = W.init_weights(cfg, seed=9, std=0.05, trivial_affine=False)
         if dtype == _lib.BF16:
             t = [W.bf16_round(a) if a.ndim == 2 else a for a in t]
-        # both ranks agree bit for bit
-        assert np.array_equal(outs[0][name + "_ids"], outs[1][name + "_ids"])
-        assert np.array_equal(outs[0][name + "_logits"], outs[1][name + "_logits"])
-        if name == "f32":
-            want_ids, want_logits = orc.generate_greedy(cfg, t, prompt, 6)
-            assert np.array_equal(outs[0]["f32_ids"], want_ids)
-            assert rel_l2(outs[0]["f32_logits"], want_logits) <= 1e-5
-        else:
-            ids = outs[0]["bf16_ids"]
-            seq = np.concatenate([prompt, ids[:, :5]], 1)
-            want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
-            assert rel_l2(outs[0]["bf16_logits"], want) <= 2e-2
+        for tag, plen in (("", 20), ("_long", 40)):
+            prompt = np.random.default_rng(3).integers(0, 512, size=(3, plen)).astype(np.int32)
+            key = name + tag
+            # both ranks agree bit for bit
+            assert np.array_equal(outs[0][key + "_ids"], outs[1][key + "_ids"])
+            assert np.array_equal(outs[0][key + "_logits"], outs[1][key + "_logits"])
+            if name == "f32":
+                want_ids, want_logits = orc.generate_greedy(cfg, t, prompt, 6)
+                assert np.array_equal(outs[0][key + "_ids"], want_ids)
+                assert rel_l2(outs[0][key + "_logits"], want_logits) <= 1e-5
+            else:
+                ids = outs[0][key + "_ids"]
+                seq = np.concatenate([prompt, ids[:, :5]], 1)
+                want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
+                assert rel_l2(outs[0][key + "_logits"], want) <= 2e-2

@@ -19,25 +19,42 @@ pytestmark = pytest.mark.gpu
 
 
 def _case(api, lib, seed, M, K, N, with_bias):
+    from oracle import orc
     from rew_b200 import _lib
     rng = np.random.default_rng(seed)
-    x = api.Tensor.from_host(rng.normal(size=(M, K)).astype(np.float32), _lib.BF16)
-    w = api.Tensor.from_host(rng.normal(0, 0.05, size=(K, N)).astype(np.float32), _lib.BF16)
-    b = api.Tensor.from_host(rng.normal(0, 0.1, size=(N,)).astype(np.float32)) if with_bias else None
+    xh = orc.bf16_round(rng.normal(size=(M, K)).astype(np.float32))
+    wh = orc.bf16_round(rng.normal(0, 0.05, size=(K, N)).astype(np.float32))
+    bh = rng.normal(0, 0.1, size=(N,)).astype(np.float32) if with_bias else None
+    x = api.Tensor.from_host(xh, _lib.BF16)
+    w = api.Tensor.from_host(wh, _lib.BF16)
+    b = api.Tensor.from_host(bh) if with_bias else None
     want = api.Linear(w, b).forward(x).to_host()
+    # and the CPU restatement of Linear.forward on the same bf16-rounded operands
+    want_orc = orc.linear(xh, wh, bh if with_bias else np.zeros(N, np.float32))
     y = api.Tensor.from_host(np.full((M, N), 7.0, np.float32), _lib.BF16)  # caller-owned output, pre-filled
     ptr = lambda t: C.c_void_p(lib.rewb200_buffer_device_ptr(t._h)) if t is not None else None
     _lib.check(lib.rewb200_linear_noalloc(0, ptr(x), ptr(w), ptr(b), ptr(y), M, K, N))
     got = y.to_host()
     assert np.isfinite(got).all()
     assert rel_l2(got, want) < 5e-3  # the tolerance of the bf16 Linear tests
+    assert rel_l2(got, want_orc) < 5e-3
     return got
 
 
-def test_noalloc_linear_matches_allocating_linear_twice_in_a_row():
+@pytest.mark.parametrize("linear", ["tc", "mma"])
+def test_noalloc_linear_matches_allocating_linear_twice_in_a_row(linear):
+    """Either GEMM that can stand behind the entry point writes its split-K slabs into the shared array."""
     from rew_b200 import _lib, api
     _lib.init()
     lib = _lib.lib()
+    api.set_option("linear", linear)
+    try:
+        _twice(api, lib)
+    finally:
+        api.set_option("linear", "tc")
+
+
+def _twice(api, lib):
     first = _case(api, lib, 1, 32, 4096, 1024, True)     # split-K > 1: several slabs of the shared array
     second = _case(api, lib, 2, 5, 1024, 4096, False)    # other shape, other data, stale slabs behind it
     again = _case(api, lib, 1, 32, 4096, 1024, True)     # and the first case once more

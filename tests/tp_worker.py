@@ -30,7 +30,7 @@ def main():
     print("rank", rank, "communicator ready", flush=True)
     fused = len(sys.argv) > 5 and sys.argv[5] == "fused"
     if fused:  # exchange the IPC handles of the all-reduce heaps through files
-        mine = api.comm_peer_alloc(1 << 20)
+        mine = api.comm_peer_alloc(1 << 20, 0)
         with open("%s.h%d.tmp" % (idfile, rank), "wb") as f:
             f.write(mine)
         os.replace("%s.h%d.tmp" % (idfile, rank), "%s.h%d" % (idfile, rank))
@@ -52,13 +52,17 @@ def main():
         t = W.init_weights(full, seed=9, std=0.05, trivial_affine=False)
         if dtype == _lib.BF16:
             t = [W.bf16_round(a) if a.ndim == 2 else a for a in t]
-        prompt = np.random.default_rng(3).integers(0, cfg.vocab, size=(3, 20)).astype(np.int32)
-        sess = api.CausalLM(cfg).load(t).session(3, 64)
-        ids, logits = sess.generate(prompt, 6, want_logits=True)
-        print("rank", rank, name, "done", flush=True)
-        results[name + "_ids"] = ids
-        results[name + "_logits"] = logits
-        sess.free()  # the captured decode graph holds the communicator; release it before comm_destroy
+        model = api.CausalLM(cfg).load(t)
+        # 60 prompt rows: every all-reduce of the step is the fused one; 120 rows: the prefill goes through NCCL
+        # (bf16 payload for the bf16 model) and only the decode steps are fused
+        for tag, plen in (("", 20), ("_long", 40)):
+            prompt = np.random.default_rng(3).integers(0, cfg.vocab, size=(3, plen)).astype(np.int32)
+            sess = model.session(3, 64)
+            ids, logits = sess.generate(prompt, 6, want_logits=True)
+            print("rank", rank, name + tag, "done", flush=True)
+            results[name + tag + "_ids"] = ids
+            results[name + tag + "_logits"] = logits
+            sess.free()  # the captured decode graph holds the communicator; release it before comm_destroy
     np.savez(outfile, **results)
     api.comm_destroy()
 
