@@ -158,6 +158,59 @@ int rewb200_embed_gather(const rewb200_buffer* ids, const rewb200_buffer* table,
 int rewb200_moe_route(const rewb200_buffer* x, const rewb200_buffer* router_w, const rewb200_buffer* router_b,
                       int top_k, rewb200_buffer** weights, rewb200_buffer** indices);
 
+/* ---- stateful layer pieces ---------------------------------------------------
+ * For a backend-aware GroupedQueryAttention.forward / DeepSeekMoE.forward / generate loop written against
+ * single layers instead of the whole-model engine below. */
+typedef struct rewb200_kv rewb200_kv;
+typedef struct rewb200_experts rewb200_experts;
+typedef struct rewb200_sampler rewb200_sampler;
+/* KvCache (src/rew/nn/kv_cache.nim:13-24): K and V of one attention layer, [batch, kv_heads, max_len,
+ * head_dim], f32 or bf16, with one length for all sequences.  `append` (kv_cache.nim:47-77) is done by
+ * rewb200_qkv_rope_kvappend in place instead of by concatenation. */
+int rewb200_kv_create(int slot, int dtype, int batch, int kv_heads, int head_dim, int max_len, rewb200_kv** out);
+void rewb200_kv_free(rewb200_kv* kv);
+int rewb200_kv_length(const rewb200_kv* kv);   /* KvCache.length; -1 for NULL */
+int rewb200_kv_reset(rewb200_kv* kv);
+/* First half of GroupedQueryAttention.forward with a cache (src/rew/nn/groupedqueryattention.nim:94-122):
+ * q / k / v Linear of x [batch, S, embedDim], RoPE of q and k at offset = cache length (tables from
+ * rewb200_rope_tables), K and V appended to the cache.  q_out [batch, S, heads*head_dim].  Biases may be NULL. */
+int rewb200_qkv_rope_kvappend(const rewb200_buffer* x, const rewb200_buffer* wq, const rewb200_buffer* bq,
+                              const rewb200_buffer* wk, const rewb200_buffer* bk, const rewb200_buffer* wv,
+                              const rewb200_buffer* bv, const rewb200_buffer* cos_t, const rewb200_buffer* sin_t,
+                              rewb200_kv* kv, rewb200_buffer** q_out);
+/* Second half (groupedqueryattention.nim:126-137 before outProj): the queries of the last append attend over
+ * everything cached so far; q and out are [batch, S, heads*head_dim]; mask_kind as rewb200_gqa_attention. */
+int rewb200_gqa_attention_cached(const rewb200_buffer* q, const rewb200_kv* kv, int causal, int mask_kind,
+                                 rewb200_buffer** out);
+/* The routed experts of a DeepSeekMoE layer (src/rew/models/deepseek.nim:36-52,74-78): n_experts triples of
+ * gate / up [hidden, intermediate] and down [intermediate, hidden] weights (device buffers, all f32 or all
+ * bf16) and optional f32 biases (array or entry NULL = zero), copied once into the fused device layout. */
+int rewb200_experts_create(int slot, int n_experts, const rewb200_buffer* const* gate_w, const rewb200_buffer* const* gate_b,
+                           const rewb200_buffer* const* up_w, const rewb200_buffer* const* up_b,
+                           const rewb200_buffer* const* down_w, const rewb200_buffer* const* down_b, rewb200_experts** out);
+void rewb200_experts_free(rewb200_experts* h);
+/* DeepSeekMoE.forward after the router (deepseek.nim:140-144): y[t] = sum_j weights[t][j] *
+ * expert_{indices[t][j]}(x[t]).  x [tokens, hidden]; weights f32 and indices int32 [tokens, k] as
+ * rewb200_moe_route returns them; y has x's shape and dtype.  bf16: tokens sorted by expert, two grouped
+ * GEMMs (SwiGLU in the first one's epilogue; tcgen05 for groups of more than 64 rows); f32: every expert on
+ * every token, masked, as the reference computes it. */
+int rewb200_moe_experts(const rewb200_experts* h, const rewb200_buffer* x, const rewb200_buffer* weights,
+                        const rewb200_buffer* indices, rewb200_buffer** y);
+/* Sampling state of `batch` sequences (GenerationConfig + Key of generate, src/rew/infer/generate.nim:12-58,
+ * 231-265): per-sequence Threefry key (initKey(seed), folded with the step after every token), step counter
+ * and the tokens seen so far (for repetitionPenalty), all on the device.  max_tokens bounds prompt +
+ * generated tokens per sequence.  seeds: host uint64 [batch] or NULL (key 0). */
+int rewb200_sampler_create(int slot, int batch, int vocab, int max_tokens, float temperature, int top_k, float top_p,
+                           float min_p, float repetition_penalty, int do_sample, const uint64_t* seeds, rewb200_sampler** out);
+void rewb200_sampler_free(rewb200_sampler* s);
+/* Adds n_per_row tokens per sequence (host int32 [batch, n_per_row], e.g. the prompt) to the tokens seen. */
+int rewb200_sampler_observe(rewb200_sampler* s, const int32_t* ids, int n_per_row);
+/* lmHead + lastLogits + applySamplingConfig + sampleGreedy / sampleTopK / sampleTopP (generate.nim:92-190):
+ * x [batch, d] (the last position's hidden state), lm_w [d, vocab], lm_b f32 [vocab] or NULL.  sampler NULL
+ * = greedy argmax, first maximum.  next_ids host int32 [batch]; logits_out host f32 [batch, vocab] or NULL. */
+int rewb200_lmhead_sample(const rewb200_buffer* x, const rewb200_buffer* lm_w, const rewb200_buffer* lm_b,
+                          rewb200_sampler* sampler, int32_t* next_ids, float* logits_out);
+
 /* ---- NF4 weight-only Linear (QLoRA base projection) -------------------------
  * nf4Quantize / nf4Dequantize (src/rew/quantize/codecs.nim:13-70) and
  * QloraLinear (src/rew/nn/lora.nim:173-191,331-431).  The reference dequantises
@@ -247,6 +300,10 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
  * and every sequence has produced it. last_logits optional [batch,vocab]. */
 int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
                      float* last_logits);
+/* The same with GenerationConfig.stopTokenIds (generate.nim:21,263): a sequence ends with the first token
+ * that is in stop_ids (host int32 [n_stop]) or equals eos (ignored when negative); ids after it are -1. */
+int rewb200_generate_stop(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, const int32_t* stop_ids,
+                          int n_stop, int32_t* out_ids, float* last_logits);
 /* ---- paged lanes: continuous batching --------------------------------------
  * PagedKvCache (src/rew/infer/generate.nim:63-88: blockSize, numBlocks,
  * freeBlocks) made operational.  The session owns `num_blocks` KV blocks of 64
@@ -311,6 +368,10 @@ int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int
 int rewb200_comm_unique_id(void* id128);                  /* 128 bytes, created on rank 0 */
 int rewb200_comm_init(int slot, const void* id128, int rank, int world);
 int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n);
+/* allToAll with equal counts (src/rew/ops/distributed.nim:106-128): bytes [p*bytes_per_peer, (p+1)*bytes_per_peer)
+ * of the device send buffer go to rank p, and rank p's block for this rank lands at the same offset of the
+ * device receive buffer.  Waits for completion and reports NCCL's asynchronous errors. */
+int rewb200_comm_alltoall(int slot, const void* send_device, void* recv_device, int64_t bytes_per_peer);
 /* Peer heap: exchange memory that the other ranks of the node write into directly over NVLink (plain peer
  * stores from inside this library's kernels; nothing is read from a peer and no library kernel is handed a
  * peer pointer).  Each rank allocates its heap and exports a 64-byte CUDA IPC handle; after the host has

@@ -100,6 +100,22 @@ SIGNATURES = {
     "rewb200_comm_unique_id": (C.c_int, [P]),
     "rewb200_comm_init": (C.c_int, [C.c_int, P, C.c_int, C.c_int]),
     "rewb200_comm_allreduce_f32": (C.c_int, [C.c_int, P, C.c_int64]),
+    "rewb200_comm_alltoall": (C.c_int, [C.c_int, P, P, C.c_int64]),
+    "rewb200_generate_stop": (C.c_int, [P, I32P, C.c_int, C.c_int, C.c_int, I32P, C.c_int, I32P, F32P]),
+    "rewb200_kv_create": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, PP]),
+    "rewb200_kv_free": (None, [P]),
+    "rewb200_kv_length": (C.c_int, [P]),
+    "rewb200_kv_reset": (C.c_int, [P]),
+    "rewb200_qkv_rope_kvappend": (C.c_int, [P, P, P, P, P, P, P, P, P, P, PP]),
+    "rewb200_gqa_attention_cached": (C.c_int, [P, P, C.c_int, C.c_int, PP]),
+    "rewb200_experts_create": (C.c_int, [C.c_int, C.c_int, P, P, P, P, P, P, PP]),
+    "rewb200_experts_free": (None, [P]),
+    "rewb200_moe_experts": (C.c_int, [P, P, P, P, PP]),
+    "rewb200_sampler_create": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_float,
+                                         C.c_float, C.c_int, C.POINTER(C.c_uint64), PP]),
+    "rewb200_sampler_free": (None, [P]),
+    "rewb200_sampler_observe": (C.c_int, [P, I32P, C.c_int]),
+    "rewb200_lmhead_sample": (C.c_int, [P, P, P, P, I32P, F32P]),
     "rewb200_comm_peer_alloc": (C.c_int, [C.c_int, C.c_int64, C.c_int64, P]),
     "rewb200_comm_peer_attach": (C.c_int, [C.c_int, P]),
     "rewb200_comm_destroy": (C.c_int, [C.c_int]),

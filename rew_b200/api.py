@@ -202,6 +202,137 @@ def moeRoute(x, router, top_k):
     return Tensor(w), Tensor(i)
 
 
+class KvCache:
+    """KvCache (src/rew/nn/kv_cache.nim:13-24): K and V of one attention layer on the device, appended in place."""
+
+    def __init__(self, batch, numKvHeads, headDim, maxLen, dtype=F32, slot=0):
+        _lib.init()
+        h = C.c_void_p()
+        check(lib().rewb200_kv_create(slot, dtype, batch, numKvHeads, headDim, maxLen, C.byref(h)))
+        self._h = h
+
+    @property
+    def length(self):
+        return lib().rewb200_kv_length(self._h)
+
+    def reset(self):
+        check(lib().rewb200_kv_reset(self._h))
+
+    def free(self):
+        if self._h is not None:
+            lib().rewb200_kv_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class GroupedQueryAttention:
+    """GroupedQueryAttention with a cache (src/rew/nn/groupedqueryattention.nim:27-38,94-144): q/k/v Linear,
+    RoPE at the cache length, in-place append, attention over the cache, outProj.  x [batch, S, embedDim]."""
+
+    def __init__(self, qProj, kProj, vProj, outProj, rope, mask_kind=0):
+        self.qProj, self.kProj, self.vProj, self.outProj, self.rope, self.mask_kind = qProj, kProj, vProj, outProj, rope, mask_kind
+
+    def forward(self, x, cache, causal=True):
+        q = _out()
+        check(lib().rewb200_qkv_rope_kvappend(_h(x), _h(self.qProj.weight), _h(self.qProj.bias), _h(self.kProj.weight),
+                                              _h(self.kProj.bias), _h(self.vProj.weight), _h(self.vProj.bias),
+                                              _h(self.rope.cosCached), _h(self.rope.sinCached), cache._h, C.byref(q)))
+        q = Tensor(q)
+        a = _out()
+        check(lib().rewb200_gqa_attention_cached(_h(q), cache._h, int(bool(causal)), self.mask_kind, C.byref(a)))
+        a = Tensor(a)
+        B, S, nq = a.shape
+        flat = reshape(a, (B * S, nq))
+        y = self.outProj.forward(flat)
+        return reshape(y, (B, S, y.shape[1]))
+
+
+def reshape(t, shape):
+    return dispatch("reshape", [t], [("shape", "[" + ",".join(str(int(v)) for v in shape) + "]")])[0]
+
+
+class RoutedExperts:
+    """The routed experts of a DeepSeekMoE layer (src/rew/models/deepseek.nim:36-52).  experts: a list of
+    (gateProj, upProj, downProj) Linear triples; forward applies DeepSeekMoE.forward's weighted sum for the
+    routing that moeRoute returned."""
+
+    def __init__(self, experts, slot=0):
+        _lib.init()
+        n = len(experts)
+
+        def arr(get):
+            return (C.c_void_p * n)(*[(_h(get(e)).value if get(e) is not None else None) for e in experts])
+
+        h = C.c_void_p()
+        check(lib().rewb200_experts_create(slot, n, arr(lambda e: e[0].weight), arr(lambda e: e[0].bias),
+                                           arr(lambda e: e[1].weight), arr(lambda e: e[1].bias),
+                                           arr(lambda e: e[2].weight), arr(lambda e: e[2].bias), C.byref(h)))
+        self._h = h
+
+    def forward(self, x, weights, indices):
+        o = _out()
+        check(lib().rewb200_moe_experts(self._h, _h(x), _h(weights), _h(indices), C.byref(o)))
+        return Tensor(o)
+
+    def free(self):
+        if self._h is not None:
+            lib().rewb200_experts_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Sampler:
+    """GenerationConfig + Key of generate (src/rew/infer/generate.nim:12-58,231-265) for a batch of sequences."""
+
+    def __init__(self, batch, vocab, max_tokens, temperature=1.0, top_k=50, top_p=1.0, min_p=0.0, repetition_penalty=1.0,
+                 do_sample=True, seeds=None, slot=0):
+        _lib.init()
+        sp = None
+        if seeds is not None:
+            sd = np.ascontiguousarray(seeds, dtype=np.uint64)
+            assert sd.shape == (batch,), "seeds must hold one value per sequence"
+            sp = sd.ctypes.data_as(C.POINTER(C.c_uint64))
+        h = C.c_void_p()
+        check(lib().rewb200_sampler_create(slot, batch, vocab, max_tokens, temperature, top_k, top_p, min_p, repetition_penalty,
+                                           int(bool(do_sample)), sp, C.byref(h)))
+        self._h, self.batch, self.vocab = h, batch, vocab
+
+    def observe(self, ids):
+        a = np.ascontiguousarray(ids, dtype=np.int32).reshape(self.batch, -1)
+        check(lib().rewb200_sampler_observe(self._h, a.ctypes.data_as(_lib.I32P), a.shape[1]))
+
+    def free(self):
+        if self._h is not None:
+            lib().rewb200_sampler_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def lmHeadSample(x, lmHead, sampler=None, want_logits=False):
+    """lmHead + sampleGreedy / sampleTopK / sampleTopP on the last hidden state x [batch, d]; returns ids (and logits)."""
+    B, V = x.shape[0], lmHead.weight.shape[1]
+    ids = np.empty(B, np.int32)
+    logits = np.empty((B, V), np.float32) if want_logits else None
+    check(lib().rewb200_lmhead_sample(_h(x), _h(lmHead.weight), _h(lmHead.bias), sampler._h if sampler is not None else None,
+                                      ids.ctypes.data_as(_lib.I32P), logits.ctypes.data_as(_lib.F32P) if want_logits else None))
+    return (ids, logits) if want_logits else ids
+
+
 def dispatch(op, operands, attrs=()):
     """dispatchEager(op, operands, attrs) (src/rew/dispatch.nim:75-85)."""
     n = len(operands)
@@ -310,13 +441,15 @@ class Session:
                                            logits.ctypes.data_as(_lib.F32P) if want_logits else None))
         return (out, logits) if want_logits else out
 
-    def generate(self, prompt, max_new_tokens, eos=-1, want_logits=False):
-        """generate (src/rew/infer/generate.nim:231-265), greedy, batched."""
+    def generate(self, prompt, max_new_tokens, eos=-1, want_logits=False, stop_ids=()):
+        """generate (src/rew/infer/generate.nim:231-265), batched; stop_ids = GenerationConfig.stopTokenIds."""
         a = self._ids(prompt)
         out = np.empty((self.batch, max_new_tokens), np.int32)
         logits = np.empty((self.batch, self.model.cfg.vocab), np.float32) if want_logits else None
-        check(lib().rewb200_generate(self._h, a.ctypes.data_as(_lib.I32P), a.shape[1], max_new_tokens, eos,
-                                     out.ctypes.data_as(_lib.I32P), logits.ctypes.data_as(_lib.F32P) if want_logits else None))
+        stops = np.ascontiguousarray(list(stop_ids), dtype=np.int32)
+        check(lib().rewb200_generate_stop(self._h, a.ctypes.data_as(_lib.I32P), a.shape[1], max_new_tokens, eos,
+                                          stops.ctypes.data_as(_lib.I32P) if stops.size else None, int(stops.size),
+                                          out.ctypes.data_as(_lib.I32P), logits.ctypes.data_as(_lib.F32P) if want_logits else None))
         return (out, logits) if want_logits else out
 
     def set_sampling(self, temperature=1.0, top_k=50, top_p=1.0, min_p=0.0, repetition_penalty=1.0, do_sample=True,

@@ -155,6 +155,20 @@ static void heap_fill(PeerInfo* info, int r, char* base, bool own) {
   if (own) info->epoch = (int*)base;
 }
 
+// After a synchronisation of the slot's stream: reports an error NCCL raised asynchronously (a rank that went
+// away, a transport fault) instead of leaving it to the next collective; the communicator is aborted then.
+int comm_check_async(int slot) {
+  if (slot < 0 || slot >= 16 || !g_comm[slot].comm) return REWB200_OK;
+  ncclResult_t async = ncclSuccess;
+  RB_NCCL(g_nccl.CommGetAsyncError(g_comm[slot].comm, &async));
+  if (async != ncclSuccess) {
+    g_nccl.CommAbort(g_comm[slot].comm);
+    g_comm[slot].comm = nullptr;
+    return fail(std::string("NCCL asynchronous error: ") + g_nccl.GetErrorString(async));
+  }
+  return REWB200_OK;
+}
+
 const PeerInfo* comm_peer_info(int slot) {
   return (slot >= 0 && slot < 16 && g_heap[slot].attached) ? &g_heap[slot].info : nullptr;
 }
@@ -237,20 +251,30 @@ int rewb200_comm_init(int slot, const void* id128, int rank, int world) {
   return REWB200_OK;
 }
 
+static int comm_finish(Ctx* c, int slot);
+
 int rewb200_comm_allreduce_f32(int slot, void* device_ptr, int64_t n) {
   Ctx* c = ctx_get(slot);
   if (!c) return REWB200_ERR;
   RB_CUDA(cudaSetDevice(c->device));
   RB_TRY(comm_allreduce_sum(c, slot, device_ptr, n, REWB200_F32));
+  return comm_finish(c, slot);
+}
+
+static int comm_finish(Ctx* c, int slot) {
   RB_CUDA(cudaStreamSynchronize(c->stream));
-  ncclResult_t async = ncclSuccess;
-  RB_NCCL(g_nccl.CommGetAsyncError(g_comm[slot].comm, &async));
-  if (async != ncclSuccess) {
-    g_nccl.CommAbort(g_comm[slot].comm);
-    g_comm[slot].comm = nullptr;
-    return fail(std::string("NCCL asynchronous error: ") + g_nccl.GetErrorString(async));
-  }
-  return REWB200_OK;
+  return comm_check_async(slot);
+}
+
+int rewb200_comm_alltoall(int slot, const void* send_device, void* recv_device, int64_t bytes_per_peer) {
+  Ctx* c = ctx_get(slot);
+  if (!c) return REWB200_ERR;
+  RB_REQUIRE(send_device && recv_device && bytes_per_peer >= 0, "allToAll: NULL buffer or negative size");
+  RB_REQUIRE(send_device != recv_device, "allToAll: send and receive buffers must differ");
+  RB_CUDA(cudaSetDevice(c->device));
+  if (bytes_per_peer == 0) return REWB200_OK;
+  RB_TRY(comm_alltoall_bytes(c, slot, send_device, recv_device, (size_t)bytes_per_peer));
+  return comm_finish(c, slot);
 }
 
 int rewb200_comm_destroy(int slot) {

@@ -191,6 +191,8 @@ int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_
                        int ksplit, void* out, int64_t ldo, const float* bias, const int* row_offsets, int max_rows_per_group);
 int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, int ksplit,
                      void* out, int64_t ldo, const float* bias);
+int linear_tc_grouped_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, void* out,
+                             int64_t ldo, const float* bias, const int* row_offsets);
 // Decode-size split-K on thread-block clusters (M <= 32, ksplit in {2,4,8}): the CTAs that share a
 // feature tile sum their accumulators through distributed shared memory and leave ONE f32 slab
 // out[M][ldo] (bias still for the consumer), or, with fuse_qkv, finished q / k / v exactly as

@@ -31,6 +31,7 @@ int comm_world(int slot);
 int comm_rank(int slot);
 int comm_allreduce_sum(Ctx* c, int slot, void* ptr, int64_t n, int dtype);
 int comm_allgather_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_rank);
+int comm_check_async(int slot);
 int slab_sum_launch(Ctx* c, float* part, int nsplit, int64_t slab_elems);
 int epoch_bump_launch(Ctx* c, int* epoch, int by);
 int comm_alltoall_bytes(Ctx* c, int slot, const void* send, void* recv, size_t bytes_per_peer);
@@ -1518,6 +1519,7 @@ int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32
   RB_CUDA(cudaStreamSynchronize(c->stream));
   RB_CUDA(cudaEventElapsedTime(&s->prefill_ms, s->ev0, s->ev1));
   s->host_pos += S;
+  if (m->cfg.tp_size > 1 || m->cfg.ep_size > 1) RB_TRY(comm_check_async(m->slot));
   return ctx_check_status(c);
 }
 
@@ -1574,6 +1576,7 @@ static int decode_core(rewb200_session* s, int n_steps, int32_t* out_ids, float*
   if (last_logits) RB_TRY(fetch_logits(s, s->B, last_logits));
   RB_CUDA(cudaStreamSynchronize(c->stream));
   RB_CUDA(cudaEventElapsedTime(&s->decode_ms, s->ev0, s->ev1));
+  if (m->cfg.tp_size > 1 || m->cfg.ep_size > 1) RB_TRY(comm_check_async(m->slot));
   return ctx_check_status(c);
 }
 
@@ -1590,33 +1593,41 @@ int rewb200_session_decode(rewb200_session* s, int n_steps, int32_t* out_ids, fl
   return REWB200_OK;
 }
 
-int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
-                     float* last_logits) {
+int rewb200_generate_stop(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, const int32_t* stop_ids,
+                          int n_stop, int32_t* out_ids, float* last_logits) {
   RB_REQUIRE(s && prompt && out_ids, "rewb200_generate: NULL argument");
   RB_REQUIRE(!s->paged, "rewb200_generate: a paged session is driven by rewb200_lane_admit / rewb200_lanes_step");
   RB_REQUIRE(n_new >= 1, "generate: maxNewTokens must be positive");
+  RB_REQUIRE(n_stop >= 0 && (n_stop == 0 || stop_ids != nullptr), "generate: stopTokenIds missing");
+  // `nextToken in config.stopTokenIds or nextToken == eosTokenId` (generate.nim:263)
+  auto is_stop = [&](int32_t id) {
+    if (eos >= 0 && id == eos) return true;
+    for (int i = 0; i < n_stop; ++i)
+      if (id == stop_ids[i]) return true;
+    return false;
+  };
+  const bool stops = eos >= 0 || n_stop > 0;
   RB_TRY(rewb200_session_reset(s));
   std::vector<int32_t> first(s->B);
   RB_TRY(rewb200_session_forward(s, prompt, S, first.data(), n_new == 1 ? last_logits : nullptr));
   for (int b = 0; b < s->B; ++b) out_ids[(size_t)b * n_new] = first[b];
   if (n_new == 1) return REWB200_OK;
   auto all_done = [&](int upto) {
-    if (eos < 0) return false;
     for (int b = 0; b < s->B; ++b) {
       bool hit = false;
-      for (int t = 0; t < upto; ++t) hit |= (out_ids[(size_t)b * n_new + t] == eos);
+      for (int t = 0; t < upto; ++t) hit |= is_stop(out_ids[(size_t)b * n_new + t]);
       if (!hit) return false;
     }
     return true;
   };
-  if (eos < 0) {
+  if (!stops) {
     std::vector<int32_t> rest((size_t)s->B * (n_new - 1));
     RB_TRY(rewb200_session_decode(s, n_new - 1, rest.data(), last_logits));
     for (int b = 0; b < s->B; ++b)
       for (int t = 1; t < n_new; ++t) out_ids[(size_t)b * n_new + t] = rest[(size_t)b * (n_new - 1) + t - 1];
     return REWB200_OK;
   }
-  // With a stop token the host looks at the ids every 8 steps.
+  // With stop tokens the host looks at the ids every 8 steps.
   int done = 1;
   for (int b = 0; b < s->B; ++b)
     for (int t = 1; t < n_new; ++t) out_ids[(size_t)b * n_new + t] = -1;
@@ -1628,15 +1639,20 @@ int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new
       for (int t = 0; t < chunk; ++t) out_ids[(size_t)b * n_new + done + t] = rest[(size_t)b * chunk + t];
     done += chunk;
   }
-  // ids after a sequence's first eos are not part of its output (generate.nim:263-264)
+  // ids after a sequence's first stop token are not part of its output (generate.nim:263-264)
   for (int b = 0; b < s->B; ++b) {
     bool hit = false;
     for (int t = 0; t < n_new; ++t) {
       if (hit) out_ids[(size_t)b * n_new + t] = -1;
-      else if (out_ids[(size_t)b * n_new + t] == eos) hit = true;
+      else if (is_stop(out_ids[(size_t)b * n_new + t])) hit = true;
     }
   }
   return REWB200_OK;
+}
+
+int rewb200_generate(rewb200_session* s, const int32_t* prompt, int S, int n_new, int eos, int32_t* out_ids,
+                     float* last_logits) {
+  return rewb200_generate_stop(s, prompt, S, n_new, eos, nullptr, 0, out_ids, last_logits);
 }
 
 

@@ -305,6 +305,9 @@ int linear_bf16_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_
   if (!grouped && (c->linear_impl == 2 || (c->linear_impl == 1 && M > 32)))
     return linear_tc_launch(c, plan, x, ldx, M, epi, ksplit, out, ldo, bias);
   RB_REQUIRE(!grouped || (row_offsets != nullptr && ksplit == 1), "grouped Linear needs row offsets and no split-K");
+  // groups of prefill size are contractions for the tcgen05 pipe; small ones (decode) stream weights from HBM here
+  if (grouped && max_rows_per_group > 64 && c->linear_impl != 0 && plan.groups <= 256 && epi != EPI_PARTIAL_F32)
+    return linear_tc_grouped_launch(c, plan, x, ldx, M, epi, out, ldo, bias, row_offsets);
   const int64_t rows_for_tile = grouped ? max_rows_per_group : M;
   const bool small = rows_for_tile <= 64;  // 33..64 rows: two 32-row tiles keep two CTAs per SM
   const int ROWS = small ? 32 : 128;

@@ -53,6 +53,8 @@ struct TcArgs {
   int64_t split_stride;
   const float* bias;
   int* status;
+  const int* row_offsets;  // grouped launches (persistent kernel): rows of group g = [row_offsets[g], row_offsets[g+1])
+  int groups;
   int fuse_qkv;       // cluster kernel: finish q|k|v in the epilogue (bias, RoPE, cache write) instead of one f32 slab
   QkvPostArgs qp;     // what qkv_post_kernel would have been given (partial / nsplit unused)
 };
@@ -462,11 +464,20 @@ struct PersistCfg {
   static constexpr int TMEM_COLS = 512;
 };
 
+// GROUPED: the weights are `groups` stacked matrices (3-D tensor map, third coordinate = group, e.g. the
+// routed experts of a MoE layer) and group g owns the rows [row_offsets[g], row_offsets[g+1]) of x and of the
+// output; the offsets are device data from an earlier kernel of the step.  The tile list is then built on
+// the device: token tiles are numbered group by group (a group's last tile may be ragged), and a tile loads a
+// full box of rows (the surplus belongs to the next group or is out of range) but stores only its own.
+constexpr int kMaxGroups = 256;
+
+template <bool GROUPED>
 __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_constant__ CUtensorMap tmW,
                                                                  const __grid_constant__ CUtensorMap tmX, TcArgs a,
                                                                  int tiles_n, int tiles_m) {
   using C = PersistCfg;
   constexpr int TN = C::TN;
+  __shared__ int s_first_tile[GROUPED ? kMaxGroups + 1 : 1];  // token tiles ahead of each group
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stg_base = smem + C::STAGES * C::STAGE_BYTES;
@@ -477,18 +488,50 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = tiles_n * tiles_m;
   const int nkb = (int)((a.K + BK - 1) / BK);
-  // same tile order as the one-tile kernel: groups of 8 token tiles per feature tile
-  auto tile_coords = [&](int lin, int& tile_n, int& tile_m) {
-    constexpr int GROUP_M = 8;
-    const int per_group = GROUP_M * tiles_n;
-    const int group = lin / per_group;
-    const int first_m = group * GROUP_M;
-    const int group_rows = min(GROUP_M, tiles_m - first_m);
-    const int in_group = lin - group * per_group;
-    tile_m = first_m + in_group % group_rows;
-    tile_n = in_group / group_rows;
+  if constexpr (GROUPED) {
+    pdl_wait();  // the row offsets come from an earlier kernel of the step
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int g = 0; g < a.groups; ++g) {
+        s_first_tile[g] = acc;
+        acc += (a.row_offsets[g + 1] - a.row_offsets[g] + TN - 1) / TN;
+      }
+      s_first_tile[a.groups] = acc;
+    }
+    __syncthreads();
+    tiles_m = s_first_tile[a.groups];
+  }
+  const int total_tiles = tiles_n * tiles_m;
+  // Dense: same tile order as the one-tile kernel, groups of 8 token tiles per feature tile.  Grouped:
+  // feature tiles fastest, so the CTAs of a wave work on a few token tiles of one or two experts.
+  // row0 = first row of the tile, rows_valid = rows of it that belong to the output, grp = weight matrix.
+  auto tile_coords = [&](int lin, int& tile_n, int& row0, int& rows_valid, int& grp) {
+    if constexpr (GROUPED) {
+      const int gm = lin / tiles_n;
+      tile_n = lin - gm * tiles_n;
+      int lo = 0, hi = a.groups;  // the group g with s_first_tile[g] <= gm < s_first_tile[g + 1]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_first_tile[mid] <= gm) lo = mid;
+        else hi = mid;
+      }
+      grp = lo;
+      row0 = a.row_offsets[lo] + (gm - s_first_tile[lo]) * TN;
+      rows_valid = min(TN, a.row_offsets[lo + 1] - row0);
+    } else {
+      constexpr int GROUP_M = 8;
+      const int per_group = GROUP_M * tiles_n;
+      const int group = lin / per_group;
+      const int first_m = group * GROUP_M;
+      const int group_rows = min(GROUP_M, tiles_m - first_m);
+      const int in_group = lin - group * per_group;
+      const int tile_m = first_m + in_group % group_rows;
+      tile_n = in_group / group_rows;
+      row0 = tile_m * TN;
+      rows_valid = (int)min((int64_t)TN, a.M - row0);
+      grp = 0;
+    }
   };
 
   if (threadIdx.x == 0) {
@@ -521,9 +564,9 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
       int it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int tile_n, tile_m;
-        tile_coords(t, tile_n, tile_m);
-        const int col0 = tile_n * BM, row0 = tile_m * TN;
+        int tile_n, row0, rows_valid, grp;
+        tile_coords(t, tile_n, row0, rows_valid, grp);
+        const int col0 = tile_n * BM;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % C::STAGES;
           if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) - 1) & 1, a.status)) {
@@ -533,8 +576,13 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
           uint8_t* st = smem + s * C::STAGE_BYTES;
           mbar_expect_tx(&full[s], C::STAGE_BYTES);
           const int k = kb * BK;
-          tma_load_2d_hint(st, &tmW, &full[s], col0, k, pol_w);
-          tma_load_2d_hint(st + A_BYTES / 2, &tmW, &full[s], col0 + 64, k, pol_w);
+          if constexpr (GROUPED) {
+            tma_load_3d_hint(st, &tmW, &full[s], col0, k, grp, pol_x);  // an expert's weights serve several token tiles: keep them in L2
+            tma_load_3d_hint(st + A_BYTES / 2, &tmW, &full[s], col0 + 64, k, grp, pol_x);
+          } else {
+            tma_load_2d_hint(st, &tmW, &full[s], col0, k, pol_w);
+            tma_load_2d_hint(st + A_BYTES / 2, &tmW, &full[s], col0 + 64, k, pol_w);
+          }
           tma_load_2d_hint(st + A_BYTES, &tmX, &full[s], k, row0, pol_x);
         }
       }
@@ -588,16 +636,16 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
     int j = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
-      int tile_n, tile_m;
-      tile_coords(t, tile_n, tile_m);
-      const int col0 = tile_n * BM, row0 = tile_m * TN;
-      const int rows_valid = (int)min((int64_t)TN, a.M - row0);
+      int tile_n, row0, rows_valid, grp;
+      tile_coords(t, tile_n, row0, rows_valid, grp);
+      const int col0 = tile_n * BM;
       const int buf = j & 1;
       if (ok) ok = mbar_wait(&tmem_full[buf], (j >> 1) & 1, a.status);
       tc::fence_after();
       const int64_t feat = (int64_t)col0 + q * 32 + lane;
       const bool feat_ok = feat < a.N;
-      const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
+      // grouped launches keep one bias row per group: [groups][N]
+      const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[(int64_t)grp * a.N + feat] : 0.f;
       const int64_t out_col0 = swiglu ? col0 / 2 : col0;
 #pragma unroll 1
       for (int c0 = 0; c0 < TN; c0 += 32) {
@@ -715,6 +763,48 @@ int linear_tc_cluster_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, 
   return REWB200_OK;
 }
 
+// Grouped launch (plan.groups stacked weight matrices, rows of group g = [row_offsets[g], row_offsets[g+1]) of
+// x / out, bias [groups][N] or NULL): the persistent kernel with its tile list built on the device.  For
+// groups of prefill size (MoE experts with hundreds of rows each); smaller ones stay on the HBM-bound
+// mma.sync kernel of linear_bf16.cu.
+int linear_tc_grouped_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t ldx, int64_t M, int epi, void* out,
+                             int64_t ldo, const float* bias, const int* row_offsets) {
+  RB_REQUIRE(plan.groups >= 1 && plan.groups <= kMaxGroups && row_offsets != nullptr, "grouped tcgen05 Linear: 1..256 groups and row offsets");
+  RB_REQUIRE(ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0, "bf16 Linear: activations must be 16-byte aligned rows");
+  RB_REQUIRE(epi != EPI_PARTIAL_F32, "grouped Linear does not split K");
+  RB_REQUIRE(epi != EPI_SWIGLU_BF16 || plan.N % 16 == 0, "SwiGLU epilogue needs interleaved width % 16 == 0");
+  if (M == 0) return REWB200_OK;
+  CUtensorMap tmX;
+  RB_TRY(make_tmap_2d_bf16(&tmX, x, (uint64_t)plan.K, (uint64_t)M, (uint64_t)ldx * 2, 64, PersistCfg::TN));
+  TcArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = M;
+  a.N = plan.N;
+  a.K = plan.K;
+  a.kb_per_split = (int)((plan.K + BK - 1) / BK);
+  a.epi = epi;
+  a.out = out;
+  a.ldo = ldo;
+  a.split_stride = M * ldo;
+  a.bias = bias;
+  a.status = c->d_status;
+  a.row_offsets = row_offsets;
+  a.groups = plan.groups;
+  static bool attr_set = false;
+  if (!attr_set) {
+    RB_CUDA(cudaFuncSetAttribute(linear_tc_persist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistCfg::SMEM));
+    attr_set = true;
+  }
+  const int tiles_n = (int)((plan.N + BM - 1) / BM);
+  // at most ceil(M / TN) + groups token tiles exist; one CTA per SM walks them
+  const int64_t max_tiles = (int64_t)tiles_n * ((M + PersistCfg::TN - 1) / PersistCfg::TN + plan.groups);
+  const int ctas = (int)std::min<int64_t>(max_tiles, c->sm_count);
+  RB_CUDA(launch_k(linear_tc_persist_kernel<true>, dim3((unsigned)ctas), dim3(192), (size_t)PersistCfg::SMEM, c->stream, c->use_pdl,
+                   plan.tmW, tmX, a, tiles_n, 0));
+  ++g_launch_total;
+  return REWB200_OK;
+}
+
 // Loads this file's module on the current device and prepares the decode-size kernel (M <= 32), so that a
 // later launch of it neither loads code nor changes function attributes.
 int linear_tc_preload() {
@@ -752,11 +842,11 @@ int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t 
   if (TN == 256 && ksplit == 1 && c->prefill_persistent && (int64_t)grid.x * grid.y >= 2 * (int64_t)c->sm_count) {
     static bool attr_set = false;
     if (!attr_set) {
-      RB_CUDA(cudaFuncSetAttribute(linear_tc_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistCfg::SMEM));
+      RB_CUDA(cudaFuncSetAttribute(linear_tc_persist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistCfg::SMEM));
       attr_set = true;
     }
     const int ctas = (int)std::min<int64_t>((int64_t)grid.x * grid.y, c->sm_count);
-    RB_CUDA(launch_k(linear_tc_persist_kernel, dim3((unsigned)ctas), dim3(192), (size_t)PersistCfg::SMEM, c->stream, c->use_pdl,
+    RB_CUDA(launch_k(linear_tc_persist_kernel<false>, dim3((unsigned)ctas), dim3(192), (size_t)PersistCfg::SMEM, c->stream, c->use_pdl,
                      plan.tmW, tmX, a, (int)grid.x, (int)grid.y));
     ++g_launch_total;
     return REWB200_OK;

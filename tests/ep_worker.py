@@ -50,6 +50,16 @@ def main():
             time.sleep(0.05)
         uid = open(idfile, "rb").read()
     api.comm_init(uid, rank, world)
+    # allToAll through the C ABI (src/rew/ops/distributed.nim:106-128): block p of the send buffer lands in block
+    # `rank` of rank p's receive buffer
+    import ctypes as C
+    L = _lib.lib()
+    send = api.Tensor.from_host((rank * 100 + np.arange(world, dtype=np.int32))[:, None].repeat(256, 1))
+    recv = api.Tensor.from_host(np.full((world, 256), -1, np.int32))
+    ptr = lambda t: C.c_void_p(L.rewb200_buffer_device_ptr(t._h))
+    _lib.check(L.rewb200_comm_alltoall(0, ptr(send), ptr(recv), 256 * 4))
+    got = recv.to_host()
+    assert all((got[p] == p * 100 + rank).all() for p in range(world)), got[:, 0]
     # peer heap with an all-to-all region: the default exchange (stores into the owner's memory, counts and
     # flags on the device); handles travel through files like the communicator id
     mine = api.comm_peer_alloc(0, 4 << 20)

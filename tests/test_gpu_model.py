@@ -256,3 +256,57 @@ def test_model_from_hf_snapshot_directory(rb, orc, tmp_path):
     loaded = ST.llama_from_hf(model.cfg, ST.read_safetensors_dir(str(tmp_path)))
     want, _ = orc.generate_greedy(model.cfg, loaded, prompt, 8)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("nth", [1, 3, 6])
+def test_failed_activation_growth_leaves_the_session_usable(rb, orc, nth):
+    """An allocation that fails while the activation buffers grow (injected on the host, the device is not
+    touched) is reported as an error, and the session then allocates again on the next call instead of
+    launching kernels on freed or NULL buffers."""
+    from rew_b200 import _lib
+    cfg = W.tiny_llama(mask_kind=1)
+    t = W.init_weights(cfg, seed=0)
+    prompt = np.random.default_rng(7).integers(0, cfg.vocab, size=(1, 12)).astype(np.int32)
+    want_ids, _ = orc.generate_greedy(cfg, t, prompt, 5)
+    sess = rb.CausalLM(cfg).load(t).session(1, 48)
+    assert np.array_equal(sess.generate(prompt[:, :4], 2).shape, (1, 2))      # buffers sized for 4 rows exist now
+    rb.set_option("inject_alloc_fail", str(nth))
+    try:
+        with pytest.raises(_lib.RewB200Error, match="injected"):
+            sess.generate(prompt, 5)                                              # 12 rows: growth fails part-way
+    finally:
+        rb.set_option("inject_alloc_fail", "0")
+    assert np.array_equal(sess.generate(prompt[:, :4], 2).shape, (1, 2))      # fewer rows than the old capacity
+    assert np.array_equal(sess.generate(prompt, 5), want_ids)
+
+
+def test_l8_shaped_layer_bf16_batch32_against_oracle(rb, orc):
+    """One decoder layer with Llama-3-8B's shapes (d_model 4096, 32 query / 8 kv heads, head_dim 128, SwiGLU
+    14336; the vocabulary cut to 32064 to keep the host arrays small) plus lm_head, bf16, batch 32: the shapes
+    the benchmark's decode step runs (32-row tcgen05 Linear tiles with split-K, cluster norm, split-KV decode
+    attention), against f32 oracle math on the bf16-rounded weights.  Prefill of 4 tokens per sequence, then two
+    cached decode steps."""
+    from rew_b200 import _lib
+    cfg = W.llama3_8b()
+    cfg.n_layers, cfg.vocab, cfg.max_seq = 1, 32064, 64
+    rng = np.random.default_rng(3)
+    t = []
+    for name, shape in W.tensor_specs(cfg):   # N(0, 0.02) matrices rounded to bf16, zero biases, unit gammas
+        if len(shape) == 2:
+            a = rng.standard_normal(size=shape, dtype=np.float32)
+            a *= 0.02
+            t.append(orc.bf16_round(a))
+        else:
+            t.append(np.ones(shape, np.float32) if name.endswith("gamma") else np.zeros(shape, np.float32))
+    B, S = 32, 4
+    prompt = np.random.default_rng(8).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+    sess = rb.CausalLM(cfg).load(t).session(B, 16)
+    nxt, logits = sess.forward(prompt, want_logits=True)
+    want = orc.model_forward(cfg, t, prompt, 0, True)[:, -1]
+    assert rel_l2(logits, want) <= 2e-2
+    assert max(rel_l2(logits[b], want[b]) for b in range(B)) <= 2e-2
+    ids, last = sess.decode(2, want_logits=True)
+    seq = np.concatenate([prompt, nxt[:, None], ids[:, :1]], 1)
+    want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
+    assert rel_l2(last, want) <= 2e-2
+    assert max(rel_l2(last[b], want[b]) for b in range(B)) <= 2e-2

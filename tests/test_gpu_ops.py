@@ -196,7 +196,8 @@ def test_attention_bf16_prefill(rb, orc, B, nh, kvh, S, hd, mode):
 
 
 def test_attention_config2_bf16_decode_shape(rb, orc):
-    """The attention-operator configuration, decode: batch 8, 32 q / 8 kv heads, head_dim 128, cache 4096 (checked on 2 sequences)."""
+    """The attention-operator configuration, decode: batch 8, 32 q / 8 kv heads, head_dim 128, one query over a
+    cache of 4096 per sequence; every sequence against the oracle."""
     from rew_b200 import _lib
     rng = np.random.default_rng(42)
     B, nh, kvh, L, hd = 8, 32, 8, 4096, 128
@@ -204,9 +205,33 @@ def test_attention_config2_bf16_decode_shape(rb, orc):
     k = orc.bf16_round(rng.normal(size=(B, kvh, L, hd)))
     v = orc.bf16_round(rng.normal(size=(B, kvh, L, hd)))
     got = rb.scaledDotProductAttention(T(rb, q, _lib.BF16), T(rb, k, _lib.BF16), T(rb, v, _lib.BF16), True, 1).to_host()
-    want = orc.gqa_attention(q[:2], k[:2], v[:2], True, 1)
-    assert rel_l2(got[:2], want) < BF16_TOL
+    want = orc.gqa_attention(q, k, v, True, 1)
+    assert rel_l2(got, want) < BF16_TOL
+    assert max(rel_l2(got[b], want[b]) for b in range(B)) < BF16_TOL
+
+
+def test_attention_config2_bf16_prefill_shape(rb, orc):
+    """The attention-operator configuration, prefill: batch 8, 32 q / 8 kv heads, head_dim 128, causal, 4096
+    positions (32 key tiles per query block on the tcgen05 kernel).  The device computes all of it; the oracle
+    (O(S^2) per head) checks the first and the last kv group of one sequence in the middle of the batch and
+    the first kv group of the last sequence: 12 of 256 query heads, all 4096 rows of each."""
+    from rew_b200 import _lib
+    rng = np.random.default_rng(43)
+    B, nh, kvh, S, hd = 8, 32, 8, 4096, 128
+    q = orc.bf16_round(rng.standard_normal(size=(B, nh, S, hd), dtype=np.float32))
+    k = orc.bf16_round(rng.standard_normal(size=(B, kvh, S, hd), dtype=np.float32))
+    v = orc.bf16_round(rng.standard_normal(size=(B, kvh, S, hd), dtype=np.float32))
+    got = rb.scaledDotProductAttention(T(rb, q, _lib.BF16), T(rb, k, _lib.BF16), T(rb, v, _lib.BF16), True, 1).to_host()
     assert np.isfinite(got).all()
+    g = nh // kvh
+    for b, groups in ((3, (0, kvh - 1)), (B - 1, (0,))):
+        heads = np.concatenate([np.arange(kg * g, (kg + 1) * g) for kg in groups])
+        want = orc.gqa_attention(np.ascontiguousarray(q[b:b + 1, heads]), np.ascontiguousarray(k[b:b + 1, list(groups)]),
+                                 np.ascontiguousarray(v[b:b + 1, list(groups)]), True, 1)
+        assert rel_l2(got[b:b + 1, heads], want) < BF16_TOL
+        # early rows see few keys and late rows all of them: check both ends on their own
+        assert rel_l2(got[b:b + 1, heads, :128], want[:, :, :128]) < BF16_TOL
+        assert rel_l2(got[b:b + 1, heads, -128:], want[:, :, -128:]) < BF16_TOL
 
 
 def test_swiglu_and_embedding(rb, orc):
