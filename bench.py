@@ -296,7 +296,7 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     if args.layers > 0:
         cfg.n_layers = args.layers
     B, S = wl["batch"], wl["prompt"]
-    max_len = S + Wm + K + 8
+    max_len = S + Wm + K + 16
     cfg.max_seq = max(cfg.max_seq, max_len)
     parallel = "single" if world == 1 else wl.get("parallel", "replicas")
     if parallel == "ep":
@@ -348,6 +348,15 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     out = {"name": name, "parallel": parallel, "batch_per_gpu": B, "prompt": S, "value": tokens / (decode_ms * 1e-3),
            "ms_per_step": decode_ms / K, "prefill_ms": prefill_ms, "prefill_tokens_per_s": B * S * mult / (prefill_ms * 1e-3),
            "launches": int(launches), "clocks": clocks, "weight_gb": model.weight_bytes() / 1e9, "cfg": cfg}
+
+    if args.trace:
+        # where a step's time goes, per category of launches (events between them: no overlap, so the sum is
+        # above the replayed step); max over ranks of the mean of three traced steps
+        acc = None
+        for _ in range(3):
+            t = sess.trace_step()
+            acc = t if acc is None else {k: acc[k] + v for k, v in t.items()}
+        out["trace_ms"] = {k: round(max_over_ranks(v / 3.0), 4) for k, v in acc.items()}
 
     # ---- end to end through the C ABI: host prompt ids -> host output ids
     if with_e2e:
@@ -437,6 +446,8 @@ def sub_record(r, which_allreduce=None):
         d["linear_ms_per_step"] = r["linear"]["ms_per_step"]
     if which_allreduce:
         d["allreduce"] = which_allreduce
+    if "trace_ms" in r:
+        d["trace_ms"] = r["trace_ms"]
     return d
 
 
@@ -452,6 +463,7 @@ def main():
                     help="skip the tensor-parallel (l70_b16) and expert-parallel (moe_b64) sub-records of the default workload")
     ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
                     help="run-time switch passed to rewb200_set_option, e.g. norm=row (repeatable)")
+    ap.add_argument("--trace", action="store_true", help="add per-category device times of a decode step to every record")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "top_k", "top_p"],
                     help="next-token rule of the decode step; greedy is the metric's configuration")
@@ -538,6 +550,8 @@ def main():
         "prefill": {"tokens_per_s": r["prefill_tokens_per_s"], "ms": r["prefill_ms"]},
         "e2e": r["e2e"], "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": roofline,
     }
+    if "trace_ms" in r:
+        line["trace_ms"] = r["trace_ms"]
     line.update(extra)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_leg(args, wl)

@@ -73,6 +73,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            "prefix" from 4 ranks on; prefix = NCCL, pair counts first and then only the
  *                                            occupied prefix of every slot array (steps of 64+ pairs outside a captured
  *                                            graph); capacity = NCCL, always the worst-case capacity
+ *   "record_routing" = "0" | "1"             test aid: sessions created afterwards keep every MoE layer's top-k expert ids
+ *                                            of their last forward for rewb200_session_routing
  *   "inject_alloc_fail" = "n"                test hook: the n-th activation-buffer allocation from now fails on the host
  *   "moe_overlap" = "on" | "off"             MoE layers on one rank, steps of at most 64 rows: the shared experts run on a
  *                                            second stream beside the routed experts (default on)
@@ -278,6 +280,19 @@ int64_t rewb200_model_tensor_count(const rewb200_model* m);
 /* Uploads logical tensor `index` from host f32 data of the FULL (unsharded)
  * shape; the library slices for tp/ep rank, converts and fuses. */
 int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host, int64_t numel);
+/* The sharding vocabulary of src/rew/sharding.nim for this model: where logical tensor `index` lives on this
+ * rank.  global_shape / local_shape / offsets (ndims entries each, at most 2) follow shardLayout's block rule
+ * (sharding.nim:255-270: localShape[dim] = shape[dim] / factor, offset = coord * local) on the tensor-parallel
+ * axis: the q / k / v / gate / up / lm_head weights are PartitionSpec(["", "tp"]) (column-parallel,
+ * *partitioned_dim = 1), their biases (["tp"]), the o / down weights (["tp", ""]) (row-parallel, dim 0), the rest
+ * replicated (-1).  A routed expert that another expert-parallel rank owns has local_shape all zero. */
+int rewb200_model_tensor_layout(const rewb200_model* m, int64_t index, int* ndims, int64_t* global_shape,
+                                int64_t* local_shape, int64_t* offsets, int* partitioned_dim);
+/* fromHostShards (src/rew/eager.nim:427-505) for one tensor: uploads exactly this rank's block (host f32 of
+ * local_shape, at offsets; both must equal what rewb200_model_tensor_layout reports), so a sharded checkpoint
+ * goes shard -> rank without the full tensor ever being assembled on a host. */
+int rewb200_model_set_tensor_shard(rewb200_model* m, int64_t index, const float* host_local, const int64_t* local_shape,
+                                   const int64_t* offsets, int ndims);
 /* Device-side N(0,std) weights, zero biases, unit gammas (synthetic benchmarks). */
 int rewb200_model_init_random(rewb200_model* m, uint64_t seed, float std);
 int rewb200_model_finalize(rewb200_model* m);
@@ -352,6 +367,17 @@ int rewb200_session_logprobs(rewb200_session* s, int n, float* out);
 int rewb200_session_last_ms(const rewb200_session* s, float* prefill_ms, float* decode_ms);
 /* Kernels in one captured decode step (0 before the first decode). */
 int rewb200_session_graph_kernels(const rewb200_session* s);
+/* Test aid (option record_routing): the expert ids MoE layer `moe_layer` (0-based among the MoE layers) chose for
+ * the `rows` tokens of the session's last forward, host int32 [rows, top_k], in the router's order. */
+int rewb200_session_routing(rewb200_session* s, int moe_layer, int32_t* topi_out, int64_t rows);
+/* Measurement aid: one decode step issued as plain launches with a CUDA event after every category of
+ * launches; ms_by_category (host, n >= 11 floats) receives the device time per category, summed over the
+ * layers: 0 embedding + first norm, 1 q|k|v Linear, 2 bias + RoPE + cache write, 3 attention, 4 o Linear,
+ * 5 residual + norm after attention (with the tensor-parallel exchange), 6 gate|up Linear, 7 down Linear,
+ * 8 routed experts (MoE), 9 residual + norm after the FFN (with the exchange), 10 lm_head + next-token.  The
+ * events keep kernels from overlapping their neighbours, so the sum exceeds a replayed step; the step
+ * advances the session by one token like rewb200_session_decode(s, 1, ...). */
+int rewb200_session_trace_step(rewb200_session* s, float* ms_by_category, int n);
 /* Measurement aid: runs only the Linear launches of one decode step (same
  * buffers, tiles and split-K as the real step) `iters` times between CUDA
  * events; reports milliseconds, algorithmic bytes and launches per step. */

@@ -249,6 +249,20 @@ def model_forward(mc, tensors, ids, offset=0, causal=True):
     return logits
 
 
+def model_routing(mc, tensors, ids, offset=0, causal=True):
+    """The no-cache forward's router decisions: (topi int32, topw f32), each [n_moe_layers, B, S, k]."""
+    cfg = cfg_of(mc)
+    keep, arr = _tensor_array(tensors)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    B, S = ids.shape
+    n_moe = sum(1 for l in range(mc.n_layers) if mc.layer_is_moe(l))
+    topi = np.empty((n_moe, B, S, mc.top_k), np.int32)
+    topw = np.empty((n_moe, B, S, mc.top_k), np.float32)
+    lib().orc_model_routing(C.byref(cfg), arr, _ip(ids), C.c_int64(B), C.c_int64(S), C.c_int64(offset), int(bool(causal)),
+                            _ip(topi), _p(topw))
+    return topi, topw
+
+
 def moe_layer(mc, tensors, layer, x):
     cfg = cfg_of(mc)
     keep, arr = _tensor_array(tensors)

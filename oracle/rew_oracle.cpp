@@ -372,6 +372,13 @@ void moe_route(const float* x, const float* rw, const float* rb, int64_t N, int6
 // src/rew/models/deepseek.nim:122-145: shared experts summed, then EVERY
 // routed expert evaluated on every token and scaled by
 // weight[n] = sum_j topW[n,j] * (topIdx[n,j] == e) (:114-120).
+// Optional record of every MoE layer's routing during a forward (tests compare it with the device's).
+struct RouteRec {
+  std::vector<std::vector<int32_t>> topi;   // per MoE layer [N][k]
+  std::vector<std::vector<float>> topw;
+};
+static RouteRec* g_route_rec = nullptr;
+
 void moe_forward(const Cfg& c, const LayerW& L, const float* x, float* out, int64_t N) {
   const int64_t d = c.d_model, f = c.moe_ffn;
   std::vector<float> tmp(N * d);
@@ -385,6 +392,10 @@ void moe_forward(const Cfg& c, const LayerW& L, const float* x, float* out, int6
   std::vector<float> topw(N * c.top_k);
   std::vector<int32_t> topi(N * c.top_k);
   moe_route(x, L.rw, L.rb, N, d, c.n_routed, c.top_k, topw.data(), topi.data());
+  if (g_route_rec) {
+    g_route_rec->topi.push_back(topi);
+    g_route_rec->topw.push_back(topw);
+  }
   std::vector<float> w(N);
   for (int e = 0; e < c.n_routed; ++e) {
     bool any = false;
@@ -656,6 +667,22 @@ ORC_API void orc_model_forward(const Cfg* c, const float* const* tensors, const 
   std::vector<float> h(B * S * c->d_model);
   backbone(m, ids, h.data(), B, S, offset, causal, nullptr);
   linear(h.data(), m.lw, m.lb, logits, B * S, c->d_model, c->vocab);
+}
+
+// The same forward, returning what every MoE layer's router chose: topi / topw [n_moe_layers][B*S][k].
+ORC_API void orc_model_routing(const Cfg* c, const float* const* tensors, const int32_t* ids, int64_t B, int64_t S,
+                               int64_t offset, int causal, int32_t* topi, float* topw) {
+  Model m = build(*c, tensors);
+  std::vector<float> h(B * S * c->d_model);
+  RouteRec rec;
+  g_route_rec = &rec;
+  backbone(m, ids, h.data(), B, S, offset, causal, nullptr);
+  g_route_rec = nullptr;
+  const size_t per = (size_t)B * S * c->top_k;
+  for (size_t l = 0; l < rec.topi.size(); ++l) {
+    std::memcpy(topi + l * per, rec.topi[l].data(), per * sizeof(int32_t));
+    std::memcpy(topw + l * per, rec.topw[l].data(), per * sizeof(float));
+  }
 }
 
 // Hidden states after the final norm for one MoE/dense block stack; used by tests.

@@ -68,6 +68,8 @@ SIGNATURES = {
     "rewb200_model_free": (None, [P]),
     "rewb200_model_tensor_count": (C.c_int64, [P]),
     "rewb200_model_set_tensor": (C.c_int, [P, C.c_int64, F32P, C.c_int64]),
+    "rewb200_model_tensor_layout": (C.c_int, [P, C.c_int64, I32P, I64P, I64P, I64P, I32P]),
+    "rewb200_model_set_tensor_shard": (C.c_int, [P, C.c_int64, F32P, I64P, I64P, C.c_int]),
     "rewb200_model_init_random": (C.c_int, [P, C.c_uint64, C.c_float]),
     "rewb200_model_finalize": (C.c_int, [P]),
     "rewb200_model_weight_bytes": (C.c_int64, [P]),
@@ -95,6 +97,8 @@ SIGNATURES = {
     "rewb200_session_logprobs": (C.c_int, [P, C.c_int, F32P]),
     "rewb200_session_last_ms": (C.c_int, [P, F32P, F32P]),
     "rewb200_session_graph_kernels": (C.c_int, [P]),
+    "rewb200_session_routing": (C.c_int, [P, C.c_int, I32P, C.c_int64]),
+    "rewb200_session_trace_step": (C.c_int, [P, F32P, C.c_int]),
     "rewb200_session_profile_linears": (C.c_int, [P, C.c_int, F32P, I64P, I32P]),
     "rewb200_model_forward_all": (C.c_int, [P, I32P, C.c_int, C.c_int64, C.c_int, F32P]),
     "rewb200_comm_unique_id": (C.c_int, [P]),

@@ -368,6 +368,41 @@ class CausalLM:
         check(lib().rewb200_model_finalize(self._h))
         return self
 
+    def tensor_layout(self, index):
+        """(global_shape, local_shape, offsets, partitioned_dim) of logical tensor `index` on this rank: shardLayout's
+        block rule (src/rew/sharding.nim:255-270) for the model's tensor- / expert-parallel placement."""
+        nd, pd = C.c_int32(), C.c_int32()
+        g, l, o = (C.c_int64 * 4)(), (C.c_int64 * 4)(), (C.c_int64 * 4)()
+        check(lib().rewb200_model_tensor_layout(self._h, index, C.byref(nd), g, l, o, C.byref(pd)))
+        n = nd.value
+        return tuple(g[:n]), tuple(l[:n]), tuple(o[:n]), pd.value
+
+    def load_shards(self, get_block):
+        """Uploads only this rank's block of every tensor.  get_block(index, name, global_shape, local_shape,
+        offsets) returns that block as a float32 array of local_shape (it is not called for tensors another
+        rank owns)."""
+        specs = tensor_specs(self.cfg)
+        assert len(specs) == lib().rewb200_model_tensor_count(self._h)
+        for i, (name, shape) in enumerate(specs):
+            g, l, o, _ = self.tensor_layout(i)
+            assert tuple(g) == tuple(shape), (name, g, shape)
+            if 0 in l:
+                continue
+            a = np.ascontiguousarray(get_block(i, name, g, l, o), dtype=np.float32)
+            assert a.shape == tuple(l), (name, a.shape, l)
+            nd = len(l)
+            check(lib().rewb200_model_set_tensor_shard(self._h, i, a.ctypes.data_as(_lib.F32P), (C.c_int64 * nd)(*l),
+                                                       (C.c_int64 * nd)(*o), nd))
+        check(lib().rewb200_model_finalize(self._h))
+        return self
+
+    def load_checkpoint(self, path):
+        """A rew checkpoint directory straight into this rank's buffers: of a sharded leaf only the shard files
+        that overlap this rank's block are read (rew_b200.checkpoint.read_block)."""
+        from . import checkpoint as CK
+        reader = CK.BlockReader(path, self.cfg)
+        return self.load_shards(lambda i, name, g, l, o: reader.read_block(name, l, o))
+
     @classmethod
     def from_hf_snapshot(cls, snap_dir, dtype=None, slot=0, **config_overrides):
         """A Hugging Face Llama snapshot directory (config.json + one or more *.safetensors) on the device:
@@ -451,6 +486,21 @@ class Session:
                                           stops.ctypes.data_as(_lib.I32P) if stops.size else None, int(stops.size),
                                           out.ctypes.data_as(_lib.I32P), logits.ctypes.data_as(_lib.F32P) if want_logits else None))
         return (out, logits) if want_logits else out
+
+    def routing(self, moe_layer, rows):
+        """Expert ids [rows, top_k] MoE layer `moe_layer` chose in the last forward (needs option record_routing=1)."""
+        out = np.empty((rows, self.model.cfg.top_k), np.int32)
+        check(lib().rewb200_session_routing(self._h, moe_layer, out.ctypes.data_as(_lib.I32P), rows))
+        return out
+
+    TRACE_CATEGORIES = ("embed_norm", "qkv_linear", "qkv_post", "attention", "o_linear", "norm_after_attention",
+                        "gate_up_linear", "down_linear", "routed_experts", "norm_after_ffn", "head_and_next_token")
+
+    def trace_step(self):
+        """One decode step with a CUDA event after every category of launches: {category: ms summed over layers}."""
+        ms = (C.c_float * 16)()
+        check(lib().rewb200_session_trace_step(self._h, ms, 16))
+        return {k: float(ms[i]) for i, k in enumerate(self.TRACE_CATEGORIES)}
 
     def set_sampling(self, temperature=1.0, top_k=50, top_p=1.0, min_p=0.0, repetition_penalty=1.0, do_sample=True,
                      seeds=None):

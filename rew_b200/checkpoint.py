@@ -121,15 +121,22 @@ def load_checkpoint(path, cfg):
             continue
         if item.get("sharded"):
             full = np.empty(tuple(item["shape"]), np.float32)
-            covered = 0
+            seen = np.zeros(full.shape, np.bool_)   # which elements a shard has written
             for sh in item["shards"]:
                 part = np.load(os.path.join(path, sh["file"]))
                 if list(part.shape) != list(sh["shape"]):
                     raise ValueError("Runtime.load: shard shape %r does not match expected %r" % (part.shape, sh["shape"]))
-                sl = tuple(slice(o, o + n) for o, n in zip(sh["offsets"], part.shape))
+                offs = list(sh["offsets"])
+                if len(offs) != full.ndim or part.ndim != full.ndim or any(
+                        o < 0 or o + n > dim for o, n, dim in zip(offs, part.shape, full.shape)):
+                    raise ValueError("Runtime.load: shard %r of leaf %d lies outside its shape %r (offsets %r, shape %r)"
+                                     % (sh.get("index"), idx, full.shape, offs, part.shape))
+                sl = tuple(slice(o, o + n) for o, n in zip(offs, part.shape))
+                if seen[sl].any():
+                    raise ValueError("Runtime.load: shards of leaf %d overlap (shard %r)" % (idx, sh.get("index")))
                 full[sl] = part
-                covered += part.size
-            if covered != full.size:
+                seen[sl] = True
+            if not seen.all():
                 raise ValueError("Runtime.load: shards of leaf %d do not cover its shape" % idx)
             arr = full
         else:
@@ -144,3 +151,64 @@ def load_checkpoint(path, cfg):
     if missing:
         raise ValueError("Runtime.load: checkpoint lacks %d tensors, first: %s" % (len(missing), missing[0]))
     return [found[n] for n, _ in tensor_specs(cfg)]
+
+
+class BlockReader:
+    """Reads blocks of a checkpoint's leaves without assembling whole tensors: for a leaf written as shards
+    (Runtime.save of a partitioned leaf, src/rew/train/runtime.nim:293-316) only the shard files that overlap
+    the requested block are opened, and when the block is exactly one shard (the checkpoint was written with the
+    partitioning the model is loaded with) that file is the block.  files_read lists what was opened."""
+
+    def __init__(self, path, cfg):
+        self.path = path
+        with open(os.path.join(path, "manifest.json")) as f:
+            manifest = json.load(f)
+        leaves = pytree_leaves(cfg)
+        if manifest.get("leaf_count") != len(leaves):
+            raise ValueError("Runtime.load: checkpoint has %r leaves, this model configuration has %d"
+                             % (manifest.get("leaf_count"), len(leaves)))
+        self.want_shape = dict(tensor_specs(cfg))
+        self.items = {}
+        for item in manifest["tensors"]:
+            idx = item["index"]
+            if not 0 <= idx < len(leaves):
+                raise ValueError("Runtime.load: leaf index %r out of range" % (idx,))
+            self.items[leaves[idx]] = item
+        self.files_read = []
+
+    def _load(self, fname, mmap=False):
+        self.files_read.append(fname)
+        return np.load(os.path.join(self.path, fname), mmap_mode="r" if mmap else None)
+
+    def read_block(self, name, local_shape, offsets):
+        if name not in self.items:
+            raise ValueError("Runtime.load: checkpoint lacks tensor %s" % name)
+        item = self.items[name]
+        if tuple(item["shape"]) != tuple(self.want_shape[name]):
+            raise ValueError("Runtime.load: leaf %s has shape %r, expected %r" % (name, tuple(item["shape"]), tuple(self.want_shape[name])))
+        lo = list(offsets)
+        hi = [o + n for o, n in zip(offsets, local_shape)]
+        sl = tuple(slice(a, b) for a, b in zip(lo, hi))
+        if not item.get("sharded"):
+            return np.array(self._load(item["file"], mmap=True)[sl], np.float32)
+        out = np.empty(tuple(local_shape), np.float32)
+        seen = np.zeros(out.shape, np.bool_)
+        for sh in item["shards"]:
+            s_lo = list(sh["offsets"])
+            s_hi = [o + n for o, n in zip(sh["offsets"], sh["shape"])]
+            i_lo = [max(a, b) for a, b in zip(lo, s_lo)]
+            i_hi = [min(a, b) for a, b in zip(hi, s_hi)]
+            if any(a >= b for a, b in zip(i_lo, i_hi)):
+                continue                                             # this shard does not touch the block
+            part = self._load(sh["file"])
+            if list(part.shape) != list(sh["shape"]):
+                raise ValueError("Runtime.load: shard shape %r does not match expected %r" % (part.shape, sh["shape"]))
+            src = tuple(slice(a - o, b - o) for a, b, o in zip(i_lo, i_hi, s_lo))
+            dst = tuple(slice(a - o, b - o) for a, b, o in zip(i_lo, i_hi, lo))
+            if seen[dst].any():
+                raise ValueError("Runtime.load: shards of leaf %s overlap" % name)
+            out[dst] = part[src]
+            seen[dst] = True
+        if not seen.all():
+            raise ValueError("Runtime.load: shards of leaf %s do not cover the requested block" % name)
+        return out

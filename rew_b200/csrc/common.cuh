@@ -63,6 +63,7 @@ struct Ctx {
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
+  bool record_routing = false;  // sessions keep every MoE layer's top-k expert ids of their last forward (a test aid)
   int inject_alloc_fail = 0;  // test hook: the n-th activation allocation from now fails on the host
   int option_epoch = 0;      // bumped by rewb200_set_option; captured graphs from older epochs are rebuilt
   void* pinned = nullptr;    // pinned host staging for H2D/D2H of buffers

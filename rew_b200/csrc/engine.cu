@@ -264,6 +264,8 @@ struct rewb200_session {
   size_t moe_ints_n = 0;
   void *moe_send = nullptr, *moe_recv = nullptr, *moe_xs = nullptr, *moe_hs = nullptr;
   float *moe_ys = nullptr, *moe_ret = nullptr, *moe_back = nullptr, *moe_tmp = nullptr;
+  int* route_rec = nullptr;            // option record_routing: every MoE layer's top-k expert ids of the last forward, [n_moe][rows_cap][k]
+  int64_t route_rows = 0;              // rows of the forward recorded last
   cudaGraphExec_t graph = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float prefill_ms = 0.f, decode_ms = 0.f;
@@ -406,7 +408,7 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
     void** ptrs[] = {(void**)&s->x_res, &s->xn, &s->q, &s->attn, &s->h, (void**)&s->part, (void**)&s->gu32,
                      (void**)&s->moe_logits, (void**)&s->moe_topw, (void**)&s->moe_topi, (void**)&s->moe_ints, &s->moe_send,
                      &s->moe_recv, &s->moe_xs, &s->moe_hs, (void**)&s->moe_ys, (void**)&s->moe_ret, (void**)&s->moe_back,
-                     (void**)&s->moe_tmp};
+                     (void**)&s->moe_tmp, (void**)&s->route_rec};
     // From here until every allocation below has succeeded the session holds no activation buffers: a failed
     // growth must leave it in a state where the next call allocates again instead of launching on NULL.
     s->rows_cap = 0;
@@ -449,6 +451,7 @@ int ensure_acts(rewb200_session* s, int64_t rows, int64_t logits_rows) {
       s->moe_ints_n = (size_t)(ep + 3 * (E_l + 1) + 3 * slots + rows * k) + 16;
       RB_TRY(acts_alloc(m->c, (void**)&s->moe_ints, s->moe_ints_n * sizeof(int)));
       RB_TRY(acts_alloc(m->c, (void**)&s->moe_tmp, (size_t)rows * c.d_model * sizeof(float)));
+      if (m->c->record_routing) RB_TRY(acts_alloc(m->c, (void**)&s->route_rec, (size_t)c.n_layers * rows * k * sizeof(int)));
       if (c.dtype == REWB200_BF16) {
         RB_TRY(acts_alloc(m->c, &s->moe_send, (size_t)slots * c.d_model * es));
         if (ep > 1) RB_TRY(acts_alloc(m->c, &s->moe_recv, (size_t)slots * c.d_model * es));
@@ -588,6 +591,11 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
     else
       RB_TRY(gemm_f32_launch(c, (const float*)s->xn, (const float*)X.router.w, X.router.b, s->moe_logits, rows, d, cf.n_routed));
     RB_TRY(moe_route_launch(c, s->moe_logits, rows, cf.n_routed, k, s->moe_topw, s->moe_topi));
+  }
+  if (s->route_rec) {
+    RB_CUDA(cudaMemcpyAsync(s->route_rec + (size_t)moe_index * s->rows_cap * k, s->moe_topi, (size_t)rows * k * sizeof(int),
+                            cudaMemcpyDeviceToDevice, c->stream));
+    s->route_rows = rows;
   }
   if (dt == REWB200_F32) {
     // parity path: every local expert on every token, masked by its routing weight, as the reference does
@@ -731,7 +739,44 @@ int fetch_logits(rewb200_session* s, int64_t rows, float* host) {
   return REWB200_OK;
 }
 
+// Per-category device times of one forward (REW_B200_TRACE-style measurement aid): an event after the
+// launches of each category, elapsed times summed per category after a synchronisation.  Events between
+// kernels switch programmatic dependent launch off at those points, so the sum exceeds the untraced step;
+// the split is what it is for.
+enum TraceCat : int { TC_EMBED = 0, TC_QKV, TC_QKV_POST, TC_ATTN, TC_O, TC_NORM_ATTN, TC_GATE_UP, TC_DOWN, TC_MOE, TC_NORM_FFN, TC_HEAD, TC_COUNT };
+struct Trace {
+  std::vector<cudaEvent_t> ev;
+  std::vector<int> cat;
+  cudaStream_t st = nullptr;
+  int begin(cudaStream_t s) {
+    st = s;
+    return mark(-1);
+  }
+  int mark(int c) {
+    cudaEvent_t e;
+    RB_CUDA(cudaEventCreate(&e));
+    RB_CUDA(cudaEventRecord(e, st));
+    ev.push_back(e);
+    cat.push_back(c);
+    return REWB200_OK;
+  }
+  int finish(float* ms) {  // ms[TC_COUNT]
+    for (int i = 0; i < TC_COUNT; ++i) ms[i] = 0.f;
+    RB_CUDA(cudaStreamSynchronize(st));
+    for (size_t i = 1; i < ev.size(); ++i) {
+      float t = 0.f;
+      RB_CUDA(cudaEventElapsedTime(&t, ev[i - 1], ev[i]));
+      if (cat[i] >= 0 && cat[i] < TC_COUNT) ms[cat[i]] += t;
+    }
+    return REWB200_OK;
+  }
+  ~Trace() {
+    for (cudaEvent_t e : ev) cudaEventDestroy(e);
+  }
+};
+
 struct FwdOpts {
+  Trace* trace = nullptr;     // when set, an event follows every category of launches
   int S = 1;
   int rope_shift = 0;
   int causal = 1;
@@ -784,7 +829,9 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     a.ids = o.ids_src ? o.ids_src : s->d_ids;
     a.gamma = m->layers[0].ln1g;
     a.beta = m->layers[0].ln1b;
+    if (o.trace) RB_TRY(o.trace->begin(c->stream));
     RB_TRY(residual_norm_launch(c, a, rows));
+    if (o.trace) RB_TRY(o.trace->mark(TC_EMBED));
   }
   // Tensor parallel: steps of up to 64 rows sum the row-parallel partials inside residual_norm (each CTA
   // pushes its columns to every rank's heap and adds the peers' in rank order); larger ones go through
@@ -860,10 +907,12 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     qa.status = c->d_status;
     qa.early_lookup = in_graph ? 1 : 0;
     RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks, dt == REWB200_BF16 ? &qa : nullptr, &qkv_done));
+    if (o.trace) RB_TRY(o.trace->mark(TC_QKV));
     if (!qkv_done) {
       qa.nsplit = ks;
       RB_TRY(qkv_post_launch(c, qa, nb));
     }
+    if (o.trace) RB_TRY(o.trace->mark(TC_QKV_POST));
 
     AttnArgs aa;
     memset(&aa, 0, sizeof(aa));
@@ -894,8 +943,10 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       aa.tmV = &s->tmV[l];
     }
     RB_TRY(attn_launch(c, aa));
+    if (o.trace) RB_TRY(o.trace->mark(TC_ATTN));
 
     RB_TRY(run_row_parallel(L.o, s->attn, m->nq, &ks));
+    if (o.trace) RB_TRY(o.trace->mark(TC_O));
     {
       NormArgs a = na;
       a.partial = s->part;
@@ -906,6 +957,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       a.beta = L.ln2b;
       RB_TRY(tp_reduce(l, 0, ks, a));
       RB_TRY(residual_norm_launch(c, a, rows));
+      if (o.trace) RB_TRY(o.trace->mark(TC_NORM_ATTN));
     }
     ks = 0;  // slabs of s->part that hold FFN output so far
     // MoE layer with shared experts on one rank, small step: the shared experts (three short launches)
@@ -942,6 +994,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       st = residual_norm_launch(c, a, rows);
       c->use_pdl = pdl;
       RB_TRY(st);
+      if (o.trace) RB_TRY(o.trace->mark(TC_MOE));
       continue;
     }
     if (L.ffn_local > 0) {  // dense FFN, or the fused shared experts of a MoE layer
@@ -954,11 +1007,14 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
         RB_CUDA(cudaGetLastError());
         ++g_launch_total;
       }
+      if (o.trace) RB_TRY(o.trace->mark(TC_GATE_UP));
       RB_TRY(run_row_parallel(L.down, s->h, L.ffn_local, &ks));
+      if (o.trace) RB_TRY(o.trace->mark(TC_DOWN));
     }
     if (L.moe) {
       RB_TRY(moe_routed(s, L, rows, ks > 0, nullptr, moe_seen++));
       if (ks == 0) ks = 1;
+      if (o.trace) RB_TRY(o.trace->mark(TC_MOE));
     }
     {
       NormArgs a = na;
@@ -971,6 +1027,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       a.beta = last ? m->nb : m->layers[l + 1].ln1b;
       RB_TRY(tp_reduce(l, 1, ks, a));
       RB_TRY(residual_norm_launch(c, a, rows));
+      if (o.trace) RB_TRY(o.trace->mark(TC_NORM_FFN));
     }
   }
   if (oneshot) RB_TRY(epoch_bump_launch(c, pi->epoch, 2 * cf.n_layers));  // same on every rank
@@ -1017,6 +1074,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
                      nb, o.S, s->out_capacity));
     ++g_launch_total;
   }
+  if (o.trace) RB_TRY(o.trace->mark(TC_HEAD));
   return REWB200_OK;
 }
 
@@ -1149,16 +1207,135 @@ int64_t rewb200_model_tensor_count(const rewb200_model* m) {
 
 int64_t rewb200_model_weight_bytes(const rewb200_model* m) { return m ? m->weight_bytes : 0; }
 
+}  // extern "C"
+
+namespace rewb {
+namespace {
+
+// Which dimension of logical tensor `index` the tensor-parallel axis splits (PartitionSpec(["", "tp"]) for the
+// column-parallel q / k / v / gate / up / lm_head weights, (["tp", ""]) for the row-parallel o / down weights,
+// (["tp"]) for the biases of column-parallel layers), following shardLayout's block rule
+// (src/rew/sharding.nim:255-270).  dim = -1: replicated.  Routed-expert tensors are whole tensors owned by
+// one expert-parallel rank: *owner_ep is that rank, -1 for everything else.
+int tensor_partition(const rewb200_model* m, int64_t index, int* dim, int* ndims, int64_t* shape, int* owner_ep) {
+  const rewb200_config& c = m->cfg;
+  TensorRef r;
+  RB_TRY(locate(m, index, &r));
+  const int64_t d = c.d_model, hd = c.head_dim;
+  const int64_t NQ = (int64_t)c.n_heads * hd, NKV = (int64_t)c.n_kv_heads * hd;
+  *dim = -1;
+  *owner_ep = -1;
+  auto mat = [&](int64_t rows, int64_t cols, int split) { *ndims = 2; shape[0] = rows; shape[1] = cols; *dim = split; };
+  auto vec = [&](int64_t n, bool split) { *ndims = 1; shape[0] = n; *dim = split ? 0 : -1; };
+  if (r.layer == -1) { mat(c.vocab, d, -1); return REWB200_OK; }
+  if (r.layer == -2) {
+    switch (r.slot) {
+      case 0: case 1: vec(d, false); break;
+      case 2: mat(d, c.vocab, 1); break;
+      default: vec(c.vocab, true); break;
+    }
+    return REWB200_OK;
+  }
+  const LayerDev& L = m->layers[r.layer];
+  const int64_t F = (c.n_routed > 0 && c.first_dense > 0) ? c.first_dense : c.ffn;
+  if (!(L.moe && r.slot >= 12)) {
+    switch (r.slot) {
+      case 0: case 1: case 10: case 11: case 9: case 17: vec(d, false); break;
+      case 2: mat(d, NQ, 1); break;
+      case 3: vec(NQ, true); break;
+      case 4: case 6: mat(d, NKV, 1); break;
+      case 5: case 7: vec(NKV, true); break;
+      case 8: mat(NQ, d, 0); break;
+      case 12: case 14: mat(d, F, 1); break;
+      case 13: case 15: vec(F, true); break;
+      case 16: mat(F, d, 0); break;
+      default: return fail("tensor slot not supported for this layer kind");
+    }
+    return REWB200_OK;
+  }
+  const int64_t f = L.x.f, E = c.n_routed;
+  if (r.slot == 12) { mat(d, E, -1); return REWB200_OK; }
+  if (r.slot == 13) { vec(E, false); return REWB200_OK; }
+  const int idx = r.slot - 14, ei = idx / 6, which = idx % 6;
+  RB_REQUIRE(ei < c.n_shared + c.n_routed, "expert index out of range");
+  switch (which) {
+    case 0: case 2: mat(d, f, -1); break;
+    case 1: case 3: vec(f, false); break;
+    case 4: mat(f, d, -1); break;
+    default: vec(d, false); break;
+  }
+  if (ei >= c.n_shared) *owner_ep = (ei - c.n_shared) / L.x.E_l;
+  return REWB200_OK;
+}
+
+int set_tensor_impl(rewb200_model* m, int64_t index, const float* host, int64_t numel, bool shard);
+
+}  // namespace
+}  // namespace rewb
+
+extern "C" {
+
 int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host, int64_t numel) {
   RB_REQUIRE(m && host, "rewb200_model_set_tensor: NULL argument");
+  return set_tensor_impl(m, index, host, numel, false);
+}
+
+int rewb200_model_tensor_layout(const rewb200_model* m, int64_t index, int* ndims, int64_t* global_shape,
+                                int64_t* local_shape, int64_t* offsets, int* partitioned_dim) {
+  RB_REQUIRE(m && ndims && global_shape && local_shape && offsets, "rewb200_model_tensor_layout: NULL argument");
+  int dim = -1, owner = -1;
+  RB_TRY(tensor_partition(m, index, &dim, ndims, global_shape, &owner));
+  for (int i = 0; i < *ndims; ++i) {
+    local_shape[i] = global_shape[i];
+    offsets[i] = 0;
+  }
+  const int tp = m->cfg.tp_size;
+  if (dim >= 0 && tp > 1) {  // shardLayout: localShape[dim] = shape[dim] / factor, offset = coord * local
+    local_shape[dim] = global_shape[dim] / tp;
+    offsets[dim] = (int64_t)m->cfg.tp_rank * local_shape[dim];
+  }
+  if (owner >= 0 && m->cfg.ep_size > 1 && owner != m->cfg.ep_rank)
+    for (int i = 0; i < *ndims; ++i) local_shape[i] = 0;  // another rank's expert: nothing of it lives here
+  if (partitioned_dim) *partitioned_dim = (dim >= 0 && tp > 1) ? dim : -1;
+  return REWB200_OK;
+}
+
+int rewb200_model_set_tensor_shard(rewb200_model* m, int64_t index, const float* host_local, const int64_t* local_shape,
+                                   const int64_t* offsets, int ndims) {
+  RB_REQUIRE(m && host_local && local_shape && offsets, "rewb200_model_set_tensor_shard: NULL argument");
+  int nd = 0, pdim = -1;
+  int64_t gs[4], ls[4], off[4];
+  RB_TRY(rewb200_model_tensor_layout(m, index, &nd, gs, ls, off, &pdim));
+  RB_REQUIRE(nd == ndims, "fromHostShards: shard rank " + std::to_string(ndims) + " does not match the tensor's " + std::to_string(nd));
+  int64_t numel = 1;
+  for (int i = 0; i < nd; ++i) {
+    RB_REQUIRE(local_shape[i] == ls[i] && offsets[i] == off[i],
+               "fromHostShards: tensor " + std::to_string(index) + " dim " + std::to_string(i) + ": this rank holds [" +
+                   std::to_string(off[i]) + ", " + std::to_string(off[i] + ls[i]) + "), the shard given covers [" +
+                   std::to_string(offsets[i]) + ", " + std::to_string(offsets[i] + local_shape[i]) + ")");
+    numel *= ls[i];
+  }
+  if (numel == 0) return REWB200_OK;
+  return set_tensor_impl(m, index, host_local, numel, true);
+}
+
+}  // extern "C"
+
+namespace rewb {
+namespace {
+
+// shard = false: `host` is the FULL logical tensor and the rank's block is cut out of it; shard = true: `host`
+// is exactly this rank's block (rewb200_model_tensor_layout), nothing else crosses the host interface.
+int set_tensor_impl(rewb200_model* m, int64_t index, const float* host, int64_t numel, bool shard) {
   RB_REQUIRE(!m->finalized, "model already finalized");
   RB_CUDA(cudaSetDevice(m->c->device));
   const rewb200_config& c = m->cfg;
   TensorRef r;
   RB_TRY(locate(m, index, &r));
   const int64_t d = c.d_model, hd = c.head_dim;
-  const int64_t NQ = (int64_t)c.n_heads * hd, NKV = (int64_t)c.n_kv_heads * hd;
-  const int tp = c.tp_size, rk = c.tp_rank;
+  const int tp = c.tp_size, rk = shard ? 0 : c.tp_rank;
+  const int64_t NQ = (int64_t)c.n_heads * hd / (shard ? tp : 1), NKV = (int64_t)c.n_kv_heads * hd / (shard ? tp : 1);
+  const int64_t VOC = (int64_t)c.vocab / (shard ? tp : 1);
   const bool bf = c.dtype == REWB200_BF16;
   auto expect = [&](int64_t n) -> int {
     RB_REQUIRE(numel == n, "tensor " + std::to_string(index) + ": expected " + std::to_string(n) + " elements, got " +
@@ -1177,15 +1354,15 @@ int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host,
     switch (r.slot) {
       case 0: return vec(m->ng, d, 0, d);
       case 1: return vec(m->nb, d, 0, d);
-      case 2: RB_TRY(expect(d * c.vocab)); return scatter(m, c.vocab, 0, rk * m->vocab_l, d, m->vocab_l, m->lm.w, true, m->vocab_l, m->vocab_l, m->vocab_l, 0);
-      default: return vec(m->lm.b, c.vocab, rk * m->vocab_l, m->vocab_l);
+      case 2: RB_TRY(expect(d * VOC)); return scatter(m, VOC, 0, rk * m->vocab_l, d, m->vocab_l, m->lm.w, true, m->vocab_l, m->vocab_l, m->vocab_l, 0);
+      default: return vec(m->lm.b, VOC, rk * m->vocab_l, m->vocab_l);
     }
   }
   LayerDev& L = m->layers[r.layer];
   const int64_t nq = m->nq, nkv = m->nkv, nqkv = m->nqkv, fl = L.ffn_local;
   // gate/up column mapping: bf16 interleaves groups of 8 (gate at +0, up at +8 of each 16); f32 concatenates.
   const int64_t ggran = bf ? 8 : fl, gstride = bf ? 16 : fl;
-  const int64_t F = (c.n_routed > 0 && c.first_dense > 0) ? c.first_dense : c.ffn;  // dense block width
+  const int64_t F = ((c.n_routed > 0 && c.first_dense > 0) ? c.first_dense : c.ffn) / (shard ? tp : 1);  // dense block width
   if (!(L.moe && r.slot >= 12)) switch (r.slot) {
     case 0: return vec(L.ln1g, d, 0, d);
     case 1: return vec(L.ln1b, d, 0, d);
@@ -1254,6 +1431,11 @@ int rewb200_model_set_tensor(rewb200_model* m, int64_t index, const float* host,
     }
   }
 }
+
+}  // namespace
+}  // namespace rewb
+
+extern "C" {
 
 int rewb200_model_init_random(rewb200_model* m, uint64_t seed, float std) {
   RB_REQUIRE(m, "rewb200_model_init_random: NULL model");
@@ -1463,7 +1645,7 @@ void rewb200_session_free(rewb200_session* s) {
   void* ptrs[] = {s->d_active, s->d_ids_prefill, s->block_table, s->d_pos, s->d_ids, s->d_next, s->d_out, s->d_step, s->x_res, s->xn, s->q,
                   s->attn, s->h, s->part, s->gu32, s->logits, s->attn_scratch, s->argmax_scratch, s->gather_scratch,
                   s->samp_hist, s->samp_hist_len, s->samp_steps, s->samp_keys, s->samp_work, s->samp_logprob, s->moe_logits, s->moe_topw, s->moe_topi, s->moe_ints,
-                  s->moe_send, s->moe_recv, s->moe_xs, s->moe_hs, s->moe_ys, s->moe_ret, s->moe_back, s->moe_tmp};
+                  s->moe_send, s->moe_recv, s->moe_xs, s->moe_hs, s->moe_ys, s->moe_ret, s->moe_back, s->moe_tmp, s->route_rec};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   if (s->h_ids) cudaFreeHost(s->h_ids);
@@ -1922,6 +2104,38 @@ int rewb200_session_profile_linears(rewb200_session* s, int iters, float* ms_per
 }
 
 int rewb200_session_graph_kernels(const rewb200_session* s) { return s ? s->graph_kernels : 0; }
+
+int rewb200_session_routing(rewb200_session* s, int moe_layer, int32_t* topi_out, int64_t rows) {
+  RB_REQUIRE(s && topi_out, "rewb200_session_routing: NULL argument");
+  RB_REQUIRE(s->route_rec != nullptr, "rewb200_session_routing: set option record_routing=1 before the session's first forward");
+  int n_moe = 0;
+  for (const LayerDev& L : s->m->layers) n_moe += L.moe ? 1 : 0;
+  RB_REQUIRE(moe_layer >= 0 && moe_layer < n_moe && rows == s->route_rows, "rewb200_session_routing: layer or row count does not match the last forward");
+  Ctx* c = s->m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_CUDA(cudaStreamSynchronize(c->stream));
+  RB_CUDA(cudaMemcpy(topi_out, s->route_rec + (size_t)moe_layer * s->rows_cap * s->m->cfg.top_k,
+                     (size_t)rows * s->m->cfg.top_k * sizeof(int), cudaMemcpyDeviceToHost));
+  return REWB200_OK;
+}
+
+int rewb200_session_trace_step(rewb200_session* s, float* ms_by_category, int n) {
+  RB_REQUIRE(s && ms_by_category && n >= TC_COUNT, "rewb200_session_trace_step: needs room for 11 categories");
+  RB_REQUIRE(!s->paged && s->host_pos > 0 && s->host_pos + 1 <= s->max_len, "rewb200_session_trace_step: feed a prompt first");
+  rewb200_model* m = s->m;
+  Ctx* c = m->c;
+  RB_CUDA(cudaSetDevice(c->device));
+  RB_TRY(ensure_acts(s, std::max<int64_t>(s->B, s->rows_cap), s->B));
+  Trace tr;
+  FwdOpts o;
+  o.S = 1;
+  o.trace = &tr;
+  RB_TRY(enqueue_forward(s, o));
+  RB_TRY(tr.finish(ms_by_category));
+  s->host_pos += 1;
+  for (int i = TC_COUNT; i < n; ++i) ms_by_category[i] = 0.f;
+  return ctx_check_status(c);
+}
 
 int rewb200_model_forward_all(rewb200_session* s, const int32_t* ids, int S, int64_t offset, int causal,
                               float* logits_out) {

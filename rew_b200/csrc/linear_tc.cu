@@ -470,6 +470,10 @@ struct PersistCfg {
 // the device: token tiles are numbered group by group (a group's last tile may be ragged), and a tile loads a
 // full box of rows (the surplus belongs to the next group or is out of range) but stores only its own.
 constexpr int kMaxGroups = 256;
+constexpr int kMaxPersistCtas = 256;
+// Per-CTA list "token tiles ahead of each group" of the grouped launches.  The kernel's shared memory is full
+// (four 48 KB stages, two staging buffers), so each CTA keeps its copy in global memory, where it stays in L1.
+static __device__ int g_first_tile[kMaxPersistCtas][kMaxGroups + 1];
 
 template <bool GROUPED>
 __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_constant__ CUtensorMap tmW,
@@ -477,7 +481,7 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
                                                                  int tiles_n, int tiles_m) {
   using C = PersistCfg;
   constexpr int TN = C::TN;
-  __shared__ int s_first_tile[GROUPED ? kMaxGroups + 1 : 1];  // token tiles ahead of each group
+  int* const s_first_tile = g_first_tile[blockIdx.x % kMaxPersistCtas];  // this CTA's copy (grouped launches only)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stg_base = smem + C::STAGES * C::STAGE_BYTES;
@@ -498,6 +502,7 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
         acc += (a.row_offsets[g + 1] - a.row_offsets[g] + TN - 1) / TN;
       }
       s_first_tile[a.groups] = acc;
+      __threadfence_block();
     }
     __syncthreads();
     tiles_m = s_first_tile[a.groups];
@@ -798,7 +803,7 @@ int linear_tc_grouped_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, 
   const int tiles_n = (int)((plan.N + BM - 1) / BM);
   // at most ceil(M / TN) + groups token tiles exist; one CTA per SM walks them
   const int64_t max_tiles = (int64_t)tiles_n * ((M + PersistCfg::TN - 1) / PersistCfg::TN + plan.groups);
-  const int ctas = (int)std::min<int64_t>(max_tiles, c->sm_count);
+  const int ctas = (int)std::min<int64_t>(std::min<int64_t>(max_tiles, c->sm_count), kMaxPersistCtas);
   RB_CUDA(launch_k(linear_tc_persist_kernel<true>, dim3((unsigned)ctas), dim3(192), (size_t)PersistCfg::SMEM, c->stream, c->use_pdl,
                    plan.tmW, tmX, a, tiles_n, 0));
   ++g_launch_total;

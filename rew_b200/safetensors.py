@@ -41,18 +41,23 @@ def read_safetensors(path):
             continue
         start, end = info["data_offsets"]
         shape = tuple(info["shape"])
+        if not (0 <= start <= end <= len(data)):
+            raise ValueError("safetensors: tensor %s has offsets outside the file" % name)
         buf = data[start:end]
         dt = info["dtype"]
+        itemsize = 2 if dt == "BF16" else (np.dtype(_DTYPES[dt]).itemsize if dt in _DTYPES else None)
+        if itemsize is None:
+            raise ValueError("unsupported safetensors dtype: " + dt)
+        numel = int(np.prod(shape, dtype=np.int64)) if shape else 1
+        if end - start != numel * itemsize:      # every dtype: the byte range must hold exactly the declared shape
+            raise ValueError("safetensors: tensor %s has inconsistent offsets (%d bytes for shape %r of %s)"
+                             % (name, end - start, shape, dt))
         if dt == "BF16":
             arr = from_bf16_bits(np.frombuffer(buf, dtype=np.uint16)).reshape(shape)
-        elif dt in _DTYPES:
+        else:
             arr = np.frombuffer(buf, dtype=_DTYPES[dt]).reshape(shape)
             if dt in ("F16", "F64"):
                 arr = arr.astype(np.float32)
-        else:
-            raise ValueError("unsupported safetensors dtype: " + dt)
-        if arr.size * arr.itemsize != (end - start) and dt != "BF16" and dt not in ("F16", "F64"):
-            raise ValueError("safetensors: tensor %s has inconsistent offsets" % name)
         out[name] = arr
     return out
 
@@ -89,6 +94,16 @@ def llama_config_from_hf(path_or_dict, dtype=None, **overrides):
             node = json.load(f)
     heads = int(node.get("num_attention_heads", 32))
     hidden = int(node.get("hidden_size", 4096))
+    # toLlamaConfig reads neither key; a checkpoint that sets them means another model than the one built here
+    # (Llama-3.1 style frequency scaling changes every RoPE angle; an explicit head_dim decouples it from
+    # hidden / heads), so loading it silently would give wrong logits.
+    scaling = node.get("rope_scaling")
+    if scaling is not None and not (isinstance(scaling, dict) and scaling.get("rope_type", scaling.get("type")) in (None, "default")):
+        raise ValueError("config.json: rope_scaling %r is not supported (initRotaryPositionEncoding has plain RoPE only, "
+                         "src/rew/nn/rope.nim:112-145)" % (scaling,))
+    if node.get("head_dim") is not None and int(node["head_dim"]) != hidden // heads:
+        raise ValueError("config.json: head_dim %r differs from hidden_size / num_attention_heads = %d, which "
+                         "initLlamaConfig assumes" % (node["head_dim"], hidden // heads))
     kw = dict(vocab=int(node.get("vocab_size", 32000)), d_model=hidden, n_layers=int(node.get("num_hidden_layers", 32)),
               n_heads=heads, n_kv_heads=int(node.get("num_key_value_heads", heads)), head_dim=hidden // heads,
               ffn=int(node.get("intermediate_size", 11008)), max_seq=int(node.get("max_position_embeddings", 2048)),

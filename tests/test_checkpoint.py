@@ -65,6 +65,74 @@ def test_load_errors(tmp_path):
         CK.load_checkpoint(str(tmp_path / "c"), cfg)
 
 
+def _hand_written_sharded_checkpoint(path, cfg, t, leaf, shards):
+    """A checkpoint written by hand in the layout Runtime.save produces (src/rew/train/runtime.nim:279-321):
+    manifest entries with "sharded", "shards": [{"index", "process", "file", "shape", "offsets"}], not by this
+    module's own writer.  `shards`: (file index, offsets, array) per shard of canonical tensor `leaf`."""
+    os.makedirs(path)
+    leaves = CK.pytree_leaves(cfg)
+    by_name = dict(zip([n for n, _ in W.tensor_specs(cfg)], t))
+    cos_t, sin_t = CK.rope_tables(cfg.head_dim, cfg.max_seq, cfg.theta)
+    entries = []
+    for i, name in enumerate(leaves):
+        arr = cos_t if name == CK.ROPE_COS else sin_t if name == CK.ROPE_SIN else by_name[name]
+        if name == leaf:
+            recs = []
+            for k, offs, part in shards:
+                fname = "tensor_%d_shard_%d.npy" % (i, k)
+                np.save(os.path.join(path, fname), np.ascontiguousarray(part, np.float32))
+                recs.append({"index": k, "process": 0, "file": fname, "shape": list(part.shape), "offsets": list(offs)})
+            entries.append({"index": i, "dtype": "float32", "shape": list(arr.shape), "sharded": True,
+                            "sharding_key": "partitioned", "shards": recs})
+        else:
+            np.save(os.path.join(path, "tensor_%d.npy" % i), arr)
+            entries.append({"index": i, "file": "tensor_%d.npy" % i, "dtype": "float32", "shape": list(arr.shape), "sharded": False})
+    with open(os.path.join(path, "manifest.json"), "w") as f:
+        json.dump({"tensors": entries, "leaf_count": len(leaves)}, f)
+
+
+def test_sharded_leaf_coverage_is_checked(tmp_path):
+    """Duplicated, overlapping, missing or out-of-range shards are errors, not uninitialised weights."""
+    cfg = W.tiny_llama()
+    t = W.init_weights(cfg, seed=3)
+    leaf = "model.layers.0.selfAttn.qProj.weight"                     # [256, 256]
+    w = dict(zip([n for n, _ in W.tensor_specs(cfg)], t))[leaf]
+    halves = [(0, (0, 0), w[:, :128]), (1, (0, 128), w[:, 128:])]
+    _hand_written_sharded_checkpoint(str(tmp_path / "ok"), cfg, t, leaf, halves)
+    back = CK.load_checkpoint(str(tmp_path / "ok"), cfg)
+    assert all(np.array_equal(a, b) for a, b in zip(t, back))
+    # the same offsets twice: element counts add up to the full size, the right half is never written
+    _hand_written_sharded_checkpoint(str(tmp_path / "dup"), cfg, t, leaf, [(0, (0, 0), w[:, :128]), (1, (0, 0), w[:, :128])])
+    with pytest.raises(ValueError, match="overlap"):
+        CK.load_checkpoint(str(tmp_path / "dup"), cfg)
+    _hand_written_sharded_checkpoint(str(tmp_path / "gap"), cfg, t, leaf, halves[:1])
+    with pytest.raises(ValueError, match="do not cover"):
+        CK.load_checkpoint(str(tmp_path / "gap"), cfg)
+    _hand_written_sharded_checkpoint(str(tmp_path / "oob"), cfg, t, leaf, [halves[0], (1, (0, 200), w[:, 128:])])
+    with pytest.raises(ValueError, match="outside its shape"):
+        CK.load_checkpoint(str(tmp_path / "oob"), cfg)
+
+
+def test_block_reader_opens_only_the_shards_a_rank_needs(tmp_path):
+    """A leaf saved as 4 column shards: the block of tensor-parallel rank 1 of 4 is one file; of rank 1 of 2
+    two files; a row block of a plain leaf comes out of a memory-mapped read."""
+    cfg = W.tiny_llama()
+    t = W.init_weights(cfg, seed=3, trivial_affine=False)
+    by = dict(zip([n for n, _ in W.tensor_specs(cfg)], t))
+    q, o = "model.layers.0.selfAttn.qProj.weight", "model.layers.1.selfAttn.outProj.weight"
+    CK.save_checkpoint(str(tmp_path / "c"), cfg, t, shard_leaves={q: (1, 4)})
+    r = CK.BlockReader(str(tmp_path / "c"), cfg)
+    got = r.read_block(q, (256, 64), (0, 64))
+    assert np.array_equal(got, by[q][:, 64:128]) and r.files_read == ["tensor_1_shard_1.npy"]
+    r.files_read.clear()
+    got = r.read_block(q, (256, 128), (0, 128))
+    assert np.array_equal(got, by[q][:, 128:]) and r.files_read == ["tensor_1_shard_2.npy", "tensor_1_shard_3.npy"]
+    got = r.read_block(o, (128, 256), (128, 0))
+    assert np.array_equal(got, by[o][128:])
+    with pytest.raises(ValueError, match="lacks tensor"):
+        r.read_block("nope", (1,), (0,))
+
+
 @pytest.mark.gpu
 def test_model_from_checkpoint_generates_the_golden_ids(tmp_path):
     from rew_b200 import _lib, api

@@ -166,3 +166,37 @@ def test_sharded_snapshot_directory_and_hf_config(tmp_path, orc):
         ST.read_safetensors_dir(str(snap))
     with pytest.raises(FileNotFoundError):
         ST.read_safetensors_dir(str(tmp_path))
+
+
+def test_config_keys_that_change_the_model_are_refused():
+    """toLlamaConfig (src/rew/hf/hub.nim:370-382) ignores rope_scaling and head_dim; a checkpoint that sets them
+    would load and then compute another model's logits, so the loader refuses instead."""
+    base = {"num_attention_heads": 8, "hidden_size": 512}
+    with pytest.raises(ValueError, match="rope_scaling"):
+        ST.llama_config_from_hf(dict(base, rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}))
+    with pytest.raises(ValueError, match="rope_scaling"):
+        ST.llama_config_from_hf(dict(base, rope_scaling={"type": "linear", "factor": 2.0}))
+    with pytest.raises(ValueError, match="head_dim"):
+        ST.llama_config_from_hf(dict(base, head_dim=128))
+    assert ST.llama_config_from_hf(dict(base, rope_scaling=None, head_dim=64)).head_dim == 64
+    assert ST.llama_config_from_hf(dict(base, rope_scaling={"rope_type": "default"})).head_dim == 64
+
+
+def test_byte_ranges_are_checked_for_every_dtype(tmp_path):
+    import json
+    import struct
+    for dt, itemsize in (("BF16", 2), ("F16", 2), ("F64", 8), ("F32", 4)):
+        header = {"w": {"dtype": dt, "shape": [4, 4], "data_offsets": [0, 16 * itemsize - itemsize]}}  # one element short
+        hj = json.dumps(header).encode()
+        hj += b" " * ((8 - len(hj) % 8) % 8)
+        path = tmp_path / ("bad_%s.safetensors" % dt)
+        path.write_bytes(struct.pack("<Q", len(hj)) + hj + b"\0" * (16 * itemsize))
+        with pytest.raises(ValueError, match="inconsistent offsets"):
+            ST.read_safetensors(str(path))
+    header = {"w": {"dtype": "F32", "shape": [4], "data_offsets": [0, 64]}}
+    hj = json.dumps(header).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    (tmp_path / "oob.safetensors").write_bytes(struct.pack("<Q", len(hj)) + hj + b"\0" * 16)
+    with pytest.raises(ValueError, match="outside the file"):
+        ST.read_safetensors(str(tmp_path / "oob.safetensors"))

@@ -52,7 +52,26 @@ def main():
         t = W.init_weights(full, seed=9, std=0.05, trivial_affine=False)
         if dtype == _lib.BF16:
             t = [W.bf16_round(a) if a.ndim == 2 else a for a in t]
-        model = api.CausalLM(cfg).load(t)
+        if name == "f32":
+            model = api.CausalLM(cfg).load(t)          # full tensors in, the library cuts out this rank's blocks
+        else:
+            # shard -> rank: only this rank's block of every tensor crosses the interface (shardLayout's block rule)
+            def block(i, tname, g, l, o):
+                return t[i][tuple(slice(a, a + n) for a, n in zip(o, l))]
+            model = api.CausalLM(cfg)
+            g, l, o, pdim = model.tensor_layout(2)     # layer 0 qProj.weight: column-parallel
+            assert pdim == 1 and l == (g[0], g[1] // world) and o == (0, rank * g[1] // world), (g, l, o, pdim)
+            g, l, o, pdim = model.tensor_layout(8)     # layer 0 outProj.weight: row-parallel
+            assert pdim == 0 and l == (g[0] // world, g[1]) and o == (rank * g[0] // world, 0), (g, l, o, pdim)
+            if world > 1:  # a block at another rank's offsets is refused
+                import ctypes as C
+                wrong = np.zeros(l, np.float32)
+                off = [((rank + 1) % world) * l[0], 0]
+                st = _lib.lib().rewb200_model_set_tensor_shard(model._h, 8, wrong.ctypes.data_as(_lib.F32P), (C.c_int64 * 2)(*l),
+                                                               (C.c_int64 * 2)(*off), 2)
+                assert st != 0 and b"this rank holds" in _lib.lib().rewb200_last_error()
+            model.free()
+            model = api.CausalLM(cfg).load_shards(block)
         # 60 prompt rows: every all-reduce of the step is the fused one; 120 rows: the prefill goes through NCCL
         # (bf16 payload for the bf16 model) and only the decode steps are fused
         for tag, plen in (("", 20), ("_long", 40)):
