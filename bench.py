@@ -394,7 +394,7 @@ def sharded_check(rank, world, pg, kind):
                     theta=500000.0, dtype=_lib.BF16, mask_kind=1)
         shard = dict(tp_rank=rank, tp_size=world)
         prompts = {"fused": np.random.default_rng(5).integers(0, 1024, size=(2, 16)).astype(np.int32),
-                   "nccl_prefill": np.random.default_rng(6).integers(0, 1024, size=(4, 24)).astype(np.int32)}
+                   "twoshot_prefill": np.random.default_rng(6).integers(0, 1024, size=(4, 24)).astype(np.int32)}
     else:
         base = dict(vocab=512, d_model=256, n_layers=3, n_heads=4, n_kv_heads=4, head_dim=64, ffn=384, max_seq=128,
                     theta=10000.0, eps=1e-6, n_routed=8, n_shared=2, top_k=3, moe_ffn=128, first_dense=384,
@@ -478,7 +478,7 @@ def main():
         run_reference(args, wl, rank, world)
         return
 
-    if world > 1 and "NCCL_DEBUG" not in os.environ:
+    if world > 1 and os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "WARN"):
         # keep NCCL's communicator-init lines ("... rank r nranks n ... Init COMPLETE") in the run's log, off stdout
         os.environ["NCCL_DEBUG"] = "INFO"
         os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
@@ -502,7 +502,10 @@ def main():
     if world > 1 and (split or parallel in ("tp", "ep")):
         moe = W.deepseek_v2_lite()
         need_a2a = a2a_bytes_for(moe, (WORKLOADS["moe_b64"]["batch"] // world) * WORKLOADS["moe_b64"]["prompt"], world)
-        comm = Comm(api, pg, rank, world, 64 * 8192 * 2, need_a2a if (split or parallel == "ep") else 0)
+        l70 = WORKLOADS["l70_b16"]
+        need_tp = 2 * l70["batch"] * l70["prompt"] * 8192 * 2     # scatter + gather buffer of the two-shot prefill all-reduce
+        bulk = max(need_a2a if (split or parallel == "ep") else 0, need_tp if (split or parallel == "tp") else 0)
+        comm = Comm(api, pg, rank, world, 64 * 8192 * 4, bulk)   # one-shot slots: 64 rows of d_model 8192 as flagged lines
 
     r = run_model(args, args.workload, rank, local_rank, world, pg, K, Wm, True, True)
     cfg = r["cfg"]

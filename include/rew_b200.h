@@ -73,6 +73,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            "prefix" from 4 ranks on; prefix = NCCL, pair counts first and then only the
  *                                            occupied prefix of every slot array (steps of 64+ pairs outside a captured
  *                                            graph); capacity = NCCL, always the worst-case capacity
+ *   "tp_allreduce" = "heap" | "nccl"         tensor-parallel steps of more than 64 rows (prefill): two-shot all-reduce over
+ *                                            the peer heap when its bulk region holds the step (default), or NCCL always
  *   "record_routing" = "0" | "1"             test aid: sessions created afterwards keep every MoE layer's top-k expert ids
  *                                            of their last forward for rewb200_session_routing
  *   "inject_alloc_fail" = "n"                test hook: the n-th activation-buffer allocation from now fails on the host
@@ -403,16 +405,21 @@ int rewb200_comm_alltoall(int slot, const void* send_device, void* recv_device, 
  * peer pointer).  Each rank allocates its heap and exports a 64-byte CUDA IPC handle; after the host has
  * gathered every rank's handle (rank order, world*64 bytes), attach maps the peers.  Sessions created
  * afterwards use it for
- *   - the tensor-parallel all-reduce of steps up to 64 rows with rows*d_model*(2 for bf16 models, 4 for
- *     f32) <= allreduce_bytes: fused into the residual+norm kernel (each CTA pushes its partial to every
- *     rank, raises a flag, waits with a bound for the peers' flags and sums the partials in rank order;
- *     src/rew/ops/distributed.nim:62-83).  Larger steps go through NCCL;
+ *   - the tensor-parallel all-reduce (src/rew/ops/distributed.nim:62-83).  Steps up to 64 rows with
+ *     rows*d_model*(4 for bf16 models, 8 for f32) <= allreduce_bytes: fused into the residual+norm kernel (each
+ *     thread stores its partial into every rank's heap as 16-byte lines that carry the payload and a flag
+ *     together, polls with a bound for the peers' lines in its own heap and sums the
+ *     partials in rank order).  Larger steps whose partial fits twice into alltoall_bytes: two-shot (every rank
+ *     stores slice p of its partial into rank p's heap, rank p stores the sum of the slices into every rank's
+ *     heap).  Anything else goes through NCCL (bf16 payload on bf16 models);
  *   - the expert-parallel all-to-all (src/rew/ops/distributed.nim:106-128) whenever the slot arrays of a
  *     step (pairs*world rows of d_model activations, their expert ids and the f32 results) fit into
  *     alltoall_bytes: dispatch and return kernels store the occupied rows straight into the owner's heap
  *     and hand over the pair counts on the device, so neither a count exchange through the host nor
  *     padding crosses NVLink.  Larger steps go through NCCL send/recv.
- * Either size may be 0.  The heap holds 16 KiB + 2*world*allreduce_bytes + alltoall_bytes. */
+ * Either size may be 0 (alltoall_bytes is one bulk region that serves whichever of the two a model uses: a
+ * model is never both tensor- and expert-parallel).  The heap holds 16 KiB + 2*world*allreduce_bytes +
+ * alltoall_bytes. */
 int rewb200_comm_peer_alloc(int slot, int64_t allreduce_bytes, int64_t alltoall_bytes, void* handle64);
 int rewb200_comm_peer_attach(int slot, const void* handles_all);
 /* Free every session of the slot first: a captured decode graph keeps the communicator in use and

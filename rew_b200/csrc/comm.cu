@@ -128,14 +128,13 @@ int comm_alltoallv_rows(Ctx* c, int slot, const void* send, void* recv, size_t p
 // ---- peer heap: exchange memory for the fused all-reduce and the expert-parallel all-to-all ----------
 // One cudaMalloc per rank, exported with CUDA IPC and mapped by every other rank of the node:
 //   [0, 16 KiB)   header: epoch counter (int 0), all-to-all epoch (int 1), arrival counters of the all-to-all
-//                 kernels (ints 2, 3); at 256 the all-reduce flags [kPeerChunks][8]; at 256 + 8 KiB the
-//                 all-to-all cells: pair counts [8], dispatch flags [8], return flags [8]
+//                 kernels (ints 2, 3); at 256 the all-to-all cells: pair counts [8], dispatch flags [8],
+//                 return flags [8]
 //   then          two alternating all-reduce exchange buffers of world x buf_bytes each
 //   then          the all-to-all region (a2a_bytes)
 // Peers are written with plain stores and never read; every rank reads only its own memory.
 constexpr size_t kHeapHeader = 16384;
-constexpr size_t kHeapFlagsOff = 256;
-constexpr size_t kHeapA2aCellsOff = 256 + (size_t)kPeerChunks * 8 * sizeof(int);
+constexpr size_t kHeapA2aCellsOff = 256;
 
 struct PeerHeap {
   void* local = nullptr;
@@ -146,7 +145,6 @@ struct PeerHeap {
 static PeerHeap g_heap[16];
 
 static void heap_fill(PeerInfo* info, int r, char* base, bool own) {
-  info->flags[r] = (int*)(base + kHeapFlagsOff);
   const size_t ar = (size_t)info->world * info->buf_bytes;
   info->bufs[0][r] = base + kHeapHeader;
   info->bufs[1][r] = base + kHeapHeader + ar;
@@ -192,7 +190,7 @@ int rewb200_comm_peer_alloc(int slot, int64_t allreduce_bytes, int64_t alltoall_
   PeerHeap& h = g_heap[slot];
   const size_t total = kHeapHeader + 2 * (size_t)g_comm[slot].world * (size_t)allreduce_bytes + (size_t)alltoall_bytes;
   RB_CUDA(cudaMalloc(&h.local, total));
-  RB_CUDA(cudaMemset(h.local, 0, kHeapHeader));
+  RB_CUDA(cudaMemset(h.local, 0, kHeapHeader + 2 * (size_t)g_comm[slot].world * (size_t)allreduce_bytes));  // flag 0 = no data yet
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are 64 bytes");
   cudaIpcMemHandle_t ih;
   RB_CUDA(cudaIpcGetMemHandle(&ih, h.local));

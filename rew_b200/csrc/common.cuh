@@ -63,6 +63,7 @@ struct Ctx {
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
+  bool tp_twoshot = true;       // tensor-parallel steps above 64 rows: sum over the peer heap (two-shot) instead of NCCL
   bool record_routing = false;  // sessions keep every MoE layer's top-k expert ids of their last forward (a test aid)
   int inject_alloc_fail = 0;  // test hook: the n-th activation allocation from now fails on the host
   int option_epoch = 0;      // bumped by rewb200_set_option; captured graphs from older epochs are rebuilt
@@ -228,22 +229,26 @@ struct NormArgs {
   int vocab;
   int* status;
   int partial_bf16;       // the partial slabs hold bf16 instead of f32 (a tensor-parallel sum that travelled as bf16)
-  // One-shot tensor-parallel all-reduce fused into this kernel (n_peers > 0), push style: a CTA sums its
-  // columns of the local split-K slabs, stores that partial (payload dtype) into slot `my_rank` of EVERY
-  // peer's exchange buffer with plain peer stores, raises its chunk's flag on every peer (release, system
-  // scope), waits (bounded) until the same chunk's flags of all peers have arrived in its OWN flag array, and
-  // then reads the peers' partials from LOCAL memory and adds them in rank order, so every rank computes
-  // the same bits.  Flag values are `*epoch + barrier_offset`, increasing from one all-reduce to the next.
+  // The partial is the gather buffer of the two-shot tensor-parallel all-reduce (Tp2Args), written by the peers:
+  // wait (bounded) until cell r of wait_cells has reached *wait_epoch + wait_offset for every rank r < wait_n.
+  const int* wait_cells;
+  int wait_n;
+  const int* wait_epoch;
+  int wait_offset;
+  // One-shot tensor-parallel all-reduce fused into this kernel (n_peers > 0), push style: a thread sums its
+  // columns of the local split-K slabs and stores that partial into slot `my_rank` of EVERY peer's exchange
+  // buffer with plain peer stores, as 16-byte lines {payload, flag, payload, flag} (flag = `*epoch +
+  // barrier_offset`, a value no earlier all-reduce has used), then polls (bounded) the same lines of the other
+  // ranks' slots in its OWN memory until they carry that flag, and adds the partials in rank order, so every
+  // rank computes the same bits.  Payload and flag arrive together: no fence and no flag round trip.
   int n_peers;
   int my_rank;
   int payload_bf16;       // partials cross NVLink as bf16 (bf16 models) or f32
-  void* peer_buf[8];      // rank r's exchange buffer of this all-reduce: [world][slot_elems] payload elements
-  int* peer_flags[8];     // rank r's flag array: [kPeerChunks][8] ints, cell (chunk, writer rank)
-  int64_t slot_elems;     // payload elements between two writers' slots
+  void* peer_buf[8];      // rank r's exchange buffer of this all-reduce: [world][slot_lines] 16-byte lines
+  int64_t slot_lines;     // lines between two writers' slots
   const int* epoch;       // device counter, advanced once per forward on every rank alike
   int barrier_offset;
 };
-constexpr int kPeerChunks = 256;  // CTAs of one fused all-reduce launch (rows * 4 on the cluster kernel)
 int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows);
 
 struct KvLayout {
@@ -313,7 +318,6 @@ struct PeerInfo {
   int world = 0, rank = 0;
   size_t buf_bytes = 0;        // capacity of ONE writer's slot; an exchange buffer holds `world` of them
   char* bufs[2][8] = {};       // [which][rank]: the two alternating exchange buffers of every rank (own rank: local)
-  int* flags[8] = {};          // [rank]: flag arrays, kPeerChunks x 8 ints
   int* epoch = nullptr;        // local device counter
   char* a2a[8] = {};           // [rank]: the expert-parallel all-to-all region of every rank (nullptr without one)
   size_t a2a_bytes = 0;
@@ -335,6 +339,26 @@ struct A2aArgs {
   int offset;
   int* status;
 };
+// Two-shot tensor-parallel all-reduce of a [rows, d] partial over the peer heap, for steps too large for the
+// fused one-shot exchange (prefill): (1) every rank stores slice p (columns [p*d/world, (p+1)*d/world)) of its
+// partial into rank p's scatter buffer, (2) rank p adds the world slices in rank order and stores the sum into
+// EVERY rank's gather buffer, (3) the residual+norm kernel reads the local gather buffer.  Each rank moves
+// 2*(world-1)/world of the partial over NVLink instead of (world-1) times all of it, and every rank reads the
+// same sums.  Regions and cells are those of the expert-parallel all-to-all (a model is never both).
+struct Tp2Args {
+  int world, my_rank;
+  int* cells[8];       // rank r's cells: [8 unused] | scatter flags [8] | gather flags [8], indexed by writer rank
+  char* region[8];     // rank r's bulk region: scatter buffer [world][rows][d/world], then the gather buffer [rows][d]
+  int64_t off_gather;  // byte offset of the gather buffer
+  int* arrive;         // two local arrival counters, zero between launches
+  const int* epoch;    // local device counter; flag value = *epoch + offset
+  int offset;
+  int* status;
+  const void* partial; // this rank's [rows][d] partial, payload dtype
+  int64_t rows, d;
+  int payload_bf16;
+};
+int tp2_allreduce_launch(Ctx* c, const Tp2Args& a);
 // nullptr when no peer heap has been attached for the slot
 const PeerInfo* comm_peer_info(int slot);
 

@@ -149,12 +149,14 @@ __device__ __forceinline__ float4 partial_sum4(const NormArgs& a, int64_t idx) {
   if (a.partial_bf16) {
     const bf16* pp = reinterpret_cast<const bf16*>(a.partial) + idx;
     for (int s = 0; s < a.nsplit; ++s) {
-      const float4 q = Vec4<bf16>::load(pp + s * a.split_stride);
-      p.x += q.x; p.y += q.y; p.z += q.z; p.w += q.w;
+      const uint2 u = __ldcg(reinterpret_cast<const uint2*>(pp + s * a.split_stride));  // may have been written by a peer
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+      p.x += __low2float(lo); p.y += __high2float(lo); p.z += __low2float(hi); p.w += __high2float(hi);
     }
     return p;
   }
   const float* pp = a.partial + idx;
+  if (a.wait_n > 0) return __ldcg(reinterpret_cast<const float4*>(pp));  // one slab, written by the peers
   int s = 0;
   for (; s + 4 <= a.nsplit; s += 4) {
     const float4 p0 = *reinterpret_cast<const float4*>(pp + (s + 0) * a.split_stride);
@@ -173,24 +175,50 @@ __device__ __forceinline__ float4 partial_sum4(const NormArgs& a, int64_t idx) {
   return p;
 }
 
-// Tensor-parallel all-reduce of this CTA's columns (see NormArgs): p[c] holds this rank's partial of the
-// float4 at element offset idx[c] (idx[c] < 0: none) and comes back as the sum over all ranks, added in
-// rank order from the values that crossed NVLink, so every rank ends up with the same bits.  `chunk`
-// numbers the CTA; the same CTA of every rank handles the same columns.
+// One 16-byte line of the one-shot exchange: two 4-byte payload words, each followed by the flag of this
+// all-reduce ({w0, flag, w1, flag}).  A line is stored with one 16-byte store; should the link split it, each
+// 8-byte half still carries its own flag, so a reader that sees both flags has both words.
+__device__ __forceinline__ void ll_store(void* line, uint32_t w0, uint32_t w1, uint32_t flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(line), "r"(w0), "r"(flag), "r"(w1), "r"(flag) : "memory");
+}
+// Polls a line of this GPU's own memory until both flags match; bounded by 2 s, and cut short once any wait
+// on this GPU has already timed out.
+__device__ __forceinline__ uint2 ll_poll(const void* line, uint32_t flag, int* status) {
+  uint32_t x, fx, y, fy;
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(x), "=r"(fx), "=r"(y), "=r"(fy) : "l"(line) : "memory");
+    if (fx == flag && fy == flag) break;
+    if ((it & 255u) == 255u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > 2000000000ull || *reinterpret_cast<volatile int*>(status) == KS_PEER_TIMEOUT) {
+        atomicExch(status, KS_PEER_TIMEOUT);
+        break;
+      }
+    }
+  }
+  return make_uint2(x, y);
+}
+
+// Tensor-parallel all-reduce of this thread's columns (see NormArgs): p[c] holds this rank's partial of the
+// float4 at element offset idx[c] (idx[c] < 0: none) and comes back as the sum over all ranks, added in rank
+// order from the values that crossed NVLink, so every rank ends up with the same bits.  Payload and flag
+// travel in the same store (no fence, no separate flag round trip): bf16 payload = one line per float4, f32
+// payload = two.  The same thread of every rank handles the same columns, so each thread waits only for
+// the lines it reads itself.
 template <int NCH>
-__device__ __forceinline__ void tp_exchange4(const NormArgs& a, float4 (&p)[NCH], const int64_t (&idx)[NCH], int chunk) {
-  const int target = *a.epoch + a.barrier_offset;
+__device__ __forceinline__ void tp_exchange4(const NormArgs& a, float4 (&p)[NCH], const int64_t (&idx)[NCH]) {
+  const uint32_t flag = (uint32_t)(*a.epoch + a.barrier_offset);
+  const int64_t mine = (int64_t)a.my_rank * a.slot_lines;
   if (a.payload_bf16) {
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       if (idx[c] < 0) continue;
-      uint2 u;
-      u.x = pack_bf16(p[c].x, p[c].y);
-      u.y = pack_bf16(p[c].z, p[c].w);
+      const uint32_t w0 = pack_bf16(p[c].x, p[c].y), w1 = pack_bf16(p[c].z, p[c].w);
       for (int r = 0; r < a.n_peers; ++r)
-        if (r != a.my_rank)
-          *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.peer_buf[r]) + (int64_t)a.my_rank * a.slot_elems + idx[c]) = u;
-      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        if (r != a.my_rank) ll_store(reinterpret_cast<uint4*>(a.peer_buf[r]) + mine + (idx[c] >> 2), w0, w1, flag);
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&w0), hi = *reinterpret_cast<const __nv_bfloat162*>(&w1);
       p[c] = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));  // what the peers see
     }
   } else {
@@ -198,15 +226,14 @@ __device__ __forceinline__ void tp_exchange4(const NormArgs& a, float4 (&p)[NCH]
     for (int c = 0; c < NCH; ++c) {
       if (idx[c] < 0) continue;
       for (int r = 0; r < a.n_peers; ++r)
-        if (r != a.my_rank)
-          *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.peer_buf[r]) + (int64_t)a.my_rank * a.slot_elems + idx[c]) = p[c];
+        if (r != a.my_rank) {
+          uint4* line = reinterpret_cast<uint4*>(a.peer_buf[r]) + mine + (idx[c] >> 1);
+          ll_store(line, __float_as_uint(p[c].x), __float_as_uint(p[c].y), flag);
+          ll_store(line + 1, __float_as_uint(p[c].z), __float_as_uint(p[c].w), flag);
+        }
     }
   }
-  __syncthreads();
-  if ((int)threadIdx.x < a.n_peers && (int)threadIdx.x != a.my_rank)
-    peer_flag_release(a.peer_flags[threadIdx.x] + chunk * 8 + a.my_rank, target);
-  peer_flags_wait(a.peer_flags[a.my_rank] + chunk * 8, 1, a.n_peers, a.my_rank, target, a.status);
-  const char* mine = reinterpret_cast<const char*>(a.peer_buf[a.my_rank]);
+  const uint4* local = reinterpret_cast<const uint4*>(a.peer_buf[a.my_rank]);
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
     if (idx[c] < 0) continue;
@@ -215,11 +242,13 @@ __device__ __forceinline__ void tp_exchange4(const NormArgs& a, float4 (&p)[NCH]
       float4 q = p[c];
       if (r != a.my_rank) {
         if (a.payload_bf16) {
-          const uint2 u = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(mine) + (int64_t)r * a.slot_elems + idx[c]));
+          const uint2 u = ll_poll(local + (int64_t)r * a.slot_lines + (idx[c] >> 2), flag, a.status);
           const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
           q = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
         } else {
-          q = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(mine) + (int64_t)r * a.slot_elems + idx[c]));
+          const uint4* line = local + (int64_t)r * a.slot_lines + (idx[c] >> 1);
+          const uint2 u0 = ll_poll(line, flag, a.status), u1 = ll_poll(line + 1, flag, a.status);
+          q = make_float4(__uint_as_float(u0.x), __uint_as_float(u0.y), __uint_as_float(u1.x), __uint_as_float(u1.y));
         }
       }
       t.x += q.x; t.y += q.y; t.z += q.z; t.w += q.w;
@@ -233,6 +262,7 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
   __shared__ float red[33];
   pdl_launch_dependents();
   pdl_wait();
+  if (a.wait_n > 0) peer_flags_wait(a.wait_cells, 1, a.wait_n, -1, *a.wait_epoch + a.wait_offset, a.status);
   const int64_t row = blockIdx.x;
   const int64_t d = a.d;
   float* xr = a.x_res + row * d;
@@ -258,7 +288,7 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
       idx[c] = i < d ? row * d + i : -1;
       vals[c] = i < d ? partial_sum4(a, idx[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx, (int)blockIdx.x);
+    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx);
   }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
@@ -350,6 +380,15 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
     erow = reinterpret_cast<const TE*>(a.embed) + id * d;
   }
   const bool summed = a.partial != nullptr;
+  // the residual (or embedding) row is requested first, so that its latency runs under the slab loads and,
+  // with tensor parallelism, under the exchange
+  float4 xin[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int64_t off = ((int64_t)c * 256 + threadIdx.x) * 4;
+    xin[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (off < dq) xin[c] = erow ? Vec4<TE>::load(erow + col0 + off) : *reinterpret_cast<const float4*>(xr + col0 + off);
+  }
   if (summed) {
     int64_t idx[NCH];
 #pragma unroll
@@ -358,7 +397,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
       idx[c] = off < dq ? row * d + col0 + off : -1;
       vals[c] = off < dq ? partial_sum4(a, idx[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx, (int)blockIdx.x);
+    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx);
   }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
@@ -366,7 +405,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
     const int64_t i = col0 + off;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (off < dq) {
-      v = erow ? Vec4<TE>::load(erow + i) : *reinterpret_cast<const float4*>(xr + i);
+      v = xin[c];
       if (summed) {
         float4 p = vals[c];
         if (a.bias) {
@@ -747,6 +786,76 @@ __global__ void __launch_bounds__(32) argmax_gathered_kernel(const void* gathere
   if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
+// ---- two-shot tensor-parallel all-reduce (Tp2Args) ----------------------------------------------------
+// 16-byte chunks: CE payload elements each.  Scatter: chunk (row, col) of the local partial goes to the rank
+// that owns its column slice.
+template <typename T>
+__global__ void __launch_bounds__(256) tp2_scatter_kernel(Tp2Args a) {
+  constexpr int CE = 16 / sizeof(T);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t cpr = a.d / CE, dn = a.d / a.world;
+  const int64_t total = a.rows * cpr;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / cpr, col = (i % cpr) * CE;
+    const int p = (int)(col / dn);
+    if (p == a.my_rank) continue;
+    const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.partial) + row * a.d + col);
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.region[p]) + ((int64_t)a.my_rank * a.rows + row) * dn + (col - p * dn)) = v;
+  }
+  if (grid_last_cta(a.arrive)) {
+    if ((int)threadIdx.x < a.world) peer_flag_release(a.cells[threadIdx.x] + 8 + a.my_rank, *a.epoch + a.offset);
+  }
+}
+
+__device__ __forceinline__ void acc_chunk(float (&acc)[8], uint4 v, bf16) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+    acc[2 * j] += __low2float(h);
+    acc[2 * j + 1] += __high2float(h);
+  }
+}
+__device__ __forceinline__ void acc_chunk(float (&acc)[8], uint4 v, float) {
+  acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y); acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+}
+
+// Reduce + gather: this rank adds the world copies of its column slice in rank order and stores the sum into
+// every rank's gather buffer (its own included).
+template <typename T>
+__global__ void __launch_bounds__(256) tp2_reduce_kernel(Tp2Args a) {
+  constexpr int CE = 16 / sizeof(T);
+  pdl_launch_dependents();
+  pdl_wait();
+  peer_flags_wait(a.cells[a.my_rank] + 8, 1, a.world, -1, *a.epoch + a.offset, a.status);
+  const int64_t dn = a.d / a.world, cps = dn / CE;
+  const int64_t total = a.rows * cps;
+  const T* scat = reinterpret_cast<const T*>(a.region[a.my_rank]);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / cps, c0 = (i % cps) * CE;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < a.world; ++r) {
+      uint4 v;
+      if (r == a.my_rank) v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.partial) + row * a.d + a.my_rank * dn + c0);
+      else v = __ldcg(reinterpret_cast<const uint4*>(scat + ((int64_t)r * a.rows + row) * dn + c0));
+      acc_chunk(acc, v, T());
+    }
+    uint4 o;
+    if constexpr (sizeof(T) == 2) {
+      o = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    } else {
+      o = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+    }
+    const int64_t at = row * a.d + a.my_rank * dn + c0;
+    for (int r = 0; r < a.world; ++r)
+      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.region[r] + a.off_gather) + at) = o;
+  }
+  if (grid_last_cta(a.arrive + 1)) {
+    if ((int)threadIdx.x < a.world) peer_flag_release(a.cells[threadIdx.x] + 16 + a.my_rank, *a.epoch + a.offset);
+  }
+}
+
 __global__ void epoch_bump_kernel(int* epoch, int by) {
   pdl_launch_dependents();
   pdl_wait();
@@ -818,8 +927,9 @@ int residual_norm_launch(Ctx* c, const NormArgs& a, int64_t rows) {
   RB_REQUIRE(a.d <= (int64_t)NORM_THREADS * NORM_MAX_PER_THREAD, "norm width above 16384 is not supported");
   const bool e16 = a.embed_dtype == REWB200_BF16, o16 = a.out_dtype == REWB200_BF16;
   cudaError_t e;
-  RB_REQUIRE(a.n_peers == 0 || (a.d % 4 == 0 && a.partial != nullptr && rows * 4 <= kPeerChunks && a.n_peers <= 8),
-             "the fused all-reduce needs d_model % 4 == 0, local partials and at most 64 rows");
+  RB_REQUIRE(a.n_peers == 0 || (a.d % 4 == 0 && a.partial != nullptr && rows <= 64 && a.n_peers <= 8 &&
+                                rows * a.d / (a.payload_bf16 ? 4 : 2) <= a.slot_lines),
+             "the fused all-reduce needs d_model % 4 == 0, local partials, at most 64 rows and a slot that holds the step");
   RB_REQUIRE(!a.partial_bf16 || a.d % 4 == 0, "bf16 partials need d_model % 4 == 0");
   if (o16 && a.norm_kind >= 0 && rows <= 64 && a.d % 16 == 0 && a.d <= 16384 && c->norm_cluster) {
     const int nch = (int)((a.d / 16 + 255) / 256);  // float4 per thread over a quarter row
@@ -925,6 +1035,23 @@ int argmax_gathered_launch(Ctx* c, const void* gathered, int world, int64_t rows
   RB_CUDA(launch_k(argmax_gathered_kernel, dim3((unsigned)rows), dim3(32), 0, c->stream, c->use_pdl, gathered, world,
                    (int)rows, nchunks, out));
   ++g_launch_total;
+  return REWB200_OK;
+}
+
+int tp2_allreduce_launch(Ctx* c, const Tp2Args& a) {
+  const int ce = a.payload_bf16 ? 8 : 4;
+  RB_REQUIRE(a.world >= 2 && a.world <= 8 && a.d % ((int64_t)a.world * ce) == 0, "two-shot all-reduce: d_model must split into 16-byte chunks per rank");
+  const int64_t chunks = a.rows * (a.d / ce);
+  const unsigned g1 = (unsigned)std::min<int64_t>((chunks + 255) / 256, (int64_t)c->sm_count * 16);
+  const unsigned g2 = (unsigned)std::min<int64_t>((chunks / a.world + 255) / 256, (int64_t)c->sm_count * 16);
+  if (a.payload_bf16) {
+    RB_CUDA(launch_k(tp2_scatter_kernel<bf16>, dim3(g1), dim3(256), 0, c->stream, c->use_pdl, a));
+    RB_CUDA(launch_k(tp2_reduce_kernel<bf16>, dim3(std::max(g2, 1u)), dim3(256), 0, c->stream, c->use_pdl, a));
+  } else {
+    RB_CUDA(launch_k(tp2_scatter_kernel<float>, dim3(g1), dim3(256), 0, c->stream, c->use_pdl, a));
+    RB_CUDA(launch_k(tp2_reduce_kernel<float>, dim3(std::max(g2, 1u)), dim3(256), 0, c->stream, c->use_pdl, a));
+  }
+  g_launch_total += 2;
   return REWB200_OK;
 }
 

@@ -837,33 +837,59 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   // pushes its columns to every rank's heap and adds the peers' in rank order); larger ones go through
   // NCCL, bf16 models with a bf16 payload (the o / down projections then write one bf16 slab, no bias).
   const PeerInfo* pi = cf.tp_size > 1 ? comm_peer_info(m->slot) : nullptr;
+  // a slot holds the step as 16-byte lines of 8 payload bytes each
   const bool oneshot = pi != nullptr && pi->buf_bytes > 0 && d % 4 == 0 && rows <= 64 &&
-                       (size_t)rows * d * dtype_size(dt) <= pi->buf_bytes && pi->world == cf.tp_size;
+                       (size_t)rows * d * dtype_size(dt) * 2 <= pi->buf_bytes && pi->world == cf.tp_size;
   const bool tp_bf16_slab = cf.tp_size > 1 && !oneshot && dt == REWB200_BF16 && d % 4 == 0 && rows > 64;  // smaller steps keep split-K slabs
+  // ... and when the heap's bulk region holds a scatter and a gather buffer of the step, the sum itself runs
+  // over the heap too (two-shot: reduce-scatter and all-gather by peer stores) instead of through NCCL
+  const size_t pay = dtype_size(dt);
+  const bool twoshot = cf.tp_size > 1 && !oneshot && rows > 64 && pi != nullptr && pi->world == cf.tp_size &&
+                       pi->a2a[pi->rank] != nullptr && d % ((int64_t)cf.tp_size * (16 / pay)) == 0 &&
+                       2 * (size_t)rows * d * pay <= pi->a2a_bytes && c->tp_twoshot;
   auto tp_reduce = [&](int l, int which, int& ks, NormArgs& a) -> int {
     if (cf.tp_size <= 1) return REWB200_OK;
     if (oneshot) {
       a.n_peers = pi->world;
       a.my_rank = pi->rank;
       a.payload_bf16 = dt == REWB200_BF16 ? 1 : 0;
-      a.slot_elems = (int64_t)(pi->buf_bytes / dtype_size(dt));
-      for (int r = 0; r < pi->world; ++r) {
-        a.peer_buf[r] = pi->bufs[which][r];
-        a.peer_flags[r] = pi->flags[r];
-      }
+      a.slot_lines = (int64_t)(pi->buf_bytes / 16);
+      for (int r = 0; r < pi->world; ++r) a.peer_buf[r] = pi->bufs[which][r];
       a.epoch = pi->epoch;
       a.barrier_offset = 2 * l + which + 1;
       return REWB200_OK;
     }
-    if (tp_bf16_slab) {
-      RB_TRY(comm_allreduce_sum(c, m->slot, s->part, rows * d, REWB200_BF16));
-      a.partial_bf16 = 1;
-    } else {
-      RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));
-      RB_TRY(comm_allreduce_sum(c, m->slot, s->part, rows * d, REWB200_F32));
-    }
+    if (!tp_bf16_slab) RB_TRY(slab_sum_launch(c, s->part, ks, rows * d));  // one slab: bf16 from the GEMM, or f32 summed here
     ks = 1;
     a.nsplit = 1;
+    a.partial_bf16 = tp_bf16_slab ? 1 : 0;
+    if (twoshot) {
+      Tp2Args t;
+      memset(&t, 0, sizeof(t));
+      t.world = pi->world;
+      t.my_rank = pi->rank;
+      for (int r = 0; r < pi->world; ++r) {
+        t.cells[r] = pi->a2a_flags[r];
+        t.region[r] = pi->a2a[r];
+      }
+      t.off_gather = (int64_t)((size_t)rows * d * pay);
+      t.arrive = pi->epoch + 2;
+      t.epoch = pi->epoch + 1;
+      t.offset = 2 * l + which + 1;
+      t.status = c->d_status;
+      t.partial = s->part;
+      t.rows = rows;
+      t.d = d;
+      t.payload_bf16 = dt == REWB200_BF16 ? 1 : 0;
+      RB_TRY(tp2_allreduce_launch(c, t));
+      a.partial = reinterpret_cast<const float*>(pi->a2a[pi->rank] + t.off_gather);
+      a.wait_cells = pi->a2a_flags[pi->rank] + 16;
+      a.wait_n = pi->world;
+      a.wait_epoch = pi->epoch + 1;
+      a.wait_offset = t.offset;
+      return REWB200_OK;
+    }
+    RB_TRY(comm_allreduce_sum(c, m->slot, s->part, rows * d, tp_bf16_slab ? REWB200_BF16 : REWB200_F32));
     return REWB200_OK;
   };
   // o-proj / down-proj: f32 split-K slabs for the consumer kernel, or one bf16 slab ahead of a bf16 NCCL sum
@@ -1032,6 +1058,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   }
   if (oneshot) RB_TRY(epoch_bump_launch(c, pi->epoch, 2 * cf.n_layers));  // same on every rank
   if (moe_seen > 0 && ep_uses_peer_heap(m, rows)) RB_TRY(epoch_bump_launch(c, comm_peer_info(m->slot)->epoch + 1, moe_seen));
+  if (twoshot) RB_TRY(epoch_bump_launch(c, pi->epoch + 1, 2 * cf.n_layers));
   // lm_head: last position of every sequence (generate.nim:172-190) or every row.
   const int64_t lrows = o.all_logits ? rows : nb;
   const char* xl = (const char*)s->xn + (o.all_logits ? 0 : (size_t)(o.S - 1) * d * dtype_size(dt));

@@ -270,24 +270,6 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 // Slot numbering is unchanged: slot = owner_rank * capacity + index on the asking side,
 // source_rank * capacity + index on the owning side.
 
-// Last CTA of a grid to arrive (every CTA calls this once, after its peer stores): returns true in all
-// threads of that CTA.  The fence before the arrival makes the CTA's stores visible system-wide first.
-__device__ __forceinline__ bool a2a_last_cta(int* arrive) {
-  __shared__ int s_last;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const int t = atomicAdd(arrive, 1);
-    s_last = (t == (int)gridDim.x - 1) ? 1 : 0;
-    if (s_last) {
-      __threadfence_system();
-      *arrive = 0;
-    }
-  }
-  __syncthreads();
-  return s_last != 0;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(128) moe_dispatch_peer_kernel(const T* __restrict__ x, const int* __restrict__ topi, int k,
                                                                 int64_t d, int experts_per_rank, int capacity, int* cursor,
@@ -311,7 +293,7 @@ __global__ void __launch_bounds__(128) moe_dispatch_peer_kernel(const T* __restr
   uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.region[s_p] + a.off_x) + ((int64_t)a.my_rank * capacity + s_idx) * d);
   const int n16 = (int)(d * sizeof(T) / 16);
   for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
-  if (a2a_last_cta(a.arrive)) {
+  if (grid_last_cta(a.arrive)) {
     // every pair of this rank has been stored: hand each owner its pair count, then the flag
     if ((int)threadIdx.x < a.world) {
       const int p = threadIdx.x;
@@ -373,7 +355,7 @@ __global__ void __launch_bounds__(128) moe_return_peer_kernel(const float* __res
     const int n4 = (int)(d / 4);
     for (int i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = from[i];
   }
-  if (a2a_last_cta(a.arrive + 1)) {
+  if (grid_last_cta(a.arrive + 1)) {
     if ((int)threadIdx.x < a.world) peer_flag_release(a.cells[threadIdx.x] + 16 + a.my_rank, *a.epoch + a.offset);
   }
 }

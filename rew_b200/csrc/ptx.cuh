@@ -161,6 +161,25 @@ __device__ __forceinline__ void peer_flags_wait(const int* cells, int stride, in
   __syncthreads();
 }
 
+// Last CTA of a grid to arrive (every CTA calls this exactly once, after its peer stores): returns true in all
+// threads of that CTA.  The fence before the arrival makes the CTA's stores visible system-wide first; the
+// counter is left at zero for the next launch.
+__device__ __forceinline__ bool grid_last_cta(int* arrive) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int t = atomicAdd(arrive, 1);
+    s_last = (t == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) ? 1 : 0;
+    if (s_last) {
+      __threadfence_system();
+      *arrive = 0;
+    }
+  }
+  __syncthreads();
+  return s_last != 0;
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)

@@ -270,6 +270,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "ep_exchange") {
     RB_REQUIRE(v == "prefix" || v == "capacity" || v == "auto", "option ep_exchange: expected auto, prefix or capacity");
     c->ep_prefix = v == "prefix" ? 1 : (v == "capacity" ? 0 : 2);
+  } else if (k == "tp_allreduce") {
+    RB_REQUIRE(v == "heap" || v == "nccl", "option tp_allreduce: expected heap or nccl");
+    c->tp_twoshot = v == "heap";
   } else if (k == "record_routing") {
     c->record_routing = v != "0";
   } else if (k == "inject_alloc_fail") {

@@ -36,8 +36,9 @@ def _bundled_nccl():
 @pytest.mark.parametrize("mode", ["nccl", "fused"])
 def test_tp2_generate_matches_oracle(orc, mode):
     """mode nccl: every all-reduce through NCCL; fused: steps of up to 64 rows use the push all-reduce over
-    the peer heap inside the residual+norm kernel (a 60-row prefill too; a 120-row prefill goes through NCCL,
-    with a bf16 payload on the bf16 model)."""
+    the peer heap inside the residual+norm kernel (a 60-row prefill too); a 120-row prefill is summed by the
+    two-shot exchange over the heap and, with option tp_allreduce=nccl, through NCCL (bf16 payload on the bf16
+    model)."""
     from rew_b200 import _lib
     with tempfile.TemporaryDirectory() as d:
         idfile = os.path.join(d, "nccl_id")
@@ -71,7 +72,7 @@ def test_tp2_generate_matches_oracle(orc, mode):
         t = W.init_weights(cfg, seed=9, std=0.05, trivial_affine=False)
         if dtype == _lib.BF16:
             t = [W.bf16_round(a) if a.ndim == 2 else a for a in t]
-        for tag, plen in (("", 20), ("_long", 40)):
+        for tag, plen in (("", 20), ("_long", 40), ("_long_nccl", 40)):
             prompt = np.random.default_rng(3).integers(0, 512, size=(3, plen)).astype(np.int32)
             key = name + tag
             # both ranks agree bit for bit

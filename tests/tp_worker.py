@@ -30,7 +30,7 @@ def main():
     print("rank", rank, "communicator ready", flush=True)
     fused = len(sys.argv) > 5 and sys.argv[5] == "fused"
     if fused:  # exchange the IPC handles of the all-reduce heaps through files
-        mine = api.comm_peer_alloc(1 << 20, 0)
+        mine = api.comm_peer_alloc(1 << 20, 1 << 20)
         with open("%s.h%d.tmp" % (idfile, rank), "wb") as f:
             f.write(mine)
         os.replace("%s.h%d.tmp" % (idfile, rank), "%s.h%d" % (idfile, rank))
@@ -59,22 +59,24 @@ def main():
             def block(i, tname, g, l, o):
                 return t[i][tuple(slice(a, a + n) for a, n in zip(o, l))]
             model = api.CausalLM(cfg)
-            g, l, o, pdim = model.tensor_layout(2)     # layer 0 qProj.weight: column-parallel
+            g, l, o, pdim = model.tensor_layout(3)     # layer 0 qProj.weight: column-parallel
             assert pdim == 1 and l == (g[0], g[1] // world) and o == (0, rank * g[1] // world), (g, l, o, pdim)
-            g, l, o, pdim = model.tensor_layout(8)     # layer 0 outProj.weight: row-parallel
+            g, l, o, pdim = model.tensor_layout(9)     # layer 0 outProj.weight: row-parallel
             assert pdim == 0 and l == (g[0] // world, g[1]) and o == (rank * g[0] // world, 0), (g, l, o, pdim)
             if world > 1:  # a block at another rank's offsets is refused
                 import ctypes as C
                 wrong = np.zeros(l, np.float32)
                 off = [((rank + 1) % world) * l[0], 0]
-                st = _lib.lib().rewb200_model_set_tensor_shard(model._h, 8, wrong.ctypes.data_as(_lib.F32P), (C.c_int64 * 2)(*l),
+                st = _lib.lib().rewb200_model_set_tensor_shard(model._h, 9, wrong.ctypes.data_as(_lib.F32P), (C.c_int64 * 2)(*l),
                                                                (C.c_int64 * 2)(*off), 2)
                 assert st != 0 and b"this rank holds" in _lib.lib().rewb200_last_error()
             model.free()
             model = api.CausalLM(cfg).load_shards(block)
-        # 60 prompt rows: every all-reduce of the step is the fused one; 120 rows: the prefill goes through NCCL
-        # (bf16 payload for the bf16 model) and only the decode steps are fused
-        for tag, plen in (("", 20), ("_long", 40)):
+        # 60 prompt rows: every all-reduce of the step is the fused one-shot exchange.  120 rows: the prefill is
+        # summed by the two-shot exchange over the heap ("_long"), or through NCCL ("_long_nccl": bf16 payload on the
+        # bf16 model); the decode steps behind both are fused again
+        for tag, plen, how in (("", 20, "heap"), ("_long", 40, "heap"), ("_long_nccl", 40, "nccl")):
+            api.set_option("tp_allreduce", how)
             prompt = np.random.default_rng(3).integers(0, cfg.vocab, size=(3, plen)).astype(np.int32)
             sess = model.session(3, 64)
             ids, logits = sess.generate(prompt, 6, want_logits=True)
@@ -82,6 +84,7 @@ def main():
             results[name + tag + "_ids"] = ids
             results[name + tag + "_logits"] = logits
             sess.free()  # the captured decode graph holds the communicator; release it before comm_destroy
+        api.set_option("tp_allreduce", "heap")
     np.savez(outfile, **results)
     api.comm_destroy()
 
