@@ -482,7 +482,10 @@ def main():
         # keep NCCL's communicator-init lines ("... rank r nranks n ... Init COMPLETE") in the run's log, off stdout
         os.environ["NCCL_DEBUG"] = "INFO"
         os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        if "NCCL_DEBUG_FILE" not in os.environ:
+            # one file per rank (ranks writing one stream tear each other's lines); echoed to stderr at the end
+            os.environ["NCCL_DEBUG_FILE"] = os.path.join(tempfile.gettempdir(), "rew_b200_nccl_%d_%%p.log" % os.getppid())
+            os.environ["REW_B200_NCCL_LOG_ECHO"] = "1"
 
     from rew_b200 import _lib, api, weights as W
     _lib.init(local_rank)
@@ -542,6 +545,16 @@ def main():
         comm.close()
     if pg:
         pg.barrier()
+        if os.environ.get("REW_B200_NCCL_LOG_ECHO") == "1":
+            # the communicator lines of every rank, whole, in rank order
+            path = os.environ["NCCL_DEBUG_FILE"].replace("%p", str(os.getpid()))
+            for r in range(world):
+                if r == rank and os.path.exists(path):
+                    keep = [l for l in open(path, errors="replace") if "Init COMPLETE" in l or "isAllDirectP2p" in l or "NVLS multicast" in l]
+                    sys.stderr.write("".join(keep))
+                    sys.stderr.flush()
+                    os.unlink(path)
+                pg.barrier()
     if rank != 0:
         return
     line = {

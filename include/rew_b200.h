@@ -73,6 +73,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            "prefix" from 4 ranks on; prefix = NCCL, pair counts first and then only the
  *                                            occupied prefix of every slot array (steps of 64+ pairs outside a captured
  *                                            graph); capacity = NCCL, always the worst-case capacity
+ *   "nf4_gemv" = "auto" | "tc"               NF4 weight-only Linear, steps of up to four rows: the CUDA-core code streamer
+ *                                            (default), or the tensor-core kernel that serves 5 to 32 rows
  *   "tp_allreduce" = "heap" | "nccl"         tensor-parallel steps of more than 64 rows (prefill): two-shot all-reduce over
  *                                            the peer heap when its bulk region holds the step (default), or NCCL always
  *   "record_routing" = "0" | "1"             test aid: sessions created afterwards keep every MoE layer's top-k expert ids

@@ -63,6 +63,7 @@ struct Ctx {
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
+  bool nf4_small = true;        // NF4 GEMV of up to four rows on the CUDA-core streamer instead of the tensor-core kernel
   bool tp_twoshot = true;       // tensor-parallel steps above 64 rows: sum over the peer heap (two-shot) instead of NCCL
   bool record_routing = false;  // sessions keep every MoE layer's top-k expert ids of their last forward (a test aid)
   int inject_alloc_fail = 0;  // test hook: the n-th activation allocation from now fails on the host
@@ -105,6 +106,7 @@ int nf4_quantize_launch(Ctx* c, const void* src, int src_dtype, int64_t ld, ColM
 int nf4_dequant_launch(Ctx* c, const Nf4W& w, bf16* dst, int64_t ld, ColMap cm);
 int nf4_codes_launch(Ctx* c, const Nf4W& w, uint8_t* codes);
 int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N);
+int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N, int64_t M);  // rows of the step: up to four run on the CUDA-core GEMV
 // out: [ksplit][M][N] f32 partial sums of x[M,K] @ W (no bias); 1 <= M <= 32
 int nf4_gemv_launch(Ctx* c, const Nf4W& w, const bf16* x, int64_t ldx, int64_t M, int ksplit, float* out);
 

@@ -39,7 +39,7 @@ int comm_alltoallv_rows(Ctx* c, int slot, const void* send, void* recv, size_t p
                         const int* send_rows, const int* recv_rows);
 int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi);
 int moe_route_slabs_launch(Ctx* c, const float* logits, int nsplit, int64_t split_stride, const float* bias, int64_t N, int E,
-                           int k, float* topw, int* topi);
+                           int k, float* topw, int* topi, int* zero, int n_zero);
 int moe_group_local_launch(Ctx* c, const void* x, int dtype, const int* topi, int64_t tokens, int k, int64_t d, int n_experts,
                            int* offsets, void* xs, int* pair_pos);
 int moe_reset_launch(Ctx* c, int* cursor, int n_cursor, int* count, int n_count, int* meta, int n_meta);
@@ -492,7 +492,7 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
   if (fused) *fused = false;
   if (w.quant && rows <= 32) {
     // weight-only NF4: codes dequantised inside the GEMV, f32 split-K slabs
-    int ks = nf4_pick_ksplit(c, w.K, w.N);
+    int ks = nf4_pick_ksplit(c, w.K, w.N, rows);
     while (ks > 1 && (size_t)ks * rows * w.N * sizeof(float) > s->part_bytes) --ks;
     RB_REQUIRE((size_t)ks * rows * w.N * sizeof(float) <= s->part_bytes, "split-K scratch too small for the quantised Linear");
     RB_TRY(nf4_gemv_launch(c, w.nf4, (const bf16*)x, ldx, rows, ks, s->part));
@@ -575,6 +575,10 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
   const int64_t d = cf.d_model, f = X.f;
   const int k = cf.top_k, ep = cf.ep_size, E_l = X.E_l;
   const int dt = cf.dtype;
+  // expert parallel over the peer heap: the routing kernel also clears the dispatch kernel's per-peer cursors
+  const bool peer = ep_uses_peer_heap(m, rows);
+  int* const clear = peer ? s->moe_ints : nullptr;
+  bool cleared = false;
   if (dt == REWB200_BF16 && rows <= 64) {
     // the router has one feature tile: split K over several CTAs, the routing kernel sums the slabs
     const int nkb = (int)((d + 63) / 64);
@@ -583,7 +587,8 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
     RB_TRY(linear_bf16_launch(c, X.router.plan, (const bf16*)s->xn, d, rows, EPI_PARTIAL_F32, ks, s->moe_logits, cf.n_routed,
                               nullptr, nullptr, 0));
     RB_TRY(moe_route_slabs_launch(c, s->moe_logits, ks, rows * cf.n_routed, X.router.b, rows, cf.n_routed, k, s->moe_topw,
-                                  s->moe_topi));
+                                  s->moe_topi, clear, peer ? ep : 0));
+    cleared = peer;
   } else {
     if (dt == REWB200_BF16)
       RB_TRY(linear_bf16_launch(c, X.router.plan, (const bf16*)s->xn, d, rows, EPI_BIAS_F32, 1, s->moe_logits, cf.n_routed,
@@ -635,7 +640,7 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
                               max_rows_l));
     return moe_combine_launch(c, s->moe_ys, pair_slot, s->moe_topw, rows, k, d, out ? out : s->part, accumulate ? 1 : 0);
   }
-  if (ep_uses_peer_heap(m, rows)) {
+  if (peer) {
     const PeerInfo* pi = comm_peer_info(m->slot);
     A2aArgs a;
     memset(&a, 0, sizeof(a));
@@ -651,7 +656,8 @@ int moe_routed(rewb200_session* s, LayerDev& L, int64_t rows, bool accumulate, f
     a.epoch = pi->epoch + 1;
     a.offset = moe_index + 1;
     a.status = c->d_status;
-    RB_TRY(moe_reset_launch(c, cursor, ep, count, E_l + 1, send_meta, 0));
+    // large steps count with atomics: clear the counters; small ones need only the cursors, cleared by the routing kernel
+    if (!cleared || slots > 4096) RB_TRY(moe_reset_launch(c, cursor, ep, count, E_l + 1, send_meta, 0));
     RB_TRY(moe_dispatch_peer_launch(c, s->xn, dt, s->moe_topi, rows, k, d, E_l, (int)cap, cursor, pair_slot, a));
     RB_TRY(moe_group_peer_launch(c, dt, (int)slots, (int)cap, d, E_l, count, offsets, cursor2, s->moe_xs, slot_pos, a));
     const int max_rows_p = (int)std::min<int64_t>(rows * ep, slots);
@@ -990,7 +996,8 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     // run on a second stream beside the routed path (router, sort, two HBM-bound grouped GEMMs, combine).
     // Their slabs sit behind the gate|up scratch, the routed sum in the slab after them.
     const size_t gu_scratch = (size_t)4 * rows * 2 * L.ffn_local;  // floats the split gate|up may use at the head of s->part
-    const bool fork = L.moe && L.ffn_local > 0 && dt == REWB200_BF16 && cf.ep_size == 1 && cf.tp_size == 1 && rows <= 64 &&
+    const bool fork = L.moe && L.ffn_local > 0 && dt == REWB200_BF16 && (cf.ep_size == 1 || ep_uses_peer_heap(m, rows)) &&
+                      cf.tp_size == 1 && rows <= 64 &&
                       c->moe_overlap && (gu_scratch + (size_t)17 * rows * d) * sizeof(float) <= s->part_bytes;
     if (fork) {
       float* base = s->part + gu_scratch;

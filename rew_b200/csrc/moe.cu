@@ -21,9 +21,10 @@ constexpr int MAX_E_PER_LANE = 8;  // E <= 256
 // logits: nsplit slabs [N][E] split_stride apart, summed in slab order, plus bias (may be null).
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int nsplit, int64_t split_stride,
                                                         const float* __restrict__ bias, int64_t N, int E, int k,
-                                                        float* __restrict__ topw, int* __restrict__ topi) {
+                                                        float* __restrict__ topw, int* __restrict__ topi, int* zero, int n_zero) {
   pdl_launch_dependents();
   pdl_wait();
+  if (blockIdx.x == 0 && (int)threadIdx.x < n_zero) zero[threadIdx.x] = 0;  // the dispatch kernel's per-peer cursors
   const int lane = threadIdx.x & 31;
   const int64_t tok = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (tok >= N) return;
@@ -341,6 +342,58 @@ __global__ void __launch_bounds__(128) moe_gather_peer_kernel(int64_t d, int cap
   for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src_row + i);
 }
 
+// Small steps (decode): count, scan and gather in ONE kernel and without atomics.  One CTA per slot; it waits
+// for the dispatch flags, looks at every occupied slot's expert id and places its own row behind all rows of
+// lower experts and the lower-numbered slots of its own expert (a fixed order), CTA 0 writes the experts' row
+// offsets.  n_slots * 4 bytes of ids per CTA out of L2: meant for a few thousand slots at most.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_group_small_peer_kernel(int n_slots, int capacity, int64_t d, int n_experts,
+                                                                   int* offsets, T* xs, int* slot_pos, A2aArgs a) {
+  __shared__ int s_cnt[8];
+  __shared__ int s_red[4];
+  __shared__ int s_hist[32 * MAX_E_PER_LANE + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  peer_flags_wait(a.cells[a.my_rank] + 8, 1, a.world, -1, *a.epoch + a.offset, a.status);
+  if ((int)threadIdx.x < a.world) s_cnt[threadIdx.x] = __ldcg(a.cells[a.my_rank] + threadIdx.x);
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i <= n_experts; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  const int* meta = reinterpret_cast<const int*>(a.region[a.my_rank] + a.off_meta);
+  const int slot = blockIdx.x;
+  const bool mine = (slot % capacity) < s_cnt[slot / capacity];
+  const int e = mine ? __ldcg(meta + slot) : -1;
+  int before = 0;
+  for (int p = threadIdx.x; p < n_slots; p += blockDim.x) {
+    if ((p % capacity) >= s_cnt[p / capacity]) continue;
+    const int ep = __ldcg(meta + p);
+    before += (ep < e || (ep == e && p < slot)) ? 1 : 0;
+    if (blockIdx.x == 0) atomicAdd(&s_hist[ep], 1);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = before;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int acc = 0;
+    for (int i = 0; i < n_experts; ++i) {
+      offsets[i] = acc;
+      acc += s_hist[i];
+    }
+    offsets[n_experts] = acc;
+  }
+  if (!mine) {
+    if (threadIdx.x == 0) slot_pos[slot] = -1;
+    return;
+  }
+  const int pos = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+  if (threadIdx.x == 0) slot_pos[slot] = pos;
+  const uint4* src_row = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.region[a.my_rank] + a.off_x) + (int64_t)slot * d);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (int64_t)pos * d);
+  const int n16 = (int)(d * sizeof(T) / 16);
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src_row + i);
+}
+
 // Expert outputs back to the rank that asked, in its slot order; the last CTA raises the return flags.
 __global__ void __launch_bounds__(128) moe_return_peer_kernel(const float* __restrict__ ys, const int* __restrict__ slot_pos,
                                                               int64_t d, int capacity, A2aArgs a) {
@@ -447,6 +500,13 @@ int moe_dispatch_peer_launch(Ctx* c, const void* x, int dtype, const int* topi, 
 }
 int moe_group_peer_launch(Ctx* c, int dtype, int n_slots, int capacity, int64_t d, int n_experts, int* count, int* offsets,
                           int* cursor2, void* xs, int* slot_pos, const A2aArgs& a) {
+  if (n_slots <= 4096 && n_experts <= 32 * MAX_E_PER_LANE) {  // decode sizes: one kernel, fixed row order
+    if (dtype == REWB200_BF16)
+      RB_LAUNCH(moe_group_small_peer_kernel<bf16>, n_slots, 128, n_slots, capacity, d, n_experts, offsets, (bf16*)xs, slot_pos, a);
+    else
+      RB_LAUNCH(moe_group_small_peer_kernel<float>, n_slots, 128, n_slots, capacity, d, n_experts, offsets, (float*)xs, slot_pos, a);
+    return REWB200_OK;
+  }
   RB_LAUNCH(moe_count_peer_kernel, (n_slots + 255) / 256, 256, n_slots, capacity, count, a);
   RB_LAUNCH(moe_scan_kernel, 1, 32, (const int*)count, n_experts, offsets, cursor2);
   if (dtype == REWB200_BF16)
@@ -466,17 +526,18 @@ int moe_combine_peer_launch(Ctx* c, const int* pair_slot, const float* topw, int
 }
 
 int moe_route_slabs_launch(Ctx* c, const float* logits, int nsplit, int64_t split_stride, const float* bias, int64_t N, int E,
-                           int k, float* topw, int* topi) {
+                           int k, float* topw, int* topi, int* zero, int n_zero) {
   RB_REQUIRE(E >= 1 && E <= 32 * MAX_E_PER_LANE, "MoE routing supports up to 256 experts");
   RB_REQUIRE(k >= 1 && k <= E, "initDeepSeekMoE: numExpertsPerTok must be in 1..numRouted");
+  RB_REQUIRE(n_zero >= 0 && n_zero <= 128, "at most 128 counters can be cleared by the routing kernel");
   if (N == 0) return REWB200_OK;
   RB_CUDA(launch_k(moe_route_kernel, dim3((unsigned)((N + 3) / 4)), dim3(128), 0, c->stream, c->use_pdl, logits, nsplit,
-                   split_stride, bias, N, E, k, topw, topi));
+                   split_stride, bias, N, E, k, topw, topi, zero, n_zero));
   ++g_launch_total;
   return REWB200_OK;
 }
 int moe_route_launch(Ctx* c, const float* logits, int64_t N, int E, int k, float* topw, int* topi) {
-  return moe_route_slabs_launch(c, logits, 1, 0, nullptr, N, E, k, topw, topi);
+  return moe_route_slabs_launch(c, logits, 1, 0, nullptr, N, E, k, topw, topi, nullptr, 0);
 }
 
 // One rank owning every expert: pos[pair] = row of pair (token, j) in the expert-sorted activation matrix

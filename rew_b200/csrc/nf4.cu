@@ -27,6 +27,7 @@
 // integer pipe at 0.17 of the HBM roofline; the pair table with per-warp cp.async staging reached 0.22.
 // A variant of this kernel with 512 features per CTA, i.e. four times the codes in flight, was slower.)
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 #include <string>
@@ -382,6 +383,129 @@ int nf4_codes_launch(Ctx* c, const Nf4W& w, uint8_t* codes) {
 
 // CTAs along K: two CTAs fit an SM; fill those slots once (a second, partial wave costs a whole CTA
 // lifetime) and keep at least 4 blocks of 64 rows per CTA.
+// ---- GEMV for one to four rows on the CUDA cores ---------------------------------------------------------
+// With so few rows the tensor core has nothing to do and the kernel is a stream of codes: 0.5 byte per weight
+// against 2 for bf16, so the instruction count per code byte is what matters.  A CTA owns 128 features and a
+// range of 64-row blocks; thread t owns feature t and reads its 32 code bytes of a block with two 16-byte
+// loads (consecutive threads, consecutive 32 bytes: the tile's 4 KB are one contiguous run); the next block's
+// codes are requested before this block's are consumed.  A code byte (two weights) costs one lookup in a
+// 256-entry table of fp16 level PAIRS (eight copies side by side, so that lanes rarely share a bank) and one HFMA2 per row with the
+// matching pair of activations, which are staged once per block already multiplied by the group's scales
+// (xs[row][j] = (x[2j] * s[2j], x[2j+1] * s[2j+1]) as fp16).  The 32 products of a block are summed in fp16
+// and the block sums in f32, which keeps the rounding error of the sum at the 1e-3 level; fp16's range holds
+// activations up to ~6e4 / scale.  Output: the same f32 split-K slabs [ksplit][M][N] the tensor-core kernel
+// leaves.
+template <int MR>
+__global__ void __launch_bounds__(128) nf4_gemv_small_kernel(const uint8_t* __restrict__ q, const float* __restrict__ sc,
+                                                             const bf16* __restrict__ x, int64_t ldx, int M, int64_t K,
+                                                             int64_t N, int kb_per_split, float* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t nf4s_smem[];
+  __half2* tab = reinterpret_cast<__half2*>(nf4s_smem);                         // [256][8]: eight copies, lane & 7 picks one
+  __half2* xs = reinterpret_cast<__half2*>(nf4s_smem + 256 * 8 * 4);            // [2 buffers][2 groups][MR][32]
+  pdl_launch_dependents();
+  const int tile = blockIdx.x, split = blockIdx.y, t = threadIdx.x, lane = t & 31;
+  const int KB = (int)(K / 64);
+  const int kb0 = split * kb_per_split;
+  const int nkb = max(0, min(kb_per_split, KB - kb0));
+  for (int i = t; i < 256 * 8; i += 128) {
+    const int byte = i >> 3;
+    tab[i] = __floats2half2_rn(kNf4[byte & 15], kNf4[byte >> 4]);
+  }
+  const int cp = lane & 7;
+  const uint4* qp = reinterpret_cast<const uint4*>(q) + (((int64_t)tile * KB + kb0) * 128 + t) * 2;
+  uint4 c0 = make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u), c1 = c0, n0 = c0, n1 = c0, m0 = c0, m1 = c0;  // code 7 = 0.0
+  if (nkb > 0) {  // the weights do not depend on the previous kernel: three blocks are requested before the wait
+    c0 = __ldcs(qp);
+    c1 = __ldcs(qp + 1);
+  }
+  if (nkb > 1) {
+    n0 = __ldcs(qp + 256);
+    n1 = __ldcs(qp + 257);
+  }
+  pdl_wait();
+  // staging: thread t prepares pair (t & 31) of group (t >> 5) & 1 for rows (t >> 6), (t >> 6) + 2
+  const int sg = (t >> 5) & 1, sj = t & 31, sm0 = t >> 6;
+  const int64_t sgi = (int64_t)tile * 2 + sg;
+  const bool sg_ok = sgi * 64 < N;
+  auto stage = [&](int kb, int buf) {
+    const int64_t k = (int64_t)(kb0 + kb) * 64 + 2 * sj;
+    float2 s2 = make_float2(0.f, 0.f);
+    if (sg_ok) s2 = *reinterpret_cast<const float2*>(sc + sgi * K + k);
+#pragma unroll
+    for (int m = sm0; m < MR; m += 2) {
+      float2 xv = make_float2(0.f, 0.f);
+      if (m < M) {
+        const __nv_bfloat162 xb = *reinterpret_cast<const __nv_bfloat162*>(x + (int64_t)m * ldx + k);
+        xv = make_float2(__low2float(xb), __high2float(xb));
+      }
+      xs[((buf * 2 + sg) * MR + m) * 32 + sj] = __floats2half2_rn(xv.x * s2.x, xv.y * s2.y);
+    }
+  };
+  float acc[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+  if (nkb > 0) stage(0, 0);
+  __syncthreads();
+  const int g = t >> 6;
+  for (int kb = 0; kb < nkb; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 2 < nkb) {
+      m0 = __ldcs(qp + (int64_t)(kb + 2) * 256);
+      m1 = __ldcs(qp + (int64_t)(kb + 2) * 256 + 1);
+    }
+    if (kb + 1 < nkb) stage(kb + 1, buf ^ 1);
+    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    __half2 hs[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) hs[m] = __float2half2_rn(0.f);
+    const __half2* xg = xs + (buf * 2 + g) * MR * 32;
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) {
+      __half2 lv[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) lv[b] = tab[((w[wi] >> (8 * b)) & 0xFFu) * 8 + cp];
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xg + m * 32 + 4 * wi);  // the pairs of rows 8wi .. 8wi+7
+        hs[m] = __hfma2(lv[0], *reinterpret_cast<const __half2*>(&xv.x), hs[m]);
+        hs[m] = __hfma2(lv[1], *reinterpret_cast<const __half2*>(&xv.y), hs[m]);
+        hs[m] = __hfma2(lv[2], *reinterpret_cast<const __half2*>(&xv.z), hs[m]);
+        hs[m] = __hfma2(lv[3], *reinterpret_cast<const __half2*>(&xv.w), hs[m]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      const float2 f = __half22float2(hs[m]);
+      acc[m] += f.x + f.y;
+    }
+    __syncthreads();  // xs[buf] is free again and xs[buf ^ 1] is complete
+    c0 = n0;
+    c1 = n1;
+    n0 = m0;
+    n1 = m1;
+  }
+  const int64_t n = (int64_t)tile * 128 + t;
+  if (n < N)
+    for (int m = 0; m < M && m < MR; ++m) out[((int64_t)split * M + m) * N + n] = acc[m];
+}
+
+template <int MR>
+constexpr int nf4_small_smem() { return 256 * 8 * 4 + 2 * 2 * MR * 32 * 4; }
+
+constexpr int kNf4SmallRows = 4;
+
+int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N);
+
+int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N, int64_t M) {
+  if (M <= kNf4SmallRows) {  // many small CTAs (8 per SM resident): about eight waves' worth keeps the stream smooth
+    const int tiles = (int)((N + 127) / 128), KB = (int)(K / 64);
+    int ks = std::max(1, 8 * c->sm_count / tiles);
+    ks = std::min(ks, std::max(1, KB / 4));  // at least four blocks per CTA: the table and pipeline start-up are per CTA
+    return std::max(1, std::min(ks, 16));
+  }
+  return nf4_pick_ksplit(c, K, N);
+}
+
 int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N) {
   const int tiles = (int)((N + 127) / 128), KB = (int)(K / 64), slots = 2 * c->sm_count;
   int ks = std::max(1, slots / tiles);
@@ -395,9 +519,27 @@ int nf4_gemv_launch(Ctx* c, const Nf4W& w, const bf16* x, int64_t ldx, int64_t M
   const int KB = (int)(w.K / 64);
   ksplit = std::max(1, std::min(ksplit, KB));
   const int per = (KB + ksplit - 1) / ksplit;
+  const dim3 grid((unsigned)((w.N + 127) / 128), (unsigned)ksplit);
+  if (M <= kNf4SmallRows && c->nf4_small) {
+    static bool small_attr = false;
+    if (!small_attr) {
+      RB_CUDA(cudaFuncSetAttribute(nf4_gemv_small_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, nf4_small_smem<1>()));
+      RB_CUDA(cudaFuncSetAttribute(nf4_gemv_small_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, nf4_small_smem<2>()));
+      RB_CUDA(cudaFuncSetAttribute(nf4_gemv_small_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, nf4_small_smem<4>()));
+      small_attr = true;
+    }
+#define RB_NF4S(MR)                                                                                                    \
+  RB_CUDA(launch_k(nf4_gemv_small_kernel<MR>, grid, dim3(128), (size_t)nf4_small_smem<MR>(), c->stream, c->use_pdl,    \
+                   (const uint8_t*)w.q, (const float*)w.sc, x, ldx, (int)M, w.K, w.N, per, out))
+    if (M == 1) RB_NF4S(1);
+    else if (M == 2) RB_NF4S(2);
+    else RB_NF4S(4);
+#undef RB_NF4S
+    ++g_launch_total;
+    return REWB200_OK;
+  }
   CUtensorMap tmX;
   RB_TRY(make_tmap_2d_bf16(&tmX, x, (uint64_t)w.K, (uint64_t)M, (uint64_t)ldx * 2, 64, 32));
-  const dim3 grid((unsigned)((w.N + 127) / 128), (unsigned)ksplit);
   static bool attr_set = false;
   if (!attr_set) {
     RB_CUDA(cudaFuncSetAttribute(nf4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, NT_SMEM));
@@ -571,7 +713,7 @@ int rewb200_qlora_linear(const rewb200_buffer* x, const rewb200_nf4* h, const re
     *y = out;
     return REWB200_OK;
   }
-  const int ks = nf4_pick_ksplit(c, K, N);
+  const int ks = nf4_pick_ksplit(c, K, N, std::min<int64_t>(M, 32));
   float *part = nullptr, *xa = nullptr;
   cudaError_t e = cudaMalloc((void**)&part, (size_t)ks * 32 * N * sizeof(float));
   if (e == cudaSuccess && rank > 0) e = cudaMalloc((void**)&xa, (size_t)M * rank * sizeof(float));

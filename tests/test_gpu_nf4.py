@@ -39,7 +39,8 @@ def test_codes_and_scales_bit_exact(rb, orc, K, N, src):
     assert np.array_equal(deq, bf16_round(orc.nf4_dequantize(want_p, want_s, K * N, 64).reshape(K, N)))
 
 
-@pytest.mark.parametrize("M,K,N", [(1, 256, 128), (7, 512, 1024), (16, 1024, 256), (32, 4096, 512), (75, 512, 192)])
+@pytest.mark.parametrize("M,K,N", [(1, 256, 128), (1, 4096, 1024), (2, 512, 192), (3, 1024, 1024), (4, 4096, 512), (7, 512, 1024),
+                                   (16, 1024, 256), (32, 4096, 512), (75, 512, 192)])
 def test_qlora_forward_matches_oracle(rb, orc, M, K, N):
     rng = np.random.default_rng(M * 7 + N)
     w = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
@@ -60,6 +61,30 @@ def test_qlora_forward_matches_oracle(rb, orc, M, K, N):
     want = orc.qlora_forward(x, packed, scales, K, N, 64, bias=bias, A=A, B=B, scaling=2.0)
     assert got.shape == (1, M, N)
     assert rel_l2(got.reshape(M, N), want) <= 2e-2
+
+
+@pytest.mark.parametrize("M", [1, 2, 4])
+def test_small_row_gemv_agrees_with_the_tensor_core_kernel(rb, orc, M):
+    """Steps of up to four rows stream the codes through the CUDA cores (f32 level x f32 scale); option
+    nf4_gemv=tc sends them to the tensor-core kernel (bf16 level x bf16 scale).  Both hold the oracle's
+    tolerance and agree with each other well inside it."""
+    rng = np.random.default_rng(M)
+    K, N = 2048, 1536
+    w = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    x = bf16_round(rng.standard_normal((M, K)))
+    packed, scales = orc.nf4_quantize(w, 64)
+    want = orc.qlora_forward(x, packed, scales, K, N, 64, bias=None)
+    T = rb.Tensor.from_host
+    layer = rb.QloraLinear(T(w))
+    small = layer.forward(T(x, dtype=_lib.BF16)).to_host()
+    rb.set_option("nf4_gemv", "tc")
+    try:
+        tc = layer.forward(T(x, dtype=_lib.BF16)).to_host()
+    finally:
+        rb.set_option("nf4_gemv", "auto")
+    assert rel_l2(small, want) <= 2e-2 and rel_l2(tc, want) <= 2e-2
+    assert rel_l2(small, tc) <= 1e-2
+    assert rel_l2(small, want) <= rel_l2(tc, want) * 1.5 + 1e-3   # f32 scales: no worse than the bf16-scale kernel
 
 
 def test_identity_weight_like_the_reference_vector(rb, orc):
@@ -96,7 +121,7 @@ def _nf4_reference_tensors(orc, cfg, tensors):
     return out
 
 
-@pytest.mark.parametrize("B,S", [(1, 5), (32, 16), (3, 70)])
+@pytest.mark.parametrize("B,S", [(1, 5), (4, 9), (32, 16), (3, 70)])
 def test_nf4_model_logits_match_reference_semantics(rb, orc, B, S):
     """A decoder whose block Linears hold NF4 codes on the device: prefill (codes expanded into a bf16
     scratch, dense tcgen05 Linear) and cached decode (codes dequantised inside the GEMV) against f32
