@@ -54,6 +54,10 @@ WORKLOADS = {
     # the l8 decoder with its block Linears held as NF4 codes (weight-only, QLoRA's frozen base weights)
     "l8_b32_nf4": dict(model="llama3_8b", batch=32, prompt=512, weight_quant=1),
     "l8_b1_nf4": dict(model="llama3_8b", batch=1, prompt=512, weight_quant=1),
+    # one rank's share of the tensor-parallel l70_b16 run as a model of its own (heads, kv heads and FFN width divided by
+    # 4 / 8, no exchange): what the sharded kernels cost without the all-reduce, measurable on one GPU
+    "l70_tp4shape": dict(model="llama3_70b", batch=16, prompt=1024, shape_div=4),
+    "l70_tp8shape": dict(model="llama3_70b", batch=16, prompt=1024, shape_div=8),
     # the attention operator alone: batch 8, 32 query / 8 kv heads, head_dim 128, 4096 positions
     "attn_op": dict(model=None, batch=8, prompt=4096),
 }
@@ -293,6 +297,10 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     wl = WORKLOADS[name]
     cfg = make_cfg(wl["model"])
     cfg.weight_quant = wl.get("weight_quant", 0)
+    if wl.get("shape_div"):
+        dv = wl["shape_div"]
+        cfg.n_heads, cfg.n_kv_heads, cfg.ffn = cfg.n_heads // dv, cfg.n_kv_heads // dv, cfg.ffn // dv
+        cfg.vocab = cfg.vocab // dv // 8 * 8
     if args.layers > 0:
         cfg.n_layers = args.layers
     B, S = wl["batch"], wl["prompt"]

@@ -73,6 +73,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            "prefix" from 4 ranks on; prefix = NCCL, pair counts first and then only the
  *                                            occupied prefix of every slot array (steps of 64+ pairs outside a captured
  *                                            graph); capacity = NCCL, always the worst-case capacity
+ *   "qkv_post" = "attention" | "launch"      bf16 decode steps: bias, RoPE and the KV-cache append of the new token inside the
+ *                                            attention kernel (default), or in a launch of their own before it
  *   "nf4_gemv" = "auto" | "tc"               NF4 weight-only Linear, steps of up to four rows: the CUDA-core code streamer
  *                                            (default), or the tensor-core kernel that serves 5 to 32 rows
  *   "tp_allreduce" = "heap" | "nccl"         tensor-parallel steps of more than 64 rows (prefill): two-shot all-reduce over

@@ -53,6 +53,17 @@ struct AttnDev {
   int early_kv;     // see AttnArgs::kv_tail_only
   int* tickets;     // [B][kvh] zero between launches: the last split of a (sequence, kv head) merges; nullptr: separate merge launch
   int* status;
+  // Decode only (S == 1), optional: q, k and v of the new token are not read from memory but finished here from
+  // the f32 split-K slabs of the q|k|v projection (sum in slab order, bias, interleaved-pair RoPE, bf16), exactly
+  // as qkv_post_kernel would have done one launch earlier; the CTA whose tile range ends the sequence also writes
+  // the new K / V row into the cache before it requests that tile.
+  const float* f_partial;  // [f_ks][B][f_ntot]; nullptr: q comes from `q`, the cache is complete
+  int f_ks;
+  int64_t f_stride;
+  const float* f_bias;     // [f_ntot] or nullptr
+  const float* f_cos;      // [f_max_seq][hd]
+  const float* f_sin;
+  int f_rope_shift, f_max_seq, f_capacity, f_ntot;
 };
 
 __device__ __forceinline__ int kv_len_of(const AttnDev& a, int b) {
@@ -201,6 +212,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + ATT_STAGES * T::STAGE_BYTES);
 
+  __shared__ uint32_t sQ[16 * (HD / 2)];  // fused q|k|v: this kv head's query group as bf16 pairs [row][HD / 2]
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3, l8 = lane & 7, lq = lane >> 3;
@@ -230,6 +242,55 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
       load_tile<HD>(smem + early * T::STAGE_BYTES, &full[early], &tmK, &tmV, tile_row0(a, b, hk, t0 + early));
   pdl_wait();
 
+  if (a.f_partial) {
+    // ---- finish q (all CTAs) and the new K / V row (the CTA that owns the sequence's last tile) from the slabs
+    const int pos = kv_len - 1, rpos = pos + a.f_rope_shift;
+    const bool pos_ok = pos >= 0 && pos < a.f_capacity && rpos >= 0 && rpos < a.f_max_seq;
+    if (!pos_ok && threadIdx.x == 0) atomicExch(a.status, KS_BAD_INDEX);
+    const float* pr = a.f_partial + (int64_t)b * a.f_ntot;
+    const float* cr = a.f_cos + (int64_t)(pos_ok ? rpos : 0) * HD;
+    const float* sr = a.f_sin + (int64_t)(pos_ok ? rpos : 0) * HD;
+    const int nq = a.nh * HD, nkv = a.kvh * HD;
+    auto pair_at = [&](int col, bool rope, int e) -> uint32_t {  // e: element index of the pair inside its head
+      float v0 = 0.f, v1 = 0.f;
+      for (int sp = 0; sp < a.f_ks; ++sp) {
+        const float2 p2 = *reinterpret_cast<const float2*>(pr + sp * a.f_stride + col);
+        v0 += p2.x;
+        v1 += p2.y;
+      }
+      if (a.f_bias) {
+        v0 += a.f_bias[col];
+        v1 += a.f_bias[col + 1];
+      }
+      if (rope) {
+        const float c0 = cr[e], s0 = sr[e];
+        const float r0 = c0 * v0 - s0 * v1, r1 = s0 * v0 + c0 * v1;
+        v0 = r0;
+        v1 = r1;
+      }
+      return pack_bf16(v0, v1);
+    };
+    for (int p = threadIdx.x; p < a.group * (HD / 2); p += blockDim.x) {
+      const int row = p / (HD / 2), e = 2 * (p % (HD / 2));
+      sQ[p] = pair_at((hk * a.group + row) * HD + e, true, e);
+    }
+    const bool owns_last = ntiles > 0 && t0 <= ntiles - 1 && ntiles - 1 < t1;
+    if (owns_last && pos_ok) {
+      const int64_t crow = kv_row(a, b, hk, pos) * HD;
+      for (int p = threadIdx.x; p < HD; p += blockDim.x) {  // HD / 2 pairs of k, then HD / 2 pairs of v
+        const bool is_k = p < HD / 2;
+        const int e = 2 * (is_k ? p : p - HD / 2);
+        const uint32_t pk = pair_at((is_k ? nq : nq + nkv) + hk * HD + e, is_k, e);
+        bf16* dst = reinterpret_cast<bf16*>(const_cast<void*>(is_k ? a.k : a.v)) + crow + e;
+        *reinterpret_cast<uint32_t*>(dst) = pk;
+      }
+      // the row is read back by the bulk tensor copy of the last tile (async proxy): order the stores before it
+      __threadfence();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+    }
+    __syncthreads();
+  }
+
   // Q fragments: rows = heads of this kv head's group (rows >= group are zero).
   uint32_t qf[HD / 16][4];
   {
@@ -241,7 +302,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
         const int row = g + (r & 1) * 8;
         const int dim = kk * 16 + (r >> 1) * 8 + 2 * t;
         uint32_t v = 0;
-        if (row < a.group) v = *reinterpret_cast<const uint32_t*>(qb + (hk * a.group + row) * a.q_sh + dim);
+        if (row < a.group) {
+          if (a.f_partial) v = sQ[row * (HD / 2) + dim / 2];
+          else v = *reinterpret_cast<const uint32_t*>(qb + (hk * a.group + row) * a.q_sh + dim);
+        }
         qf[kk][r] = v;
       }
   }
@@ -888,6 +952,18 @@ int attn_launch(Ctx* c, const AttnArgs& h) {
   a.early_kv = (h.kv_tail_only && h.S == 1) ? 1 : 0;
   a.tickets = nullptr;
   a.status = c->d_status;
+  a.f_partial = nullptr;
+  a.f_ks = 0; a.f_stride = 0; a.f_bias = nullptr; a.f_cos = nullptr; a.f_sin = nullptr;
+  a.f_rope_shift = 0; a.f_max_seq = 0; a.f_capacity = 0; a.f_ntot = 0;
+  if (h.fuse_qkv) {
+    const QkvPostArgs& f = *h.fuse_qkv;
+    RB_REQUIRE(h.S == 1 && h.dtype == REWB200_BF16 && h.pos0 != nullptr && f.hd == h.kv.hd && f.kvh == h.kv.kvh && f.nh == h.nh &&
+                   f.hd % 2 == 0 && h.nh / h.kv.kvh <= 16,
+               "fused q|k|v needs a bf16 decode step with per-sequence positions");
+    a.f_partial = f.partial; a.f_ks = f.nsplit; a.f_stride = f.split_stride; a.f_bias = f.bias;
+    a.f_cos = f.cosT; a.f_sin = f.sinT; a.f_rope_shift = f.rope_shift; a.f_max_seq = f.max_seq; a.f_capacity = f.kv_capacity;
+    a.f_ntot = (f.nh + 2 * f.kvh) * f.hd;
+  }
   RB_REQUIRE(h.nh % h.kv.kvh == 0, "numHeads must be divisible by numKVHeads");
   RB_REQUIRE(h.pos0 != nullptr || h.kv_len_fixed >= 0, "attention needs per-sequence positions or a fixed key length");
   RB_REQUIRE(!h.kv.block_table || h.kv.page == TILE, "paged KV cache must use 64-token pages");

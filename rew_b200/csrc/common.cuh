@@ -63,6 +63,7 @@ struct Ctx {
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
+  bool attn_fuse_qkv = true;    // decode steps: bias + RoPE + cache append of the new token inside the attention kernel
   bool nf4_small = true;        // NF4 GEMV of up to four rows on the CUDA-core streamer instead of the tensor-core kernel
   bool tp_twoshot = true;       // tensor-parallel steps above 64 rows: sum over the peer heap (two-shot) instead of NCCL
   bool record_routing = false;  // sessions keep every MoE layer's top-k expert ids of their last forward (a test aid)
@@ -311,6 +312,9 @@ struct AttnArgs {
   size_t scratch_bytes;
   const CUtensorMap* tmK; // bf16: TMA maps over the K / V rows ([rows][head_dim], box 64x64)
   const CUtensorMap* tmV;
+  const QkvPostArgs* fuse_qkv;  // bf16 decode (S == 1), optional: the attention kernel finishes q / k / v of the new
+                                // token from the q|k|v projection's split-K slabs itself (what qkv_post_launch would
+                                // have done in a launch of its own) and appends K / V to the cache; `q` is not read
 };
 int attn_launch(Ctx* c, const AttnArgs& a);
 size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits);

@@ -188,6 +188,11 @@ __global__ void swiglu_slabs_il_kernel(const float* part, int ksplit, int64_t ro
   *reinterpret_cast<uint4*>(out + r * f + gidx * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+__global__ void fill_i32_kernel(int* p, int n, int v) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+
 // End of a step: publish the sampled ids, make them the next step's input,
 // advance positions and the step counter.
 // `active` (optional): lanes with 0 keep their token and position and report -1.
@@ -940,10 +945,10 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     qa.early_lookup = in_graph ? 1 : 0;
     RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks, dt == REWB200_BF16 ? &qa : nullptr, &qkv_done));
     if (o.trace) RB_TRY(o.trace->mark(TC_QKV));
-    if (!qkv_done) {
-      qa.nsplit = ks;
-      RB_TRY(qkv_post_launch(c, qa, nb));
-    }
+    // decode steps: the attention kernel finishes q / k / v of the new token from the slabs itself
+    const bool fuse_into_attn = !qkv_done && o.S == 1 && dt == REWB200_BF16 && c->attn_fuse_qkv && m->nh_l / m->kvh_l <= 16;
+    qa.nsplit = ks;
+    if (!qkv_done && !fuse_into_attn) RB_TRY(qkv_post_launch(c, qa, nb));
     if (o.trace) RB_TRY(o.trace->mark(TC_QKV_POST));
 
     AttnArgs aa;
@@ -974,6 +979,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       aa.tmK = &s->tmK[l];
       aa.tmV = &s->tmV[l];
     }
+    if (fuse_into_attn) aa.fuse_qkv = &qa;
     RB_TRY(attn_launch(c, aa));
     if (o.trace) RB_TRY(o.trace->mark(TC_ATTN));
 
@@ -1722,8 +1728,10 @@ int rewb200_session_forward(rewb200_session* s, const int32_t* ids, int S, int32
     // tokens seen so far = everything fed to the model (generate.nim:248 `tokenIds & generated`)
     RB_CUDA(cudaMemcpy2DAsync(s->samp_hist + s->host_pos, (size_t)s->max_len * sizeof(int), s->d_ids, (size_t)S * sizeof(int),
                               (size_t)S * sizeof(int), s->B, cudaMemcpyDeviceToDevice, c->stream));
-    std::vector<int> len((size_t)s->B, s->host_pos + S);
-    RB_CUDA(cudaMemcpy(s->samp_hist_len, len.data(), len.size() * sizeof(int), cudaMemcpyHostToDevice));
+    // on the slot's stream (a copy on the legacy stream would not be ordered against this non-blocking stream)
+    fill_i32_kernel<<<(unsigned)((s->B + 255) / 256), 256, 0, c->stream>>>(s->samp_hist_len, s->B, s->host_pos + S);
+    RB_CUDA(cudaGetLastError());
+    ++g_launch_total;
   }
   FwdOpts o;
   o.S = S;

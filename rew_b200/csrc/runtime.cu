@@ -270,6 +270,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "ep_exchange") {
     RB_REQUIRE(v == "prefix" || v == "capacity" || v == "auto", "option ep_exchange: expected auto, prefix or capacity");
     c->ep_prefix = v == "prefix" ? 1 : (v == "capacity" ? 0 : 2);
+  } else if (k == "qkv_post") {
+    RB_REQUIRE(v == "attention" || v == "launch", "option qkv_post: expected attention or launch");
+    c->attn_fuse_qkv = v == "attention";
   } else if (k == "nf4_gemv") {
     RB_REQUIRE(v == "auto" || v == "tc", "option nf4_gemv: expected auto or tc");
     c->nf4_small = v == "auto";

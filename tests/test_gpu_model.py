@@ -310,3 +310,27 @@ def test_l8_shaped_layer_bf16_batch32_against_oracle(rb, orc):
     want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
     assert rel_l2(last, want) <= 2e-2
     assert max(rel_l2(last[b], want[b]) for b in range(B)) <= 2e-2
+
+
+def test_qkv_finish_inside_attention_equals_the_separate_launch(rb):
+    """Decode steps finish q / k / v of the new token (slab sum, bias, RoPE, cache append) inside the attention kernel
+    by default; option qkv_post=launch runs the separate kernel of the prefill path instead.  Same arithmetic in
+    the same order: identical ids and logits, with split-KV (long context, one sequence) and without."""
+    from rew_b200 import _lib
+    cfg = W.ModelConfig(vocab=512, d_model=512, n_layers=2, n_heads=8, n_kv_heads=2, head_dim=128, ffn=1024, max_seq=1024,
+                        theta=500000.0, dtype=_lib.BF16, mask_kind=1)
+    t = [W.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(cfg, seed=6, std=0.05, trivial_affine=False)]
+    model = rb.CausalLM(cfg).load(t)
+    for B, S in ((1, 700), (5, 63), (3, 64)):
+        prompt = np.random.default_rng(B + S).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+        outs = []
+        for how in ("attention", "launch"):
+            rb.set_option("qkv_post", how)
+            try:
+                sess = model.session(B, S + 16)
+                outs.append(sess.generate(prompt, 9, want_logits=True))
+                sess.free()
+            finally:
+                rb.set_option("qkv_post", "attention")
+        assert np.array_equal(outs[0][0], outs[1][0])
+        assert np.array_equal(outs[0][1], outs[1][1])
