@@ -64,8 +64,9 @@ int rewb200_sync(int slot, int timeout_ms);
  *   "linear" = "mma" | "tc_prefill" | "tc"   bf16 Linear on mma.sync, on tcgen05 for more than 32
  *                                            rows, or on tcgen05 always   (REW_B200_LINEAR)
  *   "pdl"    = "0" | "1"                     programmatic dependent launch (REW_B200_PDL)
- *   "prefill" = "persistent" | "tile"        Linear launches of 256-token tiles: one persistent CTA per SM
- *                                            with the epilogue overlapped (default), or one CTA per tile
+ *   "prefill" = "pair" | "persistent" | "tile"   Linear launches of 256-token tiles: persistent CTA pairs on 256 x 256 tiles
+ *                                            (tcgen05 cta_group::2; default, widths that are multiples of 256), one
+ *                                            persistent CTA per SM with the epilogue overlapped, or one CTA per tile
  *   "profile_linears" = "1".."31"            which launches rewb200_session_profile_linears times: bit 0 q|k|v, 1 o,
  *                                            2 gate|up, 3 down, 4 lm_head (default 31, all)
  *   "ep_exchange" = "auto" | "prefix" | "capacity"   expert-parallel all-to-all: auto (default) = over the peer heap when
@@ -75,8 +76,9 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            graph); capacity = NCCL, always the worst-case capacity
  *   "qkv_post" = "attention" | "launch"      bf16 decode steps: bias, RoPE and the KV-cache append of the new token inside the
  *                                            attention kernel (default), or in a launch of their own before it
- *   "nf4_gemv" = "auto" | "tc"               NF4 weight-only Linear, steps of up to four rows: the CUDA-core code streamer
- *                                            (default), or the tensor-core kernel that serves 5 to 32 rows
+ *   "nf4_gemv" = "tc" | "cuda"               NF4 weight-only Linear, steps of up to four rows: the tensor-core kernel that
+ *                                            serves every step up to 32 rows (default), or a CUDA-core code streamer
+ *                                            (fp16 pair lookups + HFMA2; measured slower, kept for comparison)
  *   "tp_allreduce" = "heap" | "nccl"         tensor-parallel steps of more than 64 rows (prefill): two-shot all-reduce over
  *                                            the peer heap when its bulk region holds the step (default), or NCCL always
  *   "record_routing" = "0" | "1"             test aid: sessions created afterwards keep every MoE layer's top-k expert ids

@@ -57,6 +57,7 @@ struct Ctx {
   bool use_pdl = true;
   int linear_impl = 2;       // bf16 Linear: 0 mma.sync, 1 tcgen05 when rows > 32, 2 tcgen05 always (default)
   bool prefill_persistent = true;  // 256-token Linear tiles on the persistent kernel with overlapped epilogue
+  bool prefill_pair = true;        // ... on pairs of CTAs (tcgen05 cta_group::2, 256 x 256 tiles) when the width is a multiple of 256
   int splitk_max_rows = 256;  // largest step (rows) whose Linear launches may split K
   int profile_mask = 31;      // rewb200_session_profile_linears: bit 0 q|k|v, 1 o, 2 gate|up, 3 down, 4 lm_head
   int splitk_cluster = 0;     // decode-size split-K summed inside thread-block clusters instead of through f32 slabs: bit 0 the q|k|v launch, bit 1 the others (off: measured slower)
@@ -64,7 +65,7 @@ struct Ctx {
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
   bool attn_fuse_qkv = true;    // decode steps: bias + RoPE + cache append of the new token inside the attention kernel
-  bool nf4_small = true;        // NF4 GEMV of up to four rows on the CUDA-core streamer instead of the tensor-core kernel
+  bool nf4_small = false;       // NF4 GEMV of up to four rows on the CUDA-core streamer instead of the tensor-core kernel (measured slower: off)
   bool tp_twoshot = true;       // tensor-parallel steps above 64 rows: sum over the peer heap (two-shot) instead of NCCL
   bool record_routing = false;  // sessions keep every MoE layer's top-k expert ids of their last forward (a test aid)
   int inject_alloc_fail = 0;  // test hook: the n-th activation allocation from now fails on the host

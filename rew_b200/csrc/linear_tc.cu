@@ -709,6 +709,257 @@ __global__ void __launch_bounds__(192) linear_tc_persist_kernel(const __grid_con
   }
 }
 
+// ---- two-CTA variant of the persistent kernel (prefill, dense weights) -------------------------------
+// A cluster of two CTAs on neighbouring SMs works on one 256-feature x 256-token output tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 features of W (A operand) and its own 128 tokens of x
+// (half of the B operand), the tensor cores of both SMs read both halves, and each CTA's tensor memory
+// receives the accumulator rows of its own 128 features for all 256 tokens.  Per CTA a stage is 32 KB
+// instead of 48 KB for the same tensor-core work, which takes the kernel off the shared-memory bandwidth
+// limit of the one-CTA tile (48 KB written and read per 512 tensor cycles = 188 B/cycle against 128).
+// Protocol: the bulk tensor loads of both CTAs complete on the LEADER's (even CTA's) `full` barrier (the
+// cta_group::2 form of the load; no multicast: every CTA loads only what it alone needs); the leader's MMA
+// thread issues for both and releases a stage by committing to the `empty` barrier of each CTA; finished
+// accumulators are announced to both CTAs' epilogue warps the same way; the leader reuses an accumulator
+// buffer once the epilogues of both CTAs have arrived on its `tmem_empty` barrier.
+struct PairCfg {
+  static constexpr int TN = 256;                          // tokens per tile (both CTAs together)
+  static constexpr int STAGES = 6;
+  static constexpr int B_BYTES = (TN / 2) * 128;          // this CTA's 128 tokens x 64 k
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB
+  static constexpr int STG_LD = 528;
+  static constexpr int STG_BYTES = 32 * STG_LD;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 2 * STG_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+};
+
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the bit that tells the two CTAs of a pair apart in a shared::cluster address
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, uint64_t* leader_bar, int x, int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(leader_bar) & kPeerBitMask), "r"(x), "r"(y),
+      "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// arrives on the barrier at shared::cluster address `bar_cluster_addr` once every tcgen05 operation this thread
+// has issued so far is complete
+__device__ __forceinline__ void commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192) linear_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                                                        const __grid_constant__ CUtensorMap tmX,
+                                                                                        TcArgs a, int tiles_n, int tiles_m) {
+  using C = PairCfg;
+  constexpr int TN = C::TN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stg_base = smem + C::STAGES * C::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(stg_base + 2 * C::STG_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* tmem_full = empty + C::STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();   // 0: leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int total_tiles = tiles_n * tiles_m;  // tiles of 256 features x 256 tokens
+  const int nkb = (int)((a.K + BK - 1) / BK);
+  auto tile_coords = [&](int lin, int& tile_n, int& tile_m) {
+    constexpr int GROUP_M = 8;
+    const int per_group = GROUP_M * tiles_n;
+    const int group = lin / per_group;
+    const int first_m = group * GROUP_M;
+    const int group_rows = min(GROUP_M, tiles_m - first_m);
+    const int in_group = lin - group * per_group;
+    tile_m = first_m + in_group % group_rows;
+    tile_n = in_group / group_rows;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 2);  // the epilogues of both CTAs
+    }
+    fence_barrier_init();
+    pdl_launch_dependents();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc::fence_before();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival, and both allocations are done
+  tc::fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      tma_prefetch_desc(&tmX);
+      const uint64_t pol_w = policy_evict_first();
+      const uint64_t pol_x = policy_evict_last();
+      pdl_wait();  // the activations come from the previous kernel
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        int tile_n, tile_m;
+        tile_coords(t, tile_n, tile_m);
+        const int col0 = tile_n * 256 + (int)rank * BM, row0 = tile_m * TN + (int)rank * (TN / 2);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) - 1) & 1, a.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + s * C::STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * C::STAGE_BYTES);  // this CTA's stage and the peer's
+          const int k = kb * BK;
+          tma_load_2d_pair(st, &tmW, &full[s], col0, k, pol_w);
+          tma_load_2d_pair(st + A_BYTES / 2, &tmW, &full[s], col0 + 64, k, pol_w);
+          tma_load_2d_pair(st + A_BYTES, &tmX, &full[s], k, row0, pol_x);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // D f32, A/B bf16, A MN-major, B K-major, N = 256 tokens, M = 256 features over the pair
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      const uint32_t smem_base = smem_u32(smem);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs, ++j) {
+        const int buf = j & 1;
+        if (j >= 2) {  // both epilogues must have drained this accumulator (tile j - 2)
+          ok = mbar_wait(&tmem_empty[buf], ((j >> 1) - 1) & 1, a.status);
+          if (!ok) break;
+          tc::fence_after();
+        }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * TN);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          ok = mbar_wait(&full[s], (it / C::STAGES) & 1, a.status);
+          if (!ok) break;
+          tc::fence_after();
+          const uint32_t sa = smem_base + s * C::STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = tc::smem_desc(sa + kk * 2048, A_BYTES / 2, 1024);
+            const uint64_t db = tc::smem_desc(sb + kk * 32, 16, 1024);
+            umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          // the stage is free in BOTH CTAs once these MMAs have read it
+          commit_pair(smem_u32(&empty[s]));
+          commit_pair(dsmem_addr(smem_u32(&empty[s]), 1));
+        }
+        if (ok) {
+          commit_pair(smem_u32(&tmem_full[buf]));
+          commit_pair(dsmem_addr(smem_u32(&tmem_full[buf]), 1));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 2..5 of each CTA; TMEM lanes 32*(warp%4) .. +31 = this CTA's 128 features
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    const bool swiglu = a.epi == EPI_SWIGLU_BF16;
+    const bool out_f32 = a.epi == EPI_PARTIAL_F32 || a.epi == EPI_BIAS_F32;
+    const int tile_cols = swiglu ? 64 : 128;
+    const int row_bytes = tile_cols * (out_f32 ? 4 : 2);
+    const int chunks_per_row = row_bytes / 16;
+    const int elems_per_chunk = out_f32 ? 4 : 8;
+    const size_t esz = out_f32 ? 4 : 2;
+    const int64_t out_cols = swiglu ? a.N / 2 : a.N;
+    const uint32_t leader_tmem_empty0 = dsmem_addr(smem_u32(&tmem_empty[0]), 0);
+    pdl_wait();  // the output buffer may still be read by the previous kernel
+    int j = 0;
+    bool ok = true;
+    for (int t = pair; t < total_tiles; t += n_pairs, ++j) {
+      int tile_n, tile_m;
+      tile_coords(t, tile_n, tile_m);
+      const int col0 = tile_n * 256 + (int)rank * BM, row0 = tile_m * TN;
+      const int rows_valid = (int)min((int64_t)TN, a.M - row0);
+      const int buf = j & 1;
+      if (ok) ok = mbar_wait(&tmem_full[buf], (j >> 1) & 1, a.status);
+      tc::fence_after();
+      const int64_t feat = (int64_t)col0 + q * 32 + lane;
+      const bool feat_ok = feat < a.N;
+      const float bias_v = (a.bias && feat_ok && a.epi != EPI_PARTIAL_F32) ? a.bias[feat] : 0.f;
+      const int64_t out_col0 = swiglu ? col0 / 2 : col0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        if (c0 >= rows_valid) break;  // uniform over the four warps
+        uint8_t* stg = stg_base + ((c0 >> 5) & 1) * C::STG_BYTES;
+        if (ok) {
+          uint32_t r[32];
+          tc::ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * TN + c0), r);
+          if (swiglu || out_f32) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              reinterpret_cast<float*>(stg + jj * C::STG_LD)[q * 32 + lane] = __uint_as_float(r[jj]) + bias_v;
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              reinterpret_cast<bf16*>(stg + jj * C::STG_LD)[q * 32 + lane] = __float2bfloat16_rn(__uint_as_float(r[jj]) + bias_v);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+        if (ok) {
+          const int rows_here = min(32, rows_valid - c0);
+          const int total = rows_here * chunks_per_row;
+          uint8_t* obase = reinterpret_cast<uint8_t*>(a.out);
+          for (int i = et; i < total; i += 128) {
+            const int row = i / chunks_per_row, ch = i % chunks_per_row;
+            const int64_t col = out_col0 + (int64_t)ch * elems_per_chunk;
+            if (col >= out_cols) continue;
+            uint4 v;
+            if (swiglu) {
+              const float4* gp = reinterpret_cast<const float4*>(stg + row * C::STG_LD + ch * 64);
+              const float4 g0 = gp[0], g1 = gp[1], u0 = gp[2], u1 = gp[3];
+              v.x = pack_bf16(silu_f(g0.x) * u0.x, silu_f(g0.y) * u0.y);
+              v.y = pack_bf16(silu_f(g0.z) * u0.z, silu_f(g0.w) * u0.w);
+              v.z = pack_bf16(silu_f(g1.x) * u1.x, silu_f(g1.y) * u1.y);
+              v.w = pack_bf16(silu_f(g1.z) * u1.z, silu_f(g1.w) * u1.w);
+            } else {
+              v = *reinterpret_cast<const uint4*>(stg + row * C::STG_LD + ch * 16);
+            }
+            *reinterpret_cast<uint4*>(obase + ((size_t)(row0 + c0 + row) * a.ldo + col) * esz) = v;
+          }
+        }
+      }
+      // every epilogue warp of this CTA has read its part of the accumulator: tell the leader
+      tc::fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) mbar_arrive_cluster(leader_tmem_empty0 + (uint32_t)buf * 8u);
+    }
+  }
+  tc::fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves (or frees tensor memory) while the peer may still use this CTA's memory or barriers
+  if (warp == 1) {
+    tc::fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+  }
+}
+
 template <int TN>
 int launch_tn(Ctx* c, const LinearBf16Plan& plan, const CUtensorMap& tmX, const TcArgs& a, dim3 grid) {
   using C = TcCfg<TN>;
@@ -844,6 +1095,23 @@ int linear_tc_launch(Ctx* c, const LinearBf16Plan& plan, const bf16* x, int64_t 
   a.bias = bias;
   a.status = c->d_status;
   dim3 grid((unsigned)((plan.N + BM - 1) / BM), (unsigned)((M + TN - 1) / TN), (unsigned)ksplit);
+  if (TN == 256 && ksplit == 1 && c->prefill_persistent && c->prefill_pair && plan.N % 256 == 0 && c->sm_count % 2 == 0 &&
+      (int64_t)grid.x * grid.y >= 2 * (int64_t)c->sm_count) {
+    // two-CTA tiles: 256 features x 256 tokens per pair of SMs
+    CUtensorMap tmXh;
+    RB_TRY(make_tmap_2d_bf16(&tmXh, x, (uint64_t)plan.K, (uint64_t)M, (uint64_t)ldx * 2, 64, PairCfg::TN / 2));
+    static bool pair_attr = false;
+    if (!pair_attr) {
+      RB_CUDA(cudaFuncSetAttribute(linear_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM));
+      pair_attr = true;
+    }
+    const int tiles_n = (int)(plan.N / 256), tiles_m = (int)grid.y;
+    const int ctas = (int)std::min<int64_t>(2 * (int64_t)tiles_n * tiles_m, c->sm_count);
+    RB_CUDA(launch_k(linear_tc_pair_kernel, dim3((unsigned)(ctas & ~1)), dim3(192), (size_t)PairCfg::SMEM, c->stream, c->use_pdl,
+                     plan.tmW, tmXh, a, tiles_n, tiles_m));
+    ++g_launch_total;
+    return REWB200_OK;
+  }
   if (TN == 256 && ksplit == 1 && c->prefill_persistent && (int64_t)grid.x * grid.y >= 2 * (int64_t)c->sm_count) {
     static bool attr_set = false;
     if (!attr_set) {

@@ -427,24 +427,38 @@ __global__ void __launch_bounds__(128) nf4_gemv_small_kernel(const uint8_t* __re
   const int sg = (t >> 5) & 1, sj = t & 31, sm0 = t >> 6;
   const int64_t sgi = (int64_t)tile * 2 + sg;
   const bool sg_ok = sgi * 64 < N;
-  auto stage = [&](int kb, int buf) {
+  // Staging is software-pipelined: the scales and activations of block kb + 2 are requested while block kb is
+  // consumed and written to shared memory one iteration later, so no iteration waits for a global load.
+  constexpr int SL = (MR + 1) / 2;  // rows this thread stages
+  float2 s2_reg = make_float2(0.f, 0.f);
+  uint32_t x_reg[SL];
+  auto fetch = [&](int kb) {
     const int64_t k = (int64_t)(kb0 + kb) * 64 + 2 * sj;
-    float2 s2 = make_float2(0.f, 0.f);
-    if (sg_ok) s2 = *reinterpret_cast<const float2*>(sc + sgi * K + k);
+    s2_reg = sg_ok ? *reinterpret_cast<const float2*>(sc + sgi * K + k) : make_float2(0.f, 0.f);
 #pragma unroll
-    for (int m = sm0; m < MR; m += 2) {
-      float2 xv = make_float2(0.f, 0.f);
-      if (m < M) {
-        const __nv_bfloat162 xb = *reinterpret_cast<const __nv_bfloat162*>(x + (int64_t)m * ldx + k);
-        xv = make_float2(__low2float(xb), __high2float(xb));
+    for (int i = 0; i < SL; ++i) {
+      const int m = sm0 + 2 * i;
+      x_reg[i] = (m < M && m < MR) ? *reinterpret_cast<const uint32_t*>(x + (int64_t)m * ldx + k) : 0u;
+    }
+  };
+  auto put = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < SL; ++i) {
+      const int m = sm0 + 2 * i;
+      if (m < MR) {
+        const __nv_bfloat162 xb = *reinterpret_cast<const __nv_bfloat162*>(&x_reg[i]);
+        xs[((buf * 2 + sg) * MR + m) * 32 + sj] = __floats2half2_rn(__low2float(xb) * s2_reg.x, __high2float(xb) * s2_reg.y);
       }
-      xs[((buf * 2 + sg) * MR + m) * 32 + sj] = __floats2half2_rn(xv.x * s2.x, xv.y * s2.y);
     }
   };
   float acc[MR];
 #pragma unroll
   for (int m = 0; m < MR; ++m) acc[m] = 0.f;
-  if (nkb > 0) stage(0, 0);
+  if (nkb > 0) {
+    fetch(0);
+    put(0);
+  }
+  if (nkb > 1) fetch(1);
   __syncthreads();
   const int g = t >> 6;
   for (int kb = 0; kb < nkb; ++kb) {
@@ -453,7 +467,8 @@ __global__ void __launch_bounds__(128) nf4_gemv_small_kernel(const uint8_t* __re
       m0 = __ldcs(qp + (int64_t)(kb + 2) * 256);
       m1 = __ldcs(qp + (int64_t)(kb + 2) * 256 + 1);
     }
-    if (kb + 1 < nkb) stage(kb + 1, buf ^ 1);
+    if (kb + 1 < nkb) put(buf ^ 1);     // block kb + 1, requested one iteration ago
+    if (kb + 2 < nkb) fetch(kb + 2);
     const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
     __half2 hs[MR];
 #pragma unroll
@@ -497,7 +512,7 @@ constexpr int kNf4SmallRows = 4;
 int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N);
 
 int nf4_pick_ksplit(Ctx* c, int64_t K, int64_t N, int64_t M) {
-  if (M <= kNf4SmallRows) {  // many small CTAs (8 per SM resident): about eight waves' worth keeps the stream smooth
+  if (M <= kNf4SmallRows && c->nf4_small) {  // many small CTAs (8 per SM resident): about eight waves' worth keeps the stream smooth
     const int tiles = (int)((N + 127) / 128), KB = (int)(K / 64);
     int ks = std::max(1, 8 * c->sm_count / tiles);
     ks = std::min(ks, std::max(1, KB / 4));  // at least four blocks per CTA: the table and pipeline start-up are per CTA

@@ -258,8 +258,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "pdl") {
     c->use_pdl = v != "0";
   } else if (k == "prefill") {
-    RB_REQUIRE(v == "persistent" || v == "tile", "option prefill: expected persistent or tile");
-    c->prefill_persistent = v == "persistent";
+    RB_REQUIRE(v == "pair" || v == "persistent" || v == "tile", "option prefill: expected pair, persistent or tile");
+    c->prefill_persistent = v != "tile";
+    c->prefill_pair = v == "pair";
   } else if (k == "profile_linears") {
     const int mask = atoi(v.c_str());
     RB_REQUIRE(mask >= 1 && mask <= 31, "option profile_linears: a bit mask 1..31 (1 q|k|v, 2 o, 4 gate|up, 8 down, 16 lm_head)");
@@ -274,8 +275,8 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     RB_REQUIRE(v == "attention" || v == "launch", "option qkv_post: expected attention or launch");
     c->attn_fuse_qkv = v == "attention";
   } else if (k == "nf4_gemv") {
-    RB_REQUIRE(v == "auto" || v == "tc", "option nf4_gemv: expected auto or tc");
-    c->nf4_small = v == "auto";
+    RB_REQUIRE(v == "cuda" || v == "tc", "option nf4_gemv: expected tc or cuda");
+    c->nf4_small = v == "cuda";
   } else if (k == "tp_allreduce") {
     RB_REQUIRE(v == "heap" || v == "nccl", "option tp_allreduce: expected heap or nccl");
     c->tp_twoshot = v == "heap";

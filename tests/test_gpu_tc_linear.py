@@ -75,8 +75,36 @@ def test_persistent_prefill_linear_matches_oracle(rb_tc, orc):
     try:
         again = lin.forward(T(x, _lib.BF16)).to_host()
     finally:
-        rb_tc.set_option("prefill", "persistent")
+        rb_tc.set_option("prefill", "pair")
     assert np.array_equal(got, again)   # same MMA order, same rounding: the two kernels agree bit for bit
+
+
+@pytest.mark.parametrize("M,K,N,epi_bias", [(4100, 320, 2560, True), (8192, 1024, 1024, False), (5000, 64, 512, True)])
+def test_pair_prefill_linear_matches_oracle_and_the_one_cta_kernels(rb_tc, orc, M, K, N, epi_bias):
+    """Widths that are multiples of 256 with at least two 256-token tiles per SM run on pairs of CTAs
+    (tcgen05 cta_group::2, 256 x 256 tiles, each CTA staging half of either operand).  Ragged last token tile,
+    a single 64-row k block, more tiles than pairs: against the oracle, and bit for bit against the one-CTA
+    persistent kernel and the one-tile kernel (the same k order and the same rounding)."""
+    from rew_b200 import _lib
+    rng = np.random.default_rng(M + N)
+    x = orc.bf16_round(rng.normal(size=(M, K)))
+    w = orc.bf16_round(rng.normal(0, 0.05, size=(K, N)))
+    b = rng.normal(0, 0.1, size=(N,)).astype(np.float32) if epi_bias else np.zeros(N, np.float32)
+    want = orc.linear(x, w, b)
+    T = rb_tc.Tensor.from_host
+    lin = rb_tc.Linear(T(w, _lib.BF16), T(b))
+    got = lin.forward(T(x, _lib.BF16)).to_host()
+    assert rel_l2(got, want) < 5e-3
+    assert max(rel_l2(got[r], want[r]) for r in (0, 127, 128, 255, 256, M // 2, M - 1)) < 2e-2
+    others = {}
+    for how in ("persistent", "tile"):
+        rb_tc.set_option("prefill", how)
+        try:
+            others[how] = lin.forward(T(x, _lib.BF16)).to_host()
+        finally:
+            rb_tc.set_option("prefill", "pair")
+    assert np.array_equal(others["persistent"], others["tile"])
+    assert np.array_equal(got, others["persistent"])
 
 
 def test_persistent_prefill_model_equals_tile_kernel(rb_tc):
@@ -95,5 +123,5 @@ def test_persistent_prefill_model_equals_tile_kernel(rb_tc):
         sess.reset()
         _, b = sess.forward(prompt, want_logits=True)
     finally:
-        rb_tc.set_option("prefill", "persistent")
+        rb_tc.set_option("prefill", "pair")
     assert np.isfinite(a).all() and np.array_equal(a, b)
