@@ -556,8 +556,8 @@ def main():
         if os.environ.get("REW_B200_NCCL_LOG_ECHO") == "1":
             # the communicator lines of every rank, whole, in rank order
             path = os.environ["NCCL_DEBUG_FILE"].replace("%p", str(os.getpid()))
-            for r in range(world):
-                if r == rank and os.path.exists(path):
+            for turn in range(world):
+                if turn == rank and os.path.exists(path):
                     keep = [l for l in open(path, errors="replace") if "Init COMPLETE" in l or "isAllDirectP2p" in l or "NVLS multicast" in l]
                     sys.stderr.write("".join(keep))
                     sys.stderr.flush()
