@@ -223,6 +223,9 @@ def run_attention_op(args, rank, local_rank):
     import ctypes as C
     from rew_b200 import _lib, api
     _lib.init(local_rank)
+    for kv in args.option:
+        key, _, val = kv.partition("=")
+        api.set_option(key, val)
     L = _lib.lib()
     B, nh, kvh, hd, S = 8, 32, 8, 128, 4096
     rng = np.random.default_rng(0)

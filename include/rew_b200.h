@@ -74,6 +74,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            "prefix" from 4 ranks on; prefix = NCCL, pair counts first and then only the
  *                                            occupied prefix of every slot array (steps of 64+ pairs outside a captured
  *                                            graph); capacity = NCCL, always the worst-case capacity
+ *   "gate_up_split" = "on" | "off"           decode-size gate|up launches with too few feature tiles to fill the GPU split K
+ *                                            and finish in a small sum + SwiGLU launch (default), or stay one launch
  *   "qkv_post" = "attention" | "launch"      bf16 decode steps: bias, RoPE and the KV-cache append of the new token inside the
  *                                            attention kernel (default), or in a launch of their own before it
  *   "nf4_gemv" = "tc" | "cuda"               NF4 weight-only Linear, steps of up to four rows: the tensor-core kernel that
@@ -94,7 +96,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            statistics through distributed shared memory (default), or one CTA per row
  *   "attention_merge" = "launch" | "fused"   split-KV decode attention: a second launch combines the splits (default),
  *                                            or the last CTA of a (sequence, kv head) does
- *   "attention" = "tc" | "mma"               prefill attention with head_dim 128 on tcgen05 (default) or mma.sync
+ *   "attention" = "tc" | "tc1" | "mma"       prefill attention with head_dim 128: tcgen05, two query tiles per CTA from
+ *                                            256 query rows up (default); tcgen05, one query tile per CTA; mma.sync
  *   "sampling" = "bucket" | "radix"          top-k / top-p selection: bucket histograms with the
  *                                            radix select as the exact fallback (default), or
  *                                            the radix select always

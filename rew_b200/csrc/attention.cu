@@ -916,6 +916,310 @@ __global__ void __launch_bounds__(fa::THREADS, 2) attn_prefill_tc_kernel(const _
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill attention, two query tiles per CTA ("ping-pong"): 256 queries of one head share every K / V tile.
+// Tensor memory (all 512 columns, one CTA per SM): S0 | S1 | O0 | O1, 128 columns each.
+//   warp 0        TMA: K and V tiles of 128 keys, two stages each
+//   warp 1        one thread issues, per key tile j:  O0 += P0(j) V(j);  S0 = Q0 K(j+1)^T;  O1 += P1(j) V(j);
+//                 S1 = Q1 K(j+1)^T.  While the softmax warps of tile 0 work on S0(j+1) the tensor core runs tile 1's
+//                 products and the other way round, so neither the tensor pipe nor the exp unit waits for a whole
+//                 QK^T -> softmax -> PV chain as in the one-tile kernel.
+//   warps 2-9     softmax of query tile 0, warps 10-17 of query tile 1: the same code and the same per-row
+//                 arithmetic as attn_prefill_tc_kernel (two warps per lane quarter, 64 keys each), so both kernels
+//                 return the same bits.
+// Under the conventional causal mask tile 0 sees one key tile fewer than tile 1.  Every wait is bounded.
+namespace fa2 {
+constexpr int BQ = 256, BKV = 128;
+constexpr int TILE_BYTES = fa::TILE_BYTES;
+constexpr int XCH = 2 * fa::XCH;                       // one exchange area per query tile
+constexpr int SMEM = 6 * TILE_BYTES + XCH + 256 + 1024;   // Q0, Q1, 2 x K, 2 x V
+constexpr int THREADS = 18 * 32;
+}  // namespace fa2
+
+__global__ void __launch_bounds__(fa2::THREADS, 1) attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                                        const __grid_constant__ CUtensorMap tmV, AttnDev a) {
+  using namespace fa2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                       // [2 query tiles]
+  uint8_t* sK = smem + 2 * TILE_BYTES;      // [2 stages]
+  uint8_t* sV = smem + 4 * TILE_BYTES;      // [2 stages]
+  float* xch = reinterpret_cast<float*>(smem + 6 * TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES + XCH);
+  uint64_t *k_full = bars, *k_empty = bars + 2, *v_full = bars + 4, *v_empty = bars + 6, *s_full = bars + 8, *p_full = bars + 10,
+           *o_done = bars + 12;   // two of each: ring stage for K / V, query tile for S / P / O
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;   // the long (late) query tiles first
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh_idx = head / a.group;
+  const int q0 = qt * BQ;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(k_full + i, 1);
+      mbar_init(k_empty + i, 1);
+      mbar_init(v_full + i, 1);
+      mbar_init(v_empty + i, 1);
+      mbar_init(s_full + i, 1);
+      mbar_init(p_full + i, 8);   // the eight softmax warps of a query tile
+      mbar_init(o_done + i, 1);
+    }
+    fence_barrier_init();
+    pdl_launch_dependents();
+  }
+  if (warp == 1) tc::alloc(tmem_slot, 512);
+  tc::fence_before();
+  __syncthreads();
+  tc::fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // q, k, v and positions come from the previous kernels
+
+  const int kv_len = kv_len_of(a, b);
+  const int ctx = kv_len - a.S;
+  // key tiles each query tile can see: all of them, or up to its last query's position; none for a tile past S
+  int nt[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int first = q0 + t * 128;
+    const int last_q = min(a.S, first + 128) - 1;
+    const int kv_end = a.causal ? min(kv_len, last_q + ctx + 1) : kv_len;
+    nt[t] = first < a.S ? (kv_end + BKV - 1) / BKV : 0;
+  }
+  const int nt_max = max(nt[0], nt[1]);
+
+  if (warp >= 2) {
+    // stage Q: 2 x 128 rows x 256 bytes into [tile][hd half][row][64 elements] with the 128-byte swizzle TMA would
+    // apply; 512 threads, half a row each
+    const int idx = threadIdx.x - 64;
+    const int r = idx & 127, hh = (idx >> 7) & 1, t = idx >> 8;
+    const int qi = q0 + t * 128 + r;
+    const bf16* qp = reinterpret_cast<const bf16*>(a.q) + (int64_t)b * a.q_sb + (int64_t)min(qi, a.S - 1) * a.q_ss + (int64_t)head * a.q_sh;
+#pragma unroll
+    for (int c8 = 0; c8 < 8; ++c8) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (qi < a.S) v = *reinterpret_cast<const uint4*>(qp + hh * 64 + c8 * 8);
+      *reinterpret_cast<uint4*>(sQ + t * TILE_BYTES + hh * (TILE_BYTES / 2) + swz128((uint32_t)r, (uint32_t)c8)) = v;
+    }
+    fence_proxy_async();  // the tensor core reads these bytes through the async proxy
+  }
+  __syncthreads();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      bool ok = true;
+      for (int j = 0; j < nt_max && ok; ++j) {
+        const int st = j & 1;
+        for (int kv = 0; kv < 2 && ok; ++kv) {  // K first, then V
+          uint64_t* full = (kv ? v_full : k_full) + st;
+          uint64_t* empty = (kv ? v_empty : k_empty) + st;
+          if (j >= 2 && !mbar_wait(empty, ((j >> 1) - 1) & 1, a.status)) {
+            ok = false;
+            break;
+          }
+          uint8_t* dst = (kv ? sV : sK) + st * TILE_BYTES;
+          mbar_expect_tx(full, TILE_BYTES);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int tk = min(j * BKV + half * 64, kv_len - 1) & ~63;   // a half tile past the end re-reads a valid page
+            const int row = (int)kv_row(a, b, kvh_idx, tk);
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_2d(dst + c * (TILE_BYTES / 2) + half * 8192, kv ? &tmV : &tmK, full, c * 64, row);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t idesc_pv = idesc_qk | (1u << 16);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool ok = true;
+      // S_t = Q_t K(j)^T into columns t * 128
+      auto issue_qk = [&](int t, int j) {
+        const uint32_t qa = q_addr + t * TILE_BYTES, ka = k_addr + (j & 1) * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {  // head_dim in steps of 16: two 64-element halves of four steps
+          const uint32_t off = (kk >> 2) * (TILE_BYTES / 2) + (kk & 3) * 32;
+          tc::umma_bf16_ss(tmem_base + t * 128, tc::smem_desc(qa + off, 16, 1024), tc::smem_desc(ka + off, 16, 1024), idesc_qk,
+                           kk > 0 ? 1u : 0u);
+        }
+        tc::commit(s_full + t);
+      };
+      if (nt_max > 0) {
+        ok = mbar_wait(k_full, 0, a.status);
+        if (ok) {
+          tc::fence_after();
+          for (int t = 0; t < 2; ++t)
+            if (nt[t] > 0) issue_qk(t, 0);
+          tc::commit(k_empty);
+        }
+      }
+      for (int j = 0; j < nt_max && ok; ++j) {
+        const int st = j & 1, ph = (j >> 1) & 1;
+        bool v_ready = false, k_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < nt[t]) {
+            ok = mbar_wait(p_full + t, j & 1, a.status);
+            if (ok && !v_ready) ok = v_ready = mbar_wait(v_full + st, ph, a.status);
+            if (!ok) break;
+            tc::fence_after();
+            const uint32_t va = v_addr + st * TILE_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)  // keys in steps of 16 = two 8-row swizzle atoms
+              tc::umma_bf16_ta(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8,
+                               tc::smem_desc(va + kk * 2048, TILE_BYTES / 2, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+            tc::commit(o_done + t);
+          }
+          if (j + 1 < nt[t]) {
+            if (!k_ready) ok = k_ready = mbar_wait(k_full + ((j + 1) & 1), ((j + 1) >> 1) & 1, a.status);
+            if (!ok) break;
+            tc::fence_after();
+            issue_qk(t, j + 1);
+          }
+        }
+        if (!ok) break;
+        tc::commit(v_empty + st);
+        if (j + 1 < nt_max) tc::commit(k_empty + ((j + 1) & 1));
+      }
+    }
+  } else {
+    // ---------------- softmax warps: query tile t, lane quarter = warp % 4, query row = quarter * 32 + lane,
+    // keys 64 half .. +63 of every key tile
+    const int t = (warp - 2) >> 3;
+    const int quarter = warp & 3, half = ((warp - 2) >> 2) & 1;
+    const int row = quarter * 32 + lane;
+    const int q0t = q0 + t * 128;
+    const int qi = q0t + row;
+    const int ntiles = nt[t];
+    const int qlim = a.causal ? qi + ctx : 0x7fffffff;   // last visible key
+    const uint32_t s_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + t * 128;
+    const uint32_t o_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256 + t * 128;
+    float* xmax = xch + t * (fa::XCH / 4);      // [2 buffers][2 halves][128 rows]
+    float* xsum = xmax + 2 * 2 * 128;           // [2 halves][128 rows]
+    const float sl2 = a.scale * 1.4426950408889634f;
+    float m = -INFINITY, l = 0.f;   // l: this half's share of the row sum (both halves share m)
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      if (ok) ok = mbar_wait(s_full + t, j & 1, a.status);
+      __syncwarp();  // the tensor-memory accesses below are warp-collective
+      tc::fence_after();
+      const int k0 = j * BKV + half * 64;
+      const bool edge = (a.causal && j * BKV + BKV - 1 > q0t + ctx) || (j * BKV + BKV > kv_len);
+      uint32_t r0[32], r1[32];
+      tc::ld32(s_addr + half * 64, r0);
+      tc::ld32(s_addr + half * 64 + 32, r1);
+      float mraw = -INFINITY;   // maximum of the raw scores (the scale is positive)
+      if (edge) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          if (k0 + e <= qlim && k0 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r0[e]));
+          if (k0 + 32 + e <= qlim && k0 + 32 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r1[e]));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mraw = fmaxf(mraw, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
+      }
+      float* xm = xmax + (j & 1) * 256;
+      xm[half * 128 + row] = mraw;
+      // after this barrier every score of the tile is in registers (P may overwrite S) and both half maxima are visible
+      if (t == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
+      mraw = fmaxf(mraw, xm[(half ^ 1) * 128 + row]);
+      const float mx = fmaxf(m, mraw * sl2);
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = ex2_approx(m - m_use);   // 0 on the first tile (m = -inf)
+      float lsum = 0.f;
+      uint32_t pk[16];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const uint32_t* rr = cc ? r1 : r0;
+        if (edge) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const int key = k0 + cc * 32 + e;
+            const float p0 = (key <= qlim && key < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use)) : 0.f;
+            const float p1 = (key + 1 <= qlim && key + 1 < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use)) : 0.f;
+            lsum += p0 + p1;
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use));
+            lsum += p0 + p1;
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
+        }
+        // P (bf16 pairs): keys 64 half + 32 cc .. +31 -> columns 32 half + 16 cc .. +15 of this tile's S
+        tc::st16(s_addr + half * 32 + cc * 16, pk);
+      }
+      l = l * alpha + lsum;
+      m = mx;
+      // O must be rescaled when this row's maximum moved; skip the TMEM round trip when no row of the warp needs it.
+      // s_full(j) was committed after P V of tile j - 1 was issued, so that product has landed in O by now.
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          tc::ld32(o_addr + half * 64 + c * 32, r0);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
+          tc::st32(o_addr + half * 64 + c * 32, r0);
+        }
+      }
+      tc::fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + t);
+    }
+    // ---------------- epilogue: O / l -> bf16 row (this warp's 64 of the 128 output columns)
+    xsum[half * 128 + row] = l;
+    if (t == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+    else asm volatile("bar.sync 2, 256;" ::: "memory");
+    l += xsum[(half ^ 1) * 128 + row];
+    if (ntiles > 0 && ok) ok = mbar_wait(o_done + t, (ntiles - 1) & 1, a.status);
+    __syncwarp();
+    tc::fence_after();
+    {
+      // tcgen05.ld is warp-collective: every lane takes part, only the rows that exist are stored
+      const bool store = qi < a.S && ok;
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      bf16* op = reinterpret_cast<bf16*>(a.out) + (int64_t)b * a.o_sb + (int64_t)min(qi, a.S - 1) * a.o_ss + (int64_t)head * a.o_sh +
+                 half * 64;
+      uint32_t r[32];
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        if (ntiles > 0) {
+          tc::ld32(o_addr + half * 64 + c * 32, r);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
+        if (store) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
+            *reinterpret_cast<uint4*>(op + c * 32 + e) = v;
+          }
+        }
+      }
+    }
+  }
+  tc::fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after();
+    tc::dealloc(tmem_base, 512);
+  }
+}
+
 int decode_splits(Ctx* c, int64_t B, int kvh) {
   if (const char* e = getenv("REW_B200_ATTN_SPLITS")) {  // tuning override
     const int v = atoi(e);
@@ -1025,6 +1329,17 @@ int attn_launch(Ctx* c, const AttnArgs& h) {
       RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::SMEM));
       RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
       tc_attr = true;
+    }
+    if (c->attn_pingpong && h.S >= 256) {
+      static bool tc2_attr = false;
+      if (!tc2_attr) {
+        RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa2::SMEM));
+        tc2_attr = true;
+      }
+      dim3 pgrid((unsigned)((h.S + fa2::BQ - 1) / fa2::BQ), (unsigned)h.nh, (unsigned)h.B);
+      RB_CUDA(launch_k(attn_prefill_tc2_kernel, pgrid, dim3(fa2::THREADS), (size_t)fa2::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));
+      ++g_launch_total;
+      return REWB200_OK;
     }
     dim3 tgrid((unsigned)((h.S + fa::BQ - 1) / fa::BQ), (unsigned)h.nh, (unsigned)h.B);
     RB_CUDA(launch_k(attn_prefill_tc_kernel, tgrid, dim3(fa::THREADS), (size_t)fa::SMEM, c->stream, c->use_pdl, *h.tmK, *h.tmV, a));

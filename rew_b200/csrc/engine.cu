@@ -529,7 +529,7 @@ int run_linear(rewb200_session* s, const LinW& w, const void* x, int64_t ldx, in
       }
     }
     if (ksplit_out) *ksplit_out = ks;
-    if (!partial && epi == EPI_SWIGLU_BF16 && rows <= 64 && w.N % 16 == 0) {
+    if (!partial && epi == EPI_SWIGLU_BF16 && rows <= 64 && w.N % 16 == 0 && c->gu_split) {
       // a gate|up with too few feature tiles to fill the GPU: split K, then sum + SwiGLU in a second small launch
       int kg = std::min(4, linear_bf16_pick_ksplit(c, rows, w.K, w.N));
       while (kg > 1 && (size_t)kg * rows * w.N * sizeof(float) > s->part_bytes) kg /= 2;

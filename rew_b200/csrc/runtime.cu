@@ -271,6 +271,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "ep_exchange") {
     RB_REQUIRE(v == "prefix" || v == "capacity" || v == "auto", "option ep_exchange: expected auto, prefix or capacity");
     c->ep_prefix = v == "prefix" ? 1 : (v == "capacity" ? 0 : 2);
+  } else if (k == "gate_up_split") {
+    RB_REQUIRE(v == "on" || v == "off", "option gate_up_split: expected on or off");
+    c->gu_split = v == "on";
   } else if (k == "qkv_post") {
     RB_REQUIRE(v == "attention" || v == "launch", "option qkv_post: expected attention or launch");
     c->attn_fuse_qkv = v == "attention";
@@ -300,8 +303,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     RB_REQUIRE(v == "cluster" || v == "row", "option norm: expected cluster or row");
     c->norm_cluster = v == "cluster";
   } else if (k == "attention") {
-    RB_REQUIRE(v == "tc" || v == "mma", "option attention: expected tc or mma");
-    c->attn_tc = v == "tc";
+    RB_REQUIRE(v == "tc" || v == "tc1" || v == "mma", "option attention: expected tc, tc1 or mma");
+    c->attn_tc = v != "mma";
+    c->attn_pingpong = v == "tc";
   } else if (k == "sampling") {
     RB_REQUIRE(v == "bucket" || v == "radix", "option sampling: expected bucket or radix");
     c->sampling_exact = v == "radix";

@@ -258,7 +258,7 @@ def test_swiglu_and_embedding(rb, orc):
 
 
 @pytest.mark.parametrize("B,nh,kvh,S,L", [(2, 8, 2, 512, 512), (1, 4, 4, 300, 300), (1, 8, 1, 130, 400), (3, 4, 2, 128, 128),
-                                          (1, 2, 2, 1000, 1000)])
+                                          (1, 2, 2, 1000, 1000), (2, 4, 2, 256, 256), (1, 4, 1, 384, 700)])
 @pytest.mark.parametrize("mode", ["plain", "standard"])
 def test_attention_bf16_prefill_tcgen05(rb, orc, B, nh, kvh, S, L, mode):
     """head_dim 128 and at least 128 queries: the tcgen05 kernel (S and O in tensor memory).  Ragged last
@@ -276,6 +276,10 @@ def test_attention_bf16_prefill_tcgen05(rb, orc, B, nh, kvh, S, L, mode):
     rb.set_option("attention", "mma")
     try:
         ref = rb.scaledDotProductAttention(*args).to_host()
+        rb.set_option("attention", "tc1")
+        one_tile = rb.scaledDotProductAttention(*args).to_host()
     finally:
         rb.set_option("attention", "tc")
     assert rel_l2(got, ref) < 1e-2   # two correct bf16 kernels agree far inside the tolerance
+    # one query tile per CTA and two query tiles per CTA (from 256 query rows up) do the same arithmetic per row
+    assert np.array_equal(got, one_tile)
