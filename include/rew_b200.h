@@ -88,6 +88,7 @@ int rewb200_sync(int slot, int timeout_ms);
  *   "inject_alloc_fail" = "n"                test hook: the n-th activation-buffer allocation from now fails on the host
  *   "moe_overlap" = "on" | "off"             MoE layers on one rank, steps of at most 64 rows: the shared experts run on a
  *                                            second stream beside the routed experts (default on)
+ *   "splitk_min_blocks" = "1".."64"          fewest 64-wide K blocks a split-K slice keeps (default 8)
  *   "splitk_rows" = "0".."256"               largest step, in rows, whose Linear launches may split K (default 256)
  *   "splitk" = "slabs" | "cluster" | "qkv" | "out"   decode-size split-K: f32 slabs summed by the next kernel (default),
  *                                            or summed inside thread-block clusters through distributed shared memory

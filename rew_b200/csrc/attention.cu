@@ -665,6 +665,163 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Named barrier of 64 threads with a literal id (a register id makes ptxas reserve all 16 barriers of the SM).
+__device__ __forceinline__ void pair_sync(int id) {
+  switch (id) {
+    case 1: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 3: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    case 4: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+    case 5: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
+    case 6: asm volatile("bar.sync 6, 64;" ::: "memory"); break;
+    case 7: asm volatile("bar.sync 7, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 8, 64;" ::: "memory"); break;
+  }
+}
+
+// Online softmax of one query tile of the tcgen05 prefill kernels, as run by one warp: lane quarter `quarter` (the 32
+// tensor-memory lanes = query rows this warp may touch), keys 64 half .. +63 of every 128-key tile.  S (f32 scores)
+// sits at s_addr, O (f32) at o_addr.  The two warps of a lane quarter exchange their half-row maxima through
+// shared memory and meet at their own named barrier `pair_bar` (64 threads): P (bf16 pairs) overwrites the score
+// columns, and half 1's P lands on columns whose scores belong to half 0, so half 0 must have read them first.
+// The four quarters of a tile never wait for each other, which keeps their exp2 phases apart.
+// Both kernels call this, so they return the same bits.
+__device__ __forceinline__ void fa_softmax_warp(const AttnDev& a, uint32_t s_addr, uint32_t o_addr, float* xmax, float* xsum,
+                                                uint64_t* s_full, uint64_t* p_full, uint64_t* o_done, int ntiles, int q0t,
+                                                int ctx, int kv_len, int quarter, int half, int lane, int pair_bar, int b,
+                                                int head) {
+  constexpr int BKV = 128;
+  const int row = quarter * 32 + lane;
+  const int qi = q0t + row;
+  const int qlim = a.causal ? qi + ctx : 0x7fffffff;   // last visible key
+  const float sl2 = a.scale * 1.4426950408889634f;
+  float m = -INFINITY, l = 0.f;   // l: this half's share of the row sum (both halves share m)
+  bool ok = true;
+  for (int j = 0; j < ntiles; ++j) {
+    if (ok) ok = mbar_wait(s_full, j & 1, a.status);
+    __syncwarp();  // the tensor-memory accesses below are warp-collective
+    tc::fence_after();
+    const int k0 = j * BKV + half * 64;
+    // only the last tile or two of a query block contain masked keys; the test is the same for every
+    // thread of the tile, so the common tile runs without a compare per element
+    const bool edge = (a.causal && j * BKV + BKV - 1 > q0t + ctx) || (j * BKV + BKV > kv_len);
+    uint32_t r0[32], r1[32];
+    tc::ld32_issue(s_addr + half * 64, r0);
+    tc::ld32_issue(s_addr + half * 64 + 32, r1);
+    tc::wait_ld();
+    float mraw;   // maximum of the raw scores (the scale is positive)
+    if (edge) {
+      mraw = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        if (k0 + e <= qlim && k0 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r0[e]));
+        if (k0 + 32 + e <= qlim && k0 + 32 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r1[e]));
+      }
+    } else {
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains of three-input maxima
+#pragma unroll
+      for (int e = 0; e < 32; e += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = max3(mx4[u], __uint_as_float(r0[e + u]), __uint_as_float(r1[e + u]));
+      }
+      mraw = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    }
+    float* xm = xmax + (j & 1) * 256;
+    xm[half * 128 + row] = mraw;
+    // after this barrier both warps of the quarter hold their scores in registers and both half maxima are visible
+    pair_sync(pair_bar);
+    mraw = fmaxf(mraw, xm[(half ^ 1) * 128 + row]);
+    const float mx = fmaxf(m, mraw * sl2);
+    const float m_use = (mx == -INFINITY) ? 0.f : mx;
+    const float alpha = ex2_approx(m - m_use);   // 0 on the first tile (m = -inf)
+    float ls[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t pk[32];
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      const uint32_t* rr = cc ? r1 : r0;
+      if (edge) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const int key = k0 + cc * 32 + e;
+          const float p0 = (key <= qlim && key < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use)) : 0.f;
+          const float p1 = (key + 1 <= qlim && key + 1 < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use)) : 0.f;
+          ls[(e >> 1) & 3] += p0 + p1;
+          pk[cc * 16 + (e >> 1)] = pack_bf16(p0, p1);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use));
+          ls[(e >> 1) & 3] += p0 + p1;
+          pk[cc * 16 + (e >> 1)] = pack_bf16(p0, p1);
+        }
+      }
+    }
+    // P (bf16 pairs): keys 64 half .. +63 -> columns 32 half .. +31 of this tile's S
+    tc::st32(s_addr + half * 32, pk);
+    l = l * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+    m = mx;
+    // O must be rescaled when this row's maximum moved; skip the TMEM round trip when no row of the warp needs it.
+    // s_full(j) was committed after P V of tile j - 1 was issued, so that product has landed in O by now.
+    if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      tc::ld32_issue(o_addr + half * 64, r0);
+      tc::ld32_issue(o_addr + half * 64 + 32, r1);
+      tc::wait_ld();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
+        r1[e] = __float_as_uint(__uint_as_float(r1[e]) * alpha);
+      }
+      tc::st32_issue(o_addr + half * 64, r0);
+      tc::st32_issue(o_addr + half * 64 + 32, r1);
+      tc::wait_st();
+    }
+    tc::fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(p_full);
+  }
+  // ---------------- epilogue: O / l -> bf16 row (this warp's 64 of the 128 output columns)
+  xsum[half * 128 + row] = l;
+  pair_sync(pair_bar);
+  l += xsum[(half ^ 1) * 128 + row];
+  if (ntiles > 0 && ok) ok = mbar_wait(o_done, (ntiles - 1) & 1, a.status);
+  __syncwarp();
+  tc::fence_after();
+  // tcgen05.ld is warp-collective: every lane takes part, only the rows that exist are stored
+  const bool store = qi < a.S && ok;
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  bf16* op = reinterpret_cast<bf16*>(a.out) + (int64_t)b * a.o_sb + (int64_t)min(qi, a.S - 1) * a.o_ss + (int64_t)head * a.o_sh +
+             half * 64;
+  uint32_t r[32];
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    if (ntiles > 0) {
+      tc::ld32(o_addr + half * 64 + c * 32, r);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) r[e] = 0u;
+    }
+    if (store) {
+#pragma unroll
+      for (int e = 0; e < 32; e += 8) {
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
+        v.y = pack_bf16(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+        v.z = pack_bf16(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
+        v.w = pack_bf16(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
+        *reinterpret_cast<uint4*>(op + c * 32 + e) = v;
+      }
+    }
+  }
+}
+
 namespace fa {
 constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE_BYTES = BKV * HD * 2;            // 32 KB: [hd half][128 rows][64 elements]
@@ -791,122 +948,11 @@ __global__ void __launch_bounds__(fa::THREADS, 2) attn_prefill_tc_kernel(const _
       }
     }
   } else {
-    // ---------------- softmax warps: lane quarter = warp % 4, query row = quarter * 32 + lane, keys 64 half .. +63
+    // ---------------- softmax warps: lane quarter = warp % 4, keys 64 half .. +63 of every key tile
     const int quarter = warp & 3, half = (warp - 2) >> 2;
-    const int row = quarter * 32 + lane;
-    const int qi = q0 + row;
-    const int qlim = a.causal ? qi + ctx : 0x7fffffff;   // last visible key
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const float sl2 = a.scale * 1.4426950408889634f;
-    float m = -INFINITY, l = 0.f;   // l: this half's share of the row sum (both halves share m)
-    bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      if (ok) ok = mbar_wait(s_full, j & 1, a.status);
-      __syncwarp();  // the tensor-memory accesses below are warp-collective
-      tc::fence_after();
-      const int k0 = j * BKV + half * 64;
-      // only the last tile or two of a query block contain masked keys; the test is the same for every
-      // thread of the CTA, so the common tile runs without a compare per element
-      const bool edge = (a.causal && j * BKV + BKV - 1 > q0 + ctx) || (j * BKV + BKV > kv_len);
-      uint32_t r0[32], r1[32];
-      tc::ld32(lane_addr + half * 64, r0);
-      tc::ld32(lane_addr + half * 64 + 32, r1);
-      float mraw = -INFINITY;   // maximum of the raw scores (the scale is positive)
-      if (edge) {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          if (k0 + e <= qlim && k0 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r0[e]));
-          if (k0 + 32 + e <= qlim && k0 + 32 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r1[e]));
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) mraw = fmaxf(mraw, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
-      }
-      float* xm = xmax + (j & 1) * 256;
-      xm[half * 128 + row] = mraw;
-      // after this barrier every score of the tile is in registers (P may overwrite S) and both half maxima are visible
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      mraw = fmaxf(mraw, xm[(half ^ 1) * 128 + row]);
-      const float mx = fmaxf(m, mraw * sl2);
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = ex2_approx(m - m_use);   // 0 on the first tile (m = -inf)
-      float lsum = 0.f;
-      uint32_t pk[16];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const uint32_t* rr = cc ? r1 : r0;
-        if (edge) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int key = k0 + cc * 32 + e;
-            const float p0 = (key <= qlim && key < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use)) : 0.f;
-            const float p1 = (key + 1 <= qlim && key + 1 < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use)) : 0.f;
-            lsum += p0 + p1;
-            pk[e >> 1] = pack_bf16(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use));
-            lsum += p0 + p1;
-            pk[e >> 1] = pack_bf16(p0, p1);
-          }
-        }
-        // P (bf16 pairs): keys 64 half + 32 cc .. +31 -> columns 32 half + 16 cc .. +15
-        tc::st16(lane_addr + half * 32 + cc * 16, pk);
-      }
-      l = l * alpha + lsum;
-      m = mx;
-      // O must be rescaled when this row's maximum moved; skip the TMEM round trip when no row of the warp needs it
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          tc::ld32(lane_addr + 128 + half * 64 + c * 32, r0);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
-          tc::st32(lane_addr + 128 + half * 64 + c * 32, r0);
-        }
-      }
-      tc::fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-    }
-    // ---------------- epilogue: O / l -> bf16 row (this warp's 64 of the 128 output columns)
-    xsum[half * 128 + row] = l;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    l += xsum[(half ^ 1) * 128 + row];
-    if (ntiles > 0 && ok) ok = mbar_wait(o_done, (ntiles - 1) & 1, a.status);
-    __syncwarp();
-    tc::fence_after();
-    {
-      // tcgen05.ld is warp-collective: every lane takes part, only the rows that exist are stored
-      const bool store = qi < a.S && ok;
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      bf16* op = reinterpret_cast<bf16*>(a.out) + (int64_t)b * a.o_sb + (int64_t)min(qi, a.S - 1) * a.o_ss + (int64_t)head * a.o_sh +
-                 half * 64;
-      uint32_t r[32];
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        if (ntiles > 0) {
-          tc::ld32(lane_addr + 128 + half * 64 + c * 32, r);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = 0u;
-        }
-        if (store) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c * 32 + e) = v;
-          }
-        }
-      }
-    }
+    fa_softmax_warp(a, lane_addr, lane_addr + 128, xmax, xsum, s_full, p_full, o_done, ntiles, q0, ctx, kv_len, quarter, half,
+                    lane, 1 + quarter, b, head);
   }
   tc::fence_before();
   __syncthreads();
@@ -1039,13 +1085,17 @@ __global__ void __launch_bounds__(fa2::THREADS, 1) attn_prefill_tc2_kernel(const
       const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       bool ok = true;
       // S_t = Q_t K(j)^T into columns t * 128
+      // descriptor words once; inside the loops an operand moves by one 32-bit add
+      constexpr uint32_t hi = tc::desc_hi(1024);
+      const uint32_t q_lo = tc::desc_lo(q_addr, 16), k_lo = tc::desc_lo(k_addr, 16), v_lo = tc::desc_lo(v_addr, TILE_BYTES / 2);
       auto issue_qk = [&](int t, int j) {
-        const uint32_t qa = q_addr + t * TILE_BYTES, ka = k_addr + (j & 1) * TILE_BYTES;
+        const uint32_t qa = q_lo + t * (TILE_BYTES >> 4), ka = k_lo + (j & 1) * (TILE_BYTES >> 4);
+        const uint32_t d = tmem_base + t * 128;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {  // head_dim in steps of 16: two 64-element halves of four steps
-          const uint32_t off = (kk >> 2) * (TILE_BYTES / 2) + (kk & 3) * 32;
-          tc::umma_bf16_ss(tmem_base + t * 128, tc::smem_desc(qa + off, 16, 1024), tc::smem_desc(ka + off, 16, 1024), idesc_qk,
-                           kk > 0 ? 1u : 0u);
+          constexpr uint32_t half_step = (TILE_BYTES / 2) >> 4;
+          const uint32_t off = (kk >> 2) * half_step + (kk & 3) * 2;
+          tc::umma_bf16_ss_lh(d, qa + off, ka + off, hi, idesc_qk, kk > 0 ? 1u : 0u);
         }
         tc::commit(s_full + t);
       };
@@ -1067,11 +1117,12 @@ __global__ void __launch_bounds__(fa2::THREADS, 1) attn_prefill_tc2_kernel(const
             if (ok && !v_ready) ok = v_ready = mbar_wait(v_full + st, ph, a.status);
             if (!ok) break;
             tc::fence_after();
-            const uint32_t va = v_addr + st * TILE_BYTES;
+            const uint32_t va = v_lo + st * (TILE_BYTES >> 4);
+            const uint32_t pa = tmem_base + t * 128, od = tmem_base + 256 + t * 128;
+            const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk)  // keys in steps of 16 = two 8-row swizzle atoms
-              tc::umma_bf16_ta(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8,
-                               tc::smem_desc(va + kk * 2048, TILE_BYTES / 2, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+              tc::umma_bf16_ta_lh(od, pa + kk * 8, va + kk * (2048 >> 4), hi, idesc_pv, kk > 0 ? 1u : acc0);
             tc::commit(o_done + t);
           }
           if (j + 1 < nt[t]) {
@@ -1087,130 +1138,15 @@ __global__ void __launch_bounds__(fa2::THREADS, 1) attn_prefill_tc2_kernel(const
       }
     }
   } else {
-    // ---------------- softmax warps: query tile t, lane quarter = warp % 4, query row = quarter * 32 + lane,
-    // keys 64 half .. +63 of every key tile
+    // ---------------- softmax warps: query tile t, lane quarter = warp % 4, keys 64 half .. +63 of every key tile
     const int t = (warp - 2) >> 3;
     const int quarter = warp & 3, half = ((warp - 2) >> 2) & 1;
-    const int row = quarter * 32 + lane;
-    const int q0t = q0 + t * 128;
-    const int qi = q0t + row;
-    const int ntiles = nt[t];
-    const int qlim = a.causal ? qi + ctx : 0x7fffffff;   // last visible key
     const uint32_t s_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + t * 128;
     const uint32_t o_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256 + t * 128;
     float* xmax = xch + t * (fa::XCH / 4);      // [2 buffers][2 halves][128 rows]
     float* xsum = xmax + 2 * 2 * 128;           // [2 halves][128 rows]
-    const float sl2 = a.scale * 1.4426950408889634f;
-    float m = -INFINITY, l = 0.f;   // l: this half's share of the row sum (both halves share m)
-    bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      if (ok) ok = mbar_wait(s_full + t, j & 1, a.status);
-      __syncwarp();  // the tensor-memory accesses below are warp-collective
-      tc::fence_after();
-      const int k0 = j * BKV + half * 64;
-      const bool edge = (a.causal && j * BKV + BKV - 1 > q0t + ctx) || (j * BKV + BKV > kv_len);
-      uint32_t r0[32], r1[32];
-      tc::ld32(s_addr + half * 64, r0);
-      tc::ld32(s_addr + half * 64 + 32, r1);
-      float mraw = -INFINITY;   // maximum of the raw scores (the scale is positive)
-      if (edge) {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          if (k0 + e <= qlim && k0 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r0[e]));
-          if (k0 + 32 + e <= qlim && k0 + 32 + e < kv_len) mraw = fmaxf(mraw, __uint_as_float(r1[e]));
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) mraw = fmaxf(mraw, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
-      }
-      float* xm = xmax + (j & 1) * 256;
-      xm[half * 128 + row] = mraw;
-      // after this barrier every score of the tile is in registers (P may overwrite S) and both half maxima are visible
-      if (t == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
-      else asm volatile("bar.sync 2, 256;" ::: "memory");
-      mraw = fmaxf(mraw, xm[(half ^ 1) * 128 + row]);
-      const float mx = fmaxf(m, mraw * sl2);
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = ex2_approx(m - m_use);   // 0 on the first tile (m = -inf)
-      float lsum = 0.f;
-      uint32_t pk[16];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const uint32_t* rr = cc ? r1 : r0;
-        if (edge) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int key = k0 + cc * 32 + e;
-            const float p0 = (key <= qlim && key < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use)) : 0.f;
-            const float p1 = (key + 1 <= qlim && key + 1 < kv_len) ? ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use)) : 0.f;
-            lsum += p0 + p1;
-            pk[e >> 1] = pack_bf16(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(rr[e]), sl2, -m_use));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(rr[e + 1]), sl2, -m_use));
-            lsum += p0 + p1;
-            pk[e >> 1] = pack_bf16(p0, p1);
-          }
-        }
-        // P (bf16 pairs): keys 64 half + 32 cc .. +31 -> columns 32 half + 16 cc .. +15 of this tile's S
-        tc::st16(s_addr + half * 32 + cc * 16, pk);
-      }
-      l = l * alpha + lsum;
-      m = mx;
-      // O must be rescaled when this row's maximum moved; skip the TMEM round trip when no row of the warp needs it.
-      // s_full(j) was committed after P V of tile j - 1 was issued, so that product has landed in O by now.
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          tc::ld32(o_addr + half * 64 + c * 32, r0);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
-          tc::st32(o_addr + half * 64 + c * 32, r0);
-        }
-      }
-      tc::fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full + t);
-    }
-    // ---------------- epilogue: O / l -> bf16 row (this warp's 64 of the 128 output columns)
-    xsum[half * 128 + row] = l;
-    if (t == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
-    else asm volatile("bar.sync 2, 256;" ::: "memory");
-    l += xsum[(half ^ 1) * 128 + row];
-    if (ntiles > 0 && ok) ok = mbar_wait(o_done + t, (ntiles - 1) & 1, a.status);
-    __syncwarp();
-    tc::fence_after();
-    {
-      // tcgen05.ld is warp-collective: every lane takes part, only the rows that exist are stored
-      const bool store = qi < a.S && ok;
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      bf16* op = reinterpret_cast<bf16*>(a.out) + (int64_t)b * a.o_sb + (int64_t)min(qi, a.S - 1) * a.o_ss + (int64_t)head * a.o_sh +
-                 half * 64;
-      uint32_t r[32];
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        if (ntiles > 0) {
-          tc::ld32(o_addr + half * 64 + c * 32, r);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = 0u;
-        }
-        if (store) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c * 32 + e) = v;
-          }
-        }
-      }
-    }
+    fa_softmax_warp(a, s_addr, o_addr, xmax, xsum, s_full + t, p_full + t, o_done + t, nt[t], q0 + t * 128, ctx, kv_len, quarter,
+                    half, lane, 1 + t * 4 + quarter, b, head);
   }
   tc::fence_before();
   __syncthreads();

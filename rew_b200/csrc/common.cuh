@@ -58,6 +58,7 @@ struct Ctx {
   int linear_impl = 2;       // bf16 Linear: 0 mma.sync, 1 tcgen05 when rows > 32, 2 tcgen05 always (default)
   bool prefill_persistent = true;  // 256-token Linear tiles on the persistent kernel with overlapped epilogue
   bool prefill_pair = true;        // ... on pairs of CTAs (tcgen05 cta_group::2, 256 x 256 tiles) when the width is a multiple of 256
+  int splitk_min_blocks = 8;  // a K slice keeps at least this many 64-wide blocks (a CTA's pipeline needs a few to ramp)
   int splitk_max_rows = 256;  // largest step (rows) whose Linear launches may split K
   int profile_mask = 31;      // rewb200_session_profile_linears: bit 0 q|k|v, 1 o, 2 gate|up, 3 down, 4 lm_head
   int splitk_cluster = 0;     // decode-size split-K summed inside thread-block clusters instead of through f32 slabs: bit 0 the q|k|v launch, bit 1 the others (off: measured slower)

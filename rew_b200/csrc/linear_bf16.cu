@@ -289,7 +289,9 @@ int linear_bf16_pick_ksplit(Ctx* c, int64_t M, int64_t K, int64_t N) {
   const int cap = M <= 64 ? 16 : (M <= 128 ? 4 : 2);
   int split = 1;
   // stop doubling once the CTA count would overshoot the resident slots by more than a quarter
-  while (tiles * split * 2 <= target + target / 4 && nkb / (split * 2) >= 8 && split < cap) split *= 2;
+  while (tiles * split * 2 <= target + target / 4 && nkb / (split * 2) >= c->splitk_min_blocks && split < cap) split *= 2;
+  // a launch that still leaves SMs empty (narrow layers of a tensor-parallel shard) may cut K finer
+  while (tiles * split < c->sm_count && nkb / (split * 2) >= std::min(4, c->splitk_min_blocks) && split < cap) split *= 2;
   return split;
 }
 

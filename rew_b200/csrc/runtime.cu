@@ -296,6 +296,10 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     const int r = atoi(v.c_str());
     RB_REQUIRE(r >= 0 && r <= 256, "option splitk_rows: 0..256");
     c->splitk_max_rows = r;
+  } else if (k == "splitk_min_blocks") {
+    const int r = atoi(v.c_str());
+    RB_REQUIRE(r >= 1 && r <= 64, "option splitk_min_blocks: 1..64");
+    c->splitk_min_blocks = r;
   } else if (k == "splitk") {
     RB_REQUIRE(v == "cluster" || v == "slabs" || v == "qkv" || v == "out", "option splitk: expected cluster, slabs, qkv or out");
     c->splitk_cluster = v == "cluster" ? 3 : v == "qkv" ? 1 : v == "out" ? 2 : 0;
