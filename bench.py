@@ -73,8 +73,11 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """Samples nvidia-smi clocks, power and throttle reasons while the timed region runs.  nvidia-smi needs a
+    moment to come up, so it is started ahead of the warm-up steps; every sample carries a timestamp and only
+    those inside [mark_begin, mark_end] count.  A region too short to catch two samples (a few decode steps)
+    widens to the warm-up steps before it, which run the same launches; `window` says which was used."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -82,48 +85,66 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.t_warm = self.t0 = self.t1 = None
 
     def start(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+        self.t_warm = time.time()
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if not self.proc:
             return out
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        import datetime
+        rows = []
         try:
             for line in open(self.path):
                 f = [x.strip() for x in line.split(",")]
                 if len(f) < 9:
                     continue
                 try:
-                    sm.append(float(f[1]))
-                    mx.append(float(f[2]))
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(f[1]), float(f[2]), float(f[3]), [v.lower().startswith("active") for v in f[5:9]]))
                 except ValueError:
                     continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
             os.unlink(self.path)
         except Exception:
             pass
-        if sm:
-            out["sm_mhz"] = float(np.median(sm))
-            out["sm_max_mhz"] = float(max(mx))
-        out["reasons"] = sorted(reasons)
+        t0, t1 = self.t0 or 0.0, self.t1 or time.time()
+        pick = [r for r in rows if t0 <= r[0] <= t1]
+        window = "timed region"
+        if len(pick) < 2:
+            pick = [r for r in rows if (self.t_warm or 0.0) <= r[0] <= t1]
+            window = "warm-up + timed region (the timed region alone caught %d samples)" % len([r for r in rows if t0 <= r[0] <= t1])
+        if not pick:
+            pick, window = rows, "all samples"
+        if pick:
+            out["sm_mhz"] = float(np.median([r[1] for r in pick]))
+            out["sm_max_mhz"] = float(max(r[2] for r in pick))
+            out["power_w"] = float(np.median([r[3] for r in pick]))
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            out["reasons"] = sorted({n for r in pick for n, a in zip(names, r[4]) if a})
+            out["samples"] = len(pick)
+            out["window"] = window
         return out
 
 
@@ -327,18 +348,21 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     # ---- device-resident decode: prefill, W warm-up steps, K timed steps
     sess.forward(prompt)
     prefill_ms, _ = sess.last_ms()
+    L.rewb200_sync(0, 0)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     if Wm > 0:
         sess.decode(Wm)
     if pg:
         pg.barrier()
     L.rewb200_sync(0, 0)
     launches0 = L.rewb200_launch_count(0)
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     sess.decode(K)
     _, decode_ms = sess.last_ms()
     L.rewb200_sync(0, 0)
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     launches = L.rewb200_launch_count(0) - launches0
 
