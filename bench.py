@@ -79,7 +79,7 @@ class ClockSampler:
     widens to the warm-up steps before it, which run the same launches; `window` says which was used."""
     Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_power_cap,enforced.power.limit")
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
@@ -123,7 +123,8 @@ class ClockSampler:
                     continue
                 try:
                     ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
-                    rows.append((ts, float(f[1]), float(f[2]), float(f[3]), [v.lower().startswith("active") for v in f[5:9]]))
+                    rows.append((ts, float(f[1]), float(f[2]), float(f[3]), [v.lower().startswith("active") for v in f[5:9]],
+                                 f[9] if len(f) > 9 else ""))
                 except ValueError:
                     continue
             os.unlink(self.path)
@@ -141,6 +142,10 @@ class ClockSampler:
             out["sm_mhz"] = float(np.median([r[1] for r in pick]))
             out["sm_max_mhz"] = float(max(r[2] for r in pick))
             out["power_w"] = float(np.median([r[3] for r in pick]))
+            try:
+                out["power_limit_w"] = float(pick[0][5])     # read only: the limit this GPU is run under
+            except ValueError:
+                pass
             names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
             out["reasons"] = sorted({n for r in pick for n, a in zip(names, r[4]) if a})
             out["samples"] = len(pick)
@@ -248,7 +253,7 @@ def run_attention_op(args, rank, local_rank):
         key, _, val = kv.partition("=")
         api.set_option(key, val)
     L = _lib.lib()
-    B, nh, kvh, hd, S = 8, 32, 8, 128, 4096
+    B, nh, kvh, hd, S = 8, 32, 8, 128, args.positions
     rng = np.random.default_rng(0)
     T = api.Tensor.from_host
     k = T(rng.standard_normal((B, kvh, S, hd)).astype(np.float32), dtype=_lib.BF16)
@@ -276,7 +281,7 @@ def run_attention_op(args, rank, local_rank):
             "warmup": args.warmup, "ms_per_step": out["prefill"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "attn_op", "batch": B, "q_heads": nh, "kv_heads": kvh, "head_dim": hd, "positions": S,
-                       "l2": "K and V (134 MB) exceed the 126 MB L2"},
+                       "l2": "K and V (%d MB) %s the 126 MB L2" % (kv_bytes / 1e6, "exceed" if kv_bytes > 126e6 else "fit")},
             "prefill": {"ms": out["prefill"], "tflops": tfs, "frac_of_bf16_peak": tfs / tf_peak, "flops": flops},
             "decode": {"ms": out["decode"], "gbs": gbs, "frac_of_hbm_peak": gbs / hbm, "bytes": kv_bytes},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None,
@@ -499,6 +504,7 @@ def main():
     ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
                     help="run-time switch passed to rewb200_set_option, e.g. norm=row (repeatable)")
     ap.add_argument("--trace", action="store_true", help="add per-category device times of a decode step to every record")
+    ap.add_argument("--positions", type=int, default=4096, help="attn_op only: query / key positions per sequence")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "top_k", "top_p"],
                     help="next-token rule of the decode step; greedy is the metric's configuration")

@@ -97,8 +97,9 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            statistics through distributed shared memory (default), or one CTA per row
  *   "attention_merge" = "launch" | "fused"   split-KV decode attention: a second launch combines the splits (default),
  *                                            or the last CTA of a (sequence, kv head) does
- *   "attention" = "tc" | "tc1" | "mma"       prefill attention with head_dim 128: tcgen05, two query tiles per CTA from
- *                                            256 query rows up (default); tcgen05, one query tile per CTA; mma.sync
+ *   "attention" = "tc" | "tc1" | "tc2" | "mma"   prefill attention with head_dim 128: tcgen05, one query tile per CTA below
+ *                                            3072 query rows and two from there up (default); always one; two from 256
+ *                                            rows up; mma.sync
  *   "sampling" = "bucket" | "radix"          top-k / top-p selection: bucket histograms with the
  *                                            radix select as the exact fallback (default), or
  *                                            the radix select always

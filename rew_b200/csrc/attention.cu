@@ -1266,7 +1266,9 @@ int attn_launch(Ctx* c, const AttnArgs& h) {
       RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
       tc_attr = true;
     }
-    if (c->attn_pingpong && h.S >= 256) {
+    // two query tiles per CTA pay from about 4096 query rows (a K / V tile then serves 256 rows and the L2 -> SM
+    // traffic halves); below that the one-tile kernel with two CTAs per SM hides its prologue and tail better
+    if (c->attn_pingpong && h.S >= c->attn_pingpong_min_rows) {
       static bool tc2_attr = false;
       if (!tc2_attr) {
         RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fa2::SMEM));

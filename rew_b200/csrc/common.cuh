@@ -63,7 +63,8 @@ struct Ctx {
   int profile_mask = 31;      // rewb200_session_profile_linears: bit 0 q|k|v, 1 o, 2 gate|up, 3 down, 4 lm_head
   int splitk_cluster = 0;     // decode-size split-K summed inside thread-block clusters instead of through f32 slabs: bit 0 the q|k|v launch, bit 1 the others (off: measured slower)
   bool norm_cluster = true;   // decode-size residual+norm on clusters of four CTAs per row
-  bool attn_pingpong = true;  // ... with two query tiles per CTA sharing the K / V tiles (256 or more query rows)
+  bool attn_pingpong = true;  // ... with two query tiles per CTA sharing the K / V tiles, from this many query rows up
+  int attn_pingpong_min_rows = 3072;
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
   bool gu_split = true;         // decode-size gate|up launches with too few feature tiles split K (slabs + a sum-and-SwiGLU launch)

@@ -307,9 +307,10 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     RB_REQUIRE(v == "cluster" || v == "row", "option norm: expected cluster or row");
     c->norm_cluster = v == "cluster";
   } else if (k == "attention") {
-    RB_REQUIRE(v == "tc" || v == "tc1" || v == "mma", "option attention: expected tc, tc1 or mma");
+    RB_REQUIRE(v == "tc" || v == "tc1" || v == "tc2" || v == "mma", "option attention: expected tc, tc1, tc2 or mma");
     c->attn_tc = v != "mma";
-    c->attn_pingpong = v == "tc";
+    c->attn_pingpong = v == "tc" || v == "tc2";
+    c->attn_pingpong_min_rows = v == "tc2" ? 256 : 3072;
   } else if (k == "sampling") {
     RB_REQUIRE(v == "bucket" || v == "radix", "option sampling: expected bucket or radix");
     c->sampling_exact = v == "radix";

@@ -334,3 +334,34 @@ def test_qkv_finish_inside_attention_equals_the_separate_launch(rb):
                 rb.set_option("qkv_post", "attention")
         assert np.array_equal(outs[0][0], outs[1][0])
         assert np.array_equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("key,other,default", [("gate_up_split", "off", "on"), ("splitk_min_blocks", "2", "8")])
+def test_decode_splitk_policy_switches_agree(rb, orc, key, other, default):
+    """gate_up_split=off keeps a narrow gate|up launch in one piece (SwiGLU in the GEMM epilogue) instead of
+    K slices + a sum-and-SwiGLU launch; splitk_min_blocks lets a K slice get shorter.  Both change only the order
+    in which f32 partial sums are added, so logits agree far inside the bf16 tolerance, and both settings stay
+    within it against the oracle."""
+    from rew_b200 import _lib
+    cfg = W.ModelConfig(vocab=512, d_model=2048, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1024, max_seq=128,
+                        theta=500000.0, dtype=_lib.BF16, mask_kind=1)
+    t = [orc.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(cfg, seed=13, std=0.03, trivial_affine=False)]
+    B, S = 4, 9
+    prompt = np.random.default_rng(14).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+    outs = {}
+    for val in (default, other):
+        rb.set_option(key, val)
+        try:
+            sess = rb.CausalLM(cfg).load(t).session(B, 64)
+            nxt, _ = sess.forward(prompt, want_logits=True)
+            ids, last = sess.decode(3, want_logits=True)
+            outs[val] = (nxt, ids, last)
+        finally:
+            rb.set_option(key, default)
+    a, b = outs[default], outs[other]
+    if np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]):
+        assert rel_l2(a[2], b[2]) <= 5e-3
+    for nxt, ids, last in (a, b):
+        seq = np.concatenate([prompt, nxt[:, None], ids[:, :2]], 1)
+        want = orc.model_forward(cfg, t, seq, 0, True)[:, -1]
+        assert rel_l2(last, want) <= 2e-2

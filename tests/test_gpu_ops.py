@@ -221,8 +221,15 @@ def test_attention_config2_bf16_prefill_shape(rb, orc):
     q = orc.bf16_round(rng.standard_normal(size=(B, nh, S, hd), dtype=np.float32))
     k = orc.bf16_round(rng.standard_normal(size=(B, kvh, S, hd), dtype=np.float32))
     v = orc.bf16_round(rng.standard_normal(size=(B, kvh, S, hd), dtype=np.float32))
-    got = rb.scaledDotProductAttention(T(rb, q, _lib.BF16), T(rb, k, _lib.BF16), T(rb, v, _lib.BF16), True, 1).to_host()
+    args = (T(rb, q, _lib.BF16), T(rb, k, _lib.BF16), T(rb, v, _lib.BF16), True, 1)
+    got = rb.scaledDotProductAttention(*args).to_host()     # 4096 rows: two query tiles per CTA
     assert np.isfinite(got).all()
+    rb.set_option("attention", "tc1")
+    try:
+        one_tile = rb.scaledDotProductAttention(*args).to_host()
+    finally:
+        rb.set_option("attention", "tc")
+    assert np.array_equal(got, one_tile)
     g = nh // kvh
     for b, groups in ((3, (0, kvh - 1)), (B - 1, (0,))):
         heads = np.concatenate([np.arange(kg * g, (kg + 1) * g) for kg in groups])
@@ -276,10 +283,11 @@ def test_attention_bf16_prefill_tcgen05(rb, orc, B, nh, kvh, S, L, mode):
     rb.set_option("attention", "mma")
     try:
         ref = rb.scaledDotProductAttention(*args).to_host()
-        rb.set_option("attention", "tc1")
-        one_tile = rb.scaledDotProductAttention(*args).to_host()
+        rb.set_option("attention", "tc2")
+        two_tiles = rb.scaledDotProductAttention(*args).to_host()
     finally:
         rb.set_option("attention", "tc")
     assert rel_l2(got, ref) < 1e-2   # two correct bf16 kernels agree far inside the tolerance
-    # one query tile per CTA and two query tiles per CTA (from 256 query rows up) do the same arithmetic per row
-    assert np.array_equal(got, one_tile)
+    # one query tile per CTA (the default at these sizes) and two query tiles per CTA (forced from 256 query rows
+    # up) do the same arithmetic per row
+    assert np.array_equal(got, two_tiles)
