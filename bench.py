@@ -29,6 +29,7 @@ reference's Nim + XLA-plugin build cannot run here), all host threads.
 """
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -39,6 +40,8 @@ import time
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+SETTLE_S = 0.25            # untimed decode steps run for at least this long after the prefill (see run_model)
+SETTLE_MAX_STEPS = 256
 sys.path.insert(0, ROOT)
 
 METRIC = "decode_tokens_per_s"
@@ -333,7 +336,7 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     if args.layers > 0:
         cfg.n_layers = args.layers
     B, S = wl["batch"], wl["prompt"]
-    max_len = S + Wm + K + 16
+    max_len = S + Wm + K + 16 + SETTLE_MAX_STEPS
     cfg.max_seq = max(cfg.max_seq, max_len)
     parallel = "single" if world == 1 else wl.get("parallel", "replicas")
     if parallel == "ep":
@@ -357,8 +360,25 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    def max_over_ranks(v):
+        if not pg:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        pg.all_reduce(t, op=pg.ReduceOp.MAX)
+        return float(t[0])
+
+    settle = 0
     if Wm > 0:
         sess.decode(Wm)
+        # The prefill runs power-capped, and the SM clock stays capped (~1.4 of 1.97 GHz) for about 0.15 s after it:
+        # a timed region that starts 20 ms after the prefill measures that transient, not the decode step.  So the
+        # untimed part lasts at least SETTLE_S of decode steps; every rank derives the same count from the same
+        # max-over-ranks step time (sharded steps contain an exchange, so the ranks must run the same steps).
+        step_ms = max_over_ranks(sess.last_ms()[1] / Wm)
+        settle = int(min(SETTLE_MAX_STEPS, max(0, math.ceil(SETTLE_S * 1e3 / max(step_ms, 0.05)) - Wm)))
+        if settle > 0:
+            sess.decode(settle)
     if pg:
         pg.barrier()
     L.rewb200_sync(0, 0)
@@ -371,14 +391,6 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     clocks = sampler.stop() if rank == 0 else None
     launches = L.rewb200_launch_count(0) - launches0
 
-    def max_over_ranks(v):
-        if not pg:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64)
-        pg.all_reduce(t, op=pg.ReduceOp.MAX)
-        return float(t[0])
-
     decode_ms = max_over_ranks(decode_ms)
     prefill_ms = max_over_ranks(prefill_ms)
     if pg:
@@ -387,7 +399,8 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     tokens = B * K * mult
     out = {"name": name, "parallel": parallel, "batch_per_gpu": B, "prompt": S, "value": tokens / (decode_ms * 1e-3),
            "ms_per_step": decode_ms / K, "prefill_ms": prefill_ms, "prefill_tokens_per_s": B * S * mult / (prefill_ms * 1e-3),
-           "launches": int(launches), "clocks": clocks, "weight_gb": model.weight_bytes() / 1e9, "cfg": cfg}
+           "launches": int(launches), "clocks": clocks, "weight_gb": model.weight_bytes() / 1e9, "cfg": cfg,
+           "settle_steps": settle}
 
     if args.trace:
         # where a step's time goes, per category of launches (events between them: no overlap, so the sum is
@@ -409,7 +422,7 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
 
     # ---- rooflines: whole step (weights + KV read once per step per GPU), and the Linear launches alone
     peak, which = measured_peaks()
-    kv_bytes = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + K / 2.0)
+    kv_bytes = 2 * cfg.n_layers * (cfg.n_kv_heads // cfg.tp_size) * cfg.head_dim * 2 * B * (S + Wm + settle + K / 2.0)
     step_bytes = model.weight_bytes() - cfg.vocab * cfg.d_model * 2 + kv_bytes   # the embedding table is not streamed
     out["step_bytes_per_gpu"] = step_bytes
     out["step_frac"] = step_bytes / (decode_ms / K * 1e-3) / 1e9 / peak
@@ -480,7 +493,8 @@ def sharded_check(rank, world, pg, kind):
 def sub_record(r, which_allreduce=None):
     d = {"workload": r["name"], "parallelism": r["parallel"], "batch_per_gpu": r["batch_per_gpu"], "tokens_per_s": r["value"],
          "ms_per_step": r["ms_per_step"], "prefill_ms": r["prefill_ms"], "prefill_tokens_per_s": r["prefill_tokens_per_s"],
-         "per_gpu_step_frac": r["step_frac"], "step_bytes_per_gpu": r["step_bytes_per_gpu"], "gpu_launches": r["launches"]}
+         "per_gpu_step_frac": r["step_frac"], "step_bytes_per_gpu": r["step_bytes_per_gpu"], "gpu_launches": r["launches"],
+         "settle_steps": r["settle_steps"], "clocks": r["clocks"]}
     if "linear" in r:
         d["linear_frac"] = r["linear"]["gbs"] / r["peak"]
         d["linear_ms_per_step"] = r["linear"]["ms_per_step"]
@@ -607,6 +621,8 @@ def main():
         "prefill": {"tokens_per_s": r["prefill_tokens_per_s"], "ms": r["prefill_ms"]},
         "e2e": r["e2e"], "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": roofline,
     }
+    line["config"]["settle"] = ("%d more untimed decode steps after the %d warm-up steps: the SM clock stays capped for ~0.15 s "
+                                "after the prefill's power-capped burst, so the untimed part lasts %.2f s" % (r["settle_steps"], Wm, SETTLE_S))
     if "trace_ms" in r:
         line["trace_ms"] = r["trace_ms"]
     line.update(extra)

@@ -76,8 +76,10 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            graph); capacity = NCCL, always the worst-case capacity
  *   "gate_up_split" = "on" | "off"           decode-size gate|up launches with too few feature tiles to fill the GPU split K
  *                                            and finish in a small sum + SwiGLU launch (default), or stay one launch
- *   "qkv_post" = "attention" | "launch"      bf16 decode steps: bias, RoPE and the KV-cache append of the new token inside the
- *                                            attention kernel (default), or in a launch of their own before it
+ *   "qkv_post" = "attention" | "attention_always" | "launch"
+ *                                            bf16 decode steps: bias, RoPE and the KV-cache append of the new token inside the
+ *                                            attention kernel when its grid is at most one wave (default) / whatever the
+ *                                            grid, or in a launch of their own before it
  *   "nf4_gemv" = "tc" | "cuda"               NF4 weight-only Linear, steps of up to four rows: the tensor-core kernel that
  *                                            serves every step up to 32 rows (default), or a CUDA-core code streamer
  *                                            (fp16 pair lookups + HFMA2; measured slower, kept for comparison)

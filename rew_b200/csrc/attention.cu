@@ -1156,6 +1156,8 @@ __global__ void __launch_bounds__(fa2::THREADS, 1) attn_prefill_tc2_kernel(const
   }
 }
 
+}  // namespace
+
 int decode_splits(Ctx* c, int64_t B, int kvh) {
   if (const char* e = getenv("REW_B200_ATTN_SPLITS")) {  // tuning override
     const int v = atoi(e);
@@ -1168,7 +1170,7 @@ int decode_splits(Ctx* c, int64_t B, int kvh) {
   return (int)std::min<int64_t>(s, 16);
 }
 
-}  // namespace
+
 
 size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits) {
   return (size_t)B * nh * max_splits * (hd + 2) * sizeof(float);

@@ -68,6 +68,7 @@ struct Ctx {
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
   bool gu_split = true;         // decode-size gate|up launches with too few feature tiles split K (slabs + a sum-and-SwiGLU launch)
+  bool attn_fuse_qkv_always = false;  // option qkv_post=attention_always: also with grids of several waves (tests)
   bool attn_fuse_qkv = true;    // decode steps: bias + RoPE + cache append of the new token inside the attention kernel
   bool nf4_small = false;       // NF4 GEMV of up to four rows on the CUDA-core streamer instead of the tensor-core kernel (measured slower: off)
   bool tp_twoshot = true;       // tensor-parallel steps above 64 rows: sum over the peer heap (two-shot) instead of NCCL
@@ -322,6 +323,7 @@ struct AttnArgs {
                                 // have done in a launch of its own) and appends K / V to the cache; `q` is not read
 };
 int attn_launch(Ctx* c, const AttnArgs& a);
+int decode_splits(Ctx* c, int64_t B, int kvh);  // KV splits a decode attention launch of B sequences x kvh kv heads uses
 size_t attn_scratch_bytes(int64_t B, int nh, int hd, int max_splits);
 
 // scratch (optional): rows*64*8 bytes lets wide rows be scanned by several CTAs each

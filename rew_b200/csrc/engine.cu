@@ -946,7 +946,11 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
     RB_TRY(run_linear(s, L.qkv, s->xn, d, rows, true, 0, s->part, m->nqkv, &ks, dt == REWB200_BF16 ? &qa : nullptr, &qkv_done));
     if (o.trace) RB_TRY(o.trace->mark(TC_QKV));
     // decode steps: the attention kernel finishes q / k / v of the new token from the slabs itself
-    const bool fuse_into_attn = !qkv_done && o.S == 1 && dt == REWB200_BF16 && c->attn_fuse_qkv && m->nh_l / m->kvh_l <= 16;
+    // ... when its grid is at most one wave of two CTAs per SM (measured: with several waves the prologue in front of
+    // every CTA costs more than the launch it saves: l8 batch 128 5.69 -> 6.08 ms, the MoE model 7.07 -> 7.28 ms)
+    const bool fuse_into_attn = !qkv_done && o.S == 1 && dt == REWB200_BF16 && c->attn_fuse_qkv && m->nh_l / m->kvh_l <= 16 &&
+                                (c->attn_fuse_qkv_always ||
+                                 (int64_t)nb * m->kvh_l * decode_splits(c, nb, m->kvh_l) <= 2 * (int64_t)c->sm_count);
     qa.nsplit = ks;
     if (!qkv_done && !fuse_into_attn) RB_TRY(qkv_post_launch(c, qa, nb));
     if (o.trace) RB_TRY(o.trace->mark(TC_QKV_POST));

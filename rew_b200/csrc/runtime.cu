@@ -275,8 +275,10 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
     RB_REQUIRE(v == "on" || v == "off", "option gate_up_split: expected on or off");
     c->gu_split = v == "on";
   } else if (k == "qkv_post") {
-    RB_REQUIRE(v == "attention" || v == "launch", "option qkv_post: expected attention or launch");
-    c->attn_fuse_qkv = v == "attention";
+    RB_REQUIRE(v == "attention" || v == "attention_always" || v == "launch",
+               "option qkv_post: expected attention, attention_always or launch");
+    c->attn_fuse_qkv = v != "launch";
+    c->attn_fuse_qkv_always = v == "attention_always";
   } else if (k == "nf4_gemv") {
     RB_REQUIRE(v == "cuda" || v == "tc", "option nf4_gemv: expected tc or cuda");
     c->nf4_small = v == "cuda";
