@@ -851,7 +851,9 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
   // a slot holds the step as 16-byte lines of 8 payload bytes each
   const bool oneshot = pi != nullptr && pi->buf_bytes > 0 && d % 4 == 0 && rows <= 64 &&
                        (size_t)rows * d * dtype_size(dt) * 2 <= pi->buf_bytes && pi->world == cf.tp_size;
-  const bool tp_bf16_slab = cf.tp_size > 1 && !oneshot && dt == REWB200_BF16 && d % 4 == 0 && rows > 64;  // smaller steps keep split-K slabs
+  // (steps above 256 rows never split K, so a bf16 model's o / down projections write one bf16 slab there on one GPU
+  // too: half the bytes between the GEMM and the residual+norm kernel, rounded where the reference's bf16 Linear rounds)
+  const bool tp_bf16_slab = (cf.tp_size > 1 ? rows > 64 : (rows > 256 && cf.n_routed == 0)) && !oneshot && dt == REWB200_BF16 && d % 4 == 0;  // smaller steps keep split-K slabs
   // ... and when the heap's bulk region holds a scatter and a gather buffer of the step, the sum itself runs
   // over the heap too (two-shot: reduce-scatter and all-gather by peer stores) instead of through NCCL
   const size_t pay = dtype_size(dt);
@@ -859,7 +861,14 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
                        pi->a2a[pi->rank] != nullptr && d % ((int64_t)cf.tp_size * (16 / pay)) == 0 &&
                        2 * (size_t)rows * d * pay <= pi->a2a_bytes && c->tp_twoshot;
   auto tp_reduce = [&](int l, int which, int& ks, NormArgs& a) -> int {
-    if (cf.tp_size <= 1) return REWB200_OK;
+    if (cf.tp_size <= 1) {
+      if (tp_bf16_slab) {
+        ks = 1;
+        a.nsplit = 1;
+        a.partial_bf16 = 1;
+      }
+      return REWB200_OK;
+    }
     if (oneshot) {
       a.n_peers = pi->world;
       a.my_rank = pi->rank;
