@@ -354,6 +354,10 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     prompt = np.random.default_rng(1 + data_seed).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
 
     # ---- device-resident decode: prefill, W warm-up steps, K timed steps
+    # an untimed short prefill first: the first forward of a process loads modules, sets kernel attributes and, on
+    # several ranks, makes NCCL connect its peers (hundreds of ms at 8 ranks), none of which is prefill work
+    sess.forward(prompt[:, :min(S, 64)])
+    sess.reset()
     sess.forward(prompt)
     prefill_ms, _ = sess.last_ms()
     L.rewb200_sync(0, 0)
