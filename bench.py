@@ -380,7 +380,7 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
         # untimed part lasts at least SETTLE_S of decode steps; every rank derives the same count from the same
         # max-over-ranks step time (sharded steps contain an exchange, so the ranks must run the same steps).
         step_ms = max_over_ranks(sess.last_ms()[1] / Wm)
-        settle = int(min(SETTLE_MAX_STEPS, max(0, math.ceil(SETTLE_S * 1e3 / max(step_ms, 0.05)) - Wm)))
+        settle = int(min(SETTLE_MAX_STEPS, max(0, math.ceil(args.settle_seconds * 1e3 / max(step_ms, 0.05)) - Wm)))
         if settle > 0:
             sess.decode(settle)
     if pg:
@@ -522,6 +522,8 @@ def main():
     ap.add_argument("--option", action="append", default=[], metavar="KEY=VALUE",
                     help="run-time switch passed to rewb200_set_option, e.g. norm=row (repeatable)")
     ap.add_argument("--trace", action="store_true", help="add per-category device times of a decode step to every record")
+    ap.add_argument("--settle-seconds", type=float, default=SETTLE_S,
+                    help="shortest untimed stretch of decode steps after the prefill (0: only the --warmup steps; profiling aid)")
     ap.add_argument("--positions", type=int, default=4096, help="attn_op only: query / key positions per sequence")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: keep only this many decoder layers")
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "top_k", "top_p"],
@@ -626,7 +628,7 @@ def main():
         "e2e": r["e2e"], "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": roofline,
     }
     line["config"]["settle"] = ("%d more untimed decode steps after the %d warm-up steps: the SM clock stays capped for ~0.15 s "
-                                "after the prefill's power-capped burst, so the untimed part lasts %.2f s" % (r["settle_steps"], Wm, SETTLE_S))
+                                "after the prefill's power-capped burst, so the untimed part lasts %.2f s" % (r["settle_steps"], Wm, args.settle_seconds))
     if "trace_ms" in r:
         line["trace_ms"] = r["trace_ms"]
     line.update(extra)
