@@ -627,7 +627,7 @@ def main():
         "prefill": {"tokens_per_s": r["prefill_tokens_per_s"], "ms": r["prefill_ms"]},
         "e2e": r["e2e"], "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": roofline,
     }
-    line["config"]["settle"] = ("%d more untimed decode steps after the %d warm-up steps: the SM clock stays capped for ~0.15 s "
+    line["settle"] = ("%d more untimed decode steps after the %d warm-up steps: the SM clock stays capped for ~0.15 s "
                                 "after the prefill's power-capped burst, so the untimed part lasts %.2f s" % (r["settle_steps"], Wm, args.settle_seconds))
     if "trace_ms" in r:
         line["trace_ms"] = r["trace_ms"]
