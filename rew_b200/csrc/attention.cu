@@ -204,6 +204,36 @@ __device__ __forceinline__ uint32_t kv_addr(uint32_t base, uint32_t row, uint32_
 
 // ------------------------------------------------------------------ bf16 decode (S == 1)
 // grid (nsplit, kvh, B), 128 threads.  Warp w owns tokens 16w..16w+15 of every tile.
+// Combines the split-KV partials of one (sequence, head) for output element d: log-sum-exp weights, splits in
+// ascending order.  All loads of a phase are issued before the first use (up to 16 splits, fully unrolled), so a
+// merge costs two L2 round trips instead of one per split; partials were written by other SMs: read through L2.
+__device__ __forceinline__ float merge_splits(const float* __restrict__ part_ml, const float* __restrict__ part_o, int64_t base,
+                                              int nsplit, int hd, int d) {
+  float ms[16], ls[16], os[16];
+#pragma unroll
+  for (int sp = 0; sp < 16; ++sp) {
+    const bool in = sp < nsplit;
+    const float2 ml = in ? __ldcg(reinterpret_cast<const float2*>(part_ml + (base + sp) * 2)) : make_float2(-INFINITY, 0.f);
+    ms[sp] = ml.x;
+    ls[sp] = ml.y;
+    os[sp] = in ? __ldcg(part_o + (base + sp) * hd + d) : 0.f;
+  }
+  float M = -INFINITY;
+#pragma unroll
+  for (int sp = 0; sp < 16; ++sp) M = fmaxf(M, ms[sp]);
+  const float Mu = (M == -INFINITY) ? 0.f : M;
+  float L = 0.f, acc = 0.f;
+#pragma unroll
+  for (int sp = 0; sp < 16; ++sp) {
+    if (sp < nsplit) {
+      const float f = __expf(ms[sp] - Mu);
+      L += ls[sp] * f;
+      acc += os[sp] * f;
+    }
+  }
+  return L > 0.f ? acc / L : 0.f;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ CUtensorMap tmK,
                                                           const __grid_constant__ CUtensorMap tmV, AttnDev a) {
@@ -455,18 +485,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     const int row = idx / HD, d = idx % HD;
     const int head = hk * a.group + row;
     const int64_t base = ((int64_t)b * a.nh + head) * a.nsplit;
-    // partials come from other SMs: read them from L2
-    float M = -INFINITY;
-    for (int sp = 0; sp < a.nsplit; ++sp) M = fmaxf(M, __ldcg(a.part_ml + (base + sp) * 2));
-    const float Mu = (M == -INFINITY) ? 0.f : M;
-    float L = 0.f, acc = 0.f;
-    for (int sp = 0; sp < a.nsplit; ++sp) {
-      const float f = __expf(__ldcg(a.part_ml + (base + sp) * 2) - Mu);
-      L += __ldcg(a.part_ml + (base + sp) * 2 + 1) * f;
-      acc += __ldcg(a.part_o + (base + sp) * HD + d) * f;
-    }
     bf16* op = reinterpret_cast<bf16*>(a.out) + b * a.o_sb + head * a.o_sh;
-    op[d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    op[d] = __float2bfloat16_rn(merge_splits(a.part_ml, a.part_o, base, a.nsplit, HD, d));
   }
 }
 
@@ -476,17 +496,8 @@ __global__ void attn_merge_kernel(AttnDev a) {
   pdl_wait();
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int64_t base = ((int64_t)b * a.nh + head) * a.nsplit;
-  float M = -INFINITY;
-  for (int s = 0; s < a.nsplit; ++s) M = fmaxf(M, a.part_ml[(base + s) * 2]);
-  const float Mu = (M == -INFINITY) ? 0.f : M;
-  float L = 0.f, acc = 0.f;
-  for (int s = 0; s < a.nsplit; ++s) {
-    const float f = __expf(a.part_ml[(base + s) * 2] - Mu);
-    L += a.part_ml[(base + s) * 2 + 1] * f;
-    acc += a.part_o[(base + s) * a.hd + d] * f;
-  }
   bf16* op = reinterpret_cast<bf16*>(a.out) + b * a.o_sb + head * a.o_sh;
-  op[d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  op[d] = __float2bfloat16_rn(merge_splits(a.part_ml, a.part_o, base, a.nsplit, a.hd, d));
 }
 
 // ------------------------------------------------------------------ bf16 prefill (S > 1)
