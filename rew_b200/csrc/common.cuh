@@ -67,6 +67,7 @@ struct Ctx {
   int attn_pingpong_min_rows = 3072;
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
+  int tp_exchange = 0;          // one-shot exchange of decode-size steps: 0 auto (two hops from 8 ranks), 1 one hop, 2 two hops
   bool gu_split = true;         // decode-size gate|up launches with too few feature tiles split K (slabs + a sum-and-SwiGLU launch)
   bool attn_fuse_qkv_always = false;  // option qkv_post=attention_always: also with grids of several waves (tests)
   bool attn_fuse_qkv = true;    // decode steps: bias + RoPE + cache append of the new token inside the attention kernel
@@ -253,6 +254,9 @@ struct NormArgs {
   int n_peers;
   int my_rank;
   int payload_bf16;       // partials cross NVLink as bf16 (bf16 models) or f32
+  int two_shot;           // 1: columns are owned by ranks in blocks of d / n_peers: a partial goes to the owner only, the
+                          // owner adds the n_peers values in rank order and stores the sum to every peer (one more hop,
+                          // 2 (n - 1) / n of a partial over the links instead of n - 1 partials)
   void* peer_buf[8];      // rank r's exchange buffer of this all-reduce: [world][slot_lines] 16-byte lines
   int64_t slot_lines;     // lines between two writers' slots
   const int* epoch;       // device counter, advanced once per forward on every rank alike

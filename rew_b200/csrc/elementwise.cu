@@ -257,6 +257,74 @@ __device__ __forceinline__ void tp_exchange4(const NormArgs& a, float4 (&p)[NCH]
   }
 }
 
+// The same all-reduce in two hops (NormArgs::two_shot): the columns of a row are owned by the ranks in blocks of
+// d / n_peers.  A thread stores its partial of a float4 to the owner only (slot `my_rank` of the owner's buffer);
+// the owner's thread polls the other ranks' partials, adds all of them in rank order and stores the sum into slot
+// `my_rank` of every peer (the lines of its own columns, which no partial uses); the other ranks poll that line.
+// Same threads handle the same columns on every rank, a thread sends all its partials before its first poll, and
+// an owner's polls depend on those sends only, so no wait can depend on itself.  Every rank ends up with the
+// owner's value (rounded to the payload type), so ranks stay bit-identical.
+template <int NCH>
+__device__ __forceinline__ void tp_exchange4_two(const NormArgs& a, float4 (&p)[NCH], const int64_t (&idx)[NCH]) {
+  const uint32_t flag = (uint32_t)(*a.epoch + a.barrier_offset);
+  const int64_t mine = (int64_t)a.my_rank * a.slot_lines;
+  const int64_t dn = a.d / a.n_peers;
+  const uint4* local = reinterpret_cast<const uint4*>(a.peer_buf[a.my_rank]);
+  const int sh = a.payload_bf16 ? 2 : 1;   // a float4 is one line (bf16) or two (f32)
+  auto send = [&](int r, int64_t line, const float4& v) {
+    uint4* dst = reinterpret_cast<uint4*>(a.peer_buf[r]) + mine + line;
+    if (a.payload_bf16) {
+      ll_store(dst, pack_bf16(v.x, v.y), pack_bf16(v.z, v.w), flag);
+    } else {
+      ll_store(dst, __float_as_uint(v.x), __float_as_uint(v.y), flag);
+      ll_store(dst + 1, __float_as_uint(v.z), __float_as_uint(v.w), flag);
+    }
+  };
+  auto recv = [&](int r, int64_t line) -> float4 {
+    const uint4* src = local + (int64_t)r * a.slot_lines + line;
+    if (a.payload_bf16) {
+      const uint2 u = ll_poll(src, flag, a.status);
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&u.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+      return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+    }
+    const uint2 u0 = ll_poll(src, flag, a.status), u1 = ll_poll(src + 1, flag, a.status);
+    return make_float4(__uint_as_float(u0.x), __uint_as_float(u0.y), __uint_as_float(u1.x), __uint_as_float(u1.y));
+  };
+  auto rounded = [&](const float4& v) -> float4 {   // what a value looks like after crossing a link
+    if (!a.payload_bf16) return v;
+    const uint32_t w0 = pack_bf16(v.x, v.y), w1 = pack_bf16(v.z, v.w);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&w0), hi = *reinterpret_cast<const __nv_bfloat162*>(&w1);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+  };
+  int owner[NCH];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    owner[c] = -1;
+    if (idx[c] < 0) continue;
+    owner[c] = (int)((idx[c] % a.d) / dn);
+    if (owner[c] != a.my_rank) send(owner[c], idx[c] >> sh, p[c]);
+    else p[c] = rounded(p[c]);
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    if (idx[c] < 0) continue;
+    const int64_t line = idx[c] >> sh;
+    if (owner[c] == a.my_rank) {
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < a.n_peers; ++r) {
+        const float4 q = r == a.my_rank ? p[c] : recv(r, line);
+        t.x += q.x; t.y += q.y; t.z += q.z; t.w += q.w;
+      }
+      t = rounded(t);
+      for (int r = 0; r < a.n_peers; ++r)
+        if (r != a.my_rank) send(r, line, t);
+      p[c] = t;
+    } else {
+      p[c] = recv(owner[c], line);
+    }
+  }
+}
+
 template <typename TE, typename TO, int NCH>
 __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormArgs a) {
   __shared__ float red[33];
@@ -288,7 +356,10 @@ __global__ void __launch_bounds__(NORMV_THREADS) residual_norm_vec_kernel(NormAr
       idx[c] = i < d ? row * d + i : -1;
       vals[c] = i < d ? partial_sum4(a, idx[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx);
+    if (a.n_peers > 0) {
+      if (a.two_shot) tp_exchange4_two<NCH>(a, vals, idx);
+      else tp_exchange4<NCH>(a, vals, idx);
+    }
   }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
@@ -397,7 +468,10 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(256) residual_norm_c
       idx[c] = off < dq ? row * d + col0 + off : -1;
       vals[c] = off < dq ? partial_sum4(a, idx[c]) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (a.n_peers > 0) tp_exchange4<NCH>(a, vals, idx);
+    if (a.n_peers > 0) {
+      if (a.two_shot) tp_exchange4_two<NCH>(a, vals, idx);
+      else tp_exchange4<NCH>(a, vals, idx);
+    }
   }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {

@@ -271,6 +271,9 @@ int rewb200_set_option(int slot, const char* key, const char* value) {
   } else if (k == "ep_exchange") {
     RB_REQUIRE(v == "prefix" || v == "capacity" || v == "auto", "option ep_exchange: expected auto, prefix or capacity");
     c->ep_prefix = v == "prefix" ? 1 : (v == "capacity" ? 0 : 2);
+  } else if (k == "tp_exchange") {
+    RB_REQUIRE(v == "auto" || v == "one" || v == "two", "option tp_exchange: expected auto, one or two");
+    c->tp_exchange = v == "one" ? 1 : (v == "two" ? 2 : 0);
   } else if (k == "gate_up_split") {
     RB_REQUIRE(v == "on" || v == "off", "option gate_up_split: expected on or off");
     c->gu_split = v == "on";

@@ -33,10 +33,11 @@ def _bundled_nccl():
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["nccl", "fused"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "fused_two"])
 def test_tp2_generate_matches_oracle(orc, mode):
     """mode nccl: every all-reduce through NCCL; fused: steps of up to 64 rows use the push all-reduce over
-    the peer heap inside the residual+norm kernel (a 60-row prefill too); a 120-row prefill is summed by the
+    the peer heap inside the residual+norm kernel (a 60-row prefill too), every rank storing to every peer;
+    fused_two: the same with partials sent to the column owner, which returns the sum (option tp_exchange=two); a 120-row prefill is summed by the
     two-shot exchange over the heap and, with option tp_allreduce=nccl, through NCCL (bf16 payload on the bf16
     model)."""
     from rew_b200 import _lib
