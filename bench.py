@@ -108,37 +108,44 @@ class ClockSampler:
         self.t1 = time.time()
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if not self.proc:
-            return out
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        import datetime
-        rows = []
         try:
-            for line in open(self.path):
-                f = [x.strip() for x in line.split(",")]
-                if len(f) < 9:
-                    continue
-                try:
-                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
-                    rows.append((ts, float(f[1]), float(f[2]), float(f[3]), [v.lower().startswith("active") for v in f[5:9]],
-                                 f[9] if len(f) > 9 else ""))
-                except ValueError:
-                    continue
+            text = open(self.path).read()
             os.unlink(self.path)
         except Exception:
-            pass
-        t0, t1 = self.t0 or 0.0, self.t1 or time.time()
+            text = ""
+        return self.summarise(text, self.t_warm or 0.0, self.t0 or 0.0, self.t1 or time.time())
+
+    @staticmethod
+    def summarise(text, t_warm, t0, t1):
+        """Clock record of a run from nvidia-smi's CSV lines (query Q): median SM clock and power over the samples
+        whose timestamps fall inside [t0, t1], every throttle reason seen active there."""
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        rows = []
+        for line in text.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), float(f[3]), [v.lower().startswith("active") for v in f[5:9]],
+                             f[9] if len(f) > 9 else ""))
+            except ValueError:
+                continue
         pick = [r for r in rows if t0 <= r[0] <= t1]
         window = "timed region"
         if len(pick) < 2:
-            pick = [r for r in rows if (self.t_warm or 0.0) <= r[0] <= t1]
-            window = "warm-up + timed region (the timed region alone caught %d samples)" % len([r for r in rows if t0 <= r[0] <= t1])
+            inside = len(pick)
+            pick = [r for r in rows if t_warm <= r[0] <= t1]
+            window = "warm-up + timed region (the timed region alone caught %d samples)" % inside
         if not pick:
             pick, window = rows, "all samples"
         if pick:

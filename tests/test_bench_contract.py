@@ -58,3 +58,28 @@ def test_reference_arm_ignores_an_inherited_single_thread_setting():
     assert j["cpu_baseline"]["cores"] == (os.cpu_count() or 1)
     # same config keys as the product arm prints for this workload
     assert set(j["config"]) == {"workload", "batch_per_gpu", "prompt", "decode_steps", "parallelism", "sampling", "mask", "norm", "l2"}
+
+
+def test_clock_record_counts_only_samples_inside_the_timed_region():
+    """The sampler runs from before the warm-up; a sample counts when its timestamp lies in the timed region, and a
+    region too short for two samples widens to the warm-up steps and says so."""
+    import datetime
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    base = datetime.datetime(2025, 1, 2, 3, 4, 5).timestamp()
+
+    def row(dt, mhz, watts, cap):
+        ts = datetime.datetime.fromtimestamp(base + dt).strftime("%Y/%m/%d %H:%M:%S.%f")[:-3]
+        return "%s, %d, 1965, %.2f, 0x4, Not Active, Not Active, Not Active, %s, 1000.00" % (ts, mhz, watts, cap)
+
+    text = "\n".join([row(0.00, 1400, 950.0, "Active"), row(0.10, 1410, 500.0, "Active"),     # right after the prefill
+                      row(0.30, 1950, 600.0, "Not Active"), row(0.32, 1960, 610.0, "Not Active"), row(0.34, 1965, 620.0, "Not Active"),
+                      row(0.50, 210, 90.0, "Not Active"), "garbage line"])
+    rec = bench.ClockSampler.summarise(text, base + 0.05, base + 0.29, base + 0.35)
+    assert rec["samples"] == 3 and rec["window"] == "timed region"
+    assert rec["sm_mhz"] == 1960.0 and rec["sm_max_mhz"] == 1965.0 and rec["reasons"] == []
+    assert rec["power_w"] == 610.0 and rec["power_limit_w"] == 1000.0
+    short = bench.ClockSampler.summarise(text, base + 0.05, base + 0.31, base + 0.33)
+    assert short["samples"] == 3 and short["window"].startswith("warm-up + timed region") and short["reasons"] == ["sw_power_cap"]
