@@ -76,7 +76,8 @@ int rewb200_sync(int slot, int timeout_ms);
  *                                            graph); capacity = NCCL, always the worst-case capacity
  *   "tp_exchange" = "auto" | "one" | "two"   tensor-parallel all-reduce of decode-size steps over the peer heap: every rank
  *                                            stores its partial to every peer (one hop), or to the owner of the columns,
- *                                            which returns the sum (two hops, fewer bytes); auto = two hops from 8 ranks
+ *                                            which returns the sum (two hops, fewer bytes; measured slower at 2 and at
+ *                                            8 ranks); auto = one hop
  *   "gate_up_split" = "on" | "off"           decode-size gate|up launches with too few feature tiles to fill the GPU split K
  *                                            and finish in a small sum + SwiGLU launch (default), or stay one launch
  *   "qkv_post" = "attention" | "attention_always" | "launch"

@@ -67,7 +67,7 @@ struct Ctx {
   int attn_pingpong_min_rows = 3072;
   bool attn_tc = true;        // prefill attention (head_dim 128, conventional causal) on the tcgen05 kernel
   bool sampling_exact = false; // samplers skip the bucket path and always run the full-vocabulary radix select
-  int tp_exchange = 0;          // one-shot exchange of decode-size steps: 0 auto (two hops from 8 ranks), 1 one hop, 2 two hops
+  int tp_exchange = 0;          // fused exchange of decode-size steps: 0 / 1 one hop (every rank stores to every peer), 2 two hops
   bool gu_split = true;         // decode-size gate|up launches with too few feature tiles split K (slabs + a sum-and-SwiGLU launch)
   bool attn_fuse_qkv_always = false;  // option qkv_post=attention_always: also with grids of several waves (tests)
   bool attn_fuse_qkv = true;    // decode steps: bias + RoPE + cache append of the new token inside the attention kernel

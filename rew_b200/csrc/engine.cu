@@ -873,7 +873,7 @@ int enqueue_forward(rewb200_session* s, const FwdOpts& o) {
       a.n_peers = pi->world;
       a.my_rank = pi->rank;
       a.payload_bf16 = dt == REWB200_BF16 ? 1 : 0;
-      a.two_shot = (c->tp_exchange == 2 || (c->tp_exchange == 0 && pi->world >= 8)) && d % (4 * (int64_t)pi->world) == 0 ? 1 : 0;
+      a.two_shot = c->tp_exchange == 2 && d % (4 * (int64_t)pi->world) == 0 ? 1 : 0;  // measured slower at 2 and at 8 ranks: off by default
       a.slot_lines = (int64_t)(pi->buf_bytes / 16);
       for (int r = 0; r < pi->world; ++r) a.peer_buf[r] = pi->bufs[which][r];
       a.epoch = pi->epoch;

@@ -30,7 +30,7 @@ def main():
     print("rank", rank, "communicator ready", flush=True)
     fused = len(sys.argv) > 5 and sys.argv[5] in ("fused", "fused_two")
     if fused and sys.argv[5] == "fused_two":
-        api.set_option("tp_exchange", "two")   # the two-hop form of the fused exchange (default from 8 ranks)
+        api.set_option("tp_exchange", "two")   # the two-hop form of the fused exchange
     if fused:  # exchange the IPC handles of the all-reduce heaps through files
         mine = api.comm_peer_alloc(1 << 20, 1 << 20)
         with open("%s.h%d.tmp" % (idfile, rank), "wb") as f:
