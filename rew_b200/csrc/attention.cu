@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
       }
       if (rope) {
         const float c0 = cr[e], s0 = sr[e];
-        const float r0 = c0 * v0 - s0 * v1, r1 = s0 * v0 + c0 * v1;
+        const float r0 = rope_even(c0, s0, v0, v1), r1 = rope_odd(c0, s0, v0, v1);
         v0 = r0;
         v1 = r1;
       }

@@ -607,8 +607,8 @@ __global__ void __launch_bounds__(256) qkv_post_vec_kernel(QkvPostArgs a) {
     float r[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      r[2 * j] = cs[j] * v[2 * j] - sn[j] * v[2 * j + 1];
-      r[2 * j + 1] = sn[j] * v[2 * j] + cs[j] * v[2 * j + 1];
+      r[2 * j] = rope_even(cs[j], sn[j], v[2 * j], v[2 * j + 1]);
+      r[2 * j + 1] = rope_odd(cs[j], sn[j], v[2 * j], v[2 * j + 1]);
     }
     if (col < nq) {
       store8<TA>(reinterpret_cast<TA*>(a.q_out) + row * nq + col, r);
@@ -693,8 +693,8 @@ __global__ void __launch_bounds__(256) qkv_post_kernel(QkvPostArgs a) {
       v1 += b1;
     }
     if (col < nq + nkv) {
-      const float r0 = c0 * v0 - s0 * v1;
-      const float r1 = s0 * v0 + c0 * v1;
+      const float r0 = rope_even(c0, s0, v0, v1);
+      const float r1 = rope_odd(c0, s0, v0, v1);
       if (col < nq) {
         q_out[col] = from_f<TA>(r0);
         q_out[col + 1] = from_f<TA>(r1);

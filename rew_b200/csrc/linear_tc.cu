@@ -175,7 +175,7 @@ __device__ __forceinline__ void cluster_finish(const TcArgs& a, uint8_t* smem, i
     if (!feat_ok || !epi_ok || rpos[jj] < 0) continue;
     const int64_t grow = (int64_t)row0 + j0 + jj;
     if (rot) {
-      const float r = (e & 1) ? (sn[jj] * pr + cs[jj] * x) : (cs[jj] * x - sn[jj] * pr);
+      const float r = (e & 1) ? rope_odd(cs[jj], sn[jj], pr, x) : rope_even(cs[jj], sn[jj], x, pr);
       if (col < nq)
         reinterpret_cast<bf16*>(p.q_out)[grow * nq + col] = __float2bfloat16_rn(r);
       else

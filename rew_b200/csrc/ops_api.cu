@@ -25,13 +25,13 @@ __global__ void rope_kernel(const T* x, T* y, const float* cosT, const float* si
   if constexpr (sizeof(T) == 2) {
     x0 = __bfloat162float(x[row * hd + 2 * p]);
     x1 = __bfloat162float(x[row * hd + 2 * p + 1]);
-    y[row * hd + 2 * p] = __float2bfloat16_rn(c0 * x0 - s0 * x1);
-    y[row * hd + 2 * p + 1] = __float2bfloat16_rn(s0 * x0 + c0 * x1);
+    y[row * hd + 2 * p] = __float2bfloat16_rn(rope_even(c0, s0, x0, x1));
+    y[row * hd + 2 * p + 1] = __float2bfloat16_rn(rope_odd(c0, s0, x0, x1));
   } else {
     x0 = x[row * hd + 2 * p];
     x1 = x[row * hd + 2 * p + 1];
-    y[row * hd + 2 * p] = c0 * x0 - s0 * x1;
-    y[row * hd + 2 * p + 1] = s0 * x0 + c0 * x1;
+    y[row * hd + 2 * p] = rope_even(c0, s0, x0, x1);
+    y[row * hd + 2 * p + 1] = rope_odd(c0, s0, x0, x1);
   }
 }
 

@@ -199,6 +199,12 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// One RoPE pair (v0, v1) -> (c v0 - s v1, s v0 + c v1) with a fixed rounding sequence (one product rounded, then one
+// fused multiply-add).  Left to the compiler, the contraction can differ from kernel to kernel; with this, every
+// kernel that rotates q / k returns the same bits.
+__device__ __forceinline__ float rope_even(float c, float s, float v0, float v1) { return __fmaf_rn(c, v0, -__fmul_rn(s, v1)); }
+__device__ __forceinline__ float rope_odd(float c, float s, float v0, float v1) { return __fmaf_rn(s, v0, __fmul_rn(c, v1)); }
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

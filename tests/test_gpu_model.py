@@ -321,10 +321,12 @@ def test_qkv_finish_inside_attention_equals_the_separate_launch(rb):
                         theta=500000.0, dtype=_lib.BF16, mask_kind=1)
     t = [W.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(cfg, seed=6, std=0.05, trivial_affine=False)]
     model = rb.CausalLM(cfg).load(t)
-    for B, S in ((1, 700), (5, 63), (3, 64)):
+    # 160 sequences x 2 kv heads = 320 CTAs: more than one wave, where the default keeps the separate launch and only
+    # attention_always fuses
+    for B, S in ((1, 700), (5, 63), (3, 64), (160, 9)):
         prompt = np.random.default_rng(B + S).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
         outs = []
-        for how in ("attention", "launch"):
+        for how in ("attention_always", "launch"):
             rb.set_option("qkv_post", how)
             try:
                 sess = model.session(B, S + 16)
