@@ -395,7 +395,7 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
     L.rewb200_sync(0, 0)
     launches0 = L.rewb200_launch_count(0)
     sampler.mark_begin()
-    sess.decode(K)
+    timed_ids = sess.decode(K)
     _, decode_ms = sess.last_ms()
     L.rewb200_sync(0, 0)
     sampler.mark_end()
@@ -413,6 +413,13 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
            "launches": int(launches), "clocks": clocks, "weight_gb": model.weight_bytes() / 1e9, "cfg": cfg,
            "settle_steps": settle}
 
+    if pg and parallel == "tp":
+        # tensor-parallel ranks add the same partials in the same order: the tokens of the timed steps must be the same bits
+        import hashlib
+        digests = [None] * world
+        pg.all_gather_object(digests, hashlib.sha256(np.ascontiguousarray(timed_ids).tobytes()).hexdigest())
+        out["ranks_identical"] = len(set(digests)) == 1
+
     if args.trace:
         # where a step's time goes, per category of launches (events between them: no overlap, so the sum is
         # above the replayed step); max over ranks of the mean of three traced steps
@@ -427,6 +434,7 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
         t0 = time.perf_counter()
         ids = sess.generate(prompt, K)
         e2e_s = max_over_ranks(time.perf_counter() - t0)
+
         out["e2e"] = {"value": tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": prompt.nbytes / K,
                       "d2h_bytes_per_step": ids.nbytes / K,
                       "what": "one generate() call: prefill of the prompt + %d decode steps, ids host->device->host" % K}
@@ -511,6 +519,8 @@ def sub_record(r, which_allreduce=None):
         d["linear_ms_per_step"] = r["linear"]["ms_per_step"]
     if which_allreduce:
         d["allreduce"] = which_allreduce
+    if "ranks_identical" in r:
+        d["ranks_identical"] = r["ranks_identical"]
     if "trace_ms" in r:
         d["trace_ms"] = r["trace_ms"]
     return d
