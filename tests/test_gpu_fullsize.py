@@ -118,3 +118,32 @@ def test_full_size_long_context_alone_and_in_a_batch(rb):
         assert np.array_equal(pre1[0], pre[2])      # 1500 rows alone, 6000 rows in the batch: the same bits
     finally:
         model.free()
+
+
+def test_full_size_moe_prefill_grouped_gemm_kernels_agree(rb):
+    """DeepSeek-V2-Lite shape, 64 sequences x 128 tokens (768 rows per expert on average): the prefill's expert GEMMs on
+    the persistent tcgen05 kernel with its device-built tile list against the same forward with every Linear on the
+    mma.sync kernels (option linear=mma).  Same routing (the router runs ahead of the experts on identical inputs in
+    the first MoE layer; later a near-tie may route a token differently, which moves that one sequence), so the
+    median sequence agrees to bf16 summation-order noise and at most a few sequences differ more."""
+    cfg = W.deepseek_v2_lite()
+    cfg.max_seq = 256
+    model = rb.CausalLM(cfg).init_random(seed=24, std=0.02)
+    try:
+        B, S = 64, 128
+        prompt = np.random.default_rng(8).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+        outs = {}
+        for impl in ("tc", "mma"):
+            rb.set_option("linear", impl)
+            try:
+                sess = model.session(B, S + 8)
+                outs[impl] = sess.forward(prompt, want_logits=True)[1]
+                sess.free()
+            finally:
+                rb.set_option("linear", "tc")
+        assert np.isfinite(outs["tc"]).all()
+        r = np.array([_rel_l2(outs["tc"][b], outs["mma"][b]) for b in range(B)])
+        assert np.median(r) <= 2e-2
+        assert (r > 5e-2).sum() <= B // 8
+    finally:
+        model.free()
