@@ -147,3 +147,34 @@ def test_full_size_moe_prefill_grouped_gemm_kernels_agree(rb):
         assert (r > 5e-2).sum() <= B // 8
     finally:
         model.free()
+
+
+def test_full_size_prefill_kernel_variants_return_the_same_bits(rb):
+    """Llama-3-8B shape, 8 x 512-token prompts: the prefill with the two-CTA Linear (default), the one-CTA persistent
+    Linear and the one-tile Linear, and with one or two query tiles per CTA in the attention kernel.  All variants
+    issue the same products in the same order and share their epilogue and softmax arithmetic: identical logits."""
+    cfg = W.llama3_8b()
+    cfg.max_seq = 640
+    model = rb.CausalLM(cfg).init_random(seed=25, std=0.02)
+    try:
+        B, S = 8, 512
+        prompt = np.random.default_rng(9).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+
+        def run(**opts):
+            for k, v in opts.items():
+                rb.set_option(k, v)
+            try:
+                sess = model.session(B, S + 8)
+                out = sess.forward(prompt, want_logits=True)[1]
+                sess.free()
+                return out
+            finally:
+                rb.set_option("prefill", "pair")
+                rb.set_option("attention", "tc")
+
+        base = run()
+        assert np.isfinite(base).all()
+        for opts in ({"prefill": "persistent"}, {"prefill": "tile"}, {"attention": "tc2"}, {"attention": "tc1"}):
+            assert np.array_equal(run(**opts), base), opts
+    finally:
+        model.free()
