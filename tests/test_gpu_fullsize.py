@@ -178,3 +178,32 @@ def test_full_size_prefill_kernel_variants_return_the_same_bits(rb):
             assert np.array_equal(run(**opts), base), opts
     finally:
         model.free()
+
+
+def test_full_size_decode_launch_variants_return_the_same_bits(rb):
+    """Llama-3-8B shape, 4 x 1200-token prompts (9 KV splits per sequence and kv head) and 32 x 100-token prompts (no
+    split): decode steps with q / k / v finished inside the attention kernel or in a launch of their own, and with the
+    split-KV partials merged by a launch or by the last CTA of a sequence.  Same arithmetic in the same order."""
+    cfg = W.llama3_8b()
+    cfg.max_seq = 1300
+    model = rb.CausalLM(cfg).init_random(seed=26, std=0.02)
+    defaults = {"qkv_post": "attention", "attention_merge": "launch"}
+    try:
+        for B, S in ((4, 1200), (32, 100)):
+            prompt = np.random.default_rng(B).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+
+            def run(**opts):
+                for k, v in opts.items():
+                    rb.set_option(k, v)
+                try:
+                    return _run(model, prompt, 5)
+                finally:
+                    for k, v in defaults.items():
+                        rb.set_option(k, v)
+
+            ids, logits = run()
+            for opts in ({"qkv_post": "launch"}, {"attention_merge": "fused"}, {"qkv_post": "launch", "attention_merge": "fused"}):
+                ids2, logits2 = run(**opts)
+                assert np.array_equal(ids2, ids) and np.array_equal(logits2, logits), (B, S, opts)
+    finally:
+        model.free()
