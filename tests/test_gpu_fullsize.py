@@ -207,3 +207,39 @@ def test_full_size_decode_launch_variants_return_the_same_bits(rb):
                 assert np.array_equal(ids2, ids) and np.array_equal(logits2, logits), (B, S, opts)
     finally:
         model.free()
+
+
+def test_full_size_continuous_batching_matches_the_plain_session(rb):
+    """Llama-3-8B shape: four lanes over a pool of KV blocks, admitted in a scrambled order with another lane's
+    admission and release in between (so the lanes' pages are interleaved in the pool), against a plain session with
+    the same four prompts.  A lane's prefill is its prompt alone (300 rows: above the 256 rows up to which a Linear
+    may split K, so its rows see the same sums as in the session's 1200-row prefill) and the decode steps see the
+    same batch of four: same tokens, bit for bit; releasing the lanes returns every block."""
+    cfg = W.llama3_8b()
+    cfg.max_seq = 512
+    model = rb.CausalLM(cfg).init_random(seed=27, std=0.02)
+    try:
+        B, S, steps = 4, 300, 6
+        prompt = np.random.default_rng(10).integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+        sess = model.session(B, S + steps + 8)
+        want = sess.generate(prompt, steps)          # [B, steps]: first token from the prefill, then steps - 1 decode steps
+        sess.free()
+        ps = model.paged_session(B, S + steps + 8, 64)
+        free0 = ps.free_blocks()
+        first = {}
+        first[2] = ps.admit(2, prompt[2])
+        first[0] = ps.admit(0, prompt[0])
+        ps.admit(3, prompt[1][:70])                  # a guest that leaves again: its pages return to the pool
+        first[1] = ps.admit(1, prompt[1])
+        ps.release(3)
+        first[3] = ps.admit(3, prompt[3])
+        got = ps.step(steps - 1)
+        for b in range(B):
+            assert first[b] == want[b, 0]
+            assert np.array_equal(got[b], want[b, 1:])
+        for b in range(B):
+            ps.release(b)
+        assert ps.free_blocks() == free0
+        ps.free()
+    finally:
+        model.free()
