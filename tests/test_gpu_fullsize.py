@@ -243,3 +243,45 @@ def test_full_size_continuous_batching_matches_the_plain_session(rb):
         ps.free()
     finally:
         model.free()
+
+
+@pytest.mark.parametrize("mode", ["top_k", "top_p"])
+def test_full_size_sampling_follows_the_sequence_not_its_batch_slot(rb, mode):
+    """Llama-3-8B shape (128 256-entry vocabulary), device sampling with a repetition penalty: a sequence's sampled
+    tokens and log-probabilities depend on its own logits and its own key only, so permuting the batch together with
+    the seeds permutes the results; eos and stop ids end a sequence (-1 afterwards) without disturbing the others."""
+    cfg = W.llama3_8b()
+    cfg.max_seq = 256
+    model = rb.CausalLM(cfg).init_random(seed=28, std=0.02)
+    try:
+        B, S, steps = 8, 64, 6
+        rng = np.random.default_rng(11)
+        prompt = rng.integers(0, cfg.vocab, size=(B, S)).astype(np.int32)
+        seeds = np.arange(100, 100 + B, dtype=np.uint64)
+        kw = dict(temperature=0.8, top_k=50, repetition_penalty=1.1) if mode == "top_k" else \
+            dict(temperature=0.8, top_k=0, top_p=0.9, repetition_penalty=1.1)
+
+        def run(p, sd, **gen):
+            sess = model.session(B, S + steps + 8)
+            sess.set_sampling(seeds=sd, **kw)
+            ids = sess.generate(p, steps, **gen)
+            lp = sess.logprobs(steps)
+            sess.free()
+            return ids, lp
+
+        ids, lp = run(prompt, seeds)
+        assert (ids >= 0).all() and (ids < cfg.vocab).all() and np.isfinite(lp).all() and (lp <= 0).all()
+        perm = rng.permutation(B)
+        ids_p, lp_p = run(prompt[perm], seeds[perm])
+        assert np.array_equal(ids_p, ids[perm]) and np.array_equal(lp_p, lp[perm])
+        other, _ = run(prompt, seeds + np.uint64(1000))
+        assert not np.array_equal(other, ids)           # another key, another draw
+        eos = int(ids[3, 2])
+        stop = int(ids[5, 1])
+        cut, _ = run(prompt, seeds, eos=eos, stop_ids=(stop,))
+        for b in range(B):
+            ends = [j for j in range(steps) if ids[b, j] in (eos, stop)]
+            n = ends[0] + 1 if ends else steps
+            assert np.array_equal(cut[b, :n], ids[b, :n]) and (cut[b, n:] == -1).all()
+    finally:
+        model.free()
