@@ -32,7 +32,7 @@ def main():
     if fused and sys.argv[5] == "fused_two":
         api.set_option("tp_exchange", "two")   # the two-hop form of the fused exchange
     if fused:  # exchange the IPC handles of the all-reduce heaps through files
-        mine = api.comm_peer_alloc(1 << 20, 1 << 20)
+        mine = api.comm_peer_alloc(1 << 20, 8 << 20)
         with open("%s.h%d.tmp" % (idfile, rank), "wb") as f:
             f.write(mine)
         os.replace("%s.h%d.tmp" % (idfile, rank), "%s.h%d" % (idfile, rank))
@@ -87,6 +87,29 @@ def main():
             results[name + tag + "_logits"] = logits
             sess.free()  # the captured decode graph holds the communicator; release it before comm_destroy
         api.set_option("tp_allreduce", "heap")
+    # one decoder layer at the width of the 8B shape (d_model 4096, 32 / 8 heads of 128, FFN 14336): the exchange
+    # slots, the split-K policies and the tiles of the real shards; rank 0 also runs the unsharded model
+    wide = dict(vocab=2048, d_model=4096, n_layers=1, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, max_seq=128,
+                theta=500000.0, dtype=_lib.BF16, mask_kind=1, norm_kind=0)
+    full = W.ModelConfig(**wide)
+    t = [W.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(full, seed=12, std=0.02, trivial_affine=False)]
+    model = api.CausalLM(W.ModelConfig(**wide, tp_rank=rank, tp_size=world)).load(t)
+    ref = api.CausalLM(full).load(t) if rank == 0 else None
+    for tag, plen in (("", 15), ("_long", 40)):
+        prompt = np.random.default_rng(4).integers(0, 2048, size=(4, plen)).astype(np.int32)
+        sess = model.session(4, 64)
+        ids, logits = sess.generate(prompt, 5, want_logits=True)
+        sess.free()
+        results["wide" + tag + "_ids"], results["wide" + tag + "_logits"] = ids, logits
+        if ref is not None:
+            rs = ref.session(4, 64)
+            rids, rlogits = rs.generate(prompt, 5, want_logits=True)
+            rs.free()
+            results["wide" + tag + "_ref_ids"], results["wide" + tag + "_ref_logits"] = rids, rlogits
+        print("rank", rank, "wide" + tag, "done", flush=True)
+    model.free()
+    if ref is not None:
+        ref.free()
     np.savez(outfile, **results)
     api.comm_destroy()
 
