@@ -34,7 +34,7 @@ def prompt_of(rank):
 
 def main():
     rank, world, idfile, outfile = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
-    from rew_b200 import _lib, api
+    from rew_b200 import _lib, api, weights as W
     print("rank", rank, "starting", flush=True)
     _lib.init(rank)
     if rank == 0:
@@ -96,8 +96,33 @@ def main():
     ids, last = sess.decode(4, want_logits=True)
     assert np.array_equal(ids, ids2) and np.array_equal(last, last2), "peer-heap and NCCL exchange disagree (decode)"
     print("rank", rank, "done", flush=True)
-    np.savez(outfile, nxt=nxt, logits=logits, ids=ids, last=last)
     sess.free()
+    # One MoE layer at the DeepSeek-V2-Lite width (d_model 2048, 64 routed experts of width 1408, top-6, two shared
+    # experts): 32 experts per rank, real group sizes in the grouped GEMMs and real slot counts in the exchange.
+    # Every rank holds the same 8 sequences' worth of weights; rank 0 also runs them unsharded: the expert-parallel
+    # run must return the same bits (a token adds its experts' results in fixed order wherever they were computed).
+    wide = dict(vocab=1024, d_model=2048, n_layers=2, n_heads=16, n_kv_heads=16, head_dim=128, ffn=2048, max_seq=128,
+                theta=10000.0, eps=1e-6, n_routed=64, n_shared=2, top_k=6, moe_ffn=1408, first_dense=2048,
+                dtype=_lib.BF16, mask_kind=1)
+    full = W.ModelConfig(**wide)
+    t = [W.bf16_round(a) if a.ndim == 2 else a for a in W.init_weights(full, seed=13, std=0.03, trivial_affine=False)]
+    wmodel = api.CausalLM(W.ModelConfig(**wide, ep_rank=rank, ep_size=world)).load(t)
+    wprompts = np.random.default_rng(14).integers(0, 1024, size=(world, 8, 40)).astype(np.int32)
+    ws = wmodel.session(8, 64)
+    wids, wlogits = ws.generate(wprompts[rank], 5, want_logits=True)
+    ws.free()
+    wmodel.free()
+    extra = {}
+    if rank == 0:
+        ref = api.CausalLM(full).load(t)
+        for r in range(world):
+            rs = ref.session(8, 64)
+            rids, rlogits = rs.generate(wprompts[r], 5, want_logits=True)
+            rs.free()
+            extra["wide_ref_ids%d" % r], extra["wide_ref_logits%d" % r] = rids, rlogits
+        ref.free()
+    print("rank", rank, "wide done", flush=True)
+    np.savez(outfile, nxt=nxt, logits=logits, ids=ids, last=last, wide_ids=wids, wide_logits=wlogits, **extra)
     api.comm_destroy()
 
 

@@ -40,7 +40,7 @@ def test_ep2_forward_and_decode_match_oracle(orc):
         codes = []
         for p in procs:
             try:
-                codes.append(p.wait(timeout=120))
+                codes.append(p.wait(timeout=300))
             except subprocess.TimeoutExpired:
                 codes.append("timeout")
         for p in procs:
@@ -53,6 +53,10 @@ def test_ep2_forward_and_decode_match_oracle(orc):
             f.close()
         assert codes == [0, 0], "rank exit codes %r\n--- rank 0 ---\n%s\n--- rank 1 ---\n%s" % (codes, tails[0], tails[1])
         outs = [dict(np.load(os.path.join(d, "out%d.npz" % r))) for r in range(2)]
+    # one MoE layer at the DeepSeek-V2-Lite width: the expert-parallel ranks against the unsharded model, bit for bit
+    for r in range(2):
+        assert np.array_equal(outs[r]["wide_ids"], outs[0]["wide_ref_ids%d" % r])
+        assert np.array_equal(outs[r]["wide_logits"], outs[0]["wide_ref_logits%d" % r])
     full = ep_worker.config(0, 1)
     t = ep_worker.weights(full)
     for r in range(2):
