@@ -25,11 +25,13 @@ def _run(model, prompt, steps):
     return ids, logits
 
 
-@pytest.mark.parametrize("shape", ["llama3_8b", "deepseek_v2_lite", "llama3_8b_nf4"])
+@pytest.mark.parametrize("shape", ["llama3_8b", "deepseek_v2_lite", "llama3_8b_nf4", "llama3_8b_as_written"])
 def test_full_size_decode_is_independent_of_batch_position(rb, shape):
-    cfg = getattr(W, shape.replace("_nf4", ""))()
+    cfg = getattr(W, shape.replace("_nf4", "").replace("_as_written", ""))()
     if shape.endswith("_nf4"):
         cfg.weight_quant = 1      # NF4 block weights: the quantised GEMV for the decode steps, expanded codes for the prefill
+    if shape.endswith("_as_written"):
+        cfg.mask_kind, cfg.norm_kind = 0, 1   # the reference as written: makeCausalMask's direction, LayerNorm in the layers
     B, S, steps = (64, 48, 6) if shape == "deepseek_v2_lite" else (32, 96, 6)
     cfg.max_seq = 256
     model = rb.CausalLM(cfg).init_random(seed=21, std=0.02)
