@@ -42,6 +42,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 SETTLE_S = 0.25            # untimed decode steps run for at least this long after the prefill (see run_model)
 SETTLE_MAX_STEPS = 256
+E2E_LONG_STEPS = 256       # decode steps of the second end-to-end call (fits the session: max_len has SETTLE_MAX_STEPS of slack)
 sys.path.insert(0, ROOT)
 
 METRIC = "decode_tokens_per_s"
@@ -438,6 +439,14 @@ def run_model(args, name, rank, local_rank, world, pg, K, Wm, with_e2e, with_pro
         out["e2e"] = {"value": tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": prompt.nbytes / K,
                       "d2h_bytes_per_step": ids.nbytes / K,
                       "what": "one generate() call: prefill of the prompt + %d decode steps, ids host->device->host" % K}
+        if K < E2E_LONG_STEPS:
+            # the same call with enough decode steps to show the decode loop's host overhead (with the driver's
+            # 20 steps the call is four fifths prefill)
+            t0 = time.perf_counter()
+            ids = sess.generate(prompt, E2E_LONG_STEPS)
+            long_s = max_over_ranks(time.perf_counter() - t0)
+            out["e2e_long"] = {"value": B * E2E_LONG_STEPS * mult / long_s, "unit": UNIT, "decode_steps": E2E_LONG_STEPS,
+                               "h2d_bytes_per_step": prompt.nbytes / E2E_LONG_STEPS, "d2h_bytes_per_step": ids.nbytes / E2E_LONG_STEPS}
 
     # ---- rooflines: whole step (weights + KV read once per step per GPU), and the Linear launches alone
     peak, which = measured_peaks()
@@ -644,6 +653,8 @@ def main():
         "prefill": {"tokens_per_s": r["prefill_tokens_per_s"], "ms": r["prefill_ms"]},
         "e2e": r["e2e"], "gpu_launches": r["launches"], "clocks": r["clocks"], "roofline": roofline,
     }
+    if "e2e_long" in r:
+        line["e2e_long"] = r["e2e_long"]
     line["settle"] = ("%d more untimed decode steps after the %d warm-up steps: the SM clock stays capped for ~0.15 s "
                                 "after the prefill's power-capped burst, so the untimed part lasts %.2f s" % (r["settle_steps"], Wm, args.settle_seconds))
     if "trace_ms" in r:
