@@ -167,3 +167,50 @@ proc generateB200*(sess: ptr RewbSession; tokenIds: seq[int32]; maxNewTokens: in
                               addr result[0], nil)
   let cut = result.find(-1'i32)
   if cut >= 0: result.setLen(cut)
+
+type
+  RoutedExpertsB200* = object
+    ## the routed experts of one DeepSeekMoE layer in the backend's fused layout
+    ## (src/rew/models/deepseek.nim:74-78,122-145)
+    h: ptr RewbExperts
+
+proc `=destroy`*(e: RoutedExpertsB200) {.raises: [].} =
+  if e.h != nil: rewb200_experts_free(e.h)
+
+proc initRoutedExpertsB200*(d: Device; gateW, gateB, upW, upB, downW, downB: openArray[Tensor]): RoutedExpertsB200 =
+  ## one weight / bias tensor per expert, [in, out] as rew.nn.Linear keeps them
+  var gw = gateW.mapIt(rawOf(it))
+  var gb = gateB.mapIt(rawOf(it))
+  var uw = upW.mapIt(rawOf(it))
+  var ub = upB.mapIt(rawOf(it))
+  var dw = downW.mapIt(rawOf(it))
+  var db = downB.mapIt(rawOf(it))
+  check rewb200_experts_create(cint(d.ordinal), cint(gw.len), addr gw[0], addr gb[0], addr uw[0], addr ub[0], addr dw[0],
+                               addr db[0], addr result.h)
+
+proc moeExpertsB200*(e: RoutedExpertsB200; x, weights, indices: Tensor): Tensor =
+  ## DeepSeekMoE.forward after the router (src/rew/models/deepseek.nim:140-144); weights / indices as moeRouteB200 returns them
+  one(proc (o: ptr ptr RewbBuffer): cint = rewb200_moe_experts(e.h, rawOf(x), rawOf(weights), rawOf(indices), o), x)
+
+type
+  SamplerB200* = object
+    ## GenerationConfig + Key of generate (src/rew/infer/generate.nim:12-58,231-265) held on the device
+    h: ptr RewbSampler
+
+proc `=destroy`*(s: SamplerB200) {.raises: [].} =
+  if s.h != nil: rewb200_sampler_free(s.h)
+
+proc initSamplerB200*(d: Device; batch, vocab, maxTokens: int; temperature = 1.0'f32; topK = 50; topP = 1.0'f32;
+                      minP = 0.0'f32; repetitionPenalty = 1.0'f32; doSample = true; seeds: seq[uint64] = @[]): SamplerB200 =
+  check rewb200_sampler_create(cint(d.ordinal), cint(batch), cint(vocab), cint(maxTokens), cfloat(temperature), cint(topK),
+                               cfloat(topP), cfloat(minP), cfloat(repetitionPenalty), cint(ord(doSample)),
+                               (if seeds.len > 0: unsafeAddr seeds[0] else: nil), addr result.h)
+
+proc observe*(s: SamplerB200; ids: seq[int32]; nPerRow: int) =
+  ## the prompt (or any tokens) enters the repetition-penalty history
+  check rewb200_sampler_observe(s.h, unsafeAddr ids[0], cint(nPerRow))
+
+proc lmHeadSampleB200*(x, lmW, lmB: Tensor; s: var SamplerB200; batch: int): seq[int32] =
+  ## lmHead + lastLogits + sampleGreedy / sampleTopK / sampleTopP (src/rew/infer/generate.nim:92-190) in one call
+  result = newSeq[int32](batch)
+  check rewb200_lmhead_sample(rawOf(x), rawOf(lmW), rawOf(lmB), s.h, addr result[0], nil)
